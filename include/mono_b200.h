@@ -1,0 +1,283 @@
+/*
+ * mono_b200: C ABI of the sm_100a decoder-layer kernel library.
+ *
+ * The reference (yuychang/sgl-amd-mono) dispatches "pointer-only" launches from its
+ * host runners: torch tensors are checked in Python and the kernel receives raw
+ * device pointers, a few scalars and a stream (glm53/gfx950/runner.py:240-321,
+ * kernel ABI glm53/gfx950/kernel.py:369-412; minimax_m31/runner.py:145-167).  Every
+ * entry point below is what a binding for that dispatch level binds: plain structs
+ * of device pointers and sizes, a stream handle, an int status.  No entry point
+ * blocks the host, allocates, or synchronises unless it says so.
+ *
+ * Status: 0 = ok; > 0 = a CUDA error code from the runtime; < 0 = MONO_E_* (bad
+ * argument).  mono_last_error() returns the message of the last failure on the
+ * calling thread.
+ */
+#ifndef MONO_B200_H
+#define MONO_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MONO_ABI_VERSION 1
+
+/* Cache geometry (what SGLang owns and hands over; glm53/gfx950/kernel.py:534-548,
+ * 2049-2100).  A KV page holds 64 tokens: 64 x 576 E4M3 values (512 latent + 64
+ * rope) followed by 64 f32 per-token scales.  An index page holds 64 x 64 bytes of
+ * packed E2M1 (128 dims) followed by 64 x 4 E8M0 codes (one per 32 dims). */
+#define MONO_PAGE_TOKENS 64
+#define MONO_KV_DIM 576
+#define MONO_KV_PAGE_BYTES (64 * 576 + 64 * 4)
+#define MONO_IDX_DIM 128
+#define MONO_IDX_PAGE_BYTES (64 * 64 + 64 * 4)
+#define MONO_MAX_ROWS 16 /* rows of one decode / verify step */
+
+/* Guard words: int32[MONO_GUARD_WORDS] per rank (common/guard.py:59-60,100-241). */
+#define MONO_GUARD_WORDS 16
+#define MONO_GUARD_EPOCH 0
+#define MONO_ERR_DEADLINE 3 /* site + 1 of the wait that ran out */
+#define MONO_ERR_PEER 4     /* rank + 1 of a peer that raised its flag */
+#define MONO_ERR_ARG 5      /* site + 1 of a device-side argument check */
+#define MONO_GUARD_FLAGS 8  /* flag word of rank r at MONO_GUARD_FLAGS + r */
+
+#define MONO_E_ARG (-1)
+#define MONO_E_NOT_BUILT (-2)
+#define MONO_E_DRIVER (-3)
+#define MONO_E_GUARD (-4)
+
+int mono_abi_version(void);
+const char* mono_last_error(void);
+/* SM count of the current device (the grid every persistent launch is sized by;
+ * reference: common/plan.py:23-25 BLOCKS = 256 CUs). */
+int mono_sm_count(void);
+
+/* ---- guard (common/guard.py:100-241; reads replace the reference's process kill) */
+/* Copies the three error words to out[3] = {deadline, peer, arg} with a blocking
+ * device-to-host copy on `stream`.  Returns MONO_E_GUARD if any is non-zero. */
+int mono_guard_read(const int32_t* guard_words, int32_t out[3], void* stream);
+
+/* ---- TMA descriptors ----------------------------------------------------------
+ * A weight tensor read in place: `outer` matrices of `rows` x `inner_bytes`
+ * (row-major, K contiguous), rows `row_stride_bytes` apart, matrices
+ * `outer_stride_bytes` apart.  The descriptor loads 128-byte x 128-row boxes with
+ * the 128-byte swizzle.  Replaces the reference's one-time tile repacks
+ * (glm53/gfx950/packing.py:29-133): weights stay in SGLang's layout. */
+typedef struct __attribute__((aligned(64))) mono_tmap {
+    unsigned char opaque[128];
+} mono_tmap_t;
+int mono_tmap_encode(mono_tmap_t* out, const void* base, uint64_t inner_bytes, uint64_t rows,
+                     uint64_t outer, uint64_t row_stride_bytes, uint64_t outer_stride_bytes);
+
+/* ---- activation staging (glm53/gfx950/kernel.py:1367-1414 RMSNorm staging,
+ * :1440-1466 per-128 FP8 / per-32 MXFP8 quantisation) ----------------------------
+ * Activation planes feed the GEMV B operand: uint8 [planes][16][ld] plus scales.
+ *   MONO_ACT_BF16   1 plane of bf16 values (ld = 2K bytes), no scales
+ *   MONO_ACT_A8     1 plane E4M3, f32 scale amax/448 per 128 (kernel.py:1440-1450)
+ *   MONO_ACT_HILO   2 planes E4M3 (hi, lo) of bf16 values, f32 power-of-two scale per
+ *                   128: the bf16 activation exactly split for FP8 MMAs
+ *   MONO_ACT_MX8    1 plane E4M3, E8M0 code per 32 (kernel.py:1452-1466), values of
+ *                   each group of 8 stored as k0 k2 k4 k6 k1 k3 k5 k7 (the order the
+ *                   MXFP4 weight nibbles unpack in)
+ * Rows >= `rows` of every plane stay zero. */
+enum { MONO_ACT_BF16 = 0, MONO_ACT_A8 = 1, MONO_ACT_HILO = 2, MONO_ACT_MX8 = 3 };
+
+typedef struct mono_act_prep_args {
+    int rows, k;
+    /* input: exactly one of src_bf16 [rows][k] or src_f32 [nsum][16][src_ld] (summed
+     * over nsum in order) */
+    const void* src_bf16;
+    const float* src_f32;
+    int nsum, src_ld;
+    long src_sum_stride;
+    const void* gamma_bf16; /* RMSNorm weight [k] or NULL for no norm */
+    float eps;
+    int round_bf16; /* round the (normalised) value to bf16 before quantising */
+    /* outputs (any may be NULL) */
+    int fmt;            /* MONO_ACT_* of `planes` */
+    uint8_t* planes;    /* [planes][16][ld] */
+    long plane_stride;  /* bytes between planes */
+    int ld;             /* bytes per row */
+    float* scale_f32;   /* [16][scale_ld] */
+    uint8_t* scale_e8;  /* [16][scale_ld] */
+    int scale_ld;
+    void* out_bf16;     /* optional second output: bf16 [16][k] plain */
+} mono_act_prep_args;
+int mono_act_prep_launch(const mono_act_prep_args* a, void* stream);
+
+/* ---- weight-streaming GEMV (glm53/gfx950/kernel.py:1061-1172 mma_units; q_a|kv_a
+ * :1781-1970, q_b :2183, W_UV :3975-4123, o_proj :4125, experts :4352-5187;
+ * minimax_m31/a16w4.py for MXFP4) -----------------------------------------------
+ * One persistent launch walks the tasks of up to MONO_GEMV_MAX_JOBS jobs.  A task
+ * is one 128-row block of a weight matrix over one K range (or, for
+ * MONO_JOB_EXPERT_DOWN, over a strided group of the step's experts); partial sums
+ * go to f32 buffers that the next stage adds in a fixed order. */
+#define MONO_GEMV_MAX_JOBS 4
+enum { MONO_W_FP8 = 0, MONO_W_MXFP4 = 1, MONO_W_BF16 = 2 };
+enum { MONO_JOB_DENSE = 0, MONO_JOB_EXPERT_UP = 1, MONO_JOB_EXPERT_DOWN = 2 };
+
+typedef struct mono_gemv_job {
+    mono_tmap_t tmap;
+    int mode;       /* MONO_JOB_* */
+    int n_rows;     /* rows of W this job covers (per matrix) */
+    int k_tiles;    /* K in 128-byte tiles (FP8: 128 k, BF16: 64 k, MXFP4: 256 k) */
+    int split_tiles;/* dense / up: tiles per K split (multiple of 4) */
+    int nsplit;     /* dense / up: K splits; down: expert groups */
+    int row_off;    /* first row inside each matrix */
+    int rb_per_mat; /* dense: row blocks per matrix when the job spans n_mats matrices
+                       (per-head W_UV; n_rows = 128 * rb_per_mat), else 0 */
+    int n_mats;     /* matrices of such a job, else 0 */
+    /* weight scales */
+    const float* wscale_f32;  /* FP8: [mat][row block][wscale_ld] */
+    const uint8_t* wscale_e8; /* MXFP4: [mat][row][wscale_ld] */
+    long wscale_mat_stride;   /* elements between matrices */
+    int wscale_ld;
+    /* activations */
+    const uint8_t* act; /* planes [planes][16][act_ld] */
+    int planes;
+    long act_plane_stride;
+    int act_ld;
+    long act_seg_stride; /* bytes between per-matrix (dense rb_per_mat) / per-expert
+                            (down) activation sets */
+    const float* ascale_f32;
+    const uint8_t* ascale_e8;
+    int ascale_ld;
+    long ascale_seg_stride; /* elements */
+    const float* coef; /* down: [slot][16] route coefficient, NULL = 1 */
+    /* experts of this step (device): list[0..*n_expert) */
+    const int32_t* expert_list;
+    const int32_t* n_expert;
+    int max_expert; /* upper bound of *n_expert (grid sizing only) */
+    /* output f32: dense [nsplit][16][out_ld]; up [slot][nsplit][16][out_ld];
+     * down [nsplit][16][out_ld] */
+    float* out;
+    int out_ld;
+    long out_split_stride; /* elements */
+} mono_gemv_job;
+
+typedef struct mono_gemv_args {
+    int njobs;
+    int rows;  /* live rows of the step (1..16) */
+    int wkind; /* MONO_W_*: all jobs of one launch share it */
+    int32_t* guard;
+    int max_ctas; /* 0 = one per SM */
+    mono_gemv_job job[MONO_GEMV_MAX_JOBS];
+} mono_gemv_args;
+int mono_gemv_launch(const mono_gemv_args* a, void* stream);
+
+/* ---- small matrices on CUDA cores (router logits: minimax_m31/ffn.py:601-649 fp32
+ * router; glm53/gfx950/kernel.py:4199-4330 bf16 router; indexer head weights) ------
+ * out[r][n] = out_scale * sum_k x[r][k] * w[n][k]; x bf16 [16][k]; w f32 or bf16 [n][k]. */
+typedef struct mono_rowdot_args {
+    int rows, n, k;
+    const void* w;
+    int w_is_f32;
+    const void* x_bf16;
+    float* out;
+    int out_ld;
+    float out_scale;
+} mono_rowdot_args;
+int mono_rowdot_launch(const mono_rowdot_args* a, void* stream);
+
+/* ---- router (glm53/gfx950/kernel.py:1575-1629 route_top8, :4199-4330;
+ * minimax_m31/ffn.py:601-723) ----------------------------------------------------
+ * Sums the router-logit partials, applies sigmoid, picks top_k by (score + bias)
+ * with ties to the lower expert id, writes ids / weights, and builds the step's
+ * distinct expert list (ascending id) with the per-(slot,row) route coefficients. */
+typedef struct mono_route_args {
+    int rows, n_experts, top_k;
+    float route_scale;
+    const float* logits; /* [nsum][16][ld] partial sums */
+    int nsum, ld;
+    long sum_stride;
+    const float* bias;      /* [n_experts] or NULL */
+    const int64_t* slots;   /* [rows] or NULL; < 0 = pad row (routes nowhere) */
+    int32_t* ids;           /* out [16][top_k] (-1 on pad rows) */
+    float* weights;         /* out [16][top_k] */
+    float* scores;          /* out [16][n_experts] sigmoid scores (parity witness) */
+    int32_t* expert_list;   /* out [rows*top_k] */
+    int32_t* n_expert;      /* out [1] */
+    float* coef;            /* out [rows*top_k][16] */
+} mono_route_args;
+int mono_route_launch(const mono_route_args* a, void* stream);
+
+/* ---- expert activation (glm53/gfx950/kernel.py:4396-4415 SiLU, :5061-5064 mid
+ * re-quantisation; minimax_m31/ffn.py:849-852) -----------------------------------
+ * For every (expert slot, row): adds the up/gate partial sums, mid = silu(g) * u,
+ * and stages mid as the down projection's activation planes. */
+typedef struct mono_mid_args {
+    int rows, inter; /* inter = local intermediate size */
+    const float* up;  /* [slot][nsum][16][2*inter] */
+    int nsum;
+    const int32_t* n_slot; /* device count of slots, or NULL -> max_slot */
+    int max_slot;
+    int fmt;          /* MONO_ACT_A8 | MONO_ACT_MX8 | MONO_ACT_BF16 */
+    int round_bf16;
+    uint8_t* planes;  /* [slot][16][ld] */
+    int ld;
+    float* scale_f32; /* [slot][16][scale_ld] */
+    uint8_t* scale_e8;
+    int scale_ld;
+} mono_mid_args;
+int mono_mid_launch(const mono_mid_args* a, void* stream);
+
+/* ---- sparse MLA decode attention (glm53/gfx950/kernel.py:3638-3973 split,
+ * :3975-4075 merge; operator level of BASELINE config 2) --------------------------
+ * q bf16 [rows][heads][576]; kv_pages uint8 [pages][MONO_KV_PAGE_BYTES]; topk int32
+ * [rows][topk_ld] global slots (-1 = none); out bf16 [rows][heads][512].
+ * scratch: mono_sparse_mla_scratch_bytes(rows, heads, topk). */
+typedef struct mono_sparse_mla_args {
+    int rows, heads, topk, topk_ld;
+    float sm_scale;
+    const void* q;
+    const uint8_t* kv_pages;
+    int64_t n_pages;
+    const int32_t* topk_slots;
+    void* out;
+    void* scratch;
+    int32_t* guard;
+} mono_sparse_mla_args;
+size_t mono_sparse_mla_scratch_bytes(int rows, int heads, int topk);
+int mono_sparse_mla_launch(const mono_sparse_mla_args* a, void* stream);
+
+/* ---- partial-sum reduction + all-reduce + residual (glm53/gfx950/kernel.py:1631-1688
+ * peer_reduce, :4125-4197, :5175-5185) -------------------------------------------
+ * partial = sum over nsum slices (in order) of f32 [16][ld]; rounded to bf16; with
+ * world > 1 pushed as (bf16 pair, tag) 8-byte words into every peer's buffer at
+ * [parity][rank][row][col/2], polled locally until all tags match or the deadline
+ * runs out, summed in rank order in f32; + residual; out bf16 [rows][n]. */
+typedef struct mono_reduce_args {
+    int rows, n;
+    const float* partial;
+    int nsum, ld;
+    long sum_stride;
+    const void* residual; /* bf16 [rows][n] or NULL */
+    const int64_t* slots; /* [rows] or NULL: pad rows (slot < 0) contribute zeros */
+    void* out;            /* bf16 [rows][n] */
+    /* tensor parallel */
+    int world, rank;
+    const uint64_t* peer_ptrs; /* device array [world]: base of every rank's region */
+    uint32_t tag;              /* launch tag; 0 = take epoch * 256 + site + 1 and parity =
+                                  epoch & 1 from guard word 0 (what a CUDA graph replays) */
+    int parity;
+    uint64_t deadline_ns;
+    int site;
+    int32_t* guard;
+    const uint64_t* peer_guards; /* device array [world]: every rank's guard words, or NULL */
+} mono_reduce_args;
+size_t mono_reduce_peer_bytes(int rows, int n, int world);
+int mono_reduce_launch(const mono_reduce_args* a, void* stream);
+/* Adds 1 to the epoch word on the device (glm53/gfx950/runner.py:209-210 advance_step). */
+int mono_epoch_advance_launch(int32_t* guard, void* stream);
+
+/* sizeof() of the argument structs, by index (0 gemv_job, 1 gemv_args, 2 act_prep,
+ * 3 route, 4 mid, 5 sparse_mla, 6 reduce, 7 rowdot, ...): lets a binding check its mirror. */
+size_t mono_struct_size(int which);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MONO_B200_H */

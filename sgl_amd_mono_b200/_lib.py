@@ -1,0 +1,159 @@
+"""ctypes binding of ``libmono_b200.so`` (the declarations of ``include/mono_b200.h``).
+
+The reference's runners hand raw pointers to JIT-compiled launchers
+(``glm53/gfx950/runner.py:240-321``); this module is the same seam over a C ABI.
+There is no fallback: if the library is missing or does not match the header, the
+import of a runner raises and the spec refuses to attach.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libmono_b200.so"
+
+MAX_ROWS = 16
+GUARD_WORDS = 16
+ERR_DEADLINE, ERR_PEER, ERR_ARG, GUARD_FLAGS = 3, 4, 5, 8
+ACT_BF16, ACT_A8, ACT_HILO, ACT_MX8 = 0, 1, 2, 3
+W_FP8, W_MXFP4, W_BF16 = 0, 1, 2
+JOB_DENSE, JOB_EXPERT_UP, JOB_EXPERT_DOWN = 0, 1, 2
+GEMV_MAX_JOBS = 4
+
+vp, i32, i64, f32, u32, u64 = C.c_void_p, C.c_int, C.c_long, C.c_float, C.c_uint32, C.c_uint64
+
+
+class Tmap(C.Structure):
+    _fields_ = [("opaque", C.c_ubyte * 128)]
+
+
+class GemvJob(C.Structure):
+    _fields_ = [
+        ("tmap", Tmap),
+        ("mode", i32), ("n_rows", i32), ("k_tiles", i32), ("split_tiles", i32), ("nsplit", i32),
+        ("row_off", i32), ("rb_per_mat", i32), ("n_mats", i32),
+        ("wscale_f32", vp), ("wscale_e8", vp), ("wscale_mat_stride", i64), ("wscale_ld", i32),
+        ("act", vp), ("planes", i32), ("act_plane_stride", i64), ("act_ld", i32), ("act_seg_stride", i64),
+        ("ascale_f32", vp), ("ascale_e8", vp), ("ascale_ld", i32), ("ascale_seg_stride", i64),
+        ("coef", vp), ("expert_list", vp), ("n_expert", vp), ("max_expert", i32),
+        ("out", vp), ("out_ld", i32), ("out_split_stride", i64),
+    ]
+
+
+class GemvArgs(C.Structure):
+    _fields_ = [
+        ("njobs", i32), ("rows", i32), ("wkind", i32), ("guard", vp), ("max_ctas", i32),
+        ("_pad", C.c_ubyte * 36),  # the job array is 64-byte aligned in C
+        ("job", GemvJob * GEMV_MAX_JOBS),
+    ]
+
+
+class ActPrepArgs(C.Structure):
+    _fields_ = [
+        ("rows", i32), ("k", i32), ("src_bf16", vp), ("src_f32", vp), ("nsum", i32), ("src_ld", i32),
+        ("src_sum_stride", i64), ("gamma_bf16", vp), ("eps", f32), ("round_bf16", i32),
+        ("fmt", i32), ("planes", vp), ("plane_stride", i64), ("ld", i32), ("scale_f32", vp),
+        ("scale_e8", vp), ("scale_ld", i32), ("out_bf16", vp),
+    ]
+
+
+class RouteArgs(C.Structure):
+    _fields_ = [
+        ("rows", i32), ("n_experts", i32), ("top_k", i32), ("route_scale", f32),
+        ("logits", vp), ("nsum", i32), ("ld", i32), ("sum_stride", i64), ("bias", vp), ("slots", vp),
+        ("ids", vp), ("weights", vp), ("scores", vp), ("expert_list", vp), ("n_expert", vp), ("coef", vp),
+    ]
+
+
+class MidArgs(C.Structure):
+    _fields_ = [
+        ("rows", i32), ("inter", i32), ("up", vp), ("nsum", i32), ("n_slot", vp), ("max_slot", i32),
+        ("fmt", i32), ("round_bf16", i32), ("planes", vp), ("ld", i32), ("scale_f32", vp),
+        ("scale_e8", vp), ("scale_ld", i32),
+    ]
+
+
+class SparseMlaArgs(C.Structure):
+    _fields_ = [
+        ("rows", i32), ("heads", i32), ("topk", i32), ("topk_ld", i32), ("sm_scale", f32),
+        ("q", vp), ("kv_pages", vp), ("n_pages", C.c_int64), ("topk_slots", vp), ("out", vp),
+        ("scratch", vp), ("guard", vp),
+    ]
+
+
+class ReduceArgs(C.Structure):
+    _fields_ = [
+        ("rows", i32), ("n", i32), ("partial", vp), ("nsum", i32), ("ld", i32), ("sum_stride", i64),
+        ("residual", vp), ("slots", vp), ("out", vp), ("world", i32), ("rank", i32), ("peer_ptrs", vp),
+        ("tag", u32), ("parity", i32), ("deadline_ns", u64), ("site", i32), ("guard", vp),
+        ("peer_guards", vp),
+    ]
+
+
+class RowdotArgs(C.Structure):
+    _fields_ = [
+        ("rows", i32), ("n", i32), ("k", i32), ("w", vp), ("w_is_f32", i32), ("x_bf16", vp),
+        ("out", vp), ("out_ld", i32), ("out_scale", f32),
+    ]
+
+
+_STRUCTS = [GemvJob, GemvArgs, ActPrepArgs, RouteArgs, MidArgs, SparseMlaArgs, ReduceArgs, RowdotArgs]
+
+# every symbol include/mono_b200.h declares: name -> (restype, argtypes)
+SYMBOLS = {
+    "mono_abi_version": (i32, []),
+    "mono_last_error": (C.c_char_p, []),
+    "mono_sm_count": (i32, []),
+    "mono_guard_read": (i32, [vp, C.POINTER(C.c_int32 * 3), vp]),
+    "mono_tmap_encode": (i32, [C.POINTER(Tmap), vp, u64, u64, u64, u64, u64]),
+    "mono_act_prep_launch": (i32, [C.POINTER(ActPrepArgs), vp]),
+    "mono_gemv_launch": (i32, [C.POINTER(GemvArgs), vp]),
+    "mono_rowdot_launch": (i32, [C.POINTER(RowdotArgs), vp]),
+    "mono_route_launch": (i32, [C.POINTER(RouteArgs), vp]),
+    "mono_mid_launch": (i32, [C.POINTER(MidArgs), vp]),
+    "mono_sparse_mla_scratch_bytes": (C.c_size_t, [i32, i32, i32]),
+    "mono_sparse_mla_launch": (i32, [C.POINTER(SparseMlaArgs), vp]),
+    "mono_reduce_peer_bytes": (C.c_size_t, [i32, i32, i32]),
+    "mono_reduce_launch": (i32, [C.POINTER(ReduceArgs), vp]),
+    "mono_epoch_advance_launch": (i32, [vp, vp]),
+    "mono_struct_size": (C.c_size_t, [i32]),
+}
+
+
+class MonoLibraryError(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def load():
+    """The loaded library; raises MonoLibraryError when it is missing or mismatched."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise MonoLibraryError(
+            f"{LIB_PATH} is not built: run `python -m sgl_amd_mono_b200.build` "
+            "(there is no CPU or eager fallback for the monokernel path)"
+        )
+    lib = C.CDLL(str(LIB_PATH))
+    for name, (res, args) in SYMBOLS.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError as e:
+            raise MonoLibraryError(f"{LIB_PATH} does not export {name}") from e
+        fn.restype, fn.argtypes = res, args
+    for i, st in enumerate(_STRUCTS):
+        want = lib.mono_struct_size(i)
+        if want != C.sizeof(st):
+            raise MonoLibraryError(f"{st.__name__}: binding has {C.sizeof(st)} bytes, library has {want}")
+    _lib = lib
+    return lib
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        msg = load().mono_last_error().decode(errors="replace")
+        raise RuntimeError(f"{what} failed with status {rc}: {msg}")

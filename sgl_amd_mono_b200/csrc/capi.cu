@@ -1,0 +1,118 @@
+// Host-side plumbing of the C ABI: error strings, device queries, guard reads and
+// TMA descriptor encoding.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "mono_common.cuh"
+
+static thread_local char g_err[512] = "";
+
+void mono_set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+extern "C" int mono_abi_version(void) { return MONO_ABI_VERSION; }
+extern "C" const char* mono_last_error(void) { return g_err; }
+
+extern "C" int mono_sm_count(void) {
+    static thread_local int cached_dev = -1, cached = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+        mono_set_error("mono_sm_count: no CUDA device");
+        return -1;
+    }
+    if (dev != cached_dev) {
+        if (cudaDeviceGetAttribute(&cached, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
+        cached_dev = dev;
+    }
+    return cached;
+}
+
+extern "C" int mono_guard_read(const int32_t* guard_words, int32_t out[3], void* stream) {
+    if (!guard_words || !out) {
+        mono_set_error("mono_guard_read: null pointer");
+        return MONO_E_ARG;
+    }
+    int32_t w[MONO_GUARD_WORDS];
+    cudaError_t e = cudaMemcpyAsync(w, guard_words, sizeof(w), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+    if (e != cudaSuccess) {
+        mono_set_error("mono_guard_read: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    out[0] = w[MONO_ERR_DEADLINE];
+    out[1] = w[MONO_ERR_PEER];
+    out[2] = w[MONO_ERR_ARG];
+    if (out[0] | out[1] | out[2]) {
+        mono_set_error("guard: deadline site %d, peer %d, arg site %d", out[0] - 1, out[1] - 1, out[2] - 1);
+        return MONO_E_GUARD;
+    }
+    return 0;
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no -lcuda link).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+extern "C" int mono_tmap_encode(mono_tmap_t* out, const void* base, uint64_t inner_bytes, uint64_t rows,
+                                uint64_t outer, uint64_t row_stride_bytes, uint64_t outer_stride_bytes) {
+    static_assert(sizeof(CUtensorMap) == sizeof(mono_tmap_t), "descriptor size");
+    if (!out || !base || inner_bytes == 0 || rows == 0 || outer == 0) {
+        mono_set_error("mono_tmap_encode: null or empty tensor");
+        return MONO_E_ARG;
+    }
+    if ((reinterpret_cast<uintptr_t>(base) & 15) || (row_stride_bytes & 15) || (outer_stride_bytes & 15) ||
+        (inner_bytes & 15)) {
+        mono_set_error("mono_tmap_encode: base, strides and row bytes must be multiples of 16 (base %p, row stride %llu)",
+                       base, (unsigned long long)row_stride_bytes);
+        return MONO_E_ARG;
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        mono_set_error("mono_tmap_encode: cuTensorMapEncodeTiled not available from the driver");
+        return MONO_E_DRIVER;
+    }
+    cuuint64_t dims[3] = {inner_bytes, rows, outer};
+    cuuint64_t strides[2] = {row_stride_bytes, outer > 1 ? outer_stride_bytes : row_stride_bytes * rows};
+    cuuint32_t box[3] = {128, 128, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(reinterpret_cast<CUtensorMap*>(out), CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims,
+                    strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        mono_set_error("mono_tmap_encode: cuTensorMapEncodeTiled failed with %d", (int)r);
+        return MONO_E_DRIVER;
+    }
+    return 0;
+}
+
+extern "C" size_t mono_struct_size(int which) {
+    switch (which) {
+        case 0: return sizeof(mono_gemv_job);
+        case 1: return sizeof(mono_gemv_args);
+        case 2: return sizeof(mono_act_prep_args);
+        case 3: return sizeof(mono_route_args);
+        case 4: return sizeof(mono_mid_args);
+        case 5: return sizeof(mono_sparse_mla_args);
+        case 6: return sizeof(mono_reduce_args);
+        case 7: return sizeof(mono_rowdot_args);
+        default: return 0;
+    }
+}

@@ -1,0 +1,265 @@
+// Sparse MLA decode attention over the selected KV slots (the operator of BASELINE
+// config 2, and the attention stage of the layer).
+//
+// Reference counterpart: glm53/gfx950/kernel.py:3638-3973 (split: 64 keys per task,
+// split-local max / sum, p rounded to bf16 before P.V, bf16 partial accumulator) and
+// :3975-4075 (merge: w_j = e^(m_j - M) / sum_j l_j e^(m_j - M)).
+//
+// sm_100a design: a task is (row, 64-key split).  The CTA gathers the 64 cache rows
+// (576 E4M3 bytes + one f32 scale each) with 16-byte loads that are all in flight at
+// once, widens them to bf16 in shared memory, and runs Q.K^T and P.V on bf16 warp
+// MMAs for 16 heads at a time, reusing the key tile for every head group.  The work
+// is bound by the latency of the gather, not by bytes or flops (1.2 MB per row).
+#include "mono_common.cuh"
+
+extern void mono_set_error(const char* fmt, ...);
+
+namespace mono {
+
+constexpr int kSplit = 64;             // keys per task
+constexpr int kKvPitch = kKvDim + 8;   // bf16 elements per staged key row (1168 B: conflict-free ldmatrix)
+constexpr int kPPitch = kSplit + 8;
+constexpr int kMlaThreads = 256;
+constexpr int kHeadGroup = 16;
+
+struct MlaSmem {
+    __nv_bfloat16 kv[kSplit][kKvPitch];
+    __nv_bfloat16 q[kHeadGroup][kKvPitch];
+    __nv_bfloat16 p[kHeadGroup][kPPitch];
+    float s[kHeadGroup][kSplit];
+    float ml[kHeadGroup][2];
+    int valid[kSplit];
+};
+
+__device__ __forceinline__ void e4m3x16_to_bf16(const uint4& v, float scale, __nv_bfloat16* dst) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const __nv_fp8x2_storage_t pr = (__nv_fp8x2_storage_t)((w[i] >> (16 * h)) & 0xFFFF);
+            const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(pr, __NV_E4M3);
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+            __nv_bfloat162 b = __floats2bfloat162_rn(f.x * scale, f.y * scale);
+            o[2 * i + h] = *reinterpret_cast<uint32_t*>(&b);
+        }
+    }
+    *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+    *reinterpret_cast<uint4*>(dst + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+__global__ void __launch_bounds__(kMlaThreads, 1) sparse_mla_split_kernel(const mono_sparse_mla_args a, int nsplit) {
+    extern __shared__ uint8_t smem_raw[];
+    MlaSmem& sm = *reinterpret_cast<MlaSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t4 = lane & 3;
+    const __nv_bfloat16* qg = reinterpret_cast<const __nv_bfloat16*>(a.q);
+    __nv_bfloat16* part_acc = reinterpret_cast<__nv_bfloat16*>(a.scratch);
+    float* part_ml = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(a.scratch) +
+                                              (size_t)a.rows * nsplit * a.heads * 512 * sizeof(__nv_bfloat16));
+
+    for (int task = blockIdx.x; task < a.rows * nsplit; task += gridDim.x) {
+        const int row = task / nsplit, sp = task - row * nsplit;
+        __syncthreads();
+        // ---- gather 64 cache rows, widen to bf16
+        if (tid < kSplit) {
+            const int kidx = sp * kSplit + tid;
+            int slot = kidx < a.topk ? a.topk_slots[(size_t)row * a.topk_ld + kidx] : -1;
+            if (slot >= 0 && (int64_t)slot >= a.n_pages * kPage) slot = -1;
+            sm.valid[tid] = slot;
+        }
+        __syncthreads();
+        {
+            constexpr int kChunks = kKvDim / 16;  // 36 sixteen-byte chunks per key
+            constexpr int kPer = kSplit * kChunks / kMlaThreads;  // 9
+            uint4 v[kPer];
+            float sc[kPer];
+#pragma unroll
+            for (int i = 0; i < kPer; ++i) {
+                const int c = tid + i * kMlaThreads;
+                const int key = c / kChunks, ch = c - key * kChunks;
+                const int slot = sm.valid[key];
+                if (slot >= 0) {
+                    const uint8_t* page = a.kv_pages + (size_t)(slot / kPage) * kKvPageBytes;
+                    const int off = slot % kPage;
+                    v[i] = __ldg(reinterpret_cast<const uint4*>(page + (size_t)off * kKvDim) + ch);
+                    sc[i] = __ldg(reinterpret_cast<const float*>(page + kPage * kKvDim) + off);
+                } else {
+                    v[i] = make_uint4(0, 0, 0, 0);
+                    sc[i] = 0.f;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < kPer; ++i) {
+                const int c = tid + i * kMlaThreads;
+                const int key = c / kChunks, ch = c - key * kChunks;
+                e4m3x16_to_bf16(v[i], sc[i], &sm.kv[key][ch * 16]);
+            }
+        }
+        for (int hg = 0; hg < (a.heads + kHeadGroup - 1) / kHeadGroup; ++hg) {
+            __syncthreads();
+            // ---- stage 16 heads of q
+            for (int c = tid; c < kHeadGroup * (kKvDim / 8); c += kMlaThreads) {
+                const int h = c / (kKvDim / 8), ch = c - h * (kKvDim / 8);
+                const int head = hg * kHeadGroup + h;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (head < a.heads) v = *reinterpret_cast<const uint4*>(qg + ((size_t)row * a.heads + head) * kKvDim + ch * 8);
+                *reinterpret_cast<uint4*>(&sm.q[h][ch * 8]) = v;
+            }
+            __syncthreads();
+            // ---- S = Q K^T: warp w owns keys 8w .. 8w+7
+            {
+                float d[4] = {0.f, 0.f, 0.f, 0.f};
+                const uint32_t q_addr = smem_u32(&sm.q[lane & 15][(lane >> 4) * 8]);
+                const uint32_t k_addr = smem_u32(&sm.kv[warp * 8 + (lane & 7)][((lane >> 3) & 1) * 8]);
+#pragma unroll 4
+                for (int ks = 0; ks < kKvDim / 16; ++ks) {
+                    uint32_t af[4], bfr[2];
+                    ldmatrix_x4(af, q_addr + ks * 32);
+                    ldmatrix_x2(bfr, k_addr + ks * 32);
+                    mma_bf16(d, af[0], af[1], af[2], af[3], bfr[0], bfr[1]);
+                }
+                const int k0 = warp * 8 + 2 * t4;
+                const bool v0 = sm.valid[k0] >= 0, v1 = sm.valid[k0 + 1] >= 0;
+                sm.s[g][k0] = v0 ? d[0] * a.sm_scale : -INFINITY;
+                sm.s[g][k0 + 1] = v1 ? d[1] * a.sm_scale : -INFINITY;
+                sm.s[g + 8][k0] = v0 ? d[2] * a.sm_scale : -INFINITY;
+                sm.s[g + 8][k0 + 1] = v1 ? d[3] * a.sm_scale : -INFINITY;
+            }
+            __syncthreads();
+            // ---- split-local softmax: warp w owns heads 2w, 2w+1
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int h = warp * 2 + hh;
+                const float s0 = sm.s[h][lane], s1 = sm.s[h][lane + 32];
+                const float m = warp_max(fmaxf(s0, s1));
+                const float p0 = (m == -INFINITY) ? 0.f : __expf(s0 - m);
+                const float p1 = (m == -INFINITY) ? 0.f : __expf(s1 - m);
+                const float l = warp_sum(p0 + p1);
+                sm.p[h][lane] = __float2bfloat16_rn(p0);
+                sm.p[h][lane + 32] = __float2bfloat16_rn(p1);
+                if (lane == 0) { sm.ml[h][0] = m; sm.ml[h][1] = l; }
+            }
+            __syncthreads();
+            // ---- O = P V: warp w owns latent columns 64w .. 64w+63
+            {
+                float o[8][4];
+#pragma unroll
+                for (int n = 0; n < 8; ++n)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
+                const uint32_t p_addr = smem_u32(&sm.p[lane & 15][(lane >> 4) * 8]);
+#pragma unroll
+                for (int ks = 0; ks < kSplit / 16; ++ks) {
+                    uint32_t af[4];
+                    ldmatrix_x4(af, p_addr + ks * 32);
+#pragma unroll
+                    for (int n2 = 0; n2 < 4; ++n2) {
+                        // two n-tiles (16 columns) per x4.trans: matrices (k0..7,n0..7) (k8..15,n0..7) (k0..7,n8..15) (k8..15,n8..15)
+                        uint32_t bfr[4];
+                        const int krow = ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                        const int col = warp * 64 + n2 * 16 + (lane >> 4) * 8;
+                        ldmatrix_x4_trans(bfr, smem_u32(&sm.kv[krow][col]));
+                        mma_bf16(o[2 * n2], af[0], af[1], af[2], af[3], bfr[0], bfr[1]);
+                        mma_bf16(o[2 * n2 + 1], af[0], af[1], af[2], af[3], bfr[2], bfr[3]);
+                    }
+                }
+                // ---- partial results: bf16 accumulator, f32 (m, l)
+                const int h0 = hg * kHeadGroup + g, h1 = h0 + 8;
+#pragma unroll
+                for (int n = 0; n < 8; ++n) {
+                    const int col = warp * 64 + n * 8 + 2 * t4;
+                    if (h0 < a.heads) {
+                        __nv_bfloat162 v = __floats2bfloat162_rn(o[n][0], o[n][1]);
+                        *reinterpret_cast<__nv_bfloat162*>(part_acc + (((size_t)row * nsplit + sp) * a.heads + h0) * 512 + col) = v;
+                    }
+                    if (h1 < a.heads) {
+                        __nv_bfloat162 v = __floats2bfloat162_rn(o[n][2], o[n][3]);
+                        *reinterpret_cast<__nv_bfloat162*>(part_acc + (((size_t)row * nsplit + sp) * a.heads + h1) * 512 + col) = v;
+                    }
+                }
+                if (tid < kHeadGroup && hg * kHeadGroup + tid < a.heads) {
+                    float* ml = part_ml + (((size_t)row * nsplit + sp) * a.heads + hg * kHeadGroup + tid) * 2;
+                    ml[0] = sm.ml[tid][0];
+                    ml[1] = sm.ml[tid][1];
+                }
+            }
+        }
+    }
+}
+
+// One CTA per (row, head): merge the splits.
+__global__ void __launch_bounds__(256) sparse_mla_merge_kernel(const mono_sparse_mla_args a, int nsplit) {
+    __shared__ float w[64];
+    const int row = blockIdx.x / a.heads, head = blockIdx.x - row * a.heads;
+    const __nv_bfloat16* part_acc = reinterpret_cast<const __nv_bfloat16*>(a.scratch);
+    const float* part_ml = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(a.scratch) +
+                                                          (size_t)a.rows * nsplit * a.heads * 512 * sizeof(__nv_bfloat16));
+    const int tid = threadIdx.x;
+    if (tid < 32) {
+        float mx = -INFINITY;
+        for (int j = tid; j < nsplit; j += 32) mx = fmaxf(mx, part_ml[(((size_t)row * nsplit + j) * a.heads + head) * 2]);
+        mx = warp_max(mx);
+        float den = 0.f;
+        for (int j = tid; j < nsplit; j += 32) {
+            const float* ml = part_ml + (((size_t)row * nsplit + j) * a.heads + head) * 2;
+            const float e = (ml[0] == -INFINITY) ? 0.f : __expf(ml[0] - mx);
+            w[j] = e;
+            den += ml[1] * e;
+        }
+        den = warp_sum(den);
+        __syncwarp();
+        for (int j = tid; j < nsplit; j += 32) w[j] = den > 0.f ? w[j] / den : 0.f;
+    }
+    __syncthreads();
+    const int col = 2 * tid;
+    float a0 = 0.f, a1 = 0.f;
+    for (int j = 0; j < nsplit; ++j) {
+        const __nv_bfloat162 v =
+            *reinterpret_cast<const __nv_bfloat162*>(part_acc + (((size_t)row * nsplit + j) * a.heads + head) * 512 + col);
+        a0 += __low2float(v) * w[j];
+        a1 += __high2float(v) * w[j];
+    }
+    *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(a.out) + ((size_t)row * a.heads + head) * 512 + col) =
+        __floats2bfloat162_rn(a0, a1);
+}
+
+}  // namespace mono
+
+extern "C" size_t mono_sparse_mla_scratch_bytes(int rows, int heads, int topk) {
+    const size_t nsplit = (size_t)(topk + mono::kSplit - 1) / mono::kSplit;
+    return (size_t)rows * nsplit * heads * (512 * sizeof(__nv_bfloat16) + 2 * sizeof(float)) + 256;
+}
+
+extern "C" int mono_sparse_mla_launch(const mono_sparse_mla_args* a, void* stream) {
+    if (!a || a->rows < 1 || a->rows > MONO_MAX_ROWS || a->heads < 1 || a->heads > 128 || a->topk < 1 ||
+        a->topk > 64 * 64 || a->topk_ld < a->topk || !a->q || !a->kv_pages || !a->topk_slots || !a->out || !a->scratch) {
+        mono_set_error("mono_sparse_mla_launch: rows 1..16, heads 1..128, topk 1..4096 and all pointers required");
+        return MONO_E_ARG;
+    }
+    if ((reinterpret_cast<uintptr_t>(a->kv_pages) & 15) || (reinterpret_cast<uintptr_t>(a->q) & 15) ||
+        (reinterpret_cast<uintptr_t>(a->scratch) & 15)) {
+        mono_set_error("mono_sparse_mla_launch: q, kv_pages and scratch must be 16-byte aligned");
+        return MONO_E_ARG;
+    }
+    const int nsplit = (a->topk + mono::kSplit - 1) / mono::kSplit;
+    const size_t smem = sizeof(mono::MlaSmem) + 128;
+    static thread_local bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(mono::sparse_mla_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
+            mono_set_error("mono_sparse_mla_launch: %s", cudaGetErrorString(e));
+            return (int)e;
+        }
+        attr_set = true;
+    }
+    int grid = a->rows * nsplit;
+    const int sms = mono_sm_count();
+    if (grid > 2 * sms) grid = 2 * sms;
+    mono::sparse_mla_split_kernel<<<grid, mono::kMlaThreads, smem, (cudaStream_t)stream>>>(*a, nsplit);
+    mono::sparse_mla_merge_kernel<<<a->rows * a->heads, 256, 0, (cudaStream_t)stream>>>(*a, nsplit);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) mono_set_error("mono_sparse_mla_launch: %s", cudaGetErrorString(e));
+    return (int)e;
+}

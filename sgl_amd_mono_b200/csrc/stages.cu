@@ -1,0 +1,472 @@
+// The small stages between the weight-streaming GEMVs: activation staging
+// (RMSNorm + quantisation), the router, the expert activation, and the partial-sum
+// reduction with the in-kernel tensor-parallel all-reduce.
+//
+// Reference counterparts: glm53/gfx950/kernel.py:1367-1414 (RMSNorm staging),
+// :1440-1466 (quant_scaled / quant_mxfp8), :1575-1629 (route_top8), :4396-4415 (SiLU),
+// :1631-1688 (peer_reduce); minimax_m31/ffn.py:601-723 (router).
+#include "mono_common.cuh"
+
+extern void mono_set_error(const char* fmt, ...);
+
+namespace mono {
+
+// position inside a group of 8 values of the MXFP4-ordered activation plane
+__device__ __forceinline__ int mx_perm8(int i) { return (i & 1) ? 4 + (i >> 1) : (i >> 1); }
+
+// ------------------------------------------------------------------ act_prep
+// One CTA per row.  The row is staged in shared memory as f32, normalised, then
+// quantised one 128-chunk per warp.
+constexpr int kPrepThreads = 256;
+
+__device__ __forceinline__ void quant_chunk128(const float* x /* smem, 128 values */, int fmt, int lane, int chunk,
+                                               uint8_t* plane0, uint8_t* plane1, float* scale_f32, uint8_t* scale_e8) {
+    // lane owns values 4*lane .. 4*lane+3
+    float v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = x[4 * lane + i];
+    if (fmt == MONO_ACT_A8 || fmt == MONO_ACT_HILO) {
+        float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+        amax = warp_max(amax);
+        if (fmt == MONO_ACT_A8) {
+            const float scale = amax > 0.f ? amax / 448.f : 1.f;
+            const float inv = amax > 0.f ? 448.f / amax : 1.f;
+            uint32_t w = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) w |= (uint32_t)f32_to_e4m3(v[i] * inv) << (8 * i);
+            reinterpret_cast<uint32_t*>(plane0 + chunk * 128)[lane] = w;
+            if (lane == 0) scale_f32[chunk] = scale;
+        } else {
+            const int code = code_ceil(fmaxf(amax, 7.888609052210118e-31f /* 2^-100 */) / 448.f);
+            const float sc = exp2_code(code), inv = exp2_code(254 - code);
+            uint32_t wh = 0, wl = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float s = v[i] * inv;
+                const uint8_t h = f32_to_e4m3(s);
+                const uint8_t l = f32_to_e4m3(s - e4m3_to_f32(h));
+                wh |= (uint32_t)h << (8 * i);
+                wl |= (uint32_t)l << (8 * i);
+            }
+            reinterpret_cast<uint32_t*>(plane0 + chunk * 128)[lane] = wh;
+            reinterpret_cast<uint32_t*>(plane1 + chunk * 128)[lane] = wl;
+            if (lane == 0) scale_f32[chunk] = sc;
+        }
+    } else if (fmt == MONO_ACT_MX8) {
+        // four groups of 32: lanes 8q .. 8q+7 own group q
+        float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        int code = code_ceil(fmaxf(amax, 1e-10f) * (1.0f / 448.0f));
+        code = min(max(code, 1), 254);
+        const float inv = exp2_code(254 - code);
+        // values 4*lane+i sit in group-of-8 number lane/2 at in-group index (lane&1)*4+i
+        uint8_t* dst = plane0 + chunk * 128 + (lane >> 1) * 8;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) dst[mx_perm8((lane & 1) * 4 + i)] = f32_to_e4m3(v[i] * inv);
+        if ((lane & 7) == 0) scale_e8[chunk * 4 + (lane >> 3)] = (uint8_t)code;
+    } else {  // MONO_ACT_BF16
+        __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 w = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+        reinterpret_cast<uint2*>(plane0 + chunk * 256)[lane] = w;
+    }
+}
+
+__global__ void __launch_bounds__(kPrepThreads) act_prep_kernel(const mono_act_prep_args a) {
+    extern __shared__ float xrow[];
+    __shared__ float red[kPrepThreads / 32];
+    const int row = blockIdx.x, tid = threadIdx.x;
+    float ssq = 0.f;
+    for (int i = tid; i < a.k; i += kPrepThreads) {
+        float v;
+        if (a.src_bf16) {
+            v = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.src_bf16)[(size_t)row * a.k + i]);
+        } else {
+            v = 0.f;
+            for (int s = 0; s < a.nsum; ++s) v += a.src_f32[(size_t)s * a.src_sum_stride + (size_t)row * a.src_ld + i];
+        }
+        xrow[i] = v;
+        ssq += v * v;
+    }
+    if (a.gamma_bf16) {
+        const float tot = block_sum<kPrepThreads / 32>(ssq, red);
+        const float r = rsqrtf(tot / (float)a.k + a.eps);
+        const __nv_bfloat16* gm = reinterpret_cast<const __nv_bfloat16*>(a.gamma_bf16);
+        for (int i = tid; i < a.k; i += kPrepThreads) xrow[i] = xrow[i] * r * __bfloat162float(gm[i]);
+    }
+    __syncthreads();
+    if (a.round_bf16)
+        for (int i = tid; i < a.k; i += kPrepThreads) xrow[i] = bf16_round(xrow[i]);
+    __syncthreads();
+    if (a.out_bf16) {
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(a.out_bf16) + (size_t)row * a.k;
+        for (int i = tid; i < a.k; i += kPrepThreads) o[i] = __float2bfloat16_rn(xrow[i]);
+    }
+    if (a.planes) {
+        const int warp = tid >> 5, lane = tid & 31;
+        uint8_t* p0 = a.planes + (size_t)row * a.ld;
+        uint8_t* p1 = p0 + a.plane_stride;
+        float* sf = a.scale_f32 ? a.scale_f32 + (size_t)row * a.scale_ld : nullptr;
+        uint8_t* s8 = a.scale_e8 ? a.scale_e8 + (size_t)row * a.scale_ld : nullptr;
+        for (int c = warp; c < a.k / 128; c += kPrepThreads / 32) quant_chunk128(xrow + c * 128, a.fmt, lane, c, p0, p1, sf, s8);
+    }
+}
+
+// ------------------------------------------------------------------ router
+// One CTA, one warp per row.  Picks are exact on the stored f32 scores: key =
+// monotone image of (score + bias), ties to the lower expert id.
+constexpr int kRouteThreads = 512;
+constexpr int kMaxExperts = 512;
+
+__device__ __forceinline__ uint32_t radix_key(float f) {
+    uint32_t b = __float_as_uint(f);
+    return (b & 0x80000000u) ? ~b : (b ^ 0x80000000u);
+}
+
+__global__ void __launch_bounds__(kRouteThreads) route_kernel(const mono_route_args a) {
+    __shared__ float sc[kMaxRows][kMaxExperts];
+    __shared__ int used[kMaxExperts];
+    __shared__ int sel[kMaxRows][16];
+    __shared__ float selw[kMaxRows][16];
+    __shared__ int slot_of[kMaxExperts];
+    __shared__ int warp_cnt[kRouteThreads / 32];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (int e = tid; e < a.n_experts; e += kRouteThreads) used[e] = 0;
+    __syncthreads();
+    if (warp < a.rows) {
+        const int r = warp;
+        const bool live = !a.slots || a.slots[r] >= 0;
+        for (int e = lane; e < a.n_experts; e += 32) {
+            float l = 0.f;
+            for (int s = 0; s < a.nsum; ++s) l += a.logits[(size_t)s * a.sum_stride + (size_t)r * a.ld + e];
+            const float s = 1.f / (1.f + expf(-l));
+            sc[r][e] = s;
+            if (a.scores) a.scores[(size_t)r * a.n_experts + e] = s;
+        }
+        __syncwarp();
+        float wsum = 0.f;
+        for (int k = 0; k < a.top_k; ++k) {
+            unsigned long long best = 0ull;
+            for (int e = lane; e < a.n_experts; e += 32) {
+                bool taken = false;
+                for (int q = 0; q < k; ++q) taken |= (sel[r][q] == e);
+                if (taken) continue;
+                const float key = a.bias ? sc[r][e] + a.bias[e] : sc[r][e];
+                const unsigned long long kk = ((unsigned long long)radix_key(key) << 32) | (uint32_t)(0x7FFFFFFF - e);
+                best = kk > best ? kk : best;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+                best = other > best ? other : best;
+            }
+            const int e = 0x7FFFFFFF - (int)(uint32_t)(best & 0xFFFFFFFFull);
+            if (lane == 0) { sel[r][k] = e; selw[r][k] = sc[r][e]; }
+            wsum += sc[r][e];
+            __syncwarp();
+        }
+        const float norm = a.route_scale / fmaxf(wsum, 1e-20f);
+        if (lane < a.top_k) {
+            const int e = live ? sel[r][lane] : -1;
+            const float w = live ? selw[r][lane] * norm : 0.f;
+            a.ids[r * a.top_k + lane] = e;
+            a.weights[r * a.top_k + lane] = w;
+            sel[r][lane] = e;
+            selw[r][lane] = w;
+            if (live) used[e] = 1;
+        }
+    }
+    __syncthreads();
+    // distinct experts in ascending id: ordered compaction
+    int flag = 0;
+    if (tid < a.n_experts) flag = used[tid];
+    const unsigned bal = __ballot_sync(0xffffffffu, flag);
+    if (lane == 0) warp_cnt[warp] = __popc(bal);
+    __syncthreads();
+    int base = 0;
+    for (int w = 0; w < warp; ++w) base += warp_cnt[w];
+    if (tid < a.n_experts) slot_of[tid] = flag ? base + __popc(bal & ((1u << lane) - 1)) : -1;
+    __syncthreads();
+    int total = 0;
+    for (int w = 0; w < kRouteThreads / 32; ++w) total += warp_cnt[w];
+    if (tid < a.n_experts && flag) a.expert_list[slot_of[tid]] = tid;
+    if (tid == 0) *a.n_expert = total;
+    for (int i = tid; i < total * kMaxRows; i += kRouteThreads) a.coef[i] = 0.f;
+    __syncthreads();
+    if (tid < a.rows * a.top_k) {
+        const int r = tid / a.top_k, k = tid - r * a.top_k;
+        const int e = sel[r][k];
+        if (e >= 0) a.coef[slot_of[e] * kMaxRows + r] = selw[r][k];
+    }
+}
+
+// ------------------------------------------------------------------ small row-dot GEMV
+// out[r][n] = sum_k x[r][k] * W[n][k] on CUDA cores, one warp per output column, for
+// matrices too small to be worth a tensor-core launch (router logits with f32 or bf16
+// weights: minimax_m31/ffn.py:601-649, glm53/gfx950/kernel.py:4199-4330).  The k
+// order is fixed (lane-strided, then a butterfly), so every rank gets the same bits.
+constexpr int kRowdotThreads = 256;
+
+__global__ void __launch_bounds__(kRowdotThreads) rowdot_kernel(const mono_rowdot_args a) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * (kRowdotThreads / 32) + warp;
+    if (n >= a.n) return;
+    float acc[kMaxRows];
+#pragma unroll
+    for (int r = 0; r < kMaxRows; ++r) acc[r] = 0.f;
+    const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(a.x_bf16);
+    for (int k = lane * 4; k < a.k; k += 128) {
+        float w[4];
+        if (a.w_is_f32) {
+            const float4 v = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.w) + (size_t)n * a.k + k));
+            w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+        } else {
+            const uint2 v = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.w) + (size_t)n * a.k + k));
+            const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+            const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+            w[0] = lo.x; w[1] = lo.y; w[2] = hi.x; w[3] = hi.y;
+        }
+#pragma unroll
+        for (int r = 0; r < kMaxRows; ++r) {
+            if (r < a.rows) {
+                const uint2 xv = *reinterpret_cast<const uint2*>(x + (size_t)r * a.k + k);
+                const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.x));
+                const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.y));
+                acc[r] += lo.x * w[0] + lo.y * w[1] + hi.x * w[2] + hi.y * w[3];
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < kMaxRows; ++r) {
+        if (r < a.rows) {
+            const float s = warp_sum(acc[r]);
+            if (lane == 0) a.out[(size_t)r * a.out_ld + n] = s * a.out_scale;
+        }
+    }
+}
+
+// ------------------------------------------------------------------ expert activation
+constexpr int kMidThreads = 256;
+
+__global__ void __launch_bounds__(kMidThreads) mid_kernel(const mono_mid_args a) {
+    __shared__ float chunk[kMidThreads / 32][128];
+    const int slot = blockIdx.x / a.rows, row = blockIdx.x - slot * a.rows;
+    const int nslot = a.n_slot ? min(*a.n_slot, a.max_slot) : a.max_slot;
+    if (slot >= nslot) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t ld2 = 2 * (size_t)a.inter;
+    const float* up = a.up + ((size_t)slot * a.nsum * kMaxRows + row) * ld2;
+    const size_t sum_stride = (size_t)kMaxRows * ld2;
+    const int ld_bytes = a.ld;
+    uint8_t* p0 = a.planes + ((size_t)slot * kMaxRows + row) * ld_bytes;
+    float* sf = a.scale_f32 ? a.scale_f32 + ((size_t)slot * kMaxRows + row) * a.scale_ld : nullptr;
+    uint8_t* s8 = a.scale_e8 ? a.scale_e8 + ((size_t)slot * kMaxRows + row) * a.scale_ld : nullptr;
+    for (int c = warp; c < a.inter / 128; c += kMidThreads / 32) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int idx = c * 128 + 4 * lane + i;
+            float g = 0.f, u = 0.f;
+            for (int s = 0; s < a.nsum; ++s) {
+                g += up[s * sum_stride + idx];
+                u += up[s * sum_stride + a.inter + idx];
+            }
+            float m = g / (1.f + expf(-g)) * u;
+            if (a.round_bf16) m = bf16_round(m);
+            chunk[warp][4 * lane + i] = m;
+        }
+        __syncwarp();
+        quant_chunk128(chunk[warp], a.fmt, lane, c, p0, nullptr, sf, s8);
+        __syncwarp();
+    }
+}
+
+// ------------------------------------------------------------------ reduce + all-reduce
+// Every thread owns one bf16 pair (two adjacent columns) of one row.
+constexpr int kReduceThreads = 256;
+
+__device__ __forceinline__ void st_sys_v2(uint64_t addr, uint32_t a, uint32_t b) {
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1,%2};" ::"l"(addr), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ uint2 ld_sys_v2(uint64_t addr) {
+    uint2 v;
+    asm volatile("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_sys_u32(uint64_t addr, uint32_t a) {
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(a) : "memory");
+}
+
+__global__ void __launch_bounds__(kReduceThreads) reduce_kernel(const mono_reduce_args a) {
+    const int pairs = a.n / 2;
+    const int total = a.rows * pairs;
+    uint32_t tag = a.tag;
+    int parity = a.parity;
+    if (a.world > 1 && a.guard && tag == 0) {
+        const int epoch = reinterpret_cast<const volatile int*>(a.guard)[MONO_GUARD_EPOCH];
+        tag = (uint32_t)epoch * 256u + (uint32_t)a.site + 1u;
+        parity = epoch & 1;
+    }
+    for (int idx = blockIdx.x * kReduceThreads + threadIdx.x; idx < total; idx += gridDim.x * kReduceThreads) {
+        const int row = idx / pairs, pc = idx - row * pairs;
+        const bool live = !a.slots || a.slots[row] >= 0;
+        float p0 = 0.f, p1 = 0.f;
+        if (live) {
+            for (int s = 0; s < a.nsum; ++s) {
+                const float2 v = *reinterpret_cast<const float2*>(a.partial + (size_t)s * a.sum_stride + (size_t)row * a.ld + 2 * pc);
+                p0 += v.x;
+                p1 += v.y;
+            }
+        }
+        __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+        float acc0, acc1;
+        if (a.world > 1) {
+            const uint32_t word = *reinterpret_cast<uint32_t*>(&pb);
+            const size_t slot_pairs = (size_t)kMaxRows * pairs;
+            const size_t my_off = (((size_t)parity * a.world + a.rank) * slot_pairs + (size_t)row * pairs + pc) * 8;
+            for (int d = 0; d < a.world; ++d) st_sys_v2(a.peer_ptrs[d] + my_off, word, tag);
+            acc0 = 0.f;
+            acc1 = 0.f;
+            const uint64_t mine = a.peer_ptrs[a.rank];
+            const uint64_t t0 = globaltimer_ns();
+            bool failed = guard_failed(a.guard);
+            for (int src = 0; src < a.world && !failed; ++src) {
+                const uint64_t addr = mine + (((size_t)parity * a.world + src) * slot_pairs + (size_t)row * pairs + pc) * 8;
+                uint2 v = ld_sys_v2(addr);
+                uint32_t spins = 0;
+                while (v.y != tag) {
+                    if ((++spins & 63) == 0) {
+                        if (guard_failed(a.guard)) { failed = true; break; }
+                        const volatile int* gw = a.guard;
+                        if (gw) {
+                            for (int r = 0; r < a.world; ++r)
+                                if (gw[MONO_GUARD_FLAGS + r]) { guard_fail(a.guard, MONO_ERR_PEER, r); failed = true; }
+                            if (failed) break;
+                        }
+                        if (globaltimer_ns() - t0 > a.deadline_ns) {
+                            guard_fail(a.guard, MONO_ERR_DEADLINE, a.site);
+                            if (a.peer_guards)
+                                for (int d = 0; d < a.world; ++d)
+                                    if (d != a.rank) st_sys_u32(a.peer_guards[d] + 4ull * (MONO_GUARD_FLAGS + a.rank), 1u);
+                            failed = true;
+                            break;
+                        }
+                    }
+                    v = ld_sys_v2(addr);
+                }
+                if (failed) break;
+                const __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162*>(&v.x);
+                acc0 += __low2float(b);
+                acc1 += __high2float(b);
+            }
+        } else {
+            acc0 = __low2float(pb);
+            acc1 = __high2float(pb);
+        }
+        if (a.residual) {
+            const __nv_bfloat162 r = reinterpret_cast<const __nv_bfloat162*>(a.residual)[(size_t)row * pairs + pc];
+            acc0 += __low2float(r);
+            acc1 += __high2float(r);
+        }
+        reinterpret_cast<__nv_bfloat162*>(a.out)[(size_t)row * pairs + pc] = __floats2bfloat162_rn(acc0, acc1);
+    }
+}
+
+__global__ void epoch_advance_kernel(int32_t* guard) { guard[MONO_GUARD_EPOCH] += 1; }
+
+}  // namespace mono
+
+// ------------------------------------------------------------------------ host
+extern "C" int mono_act_prep_launch(const mono_act_prep_args* a, void* stream) {
+    if (!a || a->rows < 1 || a->rows > MONO_MAX_ROWS || a->k < 128 || (a->k & 127) || a->k > 16384) {
+        mono_set_error("mono_act_prep_launch: rows in 1..16 and k a multiple of 128 up to 16384 required");
+        return MONO_E_ARG;
+    }
+    if ((a->src_bf16 == nullptr) == (a->src_f32 == nullptr)) {
+        mono_set_error("mono_act_prep_launch: exactly one of src_bf16 / src_f32");
+        return MONO_E_ARG;
+    }
+    if (a->planes) {
+        const bool need_f32 = a->fmt == MONO_ACT_A8 || a->fmt == MONO_ACT_HILO;
+        if ((need_f32 && !a->scale_f32) || (a->fmt == MONO_ACT_MX8 && !a->scale_e8) || a->fmt < 0 || a->fmt > 3) {
+            mono_set_error("mono_act_prep_launch: format %d needs its scale buffer", a->fmt);
+            return MONO_E_ARG;
+        }
+    }
+    mono::act_prep_kernel<<<a->rows, mono::kPrepThreads, a->k * sizeof(float), (cudaStream_t)stream>>>(*a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) mono_set_error("mono_act_prep_launch: %s", cudaGetErrorString(e));
+    return (int)e;
+}
+
+extern "C" int mono_route_launch(const mono_route_args* a, void* stream) {
+    if (!a || a->rows < 1 || a->rows > MONO_MAX_ROWS || a->n_experts < 1 || a->n_experts > mono::kMaxExperts ||
+        a->top_k < 1 || a->top_k > 16 || a->top_k > a->n_experts || !a->logits || !a->ids || !a->weights ||
+        !a->expert_list || !a->n_expert || !a->coef) {
+        mono_set_error("mono_route_launch: rows 1..16, experts 1..512, top_k 1..16 and output pointers required");
+        return MONO_E_ARG;
+    }
+    mono::route_kernel<<<1, mono::kRouteThreads, 0, (cudaStream_t)stream>>>(*a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) mono_set_error("mono_route_launch: %s", cudaGetErrorString(e));
+    return (int)e;
+}
+
+extern "C" int mono_rowdot_launch(const mono_rowdot_args* a, void* stream) {
+    if (!a || a->rows < 1 || a->rows > MONO_MAX_ROWS || a->n < 1 || a->k < 128 || (a->k & 127) || !a->w || !a->x_bf16 || !a->out) {
+        mono_set_error("mono_rowdot_launch: rows 1..16, k a multiple of 128 and all pointers required");
+        return MONO_E_ARG;
+    }
+    const int per = mono::kRowdotThreads / 32;
+    mono::rowdot_kernel<<<(a->n + per - 1) / per, mono::kRowdotThreads, 0, (cudaStream_t)stream>>>(*a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) mono_set_error("mono_rowdot_launch: %s", cudaGetErrorString(e));
+    return (int)e;
+}
+
+extern "C" int mono_mid_launch(const mono_mid_args* a, void* stream) {
+    if (!a || a->rows < 1 || a->rows > MONO_MAX_ROWS || a->inter < 128 || (a->inter & 127) || !a->up || !a->planes ||
+        a->max_slot < 1) {
+        mono_set_error("mono_mid_launch: rows 1..16 and inter a multiple of 128 required");
+        return MONO_E_ARG;
+    }
+    if ((a->fmt == MONO_ACT_A8 && !a->scale_f32) || (a->fmt == MONO_ACT_MX8 && !a->scale_e8) || a->fmt == MONO_ACT_HILO) {
+        mono_set_error("mono_mid_launch: format %d not supported or missing scales", a->fmt);
+        return MONO_E_ARG;
+    }
+    mono::mid_kernel<<<a->max_slot * a->rows, mono::kMidThreads, 0, (cudaStream_t)stream>>>(*a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) mono_set_error("mono_mid_launch: %s", cudaGetErrorString(e));
+    return (int)e;
+}
+
+extern "C" size_t mono_reduce_peer_bytes(int rows, int n, int world) {
+    (void)rows;
+    return (size_t)2 * world * MONO_MAX_ROWS * (n / 2) * 8;
+}
+
+extern "C" int mono_reduce_launch(const mono_reduce_args* a, void* stream) {
+    if (!a || a->rows < 1 || a->rows > MONO_MAX_ROWS || a->n < 2 || (a->n & 1) || !a->partial || !a->out || a->nsum < 1 ||
+        (a->ld & 1)) {
+        mono_set_error("mono_reduce_launch: rows 1..16, even n and ld, partial and out required");
+        return MONO_E_ARG;
+    }
+    if (a->world > 1 && (!a->peer_ptrs || a->rank < 0 || a->rank >= a->world || a->world > 8 || a->deadline_ns == 0 ||
+                         (a->tag == 0 && !a->guard))) {
+        mono_set_error("mono_reduce_launch: world %d needs peer_ptrs, a rank, a deadline and a tag or guard words", a->world);
+        return MONO_E_ARG;
+    }
+    const int total = a->rows * (a->n / 2);
+    int grid = (total + mono::kReduceThreads - 1) / mono::kReduceThreads;
+    const int sms = mono_sm_count();
+    if (grid > 2 * sms) grid = 2 * sms;
+    mono::reduce_kernel<<<grid, mono::kReduceThreads, 0, (cudaStream_t)stream>>>(*a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) mono_set_error("mono_reduce_launch: %s", cudaGetErrorString(e));
+    return (int)e;
+}
+
+extern "C" int mono_epoch_advance_launch(int32_t* guard, void* stream) {
+    if (!guard) return MONO_E_ARG;
+    mono::epoch_advance_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(guard);
+    return (int)cudaGetLastError();
+}
