@@ -1,0 +1,379 @@
+#!/usr/bin/env python
+"""Benchmark of the decode hot path: µs per decoder layer and achieved HBM GB/s.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload NAME]
+
+One "step" is one pass of the workload's hot path over one batch of synthetic rows.
+The JSON line carries: ``value`` (device-timed, inputs resident in HBM), ``e2e``
+(the same call through the public op with pinned HOST inputs, copies inside the timed
+region), ``roofline`` of the dominant kernel (timed alone with CUDA events) and
+``cpu_baseline`` (the CPU oracle on a bounded sample, host cores).  Between timed
+iterations a buffer larger than L2 is written so that no step starts warm.
+``--impl reference`` times the CPU restatement of the reference's arithmetic on the
+host cores (the reference's own kernels exist only for AMD gfx950 and cannot run here).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+L2_FLUSH_BYTES = 256 << 20
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s)"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], 0.0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx = max(mx, float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def time_steps(fn, steps: int, warmup: int, flush: torch.Tensor | None, sampler=None):
+    """Sum of per-step device times in ms (CUDA events on the current stream)."""
+    for _ in range(warmup):
+        if flush is not None:
+            flush.zero_()
+        fn()
+    torch.cuda.synchronize()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    ctx = sampler if sampler is not None else _Null()
+    with ctx:
+        for a, b in evs:
+            if flush is not None:
+                flush.zero_()
+            a.record()
+            fn()
+            b.record()
+        torch.cuda.synchronize()
+    return sum(a.elapsed_time(b) for a, b in evs)
+
+
+class _Null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+# ------------------------------------------------------------------ workloads
+class SparseMlaWorkload:
+    """BASELINE config 2: sparse MLA decode attention alone, 8 rows x 16 local heads,
+    FP8 latent cache with one f32 scale per token, 32768-token contexts, 2048 selected
+    keys per row (uniform without replacement), softmax scale 1/sqrt(192)."""
+
+    name = "cfg2_sparse_mla_8rows_16heads_ctx32768_top2048"
+    layers_per_step = 1
+    kernel = "sparse_mla_split_kernel + sparse_mla_merge_kernel"
+
+    def __init__(self, rows=8, heads=16, ctx=32768, topk=2048):
+        self.rows, self.heads, self.ctx, self.topk = rows, heads, ctx, topk
+
+    def setup(self, dev, rank, world):
+        from sgl_amd_mono_b200 import synth
+        from sgl_amd_mono_b200.attention import SparseMlaOp
+
+        self.dev = dev
+        q, pages, sel, _ = synth.sparse_mla_inputs(self.rows, self.heads, self.ctx, self.topk, device=dev, seed=rank)
+        self.q, self.pages, self.sel = q, pages, sel
+        self.op = SparseMlaOp(self.heads, self.topk, dev, sm_scale=192**-0.5)
+        self.q_host, self.sel_host = q.cpu().pin_memory(), sel.cpu().pin_memory()
+        self.q_in, self.sel_in = torch.empty_like(q), torch.empty_like(sel)
+        self.out_host = torch.empty(self.rows, self.heads, 512, dtype=torch.bfloat16).pin_memory()
+        self.launches_per_step = 2
+
+    def step(self):
+        self.op(self.q, self.pages, self.sel)
+
+    def e2e_step(self):
+        self.q_in.copy_(self.q_host, non_blocking=True)
+        self.sel_in.copy_(self.sel_host, non_blocking=True)
+        out = self.op(self.q_in, self.pages, self.sel_in)
+        self.out_host.copy_(out, non_blocking=True)
+        torch.cuda.synchronize()
+
+    def e2e_bytes(self):
+        return self.q_host.numel() * 2 + self.sel_host.numel() * 4, self.out_host.numel() * 2
+
+    def roofline_probe(self):
+        b = self.rows * (self.topk * 580 + self.heads * 576 * 2 + self.heads * 512 * 2)
+        return b, self.step
+
+    def config(self):
+        return {"workload": self.name, "rows": self.rows, "local_heads": self.heads, "context": self.ctx,
+                "topk": self.topk, "kv_cache": "fp8_e4m3 + f32 scale per token, page 64",
+                "l2": "256 MiB buffer written between timed iterations"}
+
+    def cpu_sample(self):
+        from oracle import stages as S
+
+        n = 2
+        q, pages, sel = self.q[:n].cpu(), self.pages.cpu(), self.sel[:n].cpu()
+        S.sparse_mla(q[:1], pages, sel[:1], 192**-0.5)
+        ts = []
+        for _ in range(3):
+            t0 = time.perf_counter()
+            S.sparse_mla(q, pages, sel, 192**-0.5)
+            ts.append(time.perf_counter() - t0)
+        return statistics.median(ts) * 1e6 * self.rows / n, f"{n} of {self.rows} rows, scaled by rows; median of 3"
+
+
+class MoeWorkload:
+    """The MoE FFN half of BASELINE config 3 (hidden 7168, 256 routed experts top-8 + 1
+    shared, intermediate 2048, FP8 E4M3 with 128x128 block scales) at TP = number of
+    GPUs, 8 decode rows: post-norm, router, shared + routed experts, all-reduce, residual."""
+
+    layers_per_step = 1
+    kernel = "gemv_kernel<FP8> (expert up/gate)"
+
+    def __init__(self, rows=8):
+        self.rows = rows
+
+    def setup(self, dev, rank, world, peer=None):
+        from sgl_amd_mono_b200 import synth
+        from sgl_amd_mono_b200.config import CFG_V3
+        from sgl_amd_mono_b200.moe import MoeFfn
+        from dataclasses import replace
+
+        self.cfg = replace(CFG_V3, n_heads=0, index_heads=0).with_tp(world)
+        self.name = f"cfg3_moe_half_tp{world}_{self.rows}rows"
+        self.w = synth.layer_weights(self.cfg, rank, dev)
+        self.ffn = MoeFfn(self.cfg, self.w, dev, peer=peer)
+        g = torch.Generator().manual_seed(0)
+        self.x_host = torch.randn(self.rows, self.cfg.hidden, generator=g).bfloat16().pin_memory()
+        self.x = self.x_host.to(dev)
+        self.x_in = torch.empty_like(self.x)
+        self.out_host = torch.empty_like(self.x_host).pin_memory()
+        self.ffn(self.x)
+        torch.cuda.synchronize()
+        self.launches_per_step = 8
+
+    def step(self):
+        self.ffn(self.x)
+
+    def e2e_step(self):
+        self.x_in.copy_(self.x_host, non_blocking=True)
+        out = self.ffn(self.x_in)
+        self.out_host.copy_(out, non_blocking=True)
+        torch.cuda.synchronize()
+
+    def e2e_bytes(self):
+        return self.x_host.numel() * 2, self.out_host.numel() * 2
+
+    def roofline_probe(self):
+        u = int(self.ffn.n_expert.item())
+        c = self.cfg
+        b = (u + 1) * 2 * c.inter_local * c.hidden
+        return b, lambda: self.ffn.up.launch(self.rows)
+
+    def config(self):
+        c = self.cfg
+        return {"workload": self.name, "rows": self.rows, "hidden": c.hidden, "experts": c.n_experts, "top_k": c.top_k,
+                "inter": c.inter, "tp": c.tp, "distinct_experts": int(self.ffn.n_expert.item()),
+                "weights": "fp8_e4m3 128x128 block scales", "l2": "256 MiB buffer written between timed iterations"}
+
+    def cpu_sample(self):
+        from oracle import layers as OL
+
+        ids = self.ffn.ids[: self.rows].cpu()
+        used = sorted(set(ids[:1].flatten().tolist()))
+        w = {}
+        for k, v in self.w.items():
+            if k in ("w13", "w13_s", "w2", "w2_s"):
+                w[k] = {e: v[e].cpu() for e in used}
+            else:
+                w[k] = v.cpu()
+        x = self.x_host[:1]
+        OL.moe_partial(self.cfg, w, x)
+        ts = []
+        for _ in range(3):
+            t0 = time.perf_counter()
+            OL.moe_partial(self.cfg, w, x)
+            ts.append(time.perf_counter() - t0)
+        return statistics.median(ts) * 1e6 * self.rows, f"1 of {self.rows} rows, scaled by rows; median of 3"
+
+
+WORKLOADS = {"sparse_mla": SparseMlaWorkload, "moe": MoeWorkload}
+DEFAULT_WORKLOAD = "sparse_mla"
+
+
+# ------------------------------------------------------------------ main
+def run_reference(args, wl_cls, rank: int) -> None:
+    """The CPU restatement of the reference's arithmetic, timed on the host cores."""
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    wl = wl_cls()
+    dev = "cuda:0" if torch.cuda.is_available() else "cpu"
+    if dev == "cpu":
+        print(json.dumps({"impl": "reference", "unavailable": "needs the GPU box to generate the workload's inputs"}))
+        return
+    wl.setup(dev, 0, max(args.gpus, 1))
+    vals = []
+    for _ in range(max(1, min(args.steps, 3))):
+        v, sample = wl.cpu_sample()
+        vals.append(v)
+    v = statistics.median(vals)
+    line = {
+        "impl": "reference", "metric": "us_per_decoder_layer", "value": v, "unit": "us", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": v / 1000.0, "higher_is_better": False,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32 over dequantised fp8/fp4", "data": "synthetic",
+        "config": wl.config(),
+        "cpu_baseline": {"value": v, "unit": "us", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=os.environ.get("MONO_BENCH_WORKLOAD", DEFAULT_WORKLOAD), choices=sorted(WORKLOADS))
+    ap.add_argument("--rows", type=int, default=8)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    wl_cls = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, wl_cls, rank)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the monokernel path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = f"cuda:{local}"
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device(dev))
+    wl = wl_cls(rows=args.rows)
+    wl.setup(dev, rank, world)
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    barrier()
+    sampler = ClockSampler(local)
+    total_ms = time_steps(wl.step, args.steps, args.warmup, flush, sampler)
+    barrier()
+    t = torch.tensor([total_ms], device=dev)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    us_per_layer = ms_per_step * 1000.0 / wl.layers_per_step
+    # end to end: pinned host inputs, copies and the result read inside the timed region
+    for _ in range(3):
+        wl.e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        wl.e2e_step()
+    e2e_ms = (time.perf_counter() - t0) * 1000.0 / args.steps
+    t = torch.tensor([e2e_ms], device=dev)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_us = float(t.item()) * 1000.0 / wl.layers_per_step
+    h2d, d2h = wl.e2e_bytes()
+    # roofline of the dominant kernel, timed alone
+    nbytes, probe = wl.roofline_probe()
+    probe_ms = time_steps(probe, args.steps, 3, flush) / args.steps
+    peak, peak_src = measured_peaks()
+    achieved = nbytes / (probe_ms * 1e-3) / 1e9
+    line = {
+        "metric": "us_per_decoder_layer", "value": us_per_layer, "unit": "us", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": None, "dtype": "fp8_e4m3 weights / bf16 activations, f32 accumulate", "data": "synthetic",
+        "config": wl.config(), "clocks": sampler.summary(), "gpu_launches": wl.launches_per_step * args.steps,
+        "e2e": {"value": e2e_us, "unit": "us", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "roofline": {"bound": "hbm", "kernel": wl.kernel, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "traffic": None, "algorithmic_bytes": nbytes,
+                     "kernel_us": probe_ms * 1000.0, "peak_source": peak_src},
+    }
+    if rank == 0:
+        if not args.no_cpu_baseline:
+            cores = os.cpu_count() or 1
+            torch.set_num_threads(cores)
+            v, sample = wl.cpu_sample()
+            line["cpu_baseline"] = {"value": v, "unit": "us", "cores": cores, "kind": "port", "sample": sample}
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

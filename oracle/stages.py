@@ -333,7 +333,7 @@ def tail_logits(h, gamma, eps: float, w_head) -> torch.Tensor:
     """
     x = h.float()
     x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * gamma.float()
-    return Q.bf(x) @ w_head.float().T
+    return x @ w_head.float().T
 
 
 def sm_scale_mla(nope: int, rope: int) -> float:

@@ -410,8 +410,12 @@ namespace {
 template <int WK, int NT>
 int launch_gemv(const mono::GemvParams& p, int grid, size_t smem, cudaStream_t st) {
     auto k = mono::gemv_kernel<WK, NT>;
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
+    static thread_local bool attr_set = false;  // once per instantiation, outside any graph capture
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
     k<<<grid, mono::kGemvThreads, smem, st>>>(p);
     return (int)cudaGetLastError();
 }

@@ -392,6 +392,11 @@ extern "C" int mono_act_prep_launch(const mono_act_prep_args* a, void* stream) {
             return MONO_E_ARG;
         }
     }
+    static thread_local bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(mono::act_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * (int)sizeof(float));
+        attr_set = true;
+    }
     mono::act_prep_kernel<<<a->rows, mono::kPrepThreads, a->k * sizeof(float), (cudaStream_t)stream>>>(*a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_act_prep_launch: %s", cudaGetErrorString(e));

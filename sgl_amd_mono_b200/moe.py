@@ -1,0 +1,120 @@
+"""Host runner of the MoE FFN half of a layer (post-norm, router, shared + routed
+experts, all-reduce, residual) and of the stand-alone FFN block.
+
+Reference counterparts: ``minimax_m31/runner.py:145-167`` (``FfnRunner.__call__``:
+tensors in, pointer-only launches, ``(out, res_out)`` back) and the FFN stages of
+``glm53/gfx950/kernel.py:4199-5187``.  Everything is allocated in ``__init__``; a
+call only launches kernels on torch's current stream, so it can be captured in a
+CUDA graph and replayed.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _lib as L
+from . import ops
+from .config import LayerConfig
+
+_WK = {"fp8_block": L.W_FP8, "mxfp4": L.W_MXFP4, "bf16": L.W_BF16}
+_ACT = {"fp8_block": L.ACT_A8, "mxfp4": L.ACT_MX8, "bf16": L.ACT_BF16}
+
+
+def _ktiles(t: torch.Tensor) -> int:
+    """K of a weight in 128-byte tiles."""
+    return -(-(t.shape[-1] * t.element_size()) // 128)
+
+
+class MoeFfn:
+    """``out = residual + allreduce(shared(x̂) + sum_k w_k expert_k(x̂))``, x̂ = RMSNorm(residual)."""
+
+    def __init__(self, cfg: LayerConfig, w: dict, device, max_rows: int = L.MAX_ROWS, peer=None,
+                 guard: torch.Tensor | None = None, site: int = 1, deadline_s: float = 5.0):
+        L.load()  # fail loudly when the CUDA library is missing
+        self.cfg, self.w, self.dev, self.peer, self.site = cfg, w, device, peer, site
+        self.deadline_s = deadline_s
+        self.guard = guard if guard is not None else torch.zeros(L.GUARD_WORDS, dtype=torch.int32, device=device)
+        h, il, E, k = cfg.hidden, cfg.inter_local, cfg.n_experts, cfg.top_k
+        self.max_expert = min(E, max_rows * k)
+        efmt, sfmt = cfg.expert_fmt, cfg.shared_fmt
+        z = lambda *s, dt=torch.float32: torch.zeros(*s, dtype=dt, device=device)  # noqa: E731
+        self.xq = ops.ActBuf(_ACT[efmt], h, device)
+        self.xbf = z(L.MAX_ROWS, h, dt=torch.bfloat16)
+        self.logits = z(L.MAX_ROWS, E)
+        self.ids = z(L.MAX_ROWS, k, dt=torch.int32)
+        self.weights = z(L.MAX_ROWS, k)
+        self.scores = z(L.MAX_ROWS, E)
+        self.expert_list = z(self.max_expert, dt=torch.int32)
+        self.n_expert = z(1, dt=torch.int32)
+        self.coef = z(self.max_expert, L.MAX_ROWS)
+        self.mid_r = ops.ActBuf(_ACT[efmt], il, device, segs=self.max_expert)
+        self.has_shared = sfmt != "none"
+        same = self.has_shared and sfmt == efmt
+        # ---- up / gate launch
+        self.up = ops.Gemv(_WK[efmt], self.guard)
+        probe = ops.plan_split(_ktiles(w["w13"]), -(-2 * il // 128) * self.max_expert, _WK[efmt])
+        self.ns_up = probe[1]
+        self.up_r = z(self.max_expert * self.ns_up, L.MAX_ROWS, 2 * il)
+        got = self.up.add("w13", w["w13"], self.xq, self.up_r, mode=L.JOB_EXPERT_UP, wscale=w["w13_s"],
+                          expert_list=self.expert_list, n_expert=self.n_expert, max_expert=self.max_expert,
+                          split_tiles=probe[0], nsplit=probe[1])
+        assert got == self.ns_up
+        self.up_sh = self.mid_s = self.up_s = None
+        if self.has_shared:
+            self.xs = self.xq if same else ops.ActBuf(_ACT[sfmt], h, device)
+            self.mid_s = ops.ActBuf(_ACT[sfmt], il, device)
+            st, ns = ops.plan_split(_ktiles(w["sh13"]), -(-2 * il // 128), _WK[sfmt])
+            self.ns_up_s = ns
+            self.up_s = z(ns, L.MAX_ROWS, 2 * il)
+            g = self.up if same else ops.Gemv(_WK[sfmt], self.guard)
+            g.add("sh13", w["sh13"], self.xs, self.up_s, wscale=w.get("sh13_s"), split_tiles=st, nsplit=ns)
+            self.up_sh = None if same else g
+        # ---- down launch: routed expert groups, then the shared expert's K splits
+        nrb = -(-h // 128)
+        self.groups = max(1, min(self.max_expert, -(-2 * 148 // nrb)))
+        ns_dn_s = 0
+        if self.has_shared:
+            self.st_dn_s, ns_dn_s = ops.plan_split(_ktiles(w["sh2"]), nrb, _WK[sfmt])
+        self.n_slices = self.groups + ns_dn_s
+        self.down_p = z(self.n_slices, L.MAX_ROWS, h)
+        self.down = ops.Gemv(_WK[efmt], self.guard)
+        self.down.add("w2", w["w2"], self.mid_r, self.down_p, mode=L.JOB_EXPERT_DOWN, wscale=w["w2_s"],
+                      expert_list=self.expert_list, n_expert=self.n_expert, max_expert=self.max_expert,
+                      coef=self.coef, nsplit=self.groups)
+        self.down_sh = None
+        if self.has_shared:
+            g = self.down if same else ops.Gemv(_WK[sfmt], self.guard)
+            g.add("sh2", w["sh2"], self.mid_s, self.down_p, wscale=w.get("sh2_s"), out_slice=self.groups,
+                  split_tiles=self.st_dn_s, nsplit=ns_dn_s)
+            self.down_sh = None if same else g
+        self.out = z(L.MAX_ROWS, h, dt=torch.bfloat16)
+
+    def __call__(self, residual: torch.Tensor, slots: torch.Tensor | None = None) -> torch.Tensor:
+        cfg, w = self.cfg, self.w
+        rows = residual.shape[0]
+        if not 1 <= rows <= L.MAX_ROWS:
+            raise ValueError(f"residual: {rows} rows, the launch serves 1..{L.MAX_ROWS}")
+        ops.require(residual, "residual", torch.bfloat16, (rows, cfg.hidden))
+        if slots is not None:
+            ops.require(slots, "slots", torch.int64, (rows,))
+        h, il = cfg.hidden, cfg.inter_local
+        ops.act_prep(rows, h, self.xq, src_bf16=residual, gamma=w["post_norm"], eps=cfg.eps, out_bf16=self.xbf)
+        if self.has_shared and self.xs is not self.xq:
+            ops.act_prep(rows, h, self.xs, src_bf16=self.xbf, round_bf16=False)
+        ops.rowdot(rows, w["router"], self.xbf, self.logits)
+        ops.route(rows, cfg.top_k, cfg.route_scale, self.logits, w.get("router_bias"), slots, self.ids,
+                  self.weights, self.scores, self.expert_list, self.n_expert, self.coef)
+        self.up.launch(rows)
+        if self.up_sh is not None:
+            self.up_sh.launch(rows)
+        ops.mid(rows, il, self.up_r, self.ns_up, self.mid_r, n_slot=self.n_expert, max_slot=self.max_expert,
+                round_bf16=cfg.expert_fmt != "fp8_block")
+        if self.has_shared:
+            ops.mid(rows, il, self.up_s, self.ns_up_s, self.mid_s, max_slot=1,
+                    round_bf16=cfg.shared_fmt != "fp8_block")
+        self.down.launch(rows)
+        if self.down_sh is not None:
+            self.down_sh.launch(rows)
+        ops.reduce_rows(rows, h, self.down_p, self.n_slices, self.out, residual=residual, slots=slots,
+                        peer=self.peer, site=self.site, guard=self.guard, deadline_s=self.deadline_s)
+        return self.out[:rows]

@@ -1,0 +1,250 @@
+"""Torch-facing wrappers of the C-ABI launches: tensor checks, then pointer-only dispatch.
+
+Mirrors the reference's operator level (``glm53/gfx950/runner.py:240-321``: shape /
+dtype / contiguity checks that raise ``ValueError`` naming the tensor, then raw
+pointers, scalars and the current stream go to the launcher).  All buffers are
+allocated when an op is built, never during a launch, so launches are safe under
+CUDA-graph capture (``deepseek_v41/gfx950/runner.py:127-132``).
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib as L
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _up(x: int, m: int) -> int:
+    return -(-x // m) * m
+
+
+def require(t: torch.Tensor, name: str, dtype=None, shape=None, cuda: bool = True) -> torch.Tensor:
+    if not isinstance(t, torch.Tensor):
+        raise ValueError(f"{name}: expected a tensor, got {type(t).__name__}")
+    if cuda and not t.is_cuda:
+        raise ValueError(f"{name}: must be a CUDA tensor (there is no CPU path)")
+    if dtype is not None and t.dtype != dtype:
+        raise ValueError(f"{name}: dtype {t.dtype}, needs {dtype}")
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise ValueError(f"{name}: shape {tuple(t.shape)}, needs {tuple(shape)}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name}: must be contiguous")
+    return t
+
+
+class ActBuf:
+    """Activation planes + scales of one GEMV operand ([segs][planes][16][ld] bytes)."""
+
+    def __init__(self, fmt: int, k: int, device, segs: int = 1):
+        self.fmt, self.k, self.segs = fmt, k, segs
+        self.nplanes = 2 if fmt == L.ACT_HILO else 1
+        kpad = _up(k, 256)  # room for the zero tail an MXFP4 tile may read
+        self.ld = 2 * kpad if fmt == L.ACT_BF16 else kpad
+        self.planes = torch.zeros(segs, self.nplanes, L.MAX_ROWS, self.ld, dtype=torch.uint8, device=device)
+        self.scale_f32 = self.scale_e8 = None
+        self.scale_ld = 0
+        if fmt in (L.ACT_A8, L.ACT_HILO):
+            self.scale_ld = _up(kpad // 128, 4) + 4
+            self.scale_f32 = torch.zeros(segs, L.MAX_ROWS, self.scale_ld, dtype=torch.float32, device=device)
+        elif fmt == L.ACT_MX8:
+            self.scale_ld = _up(kpad // 32, 16) + 16
+            self.scale_e8 = torch.full((segs, L.MAX_ROWS, self.scale_ld), 127, dtype=torch.uint8, device=device)
+
+    @property
+    def plane_stride(self) -> int:
+        return L.MAX_ROWS * self.ld
+
+    @property
+    def seg_stride(self) -> int:
+        return self.nplanes * L.MAX_ROWS * self.ld
+
+    @property
+    def scale_seg_stride(self) -> int:
+        return L.MAX_ROWS * self.scale_ld
+
+
+def act_prep(rows: int, k: int, dst: ActBuf | None, *, src_bf16=None, src_f32=None, nsum: int = 1,
+             gamma=None, eps: float = 0.0, round_bf16: bool = True, out_bf16=None) -> None:
+    """RMSNorm (optional) + quantisation of ``rows`` rows into ``dst`` (segment 0)."""
+    a = L.ActPrepArgs()
+    a.rows, a.k = rows, k
+    a.src_bf16, a.src_f32 = _p(src_bf16), _p(src_f32)
+    if src_f32 is not None:
+        a.nsum, a.src_ld, a.src_sum_stride = nsum, src_f32.shape[-1], L.MAX_ROWS * src_f32.shape[-1]
+    a.gamma_bf16, a.eps, a.round_bf16 = _p(gamma), eps, int(round_bf16)
+    if dst is not None:
+        a.fmt, a.planes, a.plane_stride, a.ld = dst.fmt, _p(dst.planes), dst.plane_stride, dst.ld
+        a.scale_f32, a.scale_e8, a.scale_ld = _p(dst.scale_f32), _p(dst.scale_e8), dst.scale_ld
+    a.out_bf16 = _p(out_bf16)
+    L.check(L.load().mono_act_prep_launch(C.byref(a), _stream()), "mono_act_prep_launch")
+
+
+_TILE_K = {L.W_FP8: 128, L.W_BF16: 64, L.W_MXFP4: 256}
+_MAX_SEG_TILES = {L.W_FP8: 16, L.W_BF16: 16, L.W_MXFP4: 8}
+
+
+def plan_split(k_tiles: int, row_blocks: int, wkind: int, sms: int = 148):
+    """(split_tiles, nsplit): K splits of whole 4-tile groups so that row_blocks x
+    nsplit tasks cover the SMs about twice and a segment fits the activation slot."""
+    cap = _MAX_SEG_TILES[wkind]
+    want = max(1, -(-2 * sms // max(row_blocks, 1)))
+    split = min(cap, max(4, _up(-(-k_tiles // want), 4)))
+    if split >= k_tiles:
+        return k_tiles, 1
+    return split, -(-k_tiles // split)
+
+
+class Gemv:
+    """One persistent weight-streaming launch over up to four jobs (``mono_gemv_launch``)."""
+
+    def __init__(self, wkind: int, guard: torch.Tensor | None = None):
+        self.wkind = wkind
+        self.args = L.GemvArgs()
+        self.args.wkind = wkind
+        self.args.guard = _p(guard)
+        self.args.njobs = 0
+        self._keep: list = [guard]
+
+    def _w3(self, w: torch.Tensor, name: str) -> torch.Tensor:
+        if w.dim() == 2:
+            w = w.unsqueeze(0)
+        if w.dim() != 3 or not w.is_contiguous() or not w.is_cuda:
+            raise ValueError(f"{name}: needs a contiguous CUDA [mats, rows, K] weight")
+        return w
+
+    def add(self, name: str, w: torch.Tensor, act: ActBuf, out: torch.Tensor, *, mode: int = L.JOB_DENSE,
+            wscale: torch.Tensor | None = None, n_rows: int | None = None, row_off: int = 0,
+            rb_per_mat: int = 0, n_mats: int = 0, nsplit: int | None = None, split_tiles: int | None = None,
+            out_slice: int = 0, expert_list=None, n_expert=None, max_expert: int = 0, coef=None,
+            act_per_mat: bool = False) -> int:
+        """Adds a job; returns the number of output slices (partial sums) it writes."""
+        j = self.args.njobs
+        if j >= L.GEMV_MAX_JOBS:
+            raise ValueError("a launch holds at most four jobs")
+        w = self._w3(w, name)
+        mats, rows_total, kb = w.shape[0], w.shape[1], w.shape[2] * w.element_size()
+        job = self.args.job[j]
+        L.check(L.load().mono_tmap_encode(C.byref(job.tmap), w.data_ptr(), kb, rows_total, mats, kb,
+                                          rows_total * kb), f"mono_tmap_encode({name})")
+        k_tiles = -(-kb // 128)
+        n_rows = rows_total - row_off if n_rows is None else n_rows
+        job.mode, job.n_rows, job.k_tiles, job.row_off = mode, n_rows, k_tiles, row_off
+        job.rb_per_mat, job.n_mats = rb_per_mat, n_mats
+        nrb = (n_mats * rb_per_mat) if rb_per_mat else -(-n_rows // 128)
+        if mode == L.JOB_EXPERT_DOWN:
+            if k_tiles > 32:
+                raise ValueError(f"{name}: a down projection spans {k_tiles} tiles, at most 32")
+            job.split_tiles = k_tiles
+            job.nsplit = nsplit or max(1, min(max_expert, -(-2 * 148 // nrb)))
+        else:
+            tasks_rb = nrb * (max_expert if mode == L.JOB_EXPERT_UP else 1)
+            st, ns = plan_split(k_tiles, tasks_rb, self.wkind)
+            job.split_tiles = split_tiles or st
+            job.nsplit = nsplit or -(-k_tiles // job.split_tiles)
+        if self.wkind == L.W_FP8:
+            ws = require(wscale, name + ".scale", torch.float32)
+            ws3 = ws if ws.dim() == 3 else ws.unsqueeze(0)
+            job.wscale_f32, job.wscale_mat_stride, job.wscale_ld = ws.data_ptr(), ws3.shape[1] * ws3.shape[2], ws3.shape[2]
+            if ws3.shape[2] < k_tiles or ws3.shape[1] * 128 < rows_total:
+                raise ValueError(f"{name}.scale: shape {tuple(ws.shape)} does not cover the weight")
+        elif self.wkind == L.W_MXFP4:
+            ws = require(wscale, name + ".scale", torch.uint8)
+            ws3 = ws if ws.dim() == 3 else ws.unsqueeze(0)
+            job.wscale_e8, job.wscale_mat_stride, job.wscale_ld = ws.data_ptr(), ws3.shape[1] * ws3.shape[2], ws3.shape[2]
+        job.act, job.planes, job.act_plane_stride, job.act_ld = _p(act.planes), act.nplanes, act.plane_stride, act.ld
+        per_seg = act_per_mat or mode == L.JOB_EXPERT_DOWN
+        job.act_seg_stride = act.seg_stride if per_seg else 0
+        job.ascale_f32, job.ascale_e8, job.ascale_ld = _p(act.scale_f32), _p(act.scale_e8), act.scale_ld
+        job.ascale_seg_stride = act.scale_seg_stride if per_seg else 0
+        job.coef = _p(coef)
+        job.expert_list, job.n_expert, job.max_expert = _p(expert_list), _p(n_expert), max_expert
+        out_ld = out.shape[-1]
+        slice_elems = L.MAX_ROWS * out_ld
+        job.out = out.data_ptr() + out_slice * slice_elems * 4
+        job.out_ld, job.out_split_stride = out_ld, slice_elems
+        n_slices = job.nsplit * (max_expert if mode == L.JOB_EXPERT_UP else 1)
+        if out.dtype != torch.float32 or out.numel() < (out_slice + n_slices) * slice_elems:
+            raise ValueError(f"{name}: output buffer holds {out.numel()} f32, needs {(out_slice + n_slices) * slice_elems}")
+        self._keep += [w, wscale, act, out, expert_list, n_expert, coef]
+        self.args.njobs = j + 1
+        return job.nsplit
+
+    def launch(self, rows: int) -> None:
+        self.args.rows = rows
+        L.check(L.load().mono_gemv_launch(C.byref(self.args), _stream()), "mono_gemv_launch")
+
+
+def rowdot(rows: int, w: torch.Tensor, x_bf16: torch.Tensor, out: torch.Tensor, out_scale: float = 1.0) -> None:
+    a = L.RowdotArgs()
+    a.rows, a.n, a.k = rows, w.shape[0], w.shape[1]
+    a.w, a.w_is_f32 = w.data_ptr(), int(w.dtype == torch.float32)
+    if w.dtype not in (torch.float32, torch.bfloat16):
+        raise ValueError(f"rowdot weight dtype {w.dtype}")
+    a.x_bf16, a.out, a.out_ld, a.out_scale = x_bf16.data_ptr(), out.data_ptr(), out.shape[-1], out_scale
+    L.check(L.load().mono_rowdot_launch(C.byref(a), _stream()), "mono_rowdot_launch")
+
+
+def reduce_rows(rows: int, n: int, partial: torch.Tensor, nsum: int, out: torch.Tensor, *, residual=None,
+                slots=None, peer=None, site: int = 0, guard=None, deadline_s: float = 5.0) -> None:
+    """Adds the partial slices, all-reduces across ranks in rank order, adds the residual."""
+    a = L.ReduceArgs()
+    a.rows, a.n, a.partial, a.nsum, a.ld = rows, n, partial.data_ptr(), nsum, partial.shape[-1]
+    a.sum_stride = L.MAX_ROWS * partial.shape[-1]
+    a.residual, a.slots, a.out = _p(residual), _p(slots), out.data_ptr()
+    a.world, a.rank = 1, 0
+    if peer is not None and peer.world > 1:
+        a.world, a.rank = peer.world, peer.rank
+        a.peer_ptrs = peer.region_table(site).data_ptr()
+        a.peer_guards = peer.guard_table.data_ptr()
+        a.tag, a.parity = 0, 0
+        a.deadline_ns = int(deadline_s * 1e9)
+    a.site, a.guard = site, _p(guard)
+    L.check(L.load().mono_reduce_launch(C.byref(a), _stream()), "mono_reduce_launch")
+
+
+def sparse_mla(q, kv_pages, topk_slots, out, scratch, sm_scale: float, topk: int | None = None) -> None:
+    rows, heads = q.shape[0], q.shape[1]
+    a = L.SparseMlaArgs()
+    a.rows, a.heads, a.topk, a.topk_ld = rows, heads, topk or topk_slots.shape[1], topk_slots.shape[1]
+    a.sm_scale = sm_scale
+    a.q, a.kv_pages, a.n_pages = q.data_ptr(), kv_pages.data_ptr(), kv_pages.shape[0]
+    a.topk_slots, a.out, a.scratch = topk_slots.data_ptr(), out.data_ptr(), scratch.data_ptr()
+    L.check(L.load().mono_sparse_mla_launch(C.byref(a), _stream()), "mono_sparse_mla_launch")
+
+
+def guard_read(guard: torch.Tensor):
+    out = (C.c_int32 * 3)()
+    rc = L.load().mono_guard_read(guard.data_ptr(), C.byref(out), _stream())
+    return rc, tuple(out)
+
+
+def route(rows: int, cfg_top_k: int, route_scale: float, logits, bias, slots, ids, weights, scores,
+          expert_list, n_expert, coef) -> None:
+    a = L.RouteArgs()
+    a.rows, a.n_experts, a.top_k, a.route_scale = rows, logits.shape[-1], cfg_top_k, route_scale
+    a.logits, a.nsum, a.ld, a.sum_stride = logits.data_ptr(), 1, logits.shape[-1], 0
+    a.bias, a.slots = _p(bias), _p(slots)
+    a.ids, a.weights, a.scores = ids.data_ptr(), weights.data_ptr(), _p(scores)
+    a.expert_list, a.n_expert, a.coef = expert_list.data_ptr(), n_expert.data_ptr(), coef.data_ptr()
+    L.check(L.load().mono_route_launch(C.byref(a), _stream()), "mono_route_launch")
+
+
+def mid(rows: int, inter: int, up: torch.Tensor, nsum: int, dst: ActBuf, *, n_slot=None, max_slot: int = 1,
+        round_bf16: bool = False) -> None:
+    a = L.MidArgs()
+    a.rows, a.inter, a.up, a.nsum = rows, inter, up.data_ptr(), nsum
+    a.n_slot, a.max_slot = _p(n_slot), max_slot
+    a.fmt, a.round_bf16 = dst.fmt, int(round_bf16)
+    a.planes, a.ld = dst.planes.data_ptr(), dst.ld
+    a.scale_f32, a.scale_e8, a.scale_ld = _p(dst.scale_f32), _p(dst.scale_e8), dst.scale_ld
+    L.check(L.load().mono_mid_launch(C.byref(a), _stream()), "mono_mid_launch")

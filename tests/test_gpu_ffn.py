@@ -1,0 +1,111 @@
+"""MoE FFN block on the GPU through the C ABI against the CPU oracle (BASELINE config 1
+and the FP8 block-scaled expert path of config 3 at a small size)."""
+
+from dataclasses import replace
+
+import pytest
+import torch
+
+from oracle import layers as OL
+from oracle import quant as Q
+from oracle import stages as S
+from sgl_amd_mono_b200 import _lib as L
+from sgl_amd_mono_b200 import ops, synth
+from sgl_amd_mono_b200.config import CFG_FFN_MXFP4, CFG_TINY, CFG_TINY_FFN
+from util import assert_close_hidden
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+CFG_TINY_MOE8 = replace(CFG_TINY, name="tiny_moe_fp8", n_heads=0, index_heads=0)
+
+
+def _cpu(w):
+    return {k: (v.cpu() if isinstance(v, torch.Tensor) else v) for k, v in w.items()}
+
+
+def _run(cfg, rows, seed=0, pad=()):
+    from sgl_amd_mono_b200.moe import MoeFfn
+
+    w = synth.layer_weights(cfg, 0, DEV)
+    x = torch.randn(rows, cfg.hidden, generator=torch.Generator().manual_seed(seed)).bfloat16()
+    slots = torch.arange(1, rows + 1, dtype=torch.int64)
+    for r in pad:
+        slots[r] = -1
+    ffn = MoeFfn(cfg, w, DEV)
+    out = ffn(x.to(DEV), slots.to(DEV)).clone()
+    torch.cuda.synchronize()
+    rc, words = ops.guard_read(ffn.guard)
+    assert rc == 0, f"guard words {words}"
+    return ffn, w, x, slots, out
+
+
+@pytest.mark.parametrize("cfg,rows", [(CFG_TINY_FFN, 1), (CFG_TINY_FFN, 4), (CFG_TINY_FFN, 11),
+                                      (CFG_TINY_MOE8, 1), (CFG_TINY_MOE8, 8), (CFG_TINY_MOE8, 16),
+                                      (CFG_FFN_MXFP4, 4)])
+def test_ffn_block_matches_oracle(cfg, rows):
+    ffn, w, x, slots, out = _run(cfg, rows)
+    wc = _cpu(w)
+    ref, det = OL.ffn_block(cfg, [wc], x)
+    # routing is exact given the kernel's own scores: ties to the lower id, weights renormalised
+    scores = ffn.scores[:rows].cpu()
+    ids, wts = S.route_from_scores(scores, wc.get("router_bias"), cfg.top_k, cfg.route_scale)
+    assert torch.equal(ffn.ids[:rows].cpu(), ids)
+    assert torch.allclose(ffn.weights[:rows].cpu(), wts, rtol=1e-5, atol=1e-7)
+    assert torch.allclose(scores, torch.sigmoid(det["logits"]), atol=1e-4)
+    assert torch.equal(ids, det["ids"]), "a near-tie flipped between the f32 logit sums: pick another seed"
+    n = int(ffn.n_expert.item())
+    assert ffn.expert_list[:n].cpu().tolist() == sorted(set(ids.flatten().tolist()))
+    assert_close_hidden(out, ref, f"{cfg.name} rows={rows}")
+
+
+def test_pad_rows_contribute_nothing():
+    cfg = CFG_TINY_MOE8
+    ffn, w, x, slots, out = _run(cfg, 4, pad=(1,))
+    assert torch.equal(out[1].cpu(), x[1]), "a pad row must come back as its residual"
+    assert ffn.ids[1].cpu().tolist() == [-1] * cfg.top_k
+    ref, _ = OL.ffn_block(cfg, [_cpu(w)], x)
+    keep = [0, 2, 3]
+    assert_close_hidden(out[keep], ref[keep], "live rows beside a pad row")
+
+
+def test_replays_are_bit_equal():
+    cfg = CFG_TINY_MOE8
+    ffn, w, x, slots, out = _run(cfg, 8)
+    xd, sd = x.to(DEV), slots.to(DEV)
+    for _ in range(5):
+        again = ffn(xd, sd)
+        torch.cuda.synchronize()
+        assert torch.equal(again, out)
+    # a perturbed input must change the output (negative control)
+    x2 = xd.clone()
+    x2[0, 0] += 1.0
+    assert not torch.equal(ffn(x2, sd), out)
+
+
+@pytest.mark.parametrize("fmt", [L.ACT_A8, L.ACT_HILO, L.ACT_MX8, L.ACT_BF16])
+def test_activation_formats_are_bit_exact(fmt):
+    rows, k = 5, 512
+    x = (torch.randn(rows, k, generator=torch.Generator().manual_seed(7)) * 2).bfloat16()
+    x[2, 128:256] = 0  # an all-zero chunk
+    buf = ops.ActBuf(fmt, k, DEV)
+    ops.act_prep(rows, k, buf, src_bf16=x.to(DEV), round_bf16=False)
+    torch.cuda.synchronize()
+    planes = buf.planes[0, :, :rows, : (2 * k if fmt == L.ACT_BF16 else k)].cpu()
+    if fmt == L.ACT_A8:
+        q, sc = Q.act_quant_128(x)
+        assert torch.equal(planes[0], Q.e4m3_bytes(q))
+        assert torch.equal(buf.scale_f32[0, :rows, : k // 128].cpu(), sc)
+    elif fmt == L.ACT_HILO:
+        hi, lo, sc = Q.split_hi_lo(x)
+        assert torch.equal(planes[0], Q.e4m3_bytes(hi)) and torch.equal(planes[1], Q.e4m3_bytes(lo))
+        assert torch.equal(buf.scale_f32[0, :rows, : k // 128].cpu(), sc)
+    elif fmt == L.ACT_MX8:
+        q, code = Q.mxfp8_quant(x)
+        perm = torch.tensor([0, 2, 4, 6, 1, 3, 5, 7])
+        want = Q.e4m3_bytes(q).reshape(rows, k // 8, 8)[:, :, perm].reshape(rows, k)
+        assert torch.equal(planes[0], want)
+        assert torch.equal(buf.scale_e8[0, :rows, : k // 32].cpu(), code)
+    else:
+        assert torch.equal(planes[0].contiguous().view(torch.bfloat16), x)
+    # rows past the step stay zero
+    assert int(buf.planes[0, :, rows:].abs().sum()) == 0

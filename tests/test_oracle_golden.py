@@ -1,0 +1,99 @@
+"""The oracle against the fixtures generated from the reference's own host functions
+(tests/golden/make_golden.py) and against its documented number-format rules."""
+
+import torch
+
+from oracle import host as H
+from oracle import quant as Q
+from oracle import stages as S
+
+
+def test_radix_keys_match_reference(golden):
+    assert torch.equal(S.radix_key(golden["radix_bits"]), golden["radix_keys"])
+
+
+def test_radix_order_is_score_order(golden):
+    scores = golden["radix_bits"].view(torch.float32)
+    keys = S.radix_key(golden["radix_bits"])
+    order = torch.argsort(keys, descending=True, stable=True)
+    s = scores[order]
+    assert bool((s[:-1] >= s[1:]).all())
+
+
+def test_e8m0_codes_match_reference(golden):
+    assert torch.equal(H.e8m0_code(golden["e8m0_scale"]), golden["e8m0_code"])
+    # the same codes through the round-up rule used for activations
+    assert torch.equal(Q.code_ceil(golden["e8m0_scale"]).to(torch.uint8), golden["e8m0_code"])
+
+
+def test_mxfp8_exact_matches_reference(golden):
+    q, code = H.mxfp8_exact_32x32(golden["mx8_w"])
+    assert torch.equal(q, golden["mx8_q"])
+    assert torch.equal(code, golden["mx8_code"])
+
+
+def test_rope_table_layout_matches_reference(golden):
+    assert torch.equal(H.rope_table_f32(golden["rope_freqs_cis"]), golden["rope_table"])
+    cos, sin = S.rope_table(16, 64, 10000.0)
+    ref = golden["rope_table"]
+    assert torch.allclose(cos.float(), ref[:, :32], atol=4e-3)
+    assert torch.allclose(sin.float(), ref[:, 32:], atol=4e-3)
+
+
+def test_tail_matches_reference(golden):
+    got = S.tail_logits(golden["tail_x"], golden["tail_gamma"], 1e-6, golden["tail_w"])
+    assert torch.allclose(got, golden["tail_logits"], rtol=1e-5, atol=1e-6)
+
+
+def test_causal_rows_match_reference(golden):
+    a = golden["rows_in"]
+    table, lens = H.causal_rows(a["req_to_token"], a["pool"], a["seq_lens"], a["cols"], a["slot_mapping"],
+                                a["query_len"], True, a["max_context_len"])
+    assert torch.equal(table, golden["rows_block_table"])
+    assert torch.equal(lens, golden["rows_seq_lens"])
+
+
+def test_select_slices_match_reference(golden):
+    for b, want in zip(golden["slice_bounds"], golden["slices"]):
+        assert H.select_slices(b) == tuple(want)
+
+
+def test_e2m1_round_to_nearest_even():
+    v = torch.tensor([0.0, 0.24, 0.25, 0.26, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 5.01, 7.0, -0.25, -0.75, -9.0])
+    want = torch.tensor([0.0, 0.0, 0.0, 0.5, 1.0, 1.0, 2.0, 2.0, 4.0, 4.0, 6.0, 6.0, -0.0, -1.0, -6.0])
+    assert torch.equal(Q.e2m1_decode(Q.e2m1_encode(v)), want)
+
+
+def test_mxfp4_roundtrip_and_packing():
+    g = torch.Generator().manual_seed(1)
+    w = torch.randn(8, 64, generator=g) * 0.02
+    packed, code = Q.mxfp4_quant(w)
+    assert packed.shape == (8, 32) and code.shape == (8, 2)
+    deq = Q.mxfp4_dequant(packed, code)
+    # every block's amax maps into (3, 6] and the error is at most half a step of the top binade
+    assert float((deq - w).abs().max()) <= float(w.abs().max()) / 6.0 + 1e-9
+    # even index sits in the low nibble
+    lo = Q.e2m1_decode(packed & 15) * Q.exp2_code(code).repeat_interleave(16, -1)
+    assert torch.equal(lo, deq[:, 0::2])
+
+
+def test_split_hi_lo_reproduces_bf16():
+    g = torch.Generator().manual_seed(2)
+    x = (torch.randn(4, 512, generator=g) * 3).bfloat16().float()
+    hi, lo, sc = Q.split_hi_lo(x)
+    rec = ((hi + lo).reshape(4, 4, 128) * sc[..., None]).reshape(4, 512)
+    assert float((rec - x).abs().max()) <= float(x.abs().max()) * 2.0**-9
+
+
+def test_exact_topk_order_and_ties():
+    sc = torch.tensor([1.0, 5.0, 3.0, 5.0, 3.0, 3.0, 0.5])
+    # k = 4: above threshold 3.0 are positions 1, 3 (in order); ties 2, 4, 5 -> first two
+    assert S.exact_topk_positions(sc, 7, 4).tolist() == [1, 3, 2, 4]
+    assert S.exact_topk_positions(sc, 3, 4).tolist() == [0, 1, 2]
+
+
+def test_route_ties_to_lower_id():
+    logits = torch.zeros(1, 8)
+    ids, w = S.route(logits, None, 3, 2.5)
+    assert ids.tolist() == [[0, 1, 2]]
+    assert torch.allclose(w, torch.full((1, 3), 2.5 / 3))
