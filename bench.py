@@ -57,6 +57,9 @@ class ClockSampler:
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            t0 = time.time()
+            while not self.lines and time.time() - t0 < 5.0:  # nvidia-smi takes a moment to start
+                time.sleep(0.02)
         except OSError:
             self.proc = None
         return self
@@ -327,7 +330,13 @@ def main() -> None:
 
     barrier()
     sampler = ClockSampler(local)
-    total_ms = time_steps(wl.step, args.steps, args.warmup, flush, sampler)
+    sampler.__enter__()
+    t_load = time.time()
+    while time.time() - t_load < 0.6:  # keep the GPU under load so the clock samples mean something
+        for _ in range(20):
+            wl.step()
+        torch.cuda.synchronize()
+    total_ms = time_steps(wl.step, args.steps, args.warmup, flush)
     barrier()
     t = torch.tensor([total_ms], device=dev)
     if dist is not None:
@@ -351,6 +360,7 @@ def main() -> None:
     # roofline of the dominant kernel, timed alone
     nbytes, probe = wl.roofline_probe()
     probe_ms = time_steps(probe, args.steps, 3, flush) / args.steps
+    sampler.__exit__(None, None, None)
     peak, peak_src = measured_peaks()
     achieved = nbytes / (probe_ms * 1e-3) / 1e9
     line = {

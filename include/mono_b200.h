@@ -105,6 +105,12 @@ typedef struct mono_act_prep_args {
     uint8_t* scale_e8;  /* [16][scale_ld] */
     int scale_ld;
     void* out_bf16;     /* optional second output: bf16 [16][k] plain */
+    /* segments (0 or 1 = none): the source row holds `segs` vectors of k values (one per
+     * head); vector s of row r goes to activation set s: planes + s * seg_stride bytes,
+     * scales + s * scale_seg_stride elements */
+    int segs;
+    long seg_stride;
+    long scale_seg_stride;
 } mono_act_prep_args;
 int mono_act_prep_launch(const mono_act_prep_args* a, void* stream);
 
@@ -272,6 +278,96 @@ size_t mono_reduce_peer_bytes(int rows, int n, int world);
 int mono_reduce_launch(const mono_reduce_args* a, void* stream);
 /* Adds 1 to the epoch word on the device (glm53/gfx950/runner.py:209-210 advance_step). */
 int mono_epoch_advance_launch(int32_t* guard, void* stream);
+
+/* ---- attention front, after q_a|kv_a (glm53/gfx950/kernel.py:1978-2003 q_a RMSNorm,
+ * :2005-2101 KV RMSNorm + k_pe RoPE + cache write, :2103-2181 index key) -----------
+ * One CTA per row: adds the q_a|kv_a partial sums; q_a -> RMSNorm -> bf16 -> hi/lo
+ * planes for q_b; latent -> RMSNorm -> bf16, k_pe -> interleaved RoPE -> bf16; the
+ * 576 values are stored as E4M3 with the power-of-two token scale
+ * 2^ceil(log2(max(amax, 1e-4) / 448)) at the row's slot (slot < 0: no write).  With
+ * an indexer: index key -> LayerNorm -> RoPE on dims 0..63 -> FWHT-128 -> E2M1 with
+ * one E8M0 code per 32 -> index page.  kv_out / ik_out receive the values that were
+ * quantised (parity witnesses). */
+typedef struct mono_mla_mid_args {
+    int rows, q_lora;
+    const float* qkv; /* [nsum][16][ld]: q_lora | 512 latent | 64 rope */
+    int nsum, ld;
+    long sum_stride;
+    const float* ik; /* [ik_nsum][16][ik_ld] index-key projection, or NULL */
+    int ik_nsum, ik_ld;
+    long ik_sum_stride;
+    const void* q_a_norm;  /* bf16 [q_lora] */
+    const void* kv_a_norm; /* bf16 [512] */
+    float eps;
+    const float* ik_norm_w; /* f32 [128] */
+    const float* ik_norm_b;
+    const void* cos; /* bf16 [max_pos][32] */
+    const void* sin;
+    const int64_t* positions;
+    const int64_t* slots;
+    uint8_t* qa_planes; /* hi/lo planes [2][16][qa_ld] */
+    long qa_plane_stride;
+    int qa_ld;
+    float* qa_scale; /* [16][qa_scale_ld] */
+    int qa_scale_ld;
+    uint8_t* kv_pages;
+    uint8_t* idx_pages;
+    int64_t n_pages;
+    void* kv_out;  /* bf16 [16][576] */
+    float* ik_out; /* f32 [16][128] */
+} mono_mla_mid_args;
+int mono_mla_mid_launch(const mono_mla_mid_args* a, void* stream);
+
+/* ---- q after q_b (glm53/gfx950/kernel.py:2183-2353 q_b + RoPE + index q, :2355-2443
+ * W_UK absorb) ---------------------------------------------------------------------
+ * Adds the q_b partial sums; per head: q_nope -> bf16 -> q_lat = W_UK^T q_nope (kv_b
+ * rows [h*256, h*256+128) as block-FP8) -> bf16; q_pe -> RoPE -> bf16; q_full bf16
+ * [16][heads][576] = q_lat | q_pe.  Index queries: RoPE on dims 0..63, FWHT-128, bf16. */
+typedef struct mono_q_post_args {
+    int rows, heads;
+    const float* qb; /* [nsum][16][ld], per head 128 nope + 64 rope */
+    int nsum, ld;
+    long sum_stride;
+    const uint8_t* kv_b;     /* E4M3 [heads*256][512] */
+    const float* kv_b_scale; /* [heads*2][4] */
+    const void* cos;
+    const void* sin;
+    const int64_t* positions;
+    void* q_full; /* bf16 [16][heads][576] */
+    int index_heads;
+    const float* iq; /* [iq_nsum][16][iq_ld] or NULL */
+    int iq_nsum, iq_ld;
+    long iq_sum_stride;
+    void* idx_q; /* bf16 [16][index_heads][128] */
+} mono_q_post_args;
+int mono_q_post_launch(const mono_q_post_args* a, void* stream);
+
+/* ---- lightning indexer (glm53/gfx950/kernel.py:2684-3000 scores, :3002-3636 exact
+ * top-k; FP4 keys as deepseek_v4/gfx950/kernels/stages/indexer.py:143-151) ----------
+ * score[row][pos] = sum_h relu(q_h . key_pos) * w_h for pos <= positions[row], keys
+ * read through the row's page-table row.  Then the exact top-k of each row: radix
+ * select on the monotone image of the f32 bits, ties to the lowest position, output
+ * [keys above the threshold in position order] ++ [first ties in position order],
+ * published as global KV slots page * 64 + pos % 64 (-1 fills the tail; rows with at
+ * most topk keys keep every key in order; pad rows get -1 everywhere). */
+typedef struct mono_index_args {
+    int rows, index_heads, topk;
+    const void* idx_q;  /* bf16 [16][index_heads][128] */
+    const float* idx_w; /* f32 [16][w_ld] */
+    int w_ld;
+    const uint8_t* idx_pages;
+    int64_t n_pages;
+    const int32_t* page_table; /* [rows][pt_ld] */
+    int pt_ld;
+    const int64_t* positions;
+    const int64_t* slots;
+    float* scores; /* [16][score_ld] */
+    int score_ld;
+    int32_t* topk_slots; /* [16][topk] */
+    int32_t* topk_pos;   /* [16][topk] positions (parity witness) or NULL */
+} mono_index_args;
+int mono_index_score_launch(const mono_index_args* a, void* stream);
+int mono_index_topk_launch(const mono_index_args* a, void* stream);
 
 /* sizeof() of the argument structs, by index (0 gemv_job, 1 gemv_args, 2 act_prep,
  * 3 route, 4 mid, 5 sparse_mla, 6 reduce, 7 rowdot, ...): lets a binding check its mirror. */

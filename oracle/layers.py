@@ -62,8 +62,9 @@ def attn_front(cfg, w, h, positions, slots, cos, sin, kv_pages, idx_pages):
         iq = S.gemv_fp8_block(qa, *_w8(w, "idx_wq_b")).reshape(-1, cfg.index_heads, 128)
         iq = torch.cat([S.rope_interleaved(iq[..., :64], c, s), iq[..., 64:]], -1)
         r["idx_q"] = Q.bf(S.fwht128(iq))
-        wts = Q.bf(x.float() @ w["idx_wproj"].float().T)
-        r["idx_w"] = wts * (cfg.index_heads**-0.5) * (128**-0.5)
+        # head weights stay f32 (glm53/gfx950/kernel.py:1781-1970 hands weights_proj on in f32)
+        wts = x.float() @ w["idx_wproj"].float().T
+        r["idx_w"] = wts * ((cfg.index_heads**-0.5) * (128**-0.5))
     return r
 
 

@@ -55,6 +55,7 @@ class ActPrepArgs(C.Structure):
         ("src_sum_stride", i64), ("gamma_bf16", vp), ("eps", f32), ("round_bf16", i32),
         ("fmt", i32), ("planes", vp), ("plane_stride", i64), ("ld", i32), ("scale_f32", vp),
         ("scale_e8", vp), ("scale_ld", i32), ("out_bf16", vp),
+        ("segs", i32), ("seg_stride", i64), ("scale_seg_stride", i64),
     ]
 
 
@@ -98,7 +99,36 @@ class RowdotArgs(C.Structure):
     ]
 
 
-_STRUCTS = [GemvJob, GemvArgs, ActPrepArgs, RouteArgs, MidArgs, SparseMlaArgs, ReduceArgs, RowdotArgs]
+class MlaMidArgs(C.Structure):
+    _fields_ = [
+        ("rows", i32), ("q_lora", i32), ("qkv", vp), ("nsum", i32), ("ld", i32), ("sum_stride", i64),
+        ("ik", vp), ("ik_nsum", i32), ("ik_ld", i32), ("ik_sum_stride", i64),
+        ("q_a_norm", vp), ("kv_a_norm", vp), ("eps", f32), ("ik_norm_w", vp), ("ik_norm_b", vp),
+        ("cos", vp), ("sin", vp), ("positions", vp), ("slots", vp),
+        ("qa_planes", vp), ("qa_plane_stride", i64), ("qa_ld", i32), ("qa_scale", vp), ("qa_scale_ld", i32),
+        ("kv_pages", vp), ("idx_pages", vp), ("n_pages", C.c_int64), ("kv_out", vp), ("ik_out", vp),
+    ]
+
+
+class QPostArgs(C.Structure):
+    _fields_ = [
+        ("rows", i32), ("heads", i32), ("qb", vp), ("nsum", i32), ("ld", i32), ("sum_stride", i64),
+        ("kv_b", vp), ("kv_b_scale", vp), ("cos", vp), ("sin", vp), ("positions", vp), ("q_full", vp),
+        ("index_heads", i32), ("iq", vp), ("iq_nsum", i32), ("iq_ld", i32), ("iq_sum_stride", i64),
+        ("idx_q", vp),
+    ]
+
+
+class IndexArgs(C.Structure):
+    _fields_ = [
+        ("rows", i32), ("index_heads", i32), ("topk", i32), ("idx_q", vp), ("idx_w", vp), ("w_ld", i32),
+        ("idx_pages", vp), ("n_pages", C.c_int64), ("page_table", vp), ("pt_ld", i32), ("positions", vp),
+        ("slots", vp), ("scores", vp), ("score_ld", i32), ("topk_slots", vp), ("topk_pos", vp),
+    ]
+
+
+_STRUCTS = [GemvJob, GemvArgs, ActPrepArgs, RouteArgs, MidArgs, SparseMlaArgs, ReduceArgs, RowdotArgs,
+            MlaMidArgs, QPostArgs, IndexArgs]
 
 # every symbol include/mono_b200.h declares: name -> (restype, argtypes)
 SYMBOLS = {
@@ -117,6 +147,10 @@ SYMBOLS = {
     "mono_reduce_peer_bytes": (C.c_size_t, [i32, i32, i32]),
     "mono_reduce_launch": (i32, [C.POINTER(ReduceArgs), vp]),
     "mono_epoch_advance_launch": (i32, [vp, vp]),
+    "mono_mla_mid_launch": (i32, [C.POINTER(MlaMidArgs), vp]),
+    "mono_q_post_launch": (i32, [C.POINTER(QPostArgs), vp]),
+    "mono_index_score_launch": (i32, [C.POINTER(IndexArgs), vp]),
+    "mono_index_topk_launch": (i32, [C.POINTER(IndexArgs), vp]),
     "mono_struct_size": (C.c_size_t, [i32]),
 }
 

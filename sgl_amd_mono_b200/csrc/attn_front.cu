@@ -1,0 +1,289 @@
+// Attention front stages between the projections: q_a / KV norms, RoPE, the FP8 KV
+// cache write, the FP4 index-key write, q post-processing and the W_UK absorb.
+//
+// Reference counterparts: glm53/gfx950/kernel.py:1978-2003 (q_a RMSNorm), :2005-2101
+// (KV RMSNorm, k_pe RoPE, cache row write), :2103-2181 (index key: LayerNorm, RoPE,
+// Hadamard, scale + quantise), :2183-2353 (q_b epilogue: RoPE, index q), :2355-2443
+// (W_UK absorb); FP4 key format of deepseek_v4/gfx950/kernels/stages/indexer.py:143-151.
+#include "mono_common.cuh"
+
+extern void mono_set_error(const char* fmt, ...);
+
+namespace mono {
+
+constexpr int kMidThreads2 = 256;
+
+// hi/lo E4M3 planes of 128 bf16-valued floats held 4 per lane (see MONO_ACT_HILO)
+__device__ __forceinline__ void hilo_chunk(const float v[4], int lane, uint8_t* hi, uint8_t* lo, float* scale) {
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    amax = warp_max(amax);
+    const int code = code_ceil(fmaxf(amax, 7.888609052210118e-31f) / 448.f);
+    const float inv = exp2_code(254 - code);
+    uint32_t wh = 0, wl = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float s = v[i] * inv;
+        const uint8_t h = f32_to_e4m3(s);
+        const uint8_t l = f32_to_e4m3(s - e4m3_to_f32(h));
+        wh |= (uint32_t)h << (8 * i);
+        wl |= (uint32_t)l << (8 * i);
+    }
+    reinterpret_cast<uint32_t*>(hi)[lane] = wh;
+    reinterpret_cast<uint32_t*>(lo)[lane] = wl;
+    if (lane == 0) *scale = exp2_code(code);
+}
+
+// In-place orthonormal FWHT over 128 floats in shared memory by 128 threads
+// (Sylvester order: butterflies of span 1, 2, 4 ... 64, then * 128^-1/2).
+__device__ __forceinline__ void fwht128(float* x, int t /* 0..127 */) {
+#pragma unroll
+    for (int h = 1; h < 128; h <<= 1) {
+        __syncthreads();
+        const float a = x[t & ~h], b = x[t | h];
+        __syncthreads();
+        x[t] = (t & h) ? a - b : a + b;
+    }
+    __syncthreads();
+    x[t] *= 0.08838834764831845f;
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(kMidThreads2) mla_mid_kernel(const mono_mla_mid_args a) {
+    __shared__ float xq[2048 + 64];
+    __shared__ float kv[kKvDim];
+    __shared__ float ikv[128];
+    __shared__ float red[kMidThreads2 / 32];
+    const int row = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int64_t pos = a.positions[row];
+    const int64_t slot = a.slots ? a.slots[row] : 1;
+    const float* src = a.qkv + (size_t)row * a.ld;
+    // ---- q_a: RMSNorm -> bf16 -> hi/lo planes
+    float ssq = 0.f;
+    for (int i = tid; i < a.q_lora; i += kMidThreads2) {
+        float v = 0.f;
+        for (int s = 0; s < a.nsum; ++s) v += src[(size_t)s * a.sum_stride + i];
+        xq[i] = v;
+        ssq += v * v;
+    }
+    {
+        const float r = rsqrtf(block_sum<kMidThreads2 / 32>(ssq, red) / (float)a.q_lora + a.eps);
+        const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(a.q_a_norm);
+        for (int i = tid; i < a.q_lora; i += kMidThreads2) xq[i] = bf16_round(xq[i] * r * __bfloat162float(g[i]));
+    }
+    __syncthreads();
+    for (int c = warp; c < a.q_lora / 128; c += kMidThreads2 / 32) {
+        float v[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = xq[c * 128 + 4 * lane + i];
+        uint8_t* hi = a.qa_planes + (size_t)row * a.qa_ld + c * 128;
+        hilo_chunk(v, lane, hi, hi + a.qa_plane_stride, a.qa_scale + (size_t)row * a.qa_scale_ld + c);
+    }
+    // ---- latent: RMSNorm -> bf16; k_pe: interleaved RoPE -> bf16
+    ssq = 0.f;
+    for (int i = tid; i < kKvDim; i += kMidThreads2) {
+        float v = 0.f;
+        for (int s = 0; s < a.nsum; ++s) v += src[(size_t)s * a.sum_stride + a.q_lora + i];
+        kv[i] = v;
+        if (i < 512) ssq += v * v;
+    }
+    {
+        const float r = rsqrtf(block_sum<kMidThreads2 / 32>(ssq, red) / 512.f + a.eps);
+        const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(a.kv_a_norm);
+        float rot0 = 0.f, rot1 = 0.f;
+        if (tid < 32) {
+            const float c = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.cos)[pos * 32 + tid]);
+            const float s = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.sin)[pos * 32 + tid]);
+            const float x0 = kv[512 + 2 * tid], x1 = kv[512 + 2 * tid + 1];
+            rot0 = x0 * c - x1 * s;
+            rot1 = x0 * s + x1 * c;
+        }
+        __syncthreads();
+        for (int i = tid; i < 512; i += kMidThreads2) kv[i] = bf16_round(kv[i] * r * __bfloat162float(g[i]));
+        if (tid < 32) {
+            kv[512 + 2 * tid] = bf16_round(rot0);
+            kv[512 + 2 * tid + 1] = bf16_round(rot1);
+        }
+    }
+    __syncthreads();
+    float amax = 0.f;
+    for (int i = tid; i < kKvDim; i += kMidThreads2) amax = fmaxf(amax, fabsf(kv[i]));
+    amax = block_max<kMidThreads2 / 32>(amax, red);
+    if (a.kv_out) {
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(a.kv_out) + (size_t)row * kKvDim;
+        for (int i = tid; i < kKvDim; i += kMidThreads2) o[i] = __float2bfloat16_rn(kv[i]);
+    }
+    if (slot >= 0 && slot < a.n_pages * kPage) {
+        const int code = code_ceil(fmaxf(amax, 1e-4f) / 448.f);
+        const float inv = exp2_code(254 - code);
+        uint8_t* page = a.kv_pages + (size_t)(slot / kPage) * kKvPageBytes;
+        const int off = (int)(slot % kPage);
+        if (tid < kKvDim / 4) {
+            uint32_t w = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) w |= (uint32_t)f32_to_e4m3(kv[4 * tid + i] * inv) << (8 * i);
+            reinterpret_cast<uint32_t*>(page + (size_t)off * kKvDim)[tid] = w;
+        }
+        if (tid == 0) reinterpret_cast<float*>(page + kPage * kKvDim)[off] = exp2_code(code);
+    }
+    // ---- index key: LayerNorm -> RoPE (dims 0..63) -> FWHT-128 -> E2M1 + E8M0 per 32
+    if (a.ik) {
+        __syncthreads();
+        float v = 0.f;
+        if (tid < 128) {
+            for (int s = 0; s < a.ik_nsum; ++s) v += a.ik[(size_t)s * a.ik_sum_stride + (size_t)row * a.ik_ld + tid];
+        }
+        const float mean = block_sum<kMidThreads2 / 32>(tid < 128 ? v : 0.f, red) / 128.f;
+        const float dv = tid < 128 ? v - mean : 0.f;
+        const float var = block_sum<kMidThreads2 / 32>(dv * dv, red) / 128.f;
+        if (tid < 128) ikv[tid] = dv * rsqrtf(var + 1e-6f) * a.ik_norm_w[tid] + a.ik_norm_b[tid];
+        __syncthreads();
+        float r0 = 0.f, r1 = 0.f;
+        if (tid < 32) {
+            const float c = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.cos)[pos * 32 + tid]);
+            const float s = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.sin)[pos * 32 + tid]);
+            const float x0 = ikv[2 * tid], x1 = ikv[2 * tid + 1];
+            r0 = x0 * c - x1 * s;
+            r1 = x0 * s + x1 * c;
+        }
+        __syncthreads();
+        if (tid < 32) { ikv[2 * tid] = r0; ikv[2 * tid + 1] = r1; }
+        // all 256 threads take part in the barriers; threads >= 128 mirror thread - 128
+        fwht128(ikv, tid & 127);
+        if (tid < 128) {
+            const float x = ikv[tid];
+            if (a.ik_out) a.ik_out[(size_t)row * 128 + tid] = x;
+            float am = fabsf(x);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+            const int code = min(max(code_ceil(fmaxf(am, 6.0f * 1.1754943508222875e-38f) / 6.0f), 1), 254);
+            const float q = fminf(fmaxf(x * exp2_code(254 - code), -6.f), 6.f);
+            const uint32_t nib = f32_to_e2m1(q);
+            const uint32_t other = __shfl_xor_sync(0xffffffffu, nib, 1);
+            if (slot >= 0 && slot < a.n_pages * kPage) {
+                uint8_t* page = a.idx_pages + (size_t)(slot / kPage) * kIdxPageBytes;
+                const int off = (int)(slot % kPage);
+                if ((tid & 1) == 0) page[(size_t)off * 64 + (tid >> 1)] = (uint8_t)(nib | (other << 4));
+                if ((tid & 31) == 0) page[kPage * 64 + off * 4 + (tid >> 5)] = (uint8_t)code;
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------ q_post
+// blocks [0, heads): one head each, all rows: q_nope -> bf16, W_UK absorb, q_pe RoPE.
+// blocks [heads, heads + rows * index_heads): one index query each.
+constexpr int kQPostThreads = 128;
+
+__global__ void __launch_bounds__(kQPostThreads) q_post_kernel(const mono_q_post_args a) {
+    __shared__ float qn[kMaxRows][128];
+    __shared__ float iq[128];
+    const int tid = threadIdx.x;
+    const __nv_bfloat16* cosb = reinterpret_cast<const __nv_bfloat16*>(a.cos);
+    const __nv_bfloat16* sinb = reinterpret_cast<const __nv_bfloat16*>(a.sin);
+    if ((int)blockIdx.x < a.heads) {
+        const int h = blockIdx.x;
+        __nv_bfloat16* qf = reinterpret_cast<__nv_bfloat16*>(a.q_full);
+        for (int r = 0; r < a.rows; ++r) {
+            const float* src = a.qb + (size_t)r * a.ld + h * 192;
+            float v = 0.f;
+            for (int s = 0; s < a.nsum; ++s) v += src[(size_t)s * a.sum_stride + tid];
+            qn[r][tid] = bf16_round(v);
+            if (tid < 32) {
+                float x0 = 0.f, x1 = 0.f;
+                for (int s = 0; s < a.nsum; ++s) {
+                    x0 += src[(size_t)s * a.sum_stride + 128 + 2 * tid];
+                    x1 += src[(size_t)s * a.sum_stride + 128 + 2 * tid + 1];
+                }
+                const int64_t pos = a.positions[r];
+                const float c = __bfloat162float(cosb[pos * 32 + tid]), sn = __bfloat162float(sinb[pos * 32 + tid]);
+                __nv_bfloat16* o = qf + ((size_t)r * a.heads + h) * kKvDim + 512;
+                o[2 * tid] = __float2bfloat16_rn(x0 * c - x1 * sn);
+                o[2 * tid + 1] = __float2bfloat16_rn(x0 * sn + x1 * c);
+            }
+        }
+        __syncthreads();
+        // q_lat[c] = sum_d W_UK[d][c] * q_nope[d]; thread owns columns 4*tid .. 4*tid+3
+        float acc[kMaxRows][4];
+#pragma unroll
+        for (int r = 0; r < kMaxRows; ++r)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[r][i] = 0.f;
+        const uint8_t* wbase = a.kv_b + (size_t)h * 256 * 512 + 4 * tid;
+#pragma unroll 4
+        for (int d = 0; d < 128; ++d) {
+            const uint32_t w4 = __ldg(reinterpret_cast<const uint32_t*>(wbase + (size_t)d * 512));
+            float w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) w[i] = e4m3_to_f32((uint8_t)(w4 >> (8 * i)));
+#pragma unroll
+            for (int r = 0; r < kMaxRows; ++r) {
+                if (r < a.rows) {
+                    const float q = qn[r][d];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) acc[r][i] += q * w[i];
+                }
+            }
+        }
+        const float sc = a.kv_b_scale[(size_t)(h * 2) * 4 + (4 * tid) / 128];
+#pragma unroll
+        for (int r = 0; r < kMaxRows; ++r) {
+            if (r < a.rows) {
+                __nv_bfloat16* o = qf + ((size_t)r * a.heads + h) * kKvDim + 4 * tid;
+                __nv_bfloat162 v0 = __floats2bfloat162_rn(acc[r][0] * sc, acc[r][1] * sc);
+                __nv_bfloat162 v1 = __floats2bfloat162_rn(acc[r][2] * sc, acc[r][3] * sc);
+                *reinterpret_cast<uint2*>(o) = make_uint2(*reinterpret_cast<uint32_t*>(&v0), *reinterpret_cast<uint32_t*>(&v1));
+            }
+        }
+    } else {
+        const int idx = blockIdx.x - a.heads;
+        const int r = idx / a.index_heads, ih = idx - r * a.index_heads;
+        const float* src = a.iq + (size_t)r * a.iq_ld + ih * 128;
+        float v = 0.f;
+        for (int s = 0; s < a.iq_nsum; ++s) v += src[(size_t)s * a.iq_sum_stride + tid];
+        iq[tid] = v;
+        __syncthreads();
+        float r0 = 0.f, r1 = 0.f;
+        if (tid < 32) {
+            const int64_t pos = a.positions[r];
+            const float c = __bfloat162float(cosb[pos * 32 + tid]), sn = __bfloat162float(sinb[pos * 32 + tid]);
+            const float x0 = iq[2 * tid], x1 = iq[2 * tid + 1];
+            r0 = x0 * c - x1 * sn;
+            r1 = x0 * sn + x1 * c;
+        }
+        __syncthreads();
+        if (tid < 32) { iq[2 * tid] = r0; iq[2 * tid + 1] = r1; }
+        fwht128(iq, tid);
+        reinterpret_cast<__nv_bfloat16*>(a.idx_q)[((size_t)r * a.index_heads + ih) * 128 + tid] = __float2bfloat16_rn(iq[tid]);
+    }
+}
+
+}  // namespace mono
+
+extern "C" int mono_mla_mid_launch(const mono_mla_mid_args* a, void* stream) {
+    if (!a || a->rows < 1 || a->rows > MONO_MAX_ROWS || a->q_lora < 128 || a->q_lora > 2048 || (a->q_lora & 127) || !a->qkv ||
+        !a->q_a_norm || !a->kv_a_norm || !a->cos || !a->sin || !a->positions || !a->qa_planes || !a->qa_scale || !a->kv_pages) {
+        mono_set_error("mono_mla_mid_launch: rows 1..16, q_lora a multiple of 128 up to 2048 and all pointers required");
+        return MONO_E_ARG;
+    }
+    if (a->ik && (!a->ik_norm_w || !a->ik_norm_b || !a->idx_pages)) {
+        mono_set_error("mono_mla_mid_launch: an index key needs its norm weights and the index pages");
+        return MONO_E_ARG;
+    }
+    mono::mla_mid_kernel<<<a->rows, mono::kMidThreads2, 0, (cudaStream_t)stream>>>(*a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) mono_set_error("mono_mla_mid_launch: %s", cudaGetErrorString(e));
+    return (int)e;
+}
+
+extern "C" int mono_q_post_launch(const mono_q_post_args* a, void* stream) {
+    if (!a || a->rows < 1 || a->rows > MONO_MAX_ROWS || a->heads < 1 || !a->qb || !a->kv_b || !a->kv_b_scale || !a->cos ||
+        !a->sin || !a->positions || !a->q_full || (a->index_heads > 0 && (!a->iq || !a->idx_q))) {
+        mono_set_error("mono_q_post_launch: rows 1..16, heads >= 1 and all pointers required");
+        return MONO_E_ARG;
+    }
+    const int blocks = a->heads + (a->index_heads > 0 ? a->rows * a->index_heads : 0);
+    mono::q_post_kernel<<<blocks, mono::kQPostThreads, 0, (cudaStream_t)stream>>>(*a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) mono_set_error("mono_q_post_launch: %s", cudaGetErrorString(e));
+    return (int)e;
+}

@@ -113,6 +113,9 @@ extern "C" size_t mono_struct_size(int which) {
         case 5: return sizeof(mono_sparse_mla_args);
         case 6: return sizeof(mono_reduce_args);
         case 7: return sizeof(mono_rowdot_args);
+        case 8: return sizeof(mono_mla_mid_args);
+        case 9: return sizeof(mono_q_post_args);
+        case 10: return sizeof(mono_index_args);
         default: return 0;
     }
 }

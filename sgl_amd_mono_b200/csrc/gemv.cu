@@ -412,7 +412,7 @@ int launch_gemv(const mono::GemvParams& p, int grid, size_t smem, cudaStream_t s
     auto k = mono::gemv_kernel<WK, NT>;
     static thread_local bool attr_set = false;  // once per instantiation, outside any graph capture
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);  // 227 KB less the static part
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }
@@ -491,7 +491,7 @@ extern "C" int mono_gemv_launch(const mono_gemv_args* a, void* stream) {
     p.scale_pitch = a->wkind == MONO_W_FP8 ? (((max_seg_tiles + 3) & ~3) * 4 + 16)
                                            : (a->wkind == MONO_W_MXFP4 ? (((max_seg_tiles * 8 + 15) & ~15) + 16) : 0);
     p.bslot_bytes = (p.scale_off + NPAD * p.scale_pitch + 127) & ~127;
-    const int budget = 227 * 1024 - 3072;
+    const int budget = 226 * 1024 - 3072;
     p.a_stages = kMaxAStages;
     while (p.a_stages > 3 && p.a_stages * kTileBytes + 2 * p.bslot_bytes > budget) --p.a_stages;
     p.n_bslots = (budget - p.a_stages * kTileBytes) / p.bslot_bytes;

@@ -1,0 +1,257 @@
+// Lightning indexer: scores of every causal key and the exact top-k of each row.
+//
+// Reference counterparts: glm53/gfx950/kernel.py:2684-3000 (index score: sum over
+// heads of relu(q_h . k) * w_h in f32), :2698-2699 (radix key), :3002-3636 (exact
+// top-k: histogram passes, candidates, ties to the lowest position, ordered gather)
+// and :3341-3346 (publication as global KV slots); FP4 index keys with one E8M0 code
+// per 32 dims as deepseek_v4/gfx950/kernels/stages/indexer.py:143-151.
+#include "mono_common.cuh"
+
+extern void mono_set_error(const char* fmt, ...);
+
+namespace mono {
+
+// ------------------------------------------------------------------ scores
+constexpr int kScoreThreads = 256;
+constexpr int kKeyTile = 128;
+constexpr int kIdxPitch = 128 + 8;  // bf16 elements per staged row (272 B: conflict-free ldmatrix)
+
+struct ScoreSmem {
+    __nv_bfloat16 keys[kKeyTile][kIdxPitch];
+    __nv_bfloat16 q[64][kIdxPitch];
+    float w[64];
+};
+
+__global__ void __launch_bounds__(kScoreThreads) index_score_kernel(const mono_index_args a, int max_tiles) {
+    extern __shared__ uint8_t smem_raw[];
+    ScoreSmem& sm = *reinterpret_cast<ScoreSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t4 = lane & 3;
+    const int mtiles = (a.index_heads + 15) >> 4;
+    const __nv_bfloat16* qg = reinterpret_cast<const __nv_bfloat16*>(a.idx_q);
+    for (int task = blockIdx.x; task < a.rows * max_tiles; task += gridDim.x) {
+        const int row = task / max_tiles, tile = task - row * max_tiles;
+        if (a.slots && a.slots[row] < 0) continue;
+        const int n = (int)a.positions[row] + 1;
+        if (tile * kKeyTile >= n) continue;
+        __syncthreads();
+        // ---- stage q (zero rows past index_heads) and the head weights
+        for (int c = tid; c < 64 * 16; c += kScoreThreads) {
+            const int h = c >> 4, ch = c & 15;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (h < a.index_heads) v = *reinterpret_cast<const uint4*>(qg + ((size_t)row * a.index_heads + h) * 128 + ch * 8);
+            *reinterpret_cast<uint4*>(&sm.q[h][ch * 8]) = v;
+        }
+        if (tid < 64) sm.w[tid] = tid < a.index_heads ? a.idx_w[(size_t)row * a.w_ld + tid] : 0.f;
+        // ---- stage 128 keys: E2M1 * 2^(code - 127) is exact in bf16
+        {
+            const int key = tid >> 1, half = tid & 1;
+            const int p = tile * kKeyTile + key;
+            uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
+            uint32_t codes = 0x7f7f;
+            if (p < n) {
+                const int64_t pg = a.page_table[(size_t)row * a.pt_ld + p / kPage];
+                if (pg >= 0 && pg < a.n_pages) {
+                    const uint8_t* page = a.idx_pages + (size_t)pg * kIdxPageBytes;
+                    const int off = p % kPage;
+                    const uint4* src = reinterpret_cast<const uint4*>(page + (size_t)off * 64 + half * 32);
+                    v0 = __ldg(src);
+                    v1 = __ldg(src + 1);
+                    codes = __ldg(reinterpret_cast<const uint16_t*>(page + kPage * 64 + off * 4 + half * 2));
+                }
+            }
+            const uint32_t words[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+            __nv_bfloat16* dst = &sm.keys[key][half * 64];
+#pragma unroll
+            for (int wi = 0; wi < 8; ++wi) {
+                const float sc = exp2_code(max((int)((codes >> ((wi >> 2) * 8)) & 0xFF), 1));
+                uint32_t o[4];
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    const uint32_t byte = (words[wi] >> (8 * b)) & 0xFF;
+                    __nv_bfloat162 pr = __floats2bfloat162_rn(e2m1_to_f32(byte & 15) * sc, e2m1_to_f32(byte >> 4) * sc);
+                    o[b] = *reinterpret_cast<uint32_t*>(&pr);
+                }
+                *reinterpret_cast<uint4*>(dst + wi * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+        }
+        __syncthreads();
+        // ---- dots[head][key] on bf16 MMAs: warp w owns keys 16w .. 16w+15
+        float acc[4][2][4];
+#pragma unroll
+        for (int m = 0; m < 4; ++m)
+#pragma unroll
+            for (int nn = 0; nn < 2; ++nn)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[m][nn][i] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            uint32_t bfr[2][2];
+#pragma unroll
+            for (int nn = 0; nn < 2; ++nn)
+                ldmatrix_x2(bfr[nn], smem_u32(&sm.keys[warp * 16 + nn * 8 + (lane & 7)][((lane >> 3) & 1) * 8]) + ks * 32);
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+                if (m < mtiles) {
+                    uint32_t af[4];
+                    ldmatrix_x4(af, smem_u32(&sm.q[m * 16 + (lane & 15)][(lane >> 4) * 8]) + ks * 32);
+#pragma unroll
+                    for (int nn = 0; nn < 2; ++nn) mma_bf16(acc[m][nn], af[0], af[1], af[2], af[3], bfr[nn][0], bfr[nn][1]);
+                }
+            }
+        }
+        // ---- score[key] = sum_h relu(dot) * w_h
+#pragma unroll
+        for (int nn = 0; nn < 2; ++nn) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                float s = 0.f;
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                    if (m < mtiles) {
+                        s += fmaxf(acc[m][nn][c], 0.f) * sm.w[m * 16 + g];
+                        s += fmaxf(acc[m][nn][2 + c], 0.f) * sm.w[m * 16 + g + 8];
+                    }
+                }
+                s += __shfl_xor_sync(0xffffffffu, s, 4);
+                s += __shfl_xor_sync(0xffffffffu, s, 8);
+                s += __shfl_xor_sync(0xffffffffu, s, 16);
+                const int p = tile * kKeyTile + warp * 16 + nn * 8 + 2 * t4 + c;
+                if (g == 0 && p < n) a.scores[(size_t)row * a.score_ld + p] = s;
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------ exact top-k
+// One CTA per row.  Four 8-bit radix passes find the k-th largest key exactly; one
+// ordered pass gathers [keys above it in position order] ++ [first ties in position order].
+constexpr int kTopkThreads = 1024;
+
+__device__ __forceinline__ uint32_t score_key(float f) {
+    const uint32_t b = __float_as_uint(f);
+    return (b & 0x80000000u) ? ~b : (b ^ 0x80000000u);
+}
+
+__global__ void __launch_bounds__(kTopkThreads) index_topk_kernel(const mono_index_args a) {
+    __shared__ int hist[256];
+    __shared__ uint32_t s_prefix;
+    __shared__ int s_krem;
+    __shared__ int wsum_gt[kTopkThreads / 32], wsum_eq[kTopkThreads / 32];
+    const int row = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    int32_t* out = a.topk_slots + (size_t)row * a.topk;
+    int32_t* outp = a.topk_pos ? a.topk_pos + (size_t)row * a.topk : nullptr;
+    const bool live = !a.slots || a.slots[row] >= 0;
+    const int n = live ? (int)a.positions[row] + 1 : 0;
+    const int32_t* pt = a.page_table + (size_t)row * a.pt_ld;
+    if (n <= a.topk) {
+        for (int i = tid; i < a.topk; i += kTopkThreads) {
+            int32_t v = -1;
+            if (i < n) v = pt[i / kPage] * kPage + i % kPage;
+            out[i] = v;
+            if (outp) outp[i] = i < n ? i : -1;
+        }
+        return;
+    }
+    const float* sc = a.scores + (size_t)row * a.score_ld;
+    if (tid == 0) { s_prefix = 0; s_krem = a.topk; }
+    for (int pass = 3; pass >= 0; --pass) {
+        if (tid < 256) hist[tid] = 0;
+        __syncthreads();
+        const uint32_t prefix = s_prefix;
+        const int krem = s_krem;
+        const int shift = pass * 8;
+        for (int i = tid; i < n; i += kTopkThreads) {
+            const uint32_t k = score_key(sc[i]);
+            if (pass == 3 || (k >> (shift + 8)) == prefix) atomicAdd(&hist[(k >> shift) & 0xFF], 1);
+        }
+        __syncthreads();
+        if (tid < 256) {
+            int above = 0;
+            for (int d = tid + 1; d < 256; ++d) above += hist[d];
+            if (above < krem && krem <= above + hist[tid]) {
+                s_prefix = (prefix << 8) | (uint32_t)tid;
+                s_krem = krem - above;
+            }
+        }
+        __syncthreads();
+    }
+    const uint32_t thr = s_prefix;
+    const int remain = s_krem;  // ties to take
+    const int n_gt = a.topk - remain;
+    // ordered gather: thread owns a contiguous run of positions
+    const int per = (n + kTopkThreads - 1) / kTopkThreads;
+    const int lo = min(tid * per, n), hi = min(lo + per, n);
+    int c_gt = 0, c_eq = 0;
+    for (int i = lo; i < hi; ++i) {
+        const uint32_t k = score_key(sc[i]);
+        c_gt += k > thr;
+        c_eq += k == thr;
+    }
+    int p_gt = c_gt, p_eq = c_eq;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int x = __shfl_up_sync(0xffffffffu, p_gt, o), y = __shfl_up_sync(0xffffffffu, p_eq, o);
+        if (lane >= o) { p_gt += x; p_eq += y; }
+    }
+    if (lane == 31) { wsum_gt[warp] = p_gt; wsum_eq[warp] = p_eq; }
+    __syncthreads();
+    int b_gt = 0, b_eq = 0;
+    for (int w = 0; w < warp; ++w) { b_gt += wsum_gt[w]; b_eq += wsum_eq[w]; }
+    int o_gt = b_gt + p_gt - c_gt, o_eq = b_eq + p_eq - c_eq;  // exclusive prefixes
+    for (int i = lo; i < hi; ++i) {
+        const uint32_t k = score_key(sc[i]);
+        int dst = -1;
+        if (k > thr) dst = o_gt++;
+        else if (k == thr) { if (o_eq < remain) dst = n_gt + o_eq; ++o_eq; }
+        if (dst >= 0) {
+            out[dst] = pt[i / kPage] * kPage + i % kPage;
+            if (outp) outp[dst] = i;
+        }
+    }
+}
+
+}  // namespace mono
+
+static int check_index_args(const mono_index_args* a, const char* who) {
+    if (!a || a->rows < 1 || a->rows > MONO_MAX_ROWS || a->index_heads < 1 || a->index_heads > 64 || a->topk < 1 ||
+        !a->page_table || !a->positions || !a->scores || a->score_ld < 1) {
+        mono_set_error("%s: rows 1..16, index_heads 1..64, topk >= 1 and the step tables required", who);
+        return MONO_E_ARG;
+    }
+    return 0;
+}
+
+extern "C" int mono_index_score_launch(const mono_index_args* a, void* stream) {
+    if (int rc = check_index_args(a, "mono_index_score_launch")) return rc;
+    if (!a->idx_q || !a->idx_w || !a->idx_pages) {
+        mono_set_error("mono_index_score_launch: idx_q, idx_w and idx_pages required");
+        return MONO_E_ARG;
+    }
+    const size_t smem = sizeof(mono::ScoreSmem) + 128;
+    static thread_local bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(mono::index_score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attr_set = true;
+    }
+    const int max_tiles = (a->score_ld + mono::kKeyTile - 1) / mono::kKeyTile;
+    int grid = a->rows * max_tiles;
+    const int sms = mono_sm_count();
+    if (grid > 4 * sms) grid = 4 * sms;
+    mono::index_score_kernel<<<grid, mono::kScoreThreads, smem, (cudaStream_t)stream>>>(*a, max_tiles);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) mono_set_error("mono_index_score_launch: %s", cudaGetErrorString(e));
+    return (int)e;
+}
+
+extern "C" int mono_index_topk_launch(const mono_index_args* a, void* stream) {
+    if (int rc = check_index_args(a, "mono_index_topk_launch")) return rc;
+    if (!a->topk_slots) {
+        mono_set_error("mono_index_topk_launch: topk_slots required");
+        return MONO_E_ARG;
+    }
+    mono::index_topk_kernel<<<a->rows, mono::kTopkThreads, 0, (cudaStream_t)stream>>>(*a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) mono_set_error("mono_index_topk_launch: %s", cudaGetErrorString(e));
+    return (int)e;
+}

@@ -191,7 +191,7 @@ __global__ void __launch_bounds__(kMlaThreads, 1) sparse_mla_split_kernel(const 
 
 // One CTA per (row, head): merge the splits.
 __global__ void __launch_bounds__(256) sparse_mla_merge_kernel(const mono_sparse_mla_args a, int nsplit) {
-    __shared__ float w[64];
+    __shared__ float w[128];
     const int row = blockIdx.x / a.heads, head = blockIdx.x - row * a.heads;
     const __nv_bfloat16* part_acc = reinterpret_cast<const __nv_bfloat16*>(a.scratch);
     const float* part_ml = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(a.scratch) +
@@ -234,8 +234,8 @@ extern "C" size_t mono_sparse_mla_scratch_bytes(int rows, int heads, int topk) {
 
 extern "C" int mono_sparse_mla_launch(const mono_sparse_mla_args* a, void* stream) {
     if (!a || a->rows < 1 || a->rows > MONO_MAX_ROWS || a->heads < 1 || a->heads > 128 || a->topk < 1 ||
-        a->topk > 64 * 64 || a->topk_ld < a->topk || !a->q || !a->kv_pages || !a->topk_slots || !a->out || !a->scratch) {
-        mono_set_error("mono_sparse_mla_launch: rows 1..16, heads 1..128, topk 1..4096 and all pointers required");
+        a->topk > 64 * 128 || a->topk_ld < a->topk || !a->q || !a->kv_pages || !a->topk_slots || !a->out || !a->scratch) {
+        mono_set_error("mono_sparse_mla_launch: rows 1..16, heads 1..128, topk 1..8192 and all pointers required");
         return MONO_E_ARG;
     }
     if ((reinterpret_cast<uintptr_t>(a->kv_pages) & 15) || (reinterpret_cast<uintptr_t>(a->q) & 15) ||

@@ -75,15 +75,17 @@ __device__ __forceinline__ void quant_chunk128(const float* x /* smem, 128 value
 __global__ void __launch_bounds__(kPrepThreads) act_prep_kernel(const mono_act_prep_args a) {
     extern __shared__ float xrow[];
     __shared__ float red[kPrepThreads / 32];
-    const int row = blockIdx.x, tid = threadIdx.x;
+    const int segs = a.segs > 1 ? a.segs : 1;
+    const int row = blockIdx.x / segs, seg = blockIdx.x - row * segs, tid = threadIdx.x;
     float ssq = 0.f;
     for (int i = tid; i < a.k; i += kPrepThreads) {
         float v;
         if (a.src_bf16) {
-            v = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.src_bf16)[(size_t)row * a.k + i]);
+            v = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.src_bf16)[((size_t)row * segs + seg) * a.k + i]);
         } else {
             v = 0.f;
-            for (int s = 0; s < a.nsum; ++s) v += a.src_f32[(size_t)s * a.src_sum_stride + (size_t)row * a.src_ld + i];
+            for (int s = 0; s < a.nsum; ++s)
+                v += a.src_f32[(size_t)s * a.src_sum_stride + (size_t)row * a.src_ld + (size_t)seg * a.k + i];
         }
         xrow[i] = v;
         ssq += v * v;
@@ -99,15 +101,15 @@ __global__ void __launch_bounds__(kPrepThreads) act_prep_kernel(const mono_act_p
         for (int i = tid; i < a.k; i += kPrepThreads) xrow[i] = bf16_round(xrow[i]);
     __syncthreads();
     if (a.out_bf16) {
-        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(a.out_bf16) + (size_t)row * a.k;
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(a.out_bf16) + ((size_t)row * segs + seg) * a.k;
         for (int i = tid; i < a.k; i += kPrepThreads) o[i] = __float2bfloat16_rn(xrow[i]);
     }
     if (a.planes) {
         const int warp = tid >> 5, lane = tid & 31;
-        uint8_t* p0 = a.planes + (size_t)row * a.ld;
+        uint8_t* p0 = a.planes + (size_t)seg * a.seg_stride + (size_t)row * a.ld;
         uint8_t* p1 = p0 + a.plane_stride;
-        float* sf = a.scale_f32 ? a.scale_f32 + (size_t)row * a.scale_ld : nullptr;
-        uint8_t* s8 = a.scale_e8 ? a.scale_e8 + (size_t)row * a.scale_ld : nullptr;
+        float* sf = a.scale_f32 ? a.scale_f32 + (size_t)seg * a.scale_seg_stride + (size_t)row * a.scale_ld : nullptr;
+        uint8_t* s8 = a.scale_e8 ? a.scale_e8 + (size_t)seg * a.scale_seg_stride + (size_t)row * a.scale_ld : nullptr;
         for (int c = warp; c < a.k / 128; c += kPrepThreads / 32) quant_chunk128(xrow + c * 128, a.fmt, lane, c, p0, p1, sf, s8);
     }
 }
@@ -397,7 +399,7 @@ extern "C" int mono_act_prep_launch(const mono_act_prep_args* a, void* stream) {
         cudaFuncSetAttribute(mono::act_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * (int)sizeof(float));
         attr_set = true;
     }
-    mono::act_prep_kernel<<<a->rows, mono::kPrepThreads, a->k * sizeof(float), (cudaStream_t)stream>>>(*a);
+    mono::act_prep_kernel<<<a->rows * (a->segs > 1 ? a->segs : 1), mono::kPrepThreads, a->k * sizeof(float), (cudaStream_t)stream>>>(*a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_act_prep_launch: %s", cudaGetErrorString(e));
     return (int)e;

@@ -1,0 +1,150 @@
+"""Host runner of one MLA + lightning-indexer + MoE decoder layer.
+
+Reference counterpart: ``Glm53LayerOp.launch(h, caches, cos, sin, step) -> x_out``
+(``glm53/gfx950/runner.py:240-321``) and ``Glm53Runtime`` (scratch, peer buffer and
+guard words owned by the runner, allocated at build, ``runner.py:184-210``).  The
+stage order is the reference kernel's (``glm53/gfx950/kernel.py:171``): input norm,
+q_a|kv_a (+ index key, head weights), norms + RoPE + cache writes, q_b (+ index q),
+absorb, index scores, exact top-k, sparse MLA, W_UV, o_proj, all-reduce + residual,
+then the MoE half (``moe.MoeFfn``).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib as L
+from . import ops
+from .attention import SparseMlaOp
+from .config import IDX_PAGE_BYTES, KV_DIM, KV_PAGE_BYTES, LayerConfig
+from .moe import MoeFfn
+
+
+@dataclass
+class StepTables:
+    """Fixed-address tensors a decode step reads (``glm53/spec.py:467-496``)."""
+
+    positions: torch.Tensor  # i64 [rows]
+    slots: torch.Tensor  # i64 [rows]; < 0 = pad row
+    page_table: torch.Tensor  # i32 [rows, pages]
+    kv_pages: torch.Tensor  # u8 [pages, KV_PAGE_BYTES]
+    idx_pages: torch.Tensor | None  # u8 [pages, IDX_PAGE_BYTES]
+    cos: torch.Tensor  # bf16 [max_pos, 32]
+    sin: torch.Tensor
+
+
+class MlaLayerOp:
+    def __init__(self, cfg: LayerConfig, w: dict, device, max_ctx: int, peer=None, guard=None, layer: int = 0,
+                 deadline_s: float = 5.0, max_rows: int = L.MAX_ROWS):
+        L.load()
+        if cfg.nope != 128 or cfg.v_head != 128 or cfg.rope != 64 or cfg.kv_lora != 512:
+            raise ValueError("the MLA kernels are built for nope 128, v 128, rope 64, kv_lora 512")
+        self.cfg, self.w, self.dev, self.peer, self.layer = cfg, w, device, peer, layer
+        self.deadline_s = deadline_s
+        self.guard = guard if guard is not None else torch.zeros(L.GUARD_WORDS, dtype=torch.int32, device=device)
+        h, hl, ql, ih = cfg.hidden, cfg.heads_local, cfg.q_lora, cfg.index_heads
+        R = L.MAX_ROWS
+        z = lambda *s, dt=torch.float32: torch.zeros(*s, dtype=dt, device=device)  # noqa: E731
+        self.x = ops.ActBuf(L.ACT_HILO, h, device)
+        self.xbf = z(R, h, dt=torch.bfloat16)
+        # ---- launch A: q_a|kv_a and the index-key projection
+        self.gA = ops.Gemv(L.W_FP8, self.guard)
+        kt = -(-h // 128)
+        stA, nsA = ops.plan_split(kt, -(-(ql + KV_DIM) // 128) + (1 if ih else 0), L.W_FP8)
+        self.nsA = nsA
+        self.qkv_p = z(nsA, R, ql + KV_DIM)
+        self.gA.add("qkv_a", w["qkv_a"], self.x, self.qkv_p, wscale=w["qkv_a_s"], split_tiles=stA, nsplit=nsA)
+        self.ik_p = self.idx_w = self.iq_p = self.idx_q = self.scores = None
+        if ih:
+            self.ik_p = z(nsA, R, 128)
+            self.gA.add("idx_wk", w["idx_wk"], self.x, self.ik_p, wscale=w["idx_wk_s"], split_tiles=stA, nsplit=nsA)
+            self.idx_w = z(R, ih)
+            self.ik_out = z(R, 128)
+            self.idx_q = z(R, ih, 128, dt=torch.bfloat16)
+            self.max_ctx = -(-max_ctx // 128) * 128
+            self.scores = z(R, self.max_ctx)
+        self.qa = ops.ActBuf(L.ACT_HILO, ql, device)
+        self.kv_out = z(R, KV_DIM, dt=torch.bfloat16)
+        # ---- launch B: q_b and the index-query projection
+        self.gB = ops.Gemv(L.W_FP8, self.guard)
+        ktb = -(-ql // 128)
+        stB, nsB = ops.plan_split(ktb, -(-hl * 192 // 128) + (ih if ih else 0), L.W_FP8)
+        self.nsB = nsB
+        self.qb_p = z(nsB, R, hl * 192)
+        self.gB.add("q_b", w["q_b"], self.qa, self.qb_p, wscale=w["q_b_s"], split_tiles=stB, nsplit=nsB)
+        if ih:
+            self.iq_p = z(nsB, R, ih * 128)
+            self.gB.add("idx_wq_b", w["idx_wq_b"], self.qa, self.iq_p, wscale=w["idx_wq_b_s"], split_tiles=stB, nsplit=nsB)
+        self.q_full = z(R, hl, KV_DIM, dt=torch.bfloat16)
+        # without an indexer every cached key is attended: the "selection" is the whole context
+        self.topk = cfg.index_topk if ih else -(-max_ctx // 64) * 64
+        if not ih:
+            self.max_ctx = self.topk
+            self.scores = z(R, 128)
+        self.topk_slots = torch.full((R, self.topk), -1, dtype=torch.int32, device=device)
+        self.topk_pos = torch.full((R, self.topk), -1, dtype=torch.int32, device=device)
+        self.attn = SparseMlaOp(hl, self.topk, device, max_rows=R, sm_scale=(cfg.nope + cfg.rope) ** -0.5)
+        # ---- W_UV (per head) and o_proj
+        self.lat = ops.ActBuf(L.ACT_HILO, 512, device, segs=hl)
+        self.uv_p = z(1, R, hl * 128)
+        self.gUV = ops.Gemv(L.W_FP8, self.guard)
+        self.gUV.add("kv_b(W_UV)", w["kv_b"].view(hl, 256, 512), self.lat, self.uv_p, wscale=w["kv_b_s"].view(hl, 2, 4),
+                     n_rows=128, row_off=128, rb_per_mat=1, n_mats=hl, act_per_mat=True, split_tiles=4, nsplit=1)
+        self.o = ops.ActBuf(L.ACT_HILO, hl * 128, device)
+        kto = -(-hl * 128 // 128)
+        stO, nsO = ops.plan_split(kto, -(-h // 128), L.W_FP8)
+        self.nsO = nsO
+        self.o_p = z(nsO, R, h)
+        self.gO = ops.Gemv(L.W_FP8, self.guard)
+        self.gO.add("o_proj", w["o_proj"], self.o, self.o_p, wscale=w["o_proj_s"], split_tiles=stO, nsplit=nsO)
+        self.h1 = z(R, h, dt=torch.bfloat16)
+        self.ffn = MoeFfn(cfg, w, device, max_rows=max_rows, peer=peer, guard=self.guard, site=2 * layer + 1,
+                          deadline_s=deadline_s) if cfg.n_experts else None
+        self._iargs = None
+
+    def launch(self, h: torch.Tensor, step: StepTables) -> torch.Tensor:
+        cfg, w = self.cfg, self.w
+        rows = h.shape[0]
+        if not 1 <= rows <= L.MAX_ROWS:
+            raise ValueError(f"h: {rows} rows, the launch serves 1..{L.MAX_ROWS}")
+        ops.require(h, "h", torch.bfloat16, (rows, cfg.hidden))
+        ops.require(step.positions, "step.positions", torch.int64, (rows,))
+        ops.require(step.slots, "step.slots", torch.int64, (rows,))
+        ops.require(step.page_table, "step.page_table", torch.int32)
+        ops.require(step.kv_pages, "step.kv_pages", torch.uint8)
+        if step.kv_pages.shape[-1] != KV_PAGE_BYTES:
+            raise ValueError(f"step.kv_pages: page of {step.kv_pages.shape[-1]} bytes, needs {KV_PAGE_BYTES}")
+        ih, hl = cfg.index_heads, cfg.heads_local
+        if ih:
+            ops.require(step.idx_pages, "step.idx_pages", torch.uint8)
+            if step.idx_pages.shape[-1] != IDX_PAGE_BYTES:
+                raise ValueError(f"step.idx_pages: page of {step.idx_pages.shape[-1]} bytes, needs {IDX_PAGE_BYTES}")
+        if step.page_table.shape[1] * 64 > self.max_ctx:
+            raise ValueError(f"step.page_table: {step.page_table.shape[1]} pages exceed the built context {self.max_ctx}")
+        ops.act_prep(rows, cfg.hidden, self.x, src_bf16=h, gamma=w["input_norm"], eps=cfg.eps, out_bf16=self.xbf)
+        self.gA.launch(rows)
+        if ih:
+            ops.rowdot(rows, w["idx_wproj"], self.xbf, self.idx_w, out_scale=(ih**-0.5) * (128**-0.5))
+        ops.mla_mid(rows, cfg.q_lora, self.qkv_p, self.nsA, w, cfg.eps, step.cos, step.sin, step.positions, step.slots,
+                    self.qa, step.kv_pages, step.idx_pages, self.kv_out, ik=self.ik_p, ik_nsum=self.nsA,
+                    ik_out=self.ik_out if ih else None)
+        self.gB.launch(rows)
+        ops.q_post(rows, hl, self.qb_p, self.nsB, w["kv_b"], w["kv_b_s"], step.cos, step.sin, step.positions,
+                   self.q_full, ih, self.iq_p, self.nsB, self.idx_q)
+        ia = ops.index_args(rows, max(ih, 1), self.topk, self.idx_q, self.idx_w, step.idx_pages, step.page_table,
+                            step.positions, step.slots, self.scores, self.topk_slots, self.topk_pos)
+        if ih:
+            ops.index_score(ia)
+        ops.index_topk(ia)  # rows with at most topk keys keep every key in order
+        lat = self.attn(self.q_full[:rows], step.kv_pages, self.topk_slots)
+        ops.act_prep_heads(rows, hl, 512, self.lat, src_bf16=lat)
+        self.gUV.launch(rows)
+        ops.act_prep(rows, hl * 128, self.o, src_f32=self.uv_p, nsum=1)
+        self.gO.launch(rows)
+        ops.reduce_rows(rows, cfg.hidden, self.o_p, self.nsO, self.h1, residual=h, slots=step.slots, peer=self.peer,
+                        site=2 * self.layer, guard=self.guard, deadline_s=self.deadline_s)
+        if self.ffn is None:
+            return self.h1[:rows]
+        return self.ffn(self.h1[:rows], step.slots)

@@ -222,6 +222,74 @@ def sparse_mla(q, kv_pages, topk_slots, out, scratch, sm_scale: float, topk: int
     L.check(L.load().mono_sparse_mla_launch(C.byref(a), _stream()), "mono_sparse_mla_launch")
 
 
+def act_prep_heads(rows: int, heads: int, k: int, dst: ActBuf, *, src_bf16=None, src_f32=None, nsum: int = 1,
+                   round_bf16: bool = True) -> None:
+    """Per-head activation sets: vector (row, head) of the source goes to segment ``head`` of ``dst``."""
+    a = L.ActPrepArgs()
+    a.rows, a.k, a.segs = rows, k, heads
+    a.src_bf16, a.src_f32 = _p(src_bf16), _p(src_f32)
+    if src_f32 is not None:
+        a.nsum, a.src_ld, a.src_sum_stride = nsum, src_f32.shape[-1], L.MAX_ROWS * src_f32.shape[-1]
+    a.round_bf16 = int(round_bf16)
+    a.fmt, a.planes, a.plane_stride, a.ld = dst.fmt, _p(dst.planes), dst.plane_stride, dst.ld
+    a.scale_f32, a.scale_e8, a.scale_ld = _p(dst.scale_f32), _p(dst.scale_e8), dst.scale_ld
+    a.seg_stride, a.scale_seg_stride = dst.seg_stride, dst.scale_seg_stride
+    L.check(L.load().mono_act_prep_launch(C.byref(a), _stream()), "mono_act_prep_launch")
+
+
+def mla_mid(rows: int, q_lora: int, qkv, nsum: int, w: dict, eps: float, cos, sin, positions, slots, qa: ActBuf,
+            kv_pages, idx_pages, kv_out, ik=None, ik_nsum: int = 0, ik_out=None) -> None:
+    a = L.MlaMidArgs()
+    a.rows, a.q_lora = rows, q_lora
+    a.qkv, a.nsum, a.ld, a.sum_stride = qkv.data_ptr(), nsum, qkv.shape[-1], L.MAX_ROWS * qkv.shape[-1]
+    if ik is not None:
+        a.ik, a.ik_nsum, a.ik_ld, a.ik_sum_stride = ik.data_ptr(), ik_nsum, ik.shape[-1], L.MAX_ROWS * ik.shape[-1]
+        a.ik_norm_w, a.ik_norm_b = w["idx_k_norm_w"].data_ptr(), w["idx_k_norm_b"].data_ptr()
+        a.idx_pages = idx_pages.data_ptr()
+    a.q_a_norm, a.kv_a_norm, a.eps = w["q_a_norm"].data_ptr(), w["kv_a_norm"].data_ptr(), eps
+    a.cos, a.sin, a.positions, a.slots = cos.data_ptr(), sin.data_ptr(), positions.data_ptr(), _p(slots)
+    a.qa_planes, a.qa_plane_stride, a.qa_ld = qa.planes.data_ptr(), qa.plane_stride, qa.ld
+    a.qa_scale, a.qa_scale_ld = qa.scale_f32.data_ptr(), qa.scale_ld
+    a.kv_pages, a.n_pages = kv_pages.data_ptr(), kv_pages.shape[0]
+    a.kv_out, a.ik_out = _p(kv_out), _p(ik_out)
+    L.check(L.load().mono_mla_mid_launch(C.byref(a), _stream()), "mono_mla_mid_launch")
+
+
+def q_post(rows: int, heads: int, qb, nsum: int, kv_b, kv_b_scale, cos, sin, positions, q_full,
+           index_heads: int = 0, iq=None, iq_nsum: int = 0, idx_q=None) -> None:
+    a = L.QPostArgs()
+    a.rows, a.heads = rows, heads
+    a.qb, a.nsum, a.ld, a.sum_stride = qb.data_ptr(), nsum, qb.shape[-1], L.MAX_ROWS * qb.shape[-1]
+    a.kv_b, a.kv_b_scale = kv_b.data_ptr(), kv_b_scale.data_ptr()
+    a.cos, a.sin, a.positions, a.q_full = cos.data_ptr(), sin.data_ptr(), positions.data_ptr(), q_full.data_ptr()
+    a.index_heads = index_heads
+    if index_heads:
+        a.iq, a.iq_nsum, a.iq_ld, a.iq_sum_stride = iq.data_ptr(), iq_nsum, iq.shape[-1], L.MAX_ROWS * iq.shape[-1]
+        a.idx_q = idx_q.data_ptr()
+    L.check(L.load().mono_q_post_launch(C.byref(a), _stream()), "mono_q_post_launch")
+
+
+def index_args(rows: int, index_heads: int, topk: int, idx_q, idx_w, idx_pages, page_table, positions, slots,
+               scores, topk_slots, topk_pos=None) -> "L.IndexArgs":
+    a = L.IndexArgs()
+    a.rows, a.index_heads, a.topk = rows, index_heads, topk
+    a.idx_q, a.idx_w, a.w_ld = _p(idx_q), _p(idx_w), idx_w.shape[-1] if idx_w is not None else 0
+    a.idx_pages, a.n_pages = _p(idx_pages), idx_pages.shape[0] if idx_pages is not None else 0
+    a.page_table, a.pt_ld = page_table.data_ptr(), page_table.shape[-1]
+    a.positions, a.slots = positions.data_ptr(), _p(slots)
+    a.scores, a.score_ld = scores.data_ptr(), scores.shape[-1]
+    a.topk_slots, a.topk_pos = topk_slots.data_ptr(), _p(topk_pos)
+    return a
+
+
+def index_score(a) -> None:
+    L.check(L.load().mono_index_score_launch(C.byref(a), _stream()), "mono_index_score_launch")
+
+
+def index_topk(a) -> None:
+    L.check(L.load().mono_index_topk_launch(C.byref(a), _stream()), "mono_index_topk_launch")
+
+
 def guard_read(guard: torch.Tensor):
     out = (C.c_int32 * 3)()
     rc = L.load().mono_guard_read(guard.data_ptr(), C.byref(out), _stream())

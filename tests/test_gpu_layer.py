@@ -1,0 +1,140 @@
+"""One MLA + lightning-indexer + MoE decoder layer on the GPU against the CPU oracle,
+stage by stage: cache bytes and top-k exactly (given the kernel's own pre-quantisation
+values and scores), streams within the hidden-state tolerance."""
+
+import pytest
+import torch
+
+from oracle import layers as OL
+from oracle import stages as S
+from sgl_amd_mono_b200 import ops, synth
+from sgl_amd_mono_b200.config import CFG_TINY, KV_DIM, PAGE
+from util import assert_close_hidden
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _cpu(w):
+    return {k: (v.cpu() if isinstance(v, torch.Tensor) else v) for k, v in w.items()}
+
+
+def _step_to(step, dev):
+    from sgl_amd_mono_b200.layer import StepTables
+
+    t = lambda x: None if x is None else x.to(dev)  # noqa: E731
+    return StepTables(t(step.positions), t(step.slots), t(step.page_table), t(step.kv_pages), t(step.idx_pages),
+                      t(step.cos), t(step.sin))
+
+
+def _run(cfg, rows, ctx, pad=(), seed=1):
+    from sgl_amd_mono_b200.layer import MlaLayerOp
+
+    w = synth.layer_weights(cfg, 0, DEV)
+    step = synth.decode_step(cfg, rows, ctx, pad_rows=pad)
+    h = torch.randn(rows, cfg.hidden, generator=torch.Generator().manual_seed(seed)).bfloat16()
+    op = MlaLayerOp(cfg, w, DEV, max_ctx=-(-ctx // 64) * 64)
+    dstep = _step_to(step, DEV)
+    out = op.launch(h.to(DEV), dstep).clone()
+    torch.cuda.synchronize()
+    rc, words = ops.guard_read(op.guard)
+    assert rc == 0, f"guard words {words}"
+    return op, w, step, dstep, h, out
+
+
+@pytest.mark.parametrize("rows,ctx,pad", [(1, 300, ()), (4, 700, ()), (8, 1000, (2,)), (13, 520, ())])
+def test_layer_stages_and_output(rows, ctx, pad):
+    cfg = CFG_TINY
+    op, w, step, dstep, h, out = _run(cfg, rows, ctx, pad)
+    wc = _cpu(w)
+    live = [r for r in range(rows) if r not in pad]
+    kvp, ixp = step.kv_pages.clone(), step.idx_pages.clone()
+    r = OL.attn_front(cfg, wc, h, step.positions, step.slots, step.cos, step.sin, kvp, ixp)
+    # ---- cache rows: values close, bytes exact given the kernel's own bf16 values
+    kv_k = op.kv_out[:rows].cpu().float()
+    assert_close_hidden(kv_k[live], torch.cat([r["latent"], r["k_pe"]], -1)[live], "latent | k_pe")
+    row_b, row_s = S.kv_row_encode(kv_k[:, :512], kv_k[:, 512:])
+    got_pages = dstep.kv_pages.cpu()
+    for i in live:
+        p, o = divmod(int(step.slots[i]), PAGE)
+        assert torch.equal(got_pages[p, o * KV_DIM : (o + 1) * KV_DIM], row_b[i]), f"KV bytes of row {i}"
+        assert got_pages[p, PAGE * KV_DIM :].view(torch.float32)[o] == row_s[i]
+    # exactly the live rows' cache rows changed
+    changed = (got_pages != step.kv_pages).any(1).nonzero().flatten().tolist()
+    assert set(changed) <= {int(step.slots[i]) // PAGE for i in live}
+    # ---- index keys: bytes exact given the kernel's own f32 values
+    ik_k = op.ik_out[:rows].cpu()
+    assert torch.allclose(ik_k[live], r["idx_key"][live], atol=2e-2, rtol=2e-2)
+    packed, codes = S.index_key_encode(ik_k)
+    got_idx = dstep.idx_pages.cpu()
+    for i in live:
+        p, o = divmod(int(step.slots[i]), PAGE)
+        assert torch.equal(got_idx[p, o * 64 : (o + 1) * 64], packed[i]), f"index key bytes of row {i}"
+        assert torch.equal(got_idx[p, PAGE * 64 + o * 4 : PAGE * 64 + (o + 1) * 4], codes[i])
+    # ---- queries
+    assert_close_hidden(op.q_full[:rows].cpu()[live], r["q_full"][live], "q_lat | q_pe", scale=float(r["q_full"].abs().max()))
+    assert_close_hidden(op.idx_q[:rows].cpu()[live], r["idx_q"][live], "index q", scale=float(r["idx_q"].abs().max()))
+    assert torch.allclose(op.idx_w[:rows].cpu()[live], r["idx_w"][live], atol=1e-3, rtol=1e-3)
+    # ---- scores close to the oracle's; top-k exact on the kernel's own scores
+    sc_k = op.scores[:rows].cpu()
+    topk_k, pos_k = op.topk_slots[:rows].cpu(), op.topk_pos[:rows].cpu()
+    topk_o, scores_o = OL.index_select(cfg, r, step.positions, step.slots, step.page_table, got_idx)
+    for i in range(rows):
+        if i in pad:
+            assert int((topk_k[i] >= 0).sum()) == 0
+            continue
+        n = int(step.positions[i]) + 1
+        ref_sc = scores_o[i]
+        assert torch.allclose(sc_k[i, :n], ref_sc, atol=2e-2 * float(ref_sc.abs().max()), rtol=0), f"scores of row {i}"
+        want = S.exact_topk_positions(sc_k[i], n, cfg.index_topk)
+        assert pos_k[i, : want.numel()].tolist() == want.tolist(), f"top-k positions of row {i}"
+        assert topk_k[i, : want.numel()].tolist() == S.slots_of_positions(step.page_table[i], want).tolist()
+        assert int((topk_k[i, want.numel():] >= 0).sum()) == 0
+    # ---- whole layer
+    ref, det = OL.layer_all_ranks(cfg, [wc], h, step.positions, step.slots, step.page_table, step.cos, step.sin,
+                                  step.kv_pages.clone(), step.idx_pages.clone())
+    attn_scale = float((det["h1"].float() - h.float()).abs().max())
+    assert_close_hidden(op.h1[:rows].cpu()[live], det["h1"][live], "h1 after attention", scale=attn_scale)
+    scale = max(attn_scale, float((ref.float() - det["h1"].float()).abs().max()))
+    assert_close_hidden(out.cpu()[live], ref[live], "layer output", scale=scale)
+    for i in pad:
+        assert torch.equal(out[i].cpu(), h[i]), "a pad row passes through unchanged"
+
+
+def test_ties_go_to_the_lowest_position():
+    """Equal scores everywhere: the selection is the first k positions, in order."""
+    from sgl_amd_mono_b200 import _lib as L
+
+    rows, n, k = 2, 1000, 256
+    scores = torch.zeros(16, 1024, device=DEV)
+    scores[1, 500:700] = 1.0  # row 1: 200 keys above, the rest tie
+    pt = torch.arange(32, dtype=torch.int32, device=DEV).repeat(rows, 1) + 3
+    pos = torch.full((rows,), n - 1, dtype=torch.int64, device=DEV)
+    slots = torch.ones(rows, dtype=torch.int64, device=DEV)
+    out = torch.full((16, k), -7, dtype=torch.int32, device=DEV)
+    outp = torch.full((16, k), -7, dtype=torch.int32, device=DEV)
+    a = ops.index_args(rows, 1, k, None, None, None, pt, pos, slots, scores, out, outp)
+    ops.index_topk(a)
+    torch.cuda.synchronize()
+    assert outp[0].cpu().tolist() == list(range(k))
+    assert outp[1].cpu().tolist() == list(range(500, 700)) + list(range(56))
+    assert out[0, 70].item() == (3 + 70 // 64) * 64 + 70 % 64
+    assert L.MAX_ROWS == 16
+
+
+def test_topk_long_context_matches_oracle():
+    rows, n, k = 3, 40000, 2048
+    g = torch.Generator().manual_seed(9)
+    scores = torch.randn(16, 40064, generator=g)
+    scores[2, ::3] = 0.25  # many exact ties around the threshold region
+    pt = torch.randperm(700, generator=g)[: 626].to(torch.int32).repeat(rows, 1)
+    pos = torch.tensor([n - 1, 5000, n - 1])
+    slots = torch.ones(rows, dtype=torch.int64)
+    out = torch.full((16, k), -7, dtype=torch.int32, device=DEV)
+    outp = torch.full((16, k), -7, dtype=torch.int32, device=DEV)
+    a = ops.index_args(rows, 1, k, None, None, None, pt.to(DEV), pos.to(DEV), slots.to(DEV), scores.to(DEV), out, outp)
+    ops.index_topk(a)
+    torch.cuda.synchronize()
+    for i in range(rows):
+        want = S.exact_topk_positions(scores[i], int(pos[i]) + 1, k)
+        assert outp[i].cpu().tolist() == want.tolist(), f"row {i}"

@@ -61,9 +61,8 @@ def test_full_size_config2_property():
     from sgl_amd_mono_b200.attention import SparseMlaOp
 
     pages = pages.to(DEV)
-    vals = pages[:, : 64 * 576].view(-1, 576)
-    const = vals[77].clone()
-    vals[:] = const
+    const = pages[1, 7 * 576 : 8 * 576].clone()
+    pages[:, : 64 * 576] = const.repeat(64)
     pages[:, 64 * 576 :].view(torch.float32)[:] = 0.25
     op = SparseMlaOp(16, 2048, DEV, sm_scale=SCALE)
     out = op(q.to(DEV), pages, sel.to(DEV))
