@@ -153,8 +153,10 @@ def test_gemv_stages_in_isolation(cfg, rows):
             q, c = Q.mxfp8_quant(Q.bf(mid_o))
             mid_ref = Q.mxfp8_dequant(q, c)
         # the same values up to a rounding step of the few elements that sit on a boundary
+        # (a chunk whose amax moved by an ulp rescales all its values by an ulp: not a flip)
         close = (mid_k - mid_ref).abs() <= 0.13 * mid_ref.abs() + 1e-6
-        assert bool(close.all()) and float((mid_k != mid_ref).float().mean()) < 0.02
+        flipped = (mid_k - mid_ref).abs() > 1e-4 * mid_ref.abs() + 1e-7
+        assert bool(close.all()) and float(flipped.float().mean()) < 0.02
         down_ref += coef[u, :, None] * (mid_k @ deq(wc["w2"][e], wc["w2_s"][e]).T)
     routed = ffn.down_p[: ffn.groups, :rows].cpu().sum(0)
     assert_rel(routed, down_ref, "routed down projection")

@@ -95,7 +95,8 @@ def test_layer_stages_and_output(rows, ctx, pad):
                                   step.kv_pages.clone(), step.idx_pages.clone())
     attn_scale = float((det["h1"].float() - h.float()).abs().max())
     assert_close_hidden(op.h1[:rows].cpu()[live], det["h1"][live], "h1 after attention", scale=attn_scale)
-    scale = max(attn_scale, float((ref.float() - det["h1"].float()).abs().max()))
+    # the two blocks' quantisation noise adds up in the output stream
+    scale = attn_scale + float((ref.float() - det["h1"].float()).abs().max())
     assert_close_hidden(out.cpu()[live], ref[live], "layer output", scale=scale)
     for i in pad:
         assert torch.equal(out[i].cpu(), h[i]), "a pad row passes through unchanged"
