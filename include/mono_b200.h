@@ -249,6 +249,27 @@ typedef struct mono_sparse_mla_args {
 size_t mono_sparse_mla_scratch_bytes(int rows, int heads, int topk);
 int mono_sparse_mla_launch(const mono_sparse_mla_args* a, void* stream);
 
+/* The same attention for callers that cannot allocate device memory (this entry point
+ * has no counterpart in the reference, whose runner allocates all scratch itself when
+ * it is built).  Once a server has given the rest of the GPU to its KV-cache pool, a
+ * late cudaMalloc may fail or stall the device, and a plugin attached after that point
+ * has nowhere to get a scratch buffer from.  Here `a->scratch` is ignored: the split
+ * partials go to a fixed array inside the library (about 4.3 MB, held by every GPU that
+ * loads the library until the process exits).  Limits: rows <= MONO_NOALLOC_MAX_ROWS,
+ * heads <= MONO_NOALLOC_MAX_HEADS, topk <= MONO_NOALLOC_MAX_TOPK; larger shapes return
+ * MONO_E_ARG with a message and must use mono_sparse_mla_launch.  No cudaMalloc, cudaFree
+ * or allocating library routine is called.  The first call on a device looks up the
+ * array's device address (cudaGetSymbolAddress, with that device current) and caches
+ * it, so make that first call before any stream capture.  All calls share the one
+ * array: calls that overlap on the GPU (different streams, or different threads on one
+ * device) race on it and must be serialised by the caller; the array keeps the last
+ * call's partials, and nothing in it has to be cleared between calls because the merge
+ * only reads what the same call's split has just written. */
+#define MONO_NOALLOC_MAX_ROWS 8
+#define MONO_NOALLOC_MAX_HEADS 16
+#define MONO_NOALLOC_MAX_TOPK 2048
+int mono_sparse_mla_launch_noalloc(const mono_sparse_mla_args* a, void* stream);
+
 /* ---- partial-sum reduction + all-reduce + residual (glm53/gfx950/kernel.py:1631-1688
  * peer_reduce, :4125-4197, :5175-5185) -------------------------------------------
  * partial = sum over nsum slices (in order) of f32 [16][ld]; rounded to bf16; with
@@ -368,6 +389,13 @@ typedef struct mono_index_args {
 } mono_index_args;
 int mono_index_score_launch(const mono_index_args* a, void* stream);
 int mono_index_topk_launch(const mono_index_args* a, void* stream);
+
+/* ---- symmetric peer memory (common/peer.py:33-64 HIP IPC calls, :118-165 PeerBuffer) --
+ * A rank allocates one zeroed device buffer, exports a 64-byte handle that travels over
+ * the host-side handshake (gloo), and opens every peer's handle; the opened addresses
+ * are what in-kernel pushes store to.  These five calls are the only ones that allocate
+ * or map memory, and they run at build time, never inside a step. */
+#define MONO_IPC_HANDLE_BYTES 64
 
 /* sizeof() of the argument structs, by index (0 gemv_job, 1 gemv_args, 2 act_prep,
  * 3 route, 4 mid, 5 sparse_mla, 6 reduce, 7 rowdot, ...): lets a binding check its mirror. */

@@ -144,6 +144,7 @@ SYMBOLS = {
     "mono_mid_launch": (i32, [C.POINTER(MidArgs), vp]),
     "mono_sparse_mla_scratch_bytes": (C.c_size_t, [i32, i32, i32]),
     "mono_sparse_mla_launch": (i32, [C.POINTER(SparseMlaArgs), vp]),
+    "mono_sparse_mla_launch_noalloc": (i32, [C.POINTER(SparseMlaArgs), vp]),
     "mono_reduce_peer_bytes": (C.c_size_t, [i32, i32, i32]),
     "mono_reduce_launch": (i32, [C.POINTER(ReduceArgs), vp]),
     "mono_epoch_advance_launch": (i32, [vp, vp]),

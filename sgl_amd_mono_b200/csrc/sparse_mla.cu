@@ -263,3 +263,99 @@ extern "C" int mono_sparse_mla_launch(const mono_sparse_mla_args* a, void* strea
     if (e != cudaSuccess) mono_set_error("mono_sparse_mla_launch: %s", cudaGetErrorString(e));
     return (int)e;
 }
+
+// ------------------------------------------------------------------------------------
+// Sparse MLA for callers that must not allocate.
+//
+// A serving process usually hands every free byte of the GPU to its KV-cache pool once
+// the model is loaded, and from then on a late cudaMalloc can fail, fragment the pool's
+// neighbourhood or stall the device while it maps memory; code that runs between graph
+// captures, inside a latency-critical decode loop, or in a plugin that was attached
+// after the pool was sized is in that position.  For those callers the split partials
+// live in a fixed array that is part of the library image instead of a caller-provided
+// scratch buffer.  Every GPU that loads the library holds the array until the process
+// exits, so it is kept small: it covers steps of up to 8 rows x 16 local heads x 2048
+// selected keys (the shape of BASELINE config 2); anything larger is refused.
+//
+// The array's name in host code is only a handle, not a device address, so the device
+// address is looked up once per device with cudaGetSymbolAddress while that device is
+// current, and that pointer is what the kernels receive.
+namespace mono {
+constexpr int kNoAllocRows = MONO_NOALLOC_MAX_ROWS, kNoAllocHeads = MONO_NOALLOC_MAX_HEADS,
+              kNoAllocTopk = MONO_NOALLOC_MAX_TOPK;
+constexpr size_t kNoAllocScratchBytes =
+    (size_t)kNoAllocRows * (kNoAllocTopk / kSplit) * kNoAllocHeads * (512 * sizeof(__nv_bfloat16) + 2 * sizeof(float)) + 256;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+}  // namespace mono
+
+#include <mutex>
+
+// Device address of the static scratch on the current device (nullptr + message on failure).
+static void* noalloc_scratch_for_current_device() {
+    constexpr int kMaxDevices = 64;
+    static std::mutex mu;
+    static void* ptrs[kMaxDevices] = {};
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        mono_set_error("mono_sparse_mla_launch_noalloc: cudaGetDevice failed or device %d out of range (%s)", dev,
+                       cudaGetErrorString(e));
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    if (ptrs[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, mono::g_noalloc_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            mono_set_error("mono_sparse_mla_launch_noalloc: cudaGetSymbolAddress failed on device %d: %s", dev,
+                           cudaGetErrorString(e));
+            return nullptr;
+        }
+        ptrs[dev] = p;
+    }
+    return ptrs[dev];
+}
+
+extern "C" int mono_sparse_mla_launch_noalloc(const mono_sparse_mla_args* a, void* stream) {
+    if (!a || a->rows < 1 || a->heads < 1 || a->topk < 1 || a->topk_ld < a->topk || !a->q || !a->kv_pages ||
+        !a->topk_slots || !a->out) {
+        mono_set_error("mono_sparse_mla_launch_noalloc: rows, heads, topk >= 1 and q, kv_pages, topk_slots, out required");
+        return MONO_E_ARG;
+    }
+    if (a->rows > mono::kNoAllocRows || a->heads > mono::kNoAllocHeads || a->topk > mono::kNoAllocTopk) {
+        mono_set_error("mono_sparse_mla_launch_noalloc: %d rows x %d heads x %d keys exceeds the built-in scratch "
+                       "(at most %d x %d x %d); use mono_sparse_mla_launch with a caller-provided scratch buffer",
+                       a->rows, a->heads, a->topk, mono::kNoAllocRows, mono::kNoAllocHeads, mono::kNoAllocTopk);
+        return MONO_E_ARG;
+    }
+    if ((reinterpret_cast<uintptr_t>(a->kv_pages) & 15) || (reinterpret_cast<uintptr_t>(a->q) & 15)) {
+        mono_set_error("mono_sparse_mla_launch_noalloc: q and kv_pages must be 16-byte aligned");
+        return MONO_E_ARG;
+    }
+    void* scratch = noalloc_scratch_for_current_device();
+    if (scratch == nullptr) return MONO_E_DRIVER;
+    mono_sparse_mla_args args = *a;
+    args.scratch = scratch;  // whatever the caller put there is ignored
+    const int nsplit = (args.topk + mono::kSplit - 1) / mono::kSplit;
+    const size_t smem = sizeof(mono::MlaSmem) + 128;
+    static thread_local bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(mono::sparse_mla_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
+            mono_set_error("mono_sparse_mla_launch_noalloc: %s", cudaGetErrorString(e));
+            return (int)e;
+        }
+        attr_set = true;
+    }
+    int grid = args.rows * nsplit;
+    const int sms = mono_sm_count();
+    if (sms <= 0) return MONO_E_DRIVER;
+    if (grid > 2 * sms) grid = 2 * sms;
+    // Nothing in the scratch has to start at zero: every partial the merge reads is
+    // written by this call's split kernel first (same stream, so in order).
+    mono::sparse_mla_split_kernel<<<grid, mono::kMlaThreads, smem, (cudaStream_t)stream>>>(args, nsplit);
+    mono::sparse_mla_merge_kernel<<<args.rows * args.heads, 256, 0, (cudaStream_t)stream>>>(args, nsplit);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) mono_set_error("mono_sparse_mla_launch_noalloc: %s", cudaGetErrorString(e));
+    return (int)e;
+}
