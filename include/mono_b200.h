@@ -396,6 +396,11 @@ int mono_index_topk_launch(const mono_index_args* a, void* stream);
  * are what in-kernel pushes store to.  These five calls are the only ones that allocate
  * or map memory, and they run at build time, never inside a step. */
 #define MONO_IPC_HANDLE_BYTES 64
+int mono_peer_alloc(size_t bytes, void** out_ptr);
+int mono_peer_export(void* ptr, unsigned char handle[MONO_IPC_HANDLE_BYTES]);
+int mono_peer_open(const unsigned char handle[MONO_IPC_HANDLE_BYTES], void** out_ptr);
+int mono_peer_close(void* opened_ptr);
+int mono_peer_free(void* ptr);
 
 /* sizeof() of the argument structs, by index (0 gemv_job, 1 gemv_args, 2 act_prep,
  * 3 route, 4 mid, 5 sparse_mla, 6 reduce, 7 rowdot, ...): lets a binding check its mirror. */

@@ -153,6 +153,11 @@ SYMBOLS = {
     "mono_index_score_launch": (i32, [C.POINTER(IndexArgs), vp]),
     "mono_index_topk_launch": (i32, [C.POINTER(IndexArgs), vp]),
     "mono_struct_size": (C.c_size_t, [i32]),
+    "mono_peer_alloc": (i32, [C.c_size_t, C.POINTER(vp)]),
+    "mono_peer_export": (i32, [vp, C.POINTER(C.c_ubyte * 64)]),
+    "mono_peer_open": (i32, [C.POINTER(C.c_ubyte * 64), C.POINTER(vp)]),
+    "mono_peer_close": (i32, [vp]),
+    "mono_peer_free": (i32, [vp]),
 }
 
 

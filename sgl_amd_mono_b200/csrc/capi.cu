@@ -103,6 +103,60 @@ extern "C" int mono_tmap_encode(mono_tmap_t* out, const void* base, uint64_t inn
     return 0;
 }
 
+// ---- symmetric peer memory over CUDA IPC
+extern "C" int mono_peer_alloc(size_t bytes, void** out_ptr) {
+    if (!out_ptr || bytes == 0) {
+        mono_set_error("mono_peer_alloc: null pointer or zero size");
+        return MONO_E_ARG;
+    }
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e == cudaSuccess) e = cudaMemset(p, 0, bytes);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        mono_set_error("mono_peer_alloc(%zu): %s", bytes, cudaGetErrorString(e));
+        if (p) cudaFree(p);
+        return (int)e;
+    }
+    *out_ptr = p;
+    return 0;
+}
+extern "C" int mono_peer_export(void* ptr, unsigned char handle[MONO_IPC_HANDLE_BYTES]) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == MONO_IPC_HANDLE_BYTES, "IPC handle size");
+    if (!ptr || !handle) return MONO_E_ARG;
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, ptr);
+    if (e != cudaSuccess) {
+        mono_set_error("mono_peer_export: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    memcpy(handle, &h, sizeof(h));
+    return 0;
+}
+extern "C" int mono_peer_open(const unsigned char handle[MONO_IPC_HANDLE_BYTES], void** out_ptr) {
+    if (!handle || !out_ptr) return MONO_E_ARG;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    cudaError_t e = cudaIpcOpenMemHandle(out_ptr, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+        mono_set_error("mono_peer_open: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    return 0;
+}
+extern "C" int mono_peer_close(void* opened_ptr) {
+    if (!opened_ptr) return MONO_E_ARG;
+    cudaError_t e = cudaIpcCloseMemHandle(opened_ptr);
+    if (e != cudaSuccess) mono_set_error("mono_peer_close: %s", cudaGetErrorString(e));
+    return (int)e;
+}
+extern "C" int mono_peer_free(void* ptr) {
+    if (!ptr) return MONO_E_ARG;
+    cudaError_t e = cudaFree(ptr);
+    if (e != cudaSuccess) mono_set_error("mono_peer_free: %s", cudaGetErrorString(e));
+    return (int)e;
+}
+
 extern "C" size_t mono_struct_size(int which) {
     switch (which) {
         case 0: return sizeof(mono_gemv_job);
