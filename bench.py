@@ -258,8 +258,133 @@ class MoeWorkload:
         return statistics.median(ts) * 1e6 * self.rows, f"1 of {self.rows} rows, scaled by rows; median of 3"
 
 
-WORKLOADS = {"sparse_mla": SparseMlaWorkload, "moe": MoeWorkload}
-DEFAULT_WORKLOAD = "sparse_mla"
+class LayerWorkload:
+    """BASELINE config 3: the full DeepSeek-V3-shaped MLA + lightning-indexer + MoE decoder
+    layer (hidden 7168, 128 heads, q_lora 1536, kv_lora 512, 64 index heads with FP4 keys
+    and top-2048, 256 experts top-8 + shared, FP8 128x128 block scales), context 16384,
+    at TP = number of GPUs with both all-reduces inside the reduce kernel.  BASELINE lists
+    TP 2/4/8; TP 1 is the same layer unsharded, which fits one GPU."""
+
+    layers_per_step = 1
+    kernel = "gemv_kernel<FP8> (expert up/gate)"
+
+    def __init__(self, rows=8, ctx=16384):
+        self.rows, self.ctx = rows, ctx
+
+    def setup(self, dev, rank, world):
+        from sgl_amd_mono_b200 import ops, synth
+        from sgl_amd_mono_b200.config import CFG_V3
+        from sgl_amd_mono_b200.layer import MlaLayerOp, StepTables
+
+        self.cfg = cfg = CFG_V3.with_tp(world)
+        self.name = f"cfg3_v3_mla_dsa_moe_layer_tp{world}_{self.rows}rows_ctx{self.ctx}"
+        self.peer = None
+        if world > 1:
+            import torch.distributed as dist
+            from sgl_amd_mono_b200.common.peer import PeerBuffer
+
+            self.cpu_group = dist.new_group(backend="gloo")
+            self.peer = PeerBuffer(cfg.hidden, rank, world, self.cpu_group, dev)
+        self.w = synth.layer_weights(cfg, rank, dev)
+        step = synth.decode_step(cfg, self.rows, self.ctx, device=dev)
+        self.tables = StepTables(step.positions, step.slots, step.page_table, step.kv_pages, step.idx_pages, step.cos, step.sin)
+        self.op = MlaLayerOp(cfg, self.w, dev, max_ctx=self.ctx, peer=self.peer,
+                             guard=self.peer.guard if self.peer else None)
+        self.ops = ops
+        g = torch.Generator().manual_seed(0)
+        self.h_host = torch.randn(self.rows, cfg.hidden, generator=g).bfloat16().pin_memory()
+        self.h = self.h_host.to(dev)
+        self.h_in = torch.empty_like(self.h)
+        self.out_host = torch.empty_like(self.h_host).pin_memory()
+        self._eager()
+        torch.cuda.synchronize()
+        rc, words = ops.guard_read(self.op.guard)
+        if rc != 0:
+            raise RuntimeError(f"guard words after the first step: {words}")
+        self.launches_per_step = 23 + (1 if world > 1 else 0)
+        # one CUDA graph of the step, as the reference times its layers (time_layers.py:38-77)
+        self.graph = None
+        if os.environ.get("MONO_BENCH_GRAPH", "1") == "1":
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._eager()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=s):
+                    self._eager()
+            torch.cuda.current_stream().wait_stream(s)
+            self.graph = g
+
+    def _eager(self):
+        self.out = self.op.launch(self.h, self.tables)
+        if self.peer is not None:
+            self.ops.epoch_advance(self.op.guard)
+
+    def step(self):
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self._eager()
+
+    def e2e_step(self):
+        self.h.copy_(self.h_host, non_blocking=True)
+        self.step()
+        self.out_host.copy_(self.out, non_blocking=True)
+        torch.cuda.synchronize()
+
+    def e2e_bytes(self):
+        return self.h_host.numel() * 2, self.out_host.numel() * 2
+
+    def layer_bytes(self):
+        c, u = self.cfg, int(self.op.ffn.n_expert.item())
+        hl, il, h = c.heads_local, c.inter_local, c.hidden
+        rep = (c.q_lora + 576) * h + c.index_heads * 128 * c.q_lora + 128 * h + c.index_heads * h * 2 + c.n_experts * h * 2
+        shard = hl * 192 * c.q_lora + hl * 256 * 512 + h * hl * 128
+        experts = (1 + u) * 3 * il * h
+        kv = self.rows * min(c.index_topk, self.ctx) * 580
+        idx = self.rows * self.ctx * 68
+        return rep + shard + experts + kv + idx, u
+
+    def roofline_probe(self):
+        u = int(self.op.ffn.n_expert.item())
+        c = self.cfg
+        return (u + 1) * 2 * c.inter_local * c.hidden, lambda: self.op.ffn.up.launch(self.rows)
+
+    def config(self):
+        c = self.cfg
+        nbytes, u = self.layer_bytes()
+        return {"workload": self.name, "rows": self.rows, "context": self.ctx, "hidden": c.hidden, "heads": c.n_heads,
+                "experts": c.n_experts, "top_k": c.top_k, "inter": c.inter, "tp": c.tp, "distinct_experts": u,
+                "layer_algorithmic_bytes_per_rank": nbytes, "cuda_graph": self.graph is not None,
+                "weights": "fp8_e4m3 128x128 block scales", "l2": "256 MiB buffer written between timed iterations"}
+
+    def cpu_sample(self):
+        from oracle import layers as OL
+
+        class Lazy:  # experts are copied to the host only when the oracle routes to them
+            def __init__(self, v):
+                self.v, self.c = v, {}
+
+            def __getitem__(self, e):
+                if e not in self.c:
+                    self.c[e] = self.v[e].cpu()
+                return self.c[e]
+
+        w = {k: (Lazy(v) if k in ("w13", "w13_s", "w2", "w2_s") else v.cpu()) for k, v in self.w.items()}
+        t = self.tables
+        h = self.h_host[:1]
+        args = (self.cfg, [w], h, t.positions[:1].cpu(), t.slots[:1].cpu(), t.page_table[:1].cpu(), t.cos.cpu(), t.sin.cpu())
+        kv, ix = t.kv_pages.cpu(), t.idx_pages.cpu()
+        ts = []
+        for _ in range(2):
+            t0 = time.perf_counter()
+            OL.layer_all_ranks(*args, kv.clone(), ix.clone())
+            ts.append(time.perf_counter() - t0)
+        return min(ts) * 1e6 * self.rows, f"1 of {self.rows} rows of this rank's layer share, scaled by rows; best of 2"
+
+
+WORKLOADS = {"sparse_mla": SparseMlaWorkload, "moe": MoeWorkload, "layer": LayerWorkload}
+DEFAULT_WORKLOAD = "layer"
 
 
 # ------------------------------------------------------------------ main
@@ -369,7 +494,8 @@ def main() -> None:
         "vs_baseline": None, "dtype": "fp8_e4m3 weights / bf16 activations, f32 accumulate", "data": "synthetic",
         "config": wl.config(), "clocks": sampler.summary(), "gpu_launches": wl.launches_per_step * args.steps,
         "e2e": {"value": e2e_us, "unit": "us", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "roofline": {"bound": "hbm", "kernel": wl.kernel, "achieved": achieved, "peak": peak, "unit": "GB/s",
+        "roofline": {"bound": "hbm", "kernel": wl.kernel, **({"layer_achieved_gbs": wl.layer_bytes()[0] / (us_per_layer * 1e-6) / 1e9,
+                     "layer_frac": wl.layer_bytes()[0] / (us_per_layer * 1e-6) / 1e9 / peak} if hasattr(wl, "layer_bytes") else {}), "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "traffic": None, "algorithmic_bytes": nbytes,
                      "kernel_us": probe_ms * 1000.0, "peak_source": peak_src},
     }

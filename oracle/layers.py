@@ -20,10 +20,11 @@ def _w8(w, name):
     return w[name], w[name + "_s"]
 
 
-def uk_uv(cfg, w, head: int):
+def uk_uv(cfg, w, head: int, full=None):
     """Dequantised W_UK [nope, 512] and W_UV [v, 512] of local head ``head``."""
     per = cfg.nope + cfg.v_head
-    full = Q.fp8_block_dequant(*_w8(w, "kv_b"))
+    if full is None:
+        full = Q.fp8_block_dequant(*_w8(w, "kv_b"))
     blk = full[head * per : (head + 1) * per]
     return blk[: cfg.nope], blk[cfg.nope :]
 
@@ -47,8 +48,9 @@ def attn_front(cfg, w, h, positions, slots, cos, sin, kv_pages, idx_pages):
     q_nope = Q.bf(q[..., : cfg.nope])
     q_pe = Q.bf(S.rope_interleaved(q[..., cfg.nope :], c, s))
     q_lat = torch.empty(q.shape[0], hl, 512)
+    kvb = Q.fp8_block_dequant(*_w8(w, "kv_b"))
     for hd in range(hl):
-        wuk, _ = uk_uv(cfg, w, hd)
+        wuk, _ = uk_uv(cfg, w, hd, kvb)
         q_lat[:, hd] = Q.bf(q_nope[:, hd] @ wuk)
     r["q_full"] = torch.cat([q_lat, q_pe], -1)
     if cfg.index_heads:
@@ -96,8 +98,9 @@ def attn_back(cfg, w, r, topk, kv_pages):
     lat = S.sparse_mla(r["q_full"].to(torch.bfloat16), kv_pages, topk,
                        S.sm_scale_mla(cfg.nope, cfg.rope)).float()
     o = torch.empty(lat.shape[0], hl, cfg.v_head)
+    kvb = Q.fp8_block_dequant(*_w8(w, "kv_b"))
     for hd in range(hl):
-        _, wuv = uk_uv(cfg, w, hd)
+        _, wuv = uk_uv(cfg, w, hd, kvb)
         o[:, hd] = Q.bf(lat[:, hd] @ wuv.T)
     r["attn_lat"], r["attn_o"] = lat, o
     return S.gemv_fp8_block(o.reshape(lat.shape[0], -1), *_w8(w, "o_proj"))

@@ -210,14 +210,17 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const mono_route_a
 constexpr int kRowdotThreads = 256;
 
 __global__ void __launch_bounds__(kRowdotThreads) rowdot_kernel(const mono_rowdot_args a) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n = blockIdx.x * (kRowdotThreads / 32) + warp;
-    if (n >= a.n) return;
+    // one CTA per output column; the 256 threads split K (4 values per thread per 1024),
+    // so every weight load of the column is in flight at once
+    __shared__ float red[kRowdotThreads / 32][kMaxRows];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n = blockIdx.x;
     float acc[kMaxRows];
 #pragma unroll
     for (int r = 0; r < kMaxRows; ++r) acc[r] = 0.f;
     const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(a.x_bf16);
-    for (int k = lane * 4; k < a.k; k += 128) {
+#pragma unroll 2
+    for (int k = tid * 4; k < a.k; k += kRowdotThreads * 4) {
         float w[4];
         if (a.w_is_f32) {
             const float4 v = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.w) + (size_t)n * a.k + k));
@@ -231,7 +234,7 @@ __global__ void __launch_bounds__(kRowdotThreads) rowdot_kernel(const mono_rowdo
 #pragma unroll
         for (int r = 0; r < kMaxRows; ++r) {
             if (r < a.rows) {
-                const uint2 xv = *reinterpret_cast<const uint2*>(x + (size_t)r * a.k + k);
+                const uint2 xv = __ldg(reinterpret_cast<const uint2*>(x + (size_t)r * a.k + k));
                 const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.x));
                 const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.y));
                 acc[r] += lo.x * w[0] + lo.y * w[1] + hi.x * w[2] + hi.y * w[3];
@@ -242,8 +245,15 @@ __global__ void __launch_bounds__(kRowdotThreads) rowdot_kernel(const mono_rowdo
     for (int r = 0; r < kMaxRows; ++r) {
         if (r < a.rows) {
             const float s = warp_sum(acc[r]);
-            if (lane == 0) a.out[(size_t)r * a.out_ld + n] = s * a.out_scale;
+            if (lane == 0) red[warp][r] = s;
         }
+    }
+    __syncthreads();
+    if (tid < a.rows) {
+        float s = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < kRowdotThreads / 32; ++wv) s += red[wv][tid];
+        a.out[(size_t)tid * a.out_ld + n] = s * a.out_scale;
     }
 }
 
@@ -423,8 +433,7 @@ extern "C" int mono_rowdot_launch(const mono_rowdot_args* a, void* stream) {
         mono_set_error("mono_rowdot_launch: rows 1..16, k a multiple of 128 and all pointers required");
         return MONO_E_ARG;
     }
-    const int per = mono::kRowdotThreads / 32;
-    mono::rowdot_kernel<<<(a->n + per - 1) / per, mono::kRowdotThreads, 0, (cudaStream_t)stream>>>(*a);
+    mono::rowdot_kernel<<<a->n, mono::kRowdotThreads, 0, (cudaStream_t)stream>>>(*a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_rowdot_launch: %s", cudaGetErrorString(e));
     return (int)e;

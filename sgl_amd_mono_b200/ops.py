@@ -290,6 +290,11 @@ def index_topk(a) -> None:
     L.check(L.load().mono_index_topk_launch(C.byref(a), _stream()), "mono_index_topk_launch")
 
 
+def epoch_advance(guard) -> None:
+    """Adds 1 to the epoch word on the device (after the last layer of a step)."""
+    L.check(L.load().mono_epoch_advance_launch(guard.data_ptr(), _stream()), "mono_epoch_advance_launch")
+
+
 def guard_read(guard: torch.Tensor):
     out = (C.c_int32 * 3)()
     rc = L.load().mono_guard_read(guard.data_ptr(), C.byref(out), _stream())
