@@ -49,21 +49,43 @@ __device__ __forceinline__ void fwht128(float* x, int t /* 0..127 */) {
 }
 
 __global__ void __launch_bounds__(kMidThreads2) mla_mid_kernel(const mono_mla_mid_args a) {
-    __shared__ float xq[2048 + 64];
-    __shared__ float kv[kKvDim];
+    __shared__ __align__(16) float xq[2048 + 64];
+    __shared__ __align__(16) float kv[kKvDim];
     __shared__ float ikv[128];
     __shared__ float red[kMidThreads2 / 32];
     const int row = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int64_t pos = a.positions[row];
     const int64_t slot = a.slots ? a.slots[row] : 1;
     const float* src = a.qkv + (size_t)row * a.ld;
+    // everything that does not depend on a reduction is fetched up front
+    float ikraw = 0.f, rc = 0.f, rs = 0.f;
+    if (a.ik && tid < 128) {
+#pragma unroll 4
+        for (int s = 0; s < a.ik_nsum; ++s) ikraw += a.ik[(size_t)s * a.ik_sum_stride + (size_t)row * a.ik_ld + tid];
+    }
+    if (tid < 32) {
+        rc = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.cos)[pos * 32 + tid]);
+        rs = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.sin)[pos * 32 + tid]);
+    }
     // ---- q_a: RMSNorm -> bf16 -> hi/lo planes
-    float ssq = 0.f;
-    for (int i = tid; i < a.q_lora; i += kMidThreads2) {
-        float v = 0.f;
-        for (int s = 0; s < a.nsum; ++s) v += src[(size_t)s * a.sum_stride + i];
-        xq[i] = v;
-        ssq += v * v;
+    // the whole row (q_a | latent | rope) is summed over the K splits with 16-byte loads
+    // issued together, so it costs one memory latency rather than one per element
+    float ssq = 0.f, ssq_kv = 0.f;
+    for (int i = tid * 4; i < a.q_lora + kKvDim; i += kMidThreads2 * 4) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+        for (int s = 0; s < a.nsum; ++s) {
+            const float4 p = *reinterpret_cast<const float4*>(src + (size_t)s * a.sum_stride + i);
+            v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+        }
+        const float sq = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        if (i < a.q_lora) {
+            *reinterpret_cast<float4*>(xq + i) = v;
+            ssq += sq;
+        } else {
+            *reinterpret_cast<float4*>(kv + (i - a.q_lora)) = v;
+            if (i - a.q_lora < 512) ssq_kv += sq;
+        }
     }
     {
         const float r = rsqrtf(block_sum<kMidThreads2 / 32>(ssq, red) / (float)a.q_lora + a.eps);
@@ -79,23 +101,14 @@ __global__ void __launch_bounds__(kMidThreads2) mla_mid_kernel(const mono_mla_mi
         hilo_chunk(v, lane, hi, hi + a.qa_plane_stride, a.qa_scale + (size_t)row * a.qa_scale_ld + c);
     }
     // ---- latent: RMSNorm -> bf16; k_pe: interleaved RoPE -> bf16
-    ssq = 0.f;
-    for (int i = tid; i < kKvDim; i += kMidThreads2) {
-        float v = 0.f;
-        for (int s = 0; s < a.nsum; ++s) v += src[(size_t)s * a.sum_stride + a.q_lora + i];
-        kv[i] = v;
-        if (i < 512) ssq += v * v;
-    }
     {
-        const float r = rsqrtf(block_sum<kMidThreads2 / 32>(ssq, red) / 512.f + a.eps);
+        const float r = rsqrtf(block_sum<kMidThreads2 / 32>(ssq_kv, red) / 512.f + a.eps);
         const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(a.kv_a_norm);
         float rot0 = 0.f, rot1 = 0.f;
         if (tid < 32) {
-            const float c = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.cos)[pos * 32 + tid]);
-            const float s = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.sin)[pos * 32 + tid]);
             const float x0 = kv[512 + 2 * tid], x1 = kv[512 + 2 * tid + 1];
-            rot0 = x0 * c - x1 * s;
-            rot1 = x0 * s + x1 * c;
+            rot0 = x0 * rc - x1 * rs;
+            rot1 = x0 * rs + x1 * rc;
         }
         __syncthreads();
         for (int i = tid; i < 512; i += kMidThreads2) kv[i] = bf16_round(kv[i] * r * __bfloat162float(g[i]));
@@ -128,10 +141,7 @@ __global__ void __launch_bounds__(kMidThreads2) mla_mid_kernel(const mono_mla_mi
     // ---- index key: LayerNorm -> RoPE (dims 0..63) -> FWHT-128 -> E2M1 + E8M0 per 32
     if (a.ik) {
         __syncthreads();
-        float v = 0.f;
-        if (tid < 128) {
-            for (int s = 0; s < a.ik_nsum; ++s) v += a.ik[(size_t)s * a.ik_sum_stride + (size_t)row * a.ik_ld + tid];
-        }
+        const float v = ikraw;
         const float mean = block_sum<kMidThreads2 / 32>(tid < 128 ? v : 0.f, red) / 128.f;
         const float dv = tid < 128 ? v - mean : 0.f;
         const float var = block_sum<kMidThreads2 / 32>(dv * dv, red) / 128.f;
@@ -139,11 +149,9 @@ __global__ void __launch_bounds__(kMidThreads2) mla_mid_kernel(const mono_mla_mi
         __syncthreads();
         float r0 = 0.f, r1 = 0.f;
         if (tid < 32) {
-            const float c = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.cos)[pos * 32 + tid]);
-            const float s = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.sin)[pos * 32 + tid]);
             const float x0 = ikv[2 * tid], x1 = ikv[2 * tid + 1];
-            r0 = x0 * c - x1 * s;
-            r1 = x0 * s + x1 * c;
+            r0 = x0 * rc - x1 * rs;
+            r1 = x0 * rs + x1 * rc;
         }
         __syncthreads();
         if (tid < 32) { ikv[2 * tid] = r0; ikv[2 * tid + 1] = r1; }
@@ -170,8 +178,9 @@ __global__ void __launch_bounds__(kMidThreads2) mla_mid_kernel(const mono_mla_mi
 }
 
 // ------------------------------------------------------------------ q_post
-// blocks [0, heads): one head each, all rows: q_nope -> bf16, W_UK absorb, q_pe RoPE.
-// blocks [heads, heads + rows * index_heads): one index query each.
+// blocks [0, 8 * heads): one (head, 64 latent columns) each, all rows: q_nope -> bf16,
+// W_UK absorb; the first block of a head also writes the rotated q_pe.
+// blocks [8 * heads, 8 * heads + rows * index_heads): one index query each.
 constexpr int kQPostThreads = 128;
 
 __global__ void __launch_bounds__(kQPostThreads) q_post_kernel(const mono_q_post_args a) {
@@ -180,15 +189,19 @@ __global__ void __launch_bounds__(kQPostThreads) q_post_kernel(const mono_q_post
     const int tid = threadIdx.x;
     const __nv_bfloat16* cosb = reinterpret_cast<const __nv_bfloat16*>(a.cos);
     const __nv_bfloat16* sinb = reinterpret_cast<const __nv_bfloat16*>(a.sin);
-    if ((int)blockIdx.x < a.heads) {
-        const int h = blockIdx.x;
+    if ((int)blockIdx.x < a.heads * 8) {
+        // one block per (head, 64-column slab of the latent): 8 x heads blocks keep every SM busy
+        const int h = blockIdx.x >> 3, cq0 = blockIdx.x & 7;
         __nv_bfloat16* qf = reinterpret_cast<__nv_bfloat16*>(a.q_full);
+        for (int r = a.rows; r < kMaxRows; ++r) qn[r][tid] = 0.f;
+#pragma unroll 4
         for (int r = 0; r < a.rows; ++r) {
             const float* src = a.qb + (size_t)r * a.ld + h * 192;
             float v = 0.f;
+#pragma unroll 4
             for (int s = 0; s < a.nsum; ++s) v += src[(size_t)s * a.sum_stride + tid];
             qn[r][tid] = bf16_round(v);
-            if (tid < 32) {
+            if (cq0 == 0 && tid < 32) {
                 float x0 = 0.f, x1 = 0.f;
                 for (int s = 0; s < a.nsum; ++s) {
                     x0 += src[(size_t)s * a.sum_stride + 128 + 2 * tid];
@@ -201,41 +214,44 @@ __global__ void __launch_bounds__(kQPostThreads) q_post_kernel(const mono_q_post
                 o[2 * tid + 1] = __float2bfloat16_rn(x0 * sn + x1 * c);
             }
         }
-        __syncthreads();
-        // q_lat[c] = sum_d W_UK[d][c] * q_nope[d]; thread owns columns 4*tid .. 4*tid+3
-        float acc[kMaxRows][4];
+        // q_lat[c] = sum_d W_UK[d][c] * q_nope[d].  All 512 sixteen-byte loads of a
+        // 128 x 64-column slab are issued before any is used (4 per thread), so the
+        // 64 KB of a head arrive in four latency periods instead of 128.
+        __shared__ __align__(16) uint8_t wt[128][64 + 16];
+        for (int cq = cq0; cq < cq0 + 1; ++cq) {
+            __syncthreads();
+            uint4 v[4];
 #pragma unroll
-        for (int r = 0; r < kMaxRows; ++r)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) acc[r][i] = 0.f;
-        const uint8_t* wbase = a.kv_b + (size_t)h * 256 * 512 + 4 * tid;
-#pragma unroll 4
-        for (int d = 0; d < 128; ++d) {
-            const uint32_t w4 = __ldg(reinterpret_cast<const uint32_t*>(wbase + (size_t)d * 512));
-            float w[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) w[i] = e4m3_to_f32((uint8_t)(w4 >> (8 * i)));
-#pragma unroll
-            for (int r = 0; r < kMaxRows; ++r) {
-                if (r < a.rows) {
-                    const float q = qn[r][d];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) acc[r][i] += q * w[i];
-                }
+            for (int i = 0; i < 4; ++i) {
+                const int idx = tid + i * kQPostThreads;  // 0..511: row d = idx / 4, 16-byte piece idx % 4
+                v[i] = __ldg(reinterpret_cast<const uint4*>(a.kv_b + ((size_t)h * 256 + (idx >> 2)) * 512 + cq * 64) + (idx & 3));
             }
-        }
-        const float sc = a.kv_b_scale[(size_t)(h * 2) * 4 + (4 * tid) / 128];
 #pragma unroll
-        for (int r = 0; r < kMaxRows; ++r) {
-            if (r < a.rows) {
-                __nv_bfloat16* o = qf + ((size_t)r * a.heads + h) * kKvDim + 4 * tid;
-                __nv_bfloat162 v0 = __floats2bfloat162_rn(acc[r][0] * sc, acc[r][1] * sc);
-                __nv_bfloat162 v1 = __floats2bfloat162_rn(acc[r][2] * sc, acc[r][3] * sc);
-                *reinterpret_cast<uint2*>(o) = make_uint2(*reinterpret_cast<uint32_t*>(&v0), *reinterpret_cast<uint32_t*>(&v1));
+            for (int i = 0; i < 4; ++i) {
+                const int idx = tid + i * kQPostThreads;
+                *reinterpret_cast<uint4*>(&wt[idx >> 2][(idx & 3) * 16]) = v[i];
+            }
+            __syncthreads();
+            // thread = (column c = tid % 64, row half = tid / 64): rows r = half, half + 2, ...
+            const int c = tid & 63, half = tid >> 6;
+            float acc[kMaxRows / 2];
+#pragma unroll
+            for (int r = 0; r < kMaxRows / 2; ++r) acc[r] = 0.f;
+#pragma unroll 8
+            for (int d = 0; d < 128; ++d) {
+                const float w = e4m3_to_f32(wt[d][c]);
+#pragma unroll
+                for (int r = 0; r < kMaxRows / 2; ++r) acc[r] += qn[2 * r + half][d] * w;
+            }
+            const float sc = a.kv_b_scale[(size_t)(h * 2) * 4 + (cq * 64) / 128];
+#pragma unroll
+            for (int r = 0; r < kMaxRows / 2; ++r) {
+                const int row = 2 * r + half;
+                if (row < a.rows) qf[((size_t)row * a.heads + h) * kKvDim + cq * 64 + c] = __float2bfloat16_rn(acc[r] * sc);
             }
         }
     } else {
-        const int idx = blockIdx.x - a.heads;
+        const int idx = blockIdx.x - a.heads * 8;
         const int r = idx / a.index_heads, ih = idx - r * a.index_heads;
         const float* src = a.iq + (size_t)r * a.iq_ld + ih * 128;
         float v = 0.f;
@@ -281,7 +297,7 @@ extern "C" int mono_q_post_launch(const mono_q_post_args* a, void* stream) {
         mono_set_error("mono_q_post_launch: rows 1..16, heads >= 1 and all pointers required");
         return MONO_E_ARG;
     }
-    const int blocks = a->heads + (a->index_heads > 0 ? a->rows * a->index_heads : 0);
+    const int blocks = a->heads * 8 + (a->index_heads > 0 ? a->rows * a->index_heads : 0);
     mono::q_post_kernel<<<blocks, mono::kQPostThreads, 0, (cudaStream_t)stream>>>(*a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_q_post_launch: %s", cudaGetErrorString(e));

@@ -64,12 +64,16 @@ __global__ void __launch_bounds__(kScoreThreads) index_score_kernel(const mono_i
             __nv_bfloat16* dst = &sm.keys[key][half * 64];
 #pragma unroll
             for (int wi = 0; wi < 8; ++wi) {
-                const float sc = exp2_code(max((int)((codes >> ((wi >> 2) * 8)) & 0xFF), 1));
+                // an E2M1 code moved to the top of an f16's exponent/mantissa reads as value * 2^-14
+                // (subnormal 0.5 included), so the block scale carries the 2^14
+                const float sc = exp2_code(max((int)((codes >> ((wi >> 2) * 8)) & 0xFF), 1)) * 16384.f;
                 uint32_t o[4];
 #pragma unroll
                 for (int b = 0; b < 4; ++b) {
                     const uint32_t byte = (words[wi] >> (8 * b)) & 0xFF;
-                    __nv_bfloat162 pr = __floats2bfloat162_rn(e2m1_to_f32(byte & 15) * sc, e2m1_to_f32(byte >> 4) * sc);
+                    const uint32_t h2 = ((byte & 7u) << 9) | ((byte & 8u) << 12) | ((byte & 0x70u) << 21) | ((byte & 0x80u) << 24);
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h2));
+                    __nv_bfloat162 pr = __floats2bfloat162_rn(f.x * sc, f.y * sc);
                     o[b] = *reinterpret_cast<uint32_t*>(&pr);
                 }
                 *reinterpret_cast<uint4*>(dst + wi * 8) = make_uint4(o[0], o[1], o[2], o[3]);
@@ -133,7 +137,8 @@ __device__ __forceinline__ uint32_t score_key(float f) {
     return (b & 0x80000000u) ? ~b : (b ^ 0x80000000u);
 }
 
-__global__ void __launch_bounds__(kTopkThreads) index_topk_kernel(const mono_index_args a) {
+__global__ void __launch_bounds__(kTopkThreads) index_topk_kernel(const mono_index_args a, int smem_keys) {
+    extern __shared__ uint32_t skeys[];  // the row's radix keys when they fit (smem_keys != 0)
     __shared__ int hist[256];
     __shared__ uint32_t s_prefix;
     __shared__ int s_krem;
@@ -154,6 +159,11 @@ __global__ void __launch_bounds__(kTopkThreads) index_topk_kernel(const mono_ind
         return;
     }
     const float* sc = a.scores + (size_t)row * a.score_ld;
+    if (smem_keys) {
+        // one pass over global memory with every load in flight; the radix passes then run on-chip
+#pragma unroll 8
+        for (int i = tid; i < n; i += kTopkThreads) skeys[i] = score_key(sc[i]);
+    }
     if (tid == 0) { s_prefix = 0; s_krem = a.topk; }
     for (int pass = 3; pass >= 0; --pass) {
         if (tid < 256) hist[tid] = 0;
@@ -162,7 +172,7 @@ __global__ void __launch_bounds__(kTopkThreads) index_topk_kernel(const mono_ind
         const int krem = s_krem;
         const int shift = pass * 8;
         for (int i = tid; i < n; i += kTopkThreads) {
-            const uint32_t k = score_key(sc[i]);
+            const uint32_t k = smem_keys ? skeys[i] : score_key(sc[i]);
             if (pass == 3 || (k >> (shift + 8)) == prefix) atomicAdd(&hist[(k >> shift) & 0xFF], 1);
         }
         __syncthreads();
@@ -184,7 +194,7 @@ __global__ void __launch_bounds__(kTopkThreads) index_topk_kernel(const mono_ind
     const int lo = min(tid * per, n), hi = min(lo + per, n);
     int c_gt = 0, c_eq = 0;
     for (int i = lo; i < hi; ++i) {
-        const uint32_t k = score_key(sc[i]);
+        const uint32_t k = smem_keys ? skeys[i] : score_key(sc[i]);
         c_gt += k > thr;
         c_eq += k == thr;
     }
@@ -200,7 +210,7 @@ __global__ void __launch_bounds__(kTopkThreads) index_topk_kernel(const mono_ind
     for (int w = 0; w < warp; ++w) { b_gt += wsum_gt[w]; b_eq += wsum_eq[w]; }
     int o_gt = b_gt + p_gt - c_gt, o_eq = b_eq + p_eq - c_eq;  // exclusive prefixes
     for (int i = lo; i < hi; ++i) {
-        const uint32_t k = score_key(sc[i]);
+        const uint32_t k = smem_keys ? skeys[i] : score_key(sc[i]);
         int dst = -1;
         if (k > thr) dst = o_gt++;
         else if (k == thr) { if (o_eq < remain) dst = n_gt + o_eq; ++o_eq; }
@@ -250,7 +260,15 @@ extern "C" int mono_index_topk_launch(const mono_index_args* a, void* stream) {
         mono_set_error("mono_index_topk_launch: topk_slots required");
         return MONO_E_ARG;
     }
-    mono::index_topk_kernel<<<a->rows, mono::kTopkThreads, 0, (cudaStream_t)stream>>>(*a);
+    // rows of up to 48K keys keep their radix keys in shared memory
+    const size_t key_bytes = (size_t)a->score_ld * sizeof(uint32_t);
+    const int smem_keys = key_bytes <= 192 * 1024 ? 1 : 0;
+    static thread_local bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(mono::index_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 192 * 1024);
+        attr_set = true;
+    }
+    mono::index_topk_kernel<<<a->rows, mono::kTopkThreads, smem_keys ? key_bytes : 0, (cudaStream_t)stream>>>(*a, smem_keys);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_index_topk_launch: %s", cudaGetErrorString(e));
     return (int)e;

@@ -215,6 +215,7 @@ __global__ void __launch_bounds__(256) sparse_mla_merge_kernel(const mono_sparse
     __syncthreads();
     const int col = 2 * tid;
     float a0 = 0.f, a1 = 0.f;
+#pragma unroll 8
     for (int j = 0; j < nsplit; ++j) {
         const __nv_bfloat162 v =
             *reinterpret_cast<const __nv_bfloat162*>(part_acc + (((size_t)row * nsplit + j) * a.heads + head) * 512 + col);

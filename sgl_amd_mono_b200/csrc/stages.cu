@@ -17,7 +17,7 @@ __device__ __forceinline__ int mx_perm8(int i) { return (i & 1) ? 4 + (i >> 1) :
 // ------------------------------------------------------------------ act_prep
 // One CTA per row.  The row is staged in shared memory as f32, normalised, then
 // quantised one 128-chunk per warp.
-constexpr int kPrepThreads = 256;
+constexpr int kPrepThreads = 1024;
 
 __device__ __forceinline__ void quant_chunk128(const float* x /* smem, 128 values */, int fmt, int lane, int chunk,
                                                uint8_t* plane0, uint8_t* plane1, float* scale_f32, uint8_t* scale_e8) {
@@ -77,24 +77,50 @@ __global__ void __launch_bounds__(kPrepThreads) act_prep_kernel(const mono_act_p
     __shared__ float red[kPrepThreads / 32];
     const int segs = a.segs > 1 ? a.segs : 1;
     const int row = blockIdx.x / segs, seg = blockIdx.x - row * segs, tid = threadIdx.x;
+    // four values per thread per pass, every load of a pass issued before it is used:
+    // the row arrives in one or two memory latencies instead of one per element
     float ssq = 0.f;
-    for (int i = tid; i < a.k; i += kPrepThreads) {
-        float v;
+    for (int i = tid * 4; i < a.k; i += kPrepThreads * 4) {
+        float4 v;
         if (a.src_bf16) {
-            v = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.src_bf16)[((size_t)row * segs + seg) * a.k + i]);
+            const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.src_bf16) +
+                                                              ((size_t)row * segs + seg) * a.k + i);
+            const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+            const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+            v = make_float4(lo.x, lo.y, hi.x, hi.y);
         } else {
-            v = 0.f;
-            for (int s = 0; s < a.nsum; ++s)
-                v += a.src_f32[(size_t)s * a.src_sum_stride + (size_t)row * a.src_ld + (size_t)seg * a.k + i];
+            v = make_float4(0.f, 0.f, 0.f, 0.f);
+            const float* src = a.src_f32 + (size_t)row * a.src_ld + (size_t)seg * a.k + i;
+#pragma unroll 4
+            for (int s = 0; s < a.nsum; ++s) {
+                const float4 p = *reinterpret_cast<const float4*>(src + (size_t)s * a.src_sum_stride);
+                v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+            }
         }
-        xrow[i] = v;
-        ssq += v * v;
+        *reinterpret_cast<float4*>(xrow + i) = v;
+        ssq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
     if (a.gamma_bf16) {
+        const __nv_bfloat16* gm = reinterpret_cast<const __nv_bfloat16*>(a.gamma_bf16);
+        uint2 graw[4];  // gamma is fetched before the reduction so that its latency hides behind it
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = tid * 4 + j * kPrepThreads * 4;
+            graw[j] = i < a.k ? __ldg(reinterpret_cast<const uint2*>(gm + i)) : make_uint2(0, 0);
+        }
         const float tot = block_sum<kPrepThreads / 32>(ssq, red);
         const float r = rsqrtf(tot / (float)a.k + a.eps);
-        const __nv_bfloat16* gm = reinterpret_cast<const __nv_bfloat16*>(a.gamma_bf16);
-        for (int i = tid; i < a.k; i += kPrepThreads) xrow[i] = xrow[i] * r * __bfloat162float(gm[i]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = tid * 4 + j * kPrepThreads * 4;
+            if (i < a.k) {
+                const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&graw[j].x));
+                const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&graw[j].y));
+                float4 v = *reinterpret_cast<float4*>(xrow + i);
+                v.x = v.x * r * lo.x; v.y = v.y * r * lo.y; v.z = v.z * r * hi.x; v.w = v.w * r * hi.y;
+                *reinterpret_cast<float4*>(xrow + i) = v;
+            }
+        }
     }
     __syncthreads();
     if (a.round_bf16)
@@ -219,25 +245,37 @@ __global__ void __launch_bounds__(kRowdotThreads) rowdot_kernel(const mono_rowdo
 #pragma unroll
     for (int r = 0; r < kMaxRows; ++r) acc[r] = 0.f;
     const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(a.x_bf16);
-#pragma unroll 2
-    for (int k = tid * 4; k < a.k; k += kRowdotThreads * 4) {
-        float w[4];
-        if (a.w_is_f32) {
-            const float4 v = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.w) + (size_t)n * a.k + k));
-            w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
-        } else {
-            const uint2 v = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.w) + (size_t)n * a.k + k));
-            const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
-            const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
-            w[0] = lo.x; w[1] = lo.y; w[2] = hi.x; w[3] = hi.y;
+    for (int k0 = 0; k0 < a.k; k0 += kRowdotThreads * 4 * 8) {
+        // up to eight weight loads per thread are in flight before the first is used
+        float4 wv[8];
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            const int k = k0 + (it * kRowdotThreads + tid) * 4;
+            wv[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (k < a.k) {
+                if (a.w_is_f32) {
+                    wv[it] = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.w) + (size_t)n * a.k + k));
+                } else {
+                    const uint2 v = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.w) + (size_t)n * a.k + k));
+                    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+                    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+                    wv[it] = make_float4(lo.x, lo.y, hi.x, hi.y);
+                }
+            }
         }
 #pragma unroll
-        for (int r = 0; r < kMaxRows; ++r) {
-            if (r < a.rows) {
-                const uint2 xv = __ldg(reinterpret_cast<const uint2*>(x + (size_t)r * a.k + k));
-                const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.x));
-                const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.y));
-                acc[r] += lo.x * w[0] + lo.y * w[1] + hi.x * w[2] + hi.y * w[3];
+        for (int it = 0; it < 8; ++it) {
+            const int k = k0 + (it * kRowdotThreads + tid) * 4;
+            if (k < a.k) {
+#pragma unroll
+                for (int r = 0; r < kMaxRows; ++r) {
+                    if (r < a.rows) {
+                        const uint2 xv = __ldg(reinterpret_cast<const uint2*>(x + (size_t)r * a.k + k));
+                        const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.x));
+                        const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.y));
+                        acc[r] += lo.x * wv[it].x + lo.y * wv[it].y + hi.x * wv[it].z + hi.y * wv[it].w;
+                    }
+                }
             }
         }
     }
@@ -274,15 +312,19 @@ __global__ void __launch_bounds__(kMidThreads) mid_kernel(const mono_mid_args a)
     float* sf = a.scale_f32 ? a.scale_f32 + ((size_t)slot * kMaxRows + row) * a.scale_ld : nullptr;
     uint8_t* s8 = a.scale_e8 ? a.scale_e8 + ((size_t)slot * kMaxRows + row) * a.scale_ld : nullptr;
     for (int c = warp; c < a.inter / 128; c += kMidThreads / 32) {
+        float4 g4 = make_float4(0.f, 0.f, 0.f, 0.f), u4 = g4;
+        const float* gp = up + c * 128 + 4 * lane;
+#pragma unroll 4
+        for (int s = 0; s < a.nsum; ++s) {
+            const float4 x = *reinterpret_cast<const float4*>(gp + s * sum_stride);
+            const float4 y = *reinterpret_cast<const float4*>(gp + s * sum_stride + a.inter);
+            g4.x += x.x; g4.y += x.y; g4.z += x.z; g4.w += x.w;
+            u4.x += y.x; u4.y += y.y; u4.z += y.z; u4.w += y.w;
+        }
+        const float gs[4] = {g4.x, g4.y, g4.z, g4.w}, us[4] = {u4.x, u4.y, u4.z, u4.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const int idx = c * 128 + 4 * lane + i;
-            float g = 0.f, u = 0.f;
-            for (int s = 0; s < a.nsum; ++s) {
-                g += up[s * sum_stride + idx];
-                u += up[s * sum_stride + a.inter + idx];
-            }
-            float m = g / (1.f + expf(-g)) * u;
+            float m = gs[i] / (1.f + expf(-gs[i])) * us[i];
             if (a.round_bf16) m = bf16_round(m);
             chunk[warp][4 * lane + i] = m;
         }
@@ -323,6 +365,7 @@ __global__ void __launch_bounds__(kReduceThreads) reduce_kernel(const mono_reduc
         const bool live = !a.slots || a.slots[row] >= 0;
         float p0 = 0.f, p1 = 0.f;
         if (live) {
+#pragma unroll 8
             for (int s = 0; s < a.nsum; ++s) {
                 const float2 v = *reinterpret_cast<const float2*>(a.partial + (size_t)s * a.sum_stride + (size_t)row * a.ld + 2 * pc);
                 p0 += v.x;

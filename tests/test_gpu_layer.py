@@ -108,7 +108,11 @@ def test_layer_stages_and_output(rows, ctx, pad):
         assert op.ffn.ids[i].cpu().tolist() == ids_k[i].tolist(), f"router ids of row {i}"
         assert ids_k[i].tolist() == ids_o[i].tolist(), "a near-tie flipped between the f32 logit sums: pick another seed"
     scale = float((ref.float() - h1_k.float()).abs().max())
-    assert_close_hidden(out.cpu()[live], ref[live], "layer output", scale=scale)
+    # 4e-2 of the block's scale here: after the block-FP8 recipe's O(1) weights one E4M3
+    # code step of a top-binade mid value (7 % of its chunk amax) times |W2| up to 0.4 moves
+    # an output by that much when the step falls differently in the two f32 orders; the
+    # GEMVs themselves are held to 1e-3 on identical quantised inputs in test_gpu_ffn.py
+    assert_close_hidden(out.cpu()[live], ref[live], "layer output", scale=scale, max_abs=4e-2)
     # end to end against the oracle's own chain: cosine only (selections may differ at the margin)
     full, _ = OL.layer_all_ranks(cfg, [wc], h, step.positions, step.slots, step.page_table, step.cos, step.sin,
                                  step.kv_pages.clone(), step.idx_pages.clone())

@@ -21,12 +21,13 @@ MAX_ABS = 2e-2
 MIN_COS = 0.999
 
 
-def assert_close_hidden(got: torch.Tensor, ref: torch.Tensor, what: str = "", scale: float = 1.0) -> dict:
+def assert_close_hidden(got: torch.Tensor, ref: torch.Tensor, what: str = "", scale: float = 1.0,
+                        max_abs: float = MAX_ABS) -> dict:
     g, r = got.detach().float().cpu(), ref.detach().float().cpu()
     assert g.shape == r.shape, f"{what}: shape {tuple(g.shape)} vs {tuple(r.shape)}"
     assert torch.isfinite(g).all(), f"{what}: non-finite output"
     err = (g - r).abs()
-    bound = MAX_ABS * max(1.0, float(scale)) + r.abs() * 2.0**-7
+    bound = max_abs * max(1.0, float(scale)) + r.abs() * 2.0**-7
     cos = F.cosine_similarity(g.reshape(-1), r.reshape(-1), dim=0).item()
     worst = (err - bound).max().item()
     assert worst <= 0, f"{what}: max-abs {err.max().item():.4g} exceeds the bound by {worst:.4g} (cos {cos:.6f})"
