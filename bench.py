@@ -335,6 +335,11 @@ class LayerWorkload:
     def e2e_bytes(self):
         return self.h_host.numel() * 2, self.out_host.numel() * 2
 
+    def check(self):
+        rc, words = self.ops.guard_read(self.op.guard)
+        if rc != 0:
+            raise RuntimeError(f"guard words after the timed steps: {words}")
+
     def layer_bytes(self):
         c, u = self.cfg, int(self.op.ffn.n_expert.item())
         hl, il, h = c.heads_local, c.inter_local, c.hidden
@@ -383,7 +388,110 @@ class LayerWorkload:
         return min(ts) * 1e6 * self.rows, f"1 of {self.rows} rows of this rank's layer share, scaled by rows; best of 2"
 
 
-WORKLOADS = {"sparse_mla": SparseMlaWorkload, "moe": MoeWorkload, "layer": LayerWorkload}
+class AllReduceWorkload:
+    """The in-kernel tensor-parallel all-reduce alone (rows x 7168 bf16 per rank, pushes over
+    IPC-mapped peer memory + rank-ordered sum + residual) next to an NCCL all-reduce of the
+    same message, both replayed from CUDA graphs.  Needs --gpus >= 2."""
+
+    layers_per_step = 1
+    kernel = "reduce_kernel (push + rank-ordered sum)"
+
+    def __init__(self, rows=8, n=7168):
+        self.rows, self.n = rows, n
+
+    def setup(self, dev, rank, world):
+        import torch.distributed as dist
+        from sgl_amd_mono_b200 import ops
+        from sgl_amd_mono_b200.common.peer import PeerBuffer
+
+        if world < 2:
+            raise SystemExit("the allreduce workload needs --gpus >= 2")
+        self.world, self.name = world, f"allreduce_{self.rows}x{self.n}_bf16_tp{world}"
+        self.peer = PeerBuffer(self.n, rank, world, dist.new_group(backend="gloo"), dev)
+        self.ops, self.dist = ops, dist
+        g = torch.Generator().manual_seed(rank)
+        self.part = torch.zeros(1, 16, self.n, device=dev)
+        self.part[0, : self.rows] = torch.randn(self.rows, self.n, generator=g).to(dev)
+        self.res = torch.zeros(self.rows, self.n, dtype=torch.bfloat16, device=dev)
+        self.out = torch.zeros(16, self.n, dtype=torch.bfloat16, device=dev)
+        self.msg = self.part[0, : self.rows].bfloat16().contiguous()
+        self.launches_per_step = 2
+
+        def ours():
+            ops.reduce_rows(self.rows, self.n, self.part, 1, self.out, residual=self.res, peer=self.peer, site=0,
+                            guard=self.peer.guard, deadline_s=10.0)
+            ops.epoch_advance(self.peer.guard)
+
+        def nccl():
+            dist.all_reduce(self.msg)
+
+        self.g_ours, self.g_nccl = self._graph(ours), self._graph(nccl)
+        # correctness against NCCL's sum of the same bf16 partials (NCCL's order is unspecified: tolerance)
+        self.msg.copy_(self.part[0, : self.rows].bfloat16())
+        self.g_nccl.replay()
+        self.g_ours.replay()
+        torch.cuda.synchronize()
+        err = (self.out[: self.rows].float() - self.msg.float()).abs().max().item()
+        if not err <= 0.05 * max(1.0, self.msg.float().abs().max().item()):
+            raise RuntimeError(f"in-kernel all-reduce differs from NCCL by {err}")
+        rc, words = ops.guard_read(self.peer.guard)
+        if rc:
+            raise RuntimeError(f"guard words {words}")
+        self.nccl_us = self._time(self.g_nccl)
+
+    def check(self):
+        rc, words = self.ops.guard_read(self.peer.guard)
+        if rc != 0:
+            raise RuntimeError(f"guard words after the timed steps: {words}")
+
+    def _graph(self, fn):
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(3):
+                fn()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=s):
+                fn()
+        torch.cuda.current_stream().wait_stream(s)
+        return g
+
+    def _time(self, g, n=200):
+        self.dist.barrier()
+        for _ in range(20):
+            g.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) * 1000.0 / n
+
+    def step(self):
+        self.g_ours.replay()
+
+    def e2e_step(self):
+        self.step()
+        torch.cuda.synchronize()
+
+    def e2e_bytes(self):
+        return 0, 0
+
+    def roofline_probe(self):
+        return self.rows * self.n * 2 * (self.world - 1), self.step
+
+    def config(self):
+        return {"workload": self.name, "rows": self.rows, "n": self.n, "tp": self.world,
+                "nccl_allreduce_us": self.nccl_us, "in_kernel_allreduce_us_back_to_back": self._time(self.g_ours),
+                "nvlink_peak_gbs_per_direction": 900, "l2": "256 MiB buffer written between timed iterations"}
+
+    def cpu_sample(self):
+        return float("nan"), "not applicable"
+
+
+WORKLOADS = {"sparse_mla": SparseMlaWorkload, "moe": MoeWorkload, "layer": LayerWorkload, "allreduce": AllReduceWorkload}
 DEFAULT_WORKLOAD = "layer"
 
 
@@ -456,11 +564,18 @@ def main() -> None:
     barrier()
     sampler = ClockSampler(local)
     sampler.__enter__()
-    t_load = time.time()
-    while time.time() - t_load < 0.6:  # keep the GPU under load so the clock samples mean something
-        for _ in range(20):
-            wl.step()
-        torch.cuda.synchronize()
+    # keep the GPU under load for about 0.6 s so that the clock samples mean something; the
+    # number of steps is fixed by rank 0 (ranks that exchange data must run the same count)
+    t_probe = time.time()
+    for _ in range(20):
+        wl.step()
+    torch.cuda.synchronize()
+    n_load = torch.tensor([int(min(20000, max(20, 0.6 / max((time.time() - t_probe) / 20, 1e-6))))], device=dev)
+    if dist is not None:
+        dist.broadcast(n_load, src=0)
+    for _ in range(int(n_load.item())):
+        wl.step()
+    torch.cuda.synchronize()
     total_ms = time_steps(wl.step, args.steps, args.warmup, flush)
     barrier()
     t = torch.tensor([total_ms], device=dev)
@@ -486,6 +601,8 @@ def main() -> None:
     nbytes, probe = wl.roofline_probe()
     probe_ms = time_steps(probe, args.steps, 3, flush) / args.steps
     sampler.__exit__(None, None, None)
+    if hasattr(wl, "check"):
+        wl.check()  # the guard's error words must be clean after the timed steps
     peak, peak_src = measured_peaks()
     achieved = nbytes / (probe_ms * 1e-3) / 1e9
     line = {

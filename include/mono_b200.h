@@ -50,6 +50,11 @@ extern "C" {
 #define MONO_E_GUARD (-4)
 
 int mono_abi_version(void);
+/* Programmatic dependent launch between consecutive launches of one stream (on by
+ * default): each kernel lets its successor start early and waits for its predecessors
+ * before touching their data, so prologues and the first weight tiles overlap the
+ * previous kernel's tail.  Returns the previous setting. */
+int mono_set_pdl(int on);
 const char* mono_last_error(void);
 /* SM count of the current device (the grid every persistent launch is sized by;
  * reference: common/plan.py:23-25 BLOCKS = 256 CUs). */

@@ -133,6 +133,7 @@ _STRUCTS = [GemvJob, GemvArgs, ActPrepArgs, RouteArgs, MidArgs, SparseMlaArgs, R
 # every symbol include/mono_b200.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "mono_abi_version": (i32, []),
+    "mono_set_pdl": (i32, [i32]),
     "mono_last_error": (C.c_char_p, []),
     "mono_sm_count": (i32, []),
     "mono_guard_read": (i32, [vp, C.POINTER(C.c_int32 * 3), vp]),

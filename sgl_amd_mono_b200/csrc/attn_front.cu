@@ -49,6 +49,7 @@ __device__ __forceinline__ void fwht128(float* x, int t /* 0..127 */) {
 }
 
 __global__ void __launch_bounds__(kMidThreads2) mla_mid_kernel(const mono_mla_mid_args a) {
+    pdl_prologue();
     __shared__ __align__(16) float xq[2048 + 64];
     __shared__ __align__(16) float kv[kKvDim];
     __shared__ float ikv[128];
@@ -184,6 +185,7 @@ __global__ void __launch_bounds__(kMidThreads2) mla_mid_kernel(const mono_mla_mi
 constexpr int kQPostThreads = 128;
 
 __global__ void __launch_bounds__(kQPostThreads) q_post_kernel(const mono_q_post_args a) {
+    pdl_prologue();
     __shared__ float qn[kMaxRows][128];
     __shared__ float iq[128];
     const int tid = threadIdx.x;
@@ -285,7 +287,7 @@ extern "C" int mono_mla_mid_launch(const mono_mla_mid_args* a, void* stream) {
         mono_set_error("mono_mla_mid_launch: an index key needs its norm weights and the index pages");
         return MONO_E_ARG;
     }
-    mono::mla_mid_kernel<<<a->rows, mono::kMidThreads2, 0, (cudaStream_t)stream>>>(*a);
+    mono::launch_k(mono::mla_mid_kernel, a->rows, mono::kMidThreads2, 0, (cudaStream_t)stream, *a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_mla_mid_launch: %s", cudaGetErrorString(e));
     return (int)e;
@@ -298,7 +300,7 @@ extern "C" int mono_q_post_launch(const mono_q_post_args* a, void* stream) {
         return MONO_E_ARG;
     }
     const int blocks = a->heads * 8 + (a->index_heads > 0 ? a->rows * a->index_heads : 0);
-    mono::q_post_kernel<<<blocks, mono::kQPostThreads, 0, (cudaStream_t)stream>>>(*a);
+    mono::launch_k(mono::q_post_kernel, blocks, mono::kQPostThreads, 0, (cudaStream_t)stream, *a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_q_post_launch: %s", cudaGetErrorString(e));
     return (int)e;

@@ -15,6 +15,13 @@ void mono_set_error(const char* fmt, ...) {
     va_end(ap);
 }
 
+int g_mono_pdl = 1;
+extern "C" int mono_set_pdl(int on) {
+    const int old = g_mono_pdl;
+    g_mono_pdl = on ? 1 : 0;
+    return old;
+}
+
 extern "C" int mono_abi_version(void) { return MONO_ABI_VERSION; }
 extern "C" const char* mono_last_error(void) { return g_err; }
 

@@ -118,6 +118,29 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const __grid_cons
     }
     __syncthreads();
 
+    // Let the next launch start its prologue, and request the first weight tiles of this
+    // CTA's first task before waiting for the previous launch: weights do not depend on
+    // anything upstream, so they stream while the predecessor is still finishing.
+    pdl_launch_dependents();
+    int pre = 0;
+    if (warp == kConsumerWarps) {
+        const mono_gemv_job& j0 = p.a.job[0];
+        if (lane == 0 && j0.mode == MONO_JOB_DENSE) {
+            const int nrb0 = j0.rb_per_mat > 0 ? j0.n_mats * j0.rb_per_mat : job_nrb(j0);
+            if ((int)blockIdx.x < nrb0 * j0.nsplit) {
+                const Seg s0 = make_seg<WK>(j0, blockIdx.x % nrb0, blockIdx.x / nrb0, 0, 0, p.bb);
+                pre = min(s0.nt, p.a_stages);
+                for (int t = 0; t < pre; ++t) {
+                    mbar_expect_tx(&full[t], kTileBytes);
+                    tma_load_3d(a_ring + (size_t)t * kTileBytes, reinterpret_cast<const CUtensorMap*>(&j0.tmap),
+                                (s0.t0 + t) * 128, s0.row0, s0.c2, &full[t]);
+                }
+            }
+        }
+        pre = __shfl_sync(0xffffffffu, pre, 0);
+    }
+    pdl_wait();
+
     // task counts (identical in every thread)
     int cnt[MONO_GEMV_MAX_JOBS];
     int nexp[MONO_GEMV_MAX_JOBS];
@@ -196,6 +219,11 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const __grid_cons
                 // weight tiles
                 if (lane == 0) {
                     for (int t = 0; t < s.nt; ++t) {
+                        if (pre > 0) {  // requested before the dependency wait (first task of this CTA)
+                            --pre;
+                            if (++astage == p.a_stages) { astage = 0; aphase ^= 1; }
+                            continue;
+                        }
                         if (!mbar_wait(&empty[astage], aphase ^ 1, abortp)) break;
                         mbar_expect_tx(&full[astage], kTileBytes);
                         tma_load_3d(a_ring + (size_t)astage * kTileBytes, reinterpret_cast<const CUtensorMap*>(&jb.tmap),
@@ -416,8 +444,8 @@ int launch_gemv(const mono::GemvParams& p, int grid, size_t smem, cudaStream_t s
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }
-    k<<<grid, mono::kGemvThreads, smem, st>>>(p);
-    return (int)cudaGetLastError();
+    cudaError_t e = mono::launch_k(k, grid, mono::kGemvThreads, smem, st, p);
+    return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
 }  // namespace
 

@@ -23,6 +23,7 @@ struct ScoreSmem {
 };
 
 __global__ void __launch_bounds__(kScoreThreads) index_score_kernel(const mono_index_args a, int max_tiles) {
+    pdl_prologue();
     extern __shared__ uint8_t smem_raw[];
     ScoreSmem& sm = *reinterpret_cast<ScoreSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -138,6 +139,7 @@ __device__ __forceinline__ uint32_t score_key(float f) {
 }
 
 __global__ void __launch_bounds__(kTopkThreads) index_topk_kernel(const mono_index_args a, int smem_keys) {
+    pdl_prologue();
     extern __shared__ uint32_t skeys[];  // the row's radix keys when they fit (smem_keys != 0)
     __shared__ int hist[256];
     __shared__ uint32_t s_prefix;
@@ -171,9 +173,31 @@ __global__ void __launch_bounds__(kTopkThreads) index_topk_kernel(const mono_ind
         const uint32_t prefix = s_prefix;
         const int krem = s_krem;
         const int shift = pass * 8;
+        // scores of one row share their leading bytes, so most keys of a pass fall into a
+        // few bins: lanes that hit the same bin are counted by one atomic (match + popc)
+        // (a thread counts runs of equal bins itself and adds each run with one atomic)
+        int cur = -1, run = 0;
         for (int i = tid; i < n; i += kTopkThreads) {
             const uint32_t k = smem_keys ? skeys[i] : score_key(sc[i]);
-            if (pass == 3 || (k >> (shift + 8)) == prefix) atomicAdd(&hist[(k >> shift) & 0xFF], 1);
+            if (pass == 3 || (k >> (shift + 8)) == prefix) {
+                const int bin = (int)((k >> shift) & 0xFF);
+                if (bin == cur) {
+                    ++run;
+                } else {
+                    if (run) atomicAdd(&hist[cur], run);
+                    cur = bin;
+                    run = 1;
+                }
+            }
+        }
+        {
+            const int c0 = __shfl_sync(0xffffffffu, cur, 0);
+            if (__all_sync(0xffffffffu, cur == c0 && run > 0)) {  // the whole warp ends in one bin
+                const int tot = __reduce_add_sync(0xffffffffu, run);
+                if (lane == 0) atomicAdd(&hist[c0], tot);
+            } else if (run) {
+                atomicAdd(&hist[cur], run);
+            }
         }
         __syncthreads();
         if (tid < 256) {
@@ -248,7 +272,7 @@ extern "C" int mono_index_score_launch(const mono_index_args* a, void* stream) {
     int grid = a->rows * max_tiles;
     const int sms = mono_sm_count();
     if (grid > 4 * sms) grid = 4 * sms;
-    mono::index_score_kernel<<<grid, mono::kScoreThreads, smem, (cudaStream_t)stream>>>(*a, max_tiles);
+    mono::launch_k(mono::index_score_kernel, grid, mono::kScoreThreads, smem, (cudaStream_t)stream, *a, max_tiles);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_index_score_launch: %s", cudaGetErrorString(e));
     return (int)e;
@@ -268,7 +292,7 @@ extern "C" int mono_index_topk_launch(const mono_index_args* a, void* stream) {
         cudaFuncSetAttribute(mono::index_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 192 * 1024);
         attr_set = true;
     }
-    mono::index_topk_kernel<<<a->rows, mono::kTopkThreads, smem_keys ? key_bytes : 0, (cudaStream_t)stream>>>(*a, smem_keys);
+    mono::launch_k(mono::index_topk_kernel, a->rows, mono::kTopkThreads, smem_keys ? key_bytes : 0, (cudaStream_t)stream, *a, smem_keys);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_index_topk_launch: %s", cudaGetErrorString(e));
     return (int)e;

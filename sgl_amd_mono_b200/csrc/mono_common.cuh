@@ -226,6 +226,20 @@ __device__ __forceinline__ float e2m1_to_f32(uint32_t c) {
     return (c & 8) ? -m : m;
 }
 
+// ------------------------------------------------------------------ programmatic dependent launch
+// Every kernel lets its successor start early (prologue, and for the GEMV kernel the
+// first weight tiles, overlap this kernel's tail) and waits for its predecessors before
+// it touches anything they wrote or still read.  Without the launch attribute both
+// instructions do nothing.  This is how weight loads are issued ahead of upstream
+// results across launch boundaries (the reference does it inside one kernel: each task
+// issues its weight loads before it polls its inputs, glm53/gfx950/kernel.py:24-27,649-694).
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_prologue() {
+    pdl_launch_dependents();
+    pdl_wait();
+}
+
 // ld / st that bypass the non-coherent L1 (data produced by other SMs or other GPUs)
 __device__ __forceinline__ float ld_cg_f32(const float* p) {
     float v;
@@ -233,4 +247,23 @@ __device__ __forceinline__ float ld_cg_f32(const float* p) {
     return v;
 }
 
+}  // namespace mono
+
+// Host side: one launch helper, with or without the programmatic-serialization attribute.
+extern int g_mono_pdl;
+namespace mono {
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = g_mono_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
 }  // namespace mono

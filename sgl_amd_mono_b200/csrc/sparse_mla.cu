@@ -49,7 +49,8 @@ __device__ __forceinline__ void e4m3x16_to_bf16(const uint4& v, float scale, __n
     *reinterpret_cast<uint4*>(dst + 8) = make_uint4(o[4], o[5], o[6], o[7]);
 }
 
-__global__ void __launch_bounds__(kMlaThreads, 1) sparse_mla_split_kernel(const mono_sparse_mla_args a, int nsplit) {
+__global__ void __launch_bounds__(kMlaThreads, 2) sparse_mla_split_kernel(const mono_sparse_mla_args a, int nsplit) {
+    pdl_prologue();
     extern __shared__ uint8_t smem_raw[];
     MlaSmem& sm = *reinterpret_cast<MlaSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -191,6 +192,7 @@ __global__ void __launch_bounds__(kMlaThreads, 1) sparse_mla_split_kernel(const 
 
 // One CTA per (row, head): merge the splits.
 __global__ void __launch_bounds__(256) sparse_mla_merge_kernel(const mono_sparse_mla_args a, int nsplit) {
+    pdl_prologue();
     __shared__ float w[128];
     const int row = blockIdx.x / a.heads, head = blockIdx.x - row * a.heads;
     const __nv_bfloat16* part_acc = reinterpret_cast<const __nv_bfloat16*>(a.scratch);
@@ -258,8 +260,8 @@ extern "C" int mono_sparse_mla_launch(const mono_sparse_mla_args* a, void* strea
     int grid = a->rows * nsplit;
     const int sms = mono_sm_count();
     if (grid > 2 * sms) grid = 2 * sms;
-    mono::sparse_mla_split_kernel<<<grid, mono::kMlaThreads, smem, (cudaStream_t)stream>>>(*a, nsplit);
-    mono::sparse_mla_merge_kernel<<<a->rows * a->heads, 256, 0, (cudaStream_t)stream>>>(*a, nsplit);
+    mono::launch_k(mono::sparse_mla_split_kernel, grid, mono::kMlaThreads, smem, (cudaStream_t)stream, *a, nsplit);
+    mono::launch_k(mono::sparse_mla_merge_kernel, a->rows * a->heads, 256, 0, (cudaStream_t)stream, *a, nsplit);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_sparse_mla_launch: %s", cudaGetErrorString(e));
     return (int)e;

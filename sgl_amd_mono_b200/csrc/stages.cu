@@ -73,6 +73,7 @@ __device__ __forceinline__ void quant_chunk128(const float* x /* smem, 128 value
 }
 
 __global__ void __launch_bounds__(kPrepThreads) act_prep_kernel(const mono_act_prep_args a) {
+    pdl_prologue();
     extern __shared__ float xrow[];
     __shared__ float red[kPrepThreads / 32];
     const int segs = a.segs > 1 ? a.segs : 1;
@@ -152,6 +153,7 @@ __device__ __forceinline__ uint32_t radix_key(float f) {
 }
 
 __global__ void __launch_bounds__(kRouteThreads) route_kernel(const mono_route_args a) {
+    pdl_prologue();
     __shared__ float sc[kMaxRows][kMaxExperts];
     __shared__ int used[kMaxExperts];
     __shared__ int sel[kMaxRows][16];
@@ -172,27 +174,36 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const mono_route_a
             if (a.scores) a.scores[(size_t)r * a.n_experts + e] = s;
         }
         __syncwarp();
+        // each lane keeps the keys of its experts (lane, lane + 32, ...) in registers; a pick is
+        // a warp-wide maximum of (monotone key, inverted id), so ties go to the lower expert id
+        unsigned long long keys[kMaxExperts / 32];
+#pragma unroll
+        for (int i = 0; i < kMaxExperts / 32; ++i) {
+            const int e = lane + 32 * i;
+            keys[i] = 0ull;
+            if (e < a.n_experts) {
+                const float key = a.bias ? sc[r][e] + a.bias[e] : sc[r][e];
+                keys[i] = ((unsigned long long)radix_key(key) << 32) | (uint32_t)(0x7FFFFFFF - e);
+            }
+        }
         float wsum = 0.f;
         for (int k = 0; k < a.top_k; ++k) {
             unsigned long long best = 0ull;
-            for (int e = lane; e < a.n_experts; e += 32) {
-                bool taken = false;
-                for (int q = 0; q < k; ++q) taken |= (sel[r][q] == e);
-                if (taken) continue;
-                const float key = a.bias ? sc[r][e] + a.bias[e] : sc[r][e];
-                const unsigned long long kk = ((unsigned long long)radix_key(key) << 32) | (uint32_t)(0x7FFFFFFF - e);
-                best = kk > best ? kk : best;
-            }
+#pragma unroll
+            for (int i = 0; i < kMaxExperts / 32; ++i) best = keys[i] > best ? keys[i] : best;
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) {
                 const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
                 best = other > best ? other : best;
             }
             const int e = 0x7FFFFFFF - (int)(uint32_t)(best & 0xFFFFFFFFull);
+#pragma unroll
+            for (int i = 0; i < kMaxExperts / 32; ++i)
+                if (keys[i] == best) keys[i] = 0ull;  // only the owner lane holds it
             if (lane == 0) { sel[r][k] = e; selw[r][k] = sc[r][e]; }
             wsum += sc[r][e];
-            __syncwarp();
         }
+        __syncwarp();
         const float norm = a.route_scale / fmaxf(wsum, 1e-20f);
         if (lane < a.top_k) {
             const int e = live ? sel[r][lane] : -1;
@@ -236,6 +247,7 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const mono_route_a
 constexpr int kRowdotThreads = 256;
 
 __global__ void __launch_bounds__(kRowdotThreads) rowdot_kernel(const mono_rowdot_args a) {
+    pdl_prologue();
     // one CTA per output column; the 256 threads split K (4 values per thread per 1024),
     // so every weight load of the column is in flight at once
     __shared__ float red[kRowdotThreads / 32][kMaxRows];
@@ -299,6 +311,7 @@ __global__ void __launch_bounds__(kRowdotThreads) rowdot_kernel(const mono_rowdo
 constexpr int kMidThreads = 256;
 
 __global__ void __launch_bounds__(kMidThreads) mid_kernel(const mono_mid_args a) {
+    pdl_prologue();
     __shared__ float chunk[kMidThreads / 32][128];
     const int slot = blockIdx.x / a.rows, row = blockIdx.x - slot * a.rows;
     const int nslot = a.n_slot ? min(*a.n_slot, a.max_slot) : a.max_slot;
@@ -351,6 +364,7 @@ __device__ __forceinline__ void st_sys_u32(uint64_t addr, uint32_t a) {
 }
 
 __global__ void __launch_bounds__(kReduceThreads) reduce_kernel(const mono_reduce_args a) {
+    pdl_prologue();
     const int pairs = a.n / 2;
     const int total = a.rows * pairs;
     uint32_t tag = a.tag;
@@ -426,7 +440,10 @@ __global__ void __launch_bounds__(kReduceThreads) reduce_kernel(const mono_reduc
     }
 }
 
-__global__ void epoch_advance_kernel(int32_t* guard) { guard[MONO_GUARD_EPOCH] += 1; }
+__global__ void epoch_advance_kernel(int32_t* guard) {
+    pdl_prologue();
+    guard[MONO_GUARD_EPOCH] += 1;
+}
 
 }  // namespace mono
 
@@ -452,7 +469,7 @@ extern "C" int mono_act_prep_launch(const mono_act_prep_args* a, void* stream) {
         cudaFuncSetAttribute(mono::act_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * (int)sizeof(float));
         attr_set = true;
     }
-    mono::act_prep_kernel<<<a->rows * (a->segs > 1 ? a->segs : 1), mono::kPrepThreads, a->k * sizeof(float), (cudaStream_t)stream>>>(*a);
+    mono::launch_k(mono::act_prep_kernel, a->rows * (a->segs > 1 ? a->segs : 1), mono::kPrepThreads, a->k * sizeof(float), (cudaStream_t)stream, *a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_act_prep_launch: %s", cudaGetErrorString(e));
     return (int)e;
@@ -465,7 +482,7 @@ extern "C" int mono_route_launch(const mono_route_args* a, void* stream) {
         mono_set_error("mono_route_launch: rows 1..16, experts 1..512, top_k 1..16 and output pointers required");
         return MONO_E_ARG;
     }
-    mono::route_kernel<<<1, mono::kRouteThreads, 0, (cudaStream_t)stream>>>(*a);
+    mono::launch_k(mono::route_kernel, 1, mono::kRouteThreads, 0, (cudaStream_t)stream, *a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_route_launch: %s", cudaGetErrorString(e));
     return (int)e;
@@ -476,7 +493,7 @@ extern "C" int mono_rowdot_launch(const mono_rowdot_args* a, void* stream) {
         mono_set_error("mono_rowdot_launch: rows 1..16, k a multiple of 128 and all pointers required");
         return MONO_E_ARG;
     }
-    mono::rowdot_kernel<<<a->n, mono::kRowdotThreads, 0, (cudaStream_t)stream>>>(*a);
+    mono::launch_k(mono::rowdot_kernel, a->n, mono::kRowdotThreads, 0, (cudaStream_t)stream, *a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_rowdot_launch: %s", cudaGetErrorString(e));
     return (int)e;
@@ -492,7 +509,7 @@ extern "C" int mono_mid_launch(const mono_mid_args* a, void* stream) {
         mono_set_error("mono_mid_launch: format %d not supported or missing scales", a->fmt);
         return MONO_E_ARG;
     }
-    mono::mid_kernel<<<a->max_slot * a->rows, mono::kMidThreads, 0, (cudaStream_t)stream>>>(*a);
+    mono::launch_k(mono::mid_kernel, a->max_slot * a->rows, mono::kMidThreads, 0, (cudaStream_t)stream, *a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_mid_launch: %s", cudaGetErrorString(e));
     return (int)e;
@@ -518,7 +535,7 @@ extern "C" int mono_reduce_launch(const mono_reduce_args* a, void* stream) {
     int grid = (total + mono::kReduceThreads - 1) / mono::kReduceThreads;
     const int sms = mono_sm_count();
     if (grid > 2 * sms) grid = 2 * sms;
-    mono::reduce_kernel<<<grid, mono::kReduceThreads, 0, (cudaStream_t)stream>>>(*a);
+    mono::launch_k(mono::reduce_kernel, grid, mono::kReduceThreads, 0, (cudaStream_t)stream, *a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_reduce_launch: %s", cudaGetErrorString(e));
     return (int)e;
@@ -526,6 +543,6 @@ extern "C" int mono_reduce_launch(const mono_reduce_args* a, void* stream) {
 
 extern "C" int mono_epoch_advance_launch(int32_t* guard, void* stream) {
     if (!guard) return MONO_E_ARG;
-    mono::epoch_advance_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(guard);
+    mono::launch_k(mono::epoch_advance_kernel, 1, 1, 0, (cudaStream_t)stream, guard);
     return (int)cudaGetLastError();
 }

@@ -51,14 +51,9 @@ class MoeFfn:
         self.has_shared = sfmt != "none"
         same = self.has_shared and sfmt == efmt
         # ---- up / gate launch
+        # the shared expert's dense job goes first: its weight tiles do not depend on the router,
+        # so the launch can request them before the routing of this step is known
         self.up = ops.Gemv(_WK[efmt], self.guard)
-        probe = ops.plan_split(_ktiles(w["w13"]), -(-2 * il // 128) * self.max_expert, _WK[efmt])
-        self.ns_up = probe[1]
-        self.up_r = z(self.max_expert * self.ns_up, L.MAX_ROWS, 2 * il)
-        got = self.up.add("w13", w["w13"], self.xq, self.up_r, mode=L.JOB_EXPERT_UP, wscale=w["w13_s"],
-                          expert_list=self.expert_list, n_expert=self.n_expert, max_expert=self.max_expert,
-                          split_tiles=probe[0], nsplit=probe[1])
-        assert got == self.ns_up
         self.up_sh = self.mid_s = self.up_s = None
         if self.has_shared:
             self.xs = self.xq if same else ops.ActBuf(_ACT[sfmt], h, device)
@@ -69,24 +64,38 @@ class MoeFfn:
             g = self.up if same else ops.Gemv(_WK[sfmt], self.guard)
             g.add("sh13", w["sh13"], self.xs, self.up_s, wscale=w.get("sh13_s"), split_tiles=st, nsplit=ns)
             self.up_sh = None if same else g
+        probe = ops.plan_split(_ktiles(w["w13"]), -(-2 * il // 128) * self.max_expert, _WK[efmt])
+        self.ns_up = probe[1]
+        self.up_r = z(self.max_expert * self.ns_up, L.MAX_ROWS, 2 * il)
+        got = self.up.add("w13", w["w13"], self.xq, self.up_r, mode=L.JOB_EXPERT_UP, wscale=w["w13_s"],
+                          expert_list=self.expert_list, n_expert=self.n_expert, max_expert=self.max_expert,
+                          split_tiles=probe[0], nsplit=probe[1])
+        assert got == self.ns_up
         # ---- down launch: routed expert groups, then the shared expert's K splits
         nrb = -(-h // 128)
-        self.groups = max(1, min(self.max_expert, -(-2 * 148 // nrb)))
+        # expert groups: row blocks x groups tasks should fill whole rounds of the 148 CTAs
+        best = (0.0, 1)
+        for g in range(1, min(self.max_expert, 16) + 1):
+            tasks = nrb * g
+            eff = (tasks / 148) / -(-tasks // 148)
+            if tasks >= 148 and eff > best[0] + 1e-9:
+                best = (eff, g)
+        self.groups = best[1] if best[0] > 0 else max(1, min(self.max_expert, -(-148 // nrb)))
         ns_dn_s = 0
         if self.has_shared:
             self.st_dn_s, ns_dn_s = ops.plan_split(_ktiles(w["sh2"]), nrb, _WK[sfmt])
         self.n_slices = self.groups + ns_dn_s
         self.down_p = z(self.n_slices, L.MAX_ROWS, h)
         self.down = ops.Gemv(_WK[efmt], self.guard)
-        self.down.add("w2", w["w2"], self.mid_r, self.down_p, mode=L.JOB_EXPERT_DOWN, wscale=w["w2_s"],
-                      expert_list=self.expert_list, n_expert=self.n_expert, max_expert=self.max_expert,
-                      coef=self.coef, nsplit=self.groups)
         self.down_sh = None
         if self.has_shared:
             g = self.down if same else ops.Gemv(_WK[sfmt], self.guard)
             g.add("sh2", w["sh2"], self.mid_s, self.down_p, wscale=w.get("sh2_s"), out_slice=self.groups,
                   split_tiles=self.st_dn_s, nsplit=ns_dn_s)
             self.down_sh = None if same else g
+        self.down.add("w2", w["w2"], self.mid_r, self.down_p, mode=L.JOB_EXPERT_DOWN, wscale=w["w2_s"],
+                      expert_list=self.expert_list, n_expert=self.n_expert, max_expert=self.max_expert,
+                      coef=self.coef, nsplit=self.groups)
         self.out = z(L.MAX_ROWS, h, dt=torch.bfloat16)
 
     def __call__(self, residual: torch.Tensor, slots: torch.Tensor | None = None) -> torch.Tensor:
