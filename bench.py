@@ -200,8 +200,9 @@ class MoeWorkload:
         from sgl_amd_mono_b200.moe import MoeFfn
         from dataclasses import replace
 
-        self.cfg = replace(CFG_V3, n_heads=0, index_heads=0).with_tp(world)
-        self.name = f"cfg3_moe_half_tp{world}_{self.rows}rows"
+        tp = getattr(self, "shard_of", 0) or world  # --shard-of N: one rank's share of TP = N, no peers
+        self.cfg = replace(CFG_V3, n_heads=0, index_heads=0).with_tp(tp)
+        self.name = f"cfg3_moe_half_tp{tp}_{self.rows}rows" + ("_one_shard" if tp != world else "")
         self.w = synth.layer_weights(self.cfg, rank, dev)
         self.ffn = MoeFfn(self.cfg, self.w, dev, peer=peer)
         g = torch.Generator().manual_seed(0)
@@ -276,8 +277,9 @@ class LayerWorkload:
         from sgl_amd_mono_b200.config import CFG_V3
         from sgl_amd_mono_b200.layer import MlaLayerOp, StepTables
 
-        self.cfg = cfg = CFG_V3.with_tp(world)
-        self.name = f"cfg3_v3_mla_dsa_moe_layer_tp{world}_{self.rows}rows_ctx{self.ctx}"
+        tp = getattr(self, "shard_of", 0) or world  # --shard-of N: one rank's share of TP = N, no peers
+        self.cfg = cfg = CFG_V3.with_tp(tp)
+        self.name = f"cfg3_v3_mla_dsa_moe_layer_tp{tp}_{self.rows}rows_ctx{self.ctx}" + ("_one_shard" if tp != world else "")
         self.peer = None
         if world > 1:
             import torch.distributed as dist
@@ -491,7 +493,163 @@ class AllReduceWorkload:
         return float("nan"), "not applicable"
 
 
-WORKLOADS = {"sparse_mla": SparseMlaWorkload, "moe": MoeWorkload, "layer": LayerWorkload, "allreduce": AllReduceWorkload}
+class StackWorkload:
+    """BASELINE config 5: a 40-layer flash-sized MLA + MoE stack (hidden 4096, 64 heads, kv_lora
+    512 + rope 64, 256 experts top-6 + shared, intermediate 1024, FP8 128x128), context 8192,
+    bf16 LM head over vocab 129280, one decode step under one CUDA graph.  The step carries
+    ``rows`` decode rows plus a 5-token verify of one more request (rows + 5 rows through the
+    40 layers) and a single-layer draft stage on the 5 verify rows.  q_lora 1536, nope 128 and
+    v 128 are this build's choice (BASELINE leaves them open); there is no indexer, so every
+    cached key is attended."""
+
+    kernel = "gemv_kernel<FP8> (expert up/gate, layer 0)"
+
+    def __init__(self, rows=1, ctx=8192, layers=40, verify=5):
+        self.rows, self.ctx, self.n_layers, self.verify = rows, ctx, layers, verify
+        self.layers_per_step = layers
+
+    def setup(self, dev, rank, world):
+        from sgl_amd_mono_b200 import ops, synth
+        from sgl_amd_mono_b200.config import CFG_FLASH
+        from sgl_amd_mono_b200.layer import StepTables
+        from sgl_amd_mono_b200.stack import DecoderStack
+        from dataclasses import replace as dc_replace
+
+        tp = getattr(self, "shard_of", 0) or world
+        self.n_layers = int(os.environ.get("MONO_BENCH_LAYERS", self.n_layers))
+        self.layers_per_step = self.n_layers
+        self.cfg = cfg = CFG_FLASH.with_tp(tp)
+        self.total = self.rows + self.verify
+        self.name = (f"cfg5_flash_stack_{self.n_layers}layers_tp{tp}_{self.rows}rows_plus_{self.verify}verify_ctx{self.ctx}"
+                     + ("_one_shard" if tp != world else ""))
+        self.peer = None
+        if world > 1 and tp == world:
+            import torch.distributed as dist
+            from sgl_amd_mono_b200.common.peer import PeerBuffer
+
+            self.peer = PeerBuffer(cfg.hidden, rank, world, dist.new_group(backend="gloo"), dev)
+        ws = []
+        for i in range(self.n_layers):
+            c = cfg if i == self.n_layers - 1 else dc_replace(cfg, vocab=0)
+            ws.append(synth.layer_weights(c, rank, dev, layer=i))
+        draft_w = synth.layer_weights(dc_replace(cfg, vocab=0), rank, dev, layer=999)
+        self.w0 = ws[0]
+        # rows decode requests + one request verified with `verify` tokens: every row has its own
+        # page-table row (the verify rows repeat theirs); one cache per layer
+        def tables(layer):
+            d = synth.decode_step(cfg, self.rows + 1, self.ctx, device=dev, layer=layer)
+            req = torch.tensor(list(range(self.rows)) + [self.rows] * self.verify, device=dev)
+            pos = torch.cat([d.positions[: self.rows], self.ctx - self.verify + torch.arange(self.verify, device=dev)])
+            pt = d.page_table[req].contiguous()
+            slots = pt.gather(1, (pos // 64).unsqueeze(1)).squeeze(1).long() * 64 + pos % 64
+            return StepTables(pos, slots, pt, d.kv_pages, None, d.cos, d.sin)
+
+        self.tables = [tables(i) for i in range(self.n_layers)]
+        dt = tables(999)
+        self.draft_tables = StepTables(dt.positions[self.rows:].contiguous(), dt.slots[self.rows:].contiguous(),
+                                       dt.page_table[self.rows:].contiguous(), dt.kv_pages, None, dt.cos, dt.sin)
+        self.stack = DecoderStack(cfg, ws, dev, max_ctx=self.ctx, peer=self.peer, draft_weights=draft_w)
+        self.ops = ops
+        g = torch.Generator().manual_seed(0)
+        self.h_host = torch.randn(self.total, cfg.hidden, generator=g).bfloat16().pin_memory()
+        self.h = self.h_host.to(dev)
+        self.hd = self.h[self.rows:].contiguous()
+        self._eager()
+        torch.cuda.synchronize()
+        self.check()
+        self.launches_per_step = self.stack.launches_per_step
+        self.logits_host = torch.empty(self.total, cfg.vocab // tp, dtype=torch.float32).pin_memory()
+        self.graph = None
+        if os.environ.get("MONO_BENCH_GRAPH", "1") == "1":
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._eager()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=s):
+                    self._eager()
+            torch.cuda.current_stream().wait_stream(s)
+            self.graph = g
+
+    def _eager(self):
+        st = self.stack
+        st.draft.launch(self.hd, self.draft_tables)
+        x = self.h
+        for op, t in zip(st.layers, self.tables):
+            x = op.launch(x, t)
+        self.logits = st.head(x)
+        self.ops.epoch_advance(st.guard)
+
+    def step(self):
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self._eager()
+
+    def e2e_step(self):
+        self.h.copy_(self.h_host, non_blocking=True)
+        self.step()
+        self.logits_host.copy_(self.logits, non_blocking=True)
+        torch.cuda.synchronize()
+
+    def e2e_bytes(self):
+        return self.h_host.numel() * 2, self.logits_host.numel() * 4
+
+    def check(self):
+        rc, words = self.ops.guard_read(self.stack.guard)
+        if rc != 0:
+            raise RuntimeError(f"guard words: {words}")
+
+    def layer_bytes(self):
+        c = self.cfg
+        hl, il, h = c.heads_local, c.inter_local, c.hidden
+        fixed = (c.q_lora + 576) * h + c.n_experts * h * 2 + hl * 192 * c.q_lora + hl * 256 * 512 + h * hl * 128
+        total, us = 0, []
+        for op in self.stack.layers:
+            u = int(op.ffn.n_expert.item())
+            us.append(u)
+            total += fixed + (1 + u) * 3 * il * h + self.total * self.ctx * 580
+        total += (c.vocab // c.tp) * h * 2
+        return total, round(sum(us) / len(us), 1)
+
+    def roofline_probe(self):
+        op = self.stack.layers[0]
+        u = int(op.ffn.n_expert.item())
+        return (u + 1) * 2 * self.cfg.inter_local * self.cfg.hidden, lambda: op.ffn.up.launch(self.total)
+
+    def config(self):
+        c = self.cfg
+        nbytes, u = self.layer_bytes()
+        return {"workload": self.name, "decode_rows": self.rows, "verify_rows": self.verify, "draft_layers": 1,
+                "layers": self.n_layers, "context": self.ctx, "hidden": c.hidden, "heads": c.n_heads, "experts": c.n_experts,
+                "top_k": c.top_k, "inter": c.inter, "vocab": c.vocab, "tp": c.tp, "mean_distinct_experts": u,
+                "step_algorithmic_bytes_per_rank": nbytes, "cuda_graph": self.graph is not None,
+                "l2": "256 MiB buffer written between timed iterations"}
+
+    def cpu_sample(self):
+        from oracle import layers as OL
+
+        class Lazy:
+            def __init__(self, v):
+                self.v, self.c = v, {}
+
+            def __getitem__(self, e):
+                if e not in self.c:
+                    self.c[e] = self.v[e].cpu()
+                return self.c[e]
+
+        w = {k: (Lazy(v) if k in ("w13", "w13_s", "w2", "w2_s") else v.cpu()) for k, v in self.w0.items()}
+        t = self.tables[0]
+        args = (self.cfg, [w], self.h_host[:1], t.positions[:1].cpu(), t.slots[:1].cpu(), t.page_table[:1].cpu(),
+                t.cos.cpu(), t.sin.cpu())
+        kv = t.kv_pages.cpu()
+        t0 = time.perf_counter()
+        OL.layer_all_ranks(*args, kv.clone(), None)
+        dt = time.perf_counter() - t0
+        return dt * 1e6 * self.total, f"layer 0, 1 of {self.total} rows, scaled by rows (per layer); one run"
+
+
+WORKLOADS = {"stack": StackWorkload, "sparse_mla": SparseMlaWorkload, "moe": MoeWorkload, "layer": LayerWorkload, "allreduce": AllReduceWorkload}
 DEFAULT_WORKLOAD = "layer"
 
 
@@ -532,6 +690,8 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=os.environ.get("MONO_BENCH_WORKLOAD", DEFAULT_WORKLOAD), choices=sorted(WORKLOADS))
     ap.add_argument("--rows", type=int, default=8)
+    ap.add_argument("--load-seconds", type=float, default=0.6, help="time under load before the timed steps")
+    ap.add_argument("--shard-of", type=int, default=0, help="run one rank's share of TP = N on each GPU without peers")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -553,6 +713,7 @@ def main() -> None:
         dist = dist_mod
         dist.init_process_group("nccl", device_id=torch.device(dev))
     wl = wl_cls(rows=args.rows)
+    wl.shard_of = args.shard_of
     wl.setup(dev, rank, world)
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
 
@@ -570,7 +731,7 @@ def main() -> None:
     for _ in range(20):
         wl.step()
     torch.cuda.synchronize()
-    n_load = torch.tensor([int(min(20000, max(20, 0.6 / max((time.time() - t_probe) / 20, 1e-6))))], device=dev)
+    n_load = torch.tensor([int(min(20000, max(0, args.load_seconds / max((time.time() - t_probe) / 20, 1e-6))))], device=dev)
     if dist is not None:
         dist.broadcast(n_load, src=0)
     for _ in range(int(n_load.item())):
@@ -616,6 +777,9 @@ def main() -> None:
                      "frac": achieved / peak, "traffic": None, "algorithmic_bytes": nbytes,
                      "kernel_us": probe_ms * 1000.0, "peak_source": peak_src},
     }
+    if hasattr(wl, "n_layers"):
+        line["step_us"] = ms_per_step * 1000.0
+        line["tokens_per_s"] = wl.rows * world / (ms_per_step * 1e-3) if getattr(wl, "shard_of", 0) else wl.rows / (ms_per_step * 1e-3)
     if rank == 0:
         if not args.no_cpu_baseline:
             cores = os.cpu_count() or 1

@@ -73,7 +73,9 @@ def attn_front(cfg, w, h, positions, slots, cos, sin, kv_pages, idx_pages):
 def index_select(cfg, r, positions, slots, page_table, idx_pages):
     """Scores of every causal key and the exact top-k, as global KV slots [S, topk] (-1 pad)."""
     rows = positions.shape[0]
-    topk = torch.full((rows, cfg.index_topk), -1, dtype=torch.int32)
+    # without an indexer every causal key is attended
+    width = cfg.index_topk if cfg.index_heads else int(positions.max()) + 1
+    topk = torch.full((rows, width), -1, dtype=torch.int32)
     scores = []
     for s in range(rows):
         if slots[s] < 0:
@@ -87,7 +89,7 @@ def index_select(cfg, r, positions, slots, page_table, idx_pages):
             sel = S.exact_topk_positions(sc, n, cfg.index_topk)
             scores.append(sc)
         else:
-            sel = pos[: cfg.index_topk]
+            sel = pos
         topk[s, : sel.numel()] = ksl[sel].to(torch.int32)
     return topk, scores
 

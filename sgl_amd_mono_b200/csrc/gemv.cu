@@ -486,8 +486,8 @@ extern "C" int mono_gemv_launch(const mono_gemv_args* a, void* stream) {
             }
             seg_tiles = jb.split_tiles < jb.k_tiles ? jb.split_tiles : jb.k_tiles;
         }
-        if (seg_tiles > 32) {
-            mono_set_error("mono_gemv_launch: job %d: a segment may span at most 32 tiles, got %d", j, seg_tiles);
+        if (seg_tiles > (a->wkind == MONO_W_BF16 ? 64 : 32)) {  // FP8 keeps one weight scale per lane; bf16 has none
+            mono_set_error("mono_gemv_launch: job %d: a segment may span at most 32 tiles (64 for bf16), got %d", j, seg_tiles);
             return MONO_E_ARG;
         }
         if (jb.mode != MONO_JOB_DENSE && (!jb.expert_list || !jb.n_expert || jb.max_expert < 1)) {

@@ -93,10 +93,10 @@ _TILE_K = {L.W_FP8: 128, L.W_BF16: 64, L.W_MXFP4: 256}
 _MAX_SEG_TILES = {L.W_FP8: 16, L.W_BF16: 16, L.W_MXFP4: 8}
 
 
-def plan_split(k_tiles: int, row_blocks: int, wkind: int, sms: int = 148):
+def plan_split(k_tiles: int, row_blocks: int, wkind: int, sms: int = 148, cap: int | None = None):
     """(split_tiles, nsplit): K splits of whole 4-tile groups so that row_blocks x
     nsplit tasks cover the SMs about twice and a segment fits the activation slot."""
-    cap = _MAX_SEG_TILES[wkind]
+    cap = cap or _MAX_SEG_TILES[wkind]
     want = max(1, -(-2 * sms // max(row_blocks, 1)))
     split = min(cap, max(4, _up(-(-k_tiles // want), 4)))
     if split >= k_tiles:

@@ -174,3 +174,17 @@ def sparse_mla_inputs(rows: int, heads: int, ctx: int, topk: int, device="cpu", 
         pos = torch.randperm(ctx, generator=g, device=device)[: min(topk, ctx)]
         sel[r, : pos.numel()] = (page_table[r].long()[pos // PAGE] * PAGE + pos % PAGE).to(torch.int32)
     return q, kv_pages, sel, page_table
+
+
+def verify_step(cfg: LayerConfig, n_req: int, tokens: int, ctx: int, device="cpu", layer: int = 0) -> Step:
+    """A speculative-verify step: ``n_req`` requests x ``tokens`` rows.  Row j of a request sits
+    at position ctx - tokens + j and sees the keys up to itself; the rows of one request
+    repeat its page-table row (``minimax_m3/metadata.py:7-42``; ``glm53/spec.py:489-491``)."""
+    base = decode_step(cfg, n_req, ctx, device=device, layer=layer)
+    rows = n_req * tokens
+    req = torch.arange(rows, device=device) // tokens
+    j = torch.arange(rows, device=device) % tokens
+    positions = (ctx - tokens + j).to(torch.int64)
+    page_table = base.page_table[req].contiguous()
+    slots = page_table.gather(1, (positions // PAGE).unsqueeze(1)).squeeze(1).long() * PAGE + positions % PAGE
+    return Step(positions, slots, page_table, base.kv_pages, base.idx_pages, base.cos, base.sin)
