@@ -76,6 +76,10 @@ typedef struct __attribute__((aligned(64))) mono_tmap {
 } mono_tmap_t;
 int mono_tmap_encode(mono_tmap_t* out, const void* base, uint64_t inner_bytes, uint64_t rows,
                      uint64_t outer, uint64_t row_stride_bytes, uint64_t outer_stride_bytes);
+/* The same with boxes of 128 bytes x `box_rows` rows (16 for the activation planes that
+ * feed the tcgen05 B operand). */
+int mono_tmap_encode_box(mono_tmap_t* out, const void* base, uint64_t inner_bytes, uint64_t rows, uint64_t outer,
+                         uint64_t row_stride_bytes, uint64_t outer_stride_bytes, uint32_t box_rows);
 
 /* ---- activation staging (glm53/gfx950/kernel.py:1367-1414 RMSNorm staging,
  * :1440-1466 per-128 FP8 / per-32 MXFP8 quantisation) ----------------------------
@@ -132,6 +136,8 @@ enum { MONO_JOB_DENSE = 0, MONO_JOB_EXPERT_UP = 1, MONO_JOB_EXPERT_DOWN = 2 };
 
 typedef struct mono_gemv_job {
     mono_tmap_t tmap;
+    mono_tmap_t act_tmap; /* activation planes as [set * planes + plane][16 rows][act_ld bytes], boxes of
+                             128 B x 16 rows (tcgen05 path; mono_tmap_encode_box(..., 16)) */
     int mode;       /* MONO_JOB_* */
     int n_rows;     /* rows of W this job covers (per matrix) */
     int k_tiles;    /* K in 128-byte tiles (FP8: 128 k, BF16: 64 k, MXFP4: 256 k) */
@@ -178,6 +184,9 @@ typedef struct mono_gemv_args {
     mono_gemv_job job[MONO_GEMV_MAX_JOBS];
 } mono_gemv_args;
 int mono_gemv_launch(const mono_gemv_args* a, void* stream);
+/* FP8 jobs run on tcgen05 MMAs with TMEM accumulators (1, default) or on warp-level MMAs (0).
+ * MXFP4 and bf16 weights always take the warp-level consumers.  Returns the old setting. */
+int mono_set_gemv_tcgen05(int on);
 
 /* ---- small matrices on CUDA cores (router logits: minimax_m31/ffn.py:601-649 fp32
  * router; glm53/gfx950/kernel.py:4199-4330 bf16 router; indexer head weights) ------

@@ -9,6 +9,7 @@ import of a runner raises and the spec refuses to attach.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent / "libmono_b200.so"
@@ -30,7 +31,7 @@ class Tmap(C.Structure):
 
 class GemvJob(C.Structure):
     _fields_ = [
-        ("tmap", Tmap),
+        ("tmap", Tmap), ("act_tmap", Tmap),
         ("mode", i32), ("n_rows", i32), ("k_tiles", i32), ("split_tiles", i32), ("nsplit", i32),
         ("row_off", i32), ("rb_per_mat", i32), ("n_mats", i32),
         ("wscale_f32", vp), ("wscale_e8", vp), ("wscale_mat_stride", i64), ("wscale_ld", i32),
@@ -138,6 +139,8 @@ SYMBOLS = {
     "mono_sm_count": (i32, []),
     "mono_guard_read": (i32, [vp, C.POINTER(C.c_int32 * 3), vp]),
     "mono_tmap_encode": (i32, [C.POINTER(Tmap), vp, u64, u64, u64, u64, u64]),
+    "mono_tmap_encode_box": (i32, [C.POINTER(Tmap), vp, u64, u64, u64, u64, u64, u32]),
+    "mono_set_gemv_tcgen05": (i32, [i32]),
     "mono_act_prep_launch": (i32, [C.POINTER(ActPrepArgs), vp]),
     "mono_gemv_launch": (i32, [C.POINTER(GemvArgs), vp]),
     "mono_rowdot_launch": (i32, [C.POINTER(RowdotArgs), vp]),
@@ -190,6 +193,11 @@ def load():
         want = lib.mono_struct_size(i)
         if want != C.sizeof(st):
             raise MonoLibraryError(f"{st.__name__}: binding has {C.sizeof(st)} bytes, library has {want}")
+    # process-wide switches, for A/B measurements: MONO_GEMV_TCGEN05=0|1, MONO_PDL=0|1
+    if os.environ.get("MONO_GEMV_TCGEN05") in ("0", "1"):
+        lib.mono_set_gemv_tcgen05(int(os.environ["MONO_GEMV_TCGEN05"]))
+    if os.environ.get("MONO_PDL") in ("0", "1"):
+        lib.mono_set_pdl(int(os.environ["MONO_PDL"]))
     _lib = lib
     return lib
 

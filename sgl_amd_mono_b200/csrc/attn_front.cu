@@ -54,13 +54,15 @@ __global__ void __launch_bounds__(kMidThreads2) mla_mid_kernel(const mono_mla_mi
     __shared__ __align__(16) float kv[kKvDim];
     __shared__ float ikv[128];
     __shared__ float red[kMidThreads2 / 32];
-    const int row = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // grid = (rows, parts): part 0 = q_a, part 1 = latent | rope + cache write, part 2 = index key;
+    // the three are independent, so they run on three CTAs instead of one after the other
+    const int row = blockIdx.x, part = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int64_t pos = a.positions[row];
     const int64_t slot = a.slots ? a.slots[row] : 1;
     const float* src = a.qkv + (size_t)row * a.ld;
     // everything that does not depend on a reduction is fetched up front
     float ikraw = 0.f, rc = 0.f, rs = 0.f;
-    if (a.ik && tid < 128) {
+    if (a.ik && part == 2 && tid < 128) {
 #pragma unroll 4
         for (int s = 0; s < a.ik_nsum; ++s) ikraw += a.ik[(size_t)s * a.ik_sum_stride + (size_t)row * a.ik_ld + tid];
     }
@@ -72,7 +74,8 @@ __global__ void __launch_bounds__(kMidThreads2) mla_mid_kernel(const mono_mla_mi
     // the whole row (q_a | latent | rope) is summed over the K splits with 16-byte loads
     // issued together, so it costs one memory latency rather than one per element
     float ssq = 0.f, ssq_kv = 0.f;
-    for (int i = tid * 4; i < a.q_lora + kKvDim; i += kMidThreads2 * 4) {
+    const int i_lo = part == 0 ? 0 : a.q_lora, i_hi = part == 0 ? a.q_lora : (part == 1 ? a.q_lora + kKvDim : 0);
+    for (int i = i_lo + tid * 4; i < i_hi; i += kMidThreads2 * 4) {
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 4
         for (int s = 0; s < a.nsum; ++s) {
@@ -88,21 +91,22 @@ __global__ void __launch_bounds__(kMidThreads2) mla_mid_kernel(const mono_mla_mi
             if (i - a.q_lora < 512) ssq_kv += sq;
         }
     }
-    {
+    if (part == 0) {
         const float r = rsqrtf(block_sum<kMidThreads2 / 32>(ssq, red) / (float)a.q_lora + a.eps);
         const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(a.q_a_norm);
         for (int i = tid; i < a.q_lora; i += kMidThreads2) xq[i] = bf16_round(xq[i] * r * __bfloat162float(g[i]));
-    }
-    __syncthreads();
-    for (int c = warp; c < a.q_lora / 128; c += kMidThreads2 / 32) {
-        float v[4];
+        __syncthreads();
+        for (int c = warp; c < a.q_lora / 128; c += kMidThreads2 / 32) {
+            float v[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) v[i] = xq[c * 128 + 4 * lane + i];
-        uint8_t* hi = a.qa_planes + (size_t)row * a.qa_ld + c * 128;
-        hilo_chunk(v, lane, hi, hi + a.qa_plane_stride, a.qa_scale + (size_t)row * a.qa_scale_ld + c);
+            for (int i = 0; i < 4; ++i) v[i] = xq[c * 128 + 4 * lane + i];
+            uint8_t* hi = a.qa_planes + (size_t)row * a.qa_ld + c * 128;
+            hilo_chunk(v, lane, hi, hi + a.qa_plane_stride, a.qa_scale + (size_t)row * a.qa_scale_ld + c);
+        }
+        return;
     }
     // ---- latent: RMSNorm -> bf16; k_pe: interleaved RoPE -> bf16
-    {
+    if (part == 1) {
         const float r = rsqrtf(block_sum<kMidThreads2 / 32>(ssq_kv, red) / 512.f + a.eps);
         const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(a.kv_a_norm);
         float rot0 = 0.f, rot1 = 0.f;
@@ -118,6 +122,7 @@ __global__ void __launch_bounds__(kMidThreads2) mla_mid_kernel(const mono_mla_mi
             kv[512 + 2 * tid + 1] = bf16_round(rot1);
         }
     }
+    if (part == 1) {
     __syncthreads();
     float amax = 0.f;
     for (int i = tid; i < kKvDim; i += kMidThreads2) amax = fmaxf(amax, fabsf(kv[i]));
@@ -139,9 +144,10 @@ __global__ void __launch_bounds__(kMidThreads2) mla_mid_kernel(const mono_mla_mi
         }
         if (tid == 0) reinterpret_cast<float*>(page + kPage * kKvDim)[off] = exp2_code(code);
     }
+    return;
+    }
     // ---- index key: LayerNorm -> RoPE (dims 0..63) -> FWHT-128 -> E2M1 + E8M0 per 32
-    if (a.ik) {
-        __syncthreads();
+    if (a.ik && part == 2) {
         const float v = ikraw;
         const float mean = block_sum<kMidThreads2 / 32>(tid < 128 ? v : 0.f, red) / 128.f;
         const float dv = tid < 128 ? v - mean : 0.f;
@@ -287,7 +293,7 @@ extern "C" int mono_mla_mid_launch(const mono_mla_mid_args* a, void* stream) {
         mono_set_error("mono_mla_mid_launch: an index key needs its norm weights and the index pages");
         return MONO_E_ARG;
     }
-    mono::launch_k(mono::mla_mid_kernel, a->rows, mono::kMidThreads2, 0, (cudaStream_t)stream, *a);
+    mono::launch_k(mono::mla_mid_kernel, dim3(a->rows, a->ik ? 3 : 2), mono::kMidThreads2, 0, (cudaStream_t)stream, *a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_mla_mid_launch: %s", cudaGetErrorString(e));
     return (int)e;

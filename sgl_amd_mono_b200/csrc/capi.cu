@@ -78,11 +78,19 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
+extern "C" int mono_tmap_encode_box(mono_tmap_t* out, const void* base, uint64_t inner_bytes, uint64_t rows,
+                                    uint64_t outer, uint64_t row_stride_bytes, uint64_t outer_stride_bytes, uint32_t box_rows);
+
 extern "C" int mono_tmap_encode(mono_tmap_t* out, const void* base, uint64_t inner_bytes, uint64_t rows,
                                 uint64_t outer, uint64_t row_stride_bytes, uint64_t outer_stride_bytes) {
+    return mono_tmap_encode_box(out, base, inner_bytes, rows, outer, row_stride_bytes, outer_stride_bytes, 128);
+}
+
+extern "C" int mono_tmap_encode_box(mono_tmap_t* out, const void* base, uint64_t inner_bytes, uint64_t rows,
+                                    uint64_t outer, uint64_t row_stride_bytes, uint64_t outer_stride_bytes, uint32_t box_rows) {
     static_assert(sizeof(CUtensorMap) == sizeof(mono_tmap_t), "descriptor size");
-    if (!out || !base || inner_bytes == 0 || rows == 0 || outer == 0) {
-        mono_set_error("mono_tmap_encode: null or empty tensor");
+    if (!out || !base || inner_bytes == 0 || rows == 0 || outer == 0 || box_rows == 0 || box_rows > 256) {
+        mono_set_error("mono_tmap_encode: null or empty tensor, or box rows outside 1..256");
         return MONO_E_ARG;
     }
     if ((reinterpret_cast<uintptr_t>(base) & 15) || (row_stride_bytes & 15) || (outer_stride_bytes & 15) ||
@@ -98,7 +106,7 @@ extern "C" int mono_tmap_encode(mono_tmap_t* out, const void* base, uint64_t inn
     }
     cuuint64_t dims[3] = {inner_bytes, rows, outer};
     cuuint64_t strides[2] = {row_stride_bytes, outer > 1 ? outer_stride_bytes : row_stride_bytes * rows};
-    cuuint32_t box[3] = {128, 128, 1};
+    cuuint32_t box[3] = {128, box_rows, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = fn(reinterpret_cast<CUtensorMap*>(out), CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims,
                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,

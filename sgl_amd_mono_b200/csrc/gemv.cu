@@ -433,6 +433,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const __grid_cons
 
 // ------------------------------------------------------------------------ host
 extern void mono_set_error(const char* fmt, ...);
+int mono_gemv_tc_enabled();                                                      // gemv_tc.cu
+int mono_gemv_tc_launch(const mono_gemv_args* a, long tasks, cudaStream_t st);  // gemv_tc.cu
 
 namespace {
 template <int WK, int NT>
@@ -512,6 +514,21 @@ extern "C" int mono_gemv_launch(const mono_gemv_args* a, void* stream) {
             tasks += (long)jb.max_expert * nrb * jb.nsplit;
         else
             tasks += (long)nrb * jb.nsplit;
+    }
+    if (a->wkind == MONO_W_FP8 && mono_gemv_tc_enabled()) {
+        // tcgen05 path: needs the activation tensor map of every job (an all-zero map means "not given")
+        bool maps = true;
+        for (int j = 0; j < a->njobs; ++j) {
+            const unsigned long long* w = reinterpret_cast<const unsigned long long*>(&a->job[j].act_tmap);
+            unsigned long long any = 0;
+            for (int i = 0; i < 16; ++i) any |= w[i];
+            maps = maps && any != 0;
+        }
+        if (maps) {
+            int rc = mono_gemv_tc_launch(a, tasks, (cudaStream_t)stream);
+            if (rc > 0) mono_set_error("mono_gemv_launch: CUDA error %d (%s)", rc, cudaGetErrorString((cudaError_t)rc));
+            return rc;
+        }
     }
     // row pitch = 16 (32 for the 8-byte MXFP4 reads) mod 128: conflict-free fragment loads
     p.b_pitch = max_seg_tiles * p.bb + (a->wkind == MONO_W_MXFP4 ? 32 : 16);

@@ -1,0 +1,340 @@
+// Weight-streaming GEMV on 5th-generation tensor cores: tcgen05.mma (kind::f8f6f4) with the
+// accumulators in tensor memory, both operands fed by TMA.
+//
+// Same contract, task list and arithmetic as gemv.cu (reference: the MFMA GEMV units of
+// glm53/gfx950/kernel.py:1061-1172 and the block-scale rule of :35-42): the 128 weight rows of
+// a task are the MMA's M dimension, the step's rows (padded to 16) its N dimension; every 128-k
+// chunk is accumulated on its own in TMEM and multiplied by the 128x128 weight scale and the
+// per-row activation scale when the epilogue folds it into the task's f32 sum.
+//
+// Warp roles (192 threads): warp 0 issues the TMA loads of a stage (one 128 x 128-byte weight box
+// and one 16 x 128-byte box per activation plane, all with the 128-byte swizzle, which is exactly
+// the K-major shared-memory layout tcgen05 reads); one thread of warp 1 issues the MMAs and commits
+// them to the stage's "free" barrier and the accumulator's "full" barrier; warps 2..5 own the 128
+// TMEM lanes (one weight row per thread), read a finished accumulator with tcgen05.ld, scale and add.
+#include "mono_common.cuh"
+
+extern void mono_set_error(const char* fmt, ...);
+
+namespace mono {
+
+constexpr int kTcThreads = 192;
+constexpr int kTcStages = 8;
+constexpr int kTcABytes = 128 * 128;
+constexpr int kTcBBytes = 16 * 128;
+constexpr int kTcStageBytes = kTcABytes + 2 * kTcBBytes;  // two activation planes at most
+constexpr int kTcAcc = 4;                                 // TMEM accumulators in flight (16 columns each)
+constexpr int kTcTmemCols = 64;
+constexpr int kTcMaxSegTiles = 32;
+
+struct TcParams {
+    mono_gemv_args a;
+};
+
+struct TcSeg {
+    int c2, row0, t0, nt, aset;  // aset: activation set (head / expert slot) of the segment
+    const float* asc;
+    const float* wsc;
+    const float* coef;
+};
+
+__device__ __forceinline__ int tc_nrb(const mono_gemv_job& j) {
+    return (j.mode == MONO_JOB_DENSE && j.rb_per_mat > 0) ? j.n_mats * j.rb_per_mat : (j.n_rows + 127) >> 7;
+}
+
+__device__ __forceinline__ TcSeg tc_make_seg(const mono_gemv_job& j, int rb, int ks, int u) {
+    TcSeg s;
+    int mat = 0, rbm = rb;
+    if (j.mode == MONO_JOB_DENSE) {
+        if (j.rb_per_mat > 0) { mat = rb / j.rb_per_mat; rbm = rb - mat * j.rb_per_mat; }
+        s.t0 = ks * j.split_tiles;
+        s.nt = min(j.split_tiles, j.k_tiles - s.t0);
+        s.aset = j.act_seg_stride ? mat : 0;
+        s.coef = nullptr;
+    } else if (j.mode == MONO_JOB_EXPERT_UP) {
+        mat = j.expert_list[u];
+        s.t0 = ks * j.split_tiles;
+        s.nt = min(j.split_tiles, j.k_tiles - s.t0);
+        s.aset = 0;
+        s.coef = nullptr;
+    } else {
+        mat = j.expert_list[u];
+        s.t0 = 0;
+        s.nt = j.k_tiles;
+        s.aset = u;
+        s.coef = j.coef ? j.coef + (size_t)u * kMaxRows : nullptr;
+    }
+    s.c2 = mat;
+    s.row0 = j.row_off + rbm * 128;
+    s.asc = j.ascale_f32 + (size_t)s.aset * j.ascale_seg_stride + s.t0;
+    s.wsc = j.wscale_f32 + (size_t)mat * j.wscale_mat_stride + (size_t)(s.row0 >> 7) * j.wscale_ld + s.t0;
+    return s;
+}
+
+// ---- tcgen05 wrappers
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_alloc(uint32_t* dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc], kind::f8f6f4, one CTA
+__device__ __forceinline__ void tc_mma_f8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, float v[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzle:
+// groups of 8 rows are 1024 bytes apart (stride byte offset), the leading offset is unused.
+__device__ __forceinline__ uint64_t tc_desc_sw128(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor: D f32, A and B E4M3, both K-major, M = 128, N = 16.
+constexpr uint32_t kTcIdesc = (1u << 4) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+
+__device__ __forceinline__ void bar_epilogue() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+__global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_constant__ TcParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* ring = smem;
+    float* as_s = reinterpret_cast<float*>(smem + kTcStages * kTcStageBytes);  // [16][kTcMaxSegTiles]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(as_s + kMaxRows * kTcMaxSegTiles);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + kTcStages;
+    uint64_t* acc_full = bars + 2 * kTcStages;
+    uint64_t* acc_empty = bars + 2 * kTcStages + kTcAcc;
+    __shared__ int abort_flag;
+    __shared__ uint32_t tmem_base_s;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        abort_flag = guard_failed(p.a.guard) ? 1 : 0;
+        for (int i = 0; i < kTcStages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+        for (int i = 0; i < kTcAcc; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
+        mbar_fence_init();
+    }
+    if (warp == 1) tc_alloc(&tmem_base_s, kTcTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_s;
+    pdl_launch_dependents();
+    pdl_wait();
+
+    int cnt[MONO_GEMV_MAX_JOBS], nexp[MONO_GEMV_MAX_JOBS], total = 0;
+#pragma unroll
+    for (int j = 0; j < MONO_GEMV_MAX_JOBS; ++j) {
+        cnt[j] = 0;
+        nexp[j] = 0;
+        if (j < p.a.njobs) {
+            const mono_gemv_job& jb = p.a.job[j];
+            const int nrb = tc_nrb(jb);
+            if (jb.mode == MONO_JOB_DENSE) {
+                cnt[j] = nrb * jb.nsplit;
+            } else {
+                nexp[j] = min(*jb.n_expert, jb.max_expert);
+                cnt[j] = (jb.mode == MONO_JOB_EXPERT_UP) ? nexp[j] * nrb * jb.nsplit : nrb * jb.nsplit;
+            }
+        }
+        total += cnt[j];
+    }
+    volatile int* abortp = &abort_flag;
+
+// every role walks the same (task, segment, tile) sequence
+#define TC_FOR_EACH_SEGMENT(...)                                                                             \
+    for (int task = blockIdx.x; task < total && !*abortp; task += gridDim.x) {                                  \
+        int j = 0, local = task;                                                                                \
+        while (local >= cnt[j]) { local -= cnt[j]; ++j; }                                                       \
+        const mono_gemv_job& jb = p.a.job[j];                                                                   \
+        const int nrb = tc_nrb(jb);                                                                             \
+        int u = 0, nseg = 1;                                                                                    \
+        if (jb.mode == MONO_JOB_EXPERT_UP) { u = local / (nrb * jb.nsplit); local -= u * nrb * jb.nsplit; }     \
+        const int u_up = u, rb = local % nrb, ks = local / nrb;                                                 \
+        if (jb.mode == MONO_JOB_EXPERT_DOWN) nseg = (nexp[j] > ks) ? (nexp[j] - ks + jb.nsplit - 1) / jb.nsplit : 0; \
+        (void)u_up; (void)rb;                                                                                   \
+        TASK_BEGIN                                                                                              \
+        for (int sgi = 0; sgi < nseg && !*abortp; ++sgi) {                                                      \
+            if (jb.mode == MONO_JOB_EXPERT_DOWN) u = ks + sgi * jb.nsplit;                                      \
+            const TcSeg s = tc_make_seg(jb, rb, ks, u);                                                         \
+            __VA_ARGS__                                                                                         \
+        }                                                                                                       \
+        TASK_END                                                                                                \
+    }
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+#define TASK_BEGIN
+#define TASK_END
+            TC_FOR_EACH_SEGMENT({
+                const CUtensorMap* wmap = reinterpret_cast<const CUtensorMap*>(&jb.tmap);
+                const CUtensorMap* amap = reinterpret_cast<const CUtensorMap*>(&jb.act_tmap);
+                for (int t = 0; t < s.nt; ++t) {
+                    if (!mbar_wait(&empty[stage], phase ^ 1, abortp)) break;
+                    uint8_t* st = ring + (size_t)stage * kTcStageBytes;
+                    mbar_expect_tx(&full[stage], kTcABytes + jb.planes * kTcBBytes);
+                    tma_load_3d(st, wmap, (s.t0 + t) * 128, s.row0, s.c2, &full[stage]);
+                    for (int pl = 0; pl < jb.planes; ++pl)
+                        tma_load_3d(st + kTcABytes + pl * kTcBBytes, amap, (s.t0 + t) * 128, 0, s.aset * jb.planes + pl, &full[stage]);
+                    if (++stage == kTcStages) { stage = 0; phase ^= 1; }
+                }
+            })
+#undef TASK_BEGIN
+#undef TASK_END
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0, g = 0;
+#define TASK_BEGIN
+#define TASK_END
+            TC_FOR_EACH_SEGMENT({
+                for (int t = 0; t < s.nt; ++t) {
+                    const uint32_t acc = g % kTcAcc, aphase = (g / kTcAcc) & 1;
+                    if (!mbar_wait(&full[stage], phase, abortp)) break;
+                    if (!mbar_wait(&acc_empty[acc], aphase ^ 1, abortp)) break;
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(ring + (size_t)stage * kTcStageBytes);
+                    const uint64_t adesc = tc_desc_sw128(sa);
+                    uint32_t accumulate = 0;
+                    for (int pl = 0; pl < jb.planes; ++pl) {
+                        const uint64_t bdesc = tc_desc_sw128(sa + kTcABytes + pl * kTcBBytes);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {  // 32 bytes of K per MMA: the start address moves by 32 B
+                            tc_mma_f8(tmem_base + acc * 16, adesc + 2 * k, bdesc + 2 * k, kTcIdesc, accumulate);
+                            accumulate = 1;
+                        }
+                    }
+                    tc_commit(&empty[stage]);    // the stage's shared memory is free once these MMAs have read it
+                    tc_commit(&acc_full[acc]);   // and the accumulator is complete
+                    ++g;
+                    if (++stage == kTcStages) { stage = 0; phase ^= 1; }
+                }
+            })
+#undef TASK_BEGIN
+#undef TASK_END
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (TMEM lanes 32 * (warp % 4) ..)
+        const int q = warp & 3;
+        const int row_in_tile = q * 32 + lane;
+        const int et = tid - 64;  // 0..127
+        uint32_t g = 0;
+        float total_acc[kMaxRows];
+#define TASK_BEGIN                                              \
+        _Pragma("unroll") for (int c = 0; c < kMaxRows; ++c) total_acc[c] = 0.f;
+#define TASK_END                                                                                              \
+        if (!*abortp) {                                                                                       \
+            const int out_row = rb * 128 + row_in_tile;                                                       \
+            const int row_in_mat = (jb.mode == MONO_JOB_DENSE && jb.rb_per_mat > 0) ? (rb % jb.rb_per_mat) * 128 + row_in_tile : out_row; \
+            float* out = jb.out + (size_t)((jb.mode == MONO_JOB_EXPERT_UP ? u_up * jb.nsplit : 0) + ks) * jb.out_split_stride; \
+            if (row_in_mat < jb.n_rows) {                                                                     \
+                _Pragma("unroll") for (int c = 0; c < kMaxRows; ++c)                                          \
+                    if (c < p.a.rows) out[(size_t)c * jb.out_ld + out_row] = total_acc[c];                    \
+            }                                                                                                 \
+        }
+        TC_FOR_EACH_SEGMENT({
+            // stage the segment's activation scales [16][nt] and keep the weight scales in lanes
+            bar_epilogue();
+            for (int i = et; i < kMaxRows * s.nt; i += 128) {
+                const int c = i / s.nt, t = i - c * s.nt;
+                as_s[c * kTcMaxSegTiles + t] = c < p.a.rows ? s.asc[(size_t)c * jb.ascale_ld + t] : 0.f;
+            }
+            const float ws_lane = lane < s.nt ? __ldg(s.wsc + lane) : 0.f;
+            bar_epilogue();
+            float seg_acc[kMaxRows];
+#pragma unroll
+            for (int c = 0; c < kMaxRows; ++c) seg_acc[c] = 0.f;
+            for (int t = 0; t < s.nt; ++t) {
+                const uint32_t acc = g % kTcAcc, aphase = (g / kTcAcc) & 1;
+                if (!mbar_wait(&acc_full[acc], aphase, abortp)) break;
+                tc_fence_after();
+                float d[16];
+                tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + acc * 16, d);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[acc]);
+                const float ws = __shfl_sync(0xffffffffu, ws_lane, t);
+#pragma unroll
+                for (int c = 0; c < kMaxRows; ++c) seg_acc[c] += d[c] * (ws * as_s[c * kTcMaxSegTiles + t]);
+                ++g;
+            }
+#pragma unroll
+            for (int c = 0; c < kMaxRows; ++c) total_acc[c] += seg_acc[c] * (s.coef ? s.coef[c] : 1.f);
+        })
+#undef TASK_BEGIN
+#undef TASK_END
+    }
+#undef TC_FOR_EACH_SEGMENT
+    tc_fence_before();
+    __syncthreads();
+    if (abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);  // let copies in flight land before the CTA's memory goes
+        if (tid == 0 && !guard_failed(p.a.guard)) guard_fail(p.a.guard, MONO_ERR_DEADLINE, 101);
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tc_dealloc(tmem_base, kTcTmemCols);
+    }
+}
+
+}  // namespace mono
+
+static int g_mono_gemv_tc = 1;
+extern "C" int mono_set_gemv_tcgen05(int on) {
+    const int old = g_mono_gemv_tc;
+    g_mono_gemv_tc = on ? 1 : 0;
+    return old;
+}
+int mono_gemv_tc_enabled() { return g_mono_gemv_tc; }
+
+// Launches the tcgen05 kernel for an FP8 argument block that mono_gemv_launch has validated.
+int mono_gemv_tc_launch(const mono_gemv_args* a, long tasks, cudaStream_t st) {
+    using namespace mono;
+    for (int j = 0; j < a->njobs; ++j) {
+        const mono_gemv_job& jb = a->job[j];
+        const int seg = jb.mode == MONO_JOB_EXPERT_DOWN ? jb.k_tiles : (jb.split_tiles < jb.k_tiles ? jb.split_tiles : jb.k_tiles);
+        if (seg > kTcMaxSegTiles) {
+            mono_set_error("mono_gemv_launch: job %d: a segment may span at most %d tiles", j, kTcMaxSegTiles);
+            return MONO_E_ARG;
+        }
+    }
+    TcParams p;
+    p.a = *a;
+    const size_t smem = 1024 + (size_t)kTcStages * kTcStageBytes + kMaxRows * kTcMaxSegTiles * sizeof(float) + 256;
+    static thread_local bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    int grid = a->max_ctas > 0 ? a->max_ctas : mono_sm_count();
+    if (grid > tasks) grid = (int)tasks;
+    if (grid < 1) grid = 1;
+    cudaError_t e = launch_k(gemv_tc_kernel, grid, kTcThreads, smem, st, p);
+    return (int)(e != cudaSuccess ? e : cudaGetLastError());
+}

@@ -200,10 +200,23 @@ __global__ void __launch_bounds__(kTopkThreads) index_topk_kernel(const mono_ind
             }
         }
         __syncthreads();
+        // keys above digit d = suffix sum of the histogram: a warp scan plus 8 warp totals
+        int mine = 0, suffix = 0;
         if (tid < 256) {
-            int above = 0;
-            for (int d = tid + 1; d < 256; ++d) above += hist[d];
-            if (above < krem && krem <= above + hist[tid]) {
+            mine = hist[tid];
+            suffix = mine;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_down_sync(0xffffffffu, suffix, o);
+                if (lane + o < 32) suffix += t;
+            }
+            if (lane == 0) wsum_gt[warp] = suffix;  // total of digits 32 * warp .. 32 * warp + 31
+        }
+        __syncthreads();
+        if (tid < 256) {
+            int above = suffix - mine;
+            for (int w = warp + 1; w < 8; ++w) above += wsum_gt[w];
+            if (above < krem && krem <= above + mine) {
                 s_prefix = (prefix << 8) | (uint32_t)tid;
                 s_krem = krem - above;
             }

@@ -162,6 +162,9 @@ class Gemv:
             ws3 = ws if ws.dim() == 3 else ws.unsqueeze(0)
             job.wscale_e8, job.wscale_mat_stride, job.wscale_ld = ws.data_ptr(), ws3.shape[1] * ws3.shape[2], ws3.shape[2]
         job.act, job.planes, job.act_plane_stride, job.act_ld = _p(act.planes), act.nplanes, act.plane_stride, act.ld
+        L.check(L.load().mono_tmap_encode_box(C.byref(job.act_tmap), act.planes.data_ptr(), act.ld, L.MAX_ROWS,
+                                              act.segs * act.nplanes, act.ld, act.plane_stride, 16),
+                f"mono_tmap_encode_box({name}.act)")
         per_seg = act_per_mat or mode == L.JOB_EXPERT_DOWN
         job.act_seg_stride = act.seg_stride if per_seg else 0
         job.ascale_f32, job.ascale_e8, job.ascale_ld = _p(act.scale_f32), _p(act.scale_e8), act.scale_ld

@@ -70,6 +70,26 @@ def test_pad_rows_contribute_nothing():
     assert_close_hidden(out[keep], ref[keep], "live rows beside a pad row", scale=scale)
 
 
+@pytest.mark.parametrize("rows", [1, 8, 16])
+def test_tcgen05_and_warp_mma_paths_agree(rows):
+    """The FP8 GEMV has two consumers (tcgen05 + TMEM, warp-level MMA); both compute every 128-k chunk
+    exactly in f32 from the same E4M3 bytes, so they differ only in the order of f32 additions."""
+    cfg = CFG_TINY_MOE8
+    lib = L.load()
+    old = lib.mono_set_gemv_tcgen05(1)
+    try:
+        ffn, w, x, slots, out_tc = _run(cfg, rows)
+        lib.mono_set_gemv_tcgen05(0)
+        ffn2, _, _, _, out_mma = _run(cfg, rows)
+    finally:
+        lib.mono_set_gemv_tcgen05(old)
+    assert torch.equal(ffn.ids.cpu(), ffn2.ids.cpu())
+    d = (out_tc.float() - out_mma.float()).abs()
+    tol = 2.0 ** -7 * out_mma.float().abs().clamp_min(1.0)  # at most one bf16 ulp
+    assert bool((d <= tol).all()), f"max diff {float(d.max())}"
+    assert float((d > 0).float().mean()) < 0.05, "only rare last-bit differences are expected"
+
+
 def test_replays_are_bit_equal():
     cfg = CFG_TINY_MOE8
     ffn, w, x, slots, out = _run(cfg, 8)
