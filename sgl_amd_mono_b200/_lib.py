@@ -194,7 +194,7 @@ def load():
         if want != C.sizeof(st):
             raise MonoLibraryError(f"{st.__name__}: binding has {C.sizeof(st)} bytes, library has {want}")
     # process-wide switches, for A/B measurements: MONO_GEMV_TCGEN05=0|1, MONO_PDL=0|1
-    if os.environ.get("MONO_GEMV_TCGEN05") in ("0", "1"):
+    if os.environ.get("MONO_GEMV_TCGEN05", "").isdigit():  # 2..12 also caps the tcgen05 pipeline depth
         lib.mono_set_gemv_tcgen05(int(os.environ["MONO_GEMV_TCGEN05"]))
     if os.environ.get("MONO_PDL") in ("0", "1"):
         lib.mono_set_pdl(int(os.environ["MONO_PDL"]))

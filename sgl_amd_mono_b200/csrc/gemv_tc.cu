@@ -19,16 +19,18 @@ extern void mono_set_error(const char* fmt, ...);
 namespace mono {
 
 constexpr int kTcThreads = 192;
-constexpr int kTcStages = 8;
+constexpr int kTcMaxStages = 12;  // a stage = one weight tile + one tile per activation plane
 constexpr int kTcABytes = 128 * 128;
 constexpr int kTcBBytes = 16 * 128;
-constexpr int kTcStageBytes = kTcABytes + 2 * kTcBBytes;  // two activation planes at most
-constexpr int kTcAcc = 4;                                 // TMEM accumulators in flight (16 columns each)
+constexpr int kTcAcc = 4;  // TMEM accumulators in flight (16 columns each)
 constexpr int kTcTmemCols = 64;
 constexpr int kTcMaxSegTiles = 32;
+constexpr int kTcScSlots = 4;  // segments whose scales may be in flight
+constexpr int kTcScRows = 18;  // 16 activation-scale rows, the weight scales, the row coefficients
 
 struct TcParams {
     mono_gemv_args a;
+    int stages, stage_bytes;
 };
 
 struct TcSeg {
@@ -112,26 +114,40 @@ __device__ __forceinline__ uint64_t tc_desc_sw128(uint32_t saddr) {
 // Instruction descriptor: D f32, A and B E4M3, both K-major, M = 128, N = 16.
 constexpr uint32_t kTcIdesc = (1u << 4) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
 
-__device__ __forceinline__ void bar_epilogue() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void cp_async4(void* dst_smem, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+// The barrier gets one arrival from this thread once all of its earlier cp.async copies have landed.
+__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* map, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(reinterpret_cast<uint64_t>(map)),
+                 "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
 
 __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_constant__ TcParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* ring = smem;
-    float* as_s = reinterpret_cast<float*>(smem + kTcStages * kTcStageBytes);  // [16][kTcMaxSegTiles]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(as_s + kMaxRows * kTcMaxSegTiles);
+    float* sc_ring = reinterpret_cast<float*>(smem + (size_t)p.stages * p.stage_bytes);  // [kTcScSlots][kTcScRows][32]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sc_ring + kTcScSlots * kTcScRows * kTcMaxSegTiles);
     uint64_t* full = bars;
-    uint64_t* empty = bars + kTcStages;
-    uint64_t* acc_full = bars + 2 * kTcStages;
-    uint64_t* acc_empty = bars + 2 * kTcStages + kTcAcc;
+    uint64_t* empty = full + kTcMaxStages;
+    uint64_t* acc_full = empty + kTcMaxStages;
+    uint64_t* acc_empty = acc_full + kTcAcc;
+    uint64_t* sc_full = acc_empty + kTcAcc;
+    uint64_t* sc_empty = sc_full + kTcScSlots;
     __shared__ int abort_flag;
     __shared__ uint32_t tmem_base_s;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
         abort_flag = guard_failed(p.a.guard) ? 1 : 0;
-        for (int i = 0; i < kTcStages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+        for (int i = 0; i < p.stages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
         for (int i = 0; i < kTcAcc; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
+        for (int i = 0; i < kTcScSlots; ++i) { mbar_init(&sc_full[i], 32); mbar_init(&sc_empty[i], 4); }
         mbar_fence_init();
     }
     if (warp == 1) tc_alloc(&tmem_base_s, kTcTmemCols);
@@ -140,6 +156,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_s;
     pdl_launch_dependents();
+    if (warp == 0 && lane == 0) {
+        // Weights do not depend on the kernel before this one: while it drains, pull this CTA's first
+        // tiles towards L2 (only when the first task is known without upstream data: a dense job 0).
+        const mono_gemv_job& j0 = p.a.job[0];
+        if (j0.mode == MONO_JOB_DENSE && (int)blockIdx.x < tc_nrb(j0) * j0.nsplit) {
+            const int nrb = tc_nrb(j0);
+            const TcSeg s = tc_make_seg(j0, blockIdx.x % nrb, blockIdx.x / nrb, 0);
+            const CUtensorMap* wmap = reinterpret_cast<const CUtensorMap*>(&j0.tmap);
+            for (int t = 0; t < min(s.nt, p.stages); ++t) tma_prefetch_3d(wmap, (s.t0 + t) * 128, s.row0, s.c2);
+        }
+    }
     pdl_wait();
 
     int cnt[MONO_GEMV_MAX_JOBS], nexp[MONO_GEMV_MAX_JOBS], total = 0;
@@ -162,7 +189,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
     volatile int* abortp = &abort_flag;
 
 // every role walks the same (task, segment, tile) sequence
-#define TC_FOR_EACH_SEGMENT(...)                                                                             \
+#define TC_FOR_EACH_SEGMENT(...)                                                                                \
     for (int task = blockIdx.x; task < total && !*abortp; task += gridDim.x) {                                  \
         int j = 0, local = task;                                                                                \
         while (local >= cnt[j]) { local -= cnt[j]; ++j; }                                                       \
@@ -183,28 +210,44 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
     }
 
     if (warp == 0) {
-        // ------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
+        // ------------------------------------------------------------ producer: scales by cp.async, tiles by TMA
+        int stage = 0, slot = 0;
+        uint32_t phase = 0, sphase = 0;
 #define TASK_BEGIN
 #define TASK_END
-            TC_FOR_EACH_SEGMENT({
+        TC_FOR_EACH_SEGMENT({
+            // the segment's scales: rows 0..15 activation scales [nt], row 16 weight scales, row 17 coefficients
+            int ok = 1;
+            if (lane == 0) ok = mbar_wait(&sc_empty[slot], sphase ^ 1, abortp) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            float* sl = sc_ring + (size_t)slot * kTcScRows * kTcMaxSegTiles;
+            for (int i = lane; i < p.a.rows * s.nt; i += 32) {
+                const int c = i / s.nt, t = i - c * s.nt;
+                cp_async4(&sl[c * kTcMaxSegTiles + t], s.asc + (size_t)c * jb.ascale_ld + t);
+            }
+            if (lane < s.nt) cp_async4(&sl[16 * kTcMaxSegTiles + lane], s.wsc + lane);
+            if (s.coef && lane < p.a.rows) cp_async4(&sl[17 * kTcMaxSegTiles + lane], s.coef + lane);
+            cp_async_arrive(&sc_full[slot]);
+            if (++slot == kTcScSlots) { slot = 0; sphase ^= 1; }
+            if (lane == 0) {
                 const CUtensorMap* wmap = reinterpret_cast<const CUtensorMap*>(&jb.tmap);
                 const CUtensorMap* amap = reinterpret_cast<const CUtensorMap*>(&jb.act_tmap);
                 for (int t = 0; t < s.nt; ++t) {
                     if (!mbar_wait(&empty[stage], phase ^ 1, abortp)) break;
-                    uint8_t* st = ring + (size_t)stage * kTcStageBytes;
+                    uint8_t* st = ring + (size_t)stage * p.stage_bytes;
                     mbar_expect_tx(&full[stage], kTcABytes + jb.planes * kTcBBytes);
                     tma_load_3d(st, wmap, (s.t0 + t) * 128, s.row0, s.c2, &full[stage]);
                     for (int pl = 0; pl < jb.planes; ++pl)
                         tma_load_3d(st + kTcABytes + pl * kTcBBytes, amap, (s.t0 + t) * 128, 0, s.aset * jb.planes + pl, &full[stage]);
-                    if (++stage == kTcStages) { stage = 0; phase ^= 1; }
+                    if (++stage == p.stages) { stage = 0; phase ^= 1; }
                 }
-            })
+            }
+            __syncwarp();
+        })
 #undef TASK_BEGIN
 #undef TASK_END
-        }
+        asm volatile("cp.async.wait_all;" ::: "memory");
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
@@ -218,7 +261,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
                     if (!mbar_wait(&full[stage], phase, abortp)) break;
                     if (!mbar_wait(&acc_empty[acc], aphase ^ 1, abortp)) break;
                     tc_fence_after();
-                    const uint32_t sa = smem_u32(ring + (size_t)stage * kTcStageBytes);
+                    const uint32_t sa = smem_u32(ring + (size_t)stage * p.stage_bytes);
                     const uint64_t adesc = tc_desc_sw128(sa);
                     uint32_t accumulate = 0;
                     for (int pl = 0; pl < jb.planes; ++pl) {
@@ -229,10 +272,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
                             accumulate = 1;
                         }
                     }
-                    tc_commit(&empty[stage]);    // the stage's shared memory is free once these MMAs have read it
-                    tc_commit(&acc_full[acc]);   // and the accumulator is complete
+                    tc_commit(&empty[stage]);   // the stage's shared memory is free once these MMAs have read it
+                    tc_commit(&acc_full[acc]);  // and the accumulator is complete
                     ++g;
-                    if (++stage == kTcStages) { stage = 0; phase ^= 1; }
+                    if (++stage == p.stages) { stage = 0; phase ^= 1; }
                 }
             })
 #undef TASK_BEGIN
@@ -242,10 +285,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
         // ------------------------------------------------------------ epilogue (TMEM lanes 32 * (warp % 4) ..)
         const int q = warp & 3;
         const int row_in_tile = q * 32 + lane;
-        const int et = tid - 64;  // 0..127
-        uint32_t g = 0;
+        uint32_t g = 0, sphase = 0;
+        int slot = 0;
         float total_acc[kMaxRows];
-#define TASK_BEGIN                                              \
+#define TASK_BEGIN \
         _Pragma("unroll") for (int c = 0; c < kMaxRows; ++c) total_acc[c] = 0.f;
 #define TASK_END                                                                                              \
         if (!*abortp) {                                                                                       \
@@ -258,14 +301,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
             }                                                                                                 \
         }
         TC_FOR_EACH_SEGMENT({
-            // stage the segment's activation scales [16][nt] and keep the weight scales in lanes
-            bar_epilogue();
-            for (int i = et; i < kMaxRows * s.nt; i += 128) {
-                const int c = i / s.nt, t = i - c * s.nt;
-                as_s[c * kTcMaxSegTiles + t] = c < p.a.rows ? s.asc[(size_t)c * jb.ascale_ld + t] : 0.f;
-            }
-            const float ws_lane = lane < s.nt ? __ldg(s.wsc + lane) : 0.f;
-            bar_epilogue();
+            if (!mbar_wait(&sc_full[slot], sphase, abortp)) break;
+            const float* sl = sc_ring + (size_t)slot * kTcScRows * kTcMaxSegTiles;
             float seg_acc[kMaxRows];
 #pragma unroll
             for (int c = 0; c < kMaxRows; ++c) seg_acc[c] = 0.f;
@@ -278,13 +315,18 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&acc_empty[acc]);
-                const float ws = __shfl_sync(0xffffffffu, ws_lane, t);
+                const float ws = sl[16 * kTcMaxSegTiles + t];
 #pragma unroll
-                for (int c = 0; c < kMaxRows; ++c) seg_acc[c] += d[c] * (ws * as_s[c * kTcMaxSegTiles + t]);
+                for (int c = 0; c < kMaxRows; ++c)
+                    if (c < p.a.rows) seg_acc[c] += d[c] * (ws * sl[c * kTcMaxSegTiles + t]);
                 ++g;
             }
 #pragma unroll
-            for (int c = 0; c < kMaxRows; ++c) total_acc[c] += seg_acc[c] * (s.coef ? s.coef[c] : 1.f);
+            for (int c = 0; c < kMaxRows; ++c)
+                if (c < p.a.rows) total_acc[c] += seg_acc[c] * (s.coef ? sl[17 * kTcMaxSegTiles + c] : 1.f);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sc_empty[slot]);
+            if (++slot == kTcScSlots) { slot = 0; sphase ^= 1; }
         })
 #undef TASK_BEGIN
 #undef TASK_END
@@ -307,7 +349,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
 static int g_mono_gemv_tc = 1;
 extern "C" int mono_set_gemv_tcgen05(int on) {
     const int old = g_mono_gemv_tc;
-    g_mono_gemv_tc = on ? 1 : 0;
+    g_mono_gemv_tc = on < 0 ? 0 : on;  // values above 1 also cap the number of pipeline stages
     return old;
 }
 int mono_gemv_tc_enabled() { return g_mono_gemv_tc; }
@@ -325,10 +367,19 @@ int mono_gemv_tc_launch(const mono_gemv_args* a, long tasks, cudaStream_t st) {
     }
     TcParams p;
     p.a = *a;
-    const size_t smem = 1024 + (size_t)kTcStages * kTcStageBytes + kMaxRows * kTcMaxSegTiles * sizeof(float) + 256;
+    int planes = 1;
+    for (int j = 0; j < a->njobs; ++j) planes = a->job[j].planes > planes ? a->job[j].planes : planes;
+    // as many stages as fit: the bytes in flight per SM are what hides the DRAM latency
+    const int kSmemMax = 226 * 1024;  // 227 KB less the static part
+    const size_t fixed = 1024 + (size_t)kTcScSlots * kTcScRows * kTcMaxSegTiles * sizeof(float) + 512;
+    p.stage_bytes = kTcABytes + planes * kTcBBytes;
+    p.stages = (int)((kSmemMax - fixed) / p.stage_bytes);
+    if (p.stages > kTcMaxStages) p.stages = kTcMaxStages;
+    if (g_mono_gemv_tc > 1 && g_mono_gemv_tc < p.stages) p.stages = g_mono_gemv_tc;  // measurement aid: cap the ring
+    const size_t smem = fixed + (size_t)p.stages * p.stage_bytes;
     static thread_local bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }

@@ -226,35 +226,40 @@ __global__ void __launch_bounds__(kTopkThreads) index_topk_kernel(const mono_ind
     const uint32_t thr = s_prefix;
     const int remain = s_krem;  // ties to take
     const int n_gt = a.topk - remain;
-    // ordered gather: thread owns a contiguous run of positions
-    const int per = (n + kTopkThreads - 1) / kTopkThreads;
-    const int lo = min(tid * per, n), hi = min(lo + per, n);
-    int c_gt = 0, c_eq = 0;
-    for (int i = lo; i < hi; ++i) {
-        const uint32_t k = smem_keys ? skeys[i] : score_key(sc[i]);
-        c_gt += k > thr;
-        c_eq += k == thr;
+    // ordered gather: a warp owns a contiguous range of positions and walks it 32 at a time
+    // (consecutive lanes read consecutive keys); ballots give the order inside a group
+    const int seg = (((n + 31) / 32 + 31) / 32) * 32;  // positions per warp, a multiple of 32
+    const int lo = min(warp * seg, n), hi = min(lo + seg, n);
+    const uint32_t lt = (1u << lane) - 1;
+    int c_gt = 0, c_eq = 0;  // warp totals (the same in every lane)
+    for (int i0 = lo; i0 < hi; i0 += 32) {
+        const int i = i0 + lane;
+        const uint32_t k = i < hi ? (smem_keys ? skeys[i] : score_key(sc[i])) : 0u;
+        c_gt += __popc(__ballot_sync(0xffffffffu, i < hi && k > thr));
+        c_eq += __popc(__ballot_sync(0xffffffffu, i < hi && k == thr));
     }
-    int p_gt = c_gt, p_eq = c_eq;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const int x = __shfl_up_sync(0xffffffffu, p_gt, o), y = __shfl_up_sync(0xffffffffu, p_eq, o);
-        if (lane >= o) { p_gt += x; p_eq += y; }
-    }
-    if (lane == 31) { wsum_gt[warp] = p_gt; wsum_eq[warp] = p_eq; }
+    if (lane == 0) { wsum_gt[warp] = c_gt; wsum_eq[warp] = c_eq; }
     __syncthreads();
-    int b_gt = 0, b_eq = 0;
-    for (int w = 0; w < warp; ++w) { b_gt += wsum_gt[w]; b_eq += wsum_eq[w]; }
-    int o_gt = b_gt + p_gt - c_gt, o_eq = b_eq + p_eq - c_eq;  // exclusive prefixes
-    for (int i = lo; i < hi; ++i) {
-        const uint32_t k = smem_keys ? skeys[i] : score_key(sc[i]);
+    int o_gt = 0, o_eq = 0;  // exclusive prefixes over the warps before this one
+    {
+        const int g0 = lane < warp ? wsum_gt[lane] : 0, e0 = lane < warp ? wsum_eq[lane] : 0;
+        o_gt = __reduce_add_sync(0xffffffffu, g0);
+        o_eq = __reduce_add_sync(0xffffffffu, e0);
+    }
+    for (int i0 = lo; i0 < hi; i0 += 32) {
+        const int i = i0 + lane;
+        const uint32_t k = i < hi ? (smem_keys ? skeys[i] : score_key(sc[i])) : 0u;
+        const bool gt = i < hi && k > thr, eq = i < hi && k == thr;
+        const uint32_t m_gt = __ballot_sync(0xffffffffu, gt), m_eq = __ballot_sync(0xffffffffu, eq);
         int dst = -1;
-        if (k > thr) dst = o_gt++;
-        else if (k == thr) { if (o_eq < remain) dst = n_gt + o_eq; ++o_eq; }
+        if (gt) dst = o_gt + __popc(m_gt & lt);
+        else if (eq) { const int e = o_eq + __popc(m_eq & lt); if (e < remain) dst = n_gt + e; }
         if (dst >= 0) {
             out[dst] = pt[i / kPage] * kPage + i % kPage;
             if (outp) outp[dst] = i;
         }
+        o_gt += __popc(m_gt);
+        o_eq += __popc(m_eq);
     }
 }
 
