@@ -173,6 +173,18 @@ typedef struct mono_gemv_job {
     float* out;
     int out_ld;
     long out_split_stride; /* elements */
+    /* Chaining inside one launch (FP8 on the tcgen05 path only; expert FFN stages of
+     * glm53/gfx950/kernel.py:4352-5187, where one launch runs up, activation and down).
+     * An up/gate job with feeds_job > 0 (dense, or MONO_JOB_EXPERT_UP) counts its finished
+     * tasks per slot in done[slot] (slot 0 for a dense job); the CTA that finishes the last
+     * task of a slot adds the K splits, applies SwiGLU (gate = rows [0, n_rows/2), up = the
+     * rest), quantises per 128 values into the activation planes and scales of job
+     * feeds_job - 1, zeroes done[slot] and stamps ready[slot] with the launch's generation.  The
+     * fed job (a later job of the same launch) waits on that stamp, slot by slot, before it
+     * reads the activations; its weight tiles are requested ahead of the wait. */
+    int feeds_job;  /* 1 + index of the fed job; 0 = none */
+    int32_t* done;  /* [slots] task counters, zero between launches */
+    int32_t* ready; /* [slots] generation stamps; also set on the fed job */
 } mono_gemv_job;
 
 typedef struct mono_gemv_args {
@@ -181,6 +193,7 @@ typedef struct mono_gemv_args {
     int wkind; /* MONO_W_*: all jobs of one launch share it */
     int32_t* guard;
     int max_ctas; /* 0 = one per SM */
+    int32_t* gen; /* chained launches: [0] generation (the last CTA to leave adds 1), [1] leave counter */
     mono_gemv_job job[MONO_GEMV_MAX_JOBS];
 } mono_gemv_args;
 int mono_gemv_launch(const mono_gemv_args* a, void* stream);

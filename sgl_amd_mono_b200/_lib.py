@@ -39,13 +39,15 @@ class GemvJob(C.Structure):
         ("ascale_f32", vp), ("ascale_e8", vp), ("ascale_ld", i32), ("ascale_seg_stride", i64),
         ("coef", vp), ("expert_list", vp), ("n_expert", vp), ("max_expert", i32),
         ("out", vp), ("out_ld", i32), ("out_split_stride", i64),
+        ("feeds_job", i32), ("done", vp), ("ready", vp),
+        ("_tail", C.c_ubyte * 40),  # the struct is 64-byte aligned in C (tensor maps)
     ]
 
 
 class GemvArgs(C.Structure):
     _fields_ = [
-        ("njobs", i32), ("rows", i32), ("wkind", i32), ("guard", vp), ("max_ctas", i32),
-        ("_pad", C.c_ubyte * 36),  # the job array is 64-byte aligned in C
+        ("njobs", i32), ("rows", i32), ("wkind", i32), ("guard", vp), ("max_ctas", i32), ("gen", vp),
+        ("_pad", C.c_ubyte * 24),  # the job array is 64-byte aligned in C
         ("job", GemvJob * GEMV_MAX_JOBS),
     ]
 

@@ -530,6 +530,12 @@ extern "C" int mono_gemv_launch(const mono_gemv_args* a, void* stream) {
             return rc;
         }
     }
+    for (int j = 0; j < a->njobs; ++j) {
+        if (a->job[j].feeds_job > 0) {
+            mono_set_error("mono_gemv_launch: job %d: chained jobs run on the tcgen05 path only (FP8, activation maps set)", j);
+            return MONO_E_ARG;
+        }
+    }
     // row pitch = 16 (32 for the 8-byte MXFP4 reads) mod 128: conflict-free fragment loads
     p.b_pitch = max_seg_tiles * p.bb + (a->wkind == MONO_W_MXFP4 ? 32 : 16);
     p.scale_off = max_planes * NPAD * p.b_pitch;

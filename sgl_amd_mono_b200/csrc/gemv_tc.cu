@@ -18,12 +18,12 @@ extern void mono_set_error(const char* fmt, ...);
 
 namespace mono {
 
-constexpr int kTcThreads = 192;
-constexpr int kTcMaxStages = 12;  // a stage = one weight tile + one tile per activation plane
+constexpr int kTcThreads = 320;  // TMA, MMA, 4 epilogue warps, 4 finisher warps
+constexpr int kTcMaxStages = 8;  // a stage = one weight tile + one tile per activation plane; one accumulator each
 constexpr int kTcABytes = 128 * 128;
 constexpr int kTcBBytes = 16 * 128;
-constexpr int kTcAcc = 4;  // TMEM accumulators in flight (16 columns each)
-constexpr int kTcTmemCols = 64;
+constexpr int kTcAcc = 8;  // TMEM accumulators in flight (16 columns each)
+constexpr int kTcTmemCols = 128;
 constexpr int kTcMaxSegTiles = 32;
 constexpr int kTcScSlots = 4;  // segments whose scales may be in flight
 constexpr int kTcScRows = 18;  // 16 activation-scale rows, the weight scales, the row coefficients
@@ -106,6 +106,23 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, float v[16]) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
+// The same in two steps, so that the load of the next accumulator can be in flight during the math on
+// this one.  The wait names the registers as in/out operands: no read of them may move above it.
+__device__ __forceinline__ void tc_ld16_issue(uint32_t taddr, uint32_t r[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld16_wait(uint32_t r[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                   "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+                 :
+                 : "memory");
+}
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzle:
 // groups of 8 rows are 1024 bytes apart (stride byte offset), the leading offset is unused.
 __device__ __forceinline__ uint64_t tc_desc_sw128(uint32_t saddr) {
@@ -127,6 +144,125 @@ __device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* map, int c0, 
                  : "memory");
 }
 
+__device__ __forceinline__ int ld_acquire(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release(int* p, int v) {
+    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
+// Bounded wait for a generation stamp written by another CTA of this launch.
+__device__ __forceinline__ bool wait_stamp(const int* flag, int stamp, volatile int* abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t i = 0;; ++i) {
+        if (ld_acquire(flag) == stamp) return true;
+        __nanosleep(64);
+        if ((i & 15) == 15) {
+            if (*abort_flag) return false;
+            if (globaltimer_ns() - t0 > kWaitLimitNs) break;
+        }
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+// Rendezvous of the finisher warps on an mbarrier, with the bounded wait of every other wait here:
+// a thread that left because of an abort can never leave the others stuck in a barrier.
+struct BoundedSync {
+    uint64_t* bar;
+    uint32_t phase;
+    volatile int* abortp;
+    __device__ __forceinline__ bool sync() {
+        mbar_arrive(bar);
+        const bool ok = mbar_wait(bar, phase, abortp);
+        phase ^= 1;
+        return ok;
+    }
+};
+
+// The finisher warps (128 threads) learn that an up/gate task of `slot` is complete.  The CTA that counts
+// the slot's last task turns the partial sums into the fed job's activations: sum over the K splits in
+// order, SwiGLU, E4M3 with one amax/448 scale per 128 values (glm53/gfx950/kernel.py:1440-1450, :4352-5187).
+// Every load of a (row, chunk) pair is issued before the first is used: under a saturated memory system a
+// round trip costs microseconds, and the fed job waits for this.
+__device__ __forceinline__ void tc_finish_up(const TcParams& p, const mono_gemv_job& jb, int slot, int tasks_per_slot,
+                                             int stamp, int ft, volatile int* s_last, BoundedSync& fs) {
+    const int fwarp = ft >> 5, lane = ft & 31;
+    if (ft == 0) {
+        __threadfence();  // the epilogue's stores (ordered before this by the mailbox barrier) before the count
+        *s_last = (atomicAdd(jb.done + slot, 1) + 1 == tasks_per_slot) ? 1 : 0;
+    }
+    if (!fs.sync()) return;
+    if (!*s_last) return;
+    __threadfence();
+    const mono_gemv_job& fed = p.a.job[jb.feeds_job - 1];
+    const int inter = jb.n_rows >> 1, nchunks = inter >> 7, npairs = p.a.rows * nchunks;
+    const float* base = jb.out + (size_t)(jb.mode == MONO_JOB_EXPERT_UP ? slot * jb.nsplit : 0) * jb.out_split_stride;
+    uint8_t* planes = const_cast<uint8_t*>(fed.act) + (size_t)slot * fed.act_seg_stride;
+    float* scales = const_cast<float*>(fed.ascale_f32) + (size_t)slot * fed.ascale_seg_stride;
+    constexpr int kBatch = 2, kSplits = 4;  // pairs x K splits whose loads are in flight together
+    for (int pair0 = fwarp * kBatch; pair0 < npairs; pair0 += 4 * kBatch) {
+        float4 g4[kBatch], u4[kBatch];
+#pragma unroll
+        for (int q = 0; q < kBatch; ++q) g4[q] = u4[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s0 = 0; s0 < jb.nsplit; s0 += kSplits) {
+            float4 x[kBatch][kSplits], y[kBatch][kSplits];
+#pragma unroll
+            for (int q = 0; q < kBatch; ++q) {
+                const int pair = min(pair0 + q, npairs - 1);
+                const int r = pair / nchunks, c = pair - r * nchunks;
+                const float* gp = base + (size_t)r * jb.out_ld + c * 128 + 4 * lane;
+#pragma unroll
+                for (int s = 0; s < kSplits; ++s) {
+                    const int ss = min(s0 + s, jb.nsplit - 1);
+                    x[q][s] = __ldcg(reinterpret_cast<const float4*>(gp + (size_t)ss * jb.out_split_stride));
+                    y[q][s] = __ldcg(reinterpret_cast<const float4*>(gp + (size_t)ss * jb.out_split_stride + inter));
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < kBatch; ++q) {
+#pragma unroll
+                for (int s = 0; s < kSplits; ++s) {
+                    if (s0 + s < jb.nsplit) {
+                        g4[q].x += x[q][s].x; g4[q].y += x[q][s].y; g4[q].z += x[q][s].z; g4[q].w += x[q][s].w;
+                        u4[q].x += y[q][s].x; u4[q].y += y[q][s].y; u4[q].z += y[q][s].z; u4[q].w += y[q][s].w;
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < kBatch; ++q) {
+            const int pair = pair0 + q;
+            if (pair >= npairs) break;
+            const int r = pair / nchunks, c = pair - r * nchunks;
+            const float gs[4] = {g4[q].x, g4[q].y, g4[q].z, g4[q].w}, us[4] = {u4[q].x, u4[q].y, u4[q].z, u4[q].w};
+            float m[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) m[i] = gs[i] / (1.f + expf(-gs[i])) * us[i];
+            const float amax = warp_max(fmaxf(fmaxf(fabsf(m[0]), fabsf(m[1])), fmaxf(fabsf(m[2]), fabsf(m[3]))));
+            const float scale = amax > 0.f ? amax / 448.f : 1.f, inv = amax > 0.f ? 448.f / amax : 1.f;
+            uint32_t w = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) w |= (uint32_t)f32_to_e4m3(m[i] * inv) << (8 * i);
+            reinterpret_cast<uint32_t*>(planes + (size_t)r * fed.act_ld + c * 128)[lane] = w;
+            if (lane == 0) scales[(size_t)r * fed.ascale_ld + c] = scale;
+        }
+    }
+    fence_proxy_async();  // the fed job reads the planes with TMA
+    __threadfence();
+    if (!fs.sync()) return;
+    if (ft == 0) {
+        jb.done[slot] = 0;
+        st_release(jb.ready + slot, stamp);
+    }
+}
+
+__device__ unsigned long long g_tc_trace[148 * 8];
+__device__ unsigned long long g_tc_seg[4 * 96];  // CTA 0: per segment [wait-done, tiles-issued, epilogue-start, epilogue-done]
+#define TC_TRACE(i, v) g_tc_trace[(blockIdx.x % 148) * 8 + (i)] = (v)
+
 __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_constant__ TcParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -134,20 +270,24 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
     float* sc_ring = reinterpret_cast<float*>(smem + (size_t)p.stages * p.stage_bytes);  // [kTcScSlots][kTcScRows][32]
     uint64_t* bars = reinterpret_cast<uint64_t*>(sc_ring + kTcScSlots * kTcScRows * kTcMaxSegTiles);
     uint64_t* full = bars;
-    uint64_t* empty = full + kTcMaxStages;
-    uint64_t* acc_full = empty + kTcMaxStages;
+    uint64_t* acc_full = full + kTcMaxStages;
     uint64_t* acc_empty = acc_full + kTcAcc;
     uint64_t* sc_full = acc_empty + kTcAcc;
     uint64_t* sc_empty = sc_full + kTcScSlots;
-    __shared__ int abort_flag;
+    uint64_t* mail_full = sc_empty + kTcScSlots;  // epilogue -> finisher: an up/gate task's outputs are stored
+    uint64_t* mail_free = mail_full + 2;
+    uint64_t* fin_bar = mail_free + 2;
+    __shared__ int abort_flag, s_last[2];
     __shared__ uint32_t tmem_base_s;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
         abort_flag = guard_failed(p.a.guard) ? 1 : 0;
-        for (int i = 0; i < p.stages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+        for (int i = 0; i < p.stages; ++i) mbar_init(&full[i], 1);
         for (int i = 0; i < kTcAcc; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
         for (int i = 0; i < kTcScSlots; ++i) { mbar_init(&sc_full[i], 32); mbar_init(&sc_empty[i], 4); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&mail_full[i], 128); mbar_init(&mail_free[i], 1); }
+        mbar_init(fin_bar, 128);
         mbar_fence_init();
     }
     if (warp == 1) tc_alloc(&tmem_base_s, kTcTmemCols);
@@ -168,6 +308,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
         }
     }
     pdl_wait();
+    // chained jobs stamp their per-slot "activations ready" words with this launch's generation
+    const int stamp = p.a.gen ? *reinterpret_cast<const volatile int*>(p.a.gen) + 1 : 1;
+    const unsigned long long t_start = globaltimer_ns();
+    if (tid == 0) { TC_TRACE(0, t_start); TC_TRACE(1, 0ull); TC_TRACE(2, 0ull); TC_TRACE(5, 0ull); }
+    unsigned long long t_wait = 0;
 
     int cnt[MONO_GEMV_MAX_JOBS], nexp[MONO_GEMV_MAX_JOBS], total = 0;
 #pragma unroll
@@ -212,12 +357,44 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
     if (warp == 0) {
         // ------------------------------------------------------------ producer: scales by cp.async, tiles by TMA
         int stage = 0, slot = 0;
-        uint32_t phase = 0, sphase = 0;
+        uint32_t phase = 0, sphase = 0, ready_mask = 0;
+        int nseg_seen = 0;
 #define TASK_BEGIN
 #define TASK_END
         TC_FOR_EACH_SEGMENT({
             // the segment's scales: rows 0..15 activation scales [nt], row 16 weight scales, row 17 coefficients
             int ok = 1;
+            if (jb.ready && jb.feeds_job == 0) {
+                // a fed job: the activations of a slot come from an up/gate job of this launch.  One round of
+                // flag loads per task (lane s looks at segment s); only segments that were not ready then
+                // are polled again when their turn comes.
+                const bool down = jb.mode == MONO_JOB_EXPERT_DOWN;
+                if (sgi == 0) {
+                    const bool r = lane < nseg ? ld_acquire(jb.ready + (down ? ks + lane * jb.nsplit : 0)) == stamp : true;
+                    ready_mask = __ballot_sync(0xffffffffu, r);
+                    if (ready_mask != 0xffffffffu && lane == 0) {
+                        // pull the whole task's weight tiles towards L2 while the up/gate jobs finish
+                        const CUtensorMap* wmap = reinterpret_cast<const CUtensorMap*>(&jb.tmap);
+                        for (int sg2 = 0; sg2 < nseg; ++sg2) {
+                            const TcSeg s2 = tc_make_seg(jb, rb, ks, down ? ks + sg2 * jb.nsplit : u);
+                            for (int t = 0; t < s2.nt; ++t) tma_prefetch_3d(wmap, (s2.t0 + t) * 128, s2.row0, s2.c2);
+                        }
+                    }
+                }
+                if (sgi >= 32 || !((ready_mask >> sgi) & 1u)) {
+                    if (lane == 0) {
+                        const unsigned long long t0 = globaltimer_ns();
+                        if (t_wait == 0) TC_TRACE(1, t0 - t_start);
+                        ok = wait_stamp(jb.ready + (down ? u : 0), stamp, abortp) ? 1 : 0;
+                        t_wait += globaltimer_ns() - t0;
+                        TC_TRACE(2, t_wait);
+                    }
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok) break;
+                }
+                // (the writer ordered its stores against the async proxy before it released the stamp)
+            }
+            if (lane == 0 && blockIdx.x == 0 && nseg_seen < 96) g_tc_seg[0 * 96 + nseg_seen] = globaltimer_ns() - t_start;
             if (lane == 0) ok = mbar_wait(&sc_empty[slot], sphase ^ 1, abortp) ? 1 : 0;
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
@@ -234,7 +411,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
                 const CUtensorMap* wmap = reinterpret_cast<const CUtensorMap*>(&jb.tmap);
                 const CUtensorMap* amap = reinterpret_cast<const CUtensorMap*>(&jb.act_tmap);
                 for (int t = 0; t < s.nt; ++t) {
-                    if (!mbar_wait(&empty[stage], phase ^ 1, abortp)) break;
+                    if (!mbar_wait(&acc_full[stage], phase ^ 1, abortp)) break;  // the MMAs of the stage's last tile are done
                     uint8_t* st = ring + (size_t)stage * p.stage_bytes;
                     mbar_expect_tx(&full[stage], kTcABytes + jb.planes * kTcBBytes);
                     tma_load_3d(st, wmap, (s.t0 + t) * 128, s.row0, s.c2, &full[stage]);
@@ -243,23 +420,31 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
                     if (++stage == p.stages) { stage = 0; phase ^= 1; }
                 }
             }
+            if (lane == 0 && blockIdx.x == 0 && nseg_seen < 96) g_tc_seg[1 * 96 + nseg_seen] = globaltimer_ns() - t_start;
+            ++nseg_seen;
             __syncwarp();
         })
 #undef TASK_BEGIN
 #undef TASK_END
         asm volatile("cp.async.wait_all;" ::: "memory");
+        if (lane == 0) TC_TRACE(3, globaltimer_ns() - t_start);
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0, g = 0;
+            long long cw_full = 0, cw_acc = 0, call0 = clock64();
 #define TASK_BEGIN
 #define TASK_END
             TC_FOR_EACH_SEGMENT({
                 for (int t = 0; t < s.nt; ++t) {
                     const uint32_t acc = g % kTcAcc, aphase = (g / kTcAcc) & 1;
+                    const long long w0 = clock64();
                     if (!mbar_wait(&full[stage], phase, abortp)) break;
+                    const long long w1 = clock64();
                     if (!mbar_wait(&acc_empty[acc], aphase ^ 1, abortp)) break;
+                    const long long w2 = clock64();
+                    cw_full += w1 - w0; cw_acc += w2 - w1;
                     tc_fence_after();
                     const uint32_t sa = smem_u32(ring + (size_t)stage * p.stage_bytes);
                     const uint64_t adesc = tc_desc_sw128(sa);
@@ -272,21 +457,30 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
                             accumulate = 1;
                         }
                     }
-                    tc_commit(&empty[stage]);   // the stage's shared memory is free once these MMAs have read it
-                    tc_commit(&acc_full[acc]);  // and the accumulator is complete
+                    // one commit serves both: the accumulator is complete (epilogue) and the stage's shared
+                    // memory has been read (producer); stage s and accumulator s always go together
+                    tc_commit(&acc_full[acc]);
                     ++g;
                     if (++stage == p.stages) { stage = 0; phase ^= 1; }
                 }
             })
 #undef TASK_BEGIN
 #undef TASK_END
+            if (blockIdx.x == 0) { g_tc_seg[90] = cw_full; g_tc_seg[91] = cw_acc; g_tc_seg[92] = clock64() - call0; g_tc_seg[93] = g; }
         }
-    } else {
+    } else if (warp < 6) {
         // ------------------------------------------------------------ epilogue (TMEM lanes 32 * (warp % 4) ..)
         const int q = warp & 3;
         const int row_in_tile = q * 32 + lane;
         uint32_t g = 0, sphase = 0;
         int slot = 0;
+        uint32_t nfeed = 0;
+        int nseg_seen = 0;
+        const uint32_t tmem_lane = tmem_base + ((uint32_t)(q * 32) << 16);
+        uint32_t dn[16];  // raw registers of the accumulator load in flight
+        bool have_next = false;
+        long long ce_wait = 0, ce_all0 = clock64();
+        int ce_miss = 0;
         float total_acc[kMaxRows];
 #define TASK_BEGIN \
         _Pragma("unroll") for (int c = 0; c < kMaxRows; ++c) total_acc[c] = 0.f;
@@ -299,8 +493,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
                 _Pragma("unroll") for (int c = 0; c < kMaxRows; ++c)                                          \
                     if (c < p.a.rows) out[(size_t)c * jb.out_ld + out_row] = total_acc[c];                    \
             }                                                                                                 \
+            if (jb.feeds_job > 0) {                                                                           \
+                const uint32_t k = nfeed & 1;                                                                 \
+                if (mbar_wait(&mail_free[k], ((nfeed >> 1) & 1) ^ 1, abortp)) mbar_arrive(&mail_full[k]);     \
+                if (tid == 64) TC_TRACE(7, globaltimer_ns() - t_start);                                       \
+                ++nfeed;                                                                                      \
+            }                                                                                                 \
         }
         TC_FOR_EACH_SEGMENT({
+            if (tid == 64 && blockIdx.x == 0 && nseg_seen < 96) g_tc_seg[2 * 96 + nseg_seen] = globaltimer_ns() - t_start;
             if (!mbar_wait(&sc_full[slot], sphase, abortp)) break;
             const float* sl = sc_ring + (size_t)slot * kTcScRows * kTcMaxSegTiles;
             float seg_acc[kMaxRows];
@@ -308,13 +509,31 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
             for (int c = 0; c < kMaxRows; ++c) seg_acc[c] = 0.f;
             for (int t = 0; t < s.nt; ++t) {
                 const uint32_t acc = g % kTcAcc, aphase = (g / kTcAcc) & 1;
-                if (!mbar_wait(&acc_full[acc], aphase, abortp)) break;
-                tc_fence_after();
+                if (!have_next) {
+                    const long long e0 = clock64();
+                    if (!mbar_wait(&acc_full[acc], aphase, abortp)) break;
+                    ce_wait += clock64() - e0;
+                    ++ce_miss;
+                    tc_fence_after();
+                    tc_ld16_issue(tmem_lane + acc * 16, dn);
+                }
+                tc_ld16_wait(dn);
                 float d[16];
-                tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + acc * 16, d);
+#pragma unroll
+                for (int c = 0; c < 16; ++c) d[c] = __uint_as_float(dn[c]);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&acc_empty[acc]);
+                {
+                    // if the next accumulator is complete already, start its load before the math on this one
+                    const uint32_t g1 = g + 1, acc1 = g1 % kTcAcc;
+                    int h = lane == 0 ? (mbar_try_wait(&acc_full[acc1], (g1 / kTcAcc) & 1) ? 1 : 0) : 0;
+                    have_next = __shfl_sync(0xffffffffu, h, 0) != 0;
+                    if (have_next) {
+                        tc_fence_after();
+                        tc_ld16_issue(tmem_lane + acc1 * 16, dn);
+                    }
+                }
                 const float ws = sl[16 * kTcMaxSegTiles + t];
 #pragma unroll
                 for (int c = 0; c < kMaxRows; ++c)
@@ -326,8 +545,35 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
                 if (c < p.a.rows) total_acc[c] += seg_acc[c] * (s.coef ? sl[17 * kTcMaxSegTiles + c] : 1.f);
             __syncwarp();
             if (lane == 0) mbar_arrive(&sc_empty[slot]);
+            if (tid == 64 && blockIdx.x == 0 && nseg_seen < 96) g_tc_seg[3 * 96 + nseg_seen] = globaltimer_ns() - t_start;
+            ++nseg_seen;
             if (++slot == kTcScSlots) { slot = 0; sphase ^= 1; }
         })
+#undef TASK_BEGIN
+#undef TASK_END
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");  // nothing in flight when TMEM goes (abort paths)
+        if (blockIdx.x == 0 && tid == 64) { g_tc_seg[96 + 90] = ce_wait; g_tc_seg[96 + 91] = clock64() - ce_all0; g_tc_seg[96 + 92] = ce_miss; }
+        if (tid == 64) TC_TRACE(4, globaltimer_ns() - t_start);
+    }
+    if (warp >= 6) {
+        const int ft = tid - 192;
+        BoundedSync fs{fin_bar, 0u, abortp};
+        // ------------------------------------------------------------ finisher: counts finished up/gate tasks
+        uint32_t nfeed = 0;
+#define TASK_BEGIN
+#define TASK_END                                                                                              \
+        if (jb.feeds_job > 0 && !*abortp) {                                                                   \
+            const uint32_t k = nfeed & 1;                                                                     \
+            if (mbar_wait(&mail_full[k], (nfeed >> 1) & 1, abortp)) {                                         \
+                const unsigned long long tf0 = globaltimer_ns();                                              \
+                tc_finish_up(p, jb, jb.mode == MONO_JOB_EXPERT_UP ? u_up : 0, nrb * jb.nsplit, stamp, ft, &s_last[k], fs); \
+                t_wait += globaltimer_ns() - tf0;                                                             \
+                if (ft == 0) { TC_TRACE(5, t_wait); TC_TRACE(6, globaltimer_ns() - t_start); }              \
+                if (ft == 0) mbar_arrive(&mail_free[k]);                                                    \
+            }                                                                                                 \
+            ++nfeed;                                                                                          \
+        }
+        TC_FOR_EACH_SEGMENT({ (void)s; })
 #undef TASK_BEGIN
 #undef TASK_END
     }
@@ -342,9 +588,23 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
         tc_fence_after();
         tc_dealloc(tmem_base, kTcTmemCols);
     }
+    if (tid == 0 && p.a.gen) {
+        // the last CTA to leave starts the next generation
+        __threadfence();
+        if (atomicAdd(p.a.gen + 1, 1) == (int)gridDim.x - 1) {
+            p.a.gen[1] = 0;
+            __threadfence();
+            atomicAdd(p.a.gen, 1);
+        }
+    }
 }
 
 }  // namespace mono
+
+extern "C" int mono_debug_tc_trace(unsigned long long* out) {
+    cudaMemcpyFromSymbol(out + 148 * 8, mono::g_tc_seg, sizeof(unsigned long long) * 4 * 96);
+    return (int)cudaMemcpyFromSymbol(out, mono::g_tc_trace, sizeof(unsigned long long) * 148 * 8);
+}
 
 static int g_mono_gemv_tc = 1;
 extern "C" int mono_set_gemv_tcgen05(int on) {
@@ -364,6 +624,17 @@ int mono_gemv_tc_launch(const mono_gemv_args* a, long tasks, cudaStream_t st) {
             mono_set_error("mono_gemv_launch: job %d: a segment may span at most %d tiles", j, kTcMaxSegTiles);
             return MONO_E_ARG;
         }
+        if (jb.feeds_job > 0) {
+            const int f = jb.feeds_job - 1;
+            const bool shape_ok = jb.mode != MONO_JOB_EXPERT_DOWN && jb.rb_per_mat == 0 && (jb.n_rows & 255) == 0;
+            if (!a->gen || !jb.done || !jb.ready || f <= j || f >= a->njobs || !shape_ok || a->job[f].ready != jb.ready ||
+                a->job[f].planes != 1 || a->job[f].k_tiles * 128 != jb.n_rows / 2 ||
+                (jb.mode == MONO_JOB_EXPERT_UP) != (a->job[f].mode == MONO_JOB_EXPERT_DOWN)) {
+                mono_set_error("mono_gemv_launch: job %d: a chained up/gate job needs gen, done, ready, 2 * inter rows with "
+                               "inter a multiple of 128, and a later job of matching kind with one E4M3 plane of inter bytes", j);
+                return MONO_E_ARG;
+            }
+        }
     }
     TcParams p;
     p.a = *a;
@@ -374,8 +645,8 @@ int mono_gemv_tc_launch(const mono_gemv_args* a, long tasks, cudaStream_t st) {
     const size_t fixed = 1024 + (size_t)kTcScSlots * kTcScRows * kTcMaxSegTiles * sizeof(float) + 512;
     p.stage_bytes = kTcABytes + planes * kTcBBytes;
     p.stages = (int)((kSmemMax - fixed) / p.stage_bytes);
-    if (p.stages > kTcMaxStages) p.stages = kTcMaxStages;
-    if (g_mono_gemv_tc > 1 && g_mono_gemv_tc < p.stages) p.stages = g_mono_gemv_tc;  // measurement aid: cap the ring
+    if (p.stages < kTcMaxStages) return MONO_E_ARG;
+    p.stages = kTcMaxStages;  // = kTcAcc: stage s feeds accumulator s
     const size_t smem = fixed + (size_t)p.stages * p.stage_bytes;
     static thread_local bool attr_set = false;
     if (!attr_set) {

@@ -10,6 +10,8 @@ CUDA graph and replayed.
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _lib as L
@@ -30,7 +32,9 @@ class MoeFfn:
 
     def __init__(self, cfg: LayerConfig, w: dict, device, max_rows: int = L.MAX_ROWS, peer=None,
                  guard: torch.Tensor | None = None, site: int = 1, deadline_s: float = 5.0):
-        L.load()  # fail loudly when the CUDA library is missing
+        lib = L.load()  # fail loudly when the CUDA library is missing
+        tc_on = lib.mono_set_gemv_tcgen05(1)  # read the switch ...
+        lib.mono_set_gemv_tcgen05(tc_on)      # ... and put it back
         self.cfg, self.w, self.dev, self.peer, self.site = cfg, w, device, peer, site
         self.deadline_s = deadline_s
         self.guard = guard if guard is not None else torch.zeros(L.GUARD_WORDS, dtype=torch.int32, device=device)
@@ -64,7 +68,9 @@ class MoeFfn:
             g = self.up if same else ops.Gemv(_WK[sfmt], self.guard)
             g.add("sh13", w["sh13"], self.xs, self.up_s, wscale=w.get("sh13_s"), split_tiles=st, nsplit=ns)
             self.up_sh = None if same else g
-        probe = ops.plan_split(_ktiles(w["w13"]), -(-2 * il // 128) * self.max_expert, _WK[efmt])
+        # the tcgen05 consumer takes K segments of up to 32 tiles (no activation slot to fit): fewer K splits
+        probe = ops.plan_split(_ktiles(w["w13"]), -(-2 * il // 128) * self.max_expert, _WK[efmt],
+                               cap=32 if (efmt == "fp8_block" and tc_on) else None)
         self.ns_up = probe[1]
         self.up_r = z(self.max_expert * self.ns_up, L.MAX_ROWS, 2 * il)
         got = self.up.add("w13", w["w13"], self.xq, self.up_r, mode=L.JOB_EXPERT_UP, wscale=w["w13_s"],
@@ -97,6 +103,27 @@ class MoeFfn:
                       expert_list=self.expert_list, n_expert=self.n_expert, max_expert=self.max_expert,
                       coef=self.coef, nsplit=self.groups)
         self.out = z(L.MAX_ROWS, h, dt=torch.bfloat16)
+        # ---- one launch for up/gate -> SwiGLU -> down (FP8 on the tcgen05 path): the same jobs, chained
+        self.chained = None
+        if efmt == "fp8_block" and (not self.has_shared or same) and tc_on and os.environ.get("MONO_MOE_CHAINED", "1") != "0":
+            g = ops.Gemv(L.W_FP8, self.guard)
+            first = 0
+            if self.has_shared:
+                g.add("sh13", w["sh13"], self.xs, self.up_s, wscale=w.get("sh13_s"), split_tiles=st, nsplit=self.ns_up_s)
+                first = 1
+            g.add("w13", w["w13"], self.xq, self.up_r, mode=L.JOB_EXPERT_UP, wscale=w["w13_s"],
+                  expert_list=self.expert_list, n_expert=self.n_expert, max_expert=self.max_expert,
+                  split_tiles=probe[0], nsplit=probe[1])
+            if self.has_shared:
+                g.add("sh2", w["sh2"], self.mid_s, self.down_p, wscale=w.get("sh2_s"), out_slice=self.groups,
+                      split_tiles=self.st_dn_s, nsplit=ns_dn_s)
+            g.add("w2", w["w2"], self.mid_r, self.down_p, mode=L.JOB_EXPERT_DOWN, wscale=w["w2_s"],
+                  expert_list=self.expert_list, n_expert=self.n_expert, max_expert=self.max_expert,
+                  coef=self.coef, nsplit=self.groups)
+            if self.has_shared:
+                g.chain(0, 2, 1)
+            g.chain(first, first + (2 if self.has_shared else 1), self.max_expert)
+            self.chained = g
 
     def __call__(self, residual: torch.Tensor, slots: torch.Tensor | None = None) -> torch.Tensor:
         cfg, w = self.cfg, self.w
@@ -113,6 +140,11 @@ class MoeFfn:
         ops.rowdot(rows, w["router"], self.xbf, self.logits)
         ops.route(rows, cfg.top_k, cfg.route_scale, self.logits, w.get("router_bias"), slots, self.ids,
                   self.weights, self.scores, self.expert_list, self.n_expert, self.coef)
+        if self.chained is not None:
+            self.chained.launch(rows)
+            ops.reduce_rows(rows, h, self.down_p, self.n_slices, self.out, residual=residual, slots=slots,
+                            peer=self.peer, site=self.site, guard=self.guard, deadline_s=self.deadline_s)
+            return self.out[:rows]
         self.up.launch(rows)
         if self.up_sh is not None:
             self.up_sh.launch(rows)

@@ -178,9 +178,26 @@ class Gemv:
         n_slices = job.nsplit * (max_expert if mode == L.JOB_EXPERT_UP else 1)
         if out.dtype != torch.float32 or out.numel() < (out_slice + n_slices) * slice_elems:
             raise ValueError(f"{name}: output buffer holds {out.numel()} f32, needs {(out_slice + n_slices) * slice_elems}")
+        job.feeds_job = 0
         self._keep += [w, wscale, act, out, expert_list, n_expert, coef]
         self.args.njobs = j + 1
         return job.nsplit
+
+    def chain(self, up_job: int, down_job: int, slots: int) -> None:
+        """Job ``up_job`` (up/gate) feeds job ``down_job`` inside the launch: the CTA that finishes the
+        last up task of a slot applies SwiGLU and quantises into the down job's activation buffer."""
+        if self.wkind != L.W_FP8 or not 0 <= up_job < down_job < self.args.njobs:
+            raise ValueError("chain: FP8 launches only, and the up job must come before the job it feeds")
+        dev = next(t.device for t in self._keep if isinstance(t, torch.Tensor))
+        if getattr(self, "gen", None) is None:
+            self.gen = torch.zeros(2, dtype=torch.int32, device=dev)
+            self.args.gen = self.gen.data_ptr()
+        done = torch.zeros(slots, dtype=torch.int32, device=dev)
+        ready = torch.zeros(slots, dtype=torch.int32, device=dev)
+        up, dn = self.args.job[up_job], self.args.job[down_job]
+        up.feeds_job, up.done, up.ready = down_job + 1, done.data_ptr(), ready.data_ptr()
+        dn.ready = ready.data_ptr()
+        self._keep += [done, ready]
 
     def launch(self, rows: int) -> None:
         self.args.rows = rows

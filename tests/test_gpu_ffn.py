@@ -90,6 +90,31 @@ def test_tcgen05_and_warp_mma_paths_agree(rows):
     assert float((d > 0).float().mean()) < 0.05, "only rare last-bit differences are expected"
 
 
+@pytest.mark.parametrize("rows", [1, 8, 16])
+def test_chained_launch_equals_separate_launches(rows, monkeypatch):
+    """up/gate -> SwiGLU -> down inside one launch does the arithmetic of the separate launches in the
+    same order: activations, scales and the block's output are bit-equal."""
+    cfg = CFG_TINY_MOE8
+    ffn, w, x, slots, out = _run(cfg, rows)
+    assert ffn.chained is not None, "the FP8 block takes the chained launch by default"
+    monkeypatch.setenv("MONO_MOE_CHAINED", "0")
+    ffn2, _, _, _, out2 = _run(cfg, rows)
+    assert ffn2.chained is None
+    n = int(ffn.n_expert.item())
+    assert torch.equal(ffn.mid_r.planes[:n], ffn2.mid_r.planes[:n])
+    assert torch.equal(ffn.mid_r.scale_f32[:n, :rows], ffn2.mid_r.scale_f32[:n, :rows])
+    assert torch.equal(ffn.mid_s.planes, ffn2.mid_s.planes)
+    assert torch.equal(ffn.down_p, ffn2.down_p)
+    assert torch.equal(out, out2)
+    # replays of the chained launch: the counters and stamps reset themselves
+    xd, sd = x.to(DEV), slots.to(DEV)
+    for _ in range(4):
+        assert torch.equal(ffn(xd, sd), out)
+    torch.cuda.synchronize()
+    rc, words = ops.guard_read(ffn.guard)
+    assert rc == 0, f"guard words {words}"
+
+
 def test_replays_are_bit_equal():
     cfg = CFG_TINY_MOE8
     ffn, w, x, slots, out = _run(cfg, 8)
