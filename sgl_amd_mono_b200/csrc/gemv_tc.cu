@@ -19,12 +19,13 @@ extern void mono_set_error(const char* fmt, ...);
 namespace mono {
 
 constexpr int kTcThreads = 320;  // TMA, MMA, 4 epilogue warps, 4 finisher warps
-constexpr int kTcMaxStages = 8;  // a stage = one weight tile + one tile per activation plane; one accumulator each
+constexpr int kTcUnit = 2;       // k tiles per pipeline unit: one barrier round trip, one commit, one TMEM load for both
+constexpr int kTcMaxStages = 5;  // a stage = a unit's weight tiles + its tiles of each activation plane; one accumulator pair each
 constexpr int kTcABytes = 128 * 128;
 constexpr int kTcBBytes = 16 * 128;
-constexpr int kTcAcc = 8;  // TMEM accumulators in flight (16 columns each)
-constexpr int kTcTmemCols = 128;
+constexpr int kTcTmemCols = 256;  // kTcMaxStages accumulator pairs of 2 x 16 columns (allocations are powers of two)
 constexpr int kTcMaxSegTiles = 32;
+constexpr int kTcListCache = 128;  // expert-list entries per job kept in shared memory
 constexpr int kTcScSlots = 4;  // segments whose scales may be in flight
 constexpr int kTcScRows = 18;  // 16 activation-scale rows, the weight scales, the row coefficients
 
@@ -44,7 +45,7 @@ __device__ __forceinline__ int tc_nrb(const mono_gemv_job& j) {
     return (j.mode == MONO_JOB_DENSE && j.rb_per_mat > 0) ? j.n_mats * j.rb_per_mat : (j.n_rows + 127) >> 7;
 }
 
-__device__ __forceinline__ TcSeg tc_make_seg(const mono_gemv_job& j, int rb, int ks, int u) {
+__device__ __forceinline__ TcSeg tc_make_seg(const mono_gemv_job& j, int rb, int ks, int u, const int* elist = nullptr) {
     TcSeg s;
     int mat = 0, rbm = rb;
     if (j.mode == MONO_JOB_DENSE) {
@@ -54,13 +55,13 @@ __device__ __forceinline__ TcSeg tc_make_seg(const mono_gemv_job& j, int rb, int
         s.aset = j.act_seg_stride ? mat : 0;
         s.coef = nullptr;
     } else if (j.mode == MONO_JOB_EXPERT_UP) {
-        mat = j.expert_list[u];
+        mat = (elist && u < kTcListCache) ? elist[u] : j.expert_list[u];
         s.t0 = ks * j.split_tiles;
         s.nt = min(j.split_tiles, j.k_tiles - s.t0);
         s.aset = 0;
         s.coef = nullptr;
     } else {
-        mat = j.expert_list[u];
+        mat = (elist && u < kTcListCache) ? elist[u] : j.expert_list[u];
         s.t0 = 0;
         s.nt = j.k_tiles;
         s.aset = u;
@@ -94,32 +95,18 @@ __device__ __forceinline__ void tc_mma_f8(uint32_t tmem_d, uint64_t adesc, uint6
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, float v[16]) {
-    uint32_t r[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+// TMEM -> registers in two steps, so that the load of the next accumulators can be in flight during the
+// math on these.  The wait names the registers as in/out operands: no read of them may move above it.
+// 32 columns (two accumulators) at once
+__device__ __forceinline__ void tc_ld32_issue(uint32_t taddr, uint32_t r[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr)
+                 : "memory");
 }
-// The same in two steps, so that the load of the next accumulator can be in flight during the math on
-// this one.  The wait names the registers as in/out operands: no read of them may move above it.
-__device__ __forceinline__ void tc_ld16_issue(uint32_t taddr, uint32_t r[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tc_ld16_wait(uint32_t r[16]) {
+__device__ __forceinline__ void tc_ld32_wait(uint32_t r[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;"
-                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
-                   "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
                  :
                  : "memory");
 }
@@ -155,6 +142,11 @@ __device__ __forceinline__ void st_release(int* p, int v) {
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
 // Bounded wait for a generation stamp written by another CTA of this launch.
 __device__ __forceinline__ bool wait_stamp(const int* flag, int stamp, volatile int* abort_flag) {
+#pragma unroll 1
+    for (int i = 0; i < 16; ++i) {  // the global timer is slow to read: only once the wait is clearly long
+        if (ld_acquire(flag) == stamp) return true;
+        __nanosleep(32);
+    }
     const uint64_t t0 = globaltimer_ns();
     for (uint32_t i = 0;; ++i) {
         if (ld_acquire(flag) == stamp) return true;
@@ -259,20 +251,17 @@ __device__ __forceinline__ void tc_finish_up(const TcParams& p, const mono_gemv_
     }
 }
 
-__device__ unsigned long long g_tc_trace[148 * 8];
-__device__ unsigned long long g_tc_seg[4 * 96];  // CTA 0: per segment [wait-done, tiles-issued, epilogue-start, epilogue-done]
-#define TC_TRACE(i, v) g_tc_trace[(blockIdx.x % 148) * 8 + (i)] = (v)
 
 __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_constant__ TcParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* ring = smem;
-    float* sc_ring = reinterpret_cast<float*>(smem + (size_t)p.stages * p.stage_bytes);  // [kTcScSlots][kTcScRows][32]
+    float* sc_ring = reinterpret_cast<float*>(smem + (size_t)kTcMaxStages * p.stage_bytes);  // [kTcScSlots][kTcScRows][32]
     uint64_t* bars = reinterpret_cast<uint64_t*>(sc_ring + kTcScSlots * kTcScRows * kTcMaxSegTiles);
     uint64_t* full = bars;
     uint64_t* acc_full = full + kTcMaxStages;
-    uint64_t* acc_empty = acc_full + kTcAcc;
-    uint64_t* sc_full = acc_empty + kTcAcc;
+    uint64_t* acc_empty = acc_full + kTcMaxStages;
+    uint64_t* sc_full = acc_empty + kTcMaxStages;
     uint64_t* sc_empty = sc_full + kTcScSlots;
     uint64_t* mail_full = sc_empty + kTcScSlots;  // epilogue -> finisher: an up/gate task's outputs are stored
     uint64_t* mail_free = mail_full + 2;
@@ -281,10 +270,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
     __shared__ uint32_t tmem_base_s;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // hot fields in registers: every inline asm with a memory clobber would make the compiler read them again
+    const int rows = p.a.rows, stage_bytes = p.stage_bytes;
     if (tid == 0) {
         abort_flag = guard_failed(p.a.guard) ? 1 : 0;
-        for (int i = 0; i < p.stages; ++i) mbar_init(&full[i], 1);
-        for (int i = 0; i < kTcAcc; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
+        for (int i = 0; i < kTcMaxStages; ++i) mbar_init(&full[i], 1);
+        for (int i = 0; i < kTcMaxStages; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
         for (int i = 0; i < kTcScSlots; ++i) { mbar_init(&sc_full[i], 32); mbar_init(&sc_empty[i], 4); }
         for (int i = 0; i < 2; ++i) { mbar_init(&mail_full[i], 128); mbar_init(&mail_free[i], 1); }
         mbar_init(fin_bar, 128);
@@ -304,15 +295,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
             const int nrb = tc_nrb(j0);
             const TcSeg s = tc_make_seg(j0, blockIdx.x % nrb, blockIdx.x / nrb, 0);
             const CUtensorMap* wmap = reinterpret_cast<const CUtensorMap*>(&j0.tmap);
-            for (int t = 0; t < min(s.nt, p.stages); ++t) tma_prefetch_3d(wmap, (s.t0 + t) * 128, s.row0, s.c2);
+            for (int t = 0; t < min(s.nt, kTcMaxStages * kTcUnit); ++t) tma_prefetch_3d(wmap, (s.t0 + t) * 128, s.row0, s.c2);
         }
     }
     pdl_wait();
     // chained jobs stamp their per-slot "activations ready" words with this launch's generation
     const int stamp = p.a.gen ? *reinterpret_cast<const volatile int*>(p.a.gen) + 1 : 1;
-    const unsigned long long t_start = globaltimer_ns();
-    if (tid == 0) { TC_TRACE(0, t_start); TC_TRACE(1, 0ull); TC_TRACE(2, 0ull); TC_TRACE(5, 0ull); }
-    unsigned long long t_wait = 0;
 
     int cnt[MONO_GEMV_MAX_JOBS], nexp[MONO_GEMV_MAX_JOBS], total = 0;
 #pragma unroll
@@ -331,6 +319,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
         }
         total += cnt[j];
     }
+    // the step's expert lists in shared memory: a global load per segment would put an L2 round trip on
+    // every role's path (a down segment is only two tiles long)
+    __shared__ int s_elist[MONO_GEMV_MAX_JOBS][kTcListCache];
+    for (int j = 0; j < p.a.njobs; ++j)
+        if (p.a.job[j].mode != MONO_JOB_DENSE)
+            for (int i = tid; i < min(nexp[j], kTcListCache); i += kTcThreads) s_elist[j][i] = p.a.job[j].expert_list[i];
+    __syncthreads();
     volatile int* abortp = &abort_flag;
 
 // every role walks the same (task, segment, tile) sequence
@@ -339,6 +334,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
         int j = 0, local = task;                                                                                \
         while (local >= cnt[j]) { local -= cnt[j]; ++j; }                                                       \
         const mono_gemv_job& jb = p.a.job[j];                                                                   \
+        const int planes = jb.planes;                                                                           \
+        (void)planes;                                                                                           \
         const int nrb = tc_nrb(jb);                                                                             \
         int u = 0, nseg = 1;                                                                                    \
         if (jb.mode == MONO_JOB_EXPERT_UP) { u = local / (nrb * jb.nsplit); local -= u * nrb * jb.nsplit; }     \
@@ -348,7 +345,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
         TASK_BEGIN                                                                                              \
         for (int sgi = 0; sgi < nseg && !*abortp; ++sgi) {                                                      \
             if (jb.mode == MONO_JOB_EXPERT_DOWN) u = ks + sgi * jb.nsplit;                                      \
-            const TcSeg s = tc_make_seg(jb, rb, ks, u);                                                         \
+            const TcSeg s = tc_make_seg(jb, rb, ks, u, s_elist[j]);                                             \
             __VA_ARGS__                                                                                         \
         }                                                                                                       \
         TASK_END                                                                                                \
@@ -358,7 +355,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
         // ------------------------------------------------------------ producer: scales by cp.async, tiles by TMA
         int stage = 0, slot = 0;
         uint32_t phase = 0, sphase = 0, ready_mask = 0;
-        int nseg_seen = 0;
 #define TASK_BEGIN
 #define TASK_END
         TC_FOR_EACH_SEGMENT({
@@ -376,97 +372,89 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
                         // pull the whole task's weight tiles towards L2 while the up/gate jobs finish
                         const CUtensorMap* wmap = reinterpret_cast<const CUtensorMap*>(&jb.tmap);
                         for (int sg2 = 0; sg2 < nseg; ++sg2) {
-                            const TcSeg s2 = tc_make_seg(jb, rb, ks, down ? ks + sg2 * jb.nsplit : u);
+                            const TcSeg s2 = tc_make_seg(jb, rb, ks, down ? ks + sg2 * jb.nsplit : u, s_elist[j]);
                             for (int t = 0; t < s2.nt; ++t) tma_prefetch_3d(wmap, (s2.t0 + t) * 128, s2.row0, s2.c2);
                         }
                     }
                 }
                 if (sgi >= 32 || !((ready_mask >> sgi) & 1u)) {
                     if (lane == 0) {
-                        const unsigned long long t0 = globaltimer_ns();
-                        if (t_wait == 0) TC_TRACE(1, t0 - t_start);
                         ok = wait_stamp(jb.ready + (down ? u : 0), stamp, abortp) ? 1 : 0;
-                        t_wait += globaltimer_ns() - t0;
-                        TC_TRACE(2, t_wait);
                     }
                     ok = __shfl_sync(0xffffffffu, ok, 0);
                     if (!ok) break;
                 }
                 // (the writer ordered its stores against the async proxy before it released the stamp)
             }
-            if (lane == 0 && blockIdx.x == 0 && nseg_seen < 96) g_tc_seg[0 * 96 + nseg_seen] = globaltimer_ns() - t_start;
             if (lane == 0) ok = mbar_wait(&sc_empty[slot], sphase ^ 1, abortp) ? 1 : 0;
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             float* sl = sc_ring + (size_t)slot * kTcScRows * kTcMaxSegTiles;
-            for (int i = lane; i < p.a.rows * s.nt; i += 32) {
+            for (int i = lane; i < rows * s.nt; i += 32) {
                 const int c = i / s.nt, t = i - c * s.nt;
                 cp_async4(&sl[c * kTcMaxSegTiles + t], s.asc + (size_t)c * jb.ascale_ld + t);
             }
             if (lane < s.nt) cp_async4(&sl[16 * kTcMaxSegTiles + lane], s.wsc + lane);
-            if (s.coef && lane < p.a.rows) cp_async4(&sl[17 * kTcMaxSegTiles + lane], s.coef + lane);
+            if (s.coef && lane < rows) cp_async4(&sl[17 * kTcMaxSegTiles + lane], s.coef + lane);
             cp_async_arrive(&sc_full[slot]);
             if (++slot == kTcScSlots) { slot = 0; sphase ^= 1; }
             if (lane == 0) {
                 const CUtensorMap* wmap = reinterpret_cast<const CUtensorMap*>(&jb.tmap);
                 const CUtensorMap* amap = reinterpret_cast<const CUtensorMap*>(&jb.act_tmap);
-                for (int t = 0; t < s.nt; ++t) {
-                    if (!mbar_wait(&acc_full[stage], phase ^ 1, abortp)) break;  // the MMAs of the stage's last tile are done
-                    uint8_t* st = ring + (size_t)stage * p.stage_bytes;
-                    mbar_expect_tx(&full[stage], kTcABytes + jb.planes * kTcBBytes);
-                    tma_load_3d(st, wmap, (s.t0 + t) * 128, s.row0, s.c2, &full[stage]);
-                    for (int pl = 0; pl < jb.planes; ++pl)
-                        tma_load_3d(st + kTcABytes + pl * kTcBBytes, amap, (s.t0 + t) * 128, 0, s.aset * jb.planes + pl, &full[stage]);
-                    if (++stage == p.stages) { stage = 0; phase ^= 1; }
+                for (int t = 0; t < s.nt; t += kTcUnit) {
+                    const int n2 = min(kTcUnit, s.nt - t);
+                    if (!mbar_wait(&acc_full[stage], phase ^ 1, abortp)) break;  // the MMAs of the stage's last unit are done
+                    uint8_t* st = ring + (size_t)stage * stage_bytes;
+                    mbar_expect_tx(&full[stage], n2 * (kTcABytes + planes * kTcBBytes));
+                    for (int i = 0; i < n2; ++i) {
+                        tma_load_3d(st + i * kTcABytes, wmap, (s.t0 + t + i) * 128, s.row0, s.c2, &full[stage]);
+                        for (int pl = 0; pl < planes; ++pl)
+                            tma_load_3d(st + kTcUnit * kTcABytes + (i * planes + pl) * kTcBBytes, amap, (s.t0 + t + i) * 128, 0,
+                                        s.aset * planes + pl, &full[stage]);
+                    }
+                    if (++stage == kTcMaxStages) { stage = 0; phase ^= 1; }
                 }
             }
-            if (lane == 0 && blockIdx.x == 0 && nseg_seen < 96) g_tc_seg[1 * 96 + nseg_seen] = globaltimer_ns() - t_start;
-            ++nseg_seen;
             __syncwarp();
         })
 #undef TASK_BEGIN
 #undef TASK_END
         asm volatile("cp.async.wait_all;" ::: "memory");
-        if (lane == 0) TC_TRACE(3, globaltimer_ns() - t_start);
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0, g = 0;
-            long long cw_full = 0, cw_acc = 0, call0 = clock64();
 #define TASK_BEGIN
 #define TASK_END
             TC_FOR_EACH_SEGMENT({
-                for (int t = 0; t < s.nt; ++t) {
-                    const uint32_t acc = g % kTcAcc, aphase = (g / kTcAcc) & 1;
-                    const long long w0 = clock64();
+                for (int t = 0; t < s.nt; t += kTcUnit) {
+                    const int n2 = min(kTcUnit, s.nt - t);
                     if (!mbar_wait(&full[stage], phase, abortp)) break;
-                    const long long w1 = clock64();
-                    if (!mbar_wait(&acc_empty[acc], aphase ^ 1, abortp)) break;
-                    const long long w2 = clock64();
-                    cw_full += w1 - w0; cw_acc += w2 - w1;
+                    if (!mbar_wait(&acc_empty[stage], phase ^ 1, abortp)) break;
                     tc_fence_after();
-                    const uint32_t sa = smem_u32(ring + (size_t)stage * p.stage_bytes);
-                    const uint64_t adesc = tc_desc_sw128(sa);
-                    uint32_t accumulate = 0;
-                    for (int pl = 0; pl < jb.planes; ++pl) {
-                        const uint64_t bdesc = tc_desc_sw128(sa + kTcABytes + pl * kTcBBytes);
+                    const uint32_t sa = smem_u32(ring + (size_t)stage * stage_bytes);
+                    for (int i = 0; i < n2; ++i) {
+                        const uint64_t adesc = tc_desc_sw128(sa + i * kTcABytes);
+                        uint32_t accumulate = 0;
+                        for (int pl = 0; pl < planes; ++pl) {
+                            const uint64_t bdesc = tc_desc_sw128(sa + kTcUnit * kTcABytes + (i * planes + pl) * kTcBBytes);
 #pragma unroll
-                        for (int k = 0; k < 4; ++k) {  // 32 bytes of K per MMA: the start address moves by 32 B
-                            tc_mma_f8(tmem_base + acc * 16, adesc + 2 * k, bdesc + 2 * k, kTcIdesc, accumulate);
-                            accumulate = 1;
+                            for (int k = 0; k < 4; ++k) {  // 32 bytes of K per MMA: the start address moves by 32 B
+                                tc_mma_f8(tmem_base + stage * (16 * kTcUnit) + i * 16, adesc + 2 * k, bdesc + 2 * k, kTcIdesc, accumulate);
+                                accumulate = 1;
+                            }
                         }
                     }
-                    // one commit serves both: the accumulator is complete (epilogue) and the stage's shared
-                    // memory has been read (producer); stage s and accumulator s always go together
-                    tc_commit(&acc_full[acc]);
-                    ++g;
-                    if (++stage == p.stages) { stage = 0; phase ^= 1; }
+                    // one commit serves both: the accumulators are complete (epilogue) and the stage's shared
+                    // memory has been read (producer); stage s and accumulator pair s always go together
+                    tc_commit(&acc_full[stage]);
+                    g += n2;
+                    if (++stage == kTcMaxStages) { stage = 0; phase ^= 1; }
                 }
             })
 #undef TASK_BEGIN
 #undef TASK_END
-            if (blockIdx.x == 0) { g_tc_seg[90] = cw_full; g_tc_seg[91] = cw_acc; g_tc_seg[92] = clock64() - call0; g_tc_seg[93] = g; }
         }
     } else if (warp < 6) {
         // ------------------------------------------------------------ epilogue (TMEM lanes 32 * (warp % 4) ..)
@@ -475,12 +463,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
         uint32_t g = 0, sphase = 0;
         int slot = 0;
         uint32_t nfeed = 0;
-        int nseg_seen = 0;
         const uint32_t tmem_lane = tmem_base + ((uint32_t)(q * 32) << 16);
-        uint32_t dn[16];  // raw registers of the accumulator load in flight
+        uint32_t dn[16 * kTcUnit];  // raw registers of the accumulator load in flight
+        int stage = 0;
+        uint32_t phase = 0;
         bool have_next = false;
-        long long ce_wait = 0, ce_all0 = clock64();
-        int ce_miss = 0;
         float total_acc[kMaxRows];
 #define TASK_BEGIN \
         _Pragma("unroll") for (int c = 0; c < kMaxRows; ++c) total_acc[c] = 0.f;
@@ -491,69 +478,65 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
             float* out = jb.out + (size_t)((jb.mode == MONO_JOB_EXPERT_UP ? u_up * jb.nsplit : 0) + ks) * jb.out_split_stride; \
             if (row_in_mat < jb.n_rows) {                                                                     \
                 _Pragma("unroll") for (int c = 0; c < kMaxRows; ++c)                                          \
-                    if (c < p.a.rows) out[(size_t)c * jb.out_ld + out_row] = total_acc[c];                    \
+                    if (c < rows) out[(size_t)c * jb.out_ld + out_row] = total_acc[c];                    \
             }                                                                                                 \
             if (jb.feeds_job > 0) {                                                                           \
                 const uint32_t k = nfeed & 1;                                                                 \
                 if (mbar_wait(&mail_free[k], ((nfeed >> 1) & 1) ^ 1, abortp)) mbar_arrive(&mail_full[k]);     \
-                if (tid == 64) TC_TRACE(7, globaltimer_ns() - t_start);                                       \
                 ++nfeed;                                                                                      \
             }                                                                                                 \
         }
         TC_FOR_EACH_SEGMENT({
-            if (tid == 64 && blockIdx.x == 0 && nseg_seen < 96) g_tc_seg[2 * 96 + nseg_seen] = globaltimer_ns() - t_start;
             if (!mbar_wait(&sc_full[slot], sphase, abortp)) break;
             const float* sl = sc_ring + (size_t)slot * kTcScRows * kTcMaxSegTiles;
             float seg_acc[kMaxRows];
 #pragma unroll
             for (int c = 0; c < kMaxRows; ++c) seg_acc[c] = 0.f;
-            for (int t = 0; t < s.nt; ++t) {
-                const uint32_t acc = g % kTcAcc, aphase = (g / kTcAcc) & 1;
+            for (int t = 0; t < s.nt; t += kTcUnit) {
+                const int n2 = min(kTcUnit, s.nt - t);
                 if (!have_next) {
-                    const long long e0 = clock64();
-                    if (!mbar_wait(&acc_full[acc], aphase, abortp)) break;
-                    ce_wait += clock64() - e0;
-                    ++ce_miss;
+                    if (!mbar_wait(&acc_full[stage], phase, abortp)) break;
                     tc_fence_after();
-                    tc_ld16_issue(tmem_lane + acc * 16, dn);
+                    tc_ld32_issue(tmem_lane + stage * (16 * kTcUnit), dn);
                 }
-                tc_ld16_wait(dn);
-                float d[16];
+                tc_ld32_wait(dn);
+                float d[16 * kTcUnit];
 #pragma unroll
-                for (int c = 0; c < 16; ++c) d[c] = __uint_as_float(dn[c]);
+                for (int c = 0; c < 16 * kTcUnit; ++c) d[c] = __uint_as_float(dn[c]);
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&acc_empty[acc]);
+                if (lane == 0) mbar_arrive(&acc_empty[stage]);
+                if (++stage == kTcMaxStages) { stage = 0; phase ^= 1; }
                 {
-                    // if the next accumulator is complete already, start its load before the math on this one
-                    const uint32_t g1 = g + 1, acc1 = g1 % kTcAcc;
-                    int h = lane == 0 ? (mbar_try_wait(&acc_full[acc1], (g1 / kTcAcc) & 1) ? 1 : 0) : 0;
+                    // if the next unit is complete already, start its load before the math on this one
+                    int h = lane == 0 ? (mbar_try_wait(&acc_full[stage], phase) ? 1 : 0) : 0;
                     have_next = __shfl_sync(0xffffffffu, h, 0) != 0;
                     if (have_next) {
                         tc_fence_after();
-                        tc_ld16_issue(tmem_lane + acc1 * 16, dn);
+                        tc_ld32_issue(tmem_lane + stage * (16 * kTcUnit), dn);
                     }
                 }
-                const float ws = sl[16 * kTcMaxSegTiles + t];
 #pragma unroll
-                for (int c = 0; c < kMaxRows; ++c)
-                    if (c < p.a.rows) seg_acc[c] += d[c] * (ws * sl[c * kTcMaxSegTiles + t]);
-                ++g;
+                for (int i = 0; i < kTcUnit; ++i) {
+                    if (i < n2) {
+                        const float ws = sl[16 * kTcMaxSegTiles + t + i];
+#pragma unroll
+                        for (int c = 0; c < kMaxRows; ++c)
+                            if (c < rows) seg_acc[c] += d[i * 16 + c] * (ws * sl[c * kTcMaxSegTiles + t + i]);
+                    }
+                }
+                g += n2;
             }
 #pragma unroll
             for (int c = 0; c < kMaxRows; ++c)
-                if (c < p.a.rows) total_acc[c] += seg_acc[c] * (s.coef ? sl[17 * kTcMaxSegTiles + c] : 1.f);
+                if (c < rows) total_acc[c] += seg_acc[c] * (s.coef ? sl[17 * kTcMaxSegTiles + c] : 1.f);
             __syncwarp();
             if (lane == 0) mbar_arrive(&sc_empty[slot]);
-            if (tid == 64 && blockIdx.x == 0 && nseg_seen < 96) g_tc_seg[3 * 96 + nseg_seen] = globaltimer_ns() - t_start;
-            ++nseg_seen;
             if (++slot == kTcScSlots) { slot = 0; sphase ^= 1; }
         })
 #undef TASK_BEGIN
 #undef TASK_END
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");  // nothing in flight when TMEM goes (abort paths)
-        if (blockIdx.x == 0 && tid == 64) { g_tc_seg[96 + 90] = ce_wait; g_tc_seg[96 + 91] = clock64() - ce_all0; g_tc_seg[96 + 92] = ce_miss; }
-        if (tid == 64) TC_TRACE(4, globaltimer_ns() - t_start);
     }
     if (warp >= 6) {
         const int ft = tid - 192;
@@ -565,10 +548,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
         if (jb.feeds_job > 0 && !*abortp) {                                                                   \
             const uint32_t k = nfeed & 1;                                                                     \
             if (mbar_wait(&mail_full[k], (nfeed >> 1) & 1, abortp)) {                                         \
-                const unsigned long long tf0 = globaltimer_ns();                                              \
                 tc_finish_up(p, jb, jb.mode == MONO_JOB_EXPERT_UP ? u_up : 0, nrb * jb.nsplit, stamp, ft, &s_last[k], fs); \
-                t_wait += globaltimer_ns() - tf0;                                                             \
-                if (ft == 0) { TC_TRACE(5, t_wait); TC_TRACE(6, globaltimer_ns() - t_start); }              \
                 if (ft == 0) mbar_arrive(&mail_free[k]);                                                    \
             }                                                                                                 \
             ++nfeed;                                                                                          \
@@ -601,15 +581,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
 
 }  // namespace mono
 
-extern "C" int mono_debug_tc_trace(unsigned long long* out) {
-    cudaMemcpyFromSymbol(out + 148 * 8, mono::g_tc_seg, sizeof(unsigned long long) * 4 * 96);
-    return (int)cudaMemcpyFromSymbol(out, mono::g_tc_trace, sizeof(unsigned long long) * 148 * 8);
-}
-
 static int g_mono_gemv_tc = 1;
 extern "C" int mono_set_gemv_tcgen05(int on) {
     const int old = g_mono_gemv_tc;
-    g_mono_gemv_tc = on < 0 ? 0 : on;  // values above 1 also cap the number of pipeline stages
+    g_mono_gemv_tc = on ? 1 : 0;
     return old;
 }
 int mono_gemv_tc_enabled() { return g_mono_gemv_tc; }
@@ -641,12 +616,12 @@ int mono_gemv_tc_launch(const mono_gemv_args* a, long tasks, cudaStream_t st) {
     int planes = 1;
     for (int j = 0; j < a->njobs; ++j) planes = a->job[j].planes > planes ? a->job[j].planes : planes;
     // as many stages as fit: the bytes in flight per SM are what hides the DRAM latency
-    const int kSmemMax = 226 * 1024;  // 227 KB less the static part
+    const int kSmemMax = 224 * 1024;  // 227 KB less the static part (expert lists, flags)
     const size_t fixed = 1024 + (size_t)kTcScSlots * kTcScRows * kTcMaxSegTiles * sizeof(float) + 512;
-    p.stage_bytes = kTcABytes + planes * kTcBBytes;
+    p.stage_bytes = kTcUnit * (kTcABytes + planes * kTcBBytes);
     p.stages = (int)((kSmemMax - fixed) / p.stage_bytes);
     if (p.stages < kTcMaxStages) return MONO_E_ARG;
-    p.stages = kTcMaxStages;  // = kTcAcc: stage s feeds accumulator s
+    p.stages = kTcMaxStages;  // stage s feeds accumulator pair s
     const size_t smem = fixed + (size_t)p.stages * p.stage_bytes;
     static thread_local bool attr_set = false;
     if (!attr_set) {

@@ -76,7 +76,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // limit is generous (2 s): it exists so that no launch can hang a GPU.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    if (mbar_try_wait(bar, parity)) return true;
+    // a try_wait suspends the thread for a hardware-defined interval: a few of them cover the usual wait,
+    // and the (slow) global timer is only read once a wait is clearly long
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = globaltimer_ns();
     for (uint32_t i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
