@@ -429,8 +429,65 @@ int mono_peer_open(const unsigned char handle[MONO_IPC_HANDLE_BYTES], void** out
 int mono_peer_close(void* opened_ptr);
 int mono_peer_free(void* ptr);
 
+/* ---- GQA block-sparse decode attention (minimax_m3/gfx950: pre_attn.py:8-19 head norms,
+ * RoPE and cache insert; index_score.py:1-12 block scores; post_attn.py:466-592 and
+ * select.py:1-56 block selection; post_attn.py:706-979 split and merge) -------------
+ * Head dim 128; a block is one 64-token page; 16 blocks are attended.  K and V caches hold
+ * E4M3 bytes of value / scale with the layer's fixed scalar scales, laid out
+ * [page][64][kv_heads][128]; the index cache holds E4M3 index keys [page][64][128].
+ * The four launches share one argument block:
+ *   front   sums the fused-projection partials (q heads | k heads | v heads | index q | index k),
+ *           applies the per-head Gemma RMSNorm (weight 1 + g) and the NeoX rotation of dims
+ *           (i, i + 32), i < 32, writes q / index q as bf16 and inserts K, V and the index key at
+ *           slots[row] (a negative slot inserts nothing);
+ *   score   scores[row][b] = max over block b's causal keys of index_q . index_k, times
+ *           fp32(sm_scale * log2 e);
+ *   select  a context of at most 16 blocks keeps them all in order; otherwise the 16 best by
+ *           (key, block id) descending, the first init_blocks pinned to 1e30 and the last
+ *           local_blocks to 1e29, rank by counting; full blocks in rank order, the tail block last;
+ *   attn    softmax((q . k) k_scale sm_scale) v v_scale over the selected keys: one partial per
+ *           (row, kv head, slot), then a merge. */
+typedef struct mono_gqa_args {
+    int rows, q_heads, kv_heads;
+    const float* qkv; /* [nsum][16][ld] f32 */
+    int nsum, ld;
+    long sum_stride;
+    const void* g_q;  /* bf16 [128] each */
+    const void* g_k;
+    const void* g_iq;
+    const void* g_ik;
+    float eps;
+    const void* cos; /* bf16 [positions][32] */
+    const void* sin;
+    const int64_t* positions; /* [rows]; the row's context is positions[row] + 1 keys */
+    const int64_t* slots;     /* [rows] cache slot = page * 64 + offset, negative = pad row; may be NULL */
+    float k_scale, v_scale;
+    uint8_t* k_cache;
+    uint8_t* v_cache;
+    uint8_t* index_cache;
+    int64_t n_pages;
+    void* q_out;  /* bf16 [16][q_heads][128] */
+    void* iq_out; /* bf16 [16][128] */
+    const int32_t* page_table; /* [rows][pt_ld] page of each block */
+    int pt_ld;
+    float* scores; /* [16][score_ld] */
+    int score_ld;
+    int init_blocks, local_blocks;
+    int32_t* sel_pages;  /* [16][16], -1 = empty slot */
+    int32_t* sel_blocks; /* [16][16] */
+    int32_t* n_ctx;      /* [16] keys attended */
+    float sm_scale;
+    float* scratch; /* mono_gqa_scratch_bytes(rows, q_heads) */
+    void* out;      /* bf16 [16][q_heads * 128] */
+} mono_gqa_args;
+size_t mono_gqa_scratch_bytes(int rows, int q_heads);
+int mono_gqa_front_launch(const mono_gqa_args* a, void* stream);
+int mono_gqa_score_launch(const mono_gqa_args* a, void* stream);
+int mono_gqa_select_launch(const mono_gqa_args* a, void* stream);
+int mono_gqa_attn_launch(const mono_gqa_args* a, void* stream);
+
 /* sizeof() of the argument structs, by index (0 gemv_job, 1 gemv_args, 2 act_prep,
- * 3 route, 4 mid, 5 sparse_mla, 6 reduce, 7 rowdot, ...): lets a binding check its mirror. */
+ * 3 route, 4 mid, 5 sparse_mla, 6 reduce, 7 rowdot, ..., 11 gqa): lets a binding check its mirror. */
 size_t mono_struct_size(int which);
 
 #ifdef __cplusplus

@@ -130,8 +130,20 @@ class IndexArgs(C.Structure):
     ]
 
 
+class GqaArgs(C.Structure):
+    _fields_ = [
+        ("rows", i32), ("q_heads", i32), ("kv_heads", i32), ("qkv", vp), ("nsum", i32), ("ld", i32),
+        ("sum_stride", i64), ("g_q", vp), ("g_k", vp), ("g_iq", vp), ("g_ik", vp), ("eps", f32),
+        ("cos", vp), ("sin", vp), ("positions", vp), ("slots", vp), ("k_scale", f32), ("v_scale", f32),
+        ("k_cache", vp), ("v_cache", vp), ("index_cache", vp), ("n_pages", C.c_int64), ("q_out", vp),
+        ("iq_out", vp), ("page_table", vp), ("pt_ld", i32), ("scores", vp), ("score_ld", i32),
+        ("init_blocks", i32), ("local_blocks", i32), ("sel_pages", vp), ("sel_blocks", vp), ("n_ctx", vp),
+        ("sm_scale", f32), ("scratch", vp), ("out", vp),
+    ]
+
+
 _STRUCTS = [GemvJob, GemvArgs, ActPrepArgs, RouteArgs, MidArgs, SparseMlaArgs, ReduceArgs, RowdotArgs,
-            MlaMidArgs, QPostArgs, IndexArgs]
+            MlaMidArgs, QPostArgs, IndexArgs, GqaArgs]
 
 # every symbol include/mono_b200.h declares: name -> (restype, argtypes)
 SYMBOLS = {
@@ -158,6 +170,11 @@ SYMBOLS = {
     "mono_q_post_launch": (i32, [C.POINTER(QPostArgs), vp]),
     "mono_index_score_launch": (i32, [C.POINTER(IndexArgs), vp]),
     "mono_index_topk_launch": (i32, [C.POINTER(IndexArgs), vp]),
+    "mono_gqa_scratch_bytes": (C.c_size_t, [i32, i32]),
+    "mono_gqa_front_launch": (i32, [C.POINTER(GqaArgs), vp]),
+    "mono_gqa_score_launch": (i32, [C.POINTER(GqaArgs), vp]),
+    "mono_gqa_select_launch": (i32, [C.POINTER(GqaArgs), vp]),
+    "mono_gqa_attn_launch": (i32, [C.POINTER(GqaArgs), vp]),
     "mono_struct_size": (C.c_size_t, [i32]),
     "mono_peer_alloc": (i32, [C.c_size_t, C.POINTER(vp)]),
     "mono_peer_export": (i32, [vp, C.POINTER(C.c_ubyte * 64)]),

@@ -185,6 +185,7 @@ extern "C" size_t mono_struct_size(int which) {
         case 8: return sizeof(mono_mla_mid_args);
         case 9: return sizeof(mono_q_post_args);
         case 10: return sizeof(mono_index_args);
+        case 11: return sizeof(mono_gqa_args);
         default: return 0;
     }
 }

@@ -10,10 +10,13 @@ CUDA-graph capture (``deepseek_v41/gfx950/runner.py:127-132``).
 from __future__ import annotations
 
 import ctypes as C
+import logging
 
 import torch
 
 from . import _lib as L
+
+log = logging.getLogger("sgl_amd_mono_b200")
 
 
 def _stream() -> int:
@@ -160,6 +163,16 @@ class Gemv:
         elif self.wkind == L.W_MXFP4:
             ws = require(wscale, name + ".scale", torch.uint8)
             ws3 = ws if ws.dim() == 3 else ws.unsqueeze(0)
+            if ws3.shape[2] % 8:
+                # a K that ends inside a 256-value tile (TMA zero-fills the weight bytes past it): the
+                # kernel reads eight scale codes per tile, so the rows are padded once with the code of 1.0
+                # (the reference logs its few repacks the same way: glm53/gfx950/weights.py:207-310)
+                padded = torch.full((*ws3.shape[:2], _up(ws3.shape[2], 8)), 127, dtype=torch.uint8, device=ws.device)
+                padded[..., : ws3.shape[2]] = ws3
+                log.info("%s.scale: padded %s -> %s (one-time repack, %d bytes)", name, tuple(ws3.shape),
+                         tuple(padded.shape), padded.numel())
+                ws = ws3 = padded
+                self._keep.append(padded)
             job.wscale_e8, job.wscale_mat_stride, job.wscale_ld = ws.data_ptr(), ws3.shape[1] * ws3.shape[2], ws3.shape[2]
         job.act, job.planes, job.act_plane_stride, job.act_ld = _p(act.planes), act.nplanes, act.plane_stride, act.ld
         L.check(L.load().mono_tmap_encode_box(C.byref(job.act_tmap), act.planes.data_ptr(), act.ld, L.MAX_ROWS,

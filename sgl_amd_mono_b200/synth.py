@@ -188,3 +188,45 @@ def verify_step(cfg: LayerConfig, n_req: int, tokens: int, ctx: int, device="cpu
     page_table = base.page_table[req].contiguous()
     slots = page_table.gather(1, (positions // PAGE).unsqueeze(1)).squeeze(1).long() * PAGE + positions % PAGE
     return Step(positions, slots, page_table, base.kv_pages, base.idx_pages, base.cos, base.sin)
+
+
+# ---------------------------------------------------------------- GQA block-sparse attention
+def gqa_weights(cfg, rank: int = 0, device="cpu", layer: int = 0) -> dict:
+    """One rank's tensors of the GQA attention half (``gqa.GqaConfig``): block-FP8 fused
+    projection q | k | v | index q | index k and o_proj, Gemma head-norm weights near zero,
+    the layer's fixed K / V cache scales."""
+    g = _gen(1000 * layer + 7, device)
+    gs = _gen(1000 * layer + 7 + 101 * (rank + 1), device)
+    h = cfg.hidden
+    w: dict = {"in_norm": _norm(h, g, device)}
+    for k in ("g_q", "g_k", "g_iq", "g_ik"):
+        w[k] = (0.1 * torch.randn(128, generator=g, device=device)).bfloat16()
+    w["qkv"], w["qkv_s"] = quant.random_fp8_block(cfg.qkv_rows, h, gs, device)
+    w["o"], w["o_s"] = quant.random_fp8_block(h, cfg.q_local * 128, gs, device)
+    w["k_scale"], w["v_scale"] = 0.05, 0.04
+    return w
+
+
+def gqa_step(cfg, rows: int, ctx: int, device="cpu", layer: int = 0, ragged: bool = True):
+    """Caches of ``rows`` requests with up to ``ctx`` cached tokens each (random E4M3 bytes, no
+    NaN codes), a shuffled page table, and one decode row per request at its last position."""
+    from .gqa import BLOCK, GqaTables
+
+    g = _gen(1000 * layer + 11, device)
+    blocks = -(-ctx // BLOCK)
+    n_pages = rows * blocks + 1
+    perm = torch.randperm(n_pages - 1, generator=g, device=device).to(torch.int32) + 1  # page 0 stays unused
+    page_table = perm[: rows * blocks].reshape(rows, blocks).contiguous()
+
+    def rnd(*shape):
+        # E4M3 of N(0, 1) / scale-ish values: finite codes only
+        return (torch.randn(*shape, generator=g, device=device) * 8.0).clamp(-440, 440).to(quant.F8).view(torch.uint8)
+
+    k_cache = rnd(n_pages, BLOCK, cfg.kv_local, 128)
+    v_cache = rnd(n_pages, BLOCK, cfg.kv_local, 128)
+    index_cache = (torch.randn(n_pages, BLOCK, 128, generator=g, device=device)).to(quant.F8).view(torch.uint8)
+    lens = [ctx - (17 * r if ragged else 0) for r in range(rows)]
+    positions = torch.tensor([n - 1 for n in lens], dtype=torch.int64, device=device)
+    slots = torch.stack([page_table[r, (lens[r] - 1) // BLOCK].long() * BLOCK + (lens[r] - 1) % BLOCK for r in range(rows)])
+    cos, sin = rope_tables(ctx + 1, device, dim=64, theta=cfg.rope_theta)
+    return GqaTables(positions, slots.contiguous(), page_table, k_cache, v_cache, index_cache, cos, sin)

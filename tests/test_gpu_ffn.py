@@ -17,6 +17,8 @@ from util import assert_close_hidden, assert_rel
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 CFG_TINY_MOE8 = replace(CFG_TINY, name="tiny_moe_fp8", n_heads=0, index_heads=0)
+# an intermediate size that ends inside a 256-value MXFP4 tile (config 4 at TP 4: 1536 / 4 = 384), no shared expert
+CFG_TINY_FFN_384 = replace(CFG_TINY_FFN, name="tiny_ffn_mxfp4_k384", inter=384, shared_fmt="none")
 
 
 def _cpu(w):
@@ -41,7 +43,7 @@ def _run(cfg, rows, seed=0, pad=()):
 
 @pytest.mark.parametrize("cfg,rows", [(CFG_TINY_FFN, 1), (CFG_TINY_FFN, 4), (CFG_TINY_FFN, 11),
                                       (CFG_TINY_MOE8, 1), (CFG_TINY_MOE8, 8), (CFG_TINY_MOE8, 16),
-                                      (CFG_FFN_MXFP4, 4)])
+                                      (CFG_FFN_MXFP4, 4), (CFG_TINY_FFN_384, 5), (CFG_TINY_FFN_384, 16)])
 def test_ffn_block_matches_oracle(cfg, rows):
     ffn, w, x, slots, out = _run(cfg, rows)
     wc = _cpu(w)
