@@ -390,6 +390,118 @@ class LayerWorkload:
         return min(ts) * 1e6 * self.rows, f"1 of {self.rows} rows of this rank's layer share, scaled by rows; best of 2"
 
 
+class GqaLayerWorkload(LayerWorkload):
+    """BASELINE config 4: a GQA block-sparse + MXFP4 MoE layer (hidden 6144, 48 q / 8 kv heads of 128,
+    16 blocks x 64 tokens attended per row over a 65536-token context, FP8 attention projections, 256
+    experts top-8 of intermediate 1536 in MXFP4, sigmoid router), 16 verify rows, one rank's share of
+    TP 4 (or TP = number of GPUs)."""
+
+    kernel = "gemv_kernel<MXFP4> (expert up/gate)"
+
+    def __init__(self, rows=16, ctx=65536):
+        super().__init__(rows, ctx)
+
+    def setup(self, dev, rank, world):
+        from sgl_amd_mono_b200 import ops, synth
+        from sgl_amd_mono_b200.config import LayerConfig
+        from sgl_amd_mono_b200.gqa import CFG_GQA, GqaLayerOp
+
+        tp = getattr(self, "shard_of", 0) or (world if world > 1 else 4)
+        self.gcfg = g = CFG_GQA.with_tp(tp)
+        self.cfg = cfg = LayerConfig(name="cfg4_moe_mxfp4", hidden=g.hidden, n_experts=256, top_k=8, inter=1536, route_scale=1.0,
+                                     expert_fmt="mxfp4", shared_fmt="none", router_dtype="bf16", eps=g.eps, tp=tp)
+        self.name = f"cfg4_gqa_block_sparse_mxfp4_moe_layer_tp{tp}_{self.rows}rows_ctx{self.ctx}" + ("_one_shard" if tp != world else "")
+        self.peer = None
+        if world > 1:
+            import torch.distributed as dist
+            from sgl_amd_mono_b200.common.peer import PeerBuffer
+
+            self.cpu_group = dist.new_group(backend="gloo")
+            self.peer = PeerBuffer(g.hidden, rank, world, self.cpu_group, dev)
+        self.w = {**synth.layer_weights(cfg, rank, dev), **synth.gqa_weights(g, rank, dev)}
+        self.tables = synth.gqa_step(g, self.rows, self.ctx, dev, ragged=False)
+        self.op = GqaLayerOp(g, cfg, self.w, dev, max_ctx=self.ctx, peer=self.peer)
+        self.ops = ops
+        gen = torch.Generator().manual_seed(0)
+        self.h_host = torch.randn(self.rows, g.hidden, generator=gen).bfloat16().pin_memory()
+        self.h = self.h_host.to(dev)
+        self.out_host = torch.empty_like(self.h_host).pin_memory()
+        self._eager()
+        torch.cuda.synchronize()
+        rc, words = ops.guard_read(self.op.guard)
+        if rc != 0:
+            raise RuntimeError(f"guard words after the first step: {words}")
+        self.launches_per_step = 19 + (1 if world > 1 else 0)
+        self.graph = None
+        if os.environ.get("MONO_BENCH_GRAPH", "1") == "1":
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._eager()
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr, stream=s):
+                    self._eager()
+            torch.cuda.current_stream().wait_stream(s)
+            self.graph = gr
+
+    def _eager(self):
+        self.out = self.op.launch(self.h, self.tables)
+
+    def layer_bytes(self):
+        g, c, u = self.gcfg, self.cfg, int(self.op.ffn.n_expert.item())
+        h, il = g.hidden, c.inter_local
+        attn_w = g.qkv_rows * h + h * g.q_local * 128 + c.n_experts * h * 2
+        experts = u * (3 * il * h // 2 + 3 * il * h // 32)
+        kv = self.rows * 16 * 64 * g.kv_local * 128 * 2
+        idx = self.rows * self.ctx * 128
+        return attn_w + experts + kv + idx, u
+
+    def roofline_probe(self):
+        u = int(self.op.ffn.n_expert.item())
+        c = self.cfg
+        return u * (2 * c.inter_local * c.hidden // 2 + 2 * c.inter_local * c.hidden // 32), lambda: self.op.ffn.up.launch(self.rows)
+
+    def config(self):
+        g, c = self.gcfg, self.cfg
+        nbytes, u = self.layer_bytes()
+        return {"workload": self.name, "rows": self.rows, "context": self.ctx, "hidden": g.hidden, "q_heads": g.q_heads,
+                "kv_heads": g.kv_heads, "blocks_attended": 16, "block_tokens": 64, "experts": c.n_experts, "top_k": c.top_k,
+                "inter": c.inter, "tp": c.tp, "distinct_experts": u, "layer_algorithmic_bytes_per_rank": nbytes,
+                "cuda_graph": self.graph is not None, "weights": "fp8_e4m3 attention projections, mxfp4 experts",
+                "l2": "256 MiB buffer written between timed iterations"}
+
+    def cpu_sample(self):
+        from oracle import gqa as OG
+        from oracle import layers as OL
+
+        class Lazy:
+            def __init__(self, v):
+                self.v, self.c = v, {}
+
+            def __getitem__(self, e):
+                if e not in self.c:
+                    self.c[e] = self.v[e].cpu()
+                return self.c[e]
+
+        w = {k: (Lazy(v) if k in ("w13", "w13_s", "w2", "w2_s") else (v.cpu() if isinstance(v, torch.Tensor) else v))
+             for k, v in self.w.items()}
+        t = self.tables
+        pt = t.page_table[:1].cpu()
+        pages = pt[0].long()
+        caches = [c[pages.to(c.device)].cpu() for c in (t.k_cache, t.v_cache, t.index_cache)]  # row 0's pages, renumbered
+        local_pt = torch.arange(pages.numel(), dtype=torch.int32)[None]
+        slot = int(t.slots[0])
+        local_slot = torch.tensor([int((pages == slot // 64).nonzero()[0]) * 64 + slot % 64])
+        ts = []
+        for _ in range(2):
+            t0 = time.perf_counter()
+            mid = OG.attention_half(self.gcfg, w, self.h_host[:1], t.positions[:1].cpu(), local_slot, local_pt,
+                                    [c.clone() for c in caches], t.cos.cpu(), t.sin.cpu())
+            OL.ffn_block(self.cfg, [w], mid)
+            ts.append(time.perf_counter() - t0)
+        return min(ts) * 1e6 * self.rows, f"1 of {self.rows} rows of this rank's layer share, scaled by rows; best of 2"
+
+
 class AllReduceWorkload:
     """The in-kernel tensor-parallel all-reduce alone (rows x 7168 bf16 per rank, pushes over
     IPC-mapped peer memory + rank-ordered sum + residual) next to an NCCL all-reduce of the
@@ -649,7 +761,8 @@ class StackWorkload:
         return dt * 1e6 * self.total, f"layer 0, 1 of {self.total} rows, scaled by rows (per layer); one run"
 
 
-WORKLOADS = {"stack": StackWorkload, "sparse_mla": SparseMlaWorkload, "moe": MoeWorkload, "layer": LayerWorkload, "allreduce": AllReduceWorkload}
+WORKLOADS = {"stack": StackWorkload, "sparse_mla": SparseMlaWorkload, "moe": MoeWorkload, "layer": LayerWorkload,
+             "gqa_layer": GqaLayerWorkload, "allreduce": AllReduceWorkload}
 DEFAULT_WORKLOAD = "layer"
 
 
@@ -689,7 +802,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=os.environ.get("MONO_BENCH_WORKLOAD", DEFAULT_WORKLOAD), choices=sorted(WORKLOADS))
-    ap.add_argument("--rows", type=int, default=8)
+    ap.add_argument("--rows", type=int, default=0, help="rows of the step (default: 8; 16 for gqa_layer)")
     ap.add_argument("--load-seconds", type=float, default=0.6, help="time under load before the timed steps")
     ap.add_argument("--shard-of", type=int, default=0, help="run one rank's share of TP = N on each GPU without peers")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -712,7 +825,7 @@ def main() -> None:
 
         dist = dist_mod
         dist.init_process_group("nccl", device_id=torch.device(dev))
-    wl = wl_cls(rows=args.rows)
+    wl = wl_cls(rows=args.rows) if args.rows else wl_cls()
     wl.shard_of = args.shard_of
     wl.setup(dev, rank, world)
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)

@@ -158,3 +158,44 @@ def sparse_attention_row(q_bf: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k
 
 def sm_scale_gqa(head_dim: int = HEAD_DIM) -> float:
     return 1.0 / math.sqrt(head_dim)
+
+
+def attention_half(cfg, w: dict, x: torch.Tensor, positions, slots, page_table, caches, cos, sin) -> torch.Tensor:
+    """One rank's attention half of a layer for ``x`` [rows, hidden] bf16 (``pre_attn.py:8-19`` then
+    ``post_attn.py:466-1003``): input RMSNorm, fused projection, head norms + RoPE, cache insert
+    (``caches`` = [k, v, index] uint8 tensors, modified in place), block scores, selection,
+    attention, o_proj, residual.  Single rank: the all-reduce is the identity.  bf16 [rows, hidden]."""
+    from . import stages as S
+
+    k_cache, v_cache, index_cache = caches
+    nq, nk = cfg.q_local, cfg.kv_local
+    G = nq // nk
+    xn = S.rmsnorm(x, w["in_norm"], cfg.eps)
+    qkv = S.gemv_fp8_block(xn, w["qkv"], w["qkv_s"]).reshape(x.shape[0], -1, HEAD_DIM)
+    attn = torch.zeros(x.shape[0], nq * HEAD_DIM)
+    for r in range(x.shape[0]):
+        pos, slot = int(positions[r]), int(slots[r])
+        if slot < 0:
+            continue
+        c, s = cos[pos], sin[pos]
+        q = torch.stack([head_norm_rope(qkv[r, h], w["g_q"], c, s, cfg.eps) for h in range(nq)])
+        iq = head_norm_rope(qkv[r, nq + 2 * nk], w["g_iq"], c, s, cfg.eps)
+        page, off = slot // BLOCK, slot % BLOCK
+        for h in range(nk):
+            k_cache[page, off, h] = fp8_scaled_bytes(head_norm_rope(qkv[r, nq + h], w["g_k"], c, s, cfg.eps), w["k_scale"])
+            v_cache[page, off, h] = fp8_scaled_bytes(Q.bf(qkv[r, nq + nk + h]), w["v_scale"])
+        index_cache[page, off] = Q.e4m3_bytes(head_norm_rope(qkv[r, nq + 2 * nk + 1], w["g_ik"], c, s, cfg.eps))
+        seq = pos + 1
+        n_blk = (seq + BLOCK - 1) // BLOCK
+        pt = page_table[r].long()
+        scores = block_scores(iq, Q.e4m3_from_bytes(index_cache[pt[:n_blk]].reshape(-1, HEAD_DIM)), seq, cfg.sm_scale)
+        blocks, n_ctx = select_blocks(scores, seq, cfg.init_blocks, cfg.local_blocks)
+        for h in range(nk):
+            kk = Q.e4m3_from_bytes(k_cache[pt[blocks], :, h].reshape(-1, HEAD_DIM))
+            vv = Q.e4m3_from_bytes(v_cache[pt[blocks], :, h].reshape(-1, HEAD_DIM))
+            o = sparse_attention_row(q[h * G : (h + 1) * G], kk, vv, w["k_scale"], w["v_scale"], n_ctx, cfg.sm_scale)
+            attn[r, h * G * HEAD_DIM : (h + 1) * G * HEAD_DIM] = o.reshape(-1)
+    o_proj = S.gemv_fp8_block(attn, w["o"], w["o_s"])
+    out = Q.bf(x.float() + Q.bf(o_proj))
+    live = torch.as_tensor(slots) >= 0
+    return torch.where(live[:, None], out, x.float()).bfloat16()

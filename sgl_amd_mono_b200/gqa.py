@@ -179,3 +179,22 @@ class GqaAttentionOp:
         ops.reduce_rows(rows, cfg.hidden, self.o_p, self.ns_o, self.out, residual=residual, slots=t.slots,
                         peer=self.peer, site=self.site, guard=self.guard, deadline_s=self.deadline_s)
         return self.out[:rows]
+
+
+class GqaLayerOp:
+    """One decoder layer: the GQA block-sparse attention half, then the MoE half
+    (reference: ``minimax_m3/gfx950/runner.py`` ``M3MonoRunner``: K1 + K4 per layer)."""
+
+    def __init__(self, cfg: GqaConfig, moe_cfg, w: dict, device, max_ctx: int, peer=None, deadline_s: float = 5.0):
+        from .moe import MoeFfn
+
+        self.cfg, self.moe_cfg = cfg, moe_cfg
+        self.guard = torch.zeros(L.GUARD_WORDS, dtype=torch.int32, device=device)
+        self.attn = GqaAttentionOp(cfg, w, device, max_ctx, peer=peer, guard=self.guard, site=0, deadline_s=deadline_s)
+        self.ffn = MoeFfn(moe_cfg, w, device, peer=peer, guard=self.guard, site=1, deadline_s=deadline_s)
+
+    def launch(self, h: torch.Tensor, t: GqaTables) -> torch.Tensor:
+        if self.attn.peer is not None and self.attn.peer.world > 1:
+            ops.epoch_advance(self.guard)
+        mid = self.attn.launch(h, t)
+        return self.ffn(mid, t.slots)

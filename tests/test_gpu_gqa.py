@@ -109,6 +109,33 @@ def test_attention_half_output_and_replay():
         assert torch.equal(op.launch(x, t), out)
 
 
+def test_layer_is_attention_half_then_moe_half():
+    """The whole layer (BASELINE config 4's shape family at a small size): the MoE half on top of the
+    attention half's output, against the FFN oracle fed that output."""
+    from dataclasses import replace
+
+    from oracle import layers as OL
+    from sgl_amd_mono_b200.config import CFG_TINY_FFN
+    from sgl_amd_mono_b200.gqa import GqaLayerOp
+
+    cfg = CFG_GQA_TINY
+    moe = replace(CFG_TINY_FFN, name="tiny_gqa_moe", hidden=cfg.hidden, inter=384, shared_fmt="none")
+    w = {**synth.layer_weights(moe, 0, DEV), **synth.gqa_weights(cfg, 0, DEV)}
+    t = synth.gqa_step(cfg, 5, 1800, DEV)
+    x = torch.randn(5, cfg.hidden, generator=torch.Generator().manual_seed(3)).bfloat16().to(DEV)
+    op = GqaLayerOp(cfg, moe, w, DEV, max_ctx=1800)
+    out = op.launch(x, t).clone()
+    torch.cuda.synchronize()
+    rc, words = ops.guard_read(op.guard)
+    assert rc == 0, f"guard words {words}"
+    mid = op.attn.out[:5].cpu()
+    wc = {k: (v.cpu() if isinstance(v, torch.Tensor) else v) for k, v in w.items()}
+    ref, det = OL.ffn_block(moe, [wc], mid)
+    assert torch.equal(op.ffn.ids[:5].cpu(), det["ids"]), "a near-tie flipped between the f32 logit sums: pick another seed"
+    assert_close_hidden(out, ref, "layer output", scale=float((ref.float() - mid.float()).abs().max()))
+    assert torch.equal(op.launch(x, t), out)
+
+
 def test_short_context_keeps_every_block_in_order():
     cfg, w, t, x, op, out, _ = _run(2, 64 * 9 + 3)
     for r in range(2):

@@ -82,6 +82,31 @@ def test_block_scores_are_causal_maxima():
     assert torch.equal(OG.block_scores(iq, keys2, 200, 0.1), sc)
 
 
+def test_attention_half_inserts_the_new_token_and_leaves_pad_rows_alone():
+    from sgl_amd_mono_b200 import synth
+    from sgl_amd_mono_b200.gqa import CFG_GQA_TINY as cfg
+
+    w = synth.gqa_weights(cfg, 0, "cpu")
+    t = synth.gqa_step(cfg, 3, 1300, "cpu")
+    t.slots[1] = -1
+    x = torch.randn(3, cfg.hidden, generator=torch.Generator().manual_seed(5)).bfloat16()
+    caches = [t.k_cache.clone(), t.v_cache.clone(), t.index_cache.clone()]
+    out = OG.attention_half(cfg, w, x, t.positions, t.slots, t.page_table, caches, t.cos, t.sin)
+    assert out.shape == x.shape and out.dtype == torch.bfloat16
+    assert torch.equal(out[1], x[1]), "a pad row comes back as its residual"
+    assert not torch.equal(out[0], x[0])
+    for r in (0, 2):
+        page, off = int(t.slots[r]) // 64, int(t.slots[r]) % 64
+        assert not torch.equal(caches[0][page, off], t.k_cache[page, off]), "the new token's K is inserted"
+    changed = (caches[0] != t.k_cache).any(-1).any(-1).sum()
+    assert int(changed) == 2, "nothing but the two live rows' slots is written"
+    # the new token attends to itself: dropping its key changes the output
+    caches2 = [t.k_cache.clone(), t.v_cache.clone(), t.index_cache.clone()]
+    w2 = dict(w, v_scale=w["v_scale"] * 2)
+    out2 = OG.attention_half(cfg, w2, x, t.positions, t.slots, t.page_table, caches2, t.cos, t.sin)
+    assert not torch.equal(out2[0], out[0])
+
+
 def test_attention_row_matches_plain_softmax():
     torch.manual_seed(3)
     q = torch.randn(4, 128).bfloat16().float()

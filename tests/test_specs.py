@@ -74,6 +74,30 @@ def test_the_minimax_dispatcher_picks_by_checkpoint_quantisation():
     assert any("multiples of 256" in r for r in minimax.SPEC.config_disable_reasons(CFG, odd))
 
 
+def test_the_m3_spec_lists_every_reason_and_accepts_the_block_sparse_layout():
+    from sgl_amd_mono_b200.minimax_m3 import spec as m3
+
+    hf = SimpleNamespace(hidden_size=6144, num_attention_heads=48, num_key_value_heads=8, head_dim=128,
+                         scoring_func="sigmoid", sparse_block_size=64, sparse_topk_blocks=16, n_routed_experts=256,
+                         num_experts_per_tok=8, moe_intermediate_size=1536, rms_norm_eps=1e-6,
+                         quantization_config=dict(quant_method="mxfp4"))
+    cfg4 = SimpleNamespace(page_size=64, speculative_algorithm=None, tp_size=4)
+    assert m3.SPEC.config_disable_reasons(cfg4, hf) == []
+    g = m3.gqa_config(hf, 4)
+    assert (g.q_local, g.kv_local, g.qkv_rows) == (12, 2, 18 * 128)
+    assert m3.moe_config(hf, 4).inter_local == 384 and m3.moe_config(hf, 4).expert_fmt == "mxfp4"
+    bad = SimpleNamespace(**{**vars(hf), "sparse_block_size": 128, "num_key_value_heads": 6})
+    text = "\n".join(m3.SPEC.config_disable_reasons(SimpleNamespace(page_size=16, speculative_algorithm="NGRAM", tp_size=4), bad))
+    for piece in ("sparse_block_size", "--page-size 16", "whole kv heads", "NGRAM"):
+        assert piece in text, piece
+    # loaded tensors: every mismatch is reported, by layer and name
+    layer = SimpleNamespace(weights={"in_norm": torch.zeros(6144, dtype=torch.bfloat16), "k_scale": 0.05, "v_scale": -1.0})
+    model = SimpleNamespace(layers=[SimpleNamespace(weights=None), layer], tp_size=4)
+    reasons = m3.SPEC.model_disable_reasons(model, hf, [])
+    assert any("layer 1: qkv is missing" in r for r in reasons) and any("v_scale" in r for r in reasons)
+    assert not any("in_norm" in r or "k_scale" in r for r in reasons)
+
+
 def test_step_tables_are_built_once_a_step_with_pads_and_clamped_positions():
     plan = registry.Plan(registry.ShapeKey("target_verify", batch_size=1, tokens_per_request=4))
     assert plan.key.rows == 4
