@@ -113,6 +113,35 @@ def time_steps(fn, steps: int, warmup: int, flush: torch.Tensor | None, sampler=
     return sum(a.elapsed_time(b) for a, b in evs)
 
 
+def count_kernel_launches(fn) -> int:
+    """Kernels of this library that one call of ``fn`` launches, counted at the C ABI (the entry points
+    that launch two kernels count twice)."""
+    from sgl_amd_mono_b200 import _lib as L
+
+    lib, n = L.load(), [0]
+    two = {"mono_sparse_mla_launch", "mono_sparse_mla_launch_noalloc", "mono_gqa_attn_launch"}
+
+    class Proxy:
+        def __getattr__(self, name):
+            f = getattr(lib, name)
+            if not (name.endswith("_launch") or name.endswith("_noalloc")):
+                return f
+
+            def counted(*a):
+                n[0] += 2 if name in two else 1
+                return f(*a)
+
+            return counted
+
+    L._lib = Proxy()
+    try:
+        fn()
+        torch.cuda.synchronize()
+    finally:
+        L._lib = lib
+    return n[0]
+
+
 class _Null:
     def __enter__(self):
         return self
@@ -189,7 +218,7 @@ class MoeWorkload:
     GPUs, 8 decode rows: post-norm, router, shared + routed experts, all-reduce, residual."""
 
     layers_per_step = 1
-    kernel = "gemv_kernel<FP8> (expert up/gate)"
+    kernel = "gemv_tc_kernel (tcgen05 FP8 expert up/gate, timed as its own launch)"
 
     def __init__(self, rows=8):
         self.rows = rows
@@ -267,7 +296,7 @@ class LayerWorkload:
     TP 2/4/8; TP 1 is the same layer unsharded, which fits one GPU."""
 
     layers_per_step = 1
-    kernel = "gemv_kernel<FP8> (expert up/gate)"
+    kernel = "gemv_tc_kernel (tcgen05 FP8 expert up/gate, timed as its own launch)"
 
     def __init__(self, rows=8, ctx=16384):
         self.rows, self.ctx = rows, ctx
@@ -614,7 +643,7 @@ class StackWorkload:
     v 128 are this build's choice (BASELINE leaves them open); there is no indexer, so every
     cached key is attended."""
 
-    kernel = "gemv_kernel<FP8> (expert up/gate, layer 0)"
+    kernel = "gemv_tc_kernel (tcgen05 FP8 expert up/gate of layer 0, timed as its own launch)"
 
     def __init__(self, rows=1, ctx=8192, layers=40, verify=5):
         self.rows, self.ctx, self.n_layers, self.verify = rows, ctx, layers, verify
@@ -778,7 +807,9 @@ def run_reference(args, wl_cls, rank: int) -> None:
     if dev == "cpu":
         print(json.dumps({"impl": "reference", "unavailable": "needs the GPU box to generate the workload's inputs"}))
         return
-    wl.setup(dev, 0, max(args.gpus, 1))
+    # rank 0's share of TP = N, built without peers (the other ranks of a torchrun launch do no work)
+    wl.shard_of = args.shard_of or (args.gpus if args.gpus > 1 else 0)
+    wl.setup(dev, 0, 1)
     vals = []
     for _ in range(max(1, min(args.steps, 3))):
         v, sample = wl.cpu_sample()
@@ -835,6 +866,8 @@ def main() -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
+    if hasattr(wl, "_eager"):
+        wl.launches_per_step = count_kernel_launches(wl._eager)  # every rank runs the same extra step
     barrier()
     sampler = ClockSampler(local)
     sampler.__enter__()
@@ -885,8 +918,9 @@ def main() -> None:
         "vs_baseline": None, "dtype": "fp8_e4m3 weights / bf16 activations, f32 accumulate", "data": "synthetic",
         "config": wl.config(), "clocks": sampler.summary(), "gpu_launches": wl.launches_per_step * args.steps,
         "e2e": {"value": e2e_us, "unit": "us", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "roofline": {"bound": "hbm", "kernel": wl.kernel, **({"layer_achieved_gbs": wl.layer_bytes()[0] / (us_per_layer * 1e-6) / 1e9,
-                     "layer_frac": wl.layer_bytes()[0] / (us_per_layer * 1e-6) / 1e9 / peak} if hasattr(wl, "layer_bytes") else {}), "achieved": achieved, "peak": peak, "unit": "GB/s",
+        # layer_bytes() covers what one timed step reads (one layer, or the whole stack and its tail)
+        "roofline": {"bound": "hbm", "kernel": wl.kernel, **({"layer_achieved_gbs": wl.layer_bytes()[0] / (ms_per_step * 1e-3) / 1e9,
+                     "layer_frac": wl.layer_bytes()[0] / (ms_per_step * 1e-3) / 1e9 / peak} if hasattr(wl, "layer_bytes") else {}), "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "traffic": None, "algorithmic_bytes": nbytes,
                      "kernel_us": probe_ms * 1000.0, "peak_source": peak_src},
     }

@@ -13,17 +13,20 @@
 // them to the stage's "free" barrier and the accumulator's "full" barrier; warps 2..5 own the 128
 // TMEM lanes (one weight row per thread), read a finished accumulator with tcgen05.ld, scale and add.
 #include "mono_common.cuh"
+#include <cstdlib>
 
 extern void mono_set_error(const char* fmt, ...);
 
 namespace mono {
 
 constexpr int kTcThreads = 320;  // TMA, MMA, 4 epilogue warps, 4 finisher warps
-constexpr int kTcUnit = 2;       // k tiles per pipeline unit: one barrier round trip, one commit, one TMEM load for both
-constexpr int kTcMaxStages = 5;  // a stage = a unit's weight tiles + its tiles of each activation plane; one accumulator pair each
+// A pipeline unit is kTcUnit k tiles: one barrier round trip, one commit, one TMEM load for all of them.  A stage
+// holds a unit's weight tiles and its tiles of each activation plane, and feeds its own accumulators.
+constexpr int tc_stages(int unit) { return unit == 2 ? 5 : 8; }
+constexpr int kTcBarStages = 8;  // barrier slots (the larger stage count)
 constexpr int kTcABytes = 128 * 128;
 constexpr int kTcBBytes = 16 * 128;
-constexpr int kTcTmemCols = 256;  // kTcMaxStages accumulator pairs of 2 x 16 columns (allocations are powers of two)
+constexpr int tc_tmem_cols(int unit) { return unit == 2 ? 256 : 128; }  // stages x unit x 16 columns, a power of two
 constexpr int kTcMaxSegTiles = 32;
 constexpr int kTcListCache = 128;  // expert-list entries per job kept in shared memory
 constexpr int kTcScSlots = 4;  // segments whose scales may be in flight
@@ -109,6 +112,27 @@ __device__ __forceinline__ void tc_ld32_wait(uint32_t r[32]) {
                  : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
                  :
                  : "memory");
+}
+// 16 columns (one accumulator)
+__device__ __forceinline__ void tc_ld16_issue(uint32_t taddr, uint32_t r[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_ld16_wait(uint32_t r[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+                 :
+                 : "memory");
+}
+template <int UNIT>
+__device__ __forceinline__ void tc_ld_issue(uint32_t taddr, uint32_t* r) {
+    if (UNIT == 2) tc_ld32_issue(taddr, r); else tc_ld16_issue(taddr, r);
+}
+template <int UNIT>
+__device__ __forceinline__ void tc_ld_wait(uint32_t* r) {
+    if (UNIT == 2) tc_ld32_wait(r); else tc_ld16_wait(r);
 }
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzle:
 // groups of 8 rows are 1024 bytes apart (stride byte offset), the leading offset is unused.
@@ -252,16 +276,18 @@ __device__ __forceinline__ void tc_finish_up(const TcParams& p, const mono_gemv_
 }
 
 
+template <int kTcUnit>
 __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_constant__ TcParams p) {
+    constexpr int kTcMaxStages = tc_stages(kTcUnit), kTcTmemCols = tc_tmem_cols(kTcUnit);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* ring = smem;
     float* sc_ring = reinterpret_cast<float*>(smem + (size_t)kTcMaxStages * p.stage_bytes);  // [kTcScSlots][kTcScRows][32]
     uint64_t* bars = reinterpret_cast<uint64_t*>(sc_ring + kTcScSlots * kTcScRows * kTcMaxSegTiles);
     uint64_t* full = bars;
-    uint64_t* acc_full = full + kTcMaxStages;
-    uint64_t* acc_empty = acc_full + kTcMaxStages;
-    uint64_t* sc_full = acc_empty + kTcMaxStages;
+    uint64_t* acc_full = full + kTcBarStages;
+    uint64_t* acc_empty = acc_full + kTcBarStages;
+    uint64_t* sc_full = acc_empty + kTcBarStages;
     uint64_t* sc_empty = sc_full + kTcScSlots;
     uint64_t* mail_full = sc_empty + kTcScSlots;  // epilogue -> finisher: an up/gate task's outputs are stored
     uint64_t* mail_free = mail_full + 2;
@@ -497,9 +523,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
                 if (!have_next) {
                     if (!mbar_wait(&acc_full[stage], phase, abortp)) break;
                     tc_fence_after();
-                    tc_ld32_issue(tmem_lane + stage * (16 * kTcUnit), dn);
+                    tc_ld_issue<kTcUnit>(tmem_lane + stage * (16 * kTcUnit), dn);
                 }
-                tc_ld32_wait(dn);
+                tc_ld_wait<kTcUnit>(dn);
                 float d[16 * kTcUnit];
 #pragma unroll
                 for (int c = 0; c < 16 * kTcUnit; ++c) d[c] = __uint_as_float(dn[c]);
@@ -513,7 +539,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
                     have_next = __shfl_sync(0xffffffffu, h, 0) != 0;
                     if (have_next) {
                         tc_fence_after();
-                        tc_ld32_issue(tmem_lane + stage * (16 * kTcUnit), dn);
+                        tc_ld_issue<kTcUnit>(tmem_lane + stage * (16 * kTcUnit), dn);
                     }
                 }
 #pragma unroll
@@ -618,20 +644,32 @@ int mono_gemv_tc_launch(const mono_gemv_args* a, long tasks, cudaStream_t st) {
     // as many stages as fit: the bytes in flight per SM are what hides the DRAM latency
     const int kSmemMax = 224 * 1024;  // 227 KB less the static part (expert lists, flags)
     const size_t fixed = 1024 + (size_t)kTcScSlots * kTcScRows * kTcMaxSegTiles * sizeof(float) + 512;
-    p.stage_bytes = kTcUnit * (kTcABytes + planes * kTcBBytes);
+    // two-tile pipeline units pay off when a CTA streams many tiles (expert jobs, large dense matrices: 735 vs
+    // 895 us per config-3 layer at TP 1); short dense launches are quicker with one-tile units and more stages
+    static const int forced_unit = [] { const char* e = getenv("MONO_TC_UNIT"); return e ? (e[0] == '2' ? 2 : 1) : 0; }();
+    long dense_tiles = 0;
+    bool expert = false;
+    for (int j = 0; j < a->njobs; ++j) {
+        const mono_gemv_job& jb = a->job[j];
+        if (jb.mode != MONO_JOB_DENSE) expert = true;
+        else dense_tiles += (long)(jb.rb_per_mat > 0 ? jb.n_mats * jb.rb_per_mat : (jb.n_rows + 127) / 128) * jb.k_tiles;
+    }
+    const int unit = forced_unit ? forced_unit : ((expert || dense_tiles >= 32L * mono_sm_count()) ? 2 : 1);
+    p.stage_bytes = unit * (kTcABytes + planes * kTcBBytes);
     p.stages = (int)((kSmemMax - fixed) / p.stage_bytes);
-    if (p.stages < kTcMaxStages) return MONO_E_ARG;
-    p.stages = kTcMaxStages;  // stage s feeds accumulator pair s
+    if (p.stages < tc_stages(unit)) return MONO_E_ARG;
+    p.stages = tc_stages(unit);  // stage s feeds accumulator set s
     const size_t smem = fixed + (size_t)p.stages * p.stage_bytes;
     static thread_local bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
+        cudaError_t e = cudaFuncSetAttribute(gemv_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }
     int grid = a->max_ctas > 0 ? a->max_ctas : mono_sm_count();
     if (grid > tasks) grid = (int)tasks;
     if (grid < 1) grid = 1;
-    cudaError_t e = launch_k(gemv_tc_kernel, grid, kTcThreads, smem, st, p);
+    cudaError_t e = unit == 2 ? launch_k(gemv_tc_kernel<2>, grid, kTcThreads, smem, st, p) : launch_k(gemv_tc_kernel<1>, grid, kTcThreads, smem, st, p);
     return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }

@@ -105,7 +105,11 @@ class MoeFfn:
         self.out = z(L.MAX_ROWS, h, dt=torch.bfloat16)
         # ---- one launch for up/gate -> SwiGLU -> down (FP8 on the tcgen05 path): the same jobs, chained
         self.chained = None
-        if efmt == "fp8_block" and (not self.has_shared or same) and tc_on and os.environ.get("MONO_MOE_CHAINED", "1") != "0":
+        # (the CTA that finishes an expert's last up/gate task computes the whole activation of that expert:
+        # measured on config 3: faster at TP 8 (256 intermediate values per rank), slower from TP 4 down, where
+        # an expert's activation is 4+ chunks per row and the separate activation launch spreads it better)
+        chain_default = "1" if il <= 256 else "0"
+        if efmt == "fp8_block" and (not self.has_shared or same) and tc_on and os.environ.get("MONO_MOE_CHAINED", chain_default) != "0":
             g = ops.Gemv(L.W_FP8, self.guard)
             first = 0
             if self.has_shared:

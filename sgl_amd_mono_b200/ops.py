@@ -99,6 +99,12 @@ _MAX_SEG_TILES = {L.W_FP8: 16, L.W_BF16: 16, L.W_MXFP4: 8}
 def plan_split(k_tiles: int, row_blocks: int, wkind: int, sms: int = 148, cap: int | None = None):
     """(split_tiles, nsplit): K splits of whole 4-tile groups so that row_blocks x
     nsplit tasks cover the SMs about twice and a segment fits the activation slot."""
+    if cap is None and wkind == L.W_FP8:
+        # the tcgen05 consumer has no activation slot to fit: segments of up to 32 tiles, fewer K splits
+        lib = L.load()
+        tc_on = lib.mono_set_gemv_tcgen05(1)
+        lib.mono_set_gemv_tcgen05(tc_on)
+        cap = 32 if tc_on else None
     cap = cap or _MAX_SEG_TILES[wkind]
     want = max(1, -(-2 * sms // max(row_blocks, 1)))
     split = min(cap, max(4, _up(-(-k_tiles // want), 4)))

@@ -19,6 +19,8 @@ DEV = "cuda:0"
 CFG_TINY_MOE8 = replace(CFG_TINY, name="tiny_moe_fp8", n_heads=0, index_heads=0)
 # an intermediate size that ends inside a 256-value MXFP4 tile (config 4 at TP 4: 1536 / 4 = 384), no shared expert
 CFG_TINY_FFN_384 = replace(CFG_TINY_FFN, name="tiny_ffn_mxfp4_k384", inter=384, shared_fmt="none")
+# narrow experts: up/gate, activation and down run chained inside one launch by default
+CFG_TINY_MOE8_256 = replace(CFG_TINY_MOE8, name="tiny_moe_fp8_chained", inter=256)
 
 
 def _cpu(w):
@@ -43,7 +45,8 @@ def _run(cfg, rows, seed=0, pad=()):
 
 @pytest.mark.parametrize("cfg,rows", [(CFG_TINY_FFN, 1), (CFG_TINY_FFN, 4), (CFG_TINY_FFN, 11),
                                       (CFG_TINY_MOE8, 1), (CFG_TINY_MOE8, 8), (CFG_TINY_MOE8, 16),
-                                      (CFG_FFN_MXFP4, 4), (CFG_TINY_FFN_384, 5), (CFG_TINY_FFN_384, 16)])
+                                      (CFG_FFN_MXFP4, 4), (CFG_TINY_FFN_384, 5), (CFG_TINY_FFN_384, 16),
+                                      (CFG_TINY_MOE8_256, 8), (CFG_TINY_MOE8_256, 16)])
 def test_ffn_block_matches_oracle(cfg, rows):
     ffn, w, x, slots, out = _run(cfg, rows)
     wc = _cpu(w)
@@ -97,8 +100,9 @@ def test_chained_launch_equals_separate_launches(rows, monkeypatch):
     """up/gate -> SwiGLU -> down inside one launch does the arithmetic of the separate launches in the
     same order: activations, scales and the block's output are bit-equal."""
     cfg = CFG_TINY_MOE8
+    monkeypatch.setenv("MONO_MOE_CHAINED", "1")  # the default chains only narrow per-rank experts
     ffn, w, x, slots, out = _run(cfg, rows)
-    assert ffn.chained is not None, "the FP8 block takes the chained launch by default"
+    assert ffn.chained is not None, "an FP8 block on the tcgen05 path can take the chained launch"
     monkeypatch.setenv("MONO_MOE_CHAINED", "0")
     ffn2, _, _, _, out2 = _run(cfg, rows)
     assert ffn2.chained is None
