@@ -22,14 +22,15 @@ namespace mono {
 constexpr int kTcThreads = 320;  // TMA, MMA, 4 epilogue warps, 4 finisher warps
 // A pipeline unit is kTcUnit k tiles: one barrier round trip, one commit, one TMEM load for all of them.  A stage
 // holds a unit's weight tiles and its tiles of each activation plane, and feeds its own accumulators.
-constexpr int tc_stages(int unit) { return unit == 2 ? 5 : 8; }
+constexpr int tc_stages(int unit) { return unit == 4 ? 3 : unit == 2 ? 5 : 8; }
 constexpr int kTcBarStages = 8;  // barrier slots (the larger stage count)
 constexpr int kTcABytes = 128 * 128;
 constexpr int kTcBBytes = 16 * 128;
-constexpr int tc_tmem_cols(int unit) { return unit == 2 ? 256 : 128; }  // stages x unit x 16 columns, a power of two
+constexpr int tc_tmem_cols(int unit) { return unit >= 2 ? 256 : 128; }  // stages x unit x 16 columns, a power of two
 constexpr int kTcMaxSegTiles = 32;
 constexpr int kTcListCache = 128;  // expert-list entries per job kept in shared memory
-constexpr int kTcScSlots = 4;  // segments whose scales may be in flight
+constexpr int kTcScSlotsMax = 4;  // segments whose scales may be in flight
+constexpr int tc_sc_slots(int unit) { return unit == 4 ? 2 : 4; }  // (the four-tile unit needs the room for its stages)
 constexpr int kTcScRows = 18;  // 16 activation-scale rows, the weight scales, the row coefficients
 
 struct TcParams {
@@ -126,13 +127,26 @@ __device__ __forceinline__ void tc_ld16_wait(uint32_t r[16]) {
                  :
                  : "memory");
 }
+// 64 columns (four accumulators)
+__device__ __forceinline__ void tc_ld64_issue(uint32_t taddr, uint32_t r[64]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%64];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+                 : "r"(taddr)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_ld64_wait(uint32_t r[64]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31]), "+r"(r[32]), "+r"(r[33]), "+r"(r[34]), "+r"(r[35]), "+r"(r[36]), "+r"(r[37]), "+r"(r[38]), "+r"(r[39]), "+r"(r[40]), "+r"(r[41]), "+r"(r[42]), "+r"(r[43]), "+r"(r[44]), "+r"(r[45]), "+r"(r[46]), "+r"(r[47]), "+r"(r[48]), "+r"(r[49]), "+r"(r[50]), "+r"(r[51]), "+r"(r[52]), "+r"(r[53]), "+r"(r[54]), "+r"(r[55]), "+r"(r[56]), "+r"(r[57]), "+r"(r[58]), "+r"(r[59]), "+r"(r[60]), "+r"(r[61]), "+r"(r[62]), "+r"(r[63])
+                 :
+                 : "memory");
+}
 template <int UNIT>
 __device__ __forceinline__ void tc_ld_issue(uint32_t taddr, uint32_t* r) {
-    if (UNIT == 2) tc_ld32_issue(taddr, r); else tc_ld16_issue(taddr, r);
+    if (UNIT == 4) tc_ld64_issue(taddr, r); else if (UNIT == 2) tc_ld32_issue(taddr, r); else tc_ld16_issue(taddr, r);
 }
 template <int UNIT>
 __device__ __forceinline__ void tc_ld_wait(uint32_t* r) {
-    if (UNIT == 2) tc_ld32_wait(r); else tc_ld16_wait(r);
+    if (UNIT == 4) tc_ld64_wait(r); else if (UNIT == 2) tc_ld32_wait(r); else tc_ld16_wait(r);
 }
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzle:
 // groups of 8 rows are 1024 bytes apart (stride byte offset), the leading offset is unused.
@@ -278,7 +292,7 @@ __device__ __forceinline__ void tc_finish_up(const TcParams& p, const mono_gemv_
 
 template <int kTcUnit>
 __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_constant__ TcParams p) {
-    constexpr int kTcMaxStages = tc_stages(kTcUnit), kTcTmemCols = tc_tmem_cols(kTcUnit);
+    constexpr int kTcMaxStages = tc_stages(kTcUnit), kTcTmemCols = tc_tmem_cols(kTcUnit), kTcScSlots = tc_sc_slots(kTcUnit);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* ring = smem;
@@ -288,8 +302,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
     uint64_t* acc_full = full + kTcBarStages;
     uint64_t* acc_empty = acc_full + kTcBarStages;
     uint64_t* sc_full = acc_empty + kTcBarStages;
-    uint64_t* sc_empty = sc_full + kTcScSlots;
-    uint64_t* mail_full = sc_empty + kTcScSlots;  // epilogue -> finisher: an up/gate task's outputs are stored
+    uint64_t* sc_empty = sc_full + kTcScSlotsMax;
+    uint64_t* mail_full = sc_empty + kTcScSlotsMax;  // epilogue -> finisher: an up/gate task's outputs are stored
     uint64_t* mail_free = mail_full + 2;
     uint64_t* fin_bar = mail_free + 2;
     __shared__ int abort_flag, s_last[2];
@@ -643,18 +657,27 @@ int mono_gemv_tc_launch(const mono_gemv_args* a, long tasks, cudaStream_t st) {
     for (int j = 0; j < a->njobs; ++j) planes = a->job[j].planes > planes ? a->job[j].planes : planes;
     // as many stages as fit: the bytes in flight per SM are what hides the DRAM latency
     const int kSmemMax = 224 * 1024;  // 227 KB less the static part (expert lists, flags)
-    const size_t fixed = 1024 + (size_t)kTcScSlots * kTcScRows * kTcMaxSegTiles * sizeof(float) + 512;
     // two-tile pipeline units pay off when a CTA streams many tiles (expert jobs, large dense matrices: 735 vs
     // 895 us per config-3 layer at TP 1); short dense launches are quicker with one-tile units and more stages
-    static const int forced_unit = [] { const char* e = getenv("MONO_TC_UNIT"); return e ? (e[0] == '2' ? 2 : 1) : 0; }();
+    static const int forced_unit = [] { const char* e = getenv("MONO_TC_UNIT"); return e ? (e[0] == '4' ? 4 : e[0] == '2' ? 2 : 1) : 0; }();
+    // (four-tile units: 710 us, the up/gate launch at 0.90 of the measured copy bandwidth; they need long K
+    // runs per segment, or a stage is mostly empty)
     long dense_tiles = 0;
     bool expert = false;
+    int min_seg = 1 << 30;
     for (int j = 0; j < a->njobs; ++j) {
         const mono_gemv_job& jb = a->job[j];
-        if (jb.mode != MONO_JOB_DENSE) expert = true;
-        else dense_tiles += (long)(jb.rb_per_mat > 0 ? jb.n_mats * jb.rb_per_mat : (jb.n_rows + 127) / 128) * jb.k_tiles;
+        if (jb.mode != MONO_JOB_DENSE) {
+            expert = true;
+            const int seg = jb.mode == MONO_JOB_EXPERT_DOWN ? jb.k_tiles : (jb.split_tiles < jb.k_tiles ? jb.split_tiles : jb.k_tiles);
+            min_seg = seg < min_seg ? seg : min_seg;
+        } else {
+            dense_tiles += (long)(jb.rb_per_mat > 0 ? jb.n_mats * jb.rb_per_mat : (jb.n_rows + 127) / 128) * jb.k_tiles;
+        }
     }
-    const int unit = forced_unit ? forced_unit : ((expert || dense_tiles >= 32L * mono_sm_count()) ? 2 : 1);
+    int unit = forced_unit ? forced_unit : (expert && min_seg >= 8) ? 4 : (expert || dense_tiles >= 32L * mono_sm_count()) ? 2 : 1;
+    if (unit == 4 && planes != 1) unit = 2;  // four-tile stages fit with one activation plane only
+    const size_t fixed = 1024 + (size_t)tc_sc_slots(unit) * kTcScRows * kTcMaxSegTiles * sizeof(float) + 512;
     p.stage_bytes = unit * (kTcABytes + planes * kTcBBytes);
     p.stages = (int)((kSmemMax - fixed) / p.stage_bytes);
     if (p.stages < tc_stages(unit)) return MONO_E_ARG;
@@ -664,12 +687,15 @@ int mono_gemv_tc_launch(const mono_gemv_args* a, long tasks, cudaStream_t st) {
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(gemv_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }
     int grid = a->max_ctas > 0 ? a->max_ctas : mono_sm_count();
     if (grid > tasks) grid = (int)tasks;
     if (grid < 1) grid = 1;
-    cudaError_t e = unit == 2 ? launch_k(gemv_tc_kernel<2>, grid, kTcThreads, smem, st, p) : launch_k(gemv_tc_kernel<1>, grid, kTcThreads, smem, st, p);
+    cudaError_t e = unit == 4   ? launch_k(gemv_tc_kernel<4>, grid, kTcThreads, smem, st, p)
+                    : unit == 2 ? launch_k(gemv_tc_kernel<2>, grid, kTcThreads, smem, st, p)
+                                : launch_k(gemv_tc_kernel<1>, grid, kTcThreads, smem, st, p);
     return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
