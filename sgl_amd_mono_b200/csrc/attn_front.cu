@@ -300,9 +300,12 @@ extern "C" int mono_mla_mid_launch(const mono_mla_mid_args* a, void* stream) {
 }
 
 extern "C" int mono_q_post_launch(const mono_q_post_args* a, void* stream) {
-    if (!a || a->rows < 1 || a->rows > MONO_MAX_ROWS || a->heads < 1 || !a->qb || !a->kv_b || !a->kv_b_scale || !a->cos ||
-        !a->sin || !a->positions || !a->q_full || (a->index_heads > 0 && (!a->iq || !a->idx_q))) {
-        mono_set_error("mono_q_post_launch: rows 1..16, heads >= 1 and all pointers required");
+    // heads == 0 runs the index queries alone, index_heads == 0 the head part alone: the two halves are
+    // independent and may run on different streams
+    if (!a || a->rows < 1 || a->rows > MONO_MAX_ROWS || a->heads < 0 || a->index_heads < 0 || (a->heads == 0 && a->index_heads == 0) ||
+        !a->cos || !a->sin || !a->positions || (a->heads > 0 && (!a->qb || !a->kv_b || !a->kv_b_scale || !a->q_full)) ||
+        (a->index_heads > 0 && (!a->iq || !a->idx_q))) {
+        mono_set_error("mono_q_post_launch: rows 1..16, heads and / or index_heads > 0 with their pointers required");
         return MONO_E_ARG;
     }
     const int blocks = a->heads * 8 + (a->index_heads > 0 ? a->rows * a->index_heads : 0);

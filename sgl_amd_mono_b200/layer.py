@@ -11,6 +11,8 @@ then the MoE half (``moe.MoeFfn``).
 
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass
 
 import torch
@@ -44,6 +46,11 @@ class MlaLayerOp:
         self.cfg, self.w, self.dev, self.peer, self.layer = cfg, w, device, peer, layer
         self.deadline_s = deadline_s
         self.guard = guard if guard is not None else torch.zeros(L.GUARD_WORDS, dtype=torch.int32, device=device)
+        # the index head weights depend on the normed input only: they run on a side stream, forked after the
+        # input norm; the index queries, scores and top-k follow them there and join before the attention
+        # (a fork / join that a CUDA graph capture records too)
+        self._side = torch.cuda.Stream(device=device) if os.environ.get("MONO_SIDE_STREAM", "1") == "1" else None
+        self._ev_fork, self._ev_join = torch.cuda.Event(), torch.cuda.Event()
         h, hl, ql, ih = cfg.hidden, cfg.heads_local, cfg.q_lora, cfg.index_heads
         R = L.MAX_ROWS
         z = lambda *s, dt=torch.float32: torch.zeros(*s, dtype=dt, device=device)  # noqa: E731
@@ -125,19 +132,41 @@ class MlaLayerOp:
             raise ValueError(f"step.page_table: {step.page_table.shape[1]} pages exceed the built context {self.max_ctx}")
         ops.act_prep(rows, cfg.hidden, self.x, src_bf16=h, gamma=w["input_norm"], eps=cfg.eps, out_bf16=self.xbf)
         self.gA.launch(rows)
-        if ih:
+        if ih and self._side is not None:
+            main = torch.cuda.current_stream()
+            self._ev_fork.record(main)
+            self._side.wait_event(self._ev_fork)
+            with torch.cuda.stream(self._side):
+                ops.rowdot(rows, w["idx_wproj"], self.xbf, self.idx_w, out_scale=(ih**-0.5) * (128**-0.5))
+        elif ih:
             ops.rowdot(rows, w["idx_wproj"], self.xbf, self.idx_w, out_scale=(ih**-0.5) * (128**-0.5))
         ops.mla_mid(rows, cfg.q_lora, self.qkv_p, self.nsA, w, cfg.eps, step.cos, step.sin, step.positions, step.slots,
                     self.qa, step.kv_pages, step.idx_pages, self.kv_out, ik=self.ik_p, ik_nsum=self.nsA,
                     ik_out=self.ik_out if ih else None)
         self.gB.launch(rows)
-        ops.q_post(rows, hl, self.qb_p, self.nsB, w["kv_b"], w["kv_b_s"], step.cos, step.sin, step.positions,
-                   self.q_full, ih, self.iq_p, self.nsB, self.idx_q)
         ia = ops.index_args(rows, max(ih, 1), self.topk, self.idx_q, self.idx_w, step.idx_pages, step.page_table,
                             step.positions, step.slots, self.scores, self.topk_slots, self.topk_pos)
-        if ih:
-            ops.index_score(ia)
-        ops.index_topk(ia)  # rows with at most topk keys keep every key in order
+        if ih and self._side is not None:
+            # index queries -> scores -> top-k on the side stream (behind the head weights already queued
+            # there), the W_UK absorb of the heads on the main one; joined before the attention
+            main = torch.cuda.current_stream()
+            self._ev_fork.record(main)
+            self._side.wait_event(self._ev_fork)
+            with torch.cuda.stream(self._side):
+                ops.q_post(rows, 0, self.qb_p, self.nsB, w["kv_b"], w["kv_b_s"], step.cos, step.sin, step.positions,
+                           self.q_full, ih, self.iq_p, self.nsB, self.idx_q)
+                ops.index_score(ia)
+                ops.index_topk(ia)
+                self._ev_join.record(self._side)
+            ops.q_post(rows, hl, self.qb_p, self.nsB, w["kv_b"], w["kv_b_s"], step.cos, step.sin, step.positions,
+                       self.q_full, 0, None, 0, None)
+            main.wait_event(self._ev_join)
+        else:
+            ops.q_post(rows, hl, self.qb_p, self.nsB, w["kv_b"], w["kv_b_s"], step.cos, step.sin, step.positions,
+                       self.q_full, ih, self.iq_p, self.nsB, self.idx_q)
+            if ih:
+                ops.index_score(ia)
+            ops.index_topk(ia)  # rows with at most topk keys keep every key in order
         lat = self.attn(self.q_full[:rows], step.kv_pages, self.topk_slots)
         ops.act_prep_heads(rows, hl, 512, self.lat, src_bf16=lat)
         self.gUV.launch(rows)
