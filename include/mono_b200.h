@@ -80,6 +80,11 @@ int mono_tmap_encode(mono_tmap_t* out, const void* base, uint64_t inner_bytes, u
  * feed the tcgen05 B operand). */
 int mono_tmap_encode_box(mono_tmap_t* out, const void* base, uint64_t inner_bytes, uint64_t rows, uint64_t outer,
                          uint64_t row_stride_bytes, uint64_t outer_stride_bytes, uint32_t box_rows);
+/* A weight of packed 4-bit elements (two per byte, even index in the low nibble): boxes of 128
+ * elements x 128 rows, which TMA writes to shared memory as 128-byte rows of 16-element groups
+ * padded to 16 bytes (the layout tcgen05.mma kind::f8f6f4 reads E2M1 operands in). */
+int mono_tmap_encode_fp4(mono_tmap_t* out, const void* base, uint64_t inner_elems, uint64_t rows, uint64_t outer,
+                         uint64_t row_stride_bytes, uint64_t outer_stride_bytes);
 
 /* ---- activation staging (glm53/gfx950/kernel.py:1367-1414 RMSNorm staging,
  * :1440-1466 per-128 FP8 / per-32 MXFP8 quantisation) ----------------------------
@@ -90,9 +95,10 @@ int mono_tmap_encode_box(mono_tmap_t* out, const void* base, uint64_t inner_byte
  *                   128: the bf16 activation exactly split for FP8 MMAs
  *   MONO_ACT_MX8    1 plane E4M3, E8M0 code per 32 (kernel.py:1452-1466), values of
  *                   each group of 8 stored as k0 k2 k4 k6 k1 k3 k5 k7 (the order the
- *                   MXFP4 weight nibbles unpack in)
+ *                   MXFP4 weight nibbles unpack in on the warp-MMA consumer)
+ *   MONO_ACT_MX8N   the same values in natural k order (the tcgen05 MXFP4 consumer)
  * Rows >= `rows` of every plane stay zero. */
-enum { MONO_ACT_BF16 = 0, MONO_ACT_A8 = 1, MONO_ACT_HILO = 2, MONO_ACT_MX8 = 3 };
+enum { MONO_ACT_BF16 = 0, MONO_ACT_A8 = 1, MONO_ACT_HILO = 2, MONO_ACT_MX8 = 3, MONO_ACT_MX8N = 4 };
 
 typedef struct mono_act_prep_args {
     int rows, k;
@@ -185,6 +191,12 @@ typedef struct mono_gemv_job {
     int feeds_job;  /* 1 + index of the fed job; 0 = none */
     int32_t* done;  /* [slots] task counters, zero between launches */
     int32_t* ready; /* [slots] generation stamps; also set on the fed job */
+    /* MXFP4 weights on the tcgen05 path: the weight as a tensor of packed 4-bit elements
+     * (mono_tmap_encode_fp4: TMA unpacks 128-element rows into the padded 128-byte rows the MMA
+     * reads) and activations in natural k order (MONO_ACT_MX8N).  Without them an MXFP4 job
+     * runs on the warp-MMA consumer, which needs MONO_ACT_MX8. */
+    mono_tmap_t tmap4;
+    int act_natural; /* 1 = the activation planes are MONO_ACT_MX8N */
 } mono_gemv_job;
 
 typedef struct mono_gemv_args {

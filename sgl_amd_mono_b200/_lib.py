@@ -17,7 +17,7 @@ LIB_PATH = Path(__file__).resolve().parent / "libmono_b200.so"
 MAX_ROWS = 16
 GUARD_WORDS = 16
 ERR_DEADLINE, ERR_PEER, ERR_ARG, GUARD_FLAGS = 3, 4, 5, 8
-ACT_BF16, ACT_A8, ACT_HILO, ACT_MX8 = 0, 1, 2, 3
+ACT_BF16, ACT_A8, ACT_HILO, ACT_MX8, ACT_MX8N = 0, 1, 2, 3, 4
 W_FP8, W_MXFP4, W_BF16 = 0, 1, 2
 JOB_DENSE, JOB_EXPERT_UP, JOB_EXPERT_DOWN = 0, 1, 2
 GEMV_MAX_JOBS = 4
@@ -40,7 +40,9 @@ class GemvJob(C.Structure):
         ("coef", vp), ("expert_list", vp), ("n_expert", vp), ("max_expert", i32),
         ("out", vp), ("out_ld", i32), ("out_split_stride", i64),
         ("feeds_job", i32), ("done", vp), ("ready", vp),
-        ("_tail", C.c_ubyte * 40),  # the struct is 64-byte aligned in C (tensor maps)
+        ("_pad4", C.c_ubyte * 40),  # tensor maps are 64-byte aligned in C
+        ("tmap4", Tmap), ("act_natural", i32),
+        ("_tail", C.c_ubyte * 60),
     ]
 
 
@@ -154,6 +156,7 @@ SYMBOLS = {
     "mono_guard_read": (i32, [vp, C.POINTER(C.c_int32 * 3), vp]),
     "mono_tmap_encode": (i32, [C.POINTER(Tmap), vp, u64, u64, u64, u64, u64]),
     "mono_tmap_encode_box": (i32, [C.POINTER(Tmap), vp, u64, u64, u64, u64, u64, u32]),
+    "mono_tmap_encode_fp4": (i32, [C.POINTER(Tmap), vp, u64, u64, u64, u64, u64]),
     "mono_set_gemv_tcgen05": (i32, [i32]),
     "mono_act_prep_launch": (i32, [C.POINTER(ActPrepArgs), vp]),
     "mono_gemv_launch": (i32, [C.POINTER(GemvArgs), vp]),

@@ -118,6 +118,37 @@ extern "C" int mono_tmap_encode_box(mono_tmap_t* out, const void* base, uint64_t
     return 0;
 }
 
+extern "C" int mono_tmap_encode_fp4(mono_tmap_t* out, const void* base, uint64_t inner_elems, uint64_t rows, uint64_t outer,
+                                    uint64_t row_stride_bytes, uint64_t outer_stride_bytes) {
+    if (!out || !base || inner_elems == 0 || rows == 0 || outer == 0) {
+        mono_set_error("mono_tmap_encode_fp4: null or empty tensor");
+        return MONO_E_ARG;
+    }
+    // packed 4-bit tensors: 32-byte base, strides in multiples of 16 bytes, rows of whole 128-element boxes
+    if ((reinterpret_cast<uintptr_t>(base) & 31) || (row_stride_bytes & 31) || (outer_stride_bytes & 31) || (inner_elems & 127)) {
+        mono_set_error("mono_tmap_encode_fp4: base must be 32-byte aligned, strides multiples of 32 bytes, K a multiple of 128 "
+                       "(base %p, row stride %llu, K %llu)", base, (unsigned long long)row_stride_bytes, (unsigned long long)inner_elems);
+        return MONO_E_ARG;
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        mono_set_error("mono_tmap_encode_fp4: cuTensorMapEncodeTiled not available from the driver");
+        return MONO_E_DRIVER;
+    }
+    cuuint64_t dims[3] = {inner_elems, rows, outer};
+    cuuint64_t strides[2] = {row_stride_bytes, outer > 1 ? outer_stride_bytes : row_stride_bytes * rows};
+    cuuint32_t box[3] = {128, 128, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(reinterpret_cast<CUtensorMap*>(out), CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3, const_cast<void*>(base), dims,
+                    strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        mono_set_error("mono_tmap_encode_fp4: cuTensorMapEncodeTiled failed with %d", (int)r);
+        return MONO_E_DRIVER;
+    }
+    return 0;
+}
+
 // ---- symmetric peer memory over CUDA IPC
 extern "C" int mono_peer_alloc(size_t bytes, void** out_ptr) {
     if (!out_ptr || bytes == 0) {

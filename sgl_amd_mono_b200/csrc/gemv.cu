@@ -435,6 +435,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const __grid_cons
 extern void mono_set_error(const char* fmt, ...);
 int mono_gemv_tc_enabled();                                                      // gemv_tc.cu
 int mono_gemv_tc_launch(const mono_gemv_args* a, long tasks, cudaStream_t st);  // gemv_tc.cu
+int mono_gemv_tc4_launch(const mono_gemv_args* a, long tasks, cudaStream_t st); // gemv_tc4.cu
 
 namespace {
 template <int WK, int NT>
@@ -528,6 +529,20 @@ extern "C" int mono_gemv_launch(const mono_gemv_args* a, void* stream) {
             int rc = mono_gemv_tc_launch(a, tasks, (cudaStream_t)stream);
             if (rc > 0) mono_set_error("mono_gemv_launch: CUDA error %d (%s)", rc, cudaGetErrorString((cudaError_t)rc));
             return rc;
+        }
+    }
+    if (a->wkind == MONO_W_MXFP4 && mono_gemv_tc_enabled()) {
+        const int rc = mono_gemv_tc4_launch(a, tasks, (cudaStream_t)stream);  // -100: not eligible, use the warp-MMA consumer
+        if (rc != -100) {
+            if (rc > 0) mono_set_error("mono_gemv_launch: CUDA error %d (%s)", rc, cudaGetErrorString((cudaError_t)rc));
+            return rc;
+        }
+    }
+    for (int j = 0; j < a->njobs; ++j) {
+        if (a->wkind == MONO_W_MXFP4 && a->job[j].act_natural) {
+            mono_set_error("mono_gemv_launch: job %d: natural-order MXFP8 activations need the tcgen05 path (tmap4, act_tmap, one plane, "
+                           "segments of at most 2048 values)", j);
+            return MONO_E_ARG;
         }
     }
     for (int j = 0; j < a->njobs; ++j) {

@@ -52,7 +52,7 @@ __device__ __forceinline__ void quant_chunk128(const float* x /* smem, 128 value
             reinterpret_cast<uint32_t*>(plane1 + chunk * 128)[lane] = wl;
             if (lane == 0) scale_f32[chunk] = sc;
         }
-    } else if (fmt == MONO_ACT_MX8) {
+    } else if (fmt == MONO_ACT_MX8 || fmt == MONO_ACT_MX8N) {
         // four groups of 32: lanes 8q .. 8q+7 own group q
         float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
 #pragma unroll
@@ -63,7 +63,10 @@ __device__ __forceinline__ void quant_chunk128(const float* x /* smem, 128 value
         // values 4*lane+i sit in group-of-8 number lane/2 at in-group index (lane&1)*4+i
         uint8_t* dst = plane0 + chunk * 128 + (lane >> 1) * 8;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) dst[mx_perm8((lane & 1) * 4 + i)] = f32_to_e4m3(v[i] * inv);
+        for (int i = 0; i < 4; ++i) {
+            const int k8 = (lane & 1) * 4 + i;  // index inside the group of 8
+            dst[fmt == MONO_ACT_MX8 ? mx_perm8(k8) : k8] = f32_to_e4m3(v[i] * inv);
+        }
         if ((lane & 7) == 0) scale_e8[chunk * 4 + (lane >> 3)] = (uint8_t)code;
     } else {  // MONO_ACT_BF16
         __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
@@ -459,7 +462,7 @@ extern "C" int mono_act_prep_launch(const mono_act_prep_args* a, void* stream) {
     }
     if (a->planes) {
         const bool need_f32 = a->fmt == MONO_ACT_A8 || a->fmt == MONO_ACT_HILO;
-        if ((need_f32 && !a->scale_f32) || (a->fmt == MONO_ACT_MX8 && !a->scale_e8) || a->fmt < 0 || a->fmt > 3) {
+        if ((need_f32 && !a->scale_f32) || ((a->fmt == MONO_ACT_MX8 || a->fmt == MONO_ACT_MX8N) && !a->scale_e8) || a->fmt < 0 || a->fmt > 4) {
             mono_set_error("mono_act_prep_launch: format %d needs its scale buffer", a->fmt);
             return MONO_E_ARG;
         }
@@ -505,7 +508,7 @@ extern "C" int mono_mid_launch(const mono_mid_args* a, void* stream) {
         mono_set_error("mono_mid_launch: rows 1..16 and inter a multiple of 128 required");
         return MONO_E_ARG;
     }
-    if ((a->fmt == MONO_ACT_A8 && !a->scale_f32) || (a->fmt == MONO_ACT_MX8 && !a->scale_e8) || a->fmt == MONO_ACT_HILO) {
+    if ((a->fmt == MONO_ACT_A8 && !a->scale_f32) || ((a->fmt == MONO_ACT_MX8 || a->fmt == MONO_ACT_MX8N) && !a->scale_e8) || a->fmt == MONO_ACT_HILO) {
         mono_set_error("mono_mid_launch: format %d not supported or missing scales", a->fmt);
         return MONO_E_ARG;
     }

@@ -42,7 +42,13 @@ class MoeFfn:
         self.max_expert = min(E, max_rows * k)
         efmt, sfmt = cfg.expert_fmt, cfg.shared_fmt
         z = lambda *s, dt=torch.float32: torch.zeros(*s, dtype=dt, device=device)  # noqa: E731
-        self.xq = ops.ActBuf(_ACT[efmt], h, device)
+        def act_of(fmt, weight):
+            # MXFP4 weights on the tcgen05 consumer take natural-order MXFP8 activations
+            if fmt == "mxfp4" and tc_on and ops.fp4_tma_ok(weight):
+                return L.ACT_MX8N
+            return _ACT[fmt]
+
+        self.xq = ops.ActBuf(act_of(efmt, w["w13"]), h, device)
         self.xbf = z(L.MAX_ROWS, h, dt=torch.bfloat16)
         self.logits = z(L.MAX_ROWS, E)
         self.ids = z(L.MAX_ROWS, k, dt=torch.int32)
@@ -51,7 +57,7 @@ class MoeFfn:
         self.expert_list = z(self.max_expert, dt=torch.int32)
         self.n_expert = z(1, dt=torch.int32)
         self.coef = z(self.max_expert, L.MAX_ROWS)
-        self.mid_r = ops.ActBuf(_ACT[efmt], il, device, segs=self.max_expert)
+        self.mid_r = ops.ActBuf(act_of(efmt, w["w2"]), il, device, segs=self.max_expert)
         self.has_shared = sfmt != "none"
         same = self.has_shared and sfmt == efmt
         # ---- up / gate launch
@@ -60,8 +66,8 @@ class MoeFfn:
         self.up = ops.Gemv(_WK[efmt], self.guard)
         self.up_sh = self.mid_s = self.up_s = None
         if self.has_shared:
-            self.xs = self.xq if same else ops.ActBuf(_ACT[sfmt], h, device)
-            self.mid_s = ops.ActBuf(_ACT[sfmt], il, device)
+            self.xs = self.xq if same else ops.ActBuf(act_of(sfmt, w["sh13"]), h, device)
+            self.mid_s = ops.ActBuf(act_of(sfmt, w["sh2"]), il, device)
             st, ns = ops.plan_split(_ktiles(w["sh13"]), -(-2 * il // 128), _WK[sfmt])
             self.ns_up_s = ns
             self.up_s = z(ns, L.MAX_ROWS, 2 * il)

@@ -59,7 +59,7 @@ class ActBuf:
         if fmt in (L.ACT_A8, L.ACT_HILO):
             self.scale_ld = _up(kpad // 128, 4) + 4
             self.scale_f32 = torch.zeros(segs, L.MAX_ROWS, self.scale_ld, dtype=torch.float32, device=device)
-        elif fmt == L.ACT_MX8:
+        elif fmt in (L.ACT_MX8, L.ACT_MX8N):
             self.scale_ld = _up(kpad // 32, 16) + 16
             self.scale_e8 = torch.full((segs, L.MAX_ROWS, self.scale_ld), 127, dtype=torch.uint8, device=device)
 
@@ -111,6 +111,13 @@ def plan_split(k_tiles: int, row_blocks: int, wkind: int, sms: int = 148, cap: i
     if split >= k_tiles:
         return k_tiles, 1
     return split, -(-k_tiles // split)
+
+
+def fp4_tma_ok(w: torch.Tensor) -> bool:
+    """Whether a packed-nibble weight [..., N, K/2] can be read as a 4-bit tensor by TMA: K a multiple of
+    128, rows a multiple of 32 bytes apart, base 32-byte aligned."""
+    kb = w.shape[-1] * w.element_size()
+    return w.dtype == torch.uint8 and (2 * kb) % 128 == 0 and kb % 32 == 0 and w.data_ptr() % 32 == 0 and w.is_contiguous()
 
 
 class Gemv:
@@ -198,6 +205,11 @@ class Gemv:
         if out.dtype != torch.float32 or out.numel() < (out_slice + n_slices) * slice_elems:
             raise ValueError(f"{name}: output buffer holds {out.numel()} f32, needs {(out_slice + n_slices) * slice_elems}")
         job.feeds_job = 0
+        job.act_natural = int(act.fmt == L.ACT_MX8N)
+        if self.wkind == L.W_MXFP4 and act.fmt == L.ACT_MX8N:
+            # the tcgen05 consumer reads the packed nibbles as a tensor of 4-bit elements
+            L.check(L.load().mono_tmap_encode_fp4(C.byref(job.tmap4), w.data_ptr(), 2 * kb, rows_total, mats, kb, rows_total * kb),
+                    f"mono_tmap_encode_fp4({name})")
         self._keep += [w, wscale, act, out, expert_list, n_expert, coef]
         self.args.njobs = j + 1
         return job.nsplit

@@ -135,7 +135,7 @@ def test_replays_are_bit_equal():
     assert not torch.equal(ffn(x2, sd), out)
 
 
-@pytest.mark.parametrize("fmt", [L.ACT_A8, L.ACT_HILO, L.ACT_MX8, L.ACT_BF16])
+@pytest.mark.parametrize("fmt", [L.ACT_A8, L.ACT_HILO, L.ACT_MX8, L.ACT_MX8N, L.ACT_BF16])
 def test_activation_formats_are_bit_exact(fmt):
     rows, k = 5, 512
     x = (torch.randn(rows, k, generator=torch.Generator().manual_seed(7)) * 2).bfloat16()
@@ -152,9 +152,9 @@ def test_activation_formats_are_bit_exact(fmt):
         hi, lo, sc = Q.split_hi_lo(x)
         assert torch.equal(planes[0], Q.e4m3_bytes(hi)) and torch.equal(planes[1], Q.e4m3_bytes(lo))
         assert torch.equal(buf.scale_f32[0, :rows, : k // 128].cpu(), sc)
-    elif fmt == L.ACT_MX8:
+    elif fmt in (L.ACT_MX8, L.ACT_MX8N):
         q, code = Q.mxfp8_quant(x)
-        perm = torch.tensor([0, 2, 4, 6, 1, 3, 5, 7])
+        perm = torch.tensor([0, 2, 4, 6, 1, 3, 5, 7] if fmt == L.ACT_MX8 else list(range(8)))
         want = Q.e4m3_bytes(q).reshape(rows, k // 8, 8)[:, :, perm].reshape(rows, k)
         assert torch.equal(planes[0], want)
         assert torch.equal(buf.scale_e8[0, :rows, : k // 32].cpu(), code)
@@ -170,8 +170,9 @@ def _act_values(buf, seg, rows, k, fmt):
     if fmt == L.ACT_A8:
         sc = buf.scale_f32[seg, :rows, : k // 128].cpu()
         return (Q.e4m3_from_bytes(pl[:, :k]).reshape(rows, -1, 128) * sc[..., None]).reshape(rows, k)
-    if fmt == L.ACT_MX8:
-        inv = torch.tensor([0, 4, 1, 5, 2, 6, 3, 7])  # stored k0 k2 k4 k6 k1 k3 k5 k7
+    if fmt in (L.ACT_MX8, L.ACT_MX8N):
+        # MX8 is stored k0 k2 k4 k6 k1 k3 k5 k7, MX8N in natural order
+        inv = torch.tensor([0, 4, 1, 5, 2, 6, 3, 7] if fmt == L.ACT_MX8 else list(range(8)))
         v = Q.e4m3_from_bytes(pl[:, :k]).reshape(rows, k // 8, 8)[:, :, inv].reshape(rows, k)
         return Q.mxfp8_dequant(v, buf.scale_e8[seg, :rows, : k // 32].cpu())
     return pl[:, : 2 * k].contiguous().view(torch.bfloat16).float()
@@ -185,7 +186,8 @@ def test_gemv_stages_in_isolation(cfg, rows):
     wc = _cpu(w)
     fp8 = cfg.expert_fmt == "fp8_block"
     deq = Q.fp8_block_dequant if fp8 else Q.mxfp4_dequant
-    afmt = L.ACT_A8 if fp8 else L.ACT_MX8
+    afmt = ffn.xq.fmt  # A8 for FP8 experts; MX8N (tcgen05 consumer) or MX8 (warp-MMA consumer) for MXFP4
+    assert ffn.mid_r.fmt == afmt
     h, il = cfg.hidden, cfg.inter_local
     n = int(ffn.n_expert.item())
     experts = ffn.expert_list[:n].cpu().tolist()
