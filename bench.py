@@ -41,6 +41,17 @@ def measured_peaks():
     return 6650.0, "fallback (6.65 TB/s)"
 
 
+def measured_traffic(key, nbytes):
+    """DRAM bytes per launch of the probed kernel: the ncu-measured traffic / algorithmic ratio of the
+    same kernel on a capturable case (profiles/dram_traffic.json) times this launch's algorithmic
+    bytes; None when no capture of that kernel is committed."""
+    p = ROOT / "profiles" / "dram_traffic.json"
+    if key is None or not p.exists():
+        return None
+    d = json.loads(p.read_text()).get(key)
+    return None if not d else int(nbytes * d["traffic_bytes"] / d["algorithmic_bytes"])
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
 
@@ -219,6 +230,7 @@ class MoeWorkload:
 
     layers_per_step = 1
     kernel = "gemv_tc_kernel (tcgen05 FP8 expert up/gate, timed as its own launch)"
+    traffic_key = "fp8_expert_up_gate"
 
     def __init__(self, rows=8):
         self.rows = rows
@@ -297,6 +309,7 @@ class LayerWorkload:
 
     layers_per_step = 1
     kernel = "gemv_tc_kernel (tcgen05 FP8 expert up/gate, timed as its own launch)"
+    traffic_key = "fp8_expert_up_gate"
 
     def __init__(self, rows=8, ctx=16384):
         self.rows, self.ctx = rows, ctx
@@ -425,7 +438,8 @@ class GqaLayerWorkload(LayerWorkload):
     experts top-8 of intermediate 1536 in MXFP4, sigmoid router), 16 verify rows, one rank's share of
     TP 4 (or TP = number of GPUs)."""
 
-    kernel = "gemv_kernel<MXFP4> (expert up/gate)"
+    kernel = "gemv_tc4_kernel (tcgen05 MXFP4 expert up/gate, timed as its own launch)"
+    traffic_key = "mxfp4_expert_up_gate"
 
     def __init__(self, rows=16, ctx=65536):
         super().__init__(rows, ctx)
@@ -644,6 +658,7 @@ class StackWorkload:
     cached key is attended."""
 
     kernel = "gemv_tc_kernel (tcgen05 FP8 expert up/gate of layer 0, timed as its own launch)"
+    traffic_key = "fp8_expert_up_gate"
 
     def __init__(self, rows=1, ctx=8192, layers=40, verify=5):
         self.rows, self.ctx, self.n_layers, self.verify = rows, ctx, layers, verify
@@ -921,7 +936,8 @@ def main() -> None:
         # layer_bytes() covers what one timed step reads (one layer, or the whole stack and its tail)
         "roofline": {"bound": "hbm", "kernel": wl.kernel, **({"layer_achieved_gbs": wl.layer_bytes()[0] / (ms_per_step * 1e-3) / 1e9,
                      "layer_frac": wl.layer_bytes()[0] / (ms_per_step * 1e-3) / 1e9 / peak} if hasattr(wl, "layer_bytes") else {}), "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": None, "algorithmic_bytes": nbytes,
+                     "frac": achieved / peak, "traffic": measured_traffic(getattr(wl, "traffic_key", None), nbytes),
+                     "algorithmic_bytes": nbytes,
                      "kernel_us": probe_ms * 1000.0, "peak_source": peak_src},
     }
     if hasattr(wl, "n_layers"):
