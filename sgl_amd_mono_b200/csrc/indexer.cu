@@ -14,6 +14,7 @@ namespace mono {
 // ------------------------------------------------------------------ scores
 constexpr int kScoreThreads = 256;
 constexpr int kKeyTile = 128;
+constexpr int kTilesPerTask = 2;
 constexpr int kIdxPitch = 128 + 8;  // bf16 elements per staged row (272 B: conflict-free ldmatrix)
 
 struct ScoreSmem {
@@ -30,11 +31,13 @@ __global__ void __launch_bounds__(kScoreThreads) index_score_kernel(const mono_i
     const int g = lane >> 2, t4 = lane & 3;
     const int mtiles = (a.index_heads + 15) >> 4;
     const __nv_bfloat16* qg = reinterpret_cast<const __nv_bfloat16*>(a.idx_q);
-    for (int task = blockIdx.x; task < a.rows * max_tiles; task += gridDim.x) {
-        const int row = task / max_tiles, tile = task - row * max_tiles;
+    // a task = kTilesPerTask consecutive key tiles of one row: the row's queries and head weights are staged once
+    const int groups = (max_tiles + kTilesPerTask - 1) / kTilesPerTask;
+    for (int task = blockIdx.x; task < a.rows * groups; task += gridDim.x) {
+        const int row = task / groups, tile0 = (task - row * groups) * kTilesPerTask;
         if (a.slots && a.slots[row] < 0) continue;
         const int n = (int)a.positions[row] + 1;
-        if (tile * kKeyTile >= n) continue;
+        if (tile0 * kKeyTile >= n) continue;
         __syncthreads();
         // ---- stage q (zero rows past index_heads) and the head weights
         for (int c = tid; c < 64 * 16; c += kScoreThreads) {
@@ -44,6 +47,8 @@ __global__ void __launch_bounds__(kScoreThreads) index_score_kernel(const mono_i
             *reinterpret_cast<uint4*>(&sm.q[h][ch * 8]) = v;
         }
         if (tid < 64) sm.w[tid] = tid < a.index_heads ? a.idx_w[(size_t)row * a.w_ld + tid] : 0.f;
+        for (int tile = tile0; tile < tile0 + kTilesPerTask && tile * kKeyTile < n; ++tile) {
+        if (tile != tile0) __syncthreads();  // every warp is done with the previous tile's keys
         // ---- stage 128 keys: E2M1 * 2^(code - 127) is exact in bf16
         {
             const int key = tid >> 1, half = tid & 1;
@@ -125,6 +130,7 @@ __global__ void __launch_bounds__(kScoreThreads) index_score_kernel(const mono_i
                 if (g == 0 && p < n) a.scores[(size_t)row * a.score_ld + p] = s;
             }
         }
+        }  // tiles of the task
     }
 }
 
@@ -287,7 +293,7 @@ extern "C" int mono_index_score_launch(const mono_index_args* a, void* stream) {
         attr_set = true;
     }
     const int max_tiles = (a->score_ld + mono::kKeyTile - 1) / mono::kKeyTile;
-    int grid = a->rows * max_tiles;
+    int grid = a->rows * ((max_tiles + mono::kTilesPerTask - 1) / mono::kTilesPerTask);
     const int sms = mono_sm_count();
     if (grid > 4 * sms) grid = 4 * sms;
     mono::launch_k(mono::index_score_kernel, grid, mono::kScoreThreads, smem, (cudaStream_t)stream, *a, max_tiles);
