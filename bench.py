@@ -873,7 +873,13 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=torch.device(dev))
     wl = wl_cls(rows=args.rows) if args.rows else wl_cls()
     wl.shard_of = args.shard_of
+    def trace(what):  # MONO_BENCH_TRACE=1: progress on stderr, to see where a multi-rank run stops
+        if os.environ.get("MONO_BENCH_TRACE") == "1":
+            print(f"[bench rank {rank}] {what}", file=sys.stderr, flush=True)
+
+    trace("setup")
     wl.setup(dev, rank, world)
+    trace("setup done")
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
 
     def barrier():
@@ -898,7 +904,9 @@ def main() -> None:
     for _ in range(int(n_load.item())):
         wl.step()
     torch.cuda.synchronize()
+    trace(f"load phase done ({int(n_load.item())} steps); timed steps")
     total_ms = time_steps(wl.step, args.steps, args.warmup, flush)
+    trace("timed steps done")
     barrier()
     t = torch.tensor([total_ms], device=dev)
     if dist is not None:
@@ -920,6 +928,7 @@ def main() -> None:
     e2e_us = float(t.item()) * 1000.0 / wl.layers_per_step
     h2d, d2h = wl.e2e_bytes()
     # roofline of the dominant kernel, timed alone
+    trace("e2e done; roofline probe")
     nbytes, probe = wl.roofline_probe()
     probe_ms = time_steps(probe, args.steps, 3, flush) / args.steps
     sampler.__exit__(None, None, None)
@@ -927,6 +936,7 @@ def main() -> None:
         wl.check()  # the guard's error words must be clean after the timed steps
     peak, peak_src = measured_peaks()
     achieved = nbytes / (probe_ms * 1e-3) / 1e9
+    trace("probe done; building the line")
     line = {
         "metric": "us_per_decoder_layer", "value": us_per_layer, "unit": "us", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong",
