@@ -551,6 +551,7 @@ class AllReduceWorkload:
     same message, both replayed from CUDA graphs.  Needs --gpus >= 2."""
 
     layers_per_step = 1
+    holds_nccl_graphs = True
     kernel = "reduce_kernel (push + rank-ordered sum)"
 
     def __init__(self, rows=8, n=7168):
@@ -959,9 +960,16 @@ def main() -> None:
             torch.set_num_threads(cores)
             v, sample = wl.cpu_sample()
             line["cpu_baseline"] = {"value": v, "unit": "us", "cores": cores, "kind": "port", "sample": sample}
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
+        torch.cuda.synchronize()
+        if getattr(wl, "holds_nccl_graphs", False):
+            # tearing the communicator down under live CUDA graphs of its kernels does not return: the
+            # line is out and every rank is past the barrier, so leave without the teardown
+            sys.stdout.flush()
+            sys.stderr.flush()
+            os._exit(0)
         dist.destroy_process_group()
 
 
