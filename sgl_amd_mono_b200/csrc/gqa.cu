@@ -73,41 +73,66 @@ __global__ void __launch_bounds__(kGqaDim) gqa_front_kernel(const mono_gqa_args 
 }
 
 // ------------------------------------------------------------------ block scores
-// grid (rows * score_ld blocks), 64 threads: one key each
-__global__ void __launch_bounds__(kGqaBlock) gqa_score_kernel(const mono_gqa_args a, float scale) {
+// grid (rows * ceil(score_ld / 4)), 256 threads: four blocks per CTA, two warps per block; the row's index
+// query is staged once per CTA
+constexpr int kScoreBlocksPerCta = 4;
+
+__global__ void __launch_bounds__(kGqaBlock * kScoreBlocksPerCta) gqa_score_kernel(const mono_gqa_args a, float scale) {
     pdl_prologue();
-    __shared__ float q[kGqaDim];
-    __shared__ float red[2];
-    const int row = blockIdx.x / a.score_ld, b = blockIdx.x - row * a.score_ld, tid = threadIdx.x;
+    __shared__ __align__(16) float q[kGqaDim];
+    __shared__ float red[2 * kScoreBlocksPerCta];
+    const int groups = (a.score_ld + kScoreBlocksPerCta - 1) / kScoreBlocksPerCta;
+    const int row = blockIdx.x / groups, tid = threadIdx.x;
+    const int sub = tid >> 6, key = tid & 63;
+    const int b = (blockIdx.x - row * groups) * kScoreBlocksPerCta + sub;
     if (a.slots && a.slots[row] < 0) return;
     const int seq = (int)a.positions[row] + 1;
     const int n_blk = (seq + kGqaBlock - 1) / kGqaBlock;
-    if (b >= n_blk) return;
+    if ((b - sub) >= n_blk) return;  // the whole CTA is past the row's context
     const __nv_bfloat16* iq = reinterpret_cast<const __nv_bfloat16*>(a.iq_out) + (size_t)row * kGqaDim;
-    q[tid] = __bfloat162float(iq[tid]);
-    q[tid + 64] = __bfloat162float(iq[tid + 64]);
+    if (tid < kGqaDim) q[tid] = __bfloat162float(iq[tid]);
     __syncthreads();
-    const int page = a.page_table[(size_t)row * a.pt_ld + b];
+    // eight lanes share a key row (16 bytes each: one coalesced 512-byte request covers four rows), so a warp
+    // walks its 32 keys four at a time; the eight partial dots of a row meet in a 3-step butterfly
     float dot = -INFINITY;
-    if (b * kGqaBlock + tid < seq && page >= 0 && page < a.n_pages) {
-        const uint4* src = reinterpret_cast<const uint4*>(a.index_cache + ((size_t)page * kGqaBlock + tid) * kGqaDim);
-        uint4 w[8];
+    if (b < n_blk && b < a.score_ld) {
+        const int page = a.page_table[(size_t)row * a.pt_ld + b];
+        if (page >= 0 && page < a.n_pages) {
+            const int lane = tid & 31, chunk = lane & 7, half = (tid >> 5) & 1;
+            const uint8_t* base = a.index_cache + (size_t)page * kGqaBlock * kGqaDim;
+            const float4* q4 = reinterpret_cast<const float4*>(q) + chunk * 4;
+            uint4 w[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) w[i] = src[i];
-        dot = 0.f;
+            for (int it = 0; it < 8; ++it)
+                w[it] = *reinterpret_cast<const uint4*>(base + (size_t)(half * 32 + it * 4 + (lane >> 3)) * kGqaDim + chunk * 16);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint32_t ws[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
+            for (int it = 0; it < 8; ++it) {
+                const uint32_t ws[4] = {w[it].x, w[it].y, w[it].z, w[it].w};
+                float d = 0.f;
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-#pragma unroll
-                for (int k = 0; k < 4; ++k) dot += e4m3_to_f32((ws[j] >> (8 * k)) & 0xFF) * q[i * 16 + j * 4 + k];
+                for (int j = 0; j < 4; ++j) {
+                    const __half2_raw h01 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(ws[j] & 0xFFFFu), __NV_E4M3);
+                    const __half2_raw h23 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(ws[j] >> 16), __NV_E4M3);
+                    const float2 f01 = __half22float2(*reinterpret_cast<const __half2*>(&h01));
+                    const float2 f23 = __half22float2(*reinterpret_cast<const __half2*>(&h23));
+                    const float4 qv = q4[j];
+                    d += f01.x * qv.x;
+                    d += f01.y * qv.y;
+                    d += f23.x * qv.z;
+                    d += f23.y * qv.w;
+                }
+                d += __shfl_xor_sync(0xffffffffu, d, 1);
+                d += __shfl_xor_sync(0xffffffffu, d, 2);
+                d += __shfl_xor_sync(0xffffffffu, d, 4);
+                const int k = half * 32 + it * 4 + (lane >> 3);
+                if (b * kGqaBlock + k < seq) dot = fmaxf(dot, d);
+            }
         }
     }
-    float m = warp_max(dot);
+    const float m = warp_max(dot);
     if ((tid & 31) == 0) red[tid >> 5] = m;
     __syncthreads();
-    if (tid == 0) a.scores[(size_t)row * a.score_ld + b] = fmaxf(red[0], red[1]) * scale;
+    if (key == 0 && b < n_blk && b < a.score_ld) a.scores[(size_t)row * a.score_ld + b] = fmaxf(red[2 * sub], red[2 * sub + 1]) * scale;
 }
 
 // ------------------------------------------------------------------ selection
@@ -147,16 +172,47 @@ __global__ void __launch_bounds__(kSelThreads) gqa_select_kernel(const mono_gqa_
     __syncthreads();
     const int n_sel = min(n_blk, kGqaTopk), tail = n_blk - 1;
     const long long kt = keys[tail];
-    // rank = how many entries beat this one; exact, no order of arrival
+    // A floor under the 16th largest key: the 16th largest of the 32 warps' maxima (32 distinct entries are
+    // at least their warp's maximum ... at least the 16th largest of those).  Only entries at or above the
+    // floor can rank among the first 16, and every entry that beats one of them is itself above the floor:
+    // ranks counted among those candidates are exact (select.py:57-101 group_floor / compact).
+    __shared__ long long s_wmax[kSelThreads / 32];
+    __shared__ long long s_floor;
+    __shared__ int s_ncand;
+    long long* cand = keys + kSelMaxBlocks;  // candidate list (dynamic shared memory after the keys)
+    {
+        long long mx = (long long)0x8000000000000000ll;
+        for (int b = tid; b < n_blk; b += kSelThreads) mx = keys[b] > mx ? keys[b] : mx;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const long long other = __shfl_xor_sync(0xffffffffu, mx, o);
+            mx = other > mx ? other : mx;
+        }
+        if ((tid & 31) == 0) s_wmax[tid >> 5] = mx;
+        if (tid == 0) s_ncand = 0;
+    }
+    __syncthreads();
+    if (tid < 32) {
+        const long long mine = s_wmax[tid];
+        int beaten = 0;
+        for (int j = 0; j < 32; ++j) beaten += s_wmax[j] > mine || (s_wmax[j] == mine && j < tid);
+        if (beaten == kGqaTopk - 1) s_floor = mine;  // the 16th largest warp maximum
+    }
+    __syncthreads();
+    const long long floor_key = n_blk > kGqaTopk * 2 ? s_floor : (long long)0x8000000000000000ll;
+    for (int b = tid; b < n_blk; b += kSelThreads)
+        if (keys[b] >= floor_key) cand[atomicAdd(&s_ncand, 1)] = keys[b];
+    __syncthreads();
+    const int n_cand = s_ncand;
     int my_rank[kSelMaxBlocks / kSelThreads];
 #pragma unroll
     for (int i = 0; i < kSelMaxBlocks / kSelThreads; ++i) {
         const int b = tid + i * kSelThreads;
         my_rank[i] = 1 << 30;
-        if (b < n_blk) {
+        if (b < n_blk && keys[b] >= floor_key) {
             const long long mine = keys[b];
             int r = 0;
-            for (int j = 0; j < n_blk; ++j) r += keys[j] > mine;
+            for (int j = 0; j < n_cand; ++j) r += cand[j] > mine;
             my_rank[i] = r;
             if (b == tail && r < n_sel) s_tail_sel = 1;
         }
@@ -182,6 +238,7 @@ __global__ void __launch_bounds__(kSelThreads) gqa_select_kernel(const mono_gqa_
 // per q head of the group: m, l, acc[128].
 struct GqaSplitSmem {
     float k[kGqaBlock][kGqaDim + 1];
+    uint8_t v[kGqaBlock][kGqaDim];  // E4M3 bytes
     float q[kGqaMaxGroup][kGqaDim];
     float p[kGqaMaxGroup][kGqaBlock];
 };
@@ -217,6 +274,13 @@ __global__ void __launch_bounds__(kGqaDim) gqa_split_kernel(const mono_gqa_args 
 #pragma unroll
                 for (int k = 0; k < 4; ++k) sm.k[key][piece * 16 + j * 4 + k] = e4m3_to_f32((ws[j] >> (8 * k)) & 0xFF);
         }
+        // V block: the same rows of the V cache, kept as bytes (every 16-byte load is in flight before the scores)
+        const uint8_t* vbase = a.v_cache + ((size_t)page * kGqaBlock * a.kv_heads + kvh) * kGqaDim;
+        for (int c = tid; c < kGqaBlock * 8; c += kGqaDim) {
+            const int key = c >> 3, piece = c & 7;
+            *reinterpret_cast<uint4*>(&sm.v[key][piece * 16]) =
+                *reinterpret_cast<const uint4*>(vbase + (size_t)key * a.kv_heads * kGqaDim + piece * 16);
+        }
     }
     __syncthreads();
     // scores: thread = (key, half of the group)
@@ -244,12 +308,12 @@ __global__ void __launch_bounds__(kGqaDim) gqa_split_kernel(const mono_gqa_args 
     __syncthreads();
     // PV: thread = dim
     {
-        const uint8_t* vb = a.v_cache + ((size_t)page * kGqaBlock * a.kv_heads + kvh) * kGqaDim + tid;
         float acc[kGqaMaxGroup];
 #pragma unroll
         for (int g = 0; g < kGqaMaxGroup; ++g) acc[g] = 0.f;
+#pragma unroll 8
         for (int key = 0; key < live; ++key) {
-            const float v = e4m3_to_f32(vb[(size_t)key * a.kv_heads * kGqaDim]);
+            const float v = e4m3_to_f32(sm.v[key][tid]);
 #pragma unroll
             for (int g = 0; g < kGqaMaxGroup; ++g)
                 if (g < G) acc[g] += sm.p[g][key] * v;
@@ -323,7 +387,8 @@ extern "C" int mono_gqa_score_launch(const mono_gqa_args* a, void* stream) {
     }
     // fp32(fp32(sm_scale) * fp32(log2 e)) as index_score.py:59-62
     const float scale = a->sm_scale * 1.4426950408889634f;
-    mono::launch_k(mono::gqa_score_kernel, a->rows * a->score_ld, mono::kGqaBlock, 0, (cudaStream_t)stream, *a, scale);
+    const int groups = (a->score_ld + mono::kScoreBlocksPerCta - 1) / mono::kScoreBlocksPerCta;
+    mono::launch_k(mono::gqa_score_kernel, a->rows * groups, mono::kGqaBlock * mono::kScoreBlocksPerCta, 0, (cudaStream_t)stream, *a, scale);
     return gqa_done("mono_gqa_score_launch");
 }
 
@@ -334,7 +399,13 @@ extern "C" int mono_gqa_select_launch(const mono_gqa_args* a, void* stream) {
         mono_set_error("mono_gqa_select_launch: scores of at most %d blocks, page table and selection outputs required", mono::kSelMaxBlocks);
         return MONO_E_ARG;
     }
-    mono::launch_k(mono::gqa_select_kernel, a->rows, mono::kSelThreads, (size_t)mono::kSelMaxBlocks * sizeof(long long), (cudaStream_t)stream, *a);
+    const size_t smem = 2 * (size_t)mono::kSelMaxBlocks * sizeof(long long);  // keys + candidates
+    static thread_local bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(mono::gqa_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attr_set = true;
+    }
+    mono::launch_k(mono::gqa_select_kernel, a->rows, mono::kSelThreads, smem, (cudaStream_t)stream, *a);
     return gqa_done("mono_gqa_select_launch");
 }
 
