@@ -197,6 +197,7 @@ typedef struct mono_gemv_job {
      * runs on the warp-MMA consumer, which needs MONO_ACT_MX8. */
     mono_tmap_t tmap4;
     int act_natural; /* 1 = the activation planes are MONO_ACT_MX8N */
+    int k_tiles4;    /* K in 128-element tiles (0 = 2 * k_tiles): exact when K ends inside a 128-byte tile */
 } mono_gemv_job;
 
 typedef struct mono_gemv_args {

@@ -41,8 +41,8 @@ class GemvJob(C.Structure):
         ("out", vp), ("out_ld", i32), ("out_split_stride", i64),
         ("feeds_job", i32), ("done", vp), ("ready", vp),
         ("_pad4", C.c_ubyte * 40),  # tensor maps are 64-byte aligned in C
-        ("tmap4", Tmap), ("act_natural", i32),
-        ("_tail", C.c_ubyte * 60),
+        ("tmap4", Tmap), ("act_natural", i32), ("k_tiles4", i32),
+        ("_tail", C.c_ubyte * 56),
     ]
 
 

@@ -45,21 +45,23 @@ __device__ __forceinline__ int nrb_of(const mono_gemv_job& j) { return (j.n_rows
 __device__ __forceinline__ Seg make_seg(const mono_gemv_job& j, int rb, int ks, int u, const int* elist) {
     Seg s;
     int mat = 0;
+    // K in 128-element tiles: exact when the caller gave it (a K that ends inside a 128-byte tile of nibbles)
+    const int total4 = j.k_tiles4 > 0 ? j.k_tiles4 : 2 * j.k_tiles;
     if (j.mode == MONO_JOB_DENSE) {
         s.t0 = 2 * ks * j.split_tiles;
-        s.nt = 2 * min(j.split_tiles, j.k_tiles - ks * j.split_tiles);
+        s.nt = min(2 * j.split_tiles, total4 - s.t0);
         s.aset = 0;
         s.coef = nullptr;
     } else if (j.mode == MONO_JOB_EXPERT_UP) {
         mat = (u < 128) ? elist[u] : j.expert_list[u];
         s.t0 = 2 * ks * j.split_tiles;
-        s.nt = 2 * min(j.split_tiles, j.k_tiles - ks * j.split_tiles);
+        s.nt = min(2 * j.split_tiles, total4 - s.t0);
         s.aset = 0;
         s.coef = nullptr;
     } else {
         mat = (u < 128) ? elist[u] : j.expert_list[u];
         s.t0 = 0;
-        s.nt = 2 * j.k_tiles;
+        s.nt = total4;
         s.aset = u;
         s.coef = j.coef ? j.coef + (size_t)u * kMaxRows : nullptr;
     }

@@ -210,6 +210,7 @@ class Gemv:
             # the tcgen05 consumer reads the packed nibbles as a tensor of 4-bit elements
             L.check(L.load().mono_tmap_encode_fp4(C.byref(job.tmap4), w.data_ptr(), 2 * kb, rows_total, mats, kb, rows_total * kb),
                     f"mono_tmap_encode_fp4({name})")
+            job.k_tiles4 = (2 * kb) // 128
         self._keep += [w, wscale, act, out, expert_list, n_expert, coef]
         self.args.njobs = j + 1
         return job.nsplit
