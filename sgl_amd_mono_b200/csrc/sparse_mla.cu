@@ -5,11 +5,11 @@
 // split-local max / sum, p rounded to bf16 before P.V, bf16 partial accumulator) and
 // :3975-4075 (merge: w_j = e^(m_j - M) / sum_j l_j e^(m_j - M)).
 //
-// sm_100a design: a task is (row, 64-key split).  The CTA gathers the 64 cache rows
-// (576 E4M3 bytes + one f32 scale each) with 16-byte loads that are all in flight at
-// once, widens them to bf16 in shared memory, and runs Q.K^T and P.V on bf16 warp
-// MMAs for 16 heads at a time, reusing the key tile for every head group.  The work
-// is bound by the latency of the gather, not by bytes or flops (1.2 MB per row).
+// sm_100a design: a task is (row, group of 16 heads, run of 64-key chunks).  The CTA gathers
+// each chunk's 64 cache rows (576 E4M3 bytes + one f32 scale each) with 16-byte loads that are
+// all in flight at once, widens them to bf16 in shared memory, and runs Q.K^T and P.V on bf16
+// warp MMAs with the running maximum / sum and the output accumulators in registers, so a task
+// writes one partial however many chunks it covers (the reference writes one per 64 keys).
 #include "mono_common.cuh"
 
 extern void mono_set_error(const char* fmt, ...);
@@ -45,111 +45,142 @@ __device__ __forceinline__ void e4m3x16_to_bf16(const uint4& v, float scale, __n
             o[2 * i + h] = *reinterpret_cast<uint32_t*>(&b);
         }
     }
-    *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
-    *reinterpret_cast<uint4*>(dst + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+    // consecutive lanes write consecutive 32-byte pieces: lanes 4..7 of every eight store their halves in the
+    // other order, so that eight lanes' 16-byte stores fall into eight different bank groups
+    const int swap = (threadIdx.x >> 2) & 1;
+    const uint4 lo = make_uint4(o[0], o[1], o[2], o[3]), hi = make_uint4(o[4], o[5], o[6], o[7]);
+    *reinterpret_cast<uint4*>(dst + 8 * swap) = swap ? hi : lo;
+    *reinterpret_cast<uint4*>(dst + 8 * (1 - swap)) = swap ? lo : hi;
 }
 
-__global__ void __launch_bounds__(kMlaThreads, 2) sparse_mla_split_kernel(const mono_sparse_mla_args a, int nsplit) {
+// A task is (row, head group of 16, run of `chunks` 64-key chunks).  The 16 heads' queries are staged
+// once; every chunk is gathered, widened, scored, and folded into accumulators that stay in registers
+// (running maximum and sum per head, rescaled like a flash-decoding pass), so a task writes one partial
+// however many chunks it covers.  Two CTAs per SM overlap one's gather with the other's MMAs.
+__global__ void __launch_bounds__(kMlaThreads, 2) sparse_mla_split_kernel(const mono_sparse_mla_args a, int nsplit, int chunks) {
     pdl_prologue();
     extern __shared__ uint8_t smem_raw[];
     MlaSmem& sm = *reinterpret_cast<MlaSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+    __shared__ float s_scale[kHeadGroup];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t4 = lane & 3;
     const __nv_bfloat16* qg = reinterpret_cast<const __nv_bfloat16*>(a.q);
     __nv_bfloat16* part_acc = reinterpret_cast<__nv_bfloat16*>(a.scratch);
     float* part_ml = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(a.scratch) +
                                               (size_t)a.rows * nsplit * a.heads * 512 * sizeof(__nv_bfloat16));
+    const int hgroups = (a.heads + kHeadGroup - 1) / kHeadGroup;
+    const int total_chunks = (a.topk + kSplit - 1) / kSplit;
 
-    for (int task = blockIdx.x; task < a.rows * nsplit; task += gridDim.x) {
-        const int row = task / nsplit, sp = task - row * nsplit;
+    for (int task = blockIdx.x; task < a.rows * hgroups * nsplit; task += gridDim.x) {
+        const int sp = task % nsplit, hg = (task / nsplit) % hgroups, row = task / (nsplit * hgroups);
         __syncthreads();
-        // ---- gather 64 cache rows, widen to bf16
-        if (tid < kSplit) {
-            const int kidx = sp * kSplit + tid;
-            int slot = kidx < a.topk ? a.topk_slots[(size_t)row * a.topk_ld + kidx] : -1;
-            if (slot >= 0 && (int64_t)slot >= a.n_pages * kPage) slot = -1;
-            sm.valid[tid] = slot;
+        // ---- stage the 16 heads of q, reset the running statistics
+        for (int c = tid; c < kHeadGroup * (kKvDim / 8); c += kMlaThreads) {
+            const int h = c / (kKvDim / 8), ch = c - h * (kKvDim / 8);
+            const int head = hg * kHeadGroup + h;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (head < a.heads) v = *reinterpret_cast<const uint4*>(qg + ((size_t)row * a.heads + head) * kKvDim + ch * 8);
+            *reinterpret_cast<uint4*>(&sm.q[h][ch * 8]) = v;
         }
-        __syncthreads();
-        {
-            constexpr int kChunks = kKvDim / 16;  // 36 sixteen-byte chunks per key
-            constexpr int kPer = kSplit * kChunks / kMlaThreads;  // 9
-            uint4 v[kPer];
-            float sc[kPer];
+        if (tid < kHeadGroup) { sm.ml[tid][0] = -INFINITY; sm.ml[tid][1] = 0.f; }
+        float o[8][4];  // warp w owns latent columns 64w .. 64w+63 of heads g and g + 8
 #pragma unroll
-            for (int i = 0; i < kPer; ++i) {
-                const int c = tid + i * kMlaThreads;
-                const int key = c / kChunks, ch = c - key * kChunks;
-                const int slot = sm.valid[key];
-                if (slot >= 0) {
-                    const uint8_t* page = a.kv_pages + (size_t)(slot / kPage) * kKvPageBytes;
-                    const int off = slot % kPage;
-                    v[i] = __ldg(reinterpret_cast<const uint4*>(page + (size_t)off * kKvDim) + ch);
-                    sc[i] = __ldg(reinterpret_cast<const float*>(page + kPage * kKvDim) + off);
-                } else {
-                    v[i] = make_uint4(0, 0, 0, 0);
-                    sc[i] = 0.f;
+        for (int n = 0; n < 8; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
+
+        for (int ci = 0; ci < chunks; ++ci) {
+            const int chunk = sp * chunks + ci;
+            if (chunk >= total_chunks) break;
+            __syncthreads();
+            // ---- gather 64 cache rows, widen to bf16
+            if (tid < kSplit) {
+                const int kidx = chunk * kSplit + tid;
+                int slot = kidx < a.topk ? a.topk_slots[(size_t)row * a.topk_ld + kidx] : -1;
+                if (slot >= 0 && (int64_t)slot >= a.n_pages * kPage) slot = -1;
+                sm.valid[tid] = slot;
+            }
+            __syncthreads();
+            {
+                constexpr int kChunks = kKvDim / 16;  // 36 sixteen-byte chunks per key
+                constexpr int kPer = kSplit * kChunks / kMlaThreads;  // 9
+                uint4 v[kPer];
+                float sc[kPer];
+#pragma unroll
+                for (int i = 0; i < kPer; ++i) {
+                    const int c = tid + i * kMlaThreads;
+                    const int key = c / kChunks, ch = c - key * kChunks;
+                    const int slot = sm.valid[key];
+                    if (slot >= 0) {
+                        const uint8_t* page = a.kv_pages + (size_t)(slot / kPage) * kKvPageBytes;
+                        const int off = slot % kPage;
+                        v[i] = __ldg(reinterpret_cast<const uint4*>(page + (size_t)off * kKvDim) + ch);
+                        sc[i] = __ldg(reinterpret_cast<const float*>(page + kPage * kKvDim) + off);
+                    } else {
+                        v[i] = make_uint4(0, 0, 0, 0);
+                        sc[i] = 0.f;
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < kPer; ++i) {
+                    const int c = tid + i * kMlaThreads;
+                    const int key = c / kChunks, ch = c - key * kChunks;
+                    e4m3x16_to_bf16(v[i], sc[i], &sm.kv[key][ch * 16]);
                 }
             }
-#pragma unroll
-            for (int i = 0; i < kPer; ++i) {
-                const int c = tid + i * kMlaThreads;
-                const int key = c / kChunks, ch = c - key * kChunks;
-                e4m3x16_to_bf16(v[i], sc[i], &sm.kv[key][ch * 16]);
-            }
-        }
-        for (int hg = 0; hg < (a.heads + kHeadGroup - 1) / kHeadGroup; ++hg) {
             __syncthreads();
-            // ---- stage 16 heads of q
-            for (int c = tid; c < kHeadGroup * (kKvDim / 8); c += kMlaThreads) {
-                const int h = c / (kKvDim / 8), ch = c - h * (kKvDim / 8);
-                const int head = hg * kHeadGroup + h;
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (head < a.heads) v = *reinterpret_cast<const uint4*>(qg + ((size_t)row * a.heads + head) * kKvDim + ch * 8);
-                *reinterpret_cast<uint4*>(&sm.q[h][ch * 8]) = v;
-            }
-            __syncthreads();
-            // ---- S = Q K^T: warp w owns keys 8w .. 8w+7
+            // ---- S = Q K^T: warp w owns keys 8w .. 8w+7; four accumulators over interleaved k steps keep the
+            // MMAs independent of one another
             {
-                float d[4] = {0.f, 0.f, 0.f, 0.f};
+                float d[4][4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) d[i][j] = 0.f;
                 const uint32_t q_addr = smem_u32(&sm.q[lane & 15][(lane >> 4) * 8]);
                 const uint32_t k_addr = smem_u32(&sm.kv[warp * 8 + (lane & 7)][((lane >> 3) & 1) * 8]);
-#pragma unroll 4
-                for (int ks = 0; ks < kKvDim / 16; ++ks) {
-                    uint32_t af[4], bfr[2];
-                    ldmatrix_x4(af, q_addr + ks * 32);
-                    ldmatrix_x2(bfr, k_addr + ks * 32);
-                    mma_bf16(d, af[0], af[1], af[2], af[3], bfr[0], bfr[1]);
+#pragma unroll
+                for (int ks = 0; ks < kKvDim / 16; ks += 4) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        uint32_t af[4], bfr[2];
+                        ldmatrix_x4(af, q_addr + (ks + u) * 32);
+                        ldmatrix_x2(bfr, k_addr + (ks + u) * 32);
+                        mma_bf16(d[u], af[0], af[1], af[2], af[3], bfr[0], bfr[1]);
+                    }
                 }
+                float dd[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) dd[j] = (d[0][j] + d[1][j]) + (d[2][j] + d[3][j]);
                 const int k0 = warp * 8 + 2 * t4;
                 const bool v0 = sm.valid[k0] >= 0, v1 = sm.valid[k0 + 1] >= 0;
-                sm.s[g][k0] = v0 ? d[0] * a.sm_scale : -INFINITY;
-                sm.s[g][k0 + 1] = v1 ? d[1] * a.sm_scale : -INFINITY;
-                sm.s[g + 8][k0] = v0 ? d[2] * a.sm_scale : -INFINITY;
-                sm.s[g + 8][k0 + 1] = v1 ? d[3] * a.sm_scale : -INFINITY;
+                sm.s[g][k0] = v0 ? dd[0] * a.sm_scale : -INFINITY;
+                sm.s[g][k0 + 1] = v1 ? dd[1] * a.sm_scale : -INFINITY;
+                sm.s[g + 8][k0] = v0 ? dd[2] * a.sm_scale : -INFINITY;
+                sm.s[g + 8][k0 + 1] = v1 ? dd[3] * a.sm_scale : -INFINITY;
             }
             __syncthreads();
-            // ---- split-local softmax: warp w owns heads 2w, 2w+1
+            // ---- running softmax: warp w owns heads 2w, 2w+1
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
                 const int h = warp * 2 + hh;
                 const float s0 = sm.s[h][lane], s1 = sm.s[h][lane + 32];
-                const float m = warp_max(fmaxf(s0, s1));
+                const float m_old = sm.ml[h][0];
+                const float m = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
                 const float p0 = (m == -INFINITY) ? 0.f : __expf(s0 - m);
                 const float p1 = (m == -INFINITY) ? 0.f : __expf(s1 - m);
+                const float rescale = (m == -INFINITY) ? 1.f : __expf(m_old - m);  // e^(-inf) = 0 for the first live chunk
                 const float l = warp_sum(p0 + p1);
                 sm.p[h][lane] = __float2bfloat16_rn(p0);
                 sm.p[h][lane + 32] = __float2bfloat16_rn(p1);
-                if (lane == 0) { sm.ml[h][0] = m; sm.ml[h][1] = l; }
+                if (lane == 0) { sm.ml[h][0] = m; sm.ml[h][1] = sm.ml[h][1] * rescale + l; s_scale[h] = rescale; }
             }
             __syncthreads();
-            // ---- O = P V: warp w owns latent columns 64w .. 64w+63
+            // ---- O = O * rescale + P V
             {
-                float o[8][4];
+                const float r0 = s_scale[g], r1 = s_scale[g + 8];
 #pragma unroll
-                for (int n = 0; n < 8; ++n)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
+                for (int n = 0; n < 8; ++n) { o[n][0] *= r0; o[n][1] *= r0; o[n][2] *= r1; o[n][3] *= r1; }
                 const uint32_t p_addr = smem_u32(&sm.p[lane & 15][(lane >> 4) * 8]);
 #pragma unroll
                 for (int ks = 0; ks < kSplit / 16; ++ks) {
@@ -166,25 +197,28 @@ __global__ void __launch_bounds__(kMlaThreads, 2) sparse_mla_split_kernel(const 
                         mma_bf16(o[2 * n2 + 1], af[0], af[1], af[2], af[3], bfr[2], bfr[3]);
                     }
                 }
-                // ---- partial results: bf16 accumulator, f32 (m, l)
-                const int h0 = hg * kHeadGroup + g, h1 = h0 + 8;
+            }
+        }
+        __syncthreads();
+        // ---- the task's partial: bf16 accumulator, f32 (m, l)
+        {
+            const int h0 = hg * kHeadGroup + g, h1 = h0 + 8;
 #pragma unroll
-                for (int n = 0; n < 8; ++n) {
-                    const int col = warp * 64 + n * 8 + 2 * t4;
-                    if (h0 < a.heads) {
-                        __nv_bfloat162 v = __floats2bfloat162_rn(o[n][0], o[n][1]);
-                        *reinterpret_cast<__nv_bfloat162*>(part_acc + (((size_t)row * nsplit + sp) * a.heads + h0) * 512 + col) = v;
-                    }
-                    if (h1 < a.heads) {
-                        __nv_bfloat162 v = __floats2bfloat162_rn(o[n][2], o[n][3]);
-                        *reinterpret_cast<__nv_bfloat162*>(part_acc + (((size_t)row * nsplit + sp) * a.heads + h1) * 512 + col) = v;
-                    }
+            for (int n = 0; n < 8; ++n) {
+                const int col = warp * 64 + n * 8 + 2 * t4;
+                if (h0 < a.heads) {
+                    __nv_bfloat162 v = __floats2bfloat162_rn(o[n][0], o[n][1]);
+                    *reinterpret_cast<__nv_bfloat162*>(part_acc + (((size_t)row * nsplit + sp) * a.heads + h0) * 512 + col) = v;
                 }
-                if (tid < kHeadGroup && hg * kHeadGroup + tid < a.heads) {
-                    float* ml = part_ml + (((size_t)row * nsplit + sp) * a.heads + hg * kHeadGroup + tid) * 2;
-                    ml[0] = sm.ml[tid][0];
-                    ml[1] = sm.ml[tid][1];
+                if (h1 < a.heads) {
+                    __nv_bfloat162 v = __floats2bfloat162_rn(o[n][2], o[n][3]);
+                    *reinterpret_cast<__nv_bfloat162*>(part_acc + (((size_t)row * nsplit + sp) * a.heads + h1) * 512 + col) = v;
                 }
+            }
+            if (tid < kHeadGroup && hg * kHeadGroup + tid < a.heads) {
+                float* ml = part_ml + (((size_t)row * nsplit + sp) * a.heads + hg * kHeadGroup + tid) * 2;
+                ml[0] = sm.ml[tid][0];
+                ml[1] = sm.ml[tid][1];
             }
         }
     }
@@ -235,6 +269,17 @@ extern "C" size_t mono_sparse_mla_scratch_bytes(int rows, int heads, int topk) {
     return (size_t)rows * nsplit * heads * (512 * sizeof(__nv_bfloat16) + 2 * sizeof(float)) + 256;
 }
 
+// (nsplit, chunks per task): about two rounds of the resident CTAs (2 per SM) over rows x head groups x chunks
+static void mla_plan(int rows, int heads, int topk, int sms, int* nsplit, int* chunks) {
+    const int total = (topk + mono::kSplit - 1) / mono::kSplit;
+    const int hgroups = (heads + mono::kHeadGroup - 1) / mono::kHeadGroup;
+    const long work = (long)rows * hgroups * total;
+    int c = (int)((work + 4L * sms - 1) / (4L * sms));
+    c = c < 1 ? 1 : (c > 32 ? 32 : c);
+    *chunks = c;
+    *nsplit = (total + c - 1) / c;
+}
+
 extern "C" int mono_sparse_mla_launch(const mono_sparse_mla_args* a, void* stream) {
     if (!a || a->rows < 1 || a->rows > MONO_MAX_ROWS || a->heads < 1 || a->heads > 128 || a->topk < 1 ||
         a->topk > 64 * 128 || a->topk_ld < a->topk || !a->q || !a->kv_pages || !a->topk_slots || !a->out || !a->scratch) {
@@ -246,7 +291,9 @@ extern "C" int mono_sparse_mla_launch(const mono_sparse_mla_args* a, void* strea
         mono_set_error("mono_sparse_mla_launch: q, kv_pages and scratch must be 16-byte aligned");
         return MONO_E_ARG;
     }
-    const int nsplit = (a->topk + mono::kSplit - 1) / mono::kSplit;
+    const int sms = mono_sm_count();
+    int nsplit, chunks;
+    mla_plan(a->rows, a->heads, a->topk, sms, &nsplit, &chunks);
     const size_t smem = sizeof(mono::MlaSmem) + 128;
     static thread_local bool attr_set = false;
     if (!attr_set) {
@@ -257,10 +304,9 @@ extern "C" int mono_sparse_mla_launch(const mono_sparse_mla_args* a, void* strea
         }
         attr_set = true;
     }
-    int grid = a->rows * nsplit;
-    const int sms = mono_sm_count();
+    int grid = a->rows * ((a->heads + mono::kHeadGroup - 1) / mono::kHeadGroup) * nsplit;
     if (grid > 2 * sms) grid = 2 * sms;
-    mono::launch_k(mono::sparse_mla_split_kernel, grid, mono::kMlaThreads, smem, (cudaStream_t)stream, *a, nsplit);
+    mono::launch_k(mono::sparse_mla_split_kernel, grid, mono::kMlaThreads, smem, (cudaStream_t)stream, *a, nsplit, chunks);
     mono::launch_k(mono::sparse_mla_merge_kernel, a->rows * a->heads, 256, 0, (cudaStream_t)stream, *a, nsplit);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_sparse_mla_launch: %s", cudaGetErrorString(e));
@@ -339,7 +385,10 @@ extern "C" int mono_sparse_mla_launch_noalloc(const mono_sparse_mla_args* a, voi
     if (scratch == nullptr) return MONO_E_DRIVER;
     mono_sparse_mla_args args = *a;
     args.scratch = scratch;  // whatever the caller put there is ignored
-    const int nsplit = (args.topk + mono::kSplit - 1) / mono::kSplit;
+    const int sms = mono_sm_count();
+    if (sms <= 0) return MONO_E_DRIVER;
+    int nsplit, chunks;
+    mla_plan(args.rows, args.heads, args.topk, sms, &nsplit, &chunks);
     const size_t smem = sizeof(mono::MlaSmem) + 128;
     static thread_local bool attr_set = false;
     if (!attr_set) {
@@ -350,13 +399,11 @@ extern "C" int mono_sparse_mla_launch_noalloc(const mono_sparse_mla_args* a, voi
         }
         attr_set = true;
     }
-    int grid = args.rows * nsplit;
-    const int sms = mono_sm_count();
-    if (sms <= 0) return MONO_E_DRIVER;
+    int grid = args.rows * ((args.heads + mono::kHeadGroup - 1) / mono::kHeadGroup) * nsplit;
     if (grid > 2 * sms) grid = 2 * sms;
     // Nothing in the scratch has to start at zero: every partial the merge reads is
     // written by this call's split kernel first (same stream, so in order).
-    mono::sparse_mla_split_kernel<<<grid, mono::kMlaThreads, smem, (cudaStream_t)stream>>>(args, nsplit);
+    mono::sparse_mla_split_kernel<<<grid, mono::kMlaThreads, smem, (cudaStream_t)stream>>>(args, nsplit, chunks);
     mono::sparse_mla_merge_kernel<<<args.rows * args.heads, 256, 0, (cudaStream_t)stream>>>(args, nsplit);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_sparse_mla_launch_noalloc: %s", cudaGetErrorString(e));
