@@ -327,15 +327,26 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_s;
     pdl_launch_dependents();
-    if (warp == 0 && lane == 0) {
-        // Weights do not depend on the kernel before this one: while it drains, pull this CTA's first
-        // tiles towards L2 (only when the first task is known without upstream data: a dense job 0).
-        const mono_gemv_job& j0 = p.a.job[0];
-        if (j0.mode == MONO_JOB_DENSE && (int)blockIdx.x < tc_nrb(j0) * j0.nsplit) {
-            const int nrb = tc_nrb(j0);
-            const TcSeg s = tc_make_seg(j0, blockIdx.x % nrb, blockIdx.x / nrb, 0);
-            const CUtensorMap* wmap = reinterpret_cast<const CUtensorMap*>(&j0.tmap);
-            for (int t = 0; t < min(s.nt, kTcMaxStages * kTcUnit); ++t) tma_prefetch_3d(wmap, (s.t0 + t) * 128, s.row0, s.c2);
+    if (warp == 0) {
+        // Weights do not depend on the kernel before this one: while it drains, pull this CTA's tiles towards
+        // L2, up to kPrefetchTiles of them (the leading dense jobs only: their task list needs no upstream data).
+        // Short projections then run out of L2 instead of paying the DRAM ramp after the wait.
+        constexpr int kPrefetchTiles = 24;  // 384 KB per CTA, 57 MB over the grid
+        int budget = kPrefetchTiles, base = 0;
+        for (int j = 0; j < p.a.njobs && budget > 0; ++j) {
+            const mono_gemv_job& jb = p.a.job[j];
+            if (jb.mode != MONO_JOB_DENSE) break;
+            const int nrb = tc_nrb(jb), ntask = nrb * jb.nsplit;
+            const CUtensorMap* wmap = reinterpret_cast<const CUtensorMap*>(&jb.tmap);
+            // this CTA's tasks of the job: global task index = base + local, taken round-robin over the grid
+            int first = ((int)blockIdx.x - base) % (int)gridDim.x;
+            if (first < 0) first += gridDim.x;
+            for (int local = first; local < ntask && budget > 0; local += gridDim.x) {
+                const TcSeg s = tc_make_seg(jb, local % nrb, local / nrb, 0);
+                for (int t = lane; t < min(s.nt, budget); t += 32) tma_prefetch_3d(wmap, (s.t0 + t) * 128, s.row0, s.c2);
+                budget -= s.nt;
+            }
+            base += ntask;
         }
     }
     pdl_wait();
@@ -662,6 +673,7 @@ int mono_gemv_tc_launch(const mono_gemv_args* a, long tasks, cudaStream_t st) {
     static const int forced_unit = [] { const char* e = getenv("MONO_TC_UNIT"); return e ? (e[0] == '4' ? 4 : e[0] == '2' ? 2 : 1) : 0; }();
     // (four-tile units: 710 us, the up/gate launch at 0.90 of the measured copy bandwidth; they need long K
     // runs per segment, or a stage is mostly empty)
+    static const long tile_floor = [] { const char* e = getenv("MONO_TC_UNIT2_TILES"); return e ? atol(e) : 12L; }();
     long dense_tiles = 0;
     bool expert = false;
     int min_seg = 1 << 30;
@@ -675,7 +687,7 @@ int mono_gemv_tc_launch(const mono_gemv_args* a, long tasks, cudaStream_t st) {
             dense_tiles += (long)(jb.rb_per_mat > 0 ? jb.n_mats * jb.rb_per_mat : (jb.n_rows + 127) / 128) * jb.k_tiles;
         }
     }
-    int unit = forced_unit ? forced_unit : (expert && min_seg >= 8) ? 4 : (expert || dense_tiles >= 32L * mono_sm_count()) ? 2 : 1;
+    int unit = forced_unit ? forced_unit : (expert && min_seg >= 8) ? 4 : (expert || dense_tiles >= tile_floor * mono_sm_count()) ? 2 : 1;
     if (unit == 4 && planes != 1) unit = 2;  // four-tile stages fit with one activation plane only
     const size_t fixed = 1024 + (size_t)tc_sc_slots(unit) * kTcScRows * kTcMaxSegTiles * sizeof(float) + 512;
     p.stage_bytes = unit * (kTcABytes + planes * kTcBBytes);
