@@ -249,6 +249,10 @@ typedef struct mono_route_args {
     float* coef;            /* out [rows*top_k][16] */
 } mono_route_args;
 int mono_route_launch(const mono_route_args* a, void* stream);
+/* Router logits and routing in one launch: `d` writes the logits that `r` reads (r->logits ==
+ * d->out, one partial sum); the CTA that finishes its logit columns last routes the step.
+ * `counter` is one zeroed device word owned by the caller (the launch leaves it zero). */
+int mono_router_launch(const mono_rowdot_args* d, const mono_route_args* r, int32_t* counter, void* stream);
 
 /* ---- expert activation (glm53/gfx950/kernel.py:4396-4415 SiLU, :5061-5064 mid
  * re-quantisation; minimax_m31/ffn.py:849-852) -----------------------------------
@@ -269,6 +273,8 @@ typedef struct mono_mid_args {
     int scale_ld;
 } mono_mid_args;
 int mono_mid_launch(const mono_mid_args* a, void* stream);
+/* Two activation stages in one launch (the shared expert's and the routed experts'). */
+int mono_mid_pair_launch(const mono_mid_args* a, const mono_mid_args* b, void* stream);
 
 /* ---- sparse MLA decode attention (glm53/gfx950/kernel.py:3638-3973 split,
  * :3975-4075 merge; operator level of BASELINE config 2) --------------------------

@@ -162,7 +162,9 @@ SYMBOLS = {
     "mono_gemv_launch": (i32, [C.POINTER(GemvArgs), vp]),
     "mono_rowdot_launch": (i32, [C.POINTER(RowdotArgs), vp]),
     "mono_route_launch": (i32, [C.POINTER(RouteArgs), vp]),
+    "mono_router_launch": (i32, [C.POINTER(RowdotArgs), C.POINTER(RouteArgs), vp, vp]),
     "mono_mid_launch": (i32, [C.POINTER(MidArgs), vp]),
+    "mono_mid_pair_launch": (i32, [C.POINTER(MidArgs), C.POINTER(MidArgs), vp]),
     "mono_sparse_mla_scratch_bytes": (C.c_size_t, [i32, i32, i32]),
     "mono_sparse_mla_launch": (i32, [C.POINTER(SparseMlaArgs), vp]),
     "mono_sparse_mla_launch_noalloc": (i32, [C.POINTER(SparseMlaArgs), vp]),

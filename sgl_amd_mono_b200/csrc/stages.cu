@@ -155,54 +155,80 @@ __device__ __forceinline__ uint32_t radix_key(float f) {
     return (b & 0x80000000u) ? ~b : (b ^ 0x80000000u);
 }
 
-__global__ void __launch_bounds__(kRouteThreads) route_kernel(const mono_route_args a) {
-    pdl_prologue();
-    __shared__ float sc[kMaxRows][kMaxExperts];
-    __shared__ int used[kMaxExperts];
-    __shared__ int sel[kMaxRows][16];
-    __shared__ float selw[kMaxRows][16];
-    __shared__ int slot_of[kMaxExperts];
-    __shared__ int warp_cnt[kRouteThreads / 32];
+// The routing of one step by one CTA of kRouteThreads threads, one warp per row.  A single CTA runs
+// this code once, so what it costs is the instructions it has to fetch: the loops stay rolled,
+// the row's logits arrive by one batch of asynchronous copies, and the picks scan shared memory.
+struct RouteSmem {
+    float sc[kMaxRows][kMaxExperts];
+    float bias[kMaxExperts];
+    int used[kMaxExperts];
+    int sel[kMaxRows][16];
+    float selw[kMaxRows][16];
+    int slot_of[kMaxExperts];
+    int warp_cnt[kRouteThreads / 32];
+};
+
+__device__ __forceinline__ void route_body(const mono_route_args& a, RouteSmem& sm) {
+    auto& sc = sm.sc;
+    auto& used = sm.used;
+    auto& sel = sm.sel;
+    auto& selw = sm.selw;
+    auto& slot_of = sm.slot_of;
+    auto& warp_cnt = sm.warp_cnt;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    for (int e = tid; e < a.n_experts; e += kRouteThreads) used[e] = 0;
+    // the logits may come from other CTAs of this launch: they are copied past L1 (16-byte
+    // asynchronous copies, all in flight together), or read with ld.cg where that shape does not fit
+    const bool vec = a.nsum == 1 && !(a.ld & 3) && !(a.n_experts & 3) && !(reinterpret_cast<uintptr_t>(a.logits) & 15);
+    if (vec && warp < a.rows) {
+#pragma unroll 1
+        for (int c = lane; c < a.n_experts / 4; c += 32)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(&sc[warp][4 * c])),
+                         "l"(a.logits + (size_t)warp * a.ld + 4 * c)
+                         : "memory");
+    }
+#pragma unroll 1
+    for (int e = tid; e < a.n_experts; e += kRouteThreads) {
+        used[e] = 0;
+        sm.bias[e] = a.bias ? __ldg(a.bias + e) : 0.f;
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
     __syncthreads();
     if (warp < a.rows) {
         const int r = warp;
         const bool live = !a.slots || a.slots[r] >= 0;
+#pragma unroll 1
         for (int e = lane; e < a.n_experts; e += 32) {
             float l = 0.f;
-            for (int s = 0; s < a.nsum; ++s) l += a.logits[(size_t)s * a.sum_stride + (size_t)r * a.ld + e];
+            if (vec) {
+                l = sc[r][e];
+            } else {
+                for (int p = 0; p < a.nsum; ++p) l += __ldcg(a.logits + (size_t)p * a.sum_stride + (size_t)r * a.ld + e);
+            }
             const float s = 1.f / (1.f + expf(-l));
             sc[r][e] = s;
             if (a.scores) a.scores[(size_t)r * a.n_experts + e] = s;
         }
         __syncwarp();
-        // each lane keeps the keys of its experts (lane, lane + 32, ...) in registers; a pick is
-        // a warp-wide maximum of (monotone key, inverted id), so ties go to the lower expert id
-        unsigned long long keys[kMaxExperts / 32];
-#pragma unroll
-        for (int i = 0; i < kMaxExperts / 32; ++i) {
-            const int e = lane + 32 * i;
-            keys[i] = 0ull;
-            if (e < a.n_experts) {
-                const float key = a.bias ? sc[r][e] + a.bias[e] : sc[r][e];
-                keys[i] = ((unsigned long long)radix_key(key) << 32) | (uint32_t)(0x7FFFFFFF - e);
-            }
-        }
+        // a lane owns experts lane, lane + 32, ...; `taken` has one bit per owned expert already picked.
+        // A pick = the largest key (monotone image of score + bias) of the warp, then the lowest
+        // expert id among its holders (a lane's lowest id is its lowest slot: the first strict maximum)
+        uint32_t taken = 0u;
+        const int nslots = (a.n_experts + 31) >> 5;
         float wsum = 0.f;
+#pragma unroll 1
         for (int k = 0; k < a.top_k; ++k) {
-            unsigned long long best = 0ull;
-#pragma unroll
-            for (int i = 0; i < kMaxExperts / 32; ++i) best = keys[i] > best ? keys[i] : best;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
-                best = other > best ? other : best;
+            uint32_t best = 0u;
+            int slot = 0;
+#pragma unroll 1
+            for (int i = 0; i < nslots; ++i) {
+                const int e = lane + 32 * i;
+                uint32_t key = 0u;
+                if (e < a.n_experts && !((taken >> i) & 1u)) key = radix_key(a.bias ? sc[r][e] + sm.bias[e] : sc[r][e]);
+                if (key > best) { best = key; slot = i; }
             }
-            const int e = 0x7FFFFFFF - (int)(uint32_t)(best & 0xFFFFFFFFull);
-#pragma unroll
-            for (int i = 0; i < kMaxExperts / 32; ++i)
-                if (keys[i] == best) keys[i] = 0ull;  // only the owner lane holds it
+            const uint32_t top = __reduce_max_sync(0xffffffffu, best);
+            const int e = (int)__reduce_min_sync(0xffffffffu, best == top ? (uint32_t)(lane + 32 * slot) : 0xFFFFFFFFu);
+            if (lane == (e & 31)) taken |= 1u << (e >> 5);
             if (lane == 0) { sel[r][k] = e; selw[r][k] = sc[r][e]; }
             wsum += sc[r][e];
         }
@@ -242,6 +268,12 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const mono_route_a
     }
 }
 
+__global__ void __launch_bounds__(kRouteThreads) route_kernel(const mono_route_args a) {
+    __shared__ RouteSmem sm;
+    pdl_prologue();
+    route_body(a, sm);
+}
+
 // ------------------------------------------------------------------ small row-dot GEMV
 // out[r][n] = sum_k x[r][k] * W[n][k] on CUDA cores, one warp per output column, for
 // matrices too small to be worth a tensor-core launch (router logits with f32 or bf16
@@ -249,13 +281,14 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const mono_route_a
 // order is fixed (lane-strided, then a butterfly), so every rank gets the same bits.
 constexpr int kRowdotThreads = 256;
 
-__global__ void __launch_bounds__(kRowdotThreads) rowdot_kernel(const mono_rowdot_args a) {
-    pdl_prologue();
-    // one CTA per output column; the 256 threads split K (4 values per thread per 1024),
-    // so every weight load of the column is in flight at once
-    __shared__ float red[kRowdotThreads / 32][kMaxRows];
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n = blockIdx.x;
+// Column n by the 256 threads tid = 0..255 of one group (every thread of the CTA calls this:
+// it holds a CTA-wide barrier).  The weights do not depend on the launch before this one, so
+// the first batch of weight loads is issued before the wait on that launch.
+__device__ __forceinline__ void rowdot_col(const mono_rowdot_args& a, int n, int tid, float (*red)[kMaxRows]) {
+    // the 256 threads split K (4 values per thread per 1024), so every weight load of the
+    // column is in flight at once
+    const int warp = tid >> 5, lane = tid & 31;
+    const bool active = n < a.n;
     float acc[kMaxRows];
 #pragma unroll
     for (int r = 0; r < kMaxRows; ++r) acc[r] = 0.f;
@@ -267,7 +300,7 @@ __global__ void __launch_bounds__(kRowdotThreads) rowdot_kernel(const mono_rowdo
         for (int it = 0; it < 8; ++it) {
             const int k = k0 + (it * kRowdotThreads + tid) * 4;
             wv[it] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (k < a.k) {
+            if (k < a.k && active) {
                 if (a.w_is_f32) {
                     wv[it] = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.w) + (size_t)n * a.k + k));
                 } else {
@@ -278,10 +311,11 @@ __global__ void __launch_bounds__(kRowdotThreads) rowdot_kernel(const mono_rowdo
                 }
             }
         }
+        if (k0 == 0) pdl_wait();  // the activations come from the launch before this one
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
             const int k = k0 + (it * kRowdotThreads + tid) * 4;
-            if (k < a.k) {
+            if (k < a.k && active) {
 #pragma unroll
                 for (int r = 0; r < kMaxRows; ++r) {
                     if (r < a.rows) {
@@ -302,7 +336,7 @@ __global__ void __launch_bounds__(kRowdotThreads) rowdot_kernel(const mono_rowdo
         }
     }
     __syncthreads();
-    if (tid < a.rows) {
+    if (tid < a.rows && active) {
         float s = 0.f;
 #pragma unroll
         for (int wv = 0; wv < kRowdotThreads / 32; ++wv) s += red[wv][tid];
@@ -310,13 +344,43 @@ __global__ void __launch_bounds__(kRowdotThreads) rowdot_kernel(const mono_rowdo
     }
 }
 
+__global__ void __launch_bounds__(kRowdotThreads) rowdot_kernel(const mono_rowdot_args a) {
+    // one CTA per output column
+    __shared__ float red[kRowdotThreads / 32][kMaxRows];
+    pdl_launch_dependents();
+    rowdot_col(a, blockIdx.x, threadIdx.x, red);
+}
+
+// Router logits and routing in one launch: every CTA computes two columns of the logits (one per
+// group of 256 threads, the arithmetic of rowdot_kernel), and the CTA that finishes last routes the
+// step.  No CTA waits for another: the last one is known from a counter, which it puts back to zero.
+constexpr int kRouterCols = kRouteThreads / kRowdotThreads;
+
+__global__ void __launch_bounds__(kRouteThreads) router_kernel(const mono_rowdot_args d, const mono_route_args r, int32_t* counter) {
+    __shared__ float red[kRouterCols][kRowdotThreads / 32][kMaxRows];
+    __shared__ RouteSmem sm;
+    __shared__ int is_last;
+    pdl_launch_dependents();
+    const int group = threadIdx.x / kRowdotThreads, t = threadIdx.x - group * kRowdotThreads;
+    rowdot_col(d, blockIdx.x * kRouterCols + group, t, red[group]);
+    __threadfence();  // this CTA's logits are visible device-wide before it is counted
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int prev = atomicAdd(counter, 1);
+        is_last = prev == (int)gridDim.x - 1;
+        if (is_last) *counter = 0;  // every CTA of this launch has been counted
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    route_body(r, sm);
+}
+
 // ------------------------------------------------------------------ expert activation
 constexpr int kMidThreads = 256;
 
-__global__ void __launch_bounds__(kMidThreads) mid_kernel(const mono_mid_args a) {
-    pdl_prologue();
-    __shared__ float chunk[kMidThreads / 32][128];
-    const int slot = blockIdx.x / a.rows, row = blockIdx.x - slot * a.rows;
+__device__ __forceinline__ void mid_body(const mono_mid_args& a, int block, float (*chunk)[128]) {
+    const int slot = block / a.rows, row = block - slot * a.rows;
     const int nslot = a.n_slot ? min(*a.n_slot, a.max_slot) : a.max_slot;
     if (slot >= nslot) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -348,6 +412,22 @@ __global__ void __launch_bounds__(kMidThreads) mid_kernel(const mono_mid_args a)
         quant_chunk128(chunk[warp], a.fmt, lane, c, p0, nullptr, sf, s8);
         __syncwarp();
     }
+}
+
+__global__ void __launch_bounds__(kMidThreads) mid_kernel(const mono_mid_args a) {
+    pdl_prologue();
+    __shared__ float chunk[kMidThreads / 32][128];
+    mid_body(a, blockIdx.x, chunk);
+}
+
+// Two activation stages in one launch (the shared expert's and the routed experts'): blocks
+// [0, a.max_slot * a.rows) serve `a`, the rest `b`.
+__global__ void __launch_bounds__(kMidThreads) mid_pair_kernel(const mono_mid_args a, const mono_mid_args b) {
+    pdl_prologue();
+    __shared__ float chunk[kMidThreads / 32][128];
+    const int na = a.max_slot * a.rows;
+    if ((int)blockIdx.x < na) mid_body(a, blockIdx.x, chunk);
+    else mid_body(b, blockIdx.x - na, chunk);
 }
 
 // ------------------------------------------------------------------ reduce + all-reduce
@@ -502,6 +582,26 @@ extern "C" int mono_rowdot_launch(const mono_rowdot_args* a, void* stream) {
     return (int)e;
 }
 
+extern "C" int mono_router_launch(const mono_rowdot_args* d, const mono_route_args* r, int32_t* counter, void* stream) {
+    if (!d || !r || !counter || d->rows < 1 || d->rows > MONO_MAX_ROWS || d->n < 1 || d->k < 128 || (d->k & 127) || !d->w ||
+        !d->x_bf16 || !d->out) {
+        mono_set_error("mono_router_launch: rows 1..16, k a multiple of 128, a counter and all pointers required");
+        return MONO_E_ARG;
+    }
+    if (r->rows != d->rows || r->n_experts != d->n || r->n_experts > mono::kMaxExperts || r->top_k < 1 || r->top_k > 16 ||
+        r->top_k > r->n_experts || r->logits != d->out || r->nsum != 1 || r->ld != d->out_ld || !r->ids || !r->weights ||
+        !r->expert_list || !r->n_expert || !r->coef) {
+        mono_set_error("mono_router_launch: the routing must read the logits this launch writes (same rows, experts and "
+                       "leading dimension, one partial sum), experts 1..512, top_k 1..16");
+        return MONO_E_ARG;
+    }
+    const int grid = (d->n + mono::kRouterCols - 1) / mono::kRouterCols;
+    mono::launch_k(mono::router_kernel, grid, mono::kRouteThreads, 0, (cudaStream_t)stream, *d, *r, counter);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) mono_set_error("mono_router_launch: %s", cudaGetErrorString(e));
+    return (int)e;
+}
+
 extern "C" int mono_mid_launch(const mono_mid_args* a, void* stream) {
     if (!a || a->rows < 1 || a->rows > MONO_MAX_ROWS || a->inter < 128 || (a->inter & 127) || !a->up || !a->planes ||
         a->max_slot < 1) {
@@ -515,6 +615,23 @@ extern "C" int mono_mid_launch(const mono_mid_args* a, void* stream) {
     mono::launch_k(mono::mid_kernel, a->max_slot * a->rows, mono::kMidThreads, 0, (cudaStream_t)stream, *a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_mid_launch: %s", cudaGetErrorString(e));
+    return (int)e;
+}
+
+static int mid_check(const mono_mid_args* a) {
+    if (!a || a->rows < 1 || a->rows > MONO_MAX_ROWS || a->inter < 128 || (a->inter & 127) || !a->up || !a->planes || a->max_slot < 1) return 1;
+    if ((a->fmt == MONO_ACT_A8 && !a->scale_f32) || ((a->fmt == MONO_ACT_MX8 || a->fmt == MONO_ACT_MX8N) && !a->scale_e8) || a->fmt == MONO_ACT_HILO) return 1;
+    return 0;
+}
+
+extern "C" int mono_mid_pair_launch(const mono_mid_args* a, const mono_mid_args* b, void* stream) {
+    if (mid_check(a) || mid_check(b)) {
+        mono_set_error("mono_mid_pair_launch: both stages need rows 1..16, inter a multiple of 128, buffers and a supported format");
+        return MONO_E_ARG;
+    }
+    mono::launch_k(mono::mid_pair_kernel, a->max_slot * a->rows + b->max_slot * b->rows, mono::kMidThreads, 0, (cudaStream_t)stream, *a, *b);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) mono_set_error("mono_mid_pair_launch: %s", cudaGetErrorString(e));
     return (int)e;
 }
 

@@ -109,6 +109,11 @@ class MoeFfn:
                       expert_list=self.expert_list, n_expert=self.n_expert, max_expert=self.max_expert,
                       coef=self.coef, nsplit=self.groups)
         self.out = z(L.MAX_ROWS, h, dt=torch.bfloat16)
+        # MONO_ROUTER_FUSED=1: router logits and routing in one launch (the last CTA routes).  Measured
+        # 2-3 us slower than two launches: the routing is a serial tail either way, and as a launch of
+        # its own its start-up overlaps the logits under programmatic dependent launch
+        self.route_counter = z(1, dt=torch.int32)
+        self.router_fused = os.environ.get("MONO_ROUTER_FUSED", "0") != "0"
         # ---- one launch for up/gate -> SwiGLU -> down (FP8 on the tcgen05 path): the same jobs, chained
         self.chained = None
         # (the CTA that finishes an expert's last up/gate task computes the whole activation of that expert:
@@ -147,9 +152,13 @@ class MoeFfn:
         ops.act_prep(rows, h, self.xq, src_bf16=residual, gamma=w["post_norm"], eps=cfg.eps, out_bf16=self.xbf)
         if self.has_shared and self.xs is not self.xq:
             ops.act_prep(rows, h, self.xs, src_bf16=self.xbf, round_bf16=False)
-        ops.rowdot(rows, w["router"], self.xbf, self.logits)
-        ops.route(rows, cfg.top_k, cfg.route_scale, self.logits, w.get("router_bias"), slots, self.ids,
-                  self.weights, self.scores, self.expert_list, self.n_expert, self.coef)
+        rt = (rows, cfg.top_k, cfg.route_scale, self.logits, w.get("router_bias"), slots, self.ids,
+              self.weights, self.scores, self.expert_list, self.n_expert, self.coef)
+        if self.router_fused:
+            ops.router(ops.rowdot_args(rows, w["router"], self.xbf, self.logits), ops.route_args(*rt), self.route_counter)
+        else:
+            ops.rowdot(rows, w["router"], self.xbf, self.logits)
+            ops.route(*rt)
         if self.chained is not None:
             self.chained.launch(rows)
             ops.reduce_rows(rows, h, self.down_p, self.n_slices, self.out, residual=residual, slots=slots,
@@ -158,11 +167,15 @@ class MoeFfn:
         self.up.launch(rows)
         if self.up_sh is not None:
             self.up_sh.launch(rows)
-        ops.mid(rows, il, self.up_r, self.ns_up, self.mid_r, n_slot=self.n_expert, max_slot=self.max_expert,
-                round_bf16=cfg.expert_fmt != "fp8_block")
-        if self.has_shared:
-            ops.mid(rows, il, self.up_s, self.ns_up_s, self.mid_s, max_slot=1,
-                    round_bf16=cfg.shared_fmt != "fp8_block")
+        routed = ops.mid_args(rows, il, self.up_r, self.ns_up, self.mid_r, n_slot=self.n_expert, max_slot=self.max_expert,
+                              round_bf16=cfg.expert_fmt != "fp8_block")
+        if self.has_shared:  # both activation stages in one launch
+            shared = ops.mid_args(rows, il, self.up_s, self.ns_up_s, self.mid_s, max_slot=1,
+                                  round_bf16=cfg.shared_fmt != "fp8_block")
+            ops.mid_pair(routed, shared)
+        else:
+            ops.mid(rows, il, self.up_r, self.ns_up, self.mid_r, n_slot=self.n_expert, max_slot=self.max_expert,
+                    round_bf16=cfg.expert_fmt != "fp8_block")
         self.down.launch(rows)
         if self.down_sh is not None:
             self.down_sh.launch(rows)

@@ -236,13 +236,18 @@ class Gemv:
         L.check(L.load().mono_gemv_launch(C.byref(self.args), _stream()), "mono_gemv_launch")
 
 
-def rowdot(rows: int, w: torch.Tensor, x_bf16: torch.Tensor, out: torch.Tensor, out_scale: float = 1.0) -> None:
+def rowdot_args(rows: int, w: torch.Tensor, x_bf16: torch.Tensor, out: torch.Tensor, out_scale: float = 1.0) -> "L.RowdotArgs":
     a = L.RowdotArgs()
     a.rows, a.n, a.k = rows, w.shape[0], w.shape[1]
     a.w, a.w_is_f32 = w.data_ptr(), int(w.dtype == torch.float32)
     if w.dtype not in (torch.float32, torch.bfloat16):
         raise ValueError(f"rowdot weight dtype {w.dtype}")
     a.x_bf16, a.out, a.out_ld, a.out_scale = x_bf16.data_ptr(), out.data_ptr(), out.shape[-1], out_scale
+    return a
+
+
+def rowdot(rows: int, w: torch.Tensor, x_bf16: torch.Tensor, out: torch.Tensor, out_scale: float = 1.0) -> None:
+    a = rowdot_args(rows, w, x_bf16, out, out_scale)
     L.check(L.load().mono_rowdot_launch(C.byref(a), _stream()), "mono_rowdot_launch")
 
 
@@ -353,23 +358,44 @@ def guard_read(guard: torch.Tensor):
     return rc, tuple(out)
 
 
-def route(rows: int, cfg_top_k: int, route_scale: float, logits, bias, slots, ids, weights, scores,
-          expert_list, n_expert, coef) -> None:
+def route_args(rows: int, cfg_top_k: int, route_scale: float, logits, bias, slots, ids, weights, scores,
+               expert_list, n_expert, coef) -> "L.RouteArgs":
     a = L.RouteArgs()
     a.rows, a.n_experts, a.top_k, a.route_scale = rows, logits.shape[-1], cfg_top_k, route_scale
     a.logits, a.nsum, a.ld, a.sum_stride = logits.data_ptr(), 1, logits.shape[-1], 0
     a.bias, a.slots = _p(bias), _p(slots)
     a.ids, a.weights, a.scores = ids.data_ptr(), weights.data_ptr(), _p(scores)
     a.expert_list, a.n_expert, a.coef = expert_list.data_ptr(), n_expert.data_ptr(), coef.data_ptr()
+    return a
+
+
+def route(rows: int, cfg_top_k: int, route_scale: float, logits, bias, slots, ids, weights, scores,
+          expert_list, n_expert, coef) -> None:
+    a = route_args(rows, cfg_top_k, route_scale, logits, bias, slots, ids, weights, scores, expert_list, n_expert, coef)
     L.check(L.load().mono_route_launch(C.byref(a), _stream()), "mono_route_launch")
 
 
-def mid(rows: int, inter: int, up: torch.Tensor, nsum: int, dst: ActBuf, *, n_slot=None, max_slot: int = 1,
-        round_bf16: bool = False) -> None:
+def router(dot: "L.RowdotArgs", rt: "L.RouteArgs", counter: torch.Tensor) -> None:
+    """Router logits and routing in one launch; ``counter`` is one zeroed int32 word on the device."""
+    L.check(L.load().mono_router_launch(C.byref(dot), C.byref(rt), counter.data_ptr(), _stream()), "mono_router_launch")
+
+
+def mid_args(rows: int, inter: int, up: torch.Tensor, nsum: int, dst: ActBuf, *, n_slot=None, max_slot: int = 1,
+             round_bf16: bool = False) -> "L.MidArgs":
     a = L.MidArgs()
     a.rows, a.inter, a.up, a.nsum = rows, inter, up.data_ptr(), nsum
     a.n_slot, a.max_slot = _p(n_slot), max_slot
     a.fmt, a.round_bf16 = dst.fmt, int(round_bf16)
     a.planes, a.ld = dst.planes.data_ptr(), dst.ld
     a.scale_f32, a.scale_e8, a.scale_ld = _p(dst.scale_f32), _p(dst.scale_e8), dst.scale_ld
+    return a
+
+
+def mid(rows: int, inter: int, up: torch.Tensor, nsum: int, dst: ActBuf, **kw) -> None:
+    a = mid_args(rows, inter, up, nsum, dst, **kw)
     L.check(L.load().mono_mid_launch(C.byref(a), _stream()), "mono_mid_launch")
+
+
+def mid_pair(a: "L.MidArgs", b: "L.MidArgs") -> None:
+    """Two activation stages (routed experts and the shared expert) in one launch."""
+    L.check(L.load().mono_mid_pair_launch(C.byref(a), C.byref(b), _stream()), "mono_mid_pair_launch")

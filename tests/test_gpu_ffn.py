@@ -121,6 +121,51 @@ def test_chained_launch_equals_separate_launches(rows, monkeypatch):
     assert rc == 0, f"guard words {words}"
 
 
+@pytest.mark.parametrize("cfg_name,rows", [("moe8", 1), ("moe8", 16), ("ffn", 11)])
+def test_fused_router_equals_two_launches(cfg_name, rows, monkeypatch):
+    """Logits and routing in one launch (the last CTA to finish its columns routes the step) give the
+    bits of the logits launch followed by the routing launch, on every replay."""
+    cfg = CFG_TINY_MOE8 if cfg_name == "moe8" else CFG_TINY_FFN
+    monkeypatch.setenv("MONO_ROUTER_FUSED", "1")
+    ffn, w, x, slots, out = _run(cfg, rows)
+    assert ffn.router_fused
+    monkeypatch.setenv("MONO_ROUTER_FUSED", "0")
+    ffn2, _, _, _, out2 = _run(cfg, rows)
+    assert not ffn2.router_fused
+    xd, sd = x.to(DEV), slots.to(DEV)
+    for _ in range(3):
+        for name in ("logits", "scores", "ids", "weights", "n_expert"):
+            assert torch.equal(getattr(ffn, name)[:rows], getattr(ffn2, name)[:rows]), name
+        n = int(ffn.n_expert.item())
+        assert torch.equal(ffn.expert_list[:n], ffn2.expert_list[:n])
+        assert torch.equal(ffn.coef[:n], ffn2.coef[:n])
+        assert torch.equal(out, out2)
+        assert int(ffn.route_counter.item()) == 0, "the launch leaves its counter at zero"
+        out = ffn(xd, sd).clone()
+        torch.cuda.synchronize()
+
+
+def test_paired_activation_launch_equals_two_launches(monkeypatch):
+    """The shared expert's and the routed experts' activation stages in one launch write the bytes of
+    the two single launches."""
+    cfg, rows = CFG_TINY_MOE8, 7
+    monkeypatch.setenv("MONO_MOE_CHAINED", "0")
+    ffn, w, x, slots, out = _run(cfg, rows)
+    assert ffn.chained is None and ffn.has_shared
+    il = cfg.inter_local
+    ref_r = ops.ActBuf(ffn.mid_r.fmt, il, DEV, segs=ffn.max_expert)
+    ref_s = ops.ActBuf(ffn.mid_s.fmt, il, DEV)
+    ops.mid(rows, il, ffn.up_r, ffn.ns_up, ref_r, n_slot=ffn.n_expert, max_slot=ffn.max_expert)
+    ops.mid(rows, il, ffn.up_s, ffn.ns_up_s, ref_s, max_slot=1)
+    torch.cuda.synchronize()
+    n = int(ffn.n_expert.item())
+    assert torch.equal(ffn.mid_r.planes[:n], ref_r.planes[:n])
+    assert torch.equal(ffn.mid_r.scale_f32[:n, :rows], ref_r.scale_f32[:n, :rows])
+    assert torch.equal(ffn.mid_s.planes, ref_s.planes)
+    assert torch.equal(ffn.mid_s.scale_f32[..., :rows, :], ref_s.scale_f32[..., :rows, :])
+    assert ffn.mid_s.planes.any() and ffn.mid_r.planes[:n].any()
+
+
 def test_replays_are_bit_equal():
     cfg = CFG_TINY_MOE8
     ffn, w, x, slots, out = _run(cfg, 8)

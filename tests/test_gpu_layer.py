@@ -159,3 +159,33 @@ def test_topk_long_context_matches_oracle():
     for i in range(rows):
         want = S.exact_topk_positions(scores[i], int(pos[i]) + 1, k)
         assert outp[i].cpu().tolist() == want.tolist(), f"row {i}"
+
+
+@pytest.mark.parametrize("n", [16384, 9001, 2049])
+def test_register_topk_equals_general_topk_and_oracle(n, monkeypatch):
+    """Rows of up to 16K positions keep their keys in registers: same slots and positions, in the
+    same order, as the general kernel and as the oracle's exact selection (ties, negative scores,
+    a short row and a pad row included)."""
+    rows, k, ld = 5, 2048, 16384
+    g = torch.Generator().manual_seed(n)
+    scores = torch.randn(16, ld, generator=g)
+    scores[1, ::2] = -0.5          # ties below and above zero
+    scores[2] = scores[2].round()  # few distinct values: long tie runs at the threshold
+    scores[3, :n] = torch.linspace(-4, 4, n)
+    pt = torch.randperm(400, generator=g)[: ld // 64].to(torch.int32).repeat(rows, 1)
+    pos = torch.tensor([n - 1, n - 1, n - 1, n - 1, 100])
+    slots = torch.tensor([1, 1, 1, 1, -1], dtype=torch.int64)
+    got = {}
+    for sw in ("1", "0"):
+        monkeypatch.setenv("MONO_TOPK_REGS", sw)
+        out = torch.full((16, k), -7, dtype=torch.int32, device=DEV)
+        outp = torch.full((16, k), -7, dtype=torch.int32, device=DEV)
+        a = ops.index_args(rows, 1, k, None, None, None, pt.to(DEV), pos.to(DEV), slots.to(DEV), scores.to(DEV), out, outp)
+        ops.index_topk(a)
+        torch.cuda.synchronize()
+        got[sw] = (out[:rows].cpu(), outp[:rows].cpu())
+    assert torch.equal(got["1"][0], got["0"][0]) and torch.equal(got["1"][1], got["0"][1])
+    for i in range(4):
+        want = S.exact_topk_positions(scores[i], n, k)
+        assert got["1"][1][i].tolist() == want.tolist(), f"row {i}"
+    assert int((got["1"][0][4] >= 0).sum()) == 0, "a pad row selects nothing"
