@@ -6,7 +6,10 @@
 // and :3341-3346 (publication as global KV slots); FP4 index keys with one E8M0 code
 // per 32 dims as deepseek_v4/gfx950/kernels/stages/indexer.py:143-151.
 #include <cstdlib>
+#include <cooperative_groups.h>
 #include "mono_common.cuh"
+
+namespace cg = cooperative_groups;
 
 extern void mono_set_error(const char* fmt, ...);
 
@@ -270,60 +273,72 @@ __global__ void __launch_bounds__(kTopkThreads) index_topk_kernel(const mono_ind
     }
 }
 
-// The same selection for rows of up to kTopkThreads * kRegKeys positions, with the row's keys in
-// registers (key j of a thread is position j * kTopkThreads + tid): no shared-memory traffic for
-// the keys, every loop over them unrolled.  Output order as above: keys above the k-th in position
-// order, then the first ties in position order.
-constexpr int kRegKeys = 16;
+// The same selection for rows of up to 16K positions by a cluster of eight CTAs per row: CTA c of
+// the cluster holds positions 2048 c .. 2048 c + 2047 in registers (two keys per thread).  A pass
+// counts into the CTA's own histogram; after one cluster barrier every CTA adds the eight histograms
+// over distributed shared memory and takes the same decision.  The histograms alternate between two
+// buffers, so a pass needs one cluster barrier: a buffer is zeroed again only after the barrier of
+// the pass in between, which no CTA reaches before it has read that buffer.  Output order as above.
+constexpr int kClSize = 8;
+constexpr int kClKeys = 2;
+constexpr int kClSpan = kTopkThreads * kClKeys;
 
-__global__ void __launch_bounds__(kTopkThreads) index_topk_reg_kernel(const mono_index_args a) {
+__global__ void __cluster_dims__(kClSize, 1, 1) __launch_bounds__(kTopkThreads)
+    index_topk_cluster_kernel(const mono_index_args a) {
     pdl_prologue();
-    __shared__ int hist[256];
+    cg::cluster_group cluster = cg::this_cluster();
+    __shared__ int hist[2][256];
     __shared__ uint32_t s_prefix;
     __shared__ int s_krem;
-    __shared__ int wsum[kTopkThreads / 32];
-    __shared__ int cnt_gt[kRegKeys * 32], cnt_eq[kRegKeys * 32];  // [j][warp], then their exclusive prefixes
-    __shared__ int part_gt[16], part_eq[16];
-    const int row = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    __shared__ int wsum[8];
+    __shared__ int cnt_gt[kClKeys * 32], cnt_eq[kClKeys * 32];  // [j][warp], then their exclusive prefixes
+    __shared__ int part_gt[kClKeys], part_eq[kClKeys];
+    __shared__ int ctot[2];    // this CTA's keys above the threshold / equal to it
+    __shared__ int s_base[2];  // the same, summed over the CTAs before this one
+    const int row = blockIdx.x / kClSize, crank = (int)cluster.block_rank();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     int32_t* out = a.topk_slots + (size_t)row * a.topk;
     int32_t* outp = a.topk_pos ? a.topk_pos + (size_t)row * a.topk : nullptr;
     const bool live = !a.slots || a.slots[row] >= 0;
     const int n = live ? (int)a.positions[row] + 1 : 0;
     const int32_t* pt = a.page_table + (size_t)row * a.pt_ld;
-    if (n <= a.topk) {
-        for (int i = tid; i < a.topk; i += kTopkThreads) {
-            int32_t v = -1;
-            if (i < n) v = pt[i / kPage] * kPage + i % kPage;
-            out[i] = v;
-            if (outp) outp[i] = i < n ? i : -1;
+    if (n <= a.topk) {  // the same for every CTA of the cluster: none of them reaches a cluster barrier
+        if (crank == 0) {
+            for (int i = tid; i < a.topk; i += kTopkThreads) {
+                int32_t v = -1;
+                if (i < n) v = pt[i / kPage] * kPage + i % kPage;
+                out[i] = v;
+                if (outp) outp[i] = i < n ? i : -1;
+            }
         }
         return;
     }
     const float* sc = a.scores + (size_t)row * a.score_ld;
-    uint32_t key[kRegKeys];
+    const int pos0 = crank * kClSpan + tid;
+    uint32_t key[kClKeys];
 #pragma unroll
-    for (int j = 0; j < kRegKeys; ++j) {
-        const int i = j * kTopkThreads + tid;
+    for (int j = 0; j < kClKeys; ++j) {
+        const int i = pos0 + j * kTopkThreads;
         key[j] = i < n ? score_key(sc[i]) : 0u;
     }
     if (tid == 0) { s_prefix = 0; s_krem = a.topk; }
     for (int pass = 3; pass >= 0; --pass) {
-        if (tid < 256) hist[tid] = 0;
+        int* h = hist[pass & 1];
+        if (tid < 256) h[tid] = 0;
         __syncthreads();
         const uint32_t prefix = s_prefix;
         const int krem = s_krem;
         const int shift = pass * 8;
-        // keys of one row share their leading bytes: a thread adds a run of equal bins with one atomic
         int cur = -1, run = 0;
 #pragma unroll
-        for (int j = 0; j < kRegKeys; ++j) {
+        for (int j = 0; j < kClKeys; ++j) {
             const uint32_t k = key[j];
-            if (j * kTopkThreads + tid < n && (pass == 3 || (k >> (shift + 8)) == prefix)) {
+            if (pos0 + j * kTopkThreads < n && (pass == 3 || (k >> (shift + 8)) == prefix)) {
                 const int bin = (int)((k >> shift) & 0xFF);
                 if (bin == cur) {
                     ++run;
                 } else {
-                    if (run) atomicAdd(&hist[cur], run);
+                    if (run) atomicAdd(&h[cur], run);
                     cur = bin;
                     run = 1;
                 }
@@ -333,15 +348,16 @@ __global__ void __launch_bounds__(kTopkThreads) index_topk_reg_kernel(const mono
             const int c0 = __shfl_sync(0xffffffffu, cur, 0);
             if (__all_sync(0xffffffffu, cur == c0 && run > 0)) {  // the whole warp ends in one bin
                 const int tot = __reduce_add_sync(0xffffffffu, run);
-                if (lane == 0) atomicAdd(&hist[c0], tot);
+                if (lane == 0) atomicAdd(&h[c0], tot);
             } else if (run) {
-                atomicAdd(&hist[cur], run);
+                atomicAdd(&h[cur], run);
             }
         }
-        __syncthreads();
+        cluster.sync();
         int mine = 0, suffix = 0;
         if (tid < 256) {
-            mine = hist[tid];
+#pragma unroll
+            for (int r = 0; r < kClSize; ++r) mine += cluster.map_shared_rank(h, r)[tid];
             suffix = mine;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
@@ -364,18 +380,18 @@ __global__ void __launch_bounds__(kTopkThreads) index_topk_reg_kernel(const mono
     const uint32_t thr = s_prefix;
     const int remain = s_krem;  // ties to take
     const int n_gt = a.topk - remain;
-    // position order = (j, warp, lane): counts per (j, warp), one exclusive scan over the 512 of them
+    // position order = (CTA, j, warp, lane)
     const uint32_t lt = (1u << lane) - 1;
 #pragma unroll
-    for (int j = 0; j < kRegKeys; ++j) {
-        const bool ok = j * kTopkThreads + tid < n;
+    for (int j = 0; j < kClKeys; ++j) {
+        const bool ok = pos0 + j * kTopkThreads < n;
         const uint32_t m_gt = __ballot_sync(0xffffffffu, ok && key[j] > thr);
         const uint32_t m_eq = __ballot_sync(0xffffffffu, ok && key[j] == thr);
         if (lane == 0) { cnt_gt[j * 32 + warp] = __popc(m_gt); cnt_eq[j * 32 + warp] = __popc(m_eq); }
     }
     __syncthreads();
     int g = 0, e = 0, gi = 0, ei = 0;
-    if (tid < kRegKeys * 32) {
+    if (tid < kClKeys * 32) {
         g = gi = cnt_gt[tid];
         e = ei = cnt_eq[tid];
 #pragma unroll
@@ -386,27 +402,47 @@ __global__ void __launch_bounds__(kTopkThreads) index_topk_reg_kernel(const mono
         if (lane == 31) { part_gt[warp] = gi; part_eq[warp] = ei; }
     }
     __syncthreads();
-    if (tid < kRegKeys * 32) {
+    if (tid < kClKeys * 32) {
         int bg = 0, be = 0;
         for (int w = 0; w < warp; ++w) { bg += part_gt[w]; be += part_eq[w]; }
         cnt_gt[tid] = bg + gi - g;
         cnt_eq[tid] = be + ei - e;
     }
+    if (tid == 0) {
+        int tg = 0, te = 0;
+        for (int w = 0; w < kClKeys; ++w) { tg += part_gt[w]; te += part_eq[w]; }
+        ctot[0] = tg;
+        ctot[1] = te;
+    }
+    cluster.sync();
+    if (warp == 0) {
+        int bg = 0, be = 0;
+        if (lane < crank) {
+            const int* rt = cluster.map_shared_rank(ctot, lane);
+            bg = rt[0];
+            be = rt[1];
+        }
+        bg = __reduce_add_sync(0xffffffffu, bg);
+        be = __reduce_add_sync(0xffffffffu, be);
+        if (lane == 0) { s_base[0] = bg; s_base[1] = be; }
+    }
     __syncthreads();
+    const int base_gt = s_base[0], base_eq = s_base[1];
 #pragma unroll
-    for (int j = 0; j < kRegKeys; ++j) {
-        const int i = j * kTopkThreads + tid;
+    for (int j = 0; j < kClKeys; ++j) {
+        const int i = pos0 + j * kTopkThreads;
         const bool ok = i < n;
         const bool gt = ok && key[j] > thr, eq = ok && key[j] == thr;
         const uint32_t m_gt = __ballot_sync(0xffffffffu, gt), m_eq = __ballot_sync(0xffffffffu, eq);
         int dst = -1;
-        if (gt) dst = cnt_gt[j * 32 + warp] + __popc(m_gt & lt);
-        else if (eq) { const int q = cnt_eq[j * 32 + warp] + __popc(m_eq & lt); if (q < remain) dst = n_gt + q; }
+        if (gt) dst = base_gt + cnt_gt[j * 32 + warp] + __popc(m_gt & lt);
+        else if (eq) { const int q = base_eq + cnt_eq[j * 32 + warp] + __popc(m_eq & lt); if (q < remain) dst = n_gt + q; }
         if (dst >= 0) {
             out[dst] = pt[i / kPage] * kPage + i % kPage;
             if (outp) outp[dst] = i;
         }
     }
+    cluster.sync();  // no CTA leaves while another may still read its shared memory
 }
 
 }  // namespace mono
@@ -448,11 +484,11 @@ extern "C" int mono_index_topk_launch(const mono_index_args* a, void* stream) {
         mono_set_error("mono_index_topk_launch: topk_slots required");
         return MONO_E_ARG;
     }
-    // rows of up to 16K positions keep their radix keys in registers (MONO_TOPK_REGS=0: the general kernel)
-    if (a->score_ld <= mono::kTopkThreads * mono::kRegKeys) {
-        const char* sw = getenv("MONO_TOPK_REGS");
+    // rows of up to 16K positions: a cluster of eight CTAs per row (MONO_TOPK_CLUSTER=0: the general kernel)
+    if (a->score_ld <= mono::kClSize * mono::kClSpan) {
+        const char* sw = getenv("MONO_TOPK_CLUSTER");
         if (!sw || sw[0] != '0') {
-            mono::launch_k(mono::index_topk_reg_kernel, a->rows, mono::kTopkThreads, 0, (cudaStream_t)stream, *a);
+            mono::launch_k(mono::index_topk_cluster_kernel, a->rows * mono::kClSize, mono::kTopkThreads, 0, (cudaStream_t)stream, *a);
             cudaError_t e = cudaGetLastError();
             if (e != cudaSuccess) mono_set_error("mono_index_topk_launch: %s", cudaGetErrorString(e));
             return (int)e;

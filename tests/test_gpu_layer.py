@@ -162,10 +162,10 @@ def test_topk_long_context_matches_oracle():
 
 
 @pytest.mark.parametrize("n", [16384, 9001, 2049])
-def test_register_topk_equals_general_topk_and_oracle(n, monkeypatch):
-    """Rows of up to 16K positions keep their keys in registers: same slots and positions, in the
-    same order, as the general kernel and as the oracle's exact selection (ties, negative scores,
-    a short row and a pad row included)."""
+def test_cluster_topk_equals_general_topk_and_oracle(n, monkeypatch):
+    """Rows of up to 16K positions are selected by a cluster of eight CTAs (keys in registers, histograms
+    added over distributed shared memory): same slots and positions, in the same order, as the general
+    kernel and as the oracle's exact selection (ties, negative scores, a short row and a pad row included)."""
     rows, k, ld = 5, 2048, 16384
     g = torch.Generator().manual_seed(n)
     scores = torch.randn(16, ld, generator=g)
@@ -177,7 +177,7 @@ def test_register_topk_equals_general_topk_and_oracle(n, monkeypatch):
     slots = torch.tensor([1, 1, 1, 1, -1], dtype=torch.int64)
     got = {}
     for sw in ("1", "0"):
-        monkeypatch.setenv("MONO_TOPK_REGS", sw)
+        monkeypatch.setenv("MONO_TOPK_CLUSTER", sw)
         out = torch.full((16, k), -7, dtype=torch.int32, device=DEV)
         outp = torch.full((16, k), -7, dtype=torch.int32, device=DEV)
         a = ops.index_args(rows, 1, k, None, None, None, pt.to(DEV), pos.to(DEV), slots.to(DEV), scores.to(DEV), out, outp)
