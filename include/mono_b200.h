@@ -294,6 +294,11 @@ typedef struct mono_sparse_mla_args {
 } mono_sparse_mla_args;
 size_t mono_sparse_mla_scratch_bytes(int rows, int heads, int topk);
 int mono_sparse_mla_launch(const mono_sparse_mla_args* a, void* stream);
+/* The same, and the merge also stages every head's 512 merged values as that head's activation set
+ * of the W_UV GEMV (glm53/gfx950/kernel.py:3975-4123 merges and applies W_UV in one stage): `dst`
+ * describes the destination like mono_act_prep_launch does (rows, k = 512, segs = heads, fmt, planes,
+ * scales and their strides; its source fields are not read). */
+int mono_sparse_mla_quant_launch(const mono_sparse_mla_args* a, const mono_act_prep_args* dst, void* stream);
 
 /* The same attention for callers that cannot allocate device memory (this entry point
  * has no counterpart in the reference, whose runner allocates all scratch itself when

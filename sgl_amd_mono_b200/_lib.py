@@ -167,6 +167,7 @@ SYMBOLS = {
     "mono_mid_pair_launch": (i32, [C.POINTER(MidArgs), C.POINTER(MidArgs), vp]),
     "mono_sparse_mla_scratch_bytes": (C.c_size_t, [i32, i32, i32]),
     "mono_sparse_mla_launch": (i32, [C.POINTER(SparseMlaArgs), vp]),
+    "mono_sparse_mla_quant_launch": (i32, [C.POINTER(SparseMlaArgs), C.POINTER(ActPrepArgs), vp]),
     "mono_sparse_mla_launch_noalloc": (i32, [C.POINTER(SparseMlaArgs), vp]),
     "mono_reduce_peer_bytes": (C.c_size_t, [i32, i32, i32]),
     "mono_reduce_launch": (i32, [C.POINTER(ReduceArgs), vp]),

@@ -24,7 +24,9 @@ class SparseMlaOp:
         self.out = torch.zeros(max_rows, heads, 512, dtype=torch.bfloat16, device=device)
         self.max_rows = max_rows
 
-    def __call__(self, q: torch.Tensor, kv_pages: torch.Tensor, topk_slots: torch.Tensor) -> torch.Tensor:
+    def __call__(self, q: torch.Tensor, kv_pages: torch.Tensor, topk_slots: torch.Tensor, staged=None) -> torch.Tensor:
+        """``staged``: an ``ops.ActBuf`` with one 512-value segment per head; the merge then also writes
+        every head's output there as the W_UV GEMV's activation set (no separate staging launch)."""
         rows = q.shape[0]
         if not 1 <= rows <= self.max_rows:
             raise ValueError(f"q: {rows} rows, the op was built for 1..{self.max_rows}")
@@ -35,5 +37,5 @@ class SparseMlaOp:
         ops.require(topk_slots, "topk_slots", torch.int32)
         if topk_slots.dim() != 2 or topk_slots.shape[0] < rows or topk_slots.shape[1] < self.topk:
             raise ValueError(f"topk_slots: shape {tuple(topk_slots.shape)}, needs [>= {rows}, >= {self.topk}]")
-        ops.sparse_mla(q, kv_pages, topk_slots, self.out, self.scratch, self.sm_scale, self.topk)
+        ops.sparse_mla(q, kv_pages, topk_slots, self.out, self.scratch, self.sm_scale, self.topk, staged=staged)
         return self.out[:rows]

@@ -11,6 +11,7 @@
 // warp MMAs with the running maximum / sum and the output accumulators in registers, so a task
 // writes one partial however many chunks it covers (the reference writes one per 64 keys).
 #include "mono_common.cuh"
+#include "act_quant.cuh"
 
 extern void mono_set_error(const char* fmt, ...);
 
@@ -224,10 +225,13 @@ __global__ void __launch_bounds__(kMlaThreads, 2) sparse_mla_split_kernel(const 
     }
 }
 
-// One CTA per (row, head): merge the splits.
-__global__ void __launch_bounds__(256) sparse_mla_merge_kernel(const mono_sparse_mla_args a, int nsplit) {
+// One CTA per (row, head): merge the splits.  With a destination in `q` the head's 512 merged values
+// (rounded to bf16, as they are stored) are also quantised in place as the W_UV GEMV's activation set of
+// that head: segment `head` of q.planes, four 128-value chunks, one warp each.
+__global__ void __launch_bounds__(256) sparse_mla_merge_kernel(const mono_sparse_mla_args a, int nsplit, const mono_act_prep_args q) {
     pdl_prologue();
     __shared__ float w[128];
+    __shared__ float merged[512];
     const int row = blockIdx.x / a.heads, head = blockIdx.x - row * a.heads;
     const __nv_bfloat16* part_acc = reinterpret_cast<const __nv_bfloat16*>(a.scratch);
     const float* part_ml = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(a.scratch) +
@@ -258,8 +262,20 @@ __global__ void __launch_bounds__(256) sparse_mla_merge_kernel(const mono_sparse
         a0 += __low2float(v) * w[j];
         a1 += __high2float(v) * w[j];
     }
-    *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(a.out) + ((size_t)row * a.heads + head) * 512 + col) =
-        __floats2bfloat162_rn(a0, a1);
+    const __nv_bfloat162 o2 = __floats2bfloat162_rn(a0, a1);
+    *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(a.out) + ((size_t)row * a.heads + head) * 512 + col) = o2;
+    if (q.planes) {
+        merged[col] = __low2float(o2);
+        merged[col + 1] = __high2float(o2);
+        __syncthreads();
+        const int warp = tid >> 5, lane = tid & 31;
+        if (warp < 4) {
+            uint8_t* p0 = q.planes + (size_t)head * q.seg_stride + (size_t)row * q.ld;
+            float* sf = q.scale_f32 ? q.scale_f32 + (size_t)head * q.scale_seg_stride + (size_t)row * q.scale_ld : nullptr;
+            uint8_t* s8 = q.scale_e8 ? q.scale_e8 + (size_t)head * q.scale_seg_stride + (size_t)row * q.scale_ld : nullptr;
+            quant_chunk128(merged + warp * 128, q.fmt, lane, warp, p0, p0 + q.plane_stride, sf, s8);
+        }
+    }
 }
 
 }  // namespace mono
@@ -280,7 +296,22 @@ static void mla_plan(int rows, int heads, int topk, int sms, int* nsplit, int* c
     *nsplit = (total + c - 1) / c;
 }
 
-extern "C" int mono_sparse_mla_launch(const mono_sparse_mla_args* a, void* stream) {
+static int sparse_mla_launch(const mono_sparse_mla_args* a, const mono_act_prep_args* dst, void* stream);
+
+extern "C" int mono_sparse_mla_launch(const mono_sparse_mla_args* a, void* stream) { return sparse_mla_launch(a, nullptr, stream); }
+
+extern "C" int mono_sparse_mla_quant_launch(const mono_sparse_mla_args* a, const mono_act_prep_args* dst, void* stream) {
+    if (!a || !dst || !dst->planes || dst->rows != a->rows || dst->k != 512 || dst->segs != a->heads ||
+        (dst->fmt == MONO_ACT_A8 && !dst->scale_f32) || (dst->fmt == MONO_ACT_HILO && (!dst->scale_f32 || dst->plane_stride <= 0)) ||
+        ((dst->fmt == MONO_ACT_MX8 || dst->fmt == MONO_ACT_MX8N) && !dst->scale_e8)) {
+        mono_set_error("mono_sparse_mla_quant_launch: the destination must describe rows x heads segments of 512 values "
+                       "(k = 512, segs = heads) with planes and the scales of its format");
+        return MONO_E_ARG;
+    }
+    return sparse_mla_launch(a, dst, stream);
+}
+
+static int sparse_mla_launch(const mono_sparse_mla_args* a, const mono_act_prep_args* dst, void* stream) {
     if (!a || a->rows < 1 || a->rows > MONO_MAX_ROWS || a->heads < 1 || a->heads > 128 || a->topk < 1 ||
         a->topk > 64 * 128 || a->topk_ld < a->topk || !a->q || !a->kv_pages || !a->topk_slots || !a->out || !a->scratch) {
         mono_set_error("mono_sparse_mla_launch: rows 1..16, heads 1..128, topk 1..8192 and all pointers required");
@@ -307,7 +338,8 @@ extern "C" int mono_sparse_mla_launch(const mono_sparse_mla_args* a, void* strea
     int grid = a->rows * ((a->heads + mono::kHeadGroup - 1) / mono::kHeadGroup) * nsplit;
     if (grid > 2 * sms) grid = 2 * sms;
     mono::launch_k(mono::sparse_mla_split_kernel, grid, mono::kMlaThreads, smem, (cudaStream_t)stream, *a, nsplit, chunks);
-    mono::launch_k(mono::sparse_mla_merge_kernel, a->rows * a->heads, 256, 0, (cudaStream_t)stream, *a, nsplit);
+    mono_act_prep_args none = {};
+    mono::launch_k(mono::sparse_mla_merge_kernel, a->rows * a->heads, 256, 0, (cudaStream_t)stream, *a, nsplit, dst ? *dst : none);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_sparse_mla_launch: %s", cudaGetErrorString(e));
     return (int)e;
@@ -404,7 +436,8 @@ extern "C" int mono_sparse_mla_launch_noalloc(const mono_sparse_mla_args* a, voi
     // Nothing in the scratch has to start at zero: every partial the merge reads is
     // written by this call's split kernel first (same stream, so in order).
     mono::sparse_mla_split_kernel<<<grid, mono::kMlaThreads, smem, (cudaStream_t)stream>>>(args, nsplit, chunks);
-    mono::sparse_mla_merge_kernel<<<args.rows * args.heads, 256, 0, (cudaStream_t)stream>>>(args, nsplit);
+    mono_act_prep_args none = {};
+    mono::sparse_mla_merge_kernel<<<args.rows * args.heads, 256, 0, (cudaStream_t)stream>>>(args, nsplit, none);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_sparse_mla_launch_noalloc: %s", cudaGetErrorString(e));
     return (int)e;

@@ -92,6 +92,7 @@ class MlaLayerOp:
             self.scores = z(R, 128)
         self.topk_slots = torch.full((R, self.topk), -1, dtype=torch.int32, device=device)
         self.topk_pos = torch.full((R, self.topk), -1, dtype=torch.int32, device=device)
+        self.mla_staged = os.environ.get("MONO_MLA_STAGED", "1") != "0"
         self.attn = SparseMlaOp(hl, self.topk, device, max_rows=R, sm_scale=(cfg.nope + cfg.rope) ** -0.5)
         # ---- W_UV (per head) and o_proj
         self.lat = ops.ActBuf(L.ACT_HILO, 512, device, segs=hl)
@@ -167,8 +168,13 @@ class MlaLayerOp:
             if ih:
                 ops.index_score(ia)
             ops.index_topk(ia)  # rows with at most topk keys keep every key in order
-        lat = self.attn(self.q_full[:rows], step.kv_pages, self.topk_slots)
-        ops.act_prep_heads(rows, hl, 512, self.lat, src_bf16=lat)
+        # the merge of the attention splits also stages every head's output for the W_UV GEMV
+        # (MONO_MLA_STAGED=0: a staging launch of its own)
+        if self.mla_staged:
+            self.attn(self.q_full[:rows], step.kv_pages, self.topk_slots, staged=self.lat)
+        else:
+            lat = self.attn(self.q_full[:rows], step.kv_pages, self.topk_slots)
+            ops.act_prep_heads(rows, hl, 512, self.lat, src_bf16=lat)
         self.gUV.launch(rows)
         ops.act_prep(rows, hl * 128, self.o, src_f32=self.uv_p, nsum=1)
         self.gO.launch(rows)

@@ -269,28 +269,38 @@ def reduce_rows(rows: int, n: int, partial: torch.Tensor, nsum: int, out: torch.
     L.check(L.load().mono_reduce_launch(C.byref(a), _stream()), "mono_reduce_launch")
 
 
-def sparse_mla(q, kv_pages, topk_slots, out, scratch, sm_scale: float, topk: int | None = None) -> None:
+def sparse_mla(q, kv_pages, topk_slots, out, scratch, sm_scale: float, topk: int | None = None, staged=None) -> None:
     rows, heads = q.shape[0], q.shape[1]
     a = L.SparseMlaArgs()
     a.rows, a.heads, a.topk, a.topk_ld = rows, heads, topk or topk_slots.shape[1], topk_slots.shape[1]
     a.sm_scale = sm_scale
     a.q, a.kv_pages, a.n_pages = q.data_ptr(), kv_pages.data_ptr(), kv_pages.shape[0]
     a.topk_slots, a.out, a.scratch = topk_slots.data_ptr(), out.data_ptr(), scratch.data_ptr()
+    if staged is not None:  # the merge also stages the heads' outputs for the W_UV GEMV
+        d = act_heads_args(rows, heads, 512, staged)
+        L.check(L.load().mono_sparse_mla_quant_launch(C.byref(a), C.byref(d), _stream()), "mono_sparse_mla_quant_launch")
+        return
     L.check(L.load().mono_sparse_mla_launch(C.byref(a), _stream()), "mono_sparse_mla_launch")
+
+
+def act_heads_args(rows: int, heads: int, k: int, dst: ActBuf) -> "L.ActPrepArgs":
+    """The destination half of a per-head staging: segment ``head`` of ``dst`` takes vector (row, head)."""
+    a = L.ActPrepArgs()
+    a.rows, a.k, a.segs = rows, k, heads
+    a.fmt, a.planes, a.plane_stride, a.ld = dst.fmt, _p(dst.planes), dst.plane_stride, dst.ld
+    a.scale_f32, a.scale_e8, a.scale_ld = _p(dst.scale_f32), _p(dst.scale_e8), dst.scale_ld
+    a.seg_stride, a.scale_seg_stride = dst.seg_stride, dst.scale_seg_stride
+    return a
 
 
 def act_prep_heads(rows: int, heads: int, k: int, dst: ActBuf, *, src_bf16=None, src_f32=None, nsum: int = 1,
                    round_bf16: bool = True) -> None:
     """Per-head activation sets: vector (row, head) of the source goes to segment ``head`` of ``dst``."""
-    a = L.ActPrepArgs()
-    a.rows, a.k, a.segs = rows, k, heads
+    a = act_heads_args(rows, heads, k, dst)
     a.src_bf16, a.src_f32 = _p(src_bf16), _p(src_f32)
     if src_f32 is not None:
         a.nsum, a.src_ld, a.src_sum_stride = nsum, src_f32.shape[-1], L.MAX_ROWS * src_f32.shape[-1]
     a.round_bf16 = int(round_bf16)
-    a.fmt, a.planes, a.plane_stride, a.ld = dst.fmt, _p(dst.planes), dst.plane_stride, dst.ld
-    a.scale_f32, a.scale_e8, a.scale_ld = _p(dst.scale_f32), _p(dst.scale_e8), dst.scale_ld
-    a.seg_stride, a.scale_seg_stride = dst.seg_stride, dst.scale_seg_stride
     L.check(L.load().mono_act_prep_launch(C.byref(a), _stream()), "mono_act_prep_launch")
 
 

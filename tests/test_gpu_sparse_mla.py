@@ -68,3 +68,27 @@ def test_full_size_config2_property():
     out = op(q.to(DEV), pages, sel.to(DEV))
     want = (const[:512].view(torch.float8_e4m3fn).float() * 0.25).bfloat16().float()
     assert torch.allclose(out.float(), want.expand_as(out), atol=2e-2, rtol=2**-7)
+
+
+@pytest.mark.parametrize("fmt_name", ["A8", "MX8N"])
+def test_merge_stages_the_heads_for_the_next_gemv(fmt_name):
+    """The merge can also write every head's output as that head's quantised activation set: same bf16
+    output, and the planes and scales of a staging launch run on that output, bit for bit."""
+    from sgl_amd_mono_b200 import _lib as L
+    from sgl_amd_mono_b200 import ops
+
+    rows, heads = 5, 16
+    q, pages, sel, out, op = _run(rows, heads, 3000, 512, seed=6)
+    fmt = getattr(L, "ACT_" + fmt_name)
+    staged = ops.ActBuf(fmt, 512, DEV, segs=heads)
+    ref = ops.ActBuf(fmt, 512, DEV, segs=heads)
+    out2 = op(q.to(DEV), pages.to(DEV), sel.to(DEV), staged=staged).clone()
+    ops.act_prep_heads(rows, heads, 512, ref, src_bf16=out2)
+    torch.cuda.synchronize()
+    assert torch.equal(out2, out)
+    assert torch.equal(staged.planes, ref.planes) and bool(ref.planes.any())
+    for name in ("scale_f32", "scale_e8"):
+        a, b = getattr(staged, name), getattr(ref, name)
+        assert (a is None) == (b is None)
+        if a is not None:
+            assert torch.equal(a, b) and bool(b.any())
