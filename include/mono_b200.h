@@ -198,6 +198,14 @@ typedef struct mono_gemv_job {
     mono_tmap_t tmap4;
     int act_natural; /* 1 = the activation planes are MONO_ACT_MX8N */
     int k_tiles4;    /* K in 128-element tiles (0 = 2 * k_tiles): exact when K ends inside a 128-byte tile */
+    /* Optional staging of the output as the next GEMV's activations (dense jobs on the tcgen05 consumer
+     * with nsplit == 1): output (row c, column n) is rounded to bf16 and written as E4M3 to
+     * stage_planes[c * stage_ld + n] (MONO_ACT_HILO: high byte there, low byte stage_plane_stride
+     * further), with one scale per 128 columns in stage_scale[c * stage_scale_ld + n / 128]: the bytes
+     * mono_act_prep_launch writes for stage_fmt = MONO_ACT_A8 or MONO_ACT_HILO. */
+    uint8_t* stage_planes;
+    float* stage_scale;
+    int stage_ld, stage_scale_ld, stage_fmt, stage_plane_stride;
 } mono_gemv_job;
 
 typedef struct mono_gemv_args {

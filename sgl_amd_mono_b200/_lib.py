@@ -42,7 +42,9 @@ class GemvJob(C.Structure):
         ("feeds_job", i32), ("done", vp), ("ready", vp),
         ("_pad4", C.c_ubyte * 40),  # tensor maps are 64-byte aligned in C
         ("tmap4", Tmap), ("act_natural", i32), ("k_tiles4", i32),
-        ("_tail", C.c_ubyte * 56),
+        ("stage_planes", vp), ("stage_scale", vp), ("stage_ld", i32), ("stage_scale_ld", i32),
+        ("stage_fmt", i32), ("stage_plane_stride", i32),
+        ("_tail", C.c_ubyte * 24),
     ]
 
 

@@ -531,6 +531,12 @@ extern "C" int mono_gemv_launch(const mono_gemv_args* a, void* stream) {
             return rc;
         }
     }
+    for (int j = 0; j < a->njobs; ++j) {
+        if (a->job[j].stage_planes) {
+            mono_set_error("mono_gemv_launch: job %d: an output is staged by the FP8 tcgen05 path only (activation maps set)", j);
+            return MONO_E_ARG;
+        }
+    }
     if (a->wkind == MONO_W_MXFP4 && mono_gemv_tc_enabled()) {
         const int rc = mono_gemv_tc4_launch(a, tasks, (cudaStream_t)stream);  // -100: not eligible, use the warp-MMA consumer
         if (rc != -100) {

@@ -212,6 +212,45 @@ struct BoundedSync {
     }
 };
 
+// The four epilogue warps hold a finished row block: 128 output columns (one per thread) x the step's rows.
+// Stages them as the next GEMV's activations: bf16 rounding, one amax/448 scale per row over the 128
+// columns, E4M3 bytes (the arithmetic of the activation staging launch: glm53/gfx950/kernel.py:1440-1450).
+__device__ __forceinline__ bool tc_stage_out(const mono_gemv_job& jb, int rows, int rb, int row_in_tile, int q, int lane, bool in_range,
+                                             const float* total_acc, float (*s_amax)[kMaxRows], BoundedSync& es) {
+    float v[kMaxRows];
+#pragma unroll
+    for (int c = 0; c < kMaxRows; ++c) {
+        v[c] = bf16_round(total_acc[c]);
+        const float am = warp_max(in_range ? fabsf(v[c]) : 0.f);
+        if (lane == 0) s_amax[q][c] = am;
+    }
+    if (!es.sync()) return false;
+#pragma unroll
+    for (int c = 0; c < kMaxRows; ++c) {
+        if (c < rows) {
+            const float amax = fmaxf(fmaxf(s_amax[0][c], s_amax[1][c]), fmaxf(s_amax[2][c], s_amax[3][c]));
+            uint8_t* dst = jb.stage_planes + (size_t)c * jb.stage_ld + rb * 128 + row_in_tile;
+            float scale;
+            if (jb.stage_fmt == MONO_ACT_A8) {
+                scale = amax > 0.f ? amax / 448.f : 1.f;
+                const float inv = amax > 0.f ? 448.f / amax : 1.f;
+                if (in_range) *dst = f32_to_e4m3(v[c] * inv);
+            } else {  // MONO_ACT_HILO: power-of-two scale, value = high byte + low byte
+                const int code = code_ceil(fmaxf(amax, 7.888609052210118e-31f /* 2^-100 */) / 448.f);
+                scale = exp2_code(code);
+                const float sv = v[c] * exp2_code(254 - code);
+                const uint8_t hb = f32_to_e4m3(sv);
+                if (in_range) {
+                    dst[0] = hb;
+                    dst[jb.stage_plane_stride] = f32_to_e4m3(sv - e4m3_to_f32(hb));
+                }
+            }
+            if (q == 0 && lane == 0) jb.stage_scale[(size_t)c * jb.stage_scale_ld + rb] = scale;
+        }
+    }
+    return es.sync();  // the maxima may be overwritten by the next task
+}
+
 // The finisher warps (128 threads) learn that an up/gate task of `slot` is complete.  The CTA that counts
 // the slot's last task turns the partial sums into the fed job's activations: sum over the K splits in
 // order, SwiGLU, E4M3 with one amax/448 scale per 128 values (glm53/gfx950/kernel.py:1440-1450, :4352-5187).
@@ -306,7 +345,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
     uint64_t* mail_full = sc_empty + kTcScSlotsMax;  // epilogue -> finisher: an up/gate task's outputs are stored
     uint64_t* mail_free = mail_full + 2;
     uint64_t* fin_bar = mail_free + 2;
+    uint64_t* epi_bar = fin_bar + 1;  // the four epilogue warps, when a job stages its output
     __shared__ int abort_flag, s_last[2];
+    __shared__ float s_amax[4][kMaxRows];
     __shared__ uint32_t tmem_base_s;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -319,6 +360,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
         for (int i = 0; i < kTcScSlots; ++i) { mbar_init(&sc_full[i], 32); mbar_init(&sc_empty[i], 4); }
         for (int i = 0; i < 2; ++i) { mbar_init(&mail_full[i], 128); mbar_init(&mail_free[i], 1); }
         mbar_init(fin_bar, 128);
+        mbar_init(epi_bar, 128);
         mbar_fence_init();
     }
     if (warp == 1) tc_alloc(&tmem_base_s, kTcTmemCols);
@@ -519,6 +561,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
         int stage = 0;
         uint32_t phase = 0;
         bool have_next = false;
+        BoundedSync es{epi_bar, 0u, abortp};
         float total_acc[kMaxRows];
 #define TASK_BEGIN \
         _Pragma("unroll") for (int c = 0; c < kMaxRows; ++c) total_acc[c] = 0.f;
@@ -531,6 +574,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
                 _Pragma("unroll") for (int c = 0; c < kMaxRows; ++c)                                          \
                     if (c < rows) out[(size_t)c * jb.out_ld + out_row] = total_acc[c];                    \
             }                                                                                                 \
+            if (jb.stage_planes) tc_stage_out(jb, rows, rb, row_in_tile, q, lane, row_in_mat < jb.n_rows, total_acc, s_amax, es); \
             if (jb.feeds_job > 0) {                                                                           \
                 const uint32_t k = nfeed & 1;                                                                 \
                 if (mbar_wait(&mail_free[k], ((nfeed >> 1) & 1) ^ 1, abortp)) mbar_arrive(&mail_full[k]);     \
@@ -649,6 +693,14 @@ int mono_gemv_tc_launch(const mono_gemv_args* a, long tasks, cudaStream_t st) {
         if (seg > kTcMaxSegTiles) {
             mono_set_error("mono_gemv_launch: job %d: a segment may span at most %d tiles", j, kTcMaxSegTiles);
             return MONO_E_ARG;
+        }
+        if (jb.stage_planes) {
+            if (jb.mode != MONO_JOB_DENSE || jb.nsplit != 1 || jb.feeds_job > 0 || !jb.stage_scale || jb.stage_ld < 128 || jb.stage_scale_ld < 1 ||
+                (jb.stage_fmt != MONO_ACT_A8 && jb.stage_fmt != MONO_ACT_HILO) || (jb.stage_fmt == MONO_ACT_HILO && jb.stage_plane_stride <= 0)) {
+                mono_set_error("mono_gemv_launch: job %d: only a dense job without K splits can stage its output "
+                               "(stage_planes, stage_scale, their leading dimensions and stage_fmt A8 or HILO required)", j);
+                return MONO_E_ARG;
+            }
         }
         if (jb.feeds_job > 0) {
             const int f = jb.feeds_job - 1;

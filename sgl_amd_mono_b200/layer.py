@@ -98,9 +98,18 @@ class MlaLayerOp:
         self.lat = ops.ActBuf(L.ACT_HILO, 512, device, segs=hl)
         self.uv_p = z(1, R, hl * 128)
         self.gUV = ops.Gemv(L.W_FP8, self.guard)
-        self.gUV.add("kv_b(W_UV)", w["kv_b"].view(hl, 256, 512), self.lat, self.uv_p, wscale=w["kv_b_s"].view(hl, 2, 4),
-                     n_rows=128, row_off=128, rb_per_mat=1, n_mats=hl, act_per_mat=True, split_tiles=4, nsplit=1)
         self.o = ops.ActBuf(L.ACT_HILO, hl * 128, device)
+        # on the tcgen05 consumer the W_UV job can write its output straight into o_proj's activation planes
+        # (MONO_UV_STAGED=1 / 0).  Measured on config 3: 6 us faster per layer with 128 local heads (128 CTAs
+        # share the staging), 6 us slower with 16 (the staging lengthens the one task each of 16 CTAs runs,
+        # and a staging launch of 2.4 us in between costs less than that): the default follows the head count
+        lib = L.load()
+        tc_on = lib.mono_set_gemv_tcgen05(1)
+        lib.mono_set_gemv_tcgen05(tc_on)
+        self.uv_staged = bool(tc_on) and os.environ.get("MONO_UV_STAGED", "1" if hl >= 64 else "0") != "0"
+        self.gUV.add("kv_b(W_UV)", w["kv_b"].view(hl, 256, 512), self.lat, self.uv_p, wscale=w["kv_b_s"].view(hl, 2, 4),
+                     n_rows=128, row_off=128, rb_per_mat=1, n_mats=hl, act_per_mat=True, split_tiles=4, nsplit=1,
+                     stage=self.o if self.uv_staged else None)
         kto = -(-hl * 128 // 128)
         stO, nsO = ops.plan_split(kto, -(-h // 128), L.W_FP8)
         self.nsO = nsO
@@ -176,7 +185,8 @@ class MlaLayerOp:
             lat = self.attn(self.q_full[:rows], step.kv_pages, self.topk_slots)
             ops.act_prep_heads(rows, hl, 512, self.lat, src_bf16=lat)
         self.gUV.launch(rows)
-        ops.act_prep(rows, hl * 128, self.o, src_f32=self.uv_p, nsum=1)
+        if not self.uv_staged:
+            ops.act_prep(rows, hl * 128, self.o, src_f32=self.uv_p, nsum=1)
         self.gO.launch(rows)
         ops.reduce_rows(rows, cfg.hidden, self.o_p, self.nsO, self.h1, residual=h, slots=step.slots, peer=self.peer,
                         site=2 * self.layer, guard=self.guard, deadline_s=self.deadline_s)

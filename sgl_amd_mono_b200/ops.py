@@ -142,8 +142,10 @@ class Gemv:
             wscale: torch.Tensor | None = None, n_rows: int | None = None, row_off: int = 0,
             rb_per_mat: int = 0, n_mats: int = 0, nsplit: int | None = None, split_tiles: int | None = None,
             out_slice: int = 0, expert_list=None, n_expert=None, max_expert: int = 0, coef=None,
-            act_per_mat: bool = False) -> int:
-        """Adds a job; returns the number of output slices (partial sums) it writes."""
+            act_per_mat: bool = False, stage: ActBuf | None = None) -> int:
+        """Adds a job; returns the number of output slices (partial sums) it writes.  ``stage``: the
+        activation buffer of the next GEMV (A8 or HILO); the job then also writes its output there,
+        quantised, so that no staging launch is needed in between."""
         j = self.args.njobs
         if j >= L.GEMV_MAX_JOBS:
             raise ValueError("a launch holds at most four jobs")
@@ -205,6 +207,13 @@ class Gemv:
         if out.dtype != torch.float32 or out.numel() < (out_slice + n_slices) * slice_elems:
             raise ValueError(f"{name}: output buffer holds {out.numel()} f32, needs {(out_slice + n_slices) * slice_elems}")
         job.feeds_job = 0
+        if stage is not None:
+            if stage.fmt not in (L.ACT_A8, L.ACT_HILO) or stage.segs != 1 or mode != L.JOB_DENSE or job.nsplit != 1:
+                raise ValueError(f"{name}: only a dense job without K splits can stage its output, as A8 or HILO")
+            job.stage_planes, job.stage_scale = stage.planes.data_ptr(), stage.scale_f32.data_ptr()
+            job.stage_ld, job.stage_scale_ld = stage.ld, stage.scale_ld
+            job.stage_fmt, job.stage_plane_stride = stage.fmt, stage.plane_stride
+            self._keep.append(stage)
         job.act_natural = int(act.fmt == L.ACT_MX8N)
         if self.wkind == L.W_MXFP4 and act.fmt == L.ACT_MX8N:
             # the tcgen05 consumer reads the packed nibbles as a tensor of 4-bit elements

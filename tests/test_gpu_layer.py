@@ -189,3 +189,22 @@ def test_cluster_topk_equals_general_topk_and_oracle(n, monkeypatch):
         want = S.exact_topk_positions(scores[i], n, k)
         assert got["1"][1][i].tolist() == want.tolist(), f"row {i}"
     assert int((got["1"][0][4] >= 0).sum()) == 0, "a pad row selects nothing"
+
+
+def test_fused_staging_equals_staging_launches(monkeypatch):
+    """The attention merge staging the heads for W_UV, and the W_UV job staging its output for o_proj,
+    write the bytes and scales of the separate staging launches; the layer's output is bit-equal."""
+    cfg, rows, ctx = CFG_TINY, 6, 900
+    monkeypatch.setenv("MONO_MLA_STAGED", "1")
+    monkeypatch.setenv("MONO_UV_STAGED", "1")
+    op, _, _, _, _, out = _run(cfg, rows, ctx)
+    assert op.mla_staged and op.uv_staged
+    monkeypatch.setenv("MONO_MLA_STAGED", "0")
+    monkeypatch.setenv("MONO_UV_STAGED", "0")
+    op2, _, _, _, _, out2 = _run(cfg, rows, ctx)
+    assert not op2.mla_staged and not op2.uv_staged
+    for name in ("lat", "o"):
+        a, b = getattr(op, name), getattr(op2, name)
+        assert torch.equal(a.planes, b.planes) and bool(b.planes.any()), name
+        assert torch.equal(a.scale_f32, b.scale_f32), name
+    assert torch.equal(out, out2)
