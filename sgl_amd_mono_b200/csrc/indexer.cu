@@ -447,6 +447,8 @@ __global__ void __cluster_dims__(kClSize, 1, 1) __launch_bounds__(kTopkThreads)
 
 }  // namespace mono
 
+int mono_index_score_tc_launch(const mono_index_args* a, void* stream);  // index_score_tc.cu
+
 static int check_index_args(const mono_index_args* a, const char* who) {
     if (!a || a->rows < 1 || a->rows > MONO_MAX_ROWS || a->index_heads < 1 || a->index_heads > 64 || a->topk < 1 ||
         !a->page_table || !a->positions || !a->scores || a->score_ld < 1) {
@@ -461,6 +463,15 @@ extern "C" int mono_index_score_launch(const mono_index_args* a, void* stream) {
     if (!a->idx_q || !a->idx_w || !a->idx_pages) {
         mono_set_error("mono_index_score_launch: idx_q, idx_w and idx_pages required");
         return MONO_E_ARG;
+    }
+    {
+        // the tcgen05 kernel (MONO_INDEX_SCORE_TC=0: the mma.sync kernel below)
+        const char* sw = getenv("MONO_INDEX_SCORE_TC");
+        if ((!sw || sw[0] != '0') && !(reinterpret_cast<uintptr_t>(a->idx_pages) & 15) && !(reinterpret_cast<uintptr_t>(a->idx_q) & 15)) {
+            const int rc = mono_index_score_tc_launch(a, stream);
+            if (rc != 0) mono_set_error("mono_index_score_launch: %s", cudaGetErrorString((cudaError_t)rc));
+            return rc;
+        }
     }
     const size_t smem = sizeof(mono::ScoreSmem) + 128;
     static thread_local bool attr_set = false;

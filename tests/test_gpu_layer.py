@@ -208,3 +208,22 @@ def test_fused_staging_equals_staging_launches(monkeypatch):
         assert torch.equal(a.planes, b.planes) and bool(b.planes.any()), name
         assert torch.equal(a.scale_f32, b.scale_f32), name
     assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("rows,ctx", [(8, 1000), (3, 129), (16, 2500)])
+def test_tcgen05_index_scores_match_the_mma_sync_kernel(rows, ctx, monkeypatch):
+    """The tcgen05 score kernel (keys as TMEM lanes, heads as columns) and the mma.sync kernel read the
+    same bf16 operands and add the same f32 products in a different order: 1e-4 of the row's largest
+    score, and nothing past a row's last key is written."""
+    monkeypatch.setenv("MONO_INDEX_SCORE_TC", "1")
+    op, _, step, _, _, _ = _run(CFG_TINY, rows, ctx)
+    tc = op.scores[:rows].cpu()
+    monkeypatch.setenv("MONO_INDEX_SCORE_TC", "0")
+    op2, _, _, _, _, _ = _run(CFG_TINY, rows, ctx)
+    ref = op2.scores[:rows].cpu()
+    assert bool(ref.abs().sum() > 0)
+    for i in range(rows):
+        n = int(step.positions[i]) + 1
+        scale = float(ref[i, :n].abs().max())
+        assert float((tc[i, :n] - ref[i, :n]).abs().max()) <= 1e-4 * scale + 1e-6, f"row {i}"
+        assert torch.equal(tc[i, n:], ref[i, n:]), "columns past the row's keys stay as they were"
