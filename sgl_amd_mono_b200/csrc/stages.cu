@@ -5,6 +5,7 @@
 // Reference counterparts: glm53/gfx950/kernel.py:1367-1414 (RMSNorm staging),
 // :1440-1466 (quant_scaled / quant_mxfp8), :1575-1629 (route_top8), :4396-4415 (SiLU),
 // :1631-1688 (peer_reduce); minimax_m31/ffn.py:601-723 (router).
+#include <cstdlib>
 #include "mono_common.cuh"
 #include "act_quant.cuh"
 
@@ -226,30 +227,37 @@ constexpr int kRowdotThreads = 256;
 // Column n by the 256 threads tid = 0..255 of one group (every thread of the CTA calls this:
 // it holds a CTA-wide barrier).  The weights do not depend on the launch before this one, so
 // the first batch of weight loads is issued before the wait on that launch.
-__device__ __forceinline__ void rowdot_col(const mono_rowdot_args& a, int n, int tid, float (*red)[kMaxRows]) {
-    // the 256 threads split K (4 values per thread per 1024), so every weight load of the
-    // column is in flight at once
+template <int COLS>
+__device__ __forceinline__ void rowdot_col(const mono_rowdot_args& a, int n0, int tid, float (*red)[kRowdotThreads / 32][kMaxRows]) {
+    // columns n0 .. n0 + COLS - 1 share every activation load.  The 256 threads split K (4 values per
+    // thread per 1024), so every weight load of a column is in flight at once; the order of the sums of
+    // one column does not depend on COLS
     const int warp = tid >> 5, lane = tid & 31;
-    const bool active = n < a.n;
-    float acc[kMaxRows];
+    float acc[COLS][kMaxRows];
 #pragma unroll
-    for (int r = 0; r < kMaxRows; ++r) acc[r] = 0.f;
+    for (int c = 0; c < COLS; ++c)
+#pragma unroll
+        for (int r = 0; r < kMaxRows; ++r) acc[c][r] = 0.f;
     const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(a.x_bf16);
     for (int k0 = 0; k0 < a.k; k0 += kRowdotThreads * 4 * 8) {
-        // up to eight weight loads per thread are in flight before the first is used
-        float4 wv[8];
+        // up to eight weight loads per thread and column are in flight before the first is used
+        float4 wv[COLS][8];
 #pragma unroll
-        for (int it = 0; it < 8; ++it) {
-            const int k = k0 + (it * kRowdotThreads + tid) * 4;
-            wv[it] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (k < a.k && active) {
-                if (a.w_is_f32) {
-                    wv[it] = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.w) + (size_t)n * a.k + k));
-                } else {
-                    const uint2 v = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.w) + (size_t)n * a.k + k));
-                    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
-                    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
-                    wv[it] = make_float4(lo.x, lo.y, hi.x, hi.y);
+        for (int c = 0; c < COLS; ++c) {
+            const int n = n0 + c;
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+                const int k = k0 + (it * kRowdotThreads + tid) * 4;
+                wv[c][it] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (k < a.k && n < a.n) {
+                    if (a.w_is_f32) {
+                        wv[c][it] = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.w) + (size_t)n * a.k + k));
+                    } else {
+                        const uint2 v = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.w) + (size_t)n * a.k + k));
+                        const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+                        const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+                        wv[c][it] = make_float4(lo.x, lo.y, hi.x, hi.y);
+                    }
                 }
             }
         }
@@ -257,40 +265,48 @@ __device__ __forceinline__ void rowdot_col(const mono_rowdot_args& a, int n, int
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
             const int k = k0 + (it * kRowdotThreads + tid) * 4;
-            if (k < a.k && active) {
+            if (k < a.k) {
 #pragma unroll
                 for (int r = 0; r < kMaxRows; ++r) {
                     if (r < a.rows) {
                         const uint2 xv = __ldg(reinterpret_cast<const uint2*>(x + (size_t)r * a.k + k));
                         const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.x));
                         const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.y));
-                        acc[r] += lo.x * wv[it].x + lo.y * wv[it].y + hi.x * wv[it].z + hi.y * wv[it].w;
+#pragma unroll
+                        for (int c = 0; c < COLS; ++c)
+                            acc[c][r] += lo.x * wv[c][it].x + lo.y * wv[c][it].y + hi.x * wv[c][it].z + hi.y * wv[c][it].w;
                     }
                 }
             }
         }
     }
 #pragma unroll
-    for (int r = 0; r < kMaxRows; ++r) {
-        if (r < a.rows) {
-            const float s = warp_sum(acc[r]);
-            if (lane == 0) red[warp][r] = s;
-        }
-    }
-    __syncthreads();
-    if (tid < a.rows && active) {
-        float s = 0.f;
+    for (int c = 0; c < COLS; ++c)
 #pragma unroll
-        for (int wv = 0; wv < kRowdotThreads / 32; ++wv) s += red[wv][tid];
-        a.out[(size_t)tid * a.out_ld + n] = s * a.out_scale;
+        for (int r = 0; r < kMaxRows; ++r) {
+            if (r < a.rows) {
+                const float s = warp_sum(acc[c][r]);
+                if (lane == 0) red[c][warp][r] = s;
+            }
+        }
+    __syncthreads();
+    if (tid < a.rows * COLS) {
+        const int c = tid / a.rows, r = tid - c * a.rows;
+        if (n0 + c < a.n) {
+            float s = 0.f;
+#pragma unroll
+            for (int wv = 0; wv < kRowdotThreads / 32; ++wv) s += red[c][wv][r];
+            a.out[(size_t)r * a.out_ld + n0 + c] = s * a.out_scale;
+        }
     }
 }
 
+template <int COLS>
 __global__ void __launch_bounds__(kRowdotThreads) rowdot_kernel(const mono_rowdot_args a) {
-    // one CTA per output column
-    __shared__ float red[kRowdotThreads / 32][kMaxRows];
+    // one CTA per COLS output columns
+    __shared__ float red[COLS][kRowdotThreads / 32][kMaxRows];
     pdl_launch_dependents();
-    rowdot_col(a, blockIdx.x, threadIdx.x, red);
+    rowdot_col<COLS>(a, blockIdx.x * COLS, threadIdx.x, red);
 }
 
 // Router logits and routing in one launch: every CTA computes two columns of the logits (one per
@@ -299,12 +315,12 @@ __global__ void __launch_bounds__(kRowdotThreads) rowdot_kernel(const mono_rowdo
 constexpr int kRouterCols = kRouteThreads / kRowdotThreads;
 
 __global__ void __launch_bounds__(kRouteThreads) router_kernel(const mono_rowdot_args d, const mono_route_args r, int32_t* counter) {
-    __shared__ float red[kRouterCols][kRowdotThreads / 32][kMaxRows];
+    __shared__ float red[kRouterCols][1][kRowdotThreads / 32][kMaxRows];
     __shared__ RouteSmem sm;
     __shared__ int is_last;
     pdl_launch_dependents();
     const int group = threadIdx.x / kRowdotThreads, t = threadIdx.x - group * kRowdotThreads;
-    rowdot_col(d, blockIdx.x * kRouterCols + group, t, red[group]);
+    rowdot_col<1>(d, blockIdx.x * kRouterCols + group, t, red[group]);
     __threadfence();  // this CTA's logits are visible device-wide before it is counted
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -518,7 +534,14 @@ extern "C" int mono_rowdot_launch(const mono_rowdot_args* a, void* stream) {
         mono_set_error("mono_rowdot_launch: rows 1..16, k a multiple of 128 and all pointers required");
         return MONO_E_ARG;
     }
-    mono::launch_k(mono::rowdot_kernel, a->n, mono::kRowdotThreads, 0, (cudaStream_t)stream, *a);
+    // MONO_ROWDOT_COLS=2: two columns per CTA share the activation loads.  Measured slower (router logits of
+    // 256 experts: 9.3 us against 8.8 us), so one column per CTA is the default
+    const char* cf = getenv("MONO_ROWDOT_COLS");
+    const int cols = cf && atoi(cf) == 2 ? 2 : 1;
+    if (cols == 2)
+        mono::launch_k(mono::rowdot_kernel<2>, (a->n + 1) / 2, mono::kRowdotThreads, 0, (cudaStream_t)stream, *a);
+    else
+        mono::launch_k(mono::rowdot_kernel<1>, a->n, mono::kRowdotThreads, 0, (cudaStream_t)stream, *a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_rowdot_launch: %s", cudaGetErrorString(e));
     return (int)e;

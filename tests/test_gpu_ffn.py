@@ -258,3 +258,22 @@ def test_gemv_stages_in_isolation(cfg, rows):
         down_ref += coef[u, :, None] * (mid_k @ deq(wc["w2"][e], wc["w2_s"][e]).T)
     routed = ffn.down_p[: ffn.groups, :rows].cpu().sum(0)
     assert_rel(routed, down_ref, "routed down projection")
+
+
+@pytest.mark.parametrize("dtype,n,k,rows", [(torch.float32, 257, 1024, 16), (torch.bfloat16, 256, 7168, 5)])
+def test_rowdot_columns_per_cta_do_not_change_the_bits(dtype, n, k, rows, monkeypatch):
+    """Two output columns per CTA share the activation loads; every column's sum keeps its order."""
+    g = torch.Generator().manual_seed(n)
+    w = torch.randn(n, k, generator=g).to(dtype).to(DEV)
+    x = torch.randn(16, k, generator=g).bfloat16().to(DEV)
+    outs = []
+    for cols in ("1", "2"):
+        monkeypatch.setenv("MONO_ROWDOT_COLS", cols)
+        out = torch.zeros(16, n, device=DEV)
+        ops.rowdot(rows, w, x, out, out_scale=0.5)
+        torch.cuda.synchronize()
+        outs.append(out.cpu())
+    assert torch.equal(outs[0], outs[1])
+    ref = 0.5 * (x[:rows].float().cpu() @ w.float().cpu().T)
+    assert_rel(outs[1][:rows], ref, "rowdot", 1e-3)
+    assert not bool(outs[1][rows:].any()), "rows past the step are not written"
