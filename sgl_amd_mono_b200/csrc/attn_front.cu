@@ -49,7 +49,24 @@ __device__ __forceinline__ void fwht128(float* x, int t /* 0..127 */) {
 }
 
 __global__ void __launch_bounds__(kMidThreads2) mla_mid_kernel(const mono_mla_mid_args a) {
-    pdl_prologue();
+    pdl_launch_dependents();
+    {
+        // during the wait for the GEMV before this launch: the norm weights and this row's rotary entries
+        // (the step's positions are inputs of the step, not results of that GEMV)
+        const int t = threadIdx.x, part_ = blockIdx.y;
+        if (part_ == 0) prefetch_span(a.q_a_norm, (size_t)a.q_lora * 2, t, kMidThreads2);
+        if (part_ == 1) prefetch_span(a.kv_a_norm, 512 * 2, t, kMidThreads2);
+        if (part_ == 2 && a.ik) {
+            prefetch_span(a.ik_norm_w, 128 * 4, t, kMidThreads2);
+            prefetch_span(a.ik_norm_b, 128 * 4, t, kMidThreads2);
+        }
+        if (t == 0 && part_ != 0) {
+            const int64_t pos_ = a.positions[blockIdx.x];
+            prefetch_l2(reinterpret_cast<const __nv_bfloat16*>(a.cos) + pos_ * 32);
+            prefetch_l2(reinterpret_cast<const __nv_bfloat16*>(a.sin) + pos_ * 32);
+        }
+    }
+    pdl_wait();
     __shared__ __align__(16) float xq[2048 + 64];
     __shared__ __align__(16) float kv[kKvDim];
     __shared__ float ikv[128];
@@ -191,7 +208,13 @@ __global__ void __launch_bounds__(kMidThreads2) mla_mid_kernel(const mono_mla_mi
 constexpr int kQPostThreads = 128;
 
 __global__ void __launch_bounds__(kQPostThreads) q_post_kernel(const mono_q_post_args a) {
-    pdl_prologue();
+    pdl_launch_dependents();
+    if ((int)blockIdx.x < a.heads * 8) {
+        // during the wait for the GEMV before this launch: this block's 128 x 64-byte slab of W_UK
+        const int h_ = blockIdx.x >> 3, cq_ = blockIdx.x & 7;
+        prefetch_l2(a.kv_b + ((size_t)h_ * 256 + threadIdx.x) * 512 + cq_ * 64);
+    }
+    pdl_wait();
     __shared__ float qn[kMaxRows][128];
     __shared__ float iq[128];
     const int tid = threadIdx.x;

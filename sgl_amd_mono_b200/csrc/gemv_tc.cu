@@ -386,6 +386,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
             for (int local = first; local < ntask && budget > 0; local += gridDim.x) {
                 const TcSeg s = tc_make_seg(jb, local % nrb, local / nrb, 0);
                 for (int t = lane; t < min(s.nt, budget); t += 32) tma_prefetch_3d(wmap, (s.t0 + t) * 128, s.row0, s.c2);
+                if (lane == 0 && jb.wscale_f32) prefetch_l2(s.wsc);  // the segment's weight scales (at most 128 bytes)
                 budget -= s.nt;
             }
             base += ntask;

@@ -148,6 +148,23 @@ __global__ void __launch_bounds__(kThreads) index_score_tc_kernel(const mono_ind
     __syncthreads();
     fence_after();
     const uint32_t tmem_base = tmem_base_s;
+    {
+        // during the wait for the launch that writes the index queries: the row's head weights (written
+        // by an earlier launch; an L2 prefetch is safe in any case) and the bytes of this thread's first key
+        // (the step's positions, slots and page table are inputs of the step; the index key of the new
+        // token was written launches ago)
+        if (tid == 0) prefetch_l2(a.idx_w + (size_t)row * a.w_ld);
+        const int p = tile0 * kTile + tid;
+        const int pi = p / kPage;
+        if (pi < a.pt_ld && (!a.slots || a.slots[row] >= 0) && p <= (int)a.positions[row]) {
+            const int64_t pg = a.page_table[(size_t)row * a.pt_ld + pi];
+            if (pg >= 0 && pg < a.n_pages) {
+                const uint8_t* page = a.idx_pages + (size_t)pg * kIdxPageBytes;
+                prefetch_l2(page + (size_t)(p % kPage) * 64);
+                if ((tid & 31) == 0) prefetch_l2(page + kPage * 64 + (p % kPage) * 4);
+            }
+        }
+    }
     pdl_wait();
     // the row's position, its slot and the task's page table entries are requested together (one memory
     // latency); a key request is then one more, not two

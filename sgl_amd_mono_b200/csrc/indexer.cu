@@ -285,7 +285,12 @@ constexpr int kClSpan = kTopkThreads * kClKeys;
 
 __global__ void __cluster_dims__(kClSize, 1, 1) __launch_bounds__(kTopkThreads)
     index_topk_cluster_kernel(const mono_index_args a) {
-    pdl_prologue();
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {  // during the wait for the scores: the step's tables of this row
+        prefetch_l2(a.positions + blockIdx.x / kClSize);
+        prefetch_l2(a.page_table + (size_t)(blockIdx.x / kClSize) * a.pt_ld);
+    }
+    pdl_wait();
     cg::cluster_group cluster = cg::this_cluster();
     __shared__ int hist[2][256];
     __shared__ uint32_t s_prefix;

@@ -243,6 +243,18 @@ __device__ __forceinline__ void pdl_prologue() {
     pdl_launch_dependents();
     pdl_wait();
 }
+// What a kernel may do before pdl_wait(): under programmatic dependent launch its CTAs start while the
+// launch before it still runs, so only data that launch does not write may be touched.  Between two
+// layers' weight streams nothing of a small kernel's tables is left in L2: pulling them in during the
+// wait takes their HBM latency off the dependent chain.  A prefetch into L2 is safe for any address
+// (L2 is the device's point of coherence), which is why these helpers do nothing else.
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+// the threads tid = 0 .. nthreads-1 pull `bytes` bytes at p into L2, one 128-byte line per thread and turn
+__device__ __forceinline__ void prefetch_span(const void* p, size_t bytes, int tid, int nthreads) {
+    if (!p) return;
+    const char* c = reinterpret_cast<const char*>(p);
+    for (size_t o = (size_t)tid * 128; o < bytes; o += (size_t)nthreads * 128) prefetch_l2(c + o);
+}
 
 // ld / st that bypass the non-coherent L1 (data produced by other SMs or other GPUs)
 __device__ __forceinline__ float ld_cg_f32(const float* p) {

@@ -237,6 +237,17 @@ __global__ void __launch_bounds__(256) sparse_mla_merge_kernel(const mono_sparse
     const float* part_ml = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(a.scratch) +
                                                           (size_t)a.rows * nsplit * a.heads * 512 * sizeof(__nv_bfloat16));
     const int tid = threadIdx.x;
+    const int col = 2 * tid;
+    // every thread requests its column pair of the first 32 partials before anything waits: the weights of
+    // the splits (warp 0) and the partials arrive in the same memory latency
+    constexpr int kBatch = 32;
+    uint32_t pv[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+        pv[j] = 0u;
+        if (j < nsplit)
+            pv[j] = *reinterpret_cast<const uint32_t*>(part_acc + (((size_t)row * nsplit + j) * a.heads + head) * 512 + col);
+    }
     if (tid < 32) {
         float mx = -INFINITY;
         for (int j = tid; j < nsplit; j += 32) mx = fmaxf(mx, part_ml[(((size_t)row * nsplit + j) * a.heads + head) * 2]);
@@ -253,10 +264,17 @@ __global__ void __launch_bounds__(256) sparse_mla_merge_kernel(const mono_sparse
         for (int j = tid; j < nsplit; j += 32) w[j] = den > 0.f ? w[j] / den : 0.f;
     }
     __syncthreads();
-    const int col = 2 * tid;
     float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+        if (j < nsplit) {
+            const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&pv[j]);
+            a0 += __low2float(v) * w[j];
+            a1 += __high2float(v) * w[j];
+        }
+    }
 #pragma unroll 8
-    for (int j = 0; j < nsplit; ++j) {
+    for (int j = kBatch; j < nsplit; ++j) {
         const __nv_bfloat162 v =
             *reinterpret_cast<const __nv_bfloat162*>(part_acc + (((size_t)row * nsplit + j) * a.heads + head) * 512 + col);
         a0 += __low2float(v) * w[j];

@@ -19,7 +19,9 @@ namespace mono {
 constexpr int kPrepThreads = 1024;
 
 __global__ void __launch_bounds__(kPrepThreads) act_prep_kernel(const mono_act_prep_args a) {
-    pdl_prologue();
+    pdl_launch_dependents();
+    prefetch_span(a.gamma_bf16, (size_t)a.k * 2, threadIdx.x, kPrepThreads);  // the norm weights, during the wait
+    pdl_wait();
     extern __shared__ float xrow[];
     __shared__ float red[kPrepThreads / 32];
     const int segs = a.segs > 1 ? a.segs : 1;
@@ -213,7 +215,9 @@ __device__ __forceinline__ void route_body(const mono_route_args& a, RouteSmem& 
 
 __global__ void __launch_bounds__(kRouteThreads) route_kernel(const mono_route_args a) {
     __shared__ RouteSmem sm;
-    pdl_prologue();
+    pdl_launch_dependents();
+    prefetch_span(a.bias, (size_t)a.n_experts * 4, threadIdx.x, kRouteThreads);  // during the wait for the logits
+    pdl_wait();
     route_body(a, sm);
 }
 
@@ -405,9 +409,16 @@ __device__ __forceinline__ void st_sys_u32(uint64_t addr, uint32_t a) {
 }
 
 __global__ void __launch_bounds__(kReduceThreads) reduce_kernel(const mono_reduce_args a) {
-    pdl_prologue();
+    pdl_launch_dependents();
     const int pairs = a.n / 2;
     const int total = a.rows * pairs;
+    if (a.residual && (threadIdx.x & 31) == 0) {
+        // during the wait for the GEMV before this launch: the residual pairs of this warp's first turn
+        // (128 bytes; the residual is older than that GEMV's output)
+        const int idx0 = blockIdx.x * kReduceThreads + threadIdx.x;
+        if (idx0 < total) prefetch_l2(reinterpret_cast<const __nv_bfloat162*>(a.residual) + idx0);
+    }
+    pdl_wait();
     uint32_t tag = a.tag;
     int parity = a.parity;
     if (a.world > 1 && a.guard && tag == 0) {
