@@ -445,6 +445,15 @@ typedef struct mono_index_args {
     int score_ld;
     int32_t* topk_slots; /* [16][topk] */
     int32_t* topk_pos;   /* [16][topk] positions (parity witness) or NULL */
+    /* Optional (tcgen05 score kernel only): with iq set the score launch makes the index queries itself
+     * from the q_b GEMV's partial sums (sum of iq_nsum slices, interleaved RoPE on the first 64 dims,
+     * orthonormal Hadamard over 128: glm53/gfx950/kernel.py:2262-2353, the index half of
+     * mono_q_post_launch) and, when idx_q is not NULL, also writes them there. */
+    const float* iq; /* [iq_nsum][16][iq_ld] */
+    int iq_nsum, iq_ld;
+    long iq_sum_stride;
+    const void* cos; /* bf16 [positions][32] */
+    const void* sin;
 } mono_index_args;
 int mono_index_score_launch(const mono_index_args* a, void* stream);
 int mono_index_topk_launch(const mono_index_args* a, void* stream);

@@ -131,6 +131,7 @@ class IndexArgs(C.Structure):
         ("rows", i32), ("index_heads", i32), ("topk", i32), ("idx_q", vp), ("idx_w", vp), ("w_ld", i32),
         ("idx_pages", vp), ("n_pages", C.c_int64), ("page_table", vp), ("pt_ld", i32), ("positions", vp),
         ("slots", vp), ("scores", vp), ("score_ld", i32), ("topk_slots", vp), ("topk_pos", vp),
+        ("iq", vp), ("iq_nsum", i32), ("iq_ld", i32), ("iq_sum_stride", i64), ("cos", vp), ("sin", vp),
     ]
 
 

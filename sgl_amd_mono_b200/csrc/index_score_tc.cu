@@ -183,8 +183,61 @@ __global__ void __launch_bounds__(kThreads) index_score_tc_kernel(const mono_ind
         __syncthreads();
         RawKey nk = request_key(a, pages, p0, p0 + tid, n);
         // ---- q (zero rows past index_heads) as the B operand, and the head weights
-        const __nv_bfloat16* qg = reinterpret_cast<const __nv_bfloat16*>(a.idx_q);
-        {
+        if (a.iq) {
+            // the queries are made here from the q_b GEMV's partial sums: a warp takes a head at a time, a lane
+            // dims 4 lane .. 4 lane + 3.  Sum of the slices, interleaved RoPE on dims 0..63, Hadamard
+            // butterflies of span 1, 2, 4 ... 64 (spans 1 and 2 inside the lane, the others by shuffles),
+            // x 128^-1/2: the arithmetic and its order are those of the stand-alone query stage.
+            const int lane = tid & 31;
+            const __nv_bfloat16* cosb = reinterpret_cast<const __nv_bfloat16*>(a.cos);
+            const __nv_bfloat16* sinb = reinterpret_cast<const __nv_bfloat16*>(a.sin);
+            float c0 = 0.f, s0 = 0.f, c1 = 0.f, s1 = 0.f;
+            if (lane < 16) {
+                c0 = __bfloat162float(cosb[pos * 32 + 2 * lane]);
+                s0 = __bfloat162float(sinb[pos * 32 + 2 * lane]);
+                c1 = __bfloat162float(cosb[pos * 32 + 2 * lane + 1]);
+                s1 = __bfloat162float(sinb[pos * 32 + 2 * lane + 1]);
+            }
+            __nv_bfloat16* qout = (a.idx_q && tile0 == 0) ? reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(a.idx_q)) : nullptr;
+#pragma unroll 2
+            for (int h = warp; h < 64; h += kThreads / 32) {
+                float v[4] = {0.f, 0.f, 0.f, 0.f};
+                if (h < a.index_heads) {
+                    const float* src = a.iq + (size_t)row * a.iq_ld + h * 128 + 4 * lane;
+                    for (int sl = 0; sl < a.iq_nsum; ++sl) {
+                        const float4 p = *reinterpret_cast<const float4*>(src + (size_t)sl * a.iq_sum_stride);
+                        v[0] += p.x; v[1] += p.y; v[2] += p.z; v[3] += p.w;
+                    }
+                    if (lane < 16) {
+                        const float x0 = v[0], x1 = v[1], x2 = v[2], x3 = v[3];
+                        v[0] = x0 * c0 - x1 * s0;
+                        v[1] = x0 * s0 + x1 * c0;
+                        v[2] = x2 * c1 - x3 * s1;
+                        v[3] = x2 * s1 + x3 * c1;
+                    }
+                    {   // span 1, then span 2
+                        const float a0 = v[0] + v[1], a1 = v[0] - v[1], a2 = v[2] + v[3], a3 = v[2] - v[3];
+                        v[0] = a0 + a2; v[2] = a0 - a2; v[1] = a1 + a3; v[3] = a1 - a3;
+                    }
+#pragma unroll
+                    for (int m = 1; m < 32; m <<= 1) {  // span 4 m: the partner is lane ^ m
+                        const bool upper = (lane & m) != 0;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float o = __shfl_xor_sync(0xffffffffu, v[j], m);
+                            v[j] = upper ? o - v[j] : v[j] + o;
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) v[j] *= 0.08838834764831845f;
+                }
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+                const uint2 pk = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+                *reinterpret_cast<uint2*>(bbuf + swz(h, lane >> 1, kBBytes / 2) + (lane & 1) * 8) = pk;
+                if (qout && h < a.index_heads) *reinterpret_cast<uint2*>(qout + ((size_t)row * a.index_heads + h) * 128 + 4 * lane) = pk;
+            }
+        } else {
+            const __nv_bfloat16* qg = reinterpret_cast<const __nv_bfloat16*>(a.idx_q);
             uint4 qv[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {

@@ -465,8 +465,13 @@ static int check_index_args(const mono_index_args* a, const char* who) {
 
 extern "C" int mono_index_score_launch(const mono_index_args* a, void* stream) {
     if (int rc = check_index_args(a, "mono_index_score_launch")) return rc;
-    if (!a->idx_q || !a->idx_w || !a->idx_pages) {
-        mono_set_error("mono_index_score_launch: idx_q, idx_w and idx_pages required");
+    if ((!a->idx_q && !a->iq) || !a->idx_w || !a->idx_pages) {
+        mono_set_error("mono_index_score_launch: idx_q (or iq), idx_w and idx_pages required");
+        return MONO_E_ARG;
+    }
+    if (a->iq && (!a->cos || !a->sin || a->iq_nsum < 1 || (a->iq_ld & 3) || (a->iq_sum_stride & 3) ||
+                  (reinterpret_cast<uintptr_t>(a->iq) & 15) || (reinterpret_cast<uintptr_t>(a->idx_q) & 7))) {
+        mono_set_error("mono_index_score_launch: iq needs cos, sin, iq_nsum >= 1 and 16-byte aligned rows");
         return MONO_E_ARG;
     }
     {
@@ -477,6 +482,10 @@ extern "C" int mono_index_score_launch(const mono_index_args* a, void* stream) {
             if (rc != 0) mono_set_error("mono_index_score_launch: %s", cudaGetErrorString((cudaError_t)rc));
             return rc;
         }
+    }
+    if (a->iq) {
+        mono_set_error("mono_index_score_launch: index queries from partial sums (iq) are made by the tcgen05 kernel only");
+        return MONO_E_ARG;
     }
     const size_t smem = sizeof(mono::ScoreSmem) + 128;
     static thread_local bool attr_set = false;

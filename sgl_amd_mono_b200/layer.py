@@ -93,6 +93,7 @@ class MlaLayerOp:
         self.topk_slots = torch.full((R, self.topk), -1, dtype=torch.int32, device=device)
         self.topk_pos = torch.full((R, self.topk), -1, dtype=torch.int32, device=device)
         self.mla_staged = os.environ.get("MONO_MLA_STAGED", "1") != "0"
+        self.idxq_fused = (os.environ.get("MONO_IDXQ_FUSED", "0") != "0" and os.environ.get("MONO_INDEX_SCORE_TC", "1") != "0")
         self.attn = SparseMlaOp(hl, self.topk, device, max_rows=R, sm_scale=(cfg.nope + cfg.rope) ** -0.5)
         # ---- W_UV (per head) and o_proj
         self.lat = ops.ActBuf(L.ACT_HILO, 512, device, segs=hl)
@@ -154,8 +155,13 @@ class MlaLayerOp:
                     self.qa, step.kv_pages, step.idx_pages, self.kv_out, ik=self.ik_p, ik_nsum=self.nsA,
                     ik_out=self.ik_out if ih else None)
         self.gB.launch(rows)
+        # MONO_IDXQ_FUSED=1: the score launch makes the index queries itself from the q_b partial sums instead of
+        # a query launch before it.  Same bits, but measured 4 us (TP 8 shard) to 9 us (TP 1) slower per layer:
+        # every score CTA repeats the 64 heads' sums, rotations and Hadamard butterflies.  Off by default.
+        fused_q = bool(ih) and self.idxq_fused and self._side is not None
         ia = ops.index_args(rows, max(ih, 1), self.topk, self.idx_q, self.idx_w, step.idx_pages, step.page_table,
-                            step.positions, step.slots, self.scores, self.topk_slots, self.topk_pos)
+                            step.positions, step.slots, self.scores, self.topk_slots, self.topk_pos,
+                            **(dict(iq=self.iq_p, iq_nsum=self.nsB, cos=step.cos, sin=step.sin) if fused_q else {}))
         if ih and self._side is not None:
             # index queries -> scores -> top-k on the side stream (behind the head weights already queued
             # there), the W_UK absorb of the heads on the main one; joined before the attention
@@ -163,8 +169,9 @@ class MlaLayerOp:
             self._ev_fork.record(main)
             self._side.wait_event(self._ev_fork)
             with torch.cuda.stream(self._side):
-                ops.q_post(rows, 0, self.qb_p, self.nsB, w["kv_b"], w["kv_b_s"], step.cos, step.sin, step.positions,
-                           self.q_full, ih, self.iq_p, self.nsB, self.idx_q)
+                if not fused_q:
+                    ops.q_post(rows, 0, self.qb_p, self.nsB, w["kv_b"], w["kv_b_s"], step.cos, step.sin, step.positions,
+                               self.q_full, ih, self.iq_p, self.nsB, self.idx_q)
                 ops.index_score(ia)
                 ops.index_topk(ia)
                 self._ev_join.record(self._side)

@@ -346,8 +346,13 @@ def q_post(rows: int, heads: int, qb, nsum: int, kv_b, kv_b_scale, cos, sin, pos
 
 
 def index_args(rows: int, index_heads: int, topk: int, idx_q, idx_w, idx_pages, page_table, positions, slots,
-               scores, topk_slots, topk_pos=None) -> "L.IndexArgs":
+               scores, topk_slots, topk_pos=None, iq=None, iq_nsum: int = 0, cos=None, sin=None) -> "L.IndexArgs":
+    """``iq`` (with ``cos`` / ``sin``): the q_b GEMV's partial sums of the index queries; the score launch
+    then makes the queries itself (tcgen05 kernel) instead of reading ``idx_q``."""
     a = L.IndexArgs()
+    if iq is not None:
+        a.iq, a.iq_nsum, a.iq_ld, a.iq_sum_stride = iq.data_ptr(), iq_nsum, iq.shape[-1], L.MAX_ROWS * iq.shape[-1]
+        a.cos, a.sin = cos.data_ptr(), sin.data_ptr()
     a.rows, a.index_heads, a.topk = rows, index_heads, topk
     a.idx_q, a.idx_w, a.w_ld = _p(idx_q), _p(idx_w), idx_w.shape[-1] if idx_w is not None else 0
     a.idx_pages, a.n_pages = _p(idx_pages), idx_pages.shape[0] if idx_pages is not None else 0

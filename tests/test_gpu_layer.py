@@ -227,3 +227,20 @@ def test_tcgen05_index_scores_match_the_mma_sync_kernel(rows, ctx, monkeypatch):
         scale = float(ref[i, :n].abs().max())
         assert float((tc[i, :n] - ref[i, :n]).abs().max()) <= 1e-4 * scale + 1e-6, f"row {i}"
         assert torch.equal(tc[i, n:], ref[i, n:]), "columns past the row's keys stay as they were"
+
+
+@pytest.mark.parametrize("rows,ctx", [(8, 1000), (5, 200)])
+def test_index_queries_made_by_the_score_launch(rows, ctx, monkeypatch):
+    """The tcgen05 score launch can make the index queries itself (sum of the q_b partial sums, RoPE,
+    Hadamard) with the arithmetic of the stand-alone query stage: same queries, scores and selection."""
+    monkeypatch.setenv("MONO_IDXQ_FUSED", "1")
+    op, _, step, _, _, out = _run(CFG_TINY, rows, ctx)
+    assert op.idxq_fused and op._side is not None
+    monkeypatch.setenv("MONO_IDXQ_FUSED", "0")
+    op2, _, _, _, _, out2 = _run(CFG_TINY, rows, ctx)
+    assert not op2.idxq_fused
+    assert bool(op2.idx_q[:rows].float().abs().sum() > 0)
+    assert torch.equal(op.idx_q[:rows], op2.idx_q[:rows])
+    assert torch.equal(op.scores[:rows], op2.scores[:rows])
+    assert torch.equal(op.topk_slots[:rows], op2.topk_slots[:rows])
+    assert torch.equal(out, out2)
