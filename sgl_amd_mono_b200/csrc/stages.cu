@@ -113,6 +113,7 @@ struct RouteSmem {
     int warp_cnt[kRouteThreads / 32];
 };
 
+template <int kSlots>  // experts per lane: 8 serves up to 256 experts, 16 up to 512
 __device__ __forceinline__ void route_body(const mono_route_args& a, RouteSmem& sm) {
     auto& sc = sm.sc;
     auto& used = sm.used;
@@ -154,26 +155,30 @@ __device__ __forceinline__ void route_body(const mono_route_args& a, RouteSmem& 
             if (a.scores) a.scores[(size_t)r * a.n_experts + e] = s;
         }
         __syncwarp();
-        // a lane owns experts lane, lane + 32, ...; `taken` has one bit per owned expert already picked.
-        // A pick = the largest key (monotone image of score + bias) of the warp, then the lowest
-        // expert id among its holders (a lane's lowest id is its lowest slot: the first strict maximum)
-        uint32_t taken = 0u;
-        const int nslots = (a.n_experts + 31) >> 5;
+        // a lane owns experts lane, lane + 32, ... and keeps their keys (monotone image of score + bias;
+        // 0 = none, or already picked) in kSlots registers.  A pick = the largest key of the warp, then the
+        // lowest expert id among its holders (a lane's lowest id is its lowest slot: the first strict
+        // maximum).  The loop over the picks stays rolled; only the kSlots-wide steps inside are unrolled.
+        uint32_t keys[kSlots];
+#pragma unroll
+        for (int i = 0; i < kSlots; ++i) {
+            const int e = lane + 32 * i;
+            keys[i] = 0u;
+            if (e < a.n_experts) keys[i] = radix_key(a.bias ? sc[r][e] + sm.bias[e] : sc[r][e]);
+        }
         float wsum = 0.f;
 #pragma unroll 1
         for (int k = 0; k < a.top_k; ++k) {
             uint32_t best = 0u;
             int slot = 0;
-#pragma unroll 1
-            for (int i = 0; i < nslots; ++i) {
-                const int e = lane + 32 * i;
-                uint32_t key = 0u;
-                if (e < a.n_experts && !((taken >> i) & 1u)) key = radix_key(a.bias ? sc[r][e] + sm.bias[e] : sc[r][e]);
-                if (key > best) { best = key; slot = i; }
-            }
+#pragma unroll
+            for (int i = 0; i < kSlots; ++i)
+                if (keys[i] > best) { best = keys[i]; slot = i; }
             const uint32_t top = __reduce_max_sync(0xffffffffu, best);
             const int e = (int)__reduce_min_sync(0xffffffffu, best == top ? (uint32_t)(lane + 32 * slot) : 0xFFFFFFFFu);
-            if (lane == (e & 31)) taken |= 1u << (e >> 5);
+#pragma unroll
+            for (int i = 0; i < kSlots; ++i)
+                if (lane == (e & 31) && i == (e >> 5)) keys[i] = 0u;
             if (lane == 0) { sel[r][k] = e; selw[r][k] = sc[r][e]; }
             wsum += sc[r][e];
         }
@@ -218,7 +223,8 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const mono_route_a
     pdl_launch_dependents();
     prefetch_span(a.bias, (size_t)a.n_experts * 4, threadIdx.x, kRouteThreads);  // during the wait for the logits
     pdl_wait();
-    route_body(a, sm);
+    if (a.n_experts <= 256) route_body<8>(a, sm);
+    else route_body<16>(a, sm);
 }
 
 // ------------------------------------------------------------------ small row-dot GEMV
@@ -335,7 +341,8 @@ __global__ void __launch_bounds__(kRouteThreads) router_kernel(const mono_rowdot
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    route_body(r, sm);
+    if (r.n_experts <= 256) route_body<8>(r, sm);
+    else route_body<16>(r, sm);
 }
 
 // ------------------------------------------------------------------ expert activation
