@@ -102,12 +102,13 @@ class MlaLayerOp:
         self.o = ops.ActBuf(L.ACT_HILO, hl * 128, device)
         # on the tcgen05 consumer the W_UV job can write its output straight into o_proj's activation planes
         # (MONO_UV_STAGED=1 / 0).  Measured on config 3: 6 us faster per layer with 128 local heads (128 CTAs
-        # share the staging), 6 us slower with 16 (the staging lengthens the one task each of 16 CTAs runs,
-        # and a staging launch of 2.4 us in between costs less than that): the default follows the head count
+        # share the staging), 3.5 / 5 / 6 us slower with 64 / 32 / 16 (the staging lengthens the one task each
+        # of those CTAs runs, and a staging launch of 2.4 us in between costs less than that): the default
+        # follows the head count
         lib = L.load()
         tc_on = lib.mono_set_gemv_tcgen05(1)
         lib.mono_set_gemv_tcgen05(tc_on)
-        self.uv_staged = bool(tc_on) and os.environ.get("MONO_UV_STAGED", "1" if hl >= 64 else "0") != "0"
+        self.uv_staged = bool(tc_on) and os.environ.get("MONO_UV_STAGED", "1" if hl >= 128 else "0") != "0"
         self.gUV.add("kv_b(W_UV)", w["kv_b"].view(hl, 256, 512), self.lat, self.uv_p, wscale=w["kv_b_s"].view(hl, 2, 4),
                      n_rows=128, row_off=128, rb_per_mat=1, n_mats=hl, act_per_mat=True, split_tiles=4, nsplit=1,
                      stage=self.o if self.uv_staged else None)
