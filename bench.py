@@ -161,6 +161,35 @@ class _Null:
         return False
 
 
+class Lazy:
+    """Expert tensors stay where they were generated; the oracle copies to the host only those it routes to."""
+
+    def __init__(self, v):
+        self.v, self.c = v, {}
+
+    def __getitem__(self, e):
+        e = int(e)
+        if e not in self.c:
+            self.c[e] = self.v[e].cpu()
+        return self.c[e]
+
+
+def host_weights(w):
+    return {k: (Lazy(v) if k in ("w13", "w13_s", "w2", "w2_s") else (v.cpu() if isinstance(v, torch.Tensor) else v))
+            for k, v in w.items()}
+
+
+def time_oracle(fn, runs: int):
+    """One warm-up (it also pulls the routed experts to the host), then the median of ``runs`` runs, in us."""
+    fn()
+    ts = []
+    for _ in range(runs):
+        t0 = time.perf_counter()
+        fn()
+        ts.append(time.perf_counter() - t0)
+    return statistics.median(ts) * 1e6
+
+
 # ------------------------------------------------------------------ workloads
 class SparseMlaWorkload:
     """BASELINE config 2: sparse MLA decode attention alone, 8 rows x 16 local heads,
@@ -174,13 +203,18 @@ class SparseMlaWorkload:
     def __init__(self, rows=8, heads=16, ctx=32768, topk=2048):
         self.rows, self.heads, self.ctx, self.topk = rows, heads, ctx, topk
 
-    def setup(self, dev, rank, world):
+    def make_inputs(self, dev, rank, tp):
+        """Synthetic inputs only (torch): nothing of the kernel library is touched."""
         from sgl_amd_mono_b200 import synth
-        from sgl_amd_mono_b200.attention import SparseMlaOp
 
         self.dev = dev
-        q, pages, sel, _ = synth.sparse_mla_inputs(self.rows, self.heads, self.ctx, self.topk, device=dev, seed=rank)
-        self.q, self.pages, self.sel = q, pages, sel
+        self.q, self.pages, self.sel, _ = synth.sparse_mla_inputs(self.rows, self.heads, self.ctx, self.topk, device=dev, seed=rank)
+
+    def setup(self, dev, rank, world):
+        from sgl_amd_mono_b200.attention import SparseMlaOp
+
+        self.make_inputs(dev, rank, world)
+        q, pages, sel = self.q, self.pages, self.sel
         self.op = SparseMlaOp(self.heads, self.topk, dev, sm_scale=192**-0.5)
         self.q_host, self.sel_host = q.cpu().pin_memory(), sel.cpu().pin_memory()
         self.q_in, self.sel_in = torch.empty_like(q), torch.empty_like(sel)
@@ -209,18 +243,15 @@ class SparseMlaWorkload:
                 "topk": self.topk, "kv_cache": "fp8_e4m3 + f32 scale per token, page 64",
                 "l2": "256 MiB buffer written between timed iterations"}
 
-    def cpu_sample(self):
+    def oracle_step(self):
         from oracle import stages as S
 
-        n = 2
-        q, pages, sel = self.q[:n].cpu(), self.pages.cpu(), self.sel[:n].cpu()
-        S.sparse_mla(q[:1], pages, sel[:1], 192**-0.5)
-        ts = []
-        for _ in range(3):
-            t0 = time.perf_counter()
-            S.sparse_mla(q, pages, sel, 192**-0.5)
-            ts.append(time.perf_counter() - t0)
-        return statistics.median(ts) * 1e6 * self.rows / n, f"{n} of {self.rows} rows, scaled by rows; median of 3"
+        q, pages, sel = self.q.cpu(), self.pages.cpu(), self.sel.cpu()
+        return (lambda: S.sparse_mla(q, pages, sel, 192**-0.5)), f"all {self.rows} rows"
+
+    def cpu_sample(self):
+        fn, what = self.oracle_step()
+        return time_oracle(fn, 3), what + "; median of 3 after one warm-up"
 
 
 class MoeWorkload:
@@ -235,24 +266,31 @@ class MoeWorkload:
     def __init__(self, rows=8):
         self.rows = rows
 
-    def setup(self, dev, rank, world, peer=None):
+    def make_inputs(self, dev, rank, tp, world=1):
         from sgl_amd_mono_b200 import synth
         from sgl_amd_mono_b200.config import CFG_V3
-        from sgl_amd_mono_b200.moe import MoeFfn
         from dataclasses import replace
 
-        tp = getattr(self, "shard_of", 0) or world  # --shard-of N: one rank's share of TP = N, no peers
         self.cfg = replace(CFG_V3, n_heads=0, index_heads=0).with_tp(tp)
         self.name = f"cfg3_moe_half_tp{tp}_{self.rows}rows" + ("_one_shard" if tp != world else "")
         self.w = synth.layer_weights(self.cfg, rank, dev)
-        self.ffn = MoeFfn(self.cfg, self.w, dev, peer=peer)
         g = torch.Generator().manual_seed(0)
-        self.x_host = torch.randn(self.rows, self.cfg.hidden, generator=g).bfloat16().pin_memory()
+        self.x_host = torch.randn(self.rows, self.cfg.hidden, generator=g).bfloat16()
+        self.distinct = None
+
+    def setup(self, dev, rank, world, peer=None):
+        from sgl_amd_mono_b200.moe import MoeFfn
+
+        tp = getattr(self, "shard_of", 0) or world  # --shard-of N: one rank's share of TP = N, no peers
+        self.make_inputs(dev, rank, tp, world)
+        self.ffn = MoeFfn(self.cfg, self.w, dev, peer=peer)
+        self.x_host = self.x_host.pin_memory()
         self.x = self.x_host.to(dev)
         self.x_in = torch.empty_like(self.x)
         self.out_host = torch.empty_like(self.x_host).pin_memory()
         self.ffn(self.x)
         torch.cuda.synchronize()
+        self.distinct = int(self.ffn.n_expert.item())
         self.launches_per_step = 8
 
     def step(self):
@@ -276,28 +314,24 @@ class MoeWorkload:
     def config(self):
         c = self.cfg
         return {"workload": self.name, "rows": self.rows, "hidden": c.hidden, "experts": c.n_experts, "top_k": c.top_k,
-                "inter": c.inter, "tp": c.tp, "distinct_experts": int(self.ffn.n_expert.item()),
+                "inter": c.inter, "tp": c.tp, "distinct_experts": self.distinct,
                 "weights": "fp8_e4m3 128x128 block scales", "l2": "256 MiB buffer written between timed iterations"}
 
-    def cpu_sample(self):
+    def oracle_step(self):
         from oracle import layers as OL
 
-        ids = self.ffn.ids[: self.rows].cpu()
-        used = sorted(set(ids[:1].flatten().tolist()))
-        w = {}
-        for k, v in self.w.items():
-            if k in ("w13", "w13_s", "w2", "w2_s"):
-                w[k] = {e: v[e].cpu() for e in used}
-            else:
-                w[k] = v.cpu()
-        x = self.x_host[:1]
-        OL.moe_partial(self.cfg, w, x)
-        ts = []
-        for _ in range(3):
-            t0 = time.perf_counter()
-            OL.moe_partial(self.cfg, w, x)
-            ts.append(time.perf_counter() - t0)
-        return statistics.median(ts) * 1e6 * self.rows, f"1 of {self.rows} rows, scaled by rows; median of 3"
+        w, x = host_weights(self.w), self.x_host.clone()
+
+        def fn():
+            _, ids, _, _ = OL.moe_partial(self.cfg, w, x)
+            if self.distinct is None:
+                self.distinct = int(ids.unique().numel())
+
+        return fn, f"all {self.rows} rows"
+
+    def cpu_sample(self):
+        fn, what = self.oracle_step()
+        return time_oracle(fn, 3), what + "; median of 3 after one warm-up"
 
 
 class LayerWorkload:
@@ -314,14 +348,26 @@ class LayerWorkload:
     def __init__(self, rows=8, ctx=16384):
         self.rows, self.ctx = rows, ctx
 
-    def setup(self, dev, rank, world):
-        from sgl_amd_mono_b200 import ops, synth
+    def make_inputs(self, dev, rank, tp, world=1):
+        """Synthetic weights, caches, tables and rows (torch only: nothing of the kernel library is touched)."""
+        from sgl_amd_mono_b200 import synth
         from sgl_amd_mono_b200.config import CFG_V3
+
+        self.cfg = cfg = CFG_V3.with_tp(tp)
+        self.name = f"cfg3_v3_mla_dsa_moe_layer_tp{tp}_{self.rows}rows_ctx{self.ctx}" + ("_one_shard" if tp != world else "")
+        self.w = synth.layer_weights(cfg, rank, dev)
+        self.step_in = synth.decode_step(cfg, self.rows, self.ctx, device=dev)
+        g = torch.Generator().manual_seed(0)
+        self.h_host = torch.randn(self.rows, cfg.hidden, generator=g).bfloat16()
+        self.distinct = None
+
+    def setup(self, dev, rank, world):
+        from sgl_amd_mono_b200 import ops
         from sgl_amd_mono_b200.layer import MlaLayerOp, StepTables
 
         tp = getattr(self, "shard_of", 0) or world  # --shard-of N: one rank's share of TP = N, no peers
-        self.cfg = cfg = CFG_V3.with_tp(tp)
-        self.name = f"cfg3_v3_mla_dsa_moe_layer_tp{tp}_{self.rows}rows_ctx{self.ctx}" + ("_one_shard" if tp != world else "")
+        self.make_inputs(dev, rank, tp, world)
+        cfg = self.cfg
         self.peer = None
         if world > 1:
             import torch.distributed as dist
@@ -329,14 +375,14 @@ class LayerWorkload:
 
             self.cpu_group = dist.new_group(backend="gloo")
             self.peer = PeerBuffer(cfg.hidden, rank, world, self.cpu_group, dev)
-        self.w = synth.layer_weights(cfg, rank, dev)
-        step = synth.decode_step(cfg, self.rows, self.ctx, device=dev)
+        step = self.step_in
+        # the oracle reads the caches as they were before the first step wrote this step's rows
+        self.kv0, self.ix0 = step.kv_pages.cpu(), step.idx_pages.cpu()
         self.tables = StepTables(step.positions, step.slots, step.page_table, step.kv_pages, step.idx_pages, step.cos, step.sin)
         self.op = MlaLayerOp(cfg, self.w, dev, max_ctx=self.ctx, peer=self.peer,
                              guard=self.peer.guard if self.peer else None)
         self.ops = ops
-        g = torch.Generator().manual_seed(0)
-        self.h_host = torch.randn(self.rows, cfg.hidden, generator=g).bfloat16().pin_memory()
+        self.h_host = self.h_host.pin_memory()
         self.h = self.h_host.to(dev)
         self.h_in = torch.empty_like(self.h)
         self.out_host = torch.empty_like(self.h_host).pin_memory()
@@ -345,6 +391,7 @@ class LayerWorkload:
         rc, words = ops.guard_read(self.op.guard)
         if rc != 0:
             raise RuntimeError(f"guard words after the first step: {words}")
+        self.distinct = int(self.op.ffn.n_expert.item())
         self.launches_per_step = 23 + (1 if world > 1 else 0)
         # one CUDA graph of the step, as the reference times its layers (time_layers.py:38-77)
         self.graph = None
@@ -385,7 +432,7 @@ class LayerWorkload:
             raise RuntimeError(f"guard words after the timed steps: {words}")
 
     def layer_bytes(self):
-        c, u = self.cfg, int(self.op.ffn.n_expert.item())
+        c, u = self.cfg, self.distinct
         hl, il, h = c.heads_local, c.inter_local, c.hidden
         rep = (c.q_lora + 576) * h + c.index_heads * 128 * c.q_lora + 128 * h + c.index_heads * h * 2 + c.n_experts * h * 2
         shard = hl * 192 * c.q_lora + hl * 256 * 512 + h * hl * 128
@@ -395,7 +442,7 @@ class LayerWorkload:
         return rep + shard + experts + kv + idx, u
 
     def roofline_probe(self):
-        u = int(self.op.ffn.n_expert.item())
+        u = self.distinct
         c = self.cfg
         return (u + 1) * 2 * c.inter_local * c.hidden, lambda: self.op.ffn.up.launch(self.rows)
 
@@ -404,32 +451,30 @@ class LayerWorkload:
         nbytes, u = self.layer_bytes()
         return {"workload": self.name, "rows": self.rows, "context": self.ctx, "hidden": c.hidden, "heads": c.n_heads,
                 "experts": c.n_experts, "top_k": c.top_k, "inter": c.inter, "tp": c.tp, "distinct_experts": u,
-                "layer_algorithmic_bytes_per_rank": nbytes, "cuda_graph": self.graph is not None,
+                "layer_algorithmic_bytes_per_rank": nbytes, "cuda_graph": getattr(self, "graph", None) is not None,
                 "weights": "fp8_e4m3 128x128 block scales", "l2": "256 MiB buffer written between timed iterations"}
 
-    def cpu_sample(self):
+    def oracle_step(self):
+        """The CPU restatement of the whole layer over every row of the step (this rank's share)."""
         from oracle import layers as OL
 
-        class Lazy:  # experts are copied to the host only when the oracle routes to them
-            def __init__(self, v):
-                self.v, self.c = v, {}
+        w, t = host_weights(self.w), self.step_in
+        kv = getattr(self, "kv0", None)
+        kv = kv if kv is not None else t.kv_pages.cpu()
+        ix = getattr(self, "ix0", None)
+        ix = ix if ix is not None else t.idx_pages.cpu()
+        args = (self.cfg, [w], self.h_host.clone(), t.positions.cpu(), t.slots.cpu(), t.page_table.cpu(), t.cos.cpu(), t.sin.cpu())
 
-            def __getitem__(self, e):
-                if e not in self.c:
-                    self.c[e] = self.v[e].cpu()
-                return self.c[e]
+        def fn():
+            _, det = OL.layer_all_ranks(*args, kv.clone(), ix.clone())
+            if self.distinct is None:
+                self.distinct = int(det["ids"].unique().numel())
 
-        w = {k: (Lazy(v) if k in ("w13", "w13_s", "w2", "w2_s") else v.cpu()) for k, v in self.w.items()}
-        t = self.tables
-        h = self.h_host[:1]
-        args = (self.cfg, [w], h, t.positions[:1].cpu(), t.slots[:1].cpu(), t.page_table[:1].cpu(), t.cos.cpu(), t.sin.cpu())
-        kv, ix = t.kv_pages.cpu(), t.idx_pages.cpu()
-        ts = []
-        for _ in range(2):
-            t0 = time.perf_counter()
-            OL.layer_all_ranks(*args, kv.clone(), ix.clone())
-            ts.append(time.perf_counter() - t0)
-        return min(ts) * 1e6 * self.rows, f"1 of {self.rows} rows of this rank's layer share, scaled by rows; best of 2"
+        return fn, f"all {self.rows} rows of this rank's layer share"
+
+    def cpu_sample(self):
+        fn, what = self.oracle_step()
+        return time_oracle(fn, 1), what + "; one run after one warm-up"
 
 
 class GqaLayerWorkload(LayerWorkload):
@@ -444,16 +489,34 @@ class GqaLayerWorkload(LayerWorkload):
     def __init__(self, rows=16, ctx=65536):
         super().__init__(rows, ctx)
 
-    def setup(self, dev, rank, world):
-        from sgl_amd_mono_b200 import ops, synth
+    def make_inputs(self, dev, rank, tp, world=1):
+        from sgl_amd_mono_b200 import synth
         from sgl_amd_mono_b200.config import LayerConfig
-        from sgl_amd_mono_b200.gqa import CFG_GQA, GqaLayerOp
+        from sgl_amd_mono_b200.gqa import CFG_GQA
 
-        tp = getattr(self, "shard_of", 0) or (world if world > 1 else 4)
         self.gcfg = g = CFG_GQA.with_tp(tp)
         self.cfg = cfg = LayerConfig(name="cfg4_moe_mxfp4", hidden=g.hidden, n_experts=256, top_k=8, inter=1536, route_scale=1.0,
                                      expert_fmt="mxfp4", shared_fmt="none", router_dtype="bf16", eps=g.eps, tp=tp)
         self.name = f"cfg4_gqa_block_sparse_mxfp4_moe_layer_tp{tp}_{self.rows}rows_ctx{self.ctx}" + ("_one_shard" if tp != world else "")
+        self.w = {**synth.layer_weights(cfg, rank, dev), **synth.gqa_weights(g, rank, dev)}
+        self.tables = synth.gqa_step(g, self.rows, self.ctx, dev, ragged=False)
+        gen = torch.Generator().manual_seed(0)
+        self.h_host = torch.randn(self.rows, g.hidden, generator=gen).bfloat16()
+        self.distinct = None
+        # the rows' own pages, renumbered, as they are before the step inserts this step's rows
+        t = self.tables
+        self.row_caches = []
+        for r in range(self.rows):
+            pages = t.page_table[r].long()
+            self.row_caches.append([c[pages.to(c.device)].cpu() for c in (t.k_cache, t.v_cache, t.index_cache)])
+
+    def setup(self, dev, rank, world):
+        from sgl_amd_mono_b200 import ops
+        from sgl_amd_mono_b200.gqa import GqaLayerOp
+
+        tp = getattr(self, "shard_of", 0) or (world if world > 1 else 4)
+        self.make_inputs(dev, rank, tp, world)
+        g, cfg = self.gcfg, self.cfg
         self.peer = None
         if world > 1:
             import torch.distributed as dist
@@ -461,12 +524,9 @@ class GqaLayerWorkload(LayerWorkload):
 
             self.cpu_group = dist.new_group(backend="gloo")
             self.peer = PeerBuffer(g.hidden, rank, world, self.cpu_group, dev)
-        self.w = {**synth.layer_weights(cfg, rank, dev), **synth.gqa_weights(g, rank, dev)}
-        self.tables = synth.gqa_step(g, self.rows, self.ctx, dev, ragged=False)
         self.op = GqaLayerOp(g, cfg, self.w, dev, max_ctx=self.ctx, peer=self.peer)
         self.ops = ops
-        gen = torch.Generator().manual_seed(0)
-        self.h_host = torch.randn(self.rows, g.hidden, generator=gen).bfloat16().pin_memory()
+        self.h_host = self.h_host.pin_memory()
         self.h = self.h_host.to(dev)
         self.out_host = torch.empty_like(self.h_host).pin_memory()
         self._eager()
@@ -474,6 +534,7 @@ class GqaLayerWorkload(LayerWorkload):
         rc, words = ops.guard_read(self.op.guard)
         if rc != 0:
             raise RuntimeError(f"guard words after the first step: {words}")
+        self.distinct = int(self.op.ffn.n_expert.item())
         self.launches_per_step = 19 + (1 if world > 1 else 0)
         self.graph = None
         if os.environ.get("MONO_BENCH_GRAPH", "1") == "1":
@@ -491,7 +552,7 @@ class GqaLayerWorkload(LayerWorkload):
         self.out = self.op.launch(self.h, self.tables)
 
     def layer_bytes(self):
-        g, c, u = self.gcfg, self.cfg, int(self.op.ffn.n_expert.item())
+        g, c, u = self.gcfg, self.cfg, self.distinct
         h, il = g.hidden, c.inter_local
         attn_w = g.qkv_rows * h + h * g.q_local * 128 + c.n_experts * h * 2
         experts = u * (3 * il * h // 2 + 3 * il * h // 32)
@@ -500,7 +561,7 @@ class GqaLayerWorkload(LayerWorkload):
         return attn_w + experts + kv + idx, u
 
     def roofline_probe(self):
-        u = int(self.op.ffn.n_expert.item())
+        u = self.distinct
         c = self.cfg
         return u * (2 * c.inter_local * c.hidden // 2 + 2 * c.inter_local * c.hidden // 32), lambda: self.op.ffn.up.launch(self.rows)
 
@@ -510,39 +571,33 @@ class GqaLayerWorkload(LayerWorkload):
         return {"workload": self.name, "rows": self.rows, "context": self.ctx, "hidden": g.hidden, "q_heads": g.q_heads,
                 "kv_heads": g.kv_heads, "blocks_attended": 16, "block_tokens": 64, "experts": c.n_experts, "top_k": c.top_k,
                 "inter": c.inter, "tp": c.tp, "distinct_experts": u, "layer_algorithmic_bytes_per_rank": nbytes,
-                "cuda_graph": self.graph is not None, "weights": "fp8_e4m3 attention projections, mxfp4 experts",
+                "cuda_graph": getattr(self, "graph", None) is not None, "weights": "fp8_e4m3 attention projections, mxfp4 experts",
                 "l2": "256 MiB buffer written between timed iterations"}
 
-    def cpu_sample(self):
+    def oracle_step(self):
         from oracle import gqa as OG
         from oracle import layers as OL
 
-        class Lazy:
-            def __init__(self, v):
-                self.v, self.c = v, {}
+        w, t = host_weights(self.w), self.tables
+        pos, cos, sin = t.positions.cpu(), t.cos.cpu(), t.sin.cpu()
+        local = []
+        for r in range(self.rows):
+            pages = t.page_table[r].cpu().long()
+            slot = int(t.slots[r])
+            local.append((torch.arange(pages.numel(), dtype=torch.int32)[None],
+                          torch.tensor([int((pages == slot // 64).nonzero()[0]) * 64 + slot % 64])))
 
-            def __getitem__(self, e):
-                if e not in self.c:
-                    self.c[e] = self.v[e].cpu()
-                return self.c[e]
+        def fn():
+            mids = []
+            for r in range(self.rows):  # every row is its own request: its pages, renumbered from 0
+                lpt, lslot = local[r]
+                mids.append(OG.attention_half(self.gcfg, w, self.h_host[r : r + 1].clone(), pos[r : r + 1], lslot, lpt,
+                                              [c.clone() for c in self.row_caches[r]], cos, sin))
+            _, det = OL.ffn_block(self.cfg, [w], torch.cat(mids))
+            if self.distinct is None:
+                self.distinct = int(det["ids"].unique().numel())
 
-        w = {k: (Lazy(v) if k in ("w13", "w13_s", "w2", "w2_s") else (v.cpu() if isinstance(v, torch.Tensor) else v))
-             for k, v in self.w.items()}
-        t = self.tables
-        pt = t.page_table[:1].cpu()
-        pages = pt[0].long()
-        caches = [c[pages.to(c.device)].cpu() for c in (t.k_cache, t.v_cache, t.index_cache)]  # row 0's pages, renumbered
-        local_pt = torch.arange(pages.numel(), dtype=torch.int32)[None]
-        slot = int(t.slots[0])
-        local_slot = torch.tensor([int((pages == slot // 64).nonzero()[0]) * 64 + slot % 64])
-        ts = []
-        for _ in range(2):
-            t0 = time.perf_counter()
-            mid = OG.attention_half(self.gcfg, w, self.h_host[:1], t.positions[:1].cpu(), local_slot, local_pt,
-                                    [c.clone() for c in caches], t.cos.cpu(), t.sin.cpu())
-            OL.ffn_block(self.cfg, [w], mid)
-            ts.append(time.perf_counter() - t0)
-        return min(ts) * 1e6 * self.rows, f"1 of {self.rows} rows of this rank's layer share, scaled by rows; best of 2"
+        return fn, f"all {self.rows} rows of this rank's layer share"
 
 
 class AllReduceWorkload:
@@ -665,32 +720,27 @@ class StackWorkload:
         self.rows, self.ctx, self.n_layers, self.verify = rows, ctx, layers, verify
         self.layers_per_step = layers
 
-    def setup(self, dev, rank, world):
-        from sgl_amd_mono_b200 import ops, synth
+    def make_inputs(self, dev, rank, tp, world=1, layers=None):
+        """Synthetic weights, caches and tables of ``layers`` (default: all of them).  StepTables is a plain
+        dataclass of tensors: nothing of the kernel library is touched."""
+        from sgl_amd_mono_b200 import synth
         from sgl_amd_mono_b200.config import CFG_FLASH
         from sgl_amd_mono_b200.layer import StepTables
-        from sgl_amd_mono_b200.stack import DecoderStack
         from dataclasses import replace as dc_replace
 
-        tp = getattr(self, "shard_of", 0) or world
         self.n_layers = int(os.environ.get("MONO_BENCH_LAYERS", self.n_layers))
         self.layers_per_step = self.n_layers
         self.cfg = cfg = CFG_FLASH.with_tp(tp)
         self.total = self.rows + self.verify
         self.name = (f"cfg5_flash_stack_{self.n_layers}layers_tp{tp}_{self.rows}rows_plus_{self.verify}verify_ctx{self.ctx}"
                      + ("_one_shard" if tp != world else ""))
-        self.peer = None
-        if world > 1 and tp == world:
-            import torch.distributed as dist
-            from sgl_amd_mono_b200.common.peer import PeerBuffer
-
-            self.peer = PeerBuffer(cfg.hidden, rank, world, dist.new_group(backend="gloo"), dev)
-        ws = []
-        for i in range(self.n_layers):
+        ids = list(range(self.n_layers)) if layers is None else list(layers)
+        self.ws = []
+        for i in ids:
             c = cfg if i == self.n_layers - 1 else dc_replace(cfg, vocab=0)
-            ws.append(synth.layer_weights(c, rank, dev, layer=i))
-        draft_w = synth.layer_weights(dc_replace(cfg, vocab=0), rank, dev, layer=999)
-        self.w0 = ws[0]
+            self.ws.append(synth.layer_weights(c, rank, dev, layer=i))
+        self.w0 = self.ws[0]
+
         # rows decode requests + one request verified with `verify` tokens: every row has its own
         # page-table row (the verify rows repeat theirs); one cache per layer
         def tables(layer):
@@ -701,21 +751,41 @@ class StackWorkload:
             slots = pt.gather(1, (pos // 64).unsqueeze(1)).squeeze(1).long() * 64 + pos % 64
             return StepTables(pos, slots, pt, d.kv_pages, None, d.cos, d.sin)
 
-        self.tables = [tables(i) for i in range(self.n_layers)]
-        dt = tables(999)
+        self._tables_of = tables
+        self.tables = [tables(i) for i in ids]
+        self.kv0 = self.tables[0].kv_pages.cpu()  # layer 0's cache before the first step writes this step's rows
+        g = torch.Generator().manual_seed(0)
+        self.h_host = torch.randn(self.total, cfg.hidden, generator=g).bfloat16()
+
+    def setup(self, dev, rank, world):
+        from sgl_amd_mono_b200 import ops, synth
+        from sgl_amd_mono_b200.layer import StepTables
+        from sgl_amd_mono_b200.stack import DecoderStack
+        from dataclasses import replace as dc_replace
+
+        tp = getattr(self, "shard_of", 0) or world
+        self.make_inputs(dev, rank, tp, world)
+        cfg, ws = self.cfg, self.ws
+        self.peer = None
+        if world > 1 and tp == world:
+            import torch.distributed as dist
+            from sgl_amd_mono_b200.common.peer import PeerBuffer
+
+            self.peer = PeerBuffer(cfg.hidden, rank, world, dist.new_group(backend="gloo"), dev, logits_local=cfg.vocab // tp)
+        draft_w = synth.layer_weights(dc_replace(cfg, vocab=0), rank, dev, layer=999)
+        dt = self._tables_of(999)
         self.draft_tables = StepTables(dt.positions[self.rows:].contiguous(), dt.slots[self.rows:].contiguous(),
                                        dt.page_table[self.rows:].contiguous(), dt.kv_pages, None, dt.cos, dt.sin)
         self.stack = DecoderStack(cfg, ws, dev, max_ctx=self.ctx, peer=self.peer, draft_weights=draft_w)
         self.ops = ops
-        g = torch.Generator().manual_seed(0)
-        self.h_host = torch.randn(self.total, cfg.hidden, generator=g).bfloat16().pin_memory()
+        self.h_host = self.h_host.pin_memory()
         self.h = self.h_host.to(dev)
         self.hd = self.h[self.rows:].contiguous()
         self._eager()
         torch.cuda.synchronize()
         self.check()
         self.launches_per_step = self.stack.launches_per_step
-        self.logits_host = torch.empty(self.total, cfg.vocab // tp, dtype=torch.float32).pin_memory()
+        self.logits_host = torch.empty(self.total, self.logits.shape[-1], dtype=torch.float32).pin_memory()
         self.graph = None
         if os.environ.get("MONO_BENCH_GRAPH", "1") == "1":
             s = torch.cuda.Stream()
@@ -780,30 +850,25 @@ class StackWorkload:
         return {"workload": self.name, "decode_rows": self.rows, "verify_rows": self.verify, "draft_layers": 1,
                 "layers": self.n_layers, "context": self.ctx, "hidden": c.hidden, "heads": c.n_heads, "experts": c.n_experts,
                 "top_k": c.top_k, "inter": c.inter, "vocab": c.vocab, "tp": c.tp, "mean_distinct_experts": u,
-                "step_algorithmic_bytes_per_rank": nbytes, "cuda_graph": self.graph is not None,
+                "step_algorithmic_bytes_per_rank": nbytes, "cuda_graph": getattr(self, "graph", None) is not None,
                 "l2": "256 MiB buffer written between timed iterations"}
 
-    def cpu_sample(self):
+    def oracle_step(self):
         from oracle import layers as OL
 
-        class Lazy:
-            def __init__(self, v):
-                self.v, self.c = v, {}
-
-            def __getitem__(self, e):
-                if e not in self.c:
-                    self.c[e] = self.v[e].cpu()
-                return self.c[e]
-
-        w = {k: (Lazy(v) if k in ("w13", "w13_s", "w2", "w2_s") else v.cpu()) for k, v in self.w0.items()}
+        w = host_weights(self.w0)
         t = self.tables[0]
-        args = (self.cfg, [w], self.h_host[:1], t.positions[:1].cpu(), t.slots[:1].cpu(), t.page_table[:1].cpu(),
-                t.cos.cpu(), t.sin.cpu())
-        kv = t.kv_pages.cpu()
-        t0 = time.perf_counter()
-        OL.layer_all_ranks(*args, kv.clone(), None)
-        dt = time.perf_counter() - t0
-        return dt * 1e6 * self.total, f"layer 0, 1 of {self.total} rows, scaled by rows (per layer); one run"
+        args = (self.cfg, [w], self.h_host.clone(), t.positions.cpu(), t.slots.cpu(), t.page_table.cpu(), t.cos.cpu(), t.sin.cpu())
+        kv = self.kv0
+
+        def fn():
+            OL.layer_all_ranks(*args, kv.clone(), None)
+
+        return fn, f"layer 0 of {self.n_layers}, all {self.total} rows (per layer)"
+
+    def cpu_sample(self):
+        fn, what = self.oracle_step()
+        return time_oracle(fn, 1), what + "; one run after one warm-up"
 
 
 WORKLOADS = {"stack": StackWorkload, "sparse_mla": SparseMlaWorkload, "moe": MoeWorkload, "layer": LayerWorkload,
@@ -813,29 +878,38 @@ DEFAULT_WORKLOAD = "layer"
 
 # ------------------------------------------------------------------ main
 def run_reference(args, wl_cls, rank: int) -> None:
-    """The CPU restatement of the reference's arithmetic, timed on the host cores."""
+    """The CPU restatement of the reference's arithmetic on the host cores, every row of the step, one warm-up
+    and the median of max(5, steps capped at 7) runs (the reference's own kernels exist only for AMD gfx950).
+    Only synthetic inputs are generated (torch, on the GPU when there is one, because drawing 11 GB of expert
+    weights on the host takes minutes): no operator of the kernel library is built and the library is not loaded."""
     if rank != 0:
         return
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    wl = wl_cls()
-    dev = "cuda:0" if torch.cuda.is_available() else "cpu"
-    if dev == "cpu":
-        print(json.dumps({"impl": "reference", "unavailable": "needs the GPU box to generate the workload's inputs"}))
+    wl = wl_cls(rows=args.rows) if args.rows else wl_cls()
+    if not hasattr(wl, "oracle_step"):
+        print(json.dumps({"impl": "reference", "unavailable": f"the {args.workload} workload has no CPU counterpart"}))
         return
+    dev = "cuda:0" if torch.cuda.is_available() else "cpu"
     # rank 0's share of TP = N, built without peers (the other ranks of a torchrun launch do no work)
-    wl.shard_of = args.shard_of or (args.gpus if args.gpus > 1 else 0)
-    wl.setup(dev, 0, 1)
-    vals = []
-    for _ in range(max(1, min(args.steps, 3))):
-        v, sample = wl.cpu_sample()
-        vals.append(v)
-    v = statistics.median(vals)
+    tp = args.shard_of or (args.gpus if args.gpus > 1 else (4 if args.workload == "gqa_layer" else 1))
+    if args.workload == "stack":
+        wl.make_inputs(dev, 0, tp, 1, layers=[0])
+    else:
+        wl.make_inputs(dev, 0, tp, 1) if args.workload != "sparse_mla" else wl.make_inputs(dev, 0, tp)
+    fn, what = wl.oracle_step()
+    runs = max(5, min(args.steps, 7))
+    v = time_oracle(fn, runs)
+    sample = f"{what}; median of {runs} runs after one warm-up"
+    try:
+        cfg = wl.config()
+    except AttributeError:  # a workload whose byte count needs the built operators
+        cfg = {"workload": wl.name}
     line = {
         "impl": "reference", "metric": "us_per_decoder_layer", "value": v, "unit": "us", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": v / 1000.0, "higher_is_better": False,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32 over dequantised fp8/fp4", "data": "synthetic",
-        "config": wl.config(),
+        "config": cfg,
         "cpu_baseline": {"value": v, "unit": "us", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": v, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }

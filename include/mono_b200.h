@@ -215,11 +215,21 @@ typedef struct mono_gemv_args {
     int32_t* guard;
     int max_ctas; /* 0 = one per SM */
     int32_t* gen; /* chained launches: [0] generation (the last CTA to leave adds 1), [1] leave counter */
+    uint64_t wait_ns; /* limit of every device-side wait of the launch (barriers, ready stamps) in
+                         nanoseconds; 0 = 2 s.  A wait that runs out stores 101 in the deadline word
+                         of `guard`, the launch drains and returns (common/guard.py:4-7,69 ties the
+                         reference's deadline to the server's watchdog the same way). */
     mono_gemv_job job[MONO_GEMV_MAX_JOBS];
 } mono_gemv_args;
 int mono_gemv_launch(const mono_gemv_args* a, void* stream);
-/* FP8 jobs run on tcgen05 MMAs with TMEM accumulators (1, default) or on warp-level MMAs (0).
- * MXFP4 and bf16 weights always take the warp-level consumers.  Returns the old setting. */
+/* CTAs of this argument block's kernel that the device keeps resident at once (occupancy x SM
+ * count; minimax_m31/residency.py:66-85 asks the runtime the same question for the reference's
+ * FFN kernel).  A launch with chained jobs is refused when its grid exceeds this, because its CTAs
+ * wait on one another (minimax_m31/runner.py:125-143).  Negative = error. */
+int mono_gemv_max_resident_ctas(const mono_gemv_args* a);
+/* FP8 and MXFP4 jobs run on tcgen05 MMAs with TMEM accumulators (1, default) or on warp-level
+ * MMAs (0); an MXFP4 job needs tmap4 and MONO_ACT_MX8N activations for the tcgen05 consumer.
+ * bf16 weights always take the warp-level consumer.  Returns the old setting. */
 int mono_set_gemv_tcgen05(int on);
 
 /* ---- small matrices on CUDA cores (router logits: minimax_m31/ffn.py:601-649 fp32
@@ -358,6 +368,33 @@ size_t mono_reduce_peer_bytes(int rows, int n, int world);
 int mono_reduce_launch(const mono_reduce_args* a, void* stream);
 /* Adds 1 to the epoch word on the device (glm53/gfx950/runner.py:209-210 advance_step). */
 int mono_epoch_advance_launch(int32_t* guard, void* stream);
+
+/* ---- LM-head tail: K-split sum and logits all-gather (glm53_flash/gfx950/kernel.py:3700-3770 run_head's
+ * push and gather; slots by launch parity, glm53_flash/gfx950/layout.py:193-215) ------------------------
+ * logits = sum over nsum slices (in order) of f32 [16][ld], this rank's n_local columns.  world == 1: the
+ * f32 sums go to out[row][0..n_local).  world > 1: each pair of columns is rounded to bf16 and pushed as a
+ * (bf16 pair, tag) word into every rank's logits region at [parity][row][rank * n_local / 2 + pair]; the
+ * launch then waits (deadline, sticky words and peer flags as in mono_reduce_launch) for every other
+ * rank's words in its own region and writes f32 out[row][src * n_local + col] for all ranks: every rank
+ * ends with the same bf16-rounded logits of the whole vocabulary, widened to f32. */
+typedef struct mono_logits_gather_args {
+    int rows, n_local;
+    const float* partial;
+    int nsum, ld;
+    long sum_stride;
+    float* out; /* f32 [rows][out_ld], out_ld >= world * n_local */
+    int out_ld;
+    int world, rank;
+    const uint64_t* peer_ptrs; /* device array [world]: base of every rank's logits region */
+    uint32_t tag;              /* 0 = epoch * 256 + site + 1 and parity = epoch & 1 from guard word 0 */
+    int parity;
+    uint64_t deadline_ns;
+    int site;
+    int32_t* guard;
+    const uint64_t* peer_guards;
+} mono_logits_gather_args;
+size_t mono_logits_peer_bytes(int n_local, int world);
+int mono_logits_gather_launch(const mono_logits_gather_args* a, void* stream);
 
 /* ---- attention front, after q_a|kv_a (glm53/gfx950/kernel.py:1978-2003 q_a RMSNorm,
  * :2005-2101 KV RMSNorm + k_pe RoPE + cache write, :2103-2181 index key) -----------
@@ -528,7 +565,7 @@ int mono_gqa_select_launch(const mono_gqa_args* a, void* stream);
 int mono_gqa_attn_launch(const mono_gqa_args* a, void* stream);
 
 /* sizeof() of the argument structs, by index (0 gemv_job, 1 gemv_args, 2 act_prep,
- * 3 route, 4 mid, 5 sparse_mla, 6 reduce, 7 rowdot, ..., 11 gqa): lets a binding check its mirror. */
+ * 3 route, 4 mid, 5 sparse_mla, 6 reduce, 7 rowdot, ..., 11 gqa, 12 logits_gather): lets a binding check its mirror. */
 size_t mono_struct_size(int which);
 
 #ifdef __cplusplus

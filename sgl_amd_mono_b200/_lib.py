@@ -51,7 +51,7 @@ class GemvJob(C.Structure):
 class GemvArgs(C.Structure):
     _fields_ = [
         ("njobs", i32), ("rows", i32), ("wkind", i32), ("guard", vp), ("max_ctas", i32), ("gen", vp),
-        ("_pad", C.c_ubyte * 24),  # the job array is 64-byte aligned in C
+        ("wait_ns", u64), ("_pad", C.c_ubyte * 16),  # the job array is 64-byte aligned in C
         ("job", GemvJob * GEMV_MAX_JOBS),
     ]
 
@@ -147,8 +147,16 @@ class GqaArgs(C.Structure):
     ]
 
 
+class LogitsGatherArgs(C.Structure):
+    _fields_ = [
+        ("rows", i32), ("n_local", i32), ("partial", vp), ("nsum", i32), ("ld", i32), ("sum_stride", i64),
+        ("out", vp), ("out_ld", i32), ("world", i32), ("rank", i32), ("peer_ptrs", vp), ("tag", u32), ("parity", i32),
+        ("deadline_ns", u64), ("site", i32), ("guard", vp), ("peer_guards", vp),
+    ]
+
+
 _STRUCTS = [GemvJob, GemvArgs, ActPrepArgs, RouteArgs, MidArgs, SparseMlaArgs, ReduceArgs, RowdotArgs,
-            MlaMidArgs, QPostArgs, IndexArgs, GqaArgs]
+            MlaMidArgs, QPostArgs, IndexArgs, GqaArgs, LogitsGatherArgs]
 
 # every symbol include/mono_b200.h declares: name -> (restype, argtypes)
 SYMBOLS = {
@@ -163,6 +171,7 @@ SYMBOLS = {
     "mono_set_gemv_tcgen05": (i32, [i32]),
     "mono_act_prep_launch": (i32, [C.POINTER(ActPrepArgs), vp]),
     "mono_gemv_launch": (i32, [C.POINTER(GemvArgs), vp]),
+    "mono_gemv_max_resident_ctas": (i32, [C.POINTER(GemvArgs)]),
     "mono_rowdot_launch": (i32, [C.POINTER(RowdotArgs), vp]),
     "mono_route_launch": (i32, [C.POINTER(RouteArgs), vp]),
     "mono_router_launch": (i32, [C.POINTER(RowdotArgs), C.POINTER(RouteArgs), vp, vp]),
@@ -175,6 +184,8 @@ SYMBOLS = {
     "mono_reduce_peer_bytes": (C.c_size_t, [i32, i32, i32]),
     "mono_reduce_launch": (i32, [C.POINTER(ReduceArgs), vp]),
     "mono_epoch_advance_launch": (i32, [vp, vp]),
+    "mono_logits_peer_bytes": (C.c_size_t, [i32, i32]),
+    "mono_logits_gather_launch": (i32, [C.POINTER(LogitsGatherArgs), vp]),
     "mono_mla_mid_launch": (i32, [C.POINTER(MlaMidArgs), vp]),
     "mono_q_post_launch": (i32, [C.POINTER(QPostArgs), vp]),
     "mono_index_score_launch": (i32, [C.POINTER(IndexArgs), vp]),

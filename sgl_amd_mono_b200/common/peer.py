@@ -73,13 +73,17 @@ def region_bytes(n: int, world: int, rows: int = 16) -> int:
 class PeerBuffer:
     """Collective constructor: every rank of ``group`` must call it with the same sizes."""
 
-    def __init__(self, n: int, rank: int, world: int, group, device, backend=None):
+    def __init__(self, n: int, rank: int, world: int, group, device, backend=None, logits_local: int = 0):
+        """``logits_local``: this rank's share of the vocabulary when the buffer also carries the LM-head
+        tail's logits all-gather (two parity slots of ``[16 rows][vocab / 2]`` words after the two
+        all-reduce regions; ``glm53_flash/gfx950/layout.py:193-215``)."""
         import torch.distributed as dist
 
         self.rank, self.world, self.n, self.device = rank, world, n, device
         self.backend = backend if backend is not None else CudaIpcBackend()
         self.region = region_bytes(n, world)
-        self.nbytes = GUARD_BYTES + N_REGIONS * self.region
+        self.logits_bytes = 2 * 16 * (world * logits_local // 2) * 8
+        self.nbytes = GUARD_BYTES + N_REGIONS * self.region + self.logits_bytes
         self.local = 0
         self.opened: list[int] = []
         ok, handle, why = 1, b"", ""
@@ -116,6 +120,9 @@ class PeerBuffer:
         self.guard_table = self.backend.table(self.ptrs, device)
         self._regions = [self.backend.table([p + GUARD_BYTES + i * self.region for p in self.ptrs], device)
                          for i in range(N_REGIONS)]
+        self.logits_table = None
+        if self.logits_bytes:
+            self.logits_table = self.backend.table([p + GUARD_BYTES + N_REGIONS * self.region for p in self.ptrs], device)
 
     def region_table(self, site: int):
         return self._regions[site % N_REGIONS]

@@ -217,6 +217,7 @@ extern "C" size_t mono_struct_size(int which) {
         case 9: return sizeof(mono_q_post_args);
         case 10: return sizeof(mono_index_args);
         case 11: return sizeof(mono_gqa_args);
+        case 12: return sizeof(mono_logits_gather_args);
         default: return 0;
     }
 }

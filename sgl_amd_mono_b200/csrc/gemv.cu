@@ -165,6 +165,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const __grid_cons
     }
 
     volatile int* abortp = &abort_flag;
+    const uint64_t wait_ns = p.a.wait_ns ? p.a.wait_ns : kWaitLimitNs;
 
     if (warp == kConsumerWarps) {
         // ------------------------------------------------------------ producer
@@ -191,7 +192,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const __grid_cons
                 Seg s = make_seg<WK>(jb, rb, ks, u, nexp[j], p.bb);
                 // activation planes + scales of this segment
                 int ok = 1;
-                if (lane == 0) ok = mbar_wait(&bempty[bslot], bphase ^ 1, abortp) ? 1 : 0;
+                if (lane == 0) ok = mbar_wait(&bempty[bslot], bphase ^ 1, abortp, wait_ns) ? 1 : 0;
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
                 uint8_t* slot = b_ring + (size_t)bslot * p.bslot_bytes;
@@ -224,7 +225,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const __grid_cons
                             if (++astage == p.a_stages) { astage = 0; aphase ^= 1; }
                             continue;
                         }
-                        if (!mbar_wait(&empty[astage], aphase ^ 1, abortp)) break;
+                        if (!mbar_wait(&empty[astage], aphase ^ 1, abortp, wait_ns)) break;
                         mbar_expect_tx(&full[astage], kTileBytes);
                         tma_load_3d(a_ring + (size_t)astage * kTileBytes, reinterpret_cast<const CUtensorMap*>(&jb.tmap),
                                     (s.t0 + t) * 128, s.row0, s.c2, &full[astage]);
@@ -283,7 +284,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const __grid_cons
                     ws8_g = reinterpret_cast<const uint8_t*>(s.wsc) + (size_t)(r0 - (s.row0 - jb.row_off)) * jb.wscale_ld;
                     ws8_g8 = reinterpret_cast<const uint8_t*>(s.wsc) + (size_t)(r1 - (s.row0 - jb.row_off)) * jb.wscale_ld;
                 }
-                if (!mbar_wait(&bfull[bslot], bphase, abortp)) { dead = true; break; }
+                if (!mbar_wait(&bfull[bslot], bphase, abortp, wait_ns)) { dead = true; break; }
                 const uint32_t slot = smem_u32(b_ring + (size_t)bslot * p.bslot_bytes);
                 const uint32_t sc_base = slot + p.scale_off;
 
@@ -293,7 +294,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const __grid_cons
                     wsn_g8 = __ldg(reinterpret_cast<const uint2*>(ws8_g8));
                 }
                 for (int t = 0; t < s.nt; ++t) {
-                    if (!mbar_wait(&full[astage], aphase, abortp)) { dead = true; break; }
+                    if (!mbar_wait(&full[astage], aphase, abortp, wait_ns)) { dead = true; break; }
                     const uint32_t a_base = smem_u32(a_ring + (size_t)astage * kTileBytes) + (warp * 16 + g) * 128;
                     if (WK == MONO_W_FP8 || WK == MONO_W_BF16) {
                         uint4 x0 = lds128(a_base + (((2 * t4) ^ g) << 4));
@@ -441,11 +442,11 @@ namespace {
 template <int WK, int NT>
 int launch_gemv(const mono::GemvParams& p, int grid, size_t smem, cudaStream_t st) {
     auto k = mono::gemv_kernel<WK, NT>;
-    static thread_local bool attr_set = false;  // once per instantiation, outside any graph capture
-    if (!attr_set) {
+    static std::atomic<uint64_t> attr_once{0};  // bit d: set on device d
+    if (mono::attr_needed(attr_once)) {
         cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);  // 227 KB less the static part
         if (e != cudaSuccess) return (int)e;
-        attr_set = true;
+        mono::attr_done(attr_once);
     }
     cudaError_t e = mono::launch_k(k, grid, mono::kGemvThreads, smem, st, p);
     return (int)(e != cudaSuccess ? e : cudaGetLastError());

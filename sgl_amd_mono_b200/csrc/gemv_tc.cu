@@ -14,6 +14,8 @@
 // TMEM lanes (one weight row per thread), read a finished accumulator with tcgen05.ld, scale and add.
 #include "mono_common.cuh"
 #include <cstdlib>
+#include <mutex>
+#include <vector>
 
 extern void mono_set_error(const char* fmt, ...);
 
@@ -179,7 +181,7 @@ __device__ __forceinline__ void st_release(int* p, int v) {
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
 // Bounded wait for a generation stamp written by another CTA of this launch.
-__device__ __forceinline__ bool wait_stamp(const int* flag, int stamp, volatile int* abort_flag) {
+__device__ __forceinline__ bool wait_stamp(const int* flag, int stamp, volatile int* abort_flag, uint64_t limit_ns) {
 #pragma unroll 1
     for (int i = 0; i < 16; ++i) {  // the global timer is slow to read: only once the wait is clearly long
         if (ld_acquire(flag) == stamp) return true;
@@ -191,7 +193,7 @@ __device__ __forceinline__ bool wait_stamp(const int* flag, int stamp, volatile 
         __nanosleep(64);
         if ((i & 15) == 15) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > kWaitLimitNs) break;
+            if (globaltimer_ns() - t0 > limit_ns) break;
         }
     }
     *abort_flag = 1;
@@ -204,9 +206,10 @@ struct BoundedSync {
     uint64_t* bar;
     uint32_t phase;
     volatile int* abortp;
+    uint64_t limit_ns;
     __device__ __forceinline__ bool sync() {
         mbar_arrive(bar);
-        const bool ok = mbar_wait(bar, phase, abortp);
+        const bool ok = mbar_wait(bar, phase, abortp, limit_ns);
         phase ^= 1;
         return ok;
     }
@@ -421,6 +424,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
             for (int i = tid; i < min(nexp[j], kTcListCache); i += kTcThreads) s_elist[j][i] = p.a.job[j].expert_list[i];
     __syncthreads();
     volatile int* abortp = &abort_flag;
+    const uint64_t wait_ns = p.a.wait_ns ? p.a.wait_ns : kWaitLimitNs;
 
 // every role walks the same (task, segment, tile) sequence
 #define TC_FOR_EACH_SEGMENT(...)                                                                                \
@@ -473,14 +477,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
                 }
                 if (sgi >= 32 || !((ready_mask >> sgi) & 1u)) {
                     if (lane == 0) {
-                        ok = wait_stamp(jb.ready + (down ? u : 0), stamp, abortp) ? 1 : 0;
+                        ok = wait_stamp(jb.ready + (down ? u : 0), stamp, abortp, wait_ns) ? 1 : 0;
                     }
                     ok = __shfl_sync(0xffffffffu, ok, 0);
                     if (!ok) break;
                 }
                 // (the writer ordered its stores against the async proxy before it released the stamp)
             }
-            if (lane == 0) ok = mbar_wait(&sc_empty[slot], sphase ^ 1, abortp) ? 1 : 0;
+            if (lane == 0) ok = mbar_wait(&sc_empty[slot], sphase ^ 1, abortp, wait_ns) ? 1 : 0;
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             float* sl = sc_ring + (size_t)slot * kTcScRows * kTcMaxSegTiles;
@@ -497,7 +501,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
                 const CUtensorMap* amap = reinterpret_cast<const CUtensorMap*>(&jb.act_tmap);
                 for (int t = 0; t < s.nt; t += kTcUnit) {
                     const int n2 = min(kTcUnit, s.nt - t);
-                    if (!mbar_wait(&acc_full[stage], phase ^ 1, abortp)) break;  // the MMAs of the stage's last unit are done
+                    if (!mbar_wait(&acc_full[stage], phase ^ 1, abortp, wait_ns)) break;  // the MMAs of the stage's last unit are done
                     uint8_t* st = ring + (size_t)stage * stage_bytes;
                     mbar_expect_tx(&full[stage], n2 * (kTcABytes + planes * kTcBBytes));
                     for (int i = 0; i < n2; ++i) {
@@ -524,8 +528,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
             TC_FOR_EACH_SEGMENT({
                 for (int t = 0; t < s.nt; t += kTcUnit) {
                     const int n2 = min(kTcUnit, s.nt - t);
-                    if (!mbar_wait(&full[stage], phase, abortp)) break;
-                    if (!mbar_wait(&acc_empty[stage], phase ^ 1, abortp)) break;
+                    if (!mbar_wait(&full[stage], phase, abortp, wait_ns)) break;
+                    if (!mbar_wait(&acc_empty[stage], phase ^ 1, abortp, wait_ns)) break;
                     tc_fence_after();
                     const uint32_t sa = smem_u32(ring + (size_t)stage * stage_bytes);
                     for (int i = 0; i < n2; ++i) {
@@ -562,7 +566,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
         int stage = 0;
         uint32_t phase = 0;
         bool have_next = false;
-        BoundedSync es{epi_bar, 0u, abortp};
+        BoundedSync es{epi_bar, 0u, abortp, wait_ns};
         float total_acc[kMaxRows];
 #define TASK_BEGIN \
         _Pragma("unroll") for (int c = 0; c < kMaxRows; ++c) total_acc[c] = 0.f;
@@ -578,12 +582,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
             if (jb.stage_planes) tc_stage_out(jb, rows, rb, row_in_tile, q, lane, row_in_mat < jb.n_rows, total_acc, s_amax, es); \
             if (jb.feeds_job > 0) {                                                                           \
                 const uint32_t k = nfeed & 1;                                                                 \
-                if (mbar_wait(&mail_free[k], ((nfeed >> 1) & 1) ^ 1, abortp)) mbar_arrive(&mail_full[k]);     \
+                if (mbar_wait(&mail_free[k], ((nfeed >> 1) & 1) ^ 1, abortp, wait_ns)) mbar_arrive(&mail_full[k]);     \
                 ++nfeed;                                                                                      \
             }                                                                                                 \
         }
         TC_FOR_EACH_SEGMENT({
-            if (!mbar_wait(&sc_full[slot], sphase, abortp)) break;
+            if (!mbar_wait(&sc_full[slot], sphase, abortp, wait_ns)) break;
             const float* sl = sc_ring + (size_t)slot * kTcScRows * kTcMaxSegTiles;
             float seg_acc[kMaxRows];
 #pragma unroll
@@ -591,7 +595,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
             for (int t = 0; t < s.nt; t += kTcUnit) {
                 const int n2 = min(kTcUnit, s.nt - t);
                 if (!have_next) {
-                    if (!mbar_wait(&acc_full[stage], phase, abortp)) break;
+                    if (!mbar_wait(&acc_full[stage], phase, abortp, wait_ns)) break;
                     tc_fence_after();
                     tc_ld_issue<kTcUnit>(tmem_lane + stage * (16 * kTcUnit), dn);
                 }
@@ -636,14 +640,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
     }
     if (warp >= 6) {
         const int ft = tid - 192;
-        BoundedSync fs{fin_bar, 0u, abortp};
+        BoundedSync fs{fin_bar, 0u, abortp, wait_ns};
         // ------------------------------------------------------------ finisher: counts finished up/gate tasks
         uint32_t nfeed = 0;
 #define TASK_BEGIN
 #define TASK_END                                                                                              \
         if (jb.feeds_job > 0 && !*abortp) {                                                                   \
             const uint32_t k = nfeed & 1;                                                                     \
-            if (mbar_wait(&mail_full[k], (nfeed >> 1) & 1, abortp)) {                                         \
+            if (mbar_wait(&mail_full[k], (nfeed >> 1) & 1, abortp, wait_ns)) {                                         \
                 tc_finish_up(p, jb, jb.mode == MONO_JOB_EXPERT_UP ? u_up : 0, nrb * jb.nsplit, stamp, ft, &s_last[k], fs); \
                 if (ft == 0) mbar_arrive(&mail_free[k]);                                                    \
             }                                                                                                 \
@@ -669,6 +673,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
         __threadfence();
         if (atomicAdd(p.a.gen + 1, 1) == (int)gridDim.x - 1) {
             p.a.gen[1] = 0;
+            if (guard_failed(p.a.guard)) {
+                // a launch that gave up leaves partial task counts behind: every other CTA has left, so
+                // the counters can go back to zero for the launch after the host clears the guard
+                for (int j = 0; j < p.a.njobs; ++j) {
+                    const mono_gemv_job& jb = p.a.job[j];
+                    if (jb.feeds_job > 0 && jb.done)
+                        for (int i = 0; i < (jb.mode == MONO_JOB_EXPERT_UP ? jb.max_expert : 1); ++i) jb.done[i] = 0;
+                }
+            }
             __threadfence();
             atomicAdd(p.a.gen, 1);
         }
@@ -685,37 +698,10 @@ extern "C" int mono_set_gemv_tcgen05(int on) {
 }
 int mono_gemv_tc_enabled() { return g_mono_gemv_tc; }
 
-// Launches the tcgen05 kernel for an FP8 argument block that mono_gemv_launch has validated.
-int mono_gemv_tc_launch(const mono_gemv_args* a, long tasks, cudaStream_t st) {
+// Picks the pipeline unit and the shared-memory size of a validated FP8 argument block.
+static int tc_plan(const mono_gemv_args* a, mono::TcParams* pp, int* unit_out, size_t* smem_out) {
     using namespace mono;
-    for (int j = 0; j < a->njobs; ++j) {
-        const mono_gemv_job& jb = a->job[j];
-        const int seg = jb.mode == MONO_JOB_EXPERT_DOWN ? jb.k_tiles : (jb.split_tiles < jb.k_tiles ? jb.split_tiles : jb.k_tiles);
-        if (seg > kTcMaxSegTiles) {
-            mono_set_error("mono_gemv_launch: job %d: a segment may span at most %d tiles", j, kTcMaxSegTiles);
-            return MONO_E_ARG;
-        }
-        if (jb.stage_planes) {
-            if (jb.mode != MONO_JOB_DENSE || jb.nsplit != 1 || jb.feeds_job > 0 || !jb.stage_scale || jb.stage_ld < 128 || jb.stage_scale_ld < 1 ||
-                (jb.stage_fmt != MONO_ACT_A8 && jb.stage_fmt != MONO_ACT_HILO) || (jb.stage_fmt == MONO_ACT_HILO && jb.stage_plane_stride <= 0)) {
-                mono_set_error("mono_gemv_launch: job %d: only a dense job without K splits can stage its output "
-                               "(stage_planes, stage_scale, their leading dimensions and stage_fmt A8 or HILO required)", j);
-                return MONO_E_ARG;
-            }
-        }
-        if (jb.feeds_job > 0) {
-            const int f = jb.feeds_job - 1;
-            const bool shape_ok = jb.mode != MONO_JOB_EXPERT_DOWN && jb.rb_per_mat == 0 && (jb.n_rows & 255) == 0;
-            if (!a->gen || !jb.done || !jb.ready || f <= j || f >= a->njobs || !shape_ok || a->job[f].ready != jb.ready ||
-                a->job[f].planes != 1 || a->job[f].k_tiles * 128 != jb.n_rows / 2 ||
-                (jb.mode == MONO_JOB_EXPERT_UP) != (a->job[f].mode == MONO_JOB_EXPERT_DOWN)) {
-                mono_set_error("mono_gemv_launch: job %d: a chained up/gate job needs gen, done, ready, 2 * inter rows with "
-                               "inter a multiple of 128, and a later job of matching kind with one E4M3 plane of inter bytes", j);
-                return MONO_E_ARG;
-            }
-        }
-    }
-    TcParams p;
+    TcParams& p = *pp;
     p.a = *a;
     int planes = 1;
     for (int j = 0; j < a->njobs; ++j) planes = a->job[j].planes > planes ? a->job[j].planes : planes;
@@ -748,19 +734,112 @@ int mono_gemv_tc_launch(const mono_gemv_args* a, long tasks, cudaStream_t st) {
     if (p.stages < tc_stages(unit)) return MONO_E_ARG;
     p.stages = tc_stages(unit);  // stage s feeds accumulator set s
     const size_t smem = fixed + (size_t)p.stages * p.stage_bytes;
-    static thread_local bool attr_set = false;
-    if (!attr_set) {
+    static std::atomic<uint64_t> attr_once{0};  // bit d: set on device d
+    if (mono::attr_needed(attr_once)) {
         cudaError_t e = cudaFuncSetAttribute(gemv_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
         if (e != cudaSuccess) return (int)e;
-        attr_set = true;
+        mono::attr_done(attr_once);
     }
+    *unit_out = unit;
+    *smem_out = smem;
+    return 0;
+}
+
+// CTAs of this launch's kernel that the device keeps resident at once (occupancy x SM count).
+static int tc_resident(int unit, size_t smem) {
+    using namespace mono;
+    // the answer depends on (device, unit, shared memory): asked once each, outside any hot path
+    struct Entry { int dev, unit; size_t smem; int resident; };
+    static std::mutex mu;
+    static std::vector<Entry> cache;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        for (const Entry& en : cache)
+            if (en.dev == dev && en.unit == unit && en.smem == smem) return en.resident;
+    }
+    int per_sm = 0;
+    cudaError_t e = unit == 4   ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemv_tc_kernel<4>, kTcThreads, smem)
+                    : unit == 2 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemv_tc_kernel<2>, kTcThreads, smem)
+                                : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemv_tc_kernel<1>, kTcThreads, smem);
+    if (e != cudaSuccess) return -1;
+    const int sms = mono_sm_count();
+    const int resident = sms > 0 ? per_sm * sms : -1;
+    if (resident > 0) {
+        std::lock_guard<std::mutex> lk(mu);
+        cache.push_back({dev, unit, smem, resident});
+    }
+    return resident;
+}
+
+// Launches the tcgen05 kernel for an FP8 argument block that mono_gemv_launch has validated.
+int mono_gemv_tc_launch(const mono_gemv_args* a, long tasks, cudaStream_t st) {
+    using namespace mono;
+    for (int j = 0; j < a->njobs; ++j) {
+        const mono_gemv_job& jb = a->job[j];
+        const int seg = jb.mode == MONO_JOB_EXPERT_DOWN ? jb.k_tiles : (jb.split_tiles < jb.k_tiles ? jb.split_tiles : jb.k_tiles);
+        if (seg > kTcMaxSegTiles) {
+            mono_set_error("mono_gemv_launch: job %d: a segment may span at most %d tiles", j, kTcMaxSegTiles);
+            return MONO_E_ARG;
+        }
+        if (jb.stage_planes) {
+            if (jb.mode != MONO_JOB_DENSE || jb.nsplit != 1 || jb.feeds_job > 0 || !jb.stage_scale || jb.stage_ld < 128 || jb.stage_scale_ld < 1 ||
+                (jb.stage_fmt != MONO_ACT_A8 && jb.stage_fmt != MONO_ACT_HILO) || (jb.stage_fmt == MONO_ACT_HILO && jb.stage_plane_stride <= 0)) {
+                mono_set_error("mono_gemv_launch: job %d: only a dense job without K splits can stage its output "
+                               "(stage_planes, stage_scale, their leading dimensions and stage_fmt A8 or HILO required)", j);
+                return MONO_E_ARG;
+            }
+        }
+        if (jb.feeds_job > 0) {
+            const int f = jb.feeds_job - 1;
+            const bool shape_ok = jb.mode != MONO_JOB_EXPERT_DOWN && jb.rb_per_mat == 0 && (jb.n_rows & 255) == 0;
+            if (!a->gen || !jb.done || !jb.ready || f <= j || f >= a->njobs || !shape_ok || a->job[f].ready != jb.ready ||
+                a->job[f].planes != 1 || a->job[f].k_tiles * 128 != jb.n_rows / 2 ||
+                (jb.mode == MONO_JOB_EXPERT_UP) != (a->job[f].mode == MONO_JOB_EXPERT_DOWN)) {
+                mono_set_error("mono_gemv_launch: job %d: a chained up/gate job needs gen, done, ready, 2 * inter rows with "
+                               "inter a multiple of 128, and a later job of matching kind with one E4M3 plane of inter bytes", j);
+                return MONO_E_ARG;
+            }
+        }
+    }
+    TcParams p;
+    int unit = 1;
+    size_t smem = 0;
+    if (int rc = tc_plan(a, &p, &unit, &smem)) return rc;
     int grid = a->max_ctas > 0 ? a->max_ctas : mono_sm_count();
     if (grid > tasks) grid = (int)tasks;
     if (grid < 1) grid = 1;
+    bool chained = false;
+    for (int j = 0; j < a->njobs; ++j) chained = chained || a->job[j].feeds_job > 0;
+    if (chained) {
+        // CTAs of a chained launch wait on stamps that other CTAs of the same launch write: every CTA
+        // has to be resident (minimax_m31/runner.py:125-143 refuses a grid above the co-resident count)
+        const int resident = tc_resident(unit, smem);
+        if (resident < 1 || grid > resident) {
+            mono_set_error("mono_gemv_launch: a chained launch of %d CTAs exceeds the %d the device keeps resident", grid, resident);
+            return MONO_E_ARG;
+        }
+    }
     cudaError_t e = unit == 4   ? launch_k(gemv_tc_kernel<4>, grid, kTcThreads, smem, st, p)
                     : unit == 2 ? launch_k(gemv_tc_kernel<2>, grid, kTcThreads, smem, st, p)
                                 : launch_k(gemv_tc_kernel<1>, grid, kTcThreads, smem, st, p);
     return (int)(e != cudaSuccess ? e : cudaGetLastError());
+}
+
+// CTAs the device keeps resident for this argument block's kernel (the tcgen05 FP8 kernel; other
+// weight kinds run one CTA per SM).  A chained launch needs its whole grid resident.
+extern "C" int mono_gemv_max_resident_ctas(const mono_gemv_args* a) {
+    if (!a || a->njobs < 1 || a->njobs > MONO_GEMV_MAX_JOBS) {
+        mono_set_error("mono_gemv_max_resident_ctas: njobs in 1..%d required", MONO_GEMV_MAX_JOBS);
+        return MONO_E_ARG;
+    }
+    if (a->wkind != MONO_W_FP8 || !g_mono_gemv_tc) return mono_sm_count();
+    mono::TcParams p;
+    int unit = 1;
+    size_t smem = 0;
+    if (int rc = tc_plan(a, &p, &unit, &smem)) return rc > 0 ? -rc : rc;
+    return tc_resident(unit, smem);
 }

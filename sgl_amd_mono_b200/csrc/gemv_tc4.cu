@@ -183,6 +183,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc4_kernel(const __grid_cons
             for (int i = tid; i < min(nexp[j], 128); i += kThreads) s_elist[j][i] = p.a.job[j].expert_list[i];
     __syncthreads();
     volatile int* abortp = &abort_flag;
+    const uint64_t wait_ns = p.a.wait_ns ? p.a.wait_ns : kWaitLimitNs;
 
 #define T4_FOR_EACH_SEGMENT(...)                                                                                \
     for (int task = blockIdx.x; task < total && !*abortp; task += gridDim.x) {                                  \
@@ -212,7 +213,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc4_kernel(const __grid_cons
 #define TASK_END
         T4_FOR_EACH_SEGMENT({
             int ok = 1;
-            if (lane == 0) ok = mbar_wait(&sc_empty[slot], sphase ^ 1, abortp) ? 1 : 0;
+            if (lane == 0) ok = mbar_wait(&sc_empty[slot], sphase ^ 1, abortp, wait_ns) ? 1 : 0;
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             uint32_t* sl = sc_ring + (size_t)slot * kSlotWords;
@@ -234,7 +235,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc4_kernel(const __grid_cons
                 const CUtensorMap* amap = reinterpret_cast<const CUtensorMap*>(&jb.act_tmap);
                 for (int t = 0; t < s.nt; t += kUnit) {
                     const int n2 = min(kUnit, s.nt - t);
-                    if (!mbar_wait(&acc_full[stage], phase ^ 1, abortp)) break;  // the MMAs of the stage's last unit are done
+                    if (!mbar_wait(&acc_full[stage], phase ^ 1, abortp, wait_ns)) break;  // the MMAs of the stage's last unit are done
                     uint8_t* st = ring + (size_t)stage * kStageBytes;
                     mbar_expect_tx(&full[stage], n2 * kTxBytes);
                     for (int i = 0; i < n2; ++i) {
@@ -259,8 +260,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc4_kernel(const __grid_cons
             T4_FOR_EACH_SEGMENT({
                 for (int t = 0; t < s.nt; t += kUnit) {
                     const int n2 = min(kUnit, s.nt - t);
-                    if (!mbar_wait(&full[stage], phase, abortp)) break;
-                    if (!mbar_wait(&acc_empty[stage], phase ^ 1, abortp)) break;
+                    if (!mbar_wait(&full[stage], phase, abortp, wait_ns)) break;
+                    if (!mbar_wait(&acc_empty[stage], phase ^ 1, abortp, wait_ns)) break;
                     fence_after();
                     const uint32_t sa = smem_u32(ring + (size_t)stage * kStageBytes);
                     for (int i = 0; i < n2; ++i) {
@@ -296,7 +297,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc4_kernel(const __grid_cons
             }                                                                                                 \
         }
         T4_FOR_EACH_SEGMENT({
-            if (!mbar_wait(&sc_full[slot], sphase, abortp)) break;
+            if (!mbar_wait(&sc_full[slot], sphase, abortp, wait_ns)) break;
             const uint32_t* sl = sc_ring + (size_t)slot * kSlotWords;
             // the segment's activation scales as floats, one private copy per warp (no cross-warp barrier):
             // asf[tile][row][group] = 2^(code - 127)
@@ -317,7 +318,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc4_kernel(const __grid_cons
             for (int c = 0; c < kMaxRows; ++c) seg_acc[c] = 0.f;
             for (int t = 0; t < s.nt; t += kUnit) {
                 const int n2 = min(kUnit, s.nt - t);
-                if (!mbar_wait(&acc_full[stage], phase, abortp)) break;
+                if (!mbar_wait(&acc_full[stage], phase, abortp, wait_ns)) break;
                 fence_after();
 #pragma unroll
                 for (int i = 0; i < kUnit; ++i) {
@@ -394,11 +395,11 @@ int mono_gemv_tc4_launch(const mono_gemv_args* a, long tasks, cudaStream_t st) {
     p.a = *a;
     const size_t smem = 1024 + (size_t)tc4::kStages * tc4::kStageBytes + (size_t)tc4::kScSlots * tc4::kSlotWords * 4 +
                         4 * tc4::kMaxSegTiles * 64 * sizeof(float) + 512;
-    static thread_local bool attr_set = false;
-    if (!attr_set) {
+    static std::atomic<uint64_t> attr_once{0};  // bit d: set on device d
+    if (mono::attr_needed(attr_once)) {
         cudaError_t e = cudaFuncSetAttribute(tc4::gemv_tc4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        attr_set = true;
+        mono::attr_done(attr_once);
     }
     int grid = a->max_ctas > 0 ? a->max_ctas : mono_sm_count();
     if (grid > tasks) grid = (int)tasks;

@@ -400,10 +400,14 @@ extern "C" int mono_gqa_select_launch(const mono_gqa_args* a, void* stream) {
         return MONO_E_ARG;
     }
     const size_t smem = 2 * (size_t)mono::kSelMaxBlocks * sizeof(long long);  // keys + candidates
-    static thread_local bool attr_set = false;
-    if (!attr_set) {
-        cudaFuncSetAttribute(mono::gqa_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attr_set = true;
+    static std::atomic<uint64_t> attr_once{0};  // bit d: set on device d
+    if (mono::attr_needed(attr_once)) {
+        const cudaError_t ae = cudaFuncSetAttribute(mono::gqa_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (ae != cudaSuccess) {
+            mono_set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(ae));
+            return (int)ae;
+        }
+        mono::attr_done(attr_once);
     }
     mono::launch_k(mono::gqa_select_kernel, a->rows, mono::kSelThreads, smem, (cudaStream_t)stream, *a);
     return gqa_done("mono_gqa_select_launch");
@@ -415,10 +419,14 @@ extern "C" int mono_gqa_attn_launch(const mono_gqa_args* a, void* stream) {
         mono_set_error("mono_gqa_attn_launch: q, caches, selection, scratch and out required");
         return MONO_E_ARG;
     }
-    static thread_local bool attr_set = false;
-    if (!attr_set) {
-        cudaFuncSetAttribute(mono::gqa_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(mono::GqaSplitSmem));
-        attr_set = true;
+    static std::atomic<uint64_t> attr_once{0};  // bit d: set on device d
+    if (mono::attr_needed(attr_once)) {
+        const cudaError_t ae = cudaFuncSetAttribute(mono::gqa_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(mono::GqaSplitSmem));
+        if (ae != cudaSuccess) {
+            mono_set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(ae));
+            return (int)ae;
+        }
+        mono::attr_done(attr_once);
     }
     mono::launch_k(mono::gqa_split_kernel, a->rows * a->kv_heads * mono::kGqaTopk, mono::kGqaDim, sizeof(mono::GqaSplitSmem), (cudaStream_t)stream, *a);
     mono::launch_k(mono::gqa_merge_kernel, a->rows * a->q_heads, mono::kGqaDim, 0, (cudaStream_t)stream, *a);

@@ -312,12 +312,12 @@ __global__ void __launch_bounds__(kThreads) index_score_tc_kernel(const mono_ind
 // Launches the tcgen05 score kernel for arguments mono_index_score_launch has validated.
 int mono_index_score_tc_launch(const mono_index_args* a, void* stream) {
     using namespace mono;
-    static thread_local bool attr_set = false;
-    if (!attr_set) {
+    static std::atomic<uint64_t> attr_once{0};  // bit d: set on device d
+    if (mono::attr_needed(attr_once)) {
         cudaError_t e = cudaFuncSetAttribute(isc::index_score_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, isc::kSmemBytes);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(isc::index_score_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, isc::kSmemBytes - isc::kABytes);
         if (e != cudaSuccess) return (int)e;
-        attr_set = true;
+        mono::attr_done(attr_once);
     }
     const char* nbs = getenv("MONO_ISC_BUFS");
     const int nb = nbs && nbs[0] == '1' ? 1 : 2;

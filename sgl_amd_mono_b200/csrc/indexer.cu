@@ -488,10 +488,14 @@ extern "C" int mono_index_score_launch(const mono_index_args* a, void* stream) {
         return MONO_E_ARG;
     }
     const size_t smem = sizeof(mono::ScoreSmem) + 128;
-    static thread_local bool attr_set = false;
-    if (!attr_set) {
-        cudaFuncSetAttribute(mono::index_score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attr_set = true;
+    static std::atomic<uint64_t> attr_once{0};  // bit d: set on device d
+    if (mono::attr_needed(attr_once)) {
+        const cudaError_t ae = cudaFuncSetAttribute(mono::index_score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (ae != cudaSuccess) {
+            mono_set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(ae));
+            return (int)ae;
+        }
+        mono::attr_done(attr_once);
     }
     const int max_tiles = (a->score_ld + mono::kKeyTile - 1) / mono::kKeyTile;
     int grid = a->rows * ((max_tiles + mono::kTilesPerTask - 1) / mono::kTilesPerTask);
@@ -522,10 +526,14 @@ extern "C" int mono_index_topk_launch(const mono_index_args* a, void* stream) {
     // rows of up to 48K keys keep their radix keys in shared memory
     const size_t key_bytes = (size_t)a->score_ld * sizeof(uint32_t);
     const int smem_keys = key_bytes <= 192 * 1024 ? 1 : 0;
-    static thread_local bool attr_set = false;
-    if (!attr_set) {
-        cudaFuncSetAttribute(mono::index_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 192 * 1024);
-        attr_set = true;
+    static std::atomic<uint64_t> attr_once{0};  // bit d: set on device d
+    if (mono::attr_needed(attr_once)) {
+        const cudaError_t ae = cudaFuncSetAttribute(mono::index_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 192 * 1024);
+        if (ae != cudaSuccess) {
+            mono_set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(ae));
+            return (int)ae;
+        }
+        mono::attr_done(attr_once);
     }
     mono::launch_k(mono::index_topk_kernel, a->rows, mono::kTopkThreads, smem_keys ? key_bytes : 0, (cudaStream_t)stream, *a, smem_keys);
     cudaError_t e = cudaGetLastError();

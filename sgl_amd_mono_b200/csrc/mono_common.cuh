@@ -73,9 +73,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait: false when the time limit ran out or another thread aborted.  The
-// limit is generous (2 s): it exists so that no launch can hang a GPU.
+// default limit is generous (2 s): it exists so that no launch can hang a GPU.  Launches
+// whose argument block carries a deadline (mono_gemv_args.wait_ns, set from the build
+// context's deadline_s as the reference ties its deadline to the server's watchdog,
+// common/guard.py:4-7,69) pass it as `limit_ns`.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          uint64_t limit_ns = kWaitLimitNs) {
     // a try_wait suspends the thread for a hardware-defined interval: a few of them cover the usual wait,
     // and the (slow) global timer is only read once a wait is clearly long
 #pragma unroll 1
@@ -86,7 +90,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 15) == 15) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > kWaitLimitNs) break;
+            if (globaltimer_ns() - t0 > limit_ns) break;
         }
     }
     *abort_flag = 1;
@@ -266,8 +270,28 @@ __device__ __forceinline__ float ld_cg_f32(const float* p) {
 }  // namespace mono
 
 // Host side: one launch helper, with or without the programmatic-serialization attribute.
+#include <atomic>
 extern int g_mono_pdl;
 namespace mono {
+// Function attributes (the > 48 KB dynamic shared memory opt-in) belong to a device's copy of a
+// kernel, so they are set once per device, whichever thread first launches there.  Usage:
+//   static std::atomic<uint64_t> once{0};
+//   if (attr_needed(once)) { ... cudaFuncSetAttribute ...; if ok: attr_done(once); }
+inline int current_device_bit(uint64_t* bit) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev > 63) return -1;
+    *bit = 1ull << dev;
+    return dev;
+}
+inline bool attr_needed(const std::atomic<uint64_t>& once) {
+    uint64_t bit = 0;
+    if (current_device_bit(&bit) < 0) return true;
+    return (once.load(std::memory_order_acquire) & bit) == 0;
+}
+inline void attr_done(std::atomic<uint64_t>& once) {
+    uint64_t bit = 0;
+    if (current_device_bit(&bit) >= 0) once.fetch_or(bit, std::memory_order_release);
+}
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
     cudaLaunchConfig_t cfg = {};

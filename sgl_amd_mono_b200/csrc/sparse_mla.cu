@@ -344,14 +344,14 @@ static int sparse_mla_launch(const mono_sparse_mla_args* a, const mono_act_prep_
     int nsplit, chunks;
     mla_plan(a->rows, a->heads, a->topk, sms, &nsplit, &chunks);
     const size_t smem = sizeof(mono::MlaSmem) + 128;
-    static thread_local bool attr_set = false;
-    if (!attr_set) {
+    static std::atomic<uint64_t> attr_once{0};  // bit d: set on device d
+    if (mono::attr_needed(attr_once)) {
         cudaError_t e = cudaFuncSetAttribute(mono::sparse_mla_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) {
             mono_set_error("mono_sparse_mla_launch: %s", cudaGetErrorString(e));
             return (int)e;
         }
-        attr_set = true;
+        mono::attr_done(attr_once);
     }
     int grid = a->rows * ((a->heads + mono::kHeadGroup - 1) / mono::kHeadGroup) * nsplit;
     if (grid > 2 * sms) grid = 2 * sms;
@@ -440,14 +440,14 @@ extern "C" int mono_sparse_mla_launch_noalloc(const mono_sparse_mla_args* a, voi
     int nsplit, chunks;
     mla_plan(args.rows, args.heads, args.topk, sms, &nsplit, &chunks);
     const size_t smem = sizeof(mono::MlaSmem) + 128;
-    static thread_local bool attr_set = false;
-    if (!attr_set) {
+    static std::atomic<uint64_t> attr_once{0};  // bit d: set on device d
+    if (mono::attr_needed(attr_once)) {
         cudaError_t e = cudaFuncSetAttribute(mono::sparse_mla_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) {
             mono_set_error("mono_sparse_mla_launch_noalloc: %s", cudaGetErrorString(e));
             return (int)e;
         }
-        attr_set = true;
+        mono::attr_done(attr_once);
     }
     int grid = args.rows * ((args.heads + mono::kHeadGroup - 1) / mono::kHeadGroup) * nsplit;
     if (grid > 2 * sms) grid = 2 * sms;

@@ -415,6 +415,37 @@ __device__ __forceinline__ void st_sys_u32(uint64_t addr, uint32_t a) {
     asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(a) : "memory");
 }
 
+// Waits for the (value, tag) word at `addr` of this rank's own peer region to carry `tag`.  Every 64 polls
+// it looks at the sticky error words and the peers' flag words and at the deadline (common/sync.py:31-98,
+// common/guard.py:100-241): a wait that runs out stores site + 1 in the deadline word and raises this
+// rank's flag at every peer; a wait that sees a failure elsewhere gives up at once.  *failed says which.
+__device__ __forceinline__ uint2 poll_tagged(uint64_t addr, uint32_t tag, int32_t* guard, const uint64_t* peer_guards, int world,
+                                             int rank, int site, uint64_t deadline_ns, uint64_t t0, bool* failed) {
+    uint2 v = ld_sys_v2(addr);
+    uint32_t spins = 0;
+    while (v.y != tag) {
+        if ((++spins & 63) == 0) {
+            if (guard_failed(guard)) { *failed = true; break; }
+            const volatile int* gw = guard;
+            if (gw) {
+                for (int r = 0; r < world; ++r)
+                    if (gw[MONO_GUARD_FLAGS + r]) { guard_fail(guard, MONO_ERR_PEER, r); *failed = true; }
+                if (*failed) break;
+            }
+            if (globaltimer_ns() - t0 > deadline_ns) {
+                guard_fail(guard, MONO_ERR_DEADLINE, site);
+                if (peer_guards)
+                    for (int d = 0; d < world; ++d)
+                        if (d != rank) st_sys_u32(peer_guards[d] + 4ull * (MONO_GUARD_FLAGS + rank), 1u);
+                *failed = true;
+                break;
+            }
+        }
+        v = ld_sys_v2(addr);
+    }
+    return v;
+}
+
 __global__ void __launch_bounds__(kReduceThreads) reduce_kernel(const mono_reduce_args a) {
     pdl_launch_dependents();
     const int pairs = a.n / 2;
@@ -459,30 +490,9 @@ __global__ void __launch_bounds__(kReduceThreads) reduce_kernel(const mono_reduc
             bool failed = guard_failed(a.guard);
             for (int src = 0; src < a.world && !failed; ++src) {
                 const uint64_t addr = mine + (((size_t)parity * a.world + src) * slot_pairs + (size_t)row * pairs + pc) * 8;
-                uint2 v = ld_sys_v2(addr);
-                uint32_t spins = 0;
-                while (v.y != tag) {
-                    if ((++spins & 63) == 0) {
-                        if (guard_failed(a.guard)) { failed = true; break; }
-                        const volatile int* gw = a.guard;
-                        if (gw) {
-                            for (int r = 0; r < a.world; ++r)
-                                if (gw[MONO_GUARD_FLAGS + r]) { guard_fail(a.guard, MONO_ERR_PEER, r); failed = true; }
-                            if (failed) break;
-                        }
-                        if (globaltimer_ns() - t0 > a.deadline_ns) {
-                            guard_fail(a.guard, MONO_ERR_DEADLINE, a.site);
-                            if (a.peer_guards)
-                                for (int d = 0; d < a.world; ++d)
-                                    if (d != a.rank) st_sys_u32(a.peer_guards[d] + 4ull * (MONO_GUARD_FLAGS + a.rank), 1u);
-                            failed = true;
-                            break;
-                        }
-                    }
-                    v = ld_sys_v2(addr);
-                }
+                const uint2 v = poll_tagged(addr, tag, a.guard, a.peer_guards, a.world, a.rank, a.site, a.deadline_ns, t0, &failed);
                 if (failed) break;
-                const __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162*>(&v.x);
+                const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&v.x);
                 acc0 += __low2float(b);
                 acc1 += __high2float(b);
             }
@@ -504,6 +514,60 @@ __global__ void epoch_advance_kernel(int32_t* guard) {
     guard[MONO_GUARD_EPOCH] += 1;
 }
 
+// ------------------------------------------------------------------ LM-head logits: K-split sum + all-gather
+// Every thread owns one pair of adjacent columns of one row of this rank's share of the vocabulary:
+// it adds the K splits in order, and with world > 1 rounds the pair to bf16, stores (pair, tag) into every
+// rank's logits region at [parity][row][rank * n_local / 2 + pair], then waits for the same pair of every
+// other rank in its own region and widens it to f32 (glm53_flash/gfx950/kernel.py:3700-3770; two slots by
+// launch parity, glm53_flash/gfx950/layout.py:193-215).  A thread waits for words of other GPUs only, never
+// for another CTA of this launch, so the grid need not be resident at once.
+__global__ void __launch_bounds__(kReduceThreads) logits_gather_kernel(const mono_logits_gather_args a) {
+    pdl_prologue();
+    const int pairs = a.n_local / 2;
+    const int total = a.rows * pairs;
+    const int all_pairs = a.world * pairs;
+    uint32_t tag = a.tag;
+    int parity = a.parity;
+    if (a.world > 1 && a.guard && tag == 0) {
+        const int epoch = reinterpret_cast<const volatile int*>(a.guard)[MONO_GUARD_EPOCH];
+        tag = (uint32_t)epoch * 256u + (uint32_t)a.site + 1u;
+        parity = epoch & 1;
+    }
+    const uint64_t t0 = a.world > 1 ? globaltimer_ns() : 0;
+    for (int idx = blockIdx.x * kReduceThreads + threadIdx.x; idx < total; idx += gridDim.x * kReduceThreads) {
+        const int row = idx / pairs, pc = idx - row * pairs;
+        float p0 = 0.f, p1 = 0.f;
+#pragma unroll 4
+        for (int s = 0; s < a.nsum; ++s) {
+            const float2 v = *reinterpret_cast<const float2*>(a.partial + (size_t)s * a.sum_stride + (size_t)row * a.ld + 2 * pc);
+            p0 += v.x;
+            p1 += v.y;
+        }
+        float* out = a.out + (size_t)row * a.out_ld;
+        if (a.world <= 1) {
+            *reinterpret_cast<float2*>(out + 2 * pc) = make_float2(p0, p1);
+            continue;
+        }
+        __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+        const uint32_t word = *reinterpret_cast<uint32_t*>(&pb);
+        const size_t row_base = ((size_t)parity * kMaxRows + row) * all_pairs;
+        const size_t my_off = (row_base + (size_t)a.rank * pairs + pc) * 8;
+        for (int d = 0; d < a.world; ++d)
+            if (d != a.rank) st_sys_v2(a.peer_ptrs[d] + my_off, word, tag);
+        *reinterpret_cast<float2*>(out + (size_t)a.rank * a.n_local + 2 * pc) = make_float2(__low2float(pb), __high2float(pb));
+        const uint64_t mine = a.peer_ptrs[a.rank];
+        bool failed = guard_failed(a.guard);
+        for (int src = 0; src < a.world && !failed; ++src) {
+            if (src == a.rank) continue;
+            const uint2 v = poll_tagged(mine + (row_base + (size_t)src * pairs + pc) * 8, tag, a.guard, a.peer_guards, a.world, a.rank,
+                                        a.site, a.deadline_ns, t0, &failed);
+            if (failed) break;
+            const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&v.x);
+            *reinterpret_cast<float2*>(out + (size_t)src * a.n_local + 2 * pc) = make_float2(__low2float(b), __high2float(b));
+        }
+    }
+}
+
 }  // namespace mono
 
 // ------------------------------------------------------------------------ host
@@ -523,10 +587,14 @@ extern "C" int mono_act_prep_launch(const mono_act_prep_args* a, void* stream) {
             return MONO_E_ARG;
         }
     }
-    static thread_local bool attr_set = false;
-    if (!attr_set) {
-        cudaFuncSetAttribute(mono::act_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * (int)sizeof(float));
-        attr_set = true;
+    static std::atomic<uint64_t> attr_once{0};  // bit d: set on device d
+    if (mono::attr_needed(attr_once)) {
+        const cudaError_t ae = cudaFuncSetAttribute(mono::act_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * (int)sizeof(float));
+        if (ae != cudaSuccess) {
+            mono_set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(ae));
+            return (int)ae;
+        }
+        mono::attr_done(attr_once);
     }
     mono::launch_k(mono::act_prep_kernel, a->rows * (a->segs > 1 ? a->segs : 1), mono::kPrepThreads, a->k * sizeof(float), (cudaStream_t)stream, *a);
     cudaError_t e = cudaGetLastError();
@@ -630,8 +698,9 @@ extern "C" int mono_reduce_launch(const mono_reduce_args* a, void* stream) {
         return MONO_E_ARG;
     }
     if (a->world > 1 && (!a->peer_ptrs || a->rank < 0 || a->rank >= a->world || a->world > 8 || a->deadline_ns == 0 ||
-                         (a->tag == 0 && !a->guard))) {
-        mono_set_error("mono_reduce_launch: world %d needs peer_ptrs, a rank, a deadline and a tag or guard words", a->world);
+                         (a->tag == 0 && !a->guard) || a->site < 0 || a->site > 254)) {
+        mono_set_error("mono_reduce_launch: world %d needs peer_ptrs, a rank, a deadline, a site in 0..254 (the tag is "
+                       "epoch * 256 + site + 1) and a tag or guard words", a->world);
         return MONO_E_ARG;
     }
     const int total = a->rows * (a->n / 2);
@@ -648,4 +717,30 @@ extern "C" int mono_epoch_advance_launch(int32_t* guard, void* stream) {
     if (!guard) return MONO_E_ARG;
     mono::launch_k(mono::epoch_advance_kernel, 1, 1, 0, (cudaStream_t)stream, guard);
     return (int)cudaGetLastError();
+}
+
+extern "C" size_t mono_logits_peer_bytes(int n_local, int world) {
+    return (size_t)2 * MONO_MAX_ROWS * ((size_t)world * n_local / 2) * 8;
+}
+
+extern "C" int mono_logits_gather_launch(const mono_logits_gather_args* a, void* stream) {
+    if (!a || a->rows < 1 || a->rows > MONO_MAX_ROWS || a->n_local < 2 || (a->n_local & 1) || (a->ld & 1) || !a->partial || !a->out ||
+        a->nsum < 1 || a->world < 1 || a->out_ld < a->world * a->n_local || (a->out_ld & 1)) {
+        mono_set_error("mono_logits_gather_launch: rows 1..16, even n_local and ld, partial, out and out_ld >= world * n_local required");
+        return MONO_E_ARG;
+    }
+    if (a->world > 1 && (!a->peer_ptrs || a->rank < 0 || a->rank >= a->world || a->world > 8 || a->deadline_ns == 0 ||
+                         (a->tag == 0 && !a->guard) || a->site < 0 || a->site > 254)) {
+        mono_set_error("mono_logits_gather_launch: world %d needs peer_ptrs, a rank, a deadline, a site in 0..254 and a tag or guard words",
+                       a->world);
+        return MONO_E_ARG;
+    }
+    const int total = a->rows * (a->n_local / 2);
+    int grid = (total + mono::kReduceThreads - 1) / mono::kReduceThreads;
+    const int sms = mono_sm_count();
+    if (grid > 8 * sms) grid = 8 * sms;
+    mono::launch_k(mono::logits_gather_kernel, grid, mono::kReduceThreads, 0, (cudaStream_t)stream, *a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) mono_set_error("mono_logits_gather_launch: %s", cudaGetErrorString(e));
+    return (int)e;
 }

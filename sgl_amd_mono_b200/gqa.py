@@ -151,14 +151,14 @@ class GqaAttentionOp:
         self.core = GqaCore(cfg, w, device, max_ctx)
         # the bf16 normed input goes through the FP8 tensor cores exactly, as two E4M3 planes
         self.xq = ops.ActBuf(L.ACT_HILO, h, device)
-        self.qkv_g = ops.Gemv(L.W_FP8, self.guard)
+        self.qkv_g = ops.Gemv(L.W_FP8, self.guard, deadline_s)
         st, ns = ops.plan_split(-(-h // 128), cfg.qkv_rows // 128, L.W_FP8)
         self.ns_qkv = ns
         self.qkv = z(ns, L.MAX_ROWS, cfg.qkv_rows)
         self.qkv_g.add("qkv", w["qkv"], self.xq, self.qkv, wscale=w["qkv_s"], split_tiles=st, nsplit=ns)
         ok = cfg.q_local * HEAD_DIM
         self.oq = ops.ActBuf(L.ACT_HILO, ok, device)
-        self.o_g = ops.Gemv(L.W_FP8, self.guard)
+        self.o_g = ops.Gemv(L.W_FP8, self.guard, deadline_s)
         st, ns = ops.plan_split(-(-ok // 128), -(-h // 128), L.W_FP8)
         self.ns_o = ns
         self.o_p = z(ns, L.MAX_ROWS, h)

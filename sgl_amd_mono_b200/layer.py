@@ -57,7 +57,7 @@ class MlaLayerOp:
         self.x = ops.ActBuf(L.ACT_HILO, h, device)
         self.xbf = z(R, h, dt=torch.bfloat16)
         # ---- launch A: q_a|kv_a and the index-key projection
-        self.gA = ops.Gemv(L.W_FP8, self.guard)
+        self.gA = ops.Gemv(L.W_FP8, self.guard, deadline_s)
         kt = -(-h // 128)
         stA, nsA = ops.plan_split(kt, -(-(ql + KV_DIM) // 128) + (1 if ih else 0), L.W_FP8)
         self.nsA = nsA
@@ -75,7 +75,7 @@ class MlaLayerOp:
         self.qa = ops.ActBuf(L.ACT_HILO, ql, device)
         self.kv_out = z(R, KV_DIM, dt=torch.bfloat16)
         # ---- launch B: q_b and the index-query projection
-        self.gB = ops.Gemv(L.W_FP8, self.guard)
+        self.gB = ops.Gemv(L.W_FP8, self.guard, deadline_s)
         ktb = -(-ql // 128)
         stB, nsB = ops.plan_split(ktb, -(-hl * 192 // 128) + (ih if ih else 0), L.W_FP8)
         self.nsB = nsB
@@ -98,7 +98,7 @@ class MlaLayerOp:
         # ---- W_UV (per head) and o_proj
         self.lat = ops.ActBuf(L.ACT_HILO, 512, device, segs=hl)
         self.uv_p = z(1, R, hl * 128)
-        self.gUV = ops.Gemv(L.W_FP8, self.guard)
+        self.gUV = ops.Gemv(L.W_FP8, self.guard, deadline_s)
         self.o = ops.ActBuf(L.ACT_HILO, hl * 128, device)
         # on the tcgen05 consumer the W_UV job can write its output straight into o_proj's activation planes
         # (MONO_UV_STAGED=1 / 0).  Measured on config 3: 6 us faster per layer with 128 local heads (128 CTAs
@@ -116,7 +116,7 @@ class MlaLayerOp:
         stO, nsO = ops.plan_split(kto, -(-h // 128), L.W_FP8)
         self.nsO = nsO
         self.o_p = z(nsO, R, h)
-        self.gO = ops.Gemv(L.W_FP8, self.guard)
+        self.gO = ops.Gemv(L.W_FP8, self.guard, deadline_s)
         self.gO.add("o_proj", w["o_proj"], self.o, self.o_p, wscale=w["o_proj_s"], split_tiles=stO, nsplit=nsO)
         self.h1 = z(R, h, dt=torch.bfloat16)
         self.ffn = MoeFfn(cfg, w, device, max_rows=max_rows, peer=peer, guard=self.guard, site=2 * layer + 1,
@@ -196,8 +196,12 @@ class MlaLayerOp:
         if not self.uv_staged:
             ops.act_prep(rows, hl * 128, self.o, src_f32=self.uv_p, nsum=1)
         self.gO.launch(rows)
+        # consecutive all-reduces of a step must alternate between the peer buffer's two regions (site % 2): a
+        # rank may start pushing launch n + 1 while a peer still reads launch n's words.  A layer without an
+        # FFN all-reduce therefore numbers its attention site by the layer alone
         ops.reduce_rows(rows, cfg.hidden, self.o_p, self.nsO, self.h1, residual=h, slots=step.slots, peer=self.peer,
-                        site=2 * self.layer, guard=self.guard, deadline_s=self.deadline_s)
+                        site=2 * self.layer if self.ffn is not None else self.layer, guard=self.guard,
+                        deadline_s=self.deadline_s)
         if self.ffn is None:
             return self.h1[:rows]
         return self.ffn(self.h1[:rows], step.slots)

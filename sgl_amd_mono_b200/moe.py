@@ -63,7 +63,7 @@ class MoeFfn:
         # ---- up / gate launch
         # the shared expert's dense job goes first: its weight tiles do not depend on the router,
         # so the launch can request them before the routing of this step is known
-        self.up = ops.Gemv(_WK[efmt], self.guard)
+        self.up = ops.Gemv(_WK[efmt], self.guard, deadline_s)
         self.up_sh = self.mid_s = self.up_s = None
         if self.has_shared:
             self.xs = self.xq if same else ops.ActBuf(act_of(sfmt, w["sh13"]), h, device)
@@ -71,7 +71,7 @@ class MoeFfn:
             st, ns = ops.plan_split(_ktiles(w["sh13"]), -(-2 * il // 128), _WK[sfmt])
             self.ns_up_s = ns
             self.up_s = z(ns, L.MAX_ROWS, 2 * il)
-            g = self.up if same else ops.Gemv(_WK[sfmt], self.guard)
+            g = self.up if same else ops.Gemv(_WK[sfmt], self.guard, deadline_s)
             g.add("sh13", w["sh13"], self.xs, self.up_s, wscale=w.get("sh13_s"), split_tiles=st, nsplit=ns)
             self.up_sh = None if same else g
         # the tcgen05 consumer takes K segments of up to 32 tiles (no activation slot to fit): fewer K splits
@@ -86,23 +86,24 @@ class MoeFfn:
         assert got == self.ns_up
         # ---- down launch: routed expert groups, then the shared expert's K splits
         nrb = -(-h // 128)
-        # expert groups: row blocks x groups tasks should fill whole rounds of the 148 CTAs
+        # expert groups: row blocks x groups tasks should fill whole rounds of the grid (one CTA per SM)
+        sms = ops.sm_count()
         best = (0.0, 1)
         for g in range(1, min(self.max_expert, 16) + 1):
             tasks = nrb * g
-            eff = (tasks / 148) / -(-tasks // 148)
-            if tasks >= 148 and eff > best[0] + 1e-9:
+            eff = (tasks / sms) / -(-tasks // sms)
+            if tasks >= sms and eff > best[0] + 1e-9:
                 best = (eff, g)
-        self.groups = best[1] if best[0] > 0 else max(1, min(self.max_expert, -(-148 // nrb)))
+        self.groups = best[1] if best[0] > 0 else max(1, min(self.max_expert, -(-sms // nrb)))
         ns_dn_s = 0
         if self.has_shared:
             self.st_dn_s, ns_dn_s = ops.plan_split(_ktiles(w["sh2"]), nrb, _WK[sfmt])
         self.n_slices = self.groups + ns_dn_s
         self.down_p = z(self.n_slices, L.MAX_ROWS, h)
-        self.down = ops.Gemv(_WK[efmt], self.guard)
+        self.down = ops.Gemv(_WK[efmt], self.guard, deadline_s)
         self.down_sh = None
         if self.has_shared:
-            g = self.down if same else ops.Gemv(_WK[sfmt], self.guard)
+            g = self.down if same else ops.Gemv(_WK[sfmt], self.guard, deadline_s)
             g.add("sh2", w["sh2"], self.mid_s, self.down_p, wscale=w.get("sh2_s"), out_slice=self.groups,
                   split_tiles=self.st_dn_s, nsplit=ns_dn_s)
             self.down_sh = None if same else g
@@ -122,7 +123,7 @@ class MoeFfn:
         # an expert's activation is 4+ chunks per row and the separate activation launch spreads it better)
         chain_default = "1" if il <= 256 else "0"
         if efmt == "fp8_block" and (not self.has_shared or same) and tc_on and os.environ.get("MONO_MOE_CHAINED", chain_default) != "0":
-            g = ops.Gemv(L.W_FP8, self.guard)
+            g = ops.Gemv(L.W_FP8, self.guard, deadline_s)
             first = 0
             if self.has_shared:
                 g.add("sh13", w["sh13"], self.xs, self.up_s, wscale=w.get("sh13_s"), split_tiles=st, nsplit=self.ns_up_s)

@@ -31,6 +31,14 @@ def _up(x: int, m: int) -> int:
     return -(-x // m) * m
 
 
+def sm_count() -> int:
+    """SMs of the current device (every persistent grid is sized by it: ``common/plan.py:23-25`` sizes the
+    reference's by its 256 CUs).  Without a visible device (host-only planning and its CPU tests) the
+    B200's count."""
+    n = L.load().mono_sm_count()
+    return n if n > 0 else 148
+
+
 def require(t: torch.Tensor, name: str, dtype=None, shape=None, cuda: bool = True) -> torch.Tensor:
     if not isinstance(t, torch.Tensor):
         raise ValueError(f"{name}: expected a tensor, got {type(t).__name__}")
@@ -96,7 +104,7 @@ _TILE_K = {L.W_FP8: 128, L.W_BF16: 64, L.W_MXFP4: 256}
 _MAX_SEG_TILES = {L.W_FP8: 16, L.W_BF16: 16, L.W_MXFP4: 8}
 
 
-def plan_split(k_tiles: int, row_blocks: int, wkind: int, sms: int = 148, cap: int | None = None):
+def plan_split(k_tiles: int, row_blocks: int, wkind: int, sms: int | None = None, cap: int | None = None):
     """(split_tiles, nsplit): K splits of whole 4-tile groups so that row_blocks x
     nsplit tasks cover the SMs about twice and a segment fits the activation slot."""
     if cap is None and wkind == L.W_FP8:
@@ -106,6 +114,7 @@ def plan_split(k_tiles: int, row_blocks: int, wkind: int, sms: int = 148, cap: i
         lib.mono_set_gemv_tcgen05(tc_on)
         cap = 32 if tc_on else None
     cap = cap or _MAX_SEG_TILES[wkind]
+    sms = sms or sm_count()
     want = max(1, -(-2 * sms // max(row_blocks, 1)))
     split = min(cap, max(4, _up(-(-k_tiles // want), 4)))
     if split >= k_tiles:
@@ -123,13 +132,17 @@ def fp4_tma_ok(w: torch.Tensor) -> bool:
 class Gemv:
     """One persistent weight-streaming launch over up to four jobs (``mono_gemv_launch``)."""
 
-    def __init__(self, wkind: int, guard: torch.Tensor | None = None):
+    def __init__(self, wkind: int, guard: torch.Tensor | None = None, deadline_s: float = 0.0):
+        """``deadline_s``: limit of every device-side wait of the launch (0 = the library's 2 s); the
+        build context's deadline, as the reference arms its waits from it (``common/guard.py:4-7,69``)."""
         self.wkind = wkind
         self.args = L.GemvArgs()
         self.args.wkind = wkind
         self.args.guard = _p(guard)
         self.args.njobs = 0
+        self.args.wait_ns = int(deadline_s * 1e9)
         self._keep: list = [guard]
+        self._chain_words: list = []
 
     def _w3(self, w: torch.Tensor, name: str) -> torch.Tensor:
         if w.dim() == 2:
@@ -163,7 +176,7 @@ class Gemv:
             if k_tiles > 32:
                 raise ValueError(f"{name}: a down projection spans {k_tiles} tiles, at most 32")
             job.split_tiles = k_tiles
-            job.nsplit = nsplit or max(1, min(max_expert, -(-2 * 148 // nrb)))
+            job.nsplit = nsplit or max(1, min(max_expert, -(-2 * sm_count() // nrb)))
         else:
             tasks_rb = nrb * (max_expert if mode == L.JOB_EXPERT_UP else 1)
             st, ns = plan_split(k_tiles, tasks_rb, self.wkind)
@@ -239,6 +252,22 @@ class Gemv:
         up.feeds_job, up.done, up.ready = down_job + 1, done.data_ptr(), ready.data_ptr()
         dn.ready = ready.data_ptr()
         self._keep += [done, ready]
+        self._chain_words += [done, ready]
+
+    def max_resident_ctas(self) -> int:
+        """CTAs of this launch's kernel the device keeps resident (``minimax_m31/residency.py:66-85``)."""
+        n = L.load().mono_gemv_max_resident_ctas(C.byref(self.args))
+        if n < 0:
+            L.check(n, "mono_gemv_max_resident_ctas")
+        return n
+
+    def reset_chain(self) -> None:
+        """After a launch that gave up (guard error) and once the host has cleared the guard words: the
+        task counters, stamps and the leave counter of the chained jobs go back to zero."""
+        for t in self._chain_words:
+            t.zero_()
+        if getattr(self, "gen", None) is not None:
+            self.gen[1] = 0
 
     def launch(self, rows: int) -> None:
         self.args.rows = rows
@@ -260,6 +289,17 @@ def rowdot(rows: int, w: torch.Tensor, x_bf16: torch.Tensor, out: torch.Tensor, 
     L.check(L.load().mono_rowdot_launch(C.byref(a), _stream()), "mono_rowdot_launch")
 
 
+_injectors: dict = {}
+
+
+def _injector(rank: int):
+    from .common.guard import FaultInjector
+
+    if rank not in _injectors:
+        _injectors[rank] = FaultInjector(rank)
+    return _injectors[rank]
+
+
 def reduce_rows(rows: int, n: int, partial: torch.Tensor, nsum: int, out: torch.Tensor, *, residual=None,
                 slots=None, peer=None, site: int = 0, guard=None, deadline_s: float = 5.0) -> None:
     """Adds the partial slices, all-reduces across ranks in rank order, adds the residual."""
@@ -269,13 +309,38 @@ def reduce_rows(rows: int, n: int, partial: torch.Tensor, nsum: int, out: torch.
     a.residual, a.slots, a.out = _p(residual), _p(slots), out.data_ptr()
     a.world, a.rank = 1, 0
     if peer is not None and peer.world > 1:
+        if _injector(peer.rank).skip(site):
+            return  # MONO_FAULT_INJECT: this rank's host skips the launch; the peers' waits at `site` run out
         a.world, a.rank = peer.world, peer.rank
         a.peer_ptrs = peer.region_table(site).data_ptr()
         a.peer_guards = peer.guard_table.data_ptr()
         a.tag, a.parity = 0, 0
         a.deadline_ns = int(deadline_s * 1e9)
+    if not 0 <= site <= 254:
+        raise ValueError(f"site {site}: the launch tag holds sites 0..254 (tag = epoch * 256 + site + 1)")
     a.site, a.guard = site, _p(guard)
     L.check(L.load().mono_reduce_launch(C.byref(a), _stream()), "mono_reduce_launch")
+
+
+def logits_gather(rows: int, n_local: int, partial: torch.Tensor, nsum: int, out: torch.Tensor, *, peer=None,
+                  site: int = 254, guard=None, deadline_s: float = 5.0) -> None:
+    """Adds the LM head's K splits in order and gathers every rank's bf16 logits into f32 ``out``
+    ``[rows, world * n_local]`` (``glm53_flash/gfx950/kernel.py:3700-3770``)."""
+    a = L.LogitsGatherArgs()
+    a.rows, a.n_local, a.partial, a.nsum, a.ld = rows, n_local, partial.data_ptr(), nsum, partial.shape[-1]
+    a.sum_stride = L.MAX_ROWS * partial.shape[-1]
+    a.out, a.out_ld = out.data_ptr(), out.shape[-1]
+    a.world, a.rank = 1, 0
+    if peer is not None and peer.world > 1:
+        if peer.logits_table is None:
+            raise ValueError("the peer buffer was built without a logits region (logits_local = 0)")
+        if _injector(peer.rank).skip(site):
+            return
+        a.world, a.rank = peer.world, peer.rank
+        a.peer_ptrs, a.peer_guards = peer.logits_table.data_ptr(), peer.guard_table.data_ptr()
+        a.deadline_ns = int(deadline_s * 1e9)
+    a.site, a.guard = site, _p(guard)
+    L.check(L.load().mono_logits_gather_launch(C.byref(a), _stream()), "mono_logits_gather_launch")
 
 
 def sparse_mla(q, kv_pages, topk_slots, out, scratch, sm_scale: float, topk: int | None = None, staged=None) -> None:

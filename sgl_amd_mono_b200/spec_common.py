@@ -19,7 +19,7 @@ from .registry import BuildContext, Plan
 
 log = logging.getLogger("sgl_amd_mono_b200")
 ISA = "sm_100a"
-SM_COUNT = 148
+SM_COUNT = 148  # resident_blocks a spec declares before any device is visible: one CTA per SM of a B200
 ROWS = tuple(range(1, L.MAX_ROWS + 1))
 TP_SIZES = (1, 2, 4, 8)
 

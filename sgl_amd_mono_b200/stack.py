@@ -31,8 +31,10 @@ class DecoderStack:
             self.draft = MlaLayerOp(cfg, draft_weights, device, max_ctx, peer=peer, guard=self.guard,
                                     layer=len(layer_weights), deadline_s=deadline_s)
         last = layer_weights[-1]
-        self.head = LmHeadOp(cfg.hidden, last["lm_head"], last["final_norm"], cfg.eps, device, guard=self.guard) \
-            if "lm_head" in last else None
+        # with a logits region in the peer buffer the tail gathers the whole vocabulary on every rank
+        head_peer = peer if peer is not None and getattr(peer, "logits_table", None) is not None else None
+        self.head = LmHeadOp(cfg.hidden, last["lm_head"], last["final_norm"], cfg.eps, device, guard=self.guard,
+                             peer=head_peer, site=254, deadline_s=deadline_s) if "lm_head" in last else None
         self.graph = None
 
     @property

@@ -58,9 +58,12 @@ def _experts(cfg: LayerConfig, n: int, g, device, fmt: str, chunk: int = 8):
     return w13, s13, w2, s2
 
 
-def layer_weights(cfg: LayerConfig, rank: int = 0, device="cpu", layer: int = 0) -> dict:
+def layer_weights(cfg: LayerConfig, rank: int = 0, device="cpu", layer: int = 0, out_scale: float = 1.0) -> dict:
     """One rank's tensors of one layer.  Replicated tensors depend on the layer seed
-    only, so they are identical on every rank; sharded ones also depend on the rank."""
+    only, so they are identical on every rank; sharded ones also depend on the rank.
+    ``out_scale`` multiplies the block scales of the projections that write into the
+    residual stream (o_proj, the experts' down projections): with the reference's recipe a
+    block adds values of magnitude 3..10 to the stream; 0.1 makes that O(1) ("unit scale")."""
     g = _gen(1000 * layer + 7, device)
     gs = _gen(1000 * layer + 7 + 101 * (rank + 1), device)
     w: dict = {}
@@ -91,6 +94,10 @@ def layer_weights(cfg: LayerConfig, rank: int = 0, device="cpu", layer: int = 0)
             w["sh13"], w["sh2"] = a[0], c[0]
             if b is not None:
                 w["sh13_s"], w["sh2_s"] = b[0], d[0]
+    if out_scale != 1.0:
+        for k in ("o_proj_s", "w2_s", "sh2_s"):
+            if k in w and w[k] is not None and w[k].dtype == torch.float32:
+                w[k] = w[k] * out_scale
     if cfg.vocab:
         w["final_norm"] = _norm(h, g, device)
         w["lm_head"] = (torch.randn(cfg.vocab // cfg.tp, h, generator=gs, device=device) * 0.02).bfloat16()

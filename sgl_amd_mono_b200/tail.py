@@ -2,9 +2,12 @@
 
 Reference counterpart: ``glm53_flash/gfx950/kernel.py:3626-3770`` (``run_head``) behind
 ``FlashHeadOp`` (``glm53_flash/gfx950/runner.py:504-550``); golden model
-``glm53_flash/check.py:284-302``.  Logits come back as f32 ``[rows, vocab / tp]``; the
-weight (1.06 GB at vocab 129280 x hidden 4096) is streamed once by the bf16 GEMV job,
-without a K split, so the f32 result needs no second pass.
+``glm53_flash/check.py:284-302``.  The weight (1.06 GB at vocab 129280 x hidden 4096) is
+streamed once by the bf16 GEMV job.  Without peers the logits come back as f32
+``[rows, vocab]`` (up to 8 rows straight from the GEMV; wider steps split K, and a gather
+launch adds the splits in order).  With peers every rank pushes its bf16-rounded share into
+every rank's logits region and gathers f32 ``[rows, vocab]`` of the whole vocabulary, the
+same bits on every rank (``kernel.py:3700-3770``).
 """
 
 from __future__ import annotations
@@ -16,7 +19,8 @@ from . import ops
 
 
 class LmHeadOp:
-    def __init__(self, hidden: int, w_head: torch.Tensor, final_norm: torch.Tensor, eps: float, device, guard=None):
+    def __init__(self, hidden: int, w_head: torch.Tensor, final_norm: torch.Tensor, eps: float, device, guard=None,
+                 peer=None, site: int = 254, deadline_s: float = 5.0):
         L.load()
         ops.require(w_head, "lm_head", torch.bfloat16)
         if w_head.dim() != 2 or w_head.shape[1] != hidden:
@@ -33,9 +37,12 @@ class LmHeadOp:
             cap = 32 if wide else 64
             st, ns = ops.plan_split(k_tiles, -(-self.vocab_local // 128), L.W_BF16, cap=cap)
             buf = self.logits if ns == 1 else torch.zeros(ns, L.MAX_ROWS, self.vocab_local, dtype=torch.float32, device=device)
-            g = ops.Gemv(L.W_BF16, self.guard)
+            g = ops.Gemv(L.W_BF16, self.guard, deadline_s)
             g.add("lm_head", w_head, self.x, buf, split_tiles=st, nsplit=ns)
             self.gemv[wide] = (g, buf, ns)
+        self.peer, self.site, self.deadline_s = peer, site, deadline_s
+        self.world = peer.world if peer is not None else 1
+        self.gathered = torch.zeros(L.MAX_ROWS, self.world * self.vocab_local, dtype=torch.float32, device=device)
 
     def __call__(self, h: torch.Tensor) -> torch.Tensor:
         rows = h.shape[0]
@@ -43,6 +50,8 @@ class LmHeadOp:
         ops.act_prep(rows, self.hidden, self.x, src_bf16=h, gamma=self.g, eps=self.eps)
         g, buf, ns = self.gemv[rows > 8]
         g.launch(rows)
-        if ns == 1:
+        if ns == 1 and self.world == 1:
             return buf[0, :rows]
-        return buf[:, :rows].sum(0)  # wide verify steps: K splits added by torch (not on the 1..8-row path)
+        ops.logits_gather(rows, self.vocab_local, buf, ns, self.gathered, peer=self.peer, site=self.site,
+                          guard=self.guard, deadline_s=self.deadline_s)
+        return self.gathered[:rows]

@@ -5,11 +5,10 @@ values and scores), streams within the hidden-state tolerance."""
 import pytest
 import torch
 
-from oracle import layers as OL
 from oracle import stages as S
 from sgl_amd_mono_b200 import ops, synth
-from sgl_amd_mono_b200.config import CFG_TINY, KV_DIM, PAGE
-from util import assert_close_hidden
+from sgl_amd_mono_b200.config import CFG_TINY
+from layer_checks import check_mla_layer
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -46,80 +45,26 @@ def _run(cfg, rows, ctx, pad=(), seed=1):
 def test_layer_stages_and_output(rows, ctx, pad):
     cfg = CFG_TINY
     op, w, step, dstep, h, out = _run(cfg, rows, ctx, pad)
-    wc = _cpu(w)
-    live = [r for r in range(rows) if r not in pad]
-    kvp, ixp = step.kv_pages.clone(), step.idx_pages.clone()
-    r = OL.attn_front(cfg, wc, h, step.positions, step.slots, step.cos, step.sin, kvp, ixp)
-    # ---- cache rows: values close, bytes exact given the kernel's own bf16 values
-    kv_k = op.kv_out[:rows].cpu().float()
-    assert_close_hidden(kv_k[live], torch.cat([r["latent"], r["k_pe"]], -1)[live], "latent | k_pe")
-    row_b, row_s = S.kv_row_encode(kv_k[:, :512], kv_k[:, 512:])
-    got_pages = dstep.kv_pages.cpu()
-    for i in live:
-        p, o = divmod(int(step.slots[i]), PAGE)
-        assert torch.equal(got_pages[p, o * KV_DIM : (o + 1) * KV_DIM], row_b[i]), f"KV bytes of row {i}"
-        assert got_pages[p, PAGE * KV_DIM :].view(torch.float32)[o] == row_s[i]
-    # exactly the live rows' cache rows changed
-    changed = (got_pages != step.kv_pages).any(1).nonzero().flatten().tolist()
-    assert set(changed) <= {int(step.slots[i]) // PAGE for i in live}
-    # ---- index keys: bytes exact given the kernel's own f32 values
-    ik_k = op.ik_out[:rows].cpu()
-    assert torch.allclose(ik_k[live], r["idx_key"][live], atol=2e-2, rtol=2e-2)
-    packed, codes = S.index_key_encode(ik_k)
-    got_idx = dstep.idx_pages.cpu()
-    for i in live:
-        p, o = divmod(int(step.slots[i]), PAGE)
-        assert torch.equal(got_idx[p, o * 64 : (o + 1) * 64], packed[i]), f"index key bytes of row {i}"
-        assert torch.equal(got_idx[p, PAGE * 64 + o * 4 : PAGE * 64 + (o + 1) * 4], codes[i])
-    # ---- queries
-    assert_close_hidden(op.q_full[:rows].cpu()[live], r["q_full"][live], "q_lat | q_pe", scale=float(r["q_full"].abs().max()))
-    assert_close_hidden(op.idx_q[:rows].cpu()[live], r["idx_q"][live], "index q", scale=float(r["idx_q"].abs().max()))
-    assert torch.allclose(op.idx_w[:rows].cpu()[live], r["idx_w"][live], atol=1e-3, rtol=1e-3)
-    # ---- scores close to the oracle's; top-k exact on the kernel's own scores
-    sc_k = op.scores[:rows].cpu()
-    topk_k, pos_k = op.topk_slots[:rows].cpu(), op.topk_pos[:rows].cpu()
-    topk_o, scores_o = OL.index_select(cfg, r, step.positions, step.slots, step.page_table, got_idx)
-    for i in range(rows):
-        if i in pad:
-            assert int((topk_k[i] >= 0).sum()) == 0
-            continue
-        n = int(step.positions[i]) + 1
-        ref_sc = scores_o[i]
-        assert torch.allclose(sc_k[i, :n], ref_sc, atol=2e-2 * float(ref_sc.abs().max()), rtol=0), f"scores of row {i}"
-        want = S.exact_topk_positions(sc_k[i], n, cfg.index_topk)
-        assert pos_k[i, : want.numel()].tolist() == want.tolist(), f"top-k positions of row {i}"
-        assert topk_k[i, : want.numel()].tolist() == S.slots_of_positions(step.page_table[i], want).tolist()
-        assert int((topk_k[i, want.numel():] >= 0).sum()) == 0
-    # ---- whole layer
-    # Each half is held to the tolerance on its own inputs (stage isolation, as the
-    # reference's check_k2.py:303-307 does): attention on the kernel's own selection, the
-    # MoE half on the kernel's own h1.  A borderline key or expert that flips between two
-    # f32 summation orders would otherwise be charged to the stage after it.
-    livemask = step.slots >= 0
-    part = OL.attn_back(cfg, wc, r, topk_k, kvp)
-    h1_ref = S.allreduce_rank_order([part * livemask[:, None]], h)
-    attn_scale = float((h1_ref.float() - h.float()).abs().max())
-    h1_k = op.h1[:rows].cpu()
-    assert_close_hidden(h1_k[live], h1_ref[live], "h1 after attention", scale=attn_scale)
-    mp, ids_o, wts_o, _ = OL.moe_partial(cfg, wc, h1_k, livemask)
-    ref = S.allreduce_rank_order([mp], h1_k)
-    ids_k, wts_k = S.route_from_scores(op.ffn.scores[:rows].cpu(), wc["router_bias"], cfg.top_k, cfg.route_scale)
-    for i in live:
-        assert op.ffn.ids[i].cpu().tolist() == ids_k[i].tolist(), f"router ids of row {i}"
-        assert ids_k[i].tolist() == ids_o[i].tolist(), "a near-tie flipped between the f32 logit sums: pick another seed"
-    scale = float((ref.float() - h1_k.float()).abs().max())
-    # 4e-2 of the block's scale here: after the block-FP8 recipe's O(1) weights one E4M3
-    # code step of a top-binade mid value (7 % of its chunk amax) times |W2| up to 0.4 moves
-    # an output by that much when the step falls differently in the two f32 orders; the
-    # GEMVs themselves are held to 1e-3 on identical quantised inputs in test_gpu_ffn.py
-    assert_close_hidden(out.cpu()[live], ref[live], "layer output", scale=scale, max_abs=4e-2)
-    # end to end against the oracle's own chain: cosine only (selections may differ at the margin)
-    full, _ = OL.layer_all_ranks(cfg, [wc], h, step.positions, step.slots, step.page_table, step.cos, step.sin,
-                                 step.kv_pages.clone(), step.idx_pages.clone())
-    cos = torch.nn.functional.cosine_similarity(out.cpu()[live].float().flatten(), full[live].float().flatten(), dim=0)
-    assert float(cos) >= 0.999, f"end-to-end cosine {float(cos):.6f}"
-    for i in pad:
-        assert torch.equal(out[i].cpu(), h[i]), "a pad row passes through unchanged"
+    check_mla_layer(cfg, op, w, step, dstep, h, out, pad)
+
+
+def test_layer_meets_the_literal_bar_on_unit_scale_streams():
+    """max-abs 2e-2 and cosine 0.999 exactly as stated, with no allowance for magnitude: the block
+    scales of o_proj and of the experts' down projections are a tenth of the reference's recipe and the
+    input rows a quarter, so every stream stays below |x| = 2 (one bf16 ulp < 2e-2)."""
+    cfg, rows, ctx = CFG_TINY, 6, 800
+    w = synth.layer_weights(cfg, 0, DEV, out_scale=0.1)
+    step = synth.decode_step(cfg, rows, ctx)
+    h = (torch.randn(rows, cfg.hidden, generator=torch.Generator().manual_seed(2)) * 0.25).bfloat16()
+    from sgl_amd_mono_b200.layer import MlaLayerOp
+
+    op = MlaLayerOp(cfg, w, DEV, max_ctx=-(-ctx // 64) * 64)
+    dstep = _step_to(step, DEV)
+    out = op.launch(h.to(DEV), dstep).clone()
+    torch.cuda.synchronize()
+    assert ops.guard_read(op.guard)[0] == 0
+    res = check_mla_layer(cfg, op, w, step, dstep, h, out, literal=True)
+    print("literal bar:", res["h1"], res["out"])
 
 
 def test_ties_go_to_the_lowest_position():

@@ -48,3 +48,19 @@ def assert_rel(got: torch.Tensor, ref: torch.Tensor, what: str = "", rel: float 
     e = (g - r).abs().max().item() / max(r.abs().max().item(), 1e-30)
     assert e <= rel, f"{what}: relative error {e:.3g} > {rel}"
     return e
+
+
+def assert_literal_bar(got: torch.Tensor, ref: torch.Tensor, what: str = "") -> dict:
+    """The tolerance exactly as stated: max-abs <= 2e-2 and cosine >= 0.999 (whole tensor and every
+    row), with no allowance for magnitude.  Meaningful for streams of unit scale (|x| < 2, where one
+    bf16 ulp is below 2e-2)."""
+    g, r = got.detach().float().cpu(), ref.detach().float().cpu()
+    assert g.shape == r.shape and torch.isfinite(g).all(), what
+    assert float(r.abs().max()) < 4.0, f"{what}: the literal bar is stated for unit-scale streams"
+    err = float((g - r).abs().max())
+    cos = F.cosine_similarity(g.reshape(-1), r.reshape(-1), dim=0).item()
+    assert err <= MAX_ABS, f"{what}: max-abs {err:.4g} > {MAX_ABS}"
+    assert cos >= MIN_COS, f"{what}: cosine {cos:.6f} < {MIN_COS}"
+    rows = F.cosine_similarity(g.reshape(-1, g.shape[-1]), r.reshape(-1, r.shape[-1]), dim=-1)
+    assert float(rows.min()) >= MIN_COS, f"{what}: min per-row cosine {float(rows.min()):.6f}"
+    return {"max_abs": err, "cos": cos}
