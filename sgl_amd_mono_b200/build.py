@@ -29,12 +29,17 @@ def sources() -> list[Path]:
     return sorted(CSRC.glob("*.cu"))
 
 
+def _flags() -> list[str]:
+    # MONO_TIMELINE=1: kernels record global-timer stamps at numbered points (csrc/mono_common.cuh)
+    return NVCC_FLAGS + (["-DMONO_TIMELINE"] if os.environ.get("MONO_TIMELINE") == "1" else [])
+
+
 def _digest() -> str:
     h = hashlib.sha256()
     for p in sources() + sorted(CSRC.glob("*.cuh")) + [PKG.parent / "include" / "mono_b200.h"]:
         h.update(p.name.encode())
         h.update(p.read_bytes())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(_flags()).encode())
     return h.hexdigest()
 
 
@@ -49,7 +54,7 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     procs = []
     for src in sources():
         obj = build_dir / (src.stem + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+        cmd = [nvcc, *_flags(), "-c", str(src), "-o", str(obj)]
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
         objs.append(obj)
     log = []

@@ -269,6 +269,24 @@ __device__ __forceinline__ float ld_cg_f32(const float* p) {
 
 }  // namespace mono
 
+// ------------------------------------------------------------------ timeline stamps
+// Built with -DMONO_TIMELINE (MONO_TIMELINE=1 in the environment of the build script), a kernel records the
+// global timer at numbered points, per CTA, into a per-file device array that mono_timeline_read copies out
+// (the reference's SGLANG_AMD_MONO_TIMELINE stamps: common/stamps.py:16-33, 48 points per CTA there).
+// Without the flag the macros expand to nothing.
+#ifdef MONO_TIMELINE
+#define MONO_TL_POINTS 16
+#define MONO_TL_CTAS 160
+#define MONO_TL_DECLARE(name) static __device__ unsigned long long name[MONO_TL_CTAS][MONO_TL_POINTS];
+#define MONO_TL(name, p)                                                                                         \
+    do {                                                                                                         \
+        if (threadIdx.x == 0 && blockIdx.x < MONO_TL_CTAS && (p) < MONO_TL_POINTS) name[blockIdx.x][p] = mono::globaltimer_ns(); \
+    } while (0)
+#else
+#define MONO_TL_DECLARE(name)
+#define MONO_TL(name, p) do { } while (0)
+#endif
+
 // Host side: one launch helper, with or without the programmatic-serialization attribute.
 #include <atomic>
 extern int g_mono_pdl;

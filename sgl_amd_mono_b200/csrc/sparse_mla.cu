@@ -10,6 +10,7 @@
 // all in flight at once, widens them to bf16 in shared memory, and runs Q.K^T and P.V on bf16
 // warp MMAs with the running maximum / sum and the output accumulators in registers, so a task
 // writes one partial however many chunks it covers (the reference writes one per 64 keys).
+#include <cstdlib>
 #include "mono_common.cuh"
 #include "act_quant.cuh"
 
@@ -228,7 +229,7 @@ __global__ void __launch_bounds__(kMlaThreads, 2) sparse_mla_split_kernel(const 
 // One CTA per (row, head): merge the splits.  With a destination in `q` the head's 512 merged values
 // (rounded to bf16, as they are stored) are also quantised in place as the W_UV GEMV's activation set of
 // that head: segment `head` of q.planes, four 128-value chunks, one warp each.
-__global__ void __launch_bounds__(256) sparse_mla_merge_kernel(const mono_sparse_mla_args a, int nsplit, const mono_act_prep_args q) {
+__global__ void __launch_bounds__(128) sparse_mla_merge_kernel(const mono_sparse_mla_args a, int nsplit, const mono_act_prep_args q) {
     pdl_prologue();
     __shared__ float w[128];
     __shared__ float merged[512];
@@ -237,16 +238,16 @@ __global__ void __launch_bounds__(256) sparse_mla_merge_kernel(const mono_sparse
     const float* part_ml = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(a.scratch) +
                                                           (size_t)a.rows * nsplit * a.heads * 512 * sizeof(__nv_bfloat16));
     const int tid = threadIdx.x;
-    const int col = 2 * tid;
-    // every thread requests its column pair of the first 32 partials before anything waits: the weights of
+    const int col = 4 * tid;
+    // every thread requests its four columns of the first 32 partials before anything waits: the weights of
     // the splits (warp 0) and the partials arrive in the same memory latency
     constexpr int kBatch = 32;
-    uint32_t pv[kBatch];
+    uint2 pv[kBatch];
 #pragma unroll
     for (int j = 0; j < kBatch; ++j) {
-        pv[j] = 0u;
+        pv[j] = make_uint2(0u, 0u);
         if (j < nsplit)
-            pv[j] = *reinterpret_cast<const uint32_t*>(part_acc + (((size_t)row * nsplit + j) * a.heads + head) * 512 + col);
+            pv[j] = __ldcg(reinterpret_cast<const uint2*>(part_acc + (((size_t)row * nsplit + j) * a.heads + head) * 512 + col));
     }
     if (tid < 32) {
         float mx = -INFINITY;
@@ -264,43 +265,56 @@ __global__ void __launch_bounds__(256) sparse_mla_merge_kernel(const mono_sparse
         for (int j = tid; j < nsplit; j += 32) w[j] = den > 0.f ? w[j] / den : 0.f;
     }
     __syncthreads();
-    float a0 = 0.f, a1 = 0.f;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    // a split without a live key has weight 0; whatever its accumulator holds must not reach the sum
+    auto add = [&](const uint2& v, float wj) {
+        if (wj == 0.f) return;
+        const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&v.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&v.y);
+        acc[0] += __low2float(lo) * wj;
+        acc[1] += __high2float(lo) * wj;
+        acc[2] += __low2float(hi) * wj;
+        acc[3] += __high2float(hi) * wj;
+    };
 #pragma unroll
-    for (int j = 0; j < kBatch; ++j) {
-        if (j < nsplit) {
-            const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&pv[j]);
-            a0 += __low2float(v) * w[j];
-            a1 += __high2float(v) * w[j];
-        }
-    }
+    for (int j = 0; j < kBatch; ++j)
+        if (j < nsplit) add(pv[j], w[j]);
 #pragma unroll 8
-    for (int j = kBatch; j < nsplit; ++j) {
-        const __nv_bfloat162 v =
-            *reinterpret_cast<const __nv_bfloat162*>(part_acc + (((size_t)row * nsplit + j) * a.heads + head) * 512 + col);
-        a0 += __low2float(v) * w[j];
-        a1 += __high2float(v) * w[j];
-    }
-    const __nv_bfloat162 o2 = __floats2bfloat162_rn(a0, a1);
-    *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(a.out) + ((size_t)row * a.heads + head) * 512 + col) = o2;
+    for (int j = kBatch; j < nsplit; ++j)
+        add(__ldcg(reinterpret_cast<const uint2*>(part_acc + (((size_t)row * nsplit + j) * a.heads + head) * 512 + col)), w[j]);
+    const __nv_bfloat162 o01 = __floats2bfloat162_rn(acc[0], acc[1]), o23 = __floats2bfloat162_rn(acc[2], acc[3]);
+    *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.out) + ((size_t)row * a.heads + head) * 512 + col) =
+        make_uint2(*reinterpret_cast<const uint32_t*>(&o01), *reinterpret_cast<const uint32_t*>(&o23));
     if (q.planes) {
-        merged[col] = __low2float(o2);
-        merged[col + 1] = __high2float(o2);
+        merged[col] = __low2float(o01);
+        merged[col + 1] = __high2float(o01);
+        merged[col + 2] = __low2float(o23);
+        merged[col + 3] = __high2float(o23);
         __syncthreads();
         const int warp = tid >> 5, lane = tid & 31;
-        if (warp < 4) {
-            uint8_t* p0 = q.planes + (size_t)head * q.seg_stride + (size_t)row * q.ld;
-            float* sf = q.scale_f32 ? q.scale_f32 + (size_t)head * q.scale_seg_stride + (size_t)row * q.scale_ld : nullptr;
-            uint8_t* s8 = q.scale_e8 ? q.scale_e8 + (size_t)head * q.scale_seg_stride + (size_t)row * q.scale_ld : nullptr;
-            quant_chunk128(merged + warp * 128, q.fmt, lane, warp, p0, p0 + q.plane_stride, sf, s8);
-        }
+        uint8_t* p0 = q.planes + (size_t)head * q.seg_stride + (size_t)row * q.ld;
+        float* sf = q.scale_f32 ? q.scale_f32 + (size_t)head * q.scale_seg_stride + (size_t)row * q.scale_ld : nullptr;
+        uint8_t* s8 = q.scale_e8 ? q.scale_e8 + (size_t)head * q.scale_seg_stride + (size_t)row * q.scale_ld : nullptr;
+        quant_chunk128(merged + warp * 128, q.fmt, lane, warp, p0, p0 + q.plane_stride, sf, s8);
     }
 }
 
 }  // namespace mono
 
+size_t mono_sparse_mla_tc_image_bytes(int rows);
+int mono_sparse_mla_tc_split(const mono_sparse_mla_args* a, int nchunks, cudaStream_t st);
+
+// From 64 local heads the split runs on tcgen05 with all heads of a row in one task (sparse_mla_tc.cu);
+// MONO_MLA_TC=0 keeps the warp-MMA split (one task per 16 heads) for A/B measurements.
+static bool mla_tc_wanted(int heads) {
+    const char* e = getenv("MONO_MLA_TC");  // read at every launch: a test switches it inside one process
+    return (e ? atoi(e) : 1) != 0 && heads >= 64;
+}
+
 extern "C" size_t mono_sparse_mla_scratch_bytes(int rows, int heads, int topk) {
     const size_t nsplit = (size_t)(topk + mono::kSplit - 1) / mono::kSplit;
-    return (size_t)rows * nsplit * heads * (512 * sizeof(__nv_bfloat16) + 2 * sizeof(float)) + 256;
+    size_t n = (size_t)rows * nsplit * heads * (512 * sizeof(__nv_bfloat16) + 2 * sizeof(float)) + 256;
+    if (heads >= 64) n = ((n + 1023) & ~size_t(1023)) + mono_sparse_mla_tc_image_bytes(rows);  // the query planes of the tcgen05 split
+    return n;
 }
 
 // (nsplit, chunks per task): about two rounds of the resident CTAs (2 per SM) over rows x head groups x chunks
@@ -342,6 +356,15 @@ static int sparse_mla_launch(const mono_sparse_mla_args* a, const mono_act_prep_
     }
     const int sms = mono_sm_count();
     int nsplit, chunks;
+    if (mla_tc_wanted(a->heads)) {
+        nsplit = (a->topk + mono::kSplit - 1) / mono::kSplit;
+        if (int rc = mono_sparse_mla_tc_split(a, nsplit, (cudaStream_t)stream)) return rc;
+        mono_act_prep_args none = {};
+        mono::launch_k(mono::sparse_mla_merge_kernel, a->rows * a->heads, 128, 0, (cudaStream_t)stream, *a, nsplit, dst ? *dst : none);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) mono_set_error("mono_sparse_mla_launch: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
     mla_plan(a->rows, a->heads, a->topk, sms, &nsplit, &chunks);
     const size_t smem = sizeof(mono::MlaSmem) + 128;
     static std::atomic<uint64_t> attr_once{0};  // bit d: set on device d
@@ -357,7 +380,7 @@ static int sparse_mla_launch(const mono_sparse_mla_args* a, const mono_act_prep_
     if (grid > 2 * sms) grid = 2 * sms;
     mono::launch_k(mono::sparse_mla_split_kernel, grid, mono::kMlaThreads, smem, (cudaStream_t)stream, *a, nsplit, chunks);
     mono_act_prep_args none = {};
-    mono::launch_k(mono::sparse_mla_merge_kernel, a->rows * a->heads, 256, 0, (cudaStream_t)stream, *a, nsplit, dst ? *dst : none);
+    mono::launch_k(mono::sparse_mla_merge_kernel, a->rows * a->heads, 128, 0, (cudaStream_t)stream, *a, nsplit, dst ? *dst : none);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_sparse_mla_launch: %s", cudaGetErrorString(e));
     return (int)e;
@@ -455,7 +478,7 @@ extern "C" int mono_sparse_mla_launch_noalloc(const mono_sparse_mla_args* a, voi
     // written by this call's split kernel first (same stream, so in order).
     mono::sparse_mla_split_kernel<<<grid, mono::kMlaThreads, smem, (cudaStream_t)stream>>>(args, nsplit, chunks);
     mono_act_prep_args none = {};
-    mono::sparse_mla_merge_kernel<<<args.rows * args.heads, 256, 0, (cudaStream_t)stream>>>(args, nsplit, none);
+    mono::sparse_mla_merge_kernel<<<args.rows * args.heads, 128, 0, (cudaStream_t)stream>>>(args, nsplit, none);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_sparse_mla_launch_noalloc: %s", cudaGetErrorString(e));
     return (int)e;

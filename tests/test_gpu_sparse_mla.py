@@ -92,3 +92,24 @@ def test_merge_stages_the_heads_for_the_next_gemv(fmt_name):
         assert (a is None) == (b is None)
         if a is not None:
             assert torch.equal(a, b) and bool(b.any())
+
+
+@pytest.mark.parametrize("rows,heads,ctx,topk", [(2, 128, 700, 320), (8, 128, 16384, 2048), (3, 64, 5000, 2048),
+                                                 (1, 96, 300, 256), (6, 64, 8192, 8192)])
+def test_tcgen05_split_matches_oracle_and_the_warp_mma_split(rows, heads, ctx, topk, monkeypatch):
+    """From 64 local heads the split runs on tcgen05 with every head of a row in one task (cache rows kept as
+    E4M3, queries and probabilities as exact hi / lo E4M3 planes).  Same tolerance against the oracle as the
+    warp-MMA split, and the two splits agree to a few bf16 ulps of the largest output."""
+    def edit(q, pages, sel):
+        sel[0, 7] = -1  # an invalid entry mid-list
+        if rows > 1:
+            sel[1, topk // 3:] = -1  # a short row: whole chunks without a key
+
+    monkeypatch.setenv("MONO_MLA_TC", "1")
+    q, pages, sel, out_tc, _ = _run(rows, heads, ctx, topk, seed=7, edit=edit)
+    monkeypatch.setenv("MONO_MLA_TC", "0")
+    _, _, _, out_mma, _ = _run(rows, heads, ctx, topk, seed=7, edit=edit)
+    ref = S.sparse_mla(q, pages, sel, SCALE)
+    print("tcgen05:", assert_close_hidden(out_tc, ref, "tcgen05 split"), "warp MMA:", assert_close_hidden(out_mma, ref, "warp-MMA split"))
+    d = float((out_tc.float() - out_mma.float()).abs().max())
+    assert d <= 2.0**-6 * float(ref.float().abs().max()) + 1e-3, f"the two splits differ by {d}"
