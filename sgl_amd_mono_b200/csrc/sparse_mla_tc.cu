@@ -36,7 +36,9 @@ constexpr int kQBytes = 2 * kQPlaneBytes;        // hi and lo planes
 constexpr int kKvBlockBytes = kKeys * 128;       // [64 keys][128 B]
 constexpr int kKvBytes = kBlocks * kKvBlockBytes;
 constexpr int kRowImage = kQBytes + 128 * 4;     // the planes, then one f32 scale per head
-constexpr int kSmemBytes = 1024 + kQBytes + kKvBytes;
+constexpr int kStagePitch = 80;                  // bytes per staged row of 32 bf16 values: conflict-free 16-byte accesses
+constexpr int kStageBytes = 8 * 32 * kStagePitch;  // one tile of 32 heads x 32 columns per warp
+constexpr int kSmemBytes = 1024 + kQBytes + kKvBytes + kStageBytes;
 constexpr int kTmemCols = 512;
 
 // ---- tcgen05 wrappers (one CTA per MMA group)
@@ -87,10 +89,12 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
 __device__ __forceinline__ void split16(const float v[16], float inv, uint4* hi, uint4* lo) {
     uint32_t h[4] = {0, 0, 0, 0}, l[4] = {0, 0, 0, 0};
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        const float sv = v[i] * inv;
-        const uint8_t hb = f32_to_e4m3(sv);
-        const uint8_t lb = f32_to_e4m3(sv - e4m3_to_f32(hb));
+    for (int i = 0; i < 16; i += 2) {
+        const float2 sv = make_float2(v[i] * inv, v[i + 1] * inv);
+        const __nv_fp8x2_storage_t hb = __nv_cvt_float2_to_fp8x2(sv, __NV_SATFINITE, __NV_E4M3);
+        const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(hb, __NV_E4M3);
+        const float2 hf = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+        const __nv_fp8x2_storage_t lb = __nv_cvt_float2_to_fp8x2(make_float2(sv.x - hf.x, sv.y - hf.y), __NV_SATFINITE, __NV_E4M3);
         h[i >> 2] |= (uint32_t)hb << (8 * (i & 3));
         l[i >> 2] |= (uint32_t)lb << (8 * (i & 3));
     }
@@ -151,7 +155,8 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_split_tc_kernel(const 
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* qbuf = smem;             // the query planes; the probability planes reuse its first 32 KB
     uint8_t* kvbuf = smem + kQBytes;  // the chunk's cache rows
-    __shared__ float s_kscale[kKeys], s_qscale[128], s_prow[128];
+    uint8_t* stage = kvbuf + kKvBytes;  // the epilogue's transposition tiles
+    __shared__ float s_kscale[kKeys], s_qscale[128], s_prow[128], s_x[2][128];
     __shared__ int s_slot[kKeys];
     __shared__ uint64_t bar_q, bar_mma;
     __shared__ uint32_t tmem_base_s;
@@ -182,8 +187,21 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_split_tc_kernel(const 
     const int t0 = (int)((long)blockIdx.x * total / gridDim.x), t1 = (int)((long)(blockIdx.x + 1) * total / gridDim.x);
     // Requests what `task` needs (query planes or the part of them that was overwritten, the chunk's slots and key
     // scales, the chunk's cache rows) without waiting for any of it; `have_row` is the row whose planes are resident.
-    auto request = [&](int task, int have_row) -> bool {
+    // a chunk's slot and key scale for thread tid < 64 (two dependent loads: asked for a task ahead)
+    auto slot_of = [&](int task, int* slot_out, float* scale_out) {
         const int row = task / nchunks, chunk = task - row * nchunks;
+        const int kidx = chunk * kKeys + tid;
+        int slot = kidx < a.topk ? a.topk_slots[(size_t)row * a.topk_ld + kidx] : -1;
+        if (slot >= 0 && (int64_t)slot >= a.n_pages * kPage) slot = -1;
+        float sc = 0.f;
+        if (slot >= 0) sc = __ldg(reinterpret_cast<const float*>(a.kv_pages + (size_t)(slot / kPage) * kKvPageBytes + kPage * kKvDim) + slot % kPage);
+        *slot_out = slot;
+        *scale_out = sc;
+    };
+    int pre_slot = -1;
+    float pre_scale = 0.f;
+    auto request = [&](int task, int have_row) -> bool {
+        const int row = task / nchunks;
         const bool full = row != have_row;
         if (tid == 0) {
             const uint8_t* src = image + (size_t)row * kRowImage;
@@ -193,13 +211,8 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_split_tc_kernel(const 
             for (int i = 0; i < nblk; ++i) bulk_load(qbuf + i * kQBlockBytes, src + (size_t)i * kQBlockBytes, kQBlockBytes, &bar_q);
         }
         if (tid < kKeys) {
-            const int kidx = chunk * kKeys + tid;
-            int slot = kidx < a.topk ? a.topk_slots[(size_t)row * a.topk_ld + kidx] : -1;
-            if (slot >= 0 && (int64_t)slot >= a.n_pages * kPage) slot = -1;
-            s_slot[tid] = slot;
-            float sc = 0.f;
-            if (slot >= 0) sc = __ldg(reinterpret_cast<const float*>(a.kv_pages + (size_t)(slot / kPage) * kKvPageBytes + kPage * kKvDim) + slot % kPage);
-            s_kscale[tid] = sc;
+            s_slot[tid] = pre_slot;
+            s_kscale[tid] = pre_scale;
         } else if (tid >= 128 && full) {
             s_qscale[tid - 128] = reinterpret_cast<const float*>(image + (size_t)row * kRowImage + kQBytes)[tid - 128];
         }
@@ -223,6 +236,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_split_tc_kernel(const 
         return true;
     };
     MONO_TL(tl_split, 0);
+    if (t0 < t1 && tid < kKeys) slot_of(t0, &pre_slot, &pre_scale);
     if (t0 < t1 && !*abortp) request(t0, -1);
     for (int task = t0; task < t1 && !*abortp; ++task) {
         const int row = task / nchunks, chunk = task - row * nchunks;
@@ -233,22 +247,23 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_split_tc_kernel(const 
         if (!mbar_wait(&bar_q, qph, abortp)) break;
         qph ^= 1;
         __syncthreads();
+        if (task + 1 < t1 && tid < kKeys) slot_of(task + 1, &pre_slot, &pre_scale);  // in flight during this task's products
         MONO_TL(tl_split, tl);
         // ---- S = Q K^T: hi and lo planes, five blocks, 32 bytes of the contraction per MMA
         if (tid == 0) {
             fence_after();
+            // the hi and the lo plane accumulate in columns 0..63 and 64..127: two independent chains of MMAs
             uint32_t acc = 0;
 #pragma unroll 1
-            for (int pl = 0; pl < 2; ++pl) {
-#pragma unroll 1
-                for (int blk = 0; blk < kBlocks; ++blk) {
-                    const uint64_t ad = desc_sw128(q_addr + pl * kQPlaneBytes + blk * kQBlockBytes, 0, 1024);
-                    const uint64_t bd = desc_sw128(kv_addr + blk * kKvBlockBytes, 0, 1024);
-                    const int steps = blk < 4 ? 4 : 2;
-                    for (int k = 0; k < steps; ++k) {
-                        mma_f8(tmem_base, ad + 2 * k, bd + 2 * k, kIdescS, acc);
-                        acc = 1;
-                    }
+            for (int blk = 0; blk < kBlocks; ++blk) {
+                const uint64_t ah = desc_sw128(q_addr + blk * kQBlockBytes, 0, 1024);
+                const uint64_t al = desc_sw128(q_addr + kQPlaneBytes + blk * kQBlockBytes, 0, 1024);
+                const uint64_t bd = desc_sw128(kv_addr + blk * kKvBlockBytes, 0, 1024);
+                const int steps = blk < 4 ? 4 : 2;
+                for (int k = 0; k < steps; ++k) {
+                    mma_f8(tmem_base, ah + 2 * k, bd + 2 * k, kIdescS, acc);
+                    mma_f8(tmem_base + 64, al + 2 * k, bd + 2 * k, kIdescS, acc);
+                    acc = 1;
                 }
             }
             mma_commit(&bar_mma);
@@ -257,45 +272,52 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_split_tc_kernel(const 
         mph ^= 1;
         fence_after();
         MONO_TL(tl_split, tl + 1);
-        // ---- softmax over the chunk: thread = head (TMEM lane), warps 0..3
-        if (warp < 4) {
-            const int head = tid;
-            uint32_t raw[32];
-            float s[kKeys];
+        // ---- softmax over the chunk: head = TMEM lane; warps w and w + 4 share a lane quarter and take 32 keys each
+        {
+            const int head = (warp & 3) * 32 + lane, kh = warp >> 2;  // kh: which half of the keys
+            uint32_t raw[32], raw_lo[32];
+            float s[32];
             const float qs = s_qscale[head] * a.sm_scale;
+            tmem_ld32(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + kh * 32, raw);
+            tmem_ld32(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + 64 + kh * 32, raw_lo);
+            float mloc = -INFINITY;
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + half * 32, raw);
-#pragma unroll
-                for (int k = 0; k < 32; ++k) {
-                    const int key = half * 32 + k;
-                    s[key] = s_slot[key] >= 0 ? __uint_as_float(raw[k]) * (qs * s_kscale[key]) : -INFINITY;
-                }
+            for (int k = 0; k < 32; ++k) {
+                const int key = kh * 32 + k;
+                s[k] = s_slot[key] >= 0 ? (__uint_as_float(raw[k]) + __uint_as_float(raw_lo[k])) * (qs * s_kscale[key]) : -INFINITY;
+                mloc = fmaxf(mloc, s[k]);
             }
-            float m = -INFINITY;
-#pragma unroll
-            for (int k = 0; k < kKeys; ++k) m = fmaxf(m, s[k]);
+            s_x[kh][head] = mloc;
+            __syncthreads();
+            const float m = fmaxf(s_x[0][head], s_x[1][head]);
             float l = 0.f, amax = 0.f;
 #pragma unroll
-            for (int k = 0; k < kKeys; ++k) {
+            for (int k = 0; k < 32; ++k) {
                 const float p = (m == -INFINITY) ? 0.f : __expf(s[k] - m);
                 l += p;
                 // the probability as the reference feeds it to P.V (rounded to bf16), times the key's scale
-                s[k] = bf16_round(p) * s_kscale[k];
+                s[k] = bf16_round(p) * s_kscale[kh * 32 + k];
                 amax = fmaxf(amax, s[k]);
             }
+            __syncthreads();  // both halves have read the maxima
+            s_x[kh][head] = amax;
+            if (kh == 1) s_prow[head] = l;  // the upper half's sum, on its way to the lower half's thread
+            __syncthreads();
+            amax = fmaxf(s_x[0][head], s_x[1][head]);
             const int code = code_ceil(fmaxf(amax, 7.888609052210118e-31f) / 448.f);
             const float inv = exp2_code(254 - code);
-            s_prow[head] = exp2_code(code);
+            if (kh == 0) l += s_prow[head];
+            __syncthreads();  // the sums have been taken before the slot gets the row's scale
+            if (kh == 0) s_prow[head] = exp2_code(code);
 #pragma unroll
-            for (int c = 0; c < kKeys / 16; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 uint4 hi, lo;
                 split16(&s[c * 16], inv, &hi, &lo);
-                const uint32_t dst = q_addr + head * 128 + ((c ^ (head & 7)) << 4);
+                const uint32_t dst = q_addr + head * 128 + (((kh * 2 + c) ^ (head & 7)) << 4);
                 asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w) : "memory");
                 asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + kQBlockBytes), "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w) : "memory");
             }
-            if (head < a.heads) {
+            if (kh == 0 && head < a.heads) {
                 float* ml = part_ml + (((size_t)row * nchunks + chunk) * a.heads + head) * 2;
                 ml[0] = m;
                 ml[1] = l;
@@ -331,27 +353,36 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_split_tc_kernel(const 
         // both products are done with shared memory: the next task's operands travel during this task's epilogue
         if (task + 1 < t1) request(task + 1, row);
         MONO_TL(tl_split, tl + 4);
-        // ---- the task's partial: warp w holds lanes 32 (w % 4) .., columns 256 (w / 4) ..
+        // ---- the task's partial: warp w holds lanes 32 (w % 4) .., columns 256 (w / 4) ..  A thread's 32 columns of a
+        // head are 64 bytes of that head's row; the warp transposes its 32 x 64 B tile through shared memory so that four
+        // lanes write one head's 64 bytes together (eight full half-lines per store instead of 32 quarter-filled sectors)
         {
-            const int head = (warp & 3) * 32 + lane, col0 = (warp >> 2) * 256;
-            const float sc = s_prow[head];
-            __nv_bfloat16* dst = part_acc + (((size_t)row * nchunks + chunk) * a.heads + head) * 512 + col0;
+            const int hq = (warp & 3) * 32, col0 = (warp >> 2) * 256;
+            const float sc = s_prow[hq + lane];
+            uint8_t* tile = stage + warp * 32 * kStagePitch;
+            __nv_bfloat16* dst0 = part_acc + (((size_t)row * nchunks + chunk) * a.heads + hq) * 512 + col0;
 #pragma unroll 1
             for (int c = 0; c < 256; c += 32) {
                 uint32_t raw[32];
-                tmem_ld32(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + col0 + c, raw);
-                if (head < a.heads) {
+                tmem_ld32(tmem_base + ((uint32_t)hq << 16) + col0 + c, raw);
 #pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        uint32_t w[4];
+                for (int i = 0; i < 32; i += 8) {
+                    uint32_t w[4];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(raw[i + 2 * j]) * sc, __uint_as_float(raw[i + 2 * j + 1]) * sc);
-                            w[j] = *reinterpret_cast<const uint32_t*>(&b);
-                        }
-                        *reinterpret_cast<uint4*>(dst + c + i) = make_uint4(w[0], w[1], w[2], w[3]);
+                    for (int j = 0; j < 4; ++j) {
+                        const __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(raw[i + 2 * j]) * sc, __uint_as_float(raw[i + 2 * j + 1]) * sc);
+                        w[j] = *reinterpret_cast<const uint32_t*>(&b);
                     }
+                    *reinterpret_cast<uint4*>(tile + lane * kStagePitch + i * 2) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
+                __syncwarp();
+#pragma unroll
+                for (int pass = 0; pass < 4; ++pass) {
+                    const int r = pass * 8 + (lane >> 2), piece = lane & 3;
+                    const uint4 v = *reinterpret_cast<const uint4*>(tile + r * kStagePitch + piece * 16);
+                    if (hq + r < a.heads) *reinterpret_cast<uint4*>(dst0 + (size_t)r * 512 + c + piece * 8) = v;
+                }
+                __syncwarp();
             }
         }
         fence_before();
