@@ -801,10 +801,9 @@ class StackWorkload:
     def _eager(self):
         st = self.stack
         st.draft.launch(self.hd, self.draft_tables)
-        x = self.h
-        for op, t in zip(st.layers, self.tables):
-            x = op.launch(x, t)
-        self.logits = st.head(x)
+        x = st.run_layers(self.h, self.tables)
+        pending = isinstance(x, self.ops.PendingReduce)
+        self.logits = st.head(None, pending=x) if pending else st.head(x)
         self.ops.epoch_advance(st.guard)
 
     def step(self):

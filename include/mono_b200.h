@@ -366,6 +366,14 @@ typedef struct mono_reduce_args {
 } mono_reduce_args;
 size_t mono_reduce_peer_bytes(int rows, int n, int world);
 int mono_reduce_launch(const mono_reduce_args* a, void* stream);
+/* The reduction above and the activation staging of mono_act_prep_launch in ONE launch (the reference runs
+ * the all-reduce, the residual add and the next RMSNorm staging inside one kernel too: glm53/gfx950/kernel.py
+ * :4125-4330): `r` as for mono_reduce_launch (its output, the new residual stream, is still written to r->out);
+ * `a` describes the norm and the quantised planes made from that output (a->rows == r->rows, a->k == r->n,
+ * no segments; a->src_* are not read).  r->out gets the bits of mono_reduce_launch.  A cluster of up to eight
+ * CTAs serves a row and adds its sum of squares in CTA order, so the normalised values may differ from
+ * mono_act_prep_launch's in the last bit of the f32 reciprocal root. */
+int mono_reduce_norm_launch(const mono_reduce_args* r, const struct mono_act_prep_args* a, void* stream);
 /* Adds 1 to the epoch word on the device (glm53/gfx950/runner.py:209-210 advance_step). */
 int mono_epoch_advance_launch(int32_t* guard, void* stream);
 

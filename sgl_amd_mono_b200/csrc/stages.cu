@@ -5,6 +5,7 @@
 // Reference counterparts: glm53/gfx950/kernel.py:1367-1414 (RMSNorm staging),
 // :1440-1466 (quant_scaled / quant_mxfp8), :1575-1629 (route_top8), :4396-4415 (SiLU),
 // :1631-1688 (peer_reduce); minimax_m31/ffn.py:601-723 (router).
+#include <cooperative_groups.h>
 #include <cstdlib>
 #include "mono_common.cuh"
 #include "act_quant.cuh"
@@ -18,37 +19,10 @@ namespace mono {
 // quantised one 128-chunk per warp.
 constexpr int kPrepThreads = 1024;
 
-__global__ void __launch_bounds__(kPrepThreads) act_prep_kernel(const mono_act_prep_args a) {
-    pdl_launch_dependents();
-    prefetch_span(a.gamma_bf16, (size_t)a.k * 2, threadIdx.x, kPrepThreads);  // the norm weights, during the wait
-    pdl_wait();
-    extern __shared__ float xrow[];
-    __shared__ float red[kPrepThreads / 32];
-    const int segs = a.segs > 1 ? a.segs : 1;
-    const int row = blockIdx.x / segs, seg = blockIdx.x - row * segs, tid = threadIdx.x;
-    // four values per thread per pass, every load of a pass issued before it is used:
-    // the row arrives in one or two memory latencies instead of one per element
-    float ssq = 0.f;
-    for (int i = tid * 4; i < a.k; i += kPrepThreads * 4) {
-        float4 v;
-        if (a.src_bf16) {
-            const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.src_bf16) +
-                                                              ((size_t)row * segs + seg) * a.k + i);
-            const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-            const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-            v = make_float4(lo.x, lo.y, hi.x, hi.y);
-        } else {
-            v = make_float4(0.f, 0.f, 0.f, 0.f);
-            const float* src = a.src_f32 + (size_t)row * a.src_ld + (size_t)seg * a.k + i;
-#pragma unroll 4
-            for (int s = 0; s < a.nsum; ++s) {
-                const float4 p = *reinterpret_cast<const float4*>(src + (size_t)s * a.src_sum_stride);
-                v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
-            }
-        }
-        *reinterpret_cast<float4*>(xrow + i) = v;
-        ssq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-    }
+// The part of the staging after a row is in shared memory as f32 (and `ssq` holds this thread's share of its
+// sum of squares): RMSNorm, bf16 rounding, the plain bf16 copy, the quantised planes.
+__device__ __forceinline__ void prep_tail(const mono_act_prep_args& a, int row, int seg, int segs, float* xrow, float* red, float ssq) {
+    const int tid = threadIdx.x;
     if (a.gamma_bf16) {
         const __nv_bfloat16* gm = reinterpret_cast<const __nv_bfloat16*>(a.gamma_bf16);
         uint2 graw[4];  // gamma is fetched before the reduction so that its latency hides behind it
@@ -87,6 +61,40 @@ __global__ void __launch_bounds__(kPrepThreads) act_prep_kernel(const mono_act_p
         uint8_t* s8 = a.scale_e8 ? a.scale_e8 + (size_t)seg * a.scale_seg_stride + (size_t)row * a.scale_ld : nullptr;
         for (int c = warp; c < a.k / 128; c += kPrepThreads / 32) quant_chunk128(xrow + c * 128, a.fmt, lane, c, p0, p1, sf, s8);
     }
+}
+
+__global__ void __launch_bounds__(kPrepThreads) act_prep_kernel(const mono_act_prep_args a) {
+    pdl_launch_dependents();
+    prefetch_span(a.gamma_bf16, (size_t)a.k * 2, threadIdx.x, kPrepThreads);  // the norm weights, during the wait
+    pdl_wait();
+    extern __shared__ float xrow[];
+    __shared__ float red[kPrepThreads / 32];
+    const int segs = a.segs > 1 ? a.segs : 1;
+    const int row = blockIdx.x / segs, seg = blockIdx.x - row * segs, tid = threadIdx.x;
+    // four values per thread per pass, every load of a pass issued before it is used:
+    // the row arrives in one or two memory latencies instead of one per element
+    float ssq = 0.f;
+    for (int i = tid * 4; i < a.k; i += kPrepThreads * 4) {
+        float4 v;
+        if (a.src_bf16) {
+            const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.src_bf16) +
+                                                              ((size_t)row * segs + seg) * a.k + i);
+            const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+            const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+            v = make_float4(lo.x, lo.y, hi.x, hi.y);
+        } else {
+            v = make_float4(0.f, 0.f, 0.f, 0.f);
+            const float* src = a.src_f32 + (size_t)row * a.src_ld + (size_t)seg * a.k + i;
+#pragma unroll 4
+            for (int s = 0; s < a.nsum; ++s) {
+                const float4 p = *reinterpret_cast<const float4*>(src + (size_t)s * a.src_sum_stride);
+                v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+            }
+        }
+        *reinterpret_cast<float4*>(xrow + i) = v;
+        ssq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    prep_tail(a, row, seg, segs, xrow, red, ssq);
 }
 
 // ------------------------------------------------------------------ router
@@ -509,6 +517,133 @@ __global__ void __launch_bounds__(kReduceThreads) reduce_kernel(const mono_reduc
     }
 }
 
+// The reduction of reduce_kernel and the staging of act_prep_kernel in one launch.  A cluster of C CTAs serves a
+// row, CTA c its columns [c k / C, (c + 1) k / C): the partial slices are added in order, rounded to bf16, all-reduced
+// over the ranks (pushes, bounded polls, sum in rank order), the residual is added and the bf16 result is written to
+// r.out (element for element the arithmetic of reduce_kernel: same bits).  The same values then go through the norm
+// and the quantisation of `a` (whose source fields are not read); the row's sum of squares is the C CTAs' sums added
+// in CTA order, exchanged over distributed shared memory.  A thread waits for other GPUs' words only, and every
+// CTA reaches both cluster barriers whatever its polls returned.
+constexpr int kRnThreads = 256;
+
+template <int C>
+__global__ void __cluster_dims__(C, 1, 1) __launch_bounds__(kRnThreads) reduce_norm_kernel(const mono_reduce_args r, const mono_act_prep_args a) {
+    namespace cg = cooperative_groups;
+    pdl_launch_dependents();
+    cg::cluster_group cluster = cg::this_cluster();
+    const int row = blockIdx.x / C, crank = (int)cluster.block_rank(), tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kc = a.k / C, col0 = crank * kc;  // this CTA's columns (a multiple of 128)
+    const int pairs = r.n / 2;
+    if (a.gamma_bf16) prefetch_span(reinterpret_cast<const __nv_bfloat16*>(a.gamma_bf16) + col0, (size_t)kc * 2, tid, kRnThreads);
+    if (r.residual) prefetch_span(reinterpret_cast<const __nv_bfloat16*>(r.residual) + (size_t)row * r.n + col0, (size_t)kc * 2, tid, kRnThreads);
+    pdl_wait();
+    extern __shared__ float xrow[];  // kc values
+    __shared__ float red[kRnThreads / 32];
+    __shared__ float cl_ssq;
+    uint32_t tag = r.tag;
+    int parity = r.parity;
+    if (r.world > 1 && r.guard && tag == 0) {
+        const int epoch = reinterpret_cast<const volatile int*>(r.guard)[MONO_GUARD_EPOCH];
+        tag = (uint32_t)epoch * 256u + (uint32_t)r.site + 1u;
+        parity = epoch & 1;
+    }
+    const bool live = !r.slots || r.slots[row] >= 0;
+    const uint64_t t0 = r.world > 1 ? globaltimer_ns() : 0;
+    const size_t slot_pairs = (size_t)kMaxRows * pairs;
+    float ssq = 0.f;
+    for (int li = tid * 4; li < kc; li += kRnThreads * 4) {
+        const int i = col0 + li;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (live) {
+            const float* src = r.partial + (size_t)row * r.ld + i;
+            for (int s0 = 0; s0 < r.nsum; s0 += 8) {  // eight slices' loads in flight, added in slice order
+                float4 p[8];
+#pragma unroll
+                for (int s = 0; s < 8; ++s)
+                    p[s] = s0 + s < r.nsum ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)(s0 + s) * r.sum_stride)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int s = 0; s < 8; ++s)
+                    if (s0 + s < r.nsum) { v.x += p[s].x; v.y += p[s].y; v.z += p[s].z; v.w += p[s].w; }
+            }
+        }
+        const __nv_bfloat162 pb0 = __floats2bfloat162_rn(v.x, v.y), pb1 = __floats2bfloat162_rn(v.z, v.w);
+        float acc[4];
+        if (r.world > 1) {
+            const int pc = i >> 1;  // this thread's two pairs: pc, pc + 1
+            const size_t my_off = (((size_t)parity * r.world + r.rank) * slot_pairs + (size_t)row * pairs + pc) * 8;
+            const uint32_t w0 = *reinterpret_cast<const uint32_t*>(&pb0), w1 = *reinterpret_cast<const uint32_t*>(&pb1);
+            for (int d = 0; d < r.world; ++d) {
+                st_sys_v2(r.peer_ptrs[d] + my_off, w0, tag);
+                st_sys_v2(r.peer_ptrs[d] + my_off + 8, w1, tag);
+            }
+            acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+            const uint64_t mine = r.peer_ptrs[r.rank];
+            bool failed = guard_failed(r.guard);
+            for (int src = 0; src < r.world && !failed; ++src) {
+                const uint64_t addr = mine + (((size_t)parity * r.world + src) * slot_pairs + (size_t)row * pairs + pc) * 8;
+                const uint2 x0 = poll_tagged(addr, tag, r.guard, r.peer_guards, r.world, r.rank, r.site, r.deadline_ns, t0, &failed);
+                if (failed) break;
+                const uint2 x1 = poll_tagged(addr + 8, tag, r.guard, r.peer_guards, r.world, r.rank, r.site, r.deadline_ns, t0, &failed);
+                if (failed) break;
+                const __nv_bfloat162 b0 = *reinterpret_cast<const __nv_bfloat162*>(&x0.x), b1 = *reinterpret_cast<const __nv_bfloat162*>(&x1.x);
+                acc[0] += __low2float(b0); acc[1] += __high2float(b0);
+                acc[2] += __low2float(b1); acc[3] += __high2float(b1);
+            }
+        } else {
+            acc[0] = __low2float(pb0); acc[1] = __high2float(pb0);
+            acc[2] = __low2float(pb1); acc[3] = __high2float(pb1);
+        }
+        if (r.residual) {
+            const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(r.residual) + (size_t)row * r.n + i);
+            const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+            const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+            acc[0] += lo.x; acc[1] += lo.y; acc[2] += hi.x; acc[3] += hi.y;
+        }
+        const __nv_bfloat162 o0 = __floats2bfloat162_rn(acc[0], acc[1]), o1 = __floats2bfloat162_rn(acc[2], acc[3]);
+        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(r.out) + (size_t)row * r.n + i) =
+            make_uint2(*reinterpret_cast<const uint32_t*>(&o0), *reinterpret_cast<const uint32_t*>(&o1));
+        const float4 h = make_float4(__low2float(o0), __high2float(o0), __low2float(o1), __high2float(o1));
+        *reinterpret_cast<float4*>(xrow + li) = h;
+        ssq += h.x * h.x + h.y * h.y + h.z * h.z + h.w * h.w;
+    }
+    // ---- the row's sum of squares: this CTA's share, then the C shares in CTA order
+    const float mine_ssq = block_sum<kRnThreads / 32>(ssq, red);
+    if (tid == 0) cl_ssq = mine_ssq;
+    cluster.sync();
+    float rstd = 1.f;
+    if (a.gamma_bf16) {
+        float tot = 0.f;
+#pragma unroll
+        for (int c = 0; c < C; ++c) tot += *cluster.map_shared_rank(&cl_ssq, c);
+        rstd = rsqrtf(tot / (float)a.k + a.eps);
+    }
+    for (int li = tid * 4; li < kc; li += kRnThreads * 4) {
+        float4 v = *reinterpret_cast<float4*>(xrow + li);
+        if (a.gamma_bf16) {
+            const uint2 graw = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.gamma_bf16) + col0 + li));
+            const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&graw.x));
+            const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&graw.y));
+            v.x = v.x * rstd * lo.x; v.y = v.y * rstd * lo.y; v.z = v.z * rstd * hi.x; v.w = v.w * rstd * hi.y;
+        }
+        if (a.round_bf16) { v.x = bf16_round(v.x); v.y = bf16_round(v.y); v.z = bf16_round(v.z); v.w = bf16_round(v.w); }
+        *reinterpret_cast<float4*>(xrow + li) = v;
+        if (a.out_bf16) {
+            const __nv_bfloat162 b0 = __floats2bfloat162_rn(v.x, v.y), b1 = __floats2bfloat162_rn(v.z, v.w);
+            *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.out_bf16) + (size_t)row * a.k + col0 + li) =
+                make_uint2(*reinterpret_cast<const uint32_t*>(&b0), *reinterpret_cast<const uint32_t*>(&b1));
+        }
+    }
+    __syncthreads();
+    if (a.planes) {
+        uint8_t* p0 = a.planes + (size_t)row * a.ld;
+        uint8_t* p1 = p0 + a.plane_stride;
+        float* sf = a.scale_f32 ? a.scale_f32 + (size_t)row * a.scale_ld : nullptr;
+        uint8_t* s8 = a.scale_e8 ? a.scale_e8 + (size_t)row * a.scale_ld : nullptr;
+        for (int c = warp; c < kc / 128; c += kRnThreads / 32) quant_chunk128(xrow + c * 128, a.fmt, lane, col0 / 128 + c, p0, p1, sf, s8);
+    }
+    cluster.sync();  // no CTA leaves while another may still read its sum
+}
+
 __global__ void epoch_advance_kernel(int32_t* guard) {
     pdl_prologue();
     guard[MONO_GUARD_EPOCH] += 1;
@@ -710,6 +845,53 @@ extern "C" int mono_reduce_launch(const mono_reduce_args* a, void* stream) {
     mono::launch_k(mono::reduce_kernel, grid, mono::kReduceThreads, 0, (cudaStream_t)stream, *a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_reduce_launch: %s", cudaGetErrorString(e));
+    return (int)e;
+}
+
+static int reduce_args_check(const mono_reduce_args* a, const char* who) {
+    if (!a || a->rows < 1 || a->rows > MONO_MAX_ROWS || a->n < 2 || (a->n & 1) || !a->partial || !a->out || a->nsum < 1 || (a->ld & 1)) {
+        mono_set_error("%s: rows 1..16, even n and ld, partial and out required", who);
+        return MONO_E_ARG;
+    }
+    if (a->world > 1 && (!a->peer_ptrs || a->rank < 0 || a->rank >= a->world || a->world > 8 || a->deadline_ns == 0 ||
+                         (a->tag == 0 && !a->guard) || a->site < 0 || a->site > 254)) {
+        mono_set_error("%s: world %d needs peer_ptrs, a rank, a deadline, a site in 0..254 and a tag or guard words", who, a->world);
+        return MONO_E_ARG;
+    }
+    return 0;
+}
+
+extern "C" int mono_reduce_norm_launch(const mono_reduce_args* r, const mono_act_prep_args* a, void* stream) {
+    if (int rc = reduce_args_check(r, "mono_reduce_norm_launch")) return rc;
+    if (!a || a->rows != r->rows || a->k != r->n || a->k < 128 || (a->k & 127) || a->k > 16384 || a->segs > 1 || (r->ld & 3) ||
+        (reinterpret_cast<uintptr_t>(r->partial) & 15) || (reinterpret_cast<uintptr_t>(r->out) & 7) ||
+        (r->residual && (reinterpret_cast<uintptr_t>(r->residual) & 7))) {
+        mono_set_error("mono_reduce_norm_launch: the staging must take the reduction's rows (same rows, k = n a multiple of 128 up to "
+                       "16384, no segments, ld a multiple of 4, 16-byte aligned partial sums)");
+        return MONO_E_ARG;
+    }
+    if (a->planes) {
+        const bool need_f32 = a->fmt == MONO_ACT_A8 || a->fmt == MONO_ACT_HILO;
+        if ((need_f32 && !a->scale_f32) || ((a->fmt == MONO_ACT_MX8 || a->fmt == MONO_ACT_MX8N) && !a->scale_e8) || a->fmt < 0 || a->fmt > 4) {
+            mono_set_error("mono_reduce_norm_launch: format %d needs its scale buffer", a->fmt);
+            return MONO_E_ARG;
+        }
+    }
+    // the largest cluster (8, 4, 2, 1 CTAs per row) whose CTAs get whole 128-column chunks, at most 2048 columns each
+    int c = 8;
+    while (c > 1 && (a->k % (c * 128)) != 0) c >>= 1;
+    if (a->k / c > 2048) {
+        mono_set_error("mono_reduce_norm_launch: k = %d leaves more than 2048 columns per CTA of the row's cluster", a->k);
+        return MONO_E_ARG;
+    }
+    const size_t smem = (size_t)(a->k / c) * sizeof(float);
+    const cudaStream_t st = (cudaStream_t)stream;
+    if (c == 8) mono::launch_k(mono::reduce_norm_kernel<8>, r->rows * 8, mono::kRnThreads, smem, st, *r, *a);
+    else if (c == 4) mono::launch_k(mono::reduce_norm_kernel<4>, r->rows * 4, mono::kRnThreads, smem, st, *r, *a);
+    else if (c == 2) mono::launch_k(mono::reduce_norm_kernel<2>, r->rows * 2, mono::kRnThreads, smem, st, *r, *a);
+    else mono::launch_k(mono::reduce_norm_kernel<1>, r->rows, mono::kRnThreads, smem, st, *r, *a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) mono_set_error("mono_reduce_norm_launch: %s", cudaGetErrorString(e));
     return (int)e;
 }
 

@@ -11,6 +11,8 @@ blocks -> o_proj -> all-reduce + residual.  Everything is allocated in ``__init_
 
 from __future__ import annotations
 
+import os
+
 import ctypes as C
 from dataclasses import dataclass
 
@@ -165,7 +167,9 @@ class GqaAttentionOp:
         self.o_g.add("o", w["o"], self.oq, self.o_p, wscale=w["o_s"], split_tiles=st, nsplit=ns)
         self.out = z(L.MAX_ROWS, h, dt=torch.bfloat16)
 
-    def launch(self, residual: torch.Tensor, t: GqaTables) -> torch.Tensor:
+    def launch(self, residual: torch.Tensor, t: GqaTables, defer: bool = False):
+        """``defer``: the o_proj reduction (+ all-reduce + residual) is returned unlaunched (``ops.PendingReduce``) for
+        the stage that consumes it to run inside its own norm staging launch."""
         cfg, w = self.cfg, self.w
         rows = residual.shape[0]
         if not 1 <= rows <= L.MAX_ROWS:
@@ -176,9 +180,9 @@ class GqaAttentionOp:
         attn = self.core.launch(rows, self.qkv, self.ns_qkv, t)
         ops.act_prep(rows, cfg.q_local * HEAD_DIM, self.oq, src_bf16=attn, round_bf16=False)
         self.o_g.launch(rows)
-        ops.reduce_rows(rows, cfg.hidden, self.o_p, self.ns_o, self.out, residual=residual, slots=t.slots,
-                        peer=self.peer, site=self.site, guard=self.guard, deadline_s=self.deadline_s)
-        return self.out[:rows]
+        red = ops.PendingReduce(rows, cfg.hidden, self.o_p, self.ns_o, self.out, residual, t.slots, self.peer, self.site,
+                                self.guard, self.deadline_s)
+        return red if defer else red.launch()
 
 
 class GqaLayerOp:
@@ -196,5 +200,6 @@ class GqaLayerOp:
     def launch(self, h: torch.Tensor, t: GqaTables) -> torch.Tensor:
         if self.attn.peer is not None and self.attn.peer.world > 1:
             ops.epoch_advance(self.guard)
-        mid = self.attn.launch(h, t)
-        return self.ffn(mid, t.slots)
+        if os.environ.get("MONO_FUSE_REDUCE", "1") != "0":  # the attention all-reduce inside the MoE half's norm launch
+            return self.ffn(None, t.slots, pending=self.attn.launch(h, t, defer=True))
+        return self.ffn(self.attn.launch(h, t), t.slots)

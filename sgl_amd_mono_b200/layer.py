@@ -122,9 +122,17 @@ class MlaLayerOp:
         self.ffn = MoeFfn(cfg, w, device, max_rows=max_rows, peer=peer, guard=self.guard, site=2 * layer + 1,
                           deadline_s=deadline_s) if cfg.n_experts else None
         self._iargs = None
+        # MONO_FUSE_REDUCE=0: every reduction (+ all-reduce + residual) is a launch of its own instead of running inside
+        # the norm staging launch that consumes it (same bits either way)
+        self.fuse_reduce = os.environ.get("MONO_FUSE_REDUCE", "1") != "0"
 
-    def launch(self, h: torch.Tensor, step: StepTables) -> torch.Tensor:
+    def launch(self, h: torch.Tensor | None, step: StepTables, pending=None, defer: bool = False):
+        """``pending`` (``ops.PendingReduce``): the layer before this one left its last reduction to this layer's input
+        norm launch; ``h`` is then not read.  ``defer``: this layer's last reduction is returned unlaunched for the
+        next stage.  Without either, and with ``MONO_FUSE_REDUCE=0``, every reduction is a launch of its own."""
         cfg, w = self.cfg, self.w
+        if pending is not None:
+            h = pending.out[: pending.rows]
         rows = h.shape[0]
         if not 1 <= rows <= L.MAX_ROWS:
             raise ValueError(f"h: {rows} rows, the launch serves 1..{L.MAX_ROWS}")
@@ -142,7 +150,10 @@ class MlaLayerOp:
                 raise ValueError(f"step.idx_pages: page of {step.idx_pages.shape[-1]} bytes, needs {IDX_PAGE_BYTES}")
         if step.page_table.shape[1] * 64 > self.max_ctx:
             raise ValueError(f"step.page_table: {step.page_table.shape[1]} pages exceed the built context {self.max_ctx}")
-        ops.act_prep(rows, cfg.hidden, self.x, src_bf16=h, gamma=w["input_norm"], eps=cfg.eps, out_bf16=self.xbf)
+        if pending is not None:
+            ops.reduce_norm(pending, self.x, gamma=w["input_norm"], eps=cfg.eps, out_bf16=self.xbf)
+        else:
+            ops.act_prep(rows, cfg.hidden, self.x, src_bf16=h, gamma=w["input_norm"], eps=cfg.eps, out_bf16=self.xbf)
         self.gA.launch(rows)
         if ih and self._side is not None:
             main = torch.cuda.current_stream()
@@ -199,9 +210,10 @@ class MlaLayerOp:
         # consecutive all-reduces of a step must alternate between the peer buffer's two regions (site % 2): a
         # rank may start pushing launch n + 1 while a peer still reads launch n's words.  A layer without an
         # FFN all-reduce therefore numbers its attention site by the layer alone
-        ops.reduce_rows(rows, cfg.hidden, self.o_p, self.nsO, self.h1, residual=h, slots=step.slots, peer=self.peer,
-                        site=2 * self.layer if self.ffn is not None else self.layer, guard=self.guard,
-                        deadline_s=self.deadline_s)
+        attn = ops.PendingReduce(rows, cfg.hidden, self.o_p, self.nsO, self.h1, h, step.slots, self.peer,
+                                 2 * self.layer if self.ffn is not None else self.layer, self.guard, self.deadline_s)
         if self.ffn is None:
-            return self.h1[:rows]
-        return self.ffn(self.h1[:rows], step.slots)
+            return attn if defer else attn.launch()
+        if self.fuse_reduce:  # the attention all-reduce runs inside the MoE half's norm staging launch
+            return self.ffn(None, step.slots, pending=attn, defer=defer)
+        return self.ffn(attn.launch(), step.slots, defer=defer)

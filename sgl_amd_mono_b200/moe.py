@@ -142,8 +142,13 @@ class MoeFfn:
             g.chain(first, first + (2 if self.has_shared else 1), self.max_expert)
             self.chained = g
 
-    def __call__(self, residual: torch.Tensor, slots: torch.Tensor | None = None) -> torch.Tensor:
+    def __call__(self, residual: torch.Tensor | None, slots: torch.Tensor | None = None, pending=None, defer: bool = False):
+        """``pending``: the reduction that produces this block's input rows has not been launched (``ops.PendingReduce``);
+        it runs inside this block's norm staging launch and ``residual`` is not read.  ``defer``: the block's own final
+        reduction is returned as an ``ops.PendingReduce`` instead of being launched, for the next stage to fuse."""
         cfg, w = self.cfg, self.w
+        if pending is not None:
+            residual = pending.out[: pending.rows]
         rows = residual.shape[0]
         if not 1 <= rows <= L.MAX_ROWS:
             raise ValueError(f"residual: {rows} rows, the launch serves 1..{L.MAX_ROWS}")
@@ -151,7 +156,10 @@ class MoeFfn:
         if slots is not None:
             ops.require(slots, "slots", torch.int64, (rows,))
         h, il = cfg.hidden, cfg.inter_local
-        ops.act_prep(rows, h, self.xq, src_bf16=residual, gamma=w["post_norm"], eps=cfg.eps, out_bf16=self.xbf)
+        if pending is not None:
+            ops.reduce_norm(pending, self.xq, gamma=w["post_norm"], eps=cfg.eps, out_bf16=self.xbf)
+        else:
+            ops.act_prep(rows, h, self.xq, src_bf16=residual, gamma=w["post_norm"], eps=cfg.eps, out_bf16=self.xbf)
         if self.has_shared and self.xs is not self.xq:
             ops.act_prep(rows, h, self.xs, src_bf16=self.xbf, round_bf16=False)
         rt = (rows, cfg.top_k, cfg.route_scale, self.logits, w.get("router_bias"), slots, self.ids,
@@ -161,11 +169,11 @@ class MoeFfn:
         else:
             ops.rowdot(rows, w["router"], self.xbf, self.logits)
             ops.route(*rt)
+        final = ops.PendingReduce(rows, h, self.down_p, self.n_slices, self.out, residual, slots, self.peer, self.site,
+                                  self.guard, self.deadline_s)
         if self.chained is not None:
             self.chained.launch(rows)
-            ops.reduce_rows(rows, h, self.down_p, self.n_slices, self.out, residual=residual, slots=slots,
-                            peer=self.peer, site=self.site, guard=self.guard, deadline_s=self.deadline_s)
-            return self.out[:rows]
+            return final if defer else final.launch()
         self.up.launch(rows)
         if self.up_sh is not None:
             self.up_sh.launch(rows)
@@ -181,6 +189,4 @@ class MoeFfn:
         self.down.launch(rows)
         if self.down_sh is not None:
             self.down_sh.launch(rows)
-        ops.reduce_rows(rows, h, self.down_p, self.n_slices, self.out, residual=residual, slots=slots,
-                        peer=self.peer, site=self.site, guard=self.guard, deadline_s=self.deadline_s)
-        return self.out[:rows]
+        return final if defer else final.launch()

@@ -300,17 +300,13 @@ def _injector(rank: int):
     return _injectors[rank]
 
 
-def reduce_rows(rows: int, n: int, partial: torch.Tensor, nsum: int, out: torch.Tensor, *, residual=None,
-                slots=None, peer=None, site: int = 0, guard=None, deadline_s: float = 5.0) -> None:
-    """Adds the partial slices, all-reduces across ranks in rank order, adds the residual."""
+def _reduce_args(rows, n, partial, nsum, out, residual, slots, peer, site, guard, deadline_s) -> "L.ReduceArgs":
     a = L.ReduceArgs()
     a.rows, a.n, a.partial, a.nsum, a.ld = rows, n, partial.data_ptr(), nsum, partial.shape[-1]
     a.sum_stride = L.MAX_ROWS * partial.shape[-1]
     a.residual, a.slots, a.out = _p(residual), _p(slots), out.data_ptr()
     a.world, a.rank = 1, 0
     if peer is not None and peer.world > 1:
-        if _injector(peer.rank).skip(site):
-            return  # MONO_FAULT_INJECT: this rank's host skips the launch; the peers' waits at `site` run out
         a.world, a.rank = peer.world, peer.rank
         a.peer_ptrs = peer.region_table(site).data_ptr()
         a.peer_guards = peer.guard_table.data_ptr()
@@ -319,6 +315,15 @@ def reduce_rows(rows: int, n: int, partial: torch.Tensor, nsum: int, out: torch.
     if not 0 <= site <= 254:
         raise ValueError(f"site {site}: the launch tag holds sites 0..254 (tag = epoch * 256 + site + 1)")
     a.site, a.guard = site, _p(guard)
+    return a
+
+
+def reduce_rows(rows: int, n: int, partial: torch.Tensor, nsum: int, out: torch.Tensor, *, residual=None,
+                slots=None, peer=None, site: int = 0, guard=None, deadline_s: float = 5.0) -> None:
+    """Adds the partial slices, all-reduces across ranks in rank order, adds the residual."""
+    if peer is not None and peer.world > 1 and _injector(peer.rank).skip(site):
+        return  # MONO_FAULT_INJECT: this rank's host skips the launch; the peers' waits at `site` run out
+    a = _reduce_args(rows, n, partial, nsum, out, residual, slots, peer, site, guard, deadline_s)
     L.check(L.load().mono_reduce_launch(C.byref(a), _stream()), "mono_reduce_launch")
 
 
@@ -341,6 +346,44 @@ def logits_gather(rows: int, n_local: int, partial: torch.Tensor, nsum: int, out
         a.deadline_ns = int(deadline_s * 1e9)
     a.site, a.guard = site, _p(guard)
     L.check(L.load().mono_logits_gather_launch(C.byref(a), _stream()), "mono_logits_gather_launch")
+
+
+class PendingReduce:
+    """A partial-sum reduction (+ all-reduce + residual) that has not been launched: the stage that consumes its
+    output launches it fused with its own norm staging (``reduce_norm``).  ``out`` is where the reduced rows
+    (the new residual stream, bf16 ``[16, n]``) will be."""
+
+    def __init__(self, rows, n, partial, nsum, out, residual, slots, peer, site, guard, deadline_s):
+        self.rows, self.n, self.partial, self.nsum, self.out = rows, n, partial, nsum, out
+        self.residual, self.slots, self.peer, self.site, self.guard, self.deadline_s = residual, slots, peer, site, guard, deadline_s
+
+    def args(self) -> "L.ReduceArgs":
+        return _reduce_args(self.rows, self.n, self.partial, self.nsum, self.out, self.residual, self.slots, self.peer,
+                            self.site, self.guard, self.deadline_s)
+
+    def launch(self) -> torch.Tensor:
+        """On its own after all (nothing downstream to fuse with)."""
+        reduce_rows(self.rows, self.n, self.partial, self.nsum, self.out, residual=self.residual, slots=self.slots,
+                    peer=self.peer, site=self.site, guard=self.guard, deadline_s=self.deadline_s)
+        return self.out[: self.rows]
+
+
+def reduce_norm(pending: PendingReduce, dst: ActBuf | None, *, gamma=None, eps: float = 0.0, round_bf16: bool = True,
+                out_bf16=None) -> torch.Tensor:
+    """``pending`` and the activation staging of its output in one launch (``mono_reduce_norm_launch``): the bits of
+    ``pending.launch()`` followed by ``act_prep(src_bf16=pending.out, ...)``.  Returns the reduced rows."""
+    if pending.peer is not None and pending.peer.world > 1 and _injector(pending.peer.rank).skip(pending.site):
+        return pending.out[: pending.rows]
+    r = pending.args()
+    a = L.ActPrepArgs()
+    a.rows, a.k = pending.rows, pending.n
+    a.gamma_bf16, a.eps, a.round_bf16 = _p(gamma), eps, int(round_bf16)
+    if dst is not None:
+        a.fmt, a.planes, a.plane_stride, a.ld = dst.fmt, _p(dst.planes), dst.plane_stride, dst.ld
+        a.scale_f32, a.scale_e8, a.scale_ld = _p(dst.scale_f32), _p(dst.scale_e8), dst.scale_ld
+    a.out_bf16 = _p(out_bf16)
+    L.check(L.load().mono_reduce_norm_launch(C.byref(r), C.byref(a), _stream()), "mono_reduce_norm_launch")
+    return pending.out[: pending.rows]
 
 
 def sparse_mla(q, kv_pages, topk_slots, out, scratch, sm_scale: float, topk: int | None = None, staged=None) -> None:

@@ -47,12 +47,27 @@ class DecoderStack:
         """One decode / verify step: returns (hidden rows, f32 logits or None)."""
         if self.draft is not None and draft_tables is not None:
             self.draft_out = self.draft.launch(h[:draft_rows] if draft_rows else h, draft_tables)
-        x = h
-        for op, t in zip(self.layers, tables):
-            x = op.launch(x, t)
-        logits = self.head(x) if self.head is not None else None
+        x = self.run_layers(h, tables)
+        logits = None
+        if self.head is not None:
+            if isinstance(x, ops.PendingReduce):
+                logits = self.head(None, pending=x)
+                x = x.out[: x.rows]
+            else:
+                logits = self.head(x)
         ops.epoch_advance(self.guard)
         return x, logits
+
+    def run_layers(self, h: torch.Tensor, tables: list[StepTables]):
+        """The layers in order.  A layer's last reduction (MoE all-reduce + residual) runs inside the next layer's
+        input norm launch, the last layer's inside the tail's; without a tail it is launched on its own."""
+        x, pend = h, None
+        fuse = all(op.fuse_reduce and op.ffn is not None for op in self.layers)
+        for i, (op, t) in enumerate(zip(self.layers, tables)):
+            last = i == len(self.layers) - 1
+            x = op.launch(None if pend is not None else x, t, pending=pend, defer=fuse and (not last or self.head is not None))
+            pend = x if isinstance(x, ops.PendingReduce) else None
+        return x
 
     def capture(self, h: torch.Tensor, tables, draft_tables=None, draft_rows: int = 0):
         """Runs the step once eagerly, then captures it; ``replay()`` re-runs the device work."""

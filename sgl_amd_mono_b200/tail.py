@@ -44,10 +44,16 @@ class LmHeadOp:
         self.world = peer.world if peer is not None else 1
         self.gathered = torch.zeros(L.MAX_ROWS, self.world * self.vocab_local, dtype=torch.float32, device=device)
 
-    def __call__(self, h: torch.Tensor) -> torch.Tensor:
+    def __call__(self, h: torch.Tensor | None, pending=None) -> torch.Tensor:
+        """``pending``: the last layer's final reduction, left for this launch's norm staging to run."""
+        if pending is not None:
+            h = pending.out[: pending.rows]
         rows = h.shape[0]
         ops.require(h, "h", torch.bfloat16, (rows, self.hidden))
-        ops.act_prep(rows, self.hidden, self.x, src_bf16=h, gamma=self.g, eps=self.eps)
+        if pending is not None:
+            ops.reduce_norm(pending, self.x, gamma=self.g, eps=self.eps)
+        else:
+            ops.act_prep(rows, self.hidden, self.x, src_bf16=h, gamma=self.g, eps=self.eps)
         g, buf, ns = self.gemv[rows > 8]
         g.launch(rows)
         if ns == 1 and self.world == 1:

@@ -21,6 +21,7 @@ import time
 import pytest
 import torch
 
+from oracle import quant as Q
 from oracle import stages as S
 from sgl_amd_mono_b200 import _lib as L
 from sgl_amd_mono_b200 import ops
@@ -326,3 +327,61 @@ def test_lm_head_wide_step_sums_k_splits_in_a_kernel():
         assert torch.equal(got, want), "the K splits are added in order"
     ref = S.tail_logits(h, gamma, 1e-6, w)
     assert float((got.cpu() - ref).abs().max()) <= 2e-2 * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("world,rank,n", [(1, 0, 2048), (2, 1, 7168), (8, 3, 1024), (4, 0, 512)])
+def test_reduce_fused_with_the_norm_staging_matches_the_two_launches(world, rank, n):
+    """``mono_reduce_norm_launch``: the reduction (+ all-reduce over host-written peer words + residual) and the RMSNorm
+    staging of its output in one launch.  The reduced rows are the bits of ``mono_reduce_launch`` (live and pad rows,
+    pushes at every peer); the staged values follow ``mono_act_prep_launch`` up to the last bit of the reciprocal root
+    (a row's sum of squares is added per CTA of its cluster, then in CTA order)."""
+    rows, nsum, site = 4, 11, 5
+    g = torch.Generator().manual_seed(31 * world + rank)
+    parts = [torch.randn(rows, n, generator=g) * 4 for _ in range(world)]
+    for p in parts:
+        p[2] = 0  # row 2 is a pad row on every rank
+    mine = torch.zeros(nsum, ROWS_MAX, n)
+    mine[:, :rows] = torch.randn(nsum, rows, n, generator=g)
+    residual = torch.randn(rows, n, generator=g).bfloat16().to(DEV)
+    gamma = (1 + 0.1 * torch.randn(n, generator=g)).bfloat16().to(DEV)
+    slots = torch.tensor([5, 9, -1, 77], dtype=torch.int64, device=DEV)
+    part = mine.to(DEV)
+    got = {}
+    for fused in (False, True):
+        R = OneDeviceRanks(max(world, 1), rank, n)
+        R.guard[0] = 3
+        for src in range(world):
+            if src != rank:
+                R.publish(1, src, parts[src].bfloat16(), _tag(3, site))
+        out = torch.zeros(ROWS_MAX, n, dtype=torch.bfloat16, device=DEV)
+        dst = ops.ActBuf(L.ACT_HILO, n, DEV)
+        xbf = torch.zeros(ROWS_MAX, n, dtype=torch.bfloat16, device=DEV)
+        peer = None
+        if world > 1:
+            peer = type("P", (), {"world": world, "rank": rank, "guard_table": R.gptrs, "region_table": lambda self, s: R.ptrs})()
+        pend = ops.PendingReduce(rows, n, part, nsum, out, residual, slots, peer, site, R.guard, 5.0)
+        if fused:
+            ops.reduce_norm(pend, dst, gamma=gamma, eps=1e-6, out_bf16=xbf)
+        else:
+            pend.launch()
+            ops.act_prep(rows, n, dst, src_bf16=out[:rows], gamma=gamma, eps=1e-6, out_bf16=xbf)
+        torch.cuda.synchronize()
+        assert ops.guard_read(R.guard)[0] == 0
+        got[fused] = (out.clone(), xbf.clone(), dst,
+                      [R.slot(R.regions[d], 1, rank)[:rows].cpu().clone() for d in range(max(world, 1))])
+    assert torch.equal(got[False][0], got[True][0]) and bool(got[True][0].float().abs().sum() > 0)
+    assert torch.equal(got[True][0][2], residual[2]), "a pad row's partial sums count as zero"
+    a, b = got[False][1].float(), got[True][1].float()
+    assert float((a - b).abs().max()) <= 2.0**-7 * float(a.abs().max()), "normalised rows: at most one bf16 ulp apart"
+    assert float((a != b).float().mean()) < 0.01
+    # the planes hold hi + lo = the bf16 value / scale
+    d = got[True][2]
+    val = (Q.e4m3_from_bytes(d.planes[0, 0, :rows, :n].cpu()) + Q.e4m3_from_bytes(d.planes[0, 1, :rows, :n].cpu()))
+    val = val.reshape(rows, n // 128, 128) * d.scale_f32[0, :rows, : n // 128].cpu()[..., None]
+    x = got[True][1][:rows].float().cpu()
+    # exact for values within 2^12 of their 128-chunk's largest; the smallest lose their last bits
+    assert float((val.reshape(rows, n) - x).abs().max()) <= 2.0**-11 * float(x.abs().max())
+    assert float((val.reshape(rows, n) == x).float().mean()) > 0.95
+    if world > 1:
+        for a, b in zip(got[False][3], got[True][3]):
+            assert torch.equal(a, b) and bool((a >> 32 == _tag(3, site)).all())

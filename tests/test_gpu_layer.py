@@ -189,3 +189,22 @@ def test_index_queries_made_by_the_score_launch(rows, ctx, monkeypatch):
     assert torch.equal(op.scores[:rows], op2.scores[:rows])
     assert torch.equal(op.topk_slots[:rows], op2.topk_slots[:rows])
     assert torch.equal(out, out2)
+
+
+def test_reductions_fused_into_the_norm_staging_launches(monkeypatch):
+    """With MONO_FUSE_REDUCE=1 (default) the attention all-reduce + residual runs inside the MoE half's norm staging
+    launch (and, in a stack, a layer's last reduction inside the next layer's input norm launch).  The reduced rows
+    (h1) are the bits of the separate launch; the normalised rows may differ in the last bit of the reciprocal root,
+    so routing and output are compared as the oracle comparison does: same experts, output within tolerance."""
+    cfg, rows, ctx = CFG_TINY, 7, 640
+    monkeypatch.setenv("MONO_FUSE_REDUCE", "1")
+    op, w, step, dstep, h, out = _run(cfg, rows, ctx, pad=(3,))
+    assert op.fuse_reduce
+    check_mla_layer(cfg, op, w, step, dstep, h, out, pad=(3,))
+    monkeypatch.setenv("MONO_FUSE_REDUCE", "0")
+    op2, _, _, _, _, out2 = _run(cfg, rows, ctx, pad=(3,))
+    assert not op2.fuse_reduce
+    assert torch.equal(op.h1[:rows], op2.h1[:rows]) and bool(op.h1[:rows].float().abs().sum() > 0)
+    assert torch.equal(op.ffn.ids[:rows], op2.ffn.ids[:rows])
+    d = float((out.float() - out2.float()).abs().max())
+    assert d <= 4e-2 * max(1.0, float(out2.float().abs().max())), f"fused and separate reductions differ by {d}"
