@@ -20,6 +20,7 @@
 extern void mono_set_error(const char* fmt, ...);
 
 namespace mono {
+MONO_TL_DECLARE(tl_gemv)
 
 constexpr int kTcThreads = 320;  // TMA, MMA, 4 epilogue warps, 4 finisher warps
 // A pipeline unit is kTcUnit k tiles: one barrier round trip, one commit, one TMEM load for all of them.  A stage
@@ -396,6 +397,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
         }
     }
     pdl_wait();
+    MONO_TL(tl_gemv, 0);
     // chained jobs stamp their per-slot "activations ready" words with this launch's generation
     const int stamp = p.a.gen ? *reinterpret_cast<const volatile int*>(p.a.gen) + 1 : 1;
 
@@ -453,6 +455,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
         // ------------------------------------------------------------ producer: scales by cp.async, tiles by TMA
         int stage = 0, slot = 0;
         uint32_t phase = 0, sphase = 0, ready_mask = 0;
+#ifdef MONO_TIMELINE
+        int tl_seg = 0;
+#endif
 #define TASK_BEGIN
 #define TASK_END
         TC_FOR_EACH_SEGMENT({
@@ -484,9 +489,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
                 }
                 // (the writer ordered its stores against the async proxy before it released the stamp)
             }
+#ifdef MONO_TIMELINE
+#define TLP(k) do { if (blockIdx.x == 0 && lane == 0 && tl_seg >= 4 && tl_seg < 7) tl_gemv[153][(tl_seg - 4) * 5 + (k)] = globaltimer_ns(); } while (0)
+#else
+#define TLP(k) do { } while (0)
+#endif
+            TLP(0);
             if (lane == 0) ok = mbar_wait(&sc_empty[slot], sphase ^ 1, abortp, wait_ns) ? 1 : 0;
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
+            TLP(1);
             float* sl = sc_ring + (size_t)slot * kTcScRows * kTcMaxSegTiles;
             for (int i = lane; i < rows * s.nt; i += 32) {
                 const int c = i / s.nt, t = i - c * s.nt;
@@ -496,12 +508,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
             if (s.coef && lane < rows) cp_async4(&sl[17 * kTcMaxSegTiles + lane], s.coef + lane);
             cp_async_arrive(&sc_full[slot]);
             if (++slot == kTcScSlots) { slot = 0; sphase ^= 1; }
+            TLP(2);
             if (lane == 0) {
                 const CUtensorMap* wmap = reinterpret_cast<const CUtensorMap*>(&jb.tmap);
                 const CUtensorMap* amap = reinterpret_cast<const CUtensorMap*>(&jb.act_tmap);
                 for (int t = 0; t < s.nt; t += kTcUnit) {
                     const int n2 = min(kTcUnit, s.nt - t);
                     if (!mbar_wait(&acc_full[stage], phase ^ 1, abortp, wait_ns)) break;  // the MMAs of the stage's last unit are done
+                    TLP(3);
                     uint8_t* st = ring + (size_t)stage * stage_bytes;
                     mbar_expect_tx(&full[stage], n2 * (kTcABytes + planes * kTcBBytes));
                     for (int i = 0; i < n2; ++i) {
@@ -512,7 +526,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
                     }
                     if (++stage == kTcMaxStages) { stage = 0; phase ^= 1; }
                 }
+                TLP(4);
+#ifdef MONO_TIMELINE
+                if (blockIdx.x == 0 && tl_seg < MONO_TL_POINTS) tl_gemv[150][tl_seg] = globaltimer_ns();
+#endif
             }
+#ifdef MONO_TIMELINE
+            ++tl_seg;
+#endif
             __syncwarp();
         })
 #undef TASK_BEGIN
@@ -523,6 +544,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0, g = 0;
+#ifdef MONO_TIMELINE
+            int tl_seg = 0;
+#endif
 #define TASK_BEGIN
 #define TASK_END
             TC_FOR_EACH_SEGMENT({
@@ -550,6 +574,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
                     g += n2;
                     if (++stage == kTcMaxStages) { stage = 0; phase ^= 1; }
                 }
+#ifdef MONO_TIMELINE
+                if (blockIdx.x == 0 && tl_seg < MONO_TL_POINTS) tl_gemv[151][tl_seg] = globaltimer_ns();
+                ++tl_seg;
+#endif
             })
 #undef TASK_BEGIN
 #undef TASK_END
@@ -568,6 +596,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
         bool have_next = false;
         BoundedSync es{epi_bar, 0u, abortp, wait_ns};
         float total_acc[kMaxRows];
+        int tl_n = 1;  // timeline: the end of this CTA's n-th task (first epilogue warp's lane 0)
+        (void)tl_n;
+#ifdef MONO_TIMELINE
+        int tl_seg = 0;
+#endif
 #define TASK_BEGIN \
         _Pragma("unroll") for (int c = 0; c < kMaxRows; ++c) total_acc[c] = 0.f;
 #define TASK_END                                                                                              \
@@ -585,6 +618,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
                 if (mbar_wait(&mail_free[k], ((nfeed >> 1) & 1) ^ 1, abortp, wait_ns)) mbar_arrive(&mail_full[k]);     \
                 ++nfeed;                                                                                      \
             }                                                                                                 \
+            if (warp == 2 && lane == 0) { MONO_TL_AT(tl_gemv, tl_n); ++tl_n; }                                \
         }
         TC_FOR_EACH_SEGMENT({
             if (!mbar_wait(&sc_full[slot], sphase, abortp, wait_ns)) break;
@@ -633,6 +667,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
             __syncwarp();
             if (lane == 0) mbar_arrive(&sc_empty[slot]);
             if (++slot == kTcScSlots) { slot = 0; sphase ^= 1; }
+#ifdef MONO_TIMELINE
+            if (blockIdx.x == 0 && warp == 2 && lane == 0 && tl_seg < MONO_TL_POINTS) tl_gemv[152][tl_seg] = globaltimer_ns();
+            ++tl_seg;
+#endif
         })
 #undef TASK_BEGIN
 #undef TASK_END
@@ -843,3 +881,12 @@ extern "C" int mono_gemv_max_resident_ctas(const mono_gemv_args* a) {
     if (int rc = tc_plan(a, &p, &unit, &smem)) return rc > 0 ? -rc : rc;
     return tc_resident(unit, smem);
 }
+
+#ifdef MONO_TIMELINE
+// Copies the tcgen05 GEMV's stamps of the last launch to `out` (MONO_TL_CTAS x MONO_TL_POINTS); blocks the host.
+extern "C" int mono_timeline_read_gemv_tc(unsigned long long* out, int* ctas, int* points) {
+    *ctas = MONO_TL_CTAS;
+    *points = MONO_TL_POINTS;
+    return (int)cudaMemcpyFromSymbol(out, mono::tl_gemv, sizeof(unsigned long long) * MONO_TL_CTAS * MONO_TL_POINTS);
+}
+#endif

@@ -282,9 +282,15 @@ __device__ __forceinline__ float ld_cg_f32(const float* p) {
     do {                                                                                                         \
         if (threadIdx.x == 0 && blockIdx.x < MONO_TL_CTAS && (p) < MONO_TL_POINTS) name[blockIdx.x][p] = mono::globaltimer_ns(); \
     } while (0)
+// the same from any one thread the caller has picked (e.g. lane 0 of a role's warp)
+#define MONO_TL_AT(name, p)                                                                                      \
+    do {                                                                                                         \
+        if (blockIdx.x < MONO_TL_CTAS && (p) < MONO_TL_POINTS) name[blockIdx.x][p] = mono::globaltimer_ns();     \
+    } while (0)
 #else
 #define MONO_TL_DECLARE(name)
 #define MONO_TL(name, p) do { } while (0)
+#define MONO_TL_AT(name, p) do { } while (0)
 #endif
 
 // Host side: one launch helper, with or without the programmatic-serialization attribute.

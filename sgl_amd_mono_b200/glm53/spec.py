@@ -52,7 +52,21 @@ def _config_disable_reasons(cfg, hf_config) -> list[str]:
     return reasons
 
 
+def _bound(model, hf_config, tp: int, copies: dict, i: int) -> dict:
+    """Layer i's tensors: bound to SGLang's modules (``weights.layer_weights``), or the ``weights`` dict a
+    stand-alone synthetic model carries."""
+    from ..spec_common import model_layers
+    from .weights import layer_weights
+
+    layer = model_layers(model)[i]
+    if isinstance(getattr(layer, "weights", None), dict):
+        return layer.weights
+    return layer_weights(layer, i, layer_config(hf_config, tp), copies)
+
+
 def _model_disable_reasons(model, hf_config, copies: dict) -> list[str]:
+    """Every reason the loaded model cannot be read in place (reference: ``glm53/spec.py:215-251``): each covered
+    layer's tensors go through the binding's checks, and a failed check is a reason naming the layer and the tensor."""
     import torch
 
     tp = getattr(model, "tp_size", 1)
@@ -61,7 +75,11 @@ def _model_disable_reasons(model, hf_config, copies: dict) -> list[str]:
     u8, f32, bf = torch.uint8, torch.float32, torch.bfloat16
     reasons = []
     for i in _covered_layers(hf_config):
-        w = model.layers[i].weights
+        try:
+            w = _bound(model, hf_config, tp, {}, i)  # a dry run: its copies are dropped
+        except (ValueError, AttributeError) as e:
+            reasons.append(f"layer {i}: {e}")
+            continue
         reasons += weight_reasons(i, w, {
             "qkv_a": (u8, (c.q_lora + 576, h)), "qkv_a_s": (f32, (-(-(c.q_lora + 576) // 128), h // 128)),
             "q_b": (u8, (hl * 192, c.q_lora)), "kv_b": (u8, (hl * 256, 512)), "kv_b_s": (f32, (hl * 2, 4)),
@@ -83,9 +101,10 @@ def _build(model, hf_config, ctx):
 
     def make(i, w):
         return MlaLayerOp(c, w, ctx.device, max_ctx=ctx.max_context, peer=peer, guard=peer.guard if peer else None,
-                          layer=i, deadline_s=ctx.deadline_s, max_rows=max(ctx.widths))
+                          layer=i, deadline_s=ctx.deadline_s, max_rows=max(ctx.widths), copies=ctx.copies)
 
-    return build_layers(model, c, ctx, _covered_layers(hf_config), make)
+    return build_layers(model, c, ctx, _covered_layers(hf_config), make,
+                        bind=lambda i: _bound(model, hf_config, ctx.tp_size, ctx.copies, i))
 
 
 SPEC = MonoSpec(

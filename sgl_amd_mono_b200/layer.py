@@ -39,7 +39,7 @@ class StepTables:
 
 class MlaLayerOp:
     def __init__(self, cfg: LayerConfig, w: dict, device, max_ctx: int, peer=None, guard=None, layer: int = 0,
-                 deadline_s: float = 5.0, max_rows: int = L.MAX_ROWS):
+                 deadline_s: float = 5.0, max_rows: int = L.MAX_ROWS, copies: dict | None = None):
         L.load()
         if cfg.nope != 128 or cfg.v_head != 128 or cfg.rope != 64 or cfg.kv_lora != 512:
             raise ValueError("the MLA kernels are built for nope 128, v 128, rope 64, kv_lora 512")
@@ -120,7 +120,7 @@ class MlaLayerOp:
         self.gO.add("o_proj", w["o_proj"], self.o, self.o_p, wscale=w["o_proj_s"], split_tiles=stO, nsplit=nsO)
         self.h1 = z(R, h, dt=torch.bfloat16)
         self.ffn = MoeFfn(cfg, w, device, max_rows=max_rows, peer=peer, guard=self.guard, site=2 * layer + 1,
-                          deadline_s=deadline_s) if cfg.n_experts else None
+                          deadline_s=deadline_s, copies=copies, layer=layer) if cfg.n_experts else None
         self._iargs = None
         # MONO_FUSE_REDUCE=0: every reduction (+ all-reduce + residual) is a launch of its own instead of running inside
         # the norm staging launch that consumes it (same bits either way)

@@ -31,7 +31,10 @@ class MoeFfn:
     """``out = residual + allreduce(shared(x̂) + sum_k w_k expert_k(x̂))``, x̂ = RMSNorm(residual)."""
 
     def __init__(self, cfg: LayerConfig, w: dict, device, max_rows: int = L.MAX_ROWS, peer=None,
-                 guard: torch.Tensor | None = None, site: int = 1, deadline_s: float = 5.0):
+                 guard: torch.Tensor | None = None, site: int = 1, deadline_s: float = 5.0, copies: dict | None = None,
+                 layer: int = 0):
+        """``copies``: the build context's dict of one-time copies (key tuple -> tensor, ``glm53/spec.py:499-581``);
+        the one repack this block may make (MXFP4 scale rows padded to whole tiles) is recorded there."""
         lib = L.load()  # fail loudly when the CUDA library is missing
         tc_on = lib.mono_set_gemv_tcgen05(1)  # read the switch ...
         lib.mono_set_gemv_tcgen05(tc_on)      # ... and put it back
@@ -63,7 +66,7 @@ class MoeFfn:
         # ---- up / gate launch
         # the shared expert's dense job goes first: its weight tiles do not depend on the router,
         # so the launch can request them before the routing of this step is known
-        self.up = ops.Gemv(_WK[efmt], self.guard, deadline_s)
+        self.up = ops.Gemv(_WK[efmt], self.guard, deadline_s, copies=copies, copy_tag=layer)
         self.up_sh = self.mid_s = self.up_s = None
         if self.has_shared:
             self.xs = self.xq if same else ops.ActBuf(act_of(sfmt, w["sh13"]), h, device)
@@ -100,7 +103,7 @@ class MoeFfn:
             self.st_dn_s, ns_dn_s = ops.plan_split(_ktiles(w["sh2"]), nrb, _WK[sfmt])
         self.n_slices = self.groups + ns_dn_s
         self.down_p = z(self.n_slices, L.MAX_ROWS, h)
-        self.down = ops.Gemv(_WK[efmt], self.guard, deadline_s)
+        self.down = ops.Gemv(_WK[efmt], self.guard, deadline_s, copies=copies, copy_tag=layer)
         self.down_sh = None
         if self.has_shared:
             g = self.down if same else ops.Gemv(_WK[sfmt], self.guard, deadline_s)

@@ -132,9 +132,12 @@ def fp4_tma_ok(w: torch.Tensor) -> bool:
 class Gemv:
     """One persistent weight-streaming launch over up to four jobs (``mono_gemv_launch``)."""
 
-    def __init__(self, wkind: int, guard: torch.Tensor | None = None, deadline_s: float = 0.0):
+    def __init__(self, wkind: int, guard: torch.Tensor | None = None, deadline_s: float = 0.0, copies: dict | None = None,
+                 copy_tag=None):
         """``deadline_s``: limit of every device-side wait of the launch (0 = the library's 2 s); the
-        build context's deadline, as the reference arms its waits from it (``common/guard.py:4-7,69``)."""
+        build context's deadline, as the reference arms its waits from it (``common/guard.py:4-7,69``).
+        ``copies``: where a one-time repack of this launch's weights is recorded (key tuple -> tensor)."""
+        self.copies, self.copy_tag = copies, copy_tag
         self.wkind = wkind
         self.args = L.GemvArgs()
         self.args.wkind = wkind
@@ -201,6 +204,8 @@ class Gemv:
                          tuple(padded.shape), padded.numel())
                 ws = ws3 = padded
                 self._keep.append(padded)
+                if self.copies is not None:
+                    self.copies["MXFP4 scale rows padded to whole tiles", self.copy_tag, name] = padded
             job.wscale_e8, job.wscale_mat_stride, job.wscale_ld = ws.data_ptr(), ws3.shape[1] * ws3.shape[2], ws3.shape[2]
         job.act, job.planes, job.act_plane_stride, job.act_ld = _p(act.planes), act.nplanes, act.plane_stride, act.ld
         L.check(L.load().mono_tmap_encode_box(C.byref(job.act_tmap), act.planes.data_ptr(), act.ld, L.MAX_ROWS,

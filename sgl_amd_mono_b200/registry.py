@@ -17,16 +17,25 @@ import importlib
 from dataclasses import dataclass, field
 from typing import Any, Callable
 
-try:  # pragma: no cover - SGLang is not installed in the build environment
-    from sglang.kernels.plugin_kernels.amd.spec import (  # type: ignore
-        DeviceLimits, Feature, MonoSpec, Numerics, NumericsKind, Requirements, register,
-    )
-    from sglang.kernels.plugin_kernels.amd import registry as _sgl_registry  # type: ignore
+def _sglang_spec_module():
+    """SGLang's monokernel spec module: the reference tries these two locations in this order
+    (``sgl_amd_mono/__init__.py:46-49``).  None when SGLang is not installed."""
+    for name in ("sglang.kernels.plugin_kernels.amd.spec", "sglang.srt.monokernels.spec"):
+        try:
+            return importlib.import_module(name)
+        except ModuleNotFoundError:
+            continue
+    return None
 
+
+_sgl = _sglang_spec_module()
+HAVE_SGLANG = _sgl is not None
+if HAVE_SGLANG:  # pragma: no cover - SGLang is not installed in the build environment
+    DeviceLimits, Feature, MonoSpec, Numerics = _sgl.DeviceLimits, _sgl.Feature, _sgl.MonoSpec, _sgl.Numerics
+    NumericsKind, Requirements, register = _sgl.NumericsKind, _sgl.Requirements, _sgl.register
+    _sgl_registry = importlib.import_module(_sgl.__name__.rsplit(".", 1)[0] + ".registry")
     ShapeKey, find_spec, spec_registered = _sgl_registry.ShapeKey, _sgl_registry.find_spec, _sgl_registry.spec_registered
-    HAVE_SGLANG = True
-except ModuleNotFoundError:
-    HAVE_SGLANG = False
+else:
 
     class Feature(enum.Enum):
         SPECULATIVE_DECODING = "speculative_decoding"

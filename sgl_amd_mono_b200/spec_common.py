@@ -83,7 +83,7 @@ class Built:
         st = step_tables(plan, positions, forward_batch, rows, self.max_position)
         h = input_embeds if input_embeds is not None else self.model.embed(input_ids)
         h = h[:rows]
-        for i, layer in enumerate(self.model.layers):
+        for i, layer in enumerate(model_layers(self.model)):
             op = self.ops.get(i)
             if op is None:  # an uncovered (dense) layer runs the model's own code
                 h = layer.forward(h, positions, forward_batch)
@@ -98,12 +98,24 @@ class Built:
         return self.model.finish(h, forward_batch) if hasattr(self.model, "finish") else h
 
 
-def build_layers(model, cfg: LayerConfig, ctx: BuildContext, covered: list[int], make_op) -> Built:
+def model_layers(model):
+    """The decoder layers: SGLang's ``lm.model.layers``, or ``model.layers`` of a stand-alone model."""
+    return getattr(model, "model", model).layers
+
+
+def build_layers(model, cfg: LayerConfig, ctx: BuildContext, covered: list[int], make_op, bind=None) -> Built:
     """Builds one op per covered layer in layer order (a collective when tp_size > 1:
-    every rank builds the same runtimes in the same order, ``glm53/spec.py:499-581``)."""
+    every rank builds the same runtimes in the same order, ``glm53/spec.py:499-581``).  ``bind(i)`` returns
+    layer i's tensors bound to SGLang's storage and records every one-time copy in ``ctx.copies``; without
+    it the layer carries its tensors as a ``weights`` dict (the stand-alone synthetic model)."""
     ops_by_layer = {}
+    before = len(ctx.copies)
     for i in covered:
-        ops_by_layer[i] = make_op(i, model.layers[i].weights)
-    log.info("%s: %d layers on the monokernels, widths %s, TP %d, no weight copies (tensors are read in place)",
-             cfg.name, len(covered), ctx.widths, ctx.tp_size)
+        ops_by_layer[i] = make_op(i, bind(i) if bind is not None else model_layers(model)[i].weights)
+    nbytes = sum(t.numel() * t.element_size() for t in ctx.copies.values() if isinstance(t, torch.Tensor))
+    log.info("%s: %d layers on the monokernels, widths %s, TP %d; %d one-time copies (%.1f MB in all), every other "
+             "tensor is read in place", cfg.name, len(covered), ctx.widths, ctx.tp_size, len(ctx.copies) - before, nbytes / 1e6)
+    for key in list(ctx.copies)[before:]:
+        t = ctx.copies[key]
+        log.info("  copy %s: %s %s", key, getattr(t, "dtype", type(t).__name__), tuple(getattr(t, "shape", ())))
     return Built(model, cfg, ops_by_layer, max(ctx.widths), ctx.max_context - 1)
