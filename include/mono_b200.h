@@ -329,7 +329,9 @@ int mono_sparse_mla_quant_launch(const mono_sparse_mla_args* a, const mono_act_p
  * MONO_E_ARG with a message and must use mono_sparse_mla_launch.  No cudaMalloc, cudaFree
  * or allocating library routine is called.  The first call on a device looks up the
  * array's device address (cudaGetSymbolAddress, with that device current) and caches
- * it, so make that first call before any stream capture.  All calls share the one
+ * it, so make that first call before any stream capture, and before the server sizes its
+ * KV-cache pool: the array comes into being when the library's device code is first loaded on
+ * the GPU, and a pool sized before that would have taken the memory it needs.  All calls share the one
  * array: calls that overlap on the GPU (different streams, or different threads on one
  * device) race on it and must be serialised by the caller; the array keeps the last
  * call's partials, and nothing in it has to be cleared between calls because the merge

@@ -89,7 +89,8 @@ def index_select(cfg, r, positions, slots, page_table, idx_pages):
             sel = S.exact_topk_positions(sc, n, cfg.index_topk)
             scores.append(sc)
         else:
-            sel = pos
+            # no indexer: every causal key, or the last `window` of them (the draft model's attention)
+            sel = pos[-cfg.window:] if getattr(cfg, "window", 0) else pos
         topk[s, : sel.numel()] = ksl[sel].to(torch.int32)
     return topk, scores
 

@@ -10,9 +10,9 @@ the specs sit Python host runners over a C-ABI library of hand-written CUDA kern
 
 __version__ = "0.1.0.dev0"
 
-# the backend name every spec registers under
+# one backend name for all of this package's specs: SGLang selects them with it
 BACKEND = "monokernel"
-# each spec by (HF architecture, model type), None for any model type
+# where each spec lives, keyed by the checkpoint's architecture string and its model type (None: whatever the type)
 SPECS = {
     ("DeepseekV4ForCausalLM", "deepseek_v4"): "sgl_amd_mono_b200.deepseek_v4.spec:SPEC",
     ("DeepseekV4ForCausalLM", "deepseek_v41"): "sgl_amd_mono_b200.deepseek_v41.spec:SPEC",

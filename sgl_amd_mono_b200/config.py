@@ -33,6 +33,7 @@ class LayerConfig:
     v_head: int = 128
     index_heads: int = 0
     index_topk: int = 2048
+    window: int = 0  # > 0 (and no indexer): a row attends its last `window` keys only (a draft model's attention)
     # MoE
     n_experts: int = 0
     top_k: int = 0

@@ -85,10 +85,14 @@ class MlaLayerOp:
             self.iq_p = z(nsB, R, ih * 128)
             self.gB.add("idx_wq_b", w["idx_wq_b"], self.qa, self.iq_p, wscale=w["idx_wq_b_s"], split_tiles=stB, nsplit=nsB)
         self.q_full = z(R, hl, KV_DIM, dt=torch.bfloat16)
-        # without an indexer every cached key is attended: the "selection" is the whole context
-        self.topk = cfg.index_topk if ih else -(-max_ctx // 64) * 64
+        # without an indexer every cached key is attended: the "selection" is the whole context, or with a window
+        # (the draft model: deepseek_v41/draft.py:34-35) the last `window` keys of each row
+        self.window = 0 if ih else min(cfg.window, max_ctx)
+        self.topk = cfg.index_topk if ih else (-(-self.window // 64) * 64 if self.window else -(-max_ctx // 64) * 64)
+        if self.window:
+            self._wcols = torch.arange(self.topk, dtype=torch.int64, device=device)
         if not ih:
-            self.max_ctx = self.topk
+            self.max_ctx = -(-max_ctx // 64) * 64 if self.window else self.topk
             self.scores = z(R, 128)
         self.topk_slots = torch.full((R, self.topk), -1, dtype=torch.int32, device=device)
         self.topk_pos = torch.full((R, self.topk), -1, dtype=torch.int32, device=device)
@@ -125,6 +129,16 @@ class MlaLayerOp:
         # MONO_FUSE_REDUCE=0: every reduction (+ all-reduce + residual) is a launch of its own instead of running inside
         # the norm staging launch that consumes it (same bits either way)
         self.fuse_reduce = os.environ.get("MONO_FUSE_REDUCE", "1") != "0"
+
+    def _window_slots(self, rows: int, step: StepTables) -> None:
+        """The step's selection for window-only attention: row r takes positions pos_r - window + 1 .. pos_r (those
+        that exist), in order, as global KV slots; pad rows take none.  A handful of fixed-shape torch ops, captured
+        with the step like the reference's step tables (``glm53/spec.py:467-496``)."""
+        pos = step.positions[:rows, None] - (self.window - 1) + self._wcols[None, :]
+        ok = (pos >= 0) & (self._wcols[None, :] < self.window) & (step.slots[:rows, None] >= 0)
+        p = pos.clamp(min=0)
+        slot = step.page_table[:rows].gather(1, (p // 64).clamp(max=step.page_table.shape[1] - 1)).long() * 64 + p % 64
+        self.topk_slots[:rows] = torch.where(ok, slot, torch.full_like(slot, -1)).to(torch.int32)
 
     def launch(self, h: torch.Tensor | None, step: StepTables, pending=None, defer: bool = False):
         """``pending`` (``ops.PendingReduce``): the layer before this one left its last reduction to this layer's input
@@ -195,7 +209,10 @@ class MlaLayerOp:
                        self.q_full, ih, self.iq_p, self.nsB, self.idx_q)
             if ih:
                 ops.index_score(ia)
-            ops.index_topk(ia)  # rows with at most topk keys keep every key in order
+            if self.window:
+                self._window_slots(rows, step)
+            else:
+                ops.index_topk(ia)  # rows with at most topk keys keep every key in order
         # the merge of the attention splits also stages every head's output for the W_UV GEMV
         # (MONO_MLA_STAGED=0: a staging launch of its own)
         if self.mla_staged:

@@ -37,7 +37,8 @@ def _build(model, hf_config, ctx):
     from .runner import FfnRunner
 
     c = layer_config(hf_config, ctx.tp_size)
-    ops = {i: FfnRunner(c, layer.weights, ctx.device, deadline_s=ctx.deadline_s) for i, layer in enumerate(model.layers)}
+    ops = {i: FfnRunner(c, layer.weights, ctx.device, deadline_s=ctx.deadline_s, copies=ctx.copies, layer=i)
+           for i, layer in enumerate(model.layers)}
     log.info("%s: %d FFN launches, widths %s", c.name, len(ops), ctx.widths)
     return Built(model, c, ops, max(ctx.widths), ctx.max_context - 1)
 

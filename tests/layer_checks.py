@@ -90,10 +90,12 @@ def check_mla_layer(cfg, op, w, step, dstep, h, out, pad=(), out_max_abs=4e-2, c
             assert topk_k[i, : want.numel()].tolist() == S.slots_of_positions(step.page_table[i], want).tolist()
             assert int((topk_k[i, want.numel():] >= 0).sum()) == 0
     else:
-        for i in live:  # no indexer: every causal key, in order
+        for i in live:  # no indexer: every causal key in order, or the last `window` of them
             n = int(step.positions[i]) + 1
-            want = S.slots_of_positions(step.page_table[i], torch.arange(n))
-            assert topk_k[i, :n].tolist() == want.tolist() and int((topk_k[i, n:] >= 0).sum()) == 0
+            pos = torch.arange(n)[-cfg.window:] if getattr(cfg, "window", 0) else torch.arange(n)
+            want = S.slots_of_positions(step.page_table[i], pos)
+            got = topk_k[i][topk_k[i] >= 0]
+            assert got.tolist() == want.tolist(), f"selection of row {i}"
     res["q"] = assert_close_hidden(op.q_full[:rows].cpu()[live], r["q_full"][live], "q_lat | q_pe",
                                    scale=float(r["q_full"].abs().max()))
     # ---- attention half on the kernel's own selection

@@ -91,7 +91,8 @@ def test_stack_replays_from_one_graph():
     # here: one request of 5 verify rows and a second of 2
     steps = [synth.verify_step(cfg, 7, 1, ctx, layer=i) for i in range(n_layers)]
     tables = [_tables(s) for s in steps]
-    st = DecoderStack(cfg, ws, DEV, max_ctx=192, draft_weights=synth.layer_weights(cfg, 0, DEV, layer=99))
+    dw = synth.layer_weights(cfg, 0, DEV, layer=99)
+    st = DecoderStack(cfg, ws, DEV, max_ctx=192, draft_weights=dw)
     h = torch.randn(rows, cfg.hidden, generator=torch.Generator().manual_seed(6)).bfloat16().to(DEV)
     draft_tables = _tables(synth.verify_step(cfg, 7, 1, ctx, layer=99))
     x0, logits0 = st.step(h, tables, draft_tables)
@@ -106,13 +107,91 @@ def test_stack_replays_from_one_graph():
         assert torch.equal(x, x0) and torch.equal(logits, logits0)
     assert logits0.shape == (rows, cfg.vocab) and torch.isfinite(logits0).all()
     # oracle chain over the layers: cosine (selections are whole contexts here, no indexer)
-    hh = h.cpu()
+    # oracle, layer by layer, each fed the kernels' own input rows of that layer (stage isolation: what layer i reads is
+    # layer i - 1's `out` buffer), held to cosine 0.999 per layer and per row
+    F = torch.nn.functional
+    x_in = h.cpu()
     for i in range(n_layers):
         s = steps[i]
-        hh, _ = OL.layer_all_ranks(cfg, [_cpu(ws[i])], hh, s.positions, s.slots, s.page_table, s.cos, s.sin,
-                                   s.kv_pages.clone(), None)
-    cos = torch.nn.functional.cosine_similarity(x0.cpu().float().flatten(), hh.float().flatten(), dim=0)
-    assert float(cos) >= 0.995, f"cosine after {n_layers} layers {float(cos):.6f}"
-    ref_logits = S.tail_logits(hh, _cpu(ws[-1])["final_norm"], cfg.eps, _cpu(ws[-1])["lm_head"])
-    cos = torch.nn.functional.cosine_similarity(logits0.cpu().flatten(), ref_logits.flatten(), dim=0)
-    assert float(cos) >= 0.995
+        ref_i, _ = OL.layer_all_ranks(cfg, [_cpu(ws[i])], x_in, s.positions, s.slots, s.page_table, s.cos, s.sin,
+                                      s.kv_pages.clone(), None)
+        got_i = st.layers[i].ffn.out[:rows].cpu()
+        cos = F.cosine_similarity(got_i.float(), ref_i.float(), dim=-1)
+        assert float(cos.min()) >= 0.999, f"layer {i}: min per-row cosine {float(cos.min()):.6f}"
+        x_in = got_i
+    assert torch.equal(x_in, x0.cpu())
+    ref_logits = S.tail_logits(x0.cpu(), _cpu(ws[-1])["final_norm"], cfg.eps, _cpu(ws[-1])["lm_head"])
+    cos = F.cosine_similarity(logits0.cpu(), ref_logits, dim=-1)
+    assert float(cos.min()) >= 0.999
+    assert torch.equal(logits0.argmax(-1).cpu(), ref_logits.argmax(-1))
+    # the draft stage's output against the oracle on the draft's own tables and weights
+    ds = synth.verify_step(cfg, 7, 1, ctx, layer=99)
+    dref, _ = OL.layer_all_ranks(cfg, [_cpu(dw)], h.cpu(), ds.positions, ds.slots,
+                                 ds.page_table, ds.cos, ds.sin, ds.kv_pages.clone(), None)
+    dcos = F.cosine_similarity(st.draft_out.cpu().float(), dref.float(), dim=-1)
+    assert float(dcos.min()) >= 0.999, f"draft stage: min per-row cosine {float(dcos.min()):.6f}"
+
+
+def test_draft_layer_attends_its_window_and_routes_top3():
+    """The draft model's stage (reference ``deepseek_v41/draft.py``): the target's layer with 128 experts top-3 (here 8,
+    top-3) and window-only attention.  A block of 5 verify rows of one request + 3 of another: each row selects exactly
+    its last `window` keys (its earlier drafts among them), and the layer matches the oracle stage by stage."""
+    from layer_checks import check_mla_layer
+    from sgl_amd_mono_b200.layer import MlaLayerOp
+
+    cfg = replace(CFG_TINY_FLASH, name="tiny_draft", n_experts=8, top_k=3, window=128 + 16, vocab=0)
+    w = synth.layer_weights(cfg, 0, DEV)
+    step = synth.verify_step(cfg, n_req=2, tokens=4, ctx=700)
+    rows = 8
+    h = torch.randn(rows, cfg.hidden, generator=torch.Generator().manual_seed(8)).bfloat16()
+    op = MlaLayerOp(cfg, w, DEV, max_ctx=704)
+    assert op.topk == 192 and op.window == 144
+    tables = _tables(step)
+    out = op.launch(h.to(DEV), tables).clone()
+    torch.cuda.synchronize()
+    assert ops.guard_read(op.guard)[0] == 0
+    res = check_mla_layer(cfg, op, w, step, tables, h, out)
+    assert op.ffn.ids[:rows].shape[1] == 3
+    print("draft layer:", res["h1"], res["out"])
+    # a short context (fewer keys than the window): every key, in order
+    step2 = synth.verify_step(cfg, n_req=1, tokens=3, ctx=100)
+    h2 = h[:3]
+    t2 = _tables(step2)
+    out2 = op.launch(h2.to(DEV), t2).clone()
+    check_mla_layer(cfg, op, w, step2, t2, h2, out2, chain=False)
+
+
+def test_ffn_runner_takes_the_attention_output_through_the_seam():
+    """``FfnRunner(attn, residual, weights, slots) -> (out, res_out)`` (``minimax_m31/runner.py:145-167``): o_proj of the
+    rank's attention output, the attention reduction and residual, then the MoE block; a pad row joins no expert."""
+    from sgl_amd_mono_b200.config import CFG_TINY
+    from sgl_amd_mono_b200.minimax_m31.runner import FfnRunner
+    from oracle import quant as Q
+    from util import assert_close_hidden
+
+    cfg = replace(CFG_TINY, index_heads=0)
+    w = synth.layer_weights(cfg, 0, DEV)
+    rows = 5
+    g = torch.Generator().manual_seed(12)
+    attn = torch.randn(rows, cfg.heads_local * cfg.v_head, generator=g).bfloat16()
+    residual = torch.randn(rows, cfg.hidden, generator=g).bfloat16()
+    slots = torch.tensor([3, 4, -1, 9, 11], dtype=torch.int64)
+    run = FfnRunner(cfg, w, DEV)
+    out, res_out = run(attn.to(DEV), residual.to(DEV), w, slots.to(DEV))
+    torch.cuda.synchronize()
+    assert ops.guard_read(run.guard)[0] == 0
+    wc = _cpu(w)
+    live = slots >= 0
+    part = attn.float() @ Q.fp8_block_dequant(wc["o_proj"], wc["o_proj_s"]).T
+    h1 = S.allreduce_rank_order([part * live[:, None]], residual)
+    assert_close_hidden(res_out, h1, "residual after the seam", scale=float((h1.float() - residual.float()).abs().max()))
+    assert torch.equal(res_out[2].cpu(), residual[2])
+    mp, ids, _, _ = OL.moe_partial(cfg, wc, res_out.cpu(), live)
+    ref = S.allreduce_rank_order([mp], res_out.cpu())
+    assert torch.equal(run.ffn.ids[:rows].cpu()[live], ids[live])
+    assert_close_hidden(out, ref, "FFN output", scale=float((ref.float() - res_out.cpu().float()).abs().max()), max_abs=4e-2)
+    assert torch.equal(out[2].cpu(), res_out[2].cpu()), "a pad row's MoE output is zero"
+    with pytest.raises(ValueError, match="bound to the tensors"):
+        run(attn.to(DEV), residual.to(DEV), dict(w), slots.to(DEV))
+    out_b, res_b = run(None, residual.to(DEV), None, slots.to(DEV))
+    assert res_b.data_ptr() == residual.to(DEV).data_ptr() or torch.equal(res_b.cpu(), residual)
