@@ -639,6 +639,22 @@ class AllReduceWorkload:
             dist.all_reduce(self.msg)
 
         self.g_ours, self.g_nccl = self._graph(ours), self._graph(nccl)
+        # the NVLS variant: the same kernel, each word pushed by one multimem.st through the switch
+        self.mc_us, self.mc_note = None, None
+        try:
+            from sgl_amd_mono_b200.common.peer import MulticastPeerBuffer
+
+            self.peer_mc = MulticastPeerBuffer(self.n, rank, world, dist.group.WORLD, dev)
+            self.out_mc = torch.zeros_like(self.out)
+
+            def ours_mc():
+                ops.reduce_rows(self.rows, self.n, self.part, 1, self.out_mc, residual=self.res, peer=self.peer_mc, site=0,
+                                guard=self.peer_mc.guard, deadline_s=10.0)
+                ops.epoch_advance(self.peer_mc.guard)
+
+            self.g_mc = self._graph(ours_mc)
+        except Exception as e:  # raised on every rank together (no multicast address): reported, not hidden
+            self.g_mc, self.mc_note = None, f"{type(e).__name__}: {e}"[:200]
         # correctness against NCCL's sum of the same bf16 partials (NCCL's order is unspecified: tolerance)
         self.msg.copy_(self.part[0, : self.rows].bfloat16())
         self.g_nccl.replay()
@@ -651,6 +667,13 @@ class AllReduceWorkload:
         if rc:
             raise RuntimeError(f"guard words {words}")
         self.nccl_us = self._time(self.g_nccl)
+        if self.g_mc is not None:
+            self.g_mc.replay()
+            torch.cuda.synchronize()
+            rc, words = ops.guard_read(self.peer_mc.guard)
+            if rc or not torch.equal(self.out_mc, self.out):
+                raise RuntimeError(f"multicast pushes changed the all-reduce's bits (guard words {words})")
+            self.mc_us = self._time(self.g_mc)
 
     def check(self):
         rc, words = self.ops.guard_read(self.peer.guard)
@@ -698,6 +721,7 @@ class AllReduceWorkload:
     def config(self):
         return {"workload": self.name, "rows": self.rows, "n": self.n, "tp": self.world,
                 "nccl_allreduce_us": self.nccl_us, "in_kernel_allreduce_us_back_to_back": self._time(self.g_ours),
+                "in_kernel_allreduce_multicast_us": self.mc_us, "multicast_unavailable": self.mc_note,
                 "nvlink_peak_gbs_per_direction": 900, "l2": "256 MiB buffer written between timed iterations"}
 
     def cpu_sample(self):

@@ -365,6 +365,12 @@ typedef struct mono_reduce_args {
     int site;
     int32_t* guard;
     const uint64_t* peer_guards; /* device array [world]: every rank's guard words, or NULL */
+    /* NVLS variant of the push: the multicast address of the region (the same offset in every rank's
+     * buffer reaches all of them through the switch), or 0 for one st.relaxed.sys store per peer.  A rank's
+     * word goes out as ONE multimem.st; the waits, the reads (this rank's own copy) and the rank-ordered
+     * f32 sum are the same, so both variants give the same bits.  No reduction happens in the switch: an
+     * order the hardware chooses would let routing decisions differ between ranks. */
+    uint64_t mc_ptr;
 } mono_reduce_args;
 size_t mono_reduce_peer_bytes(int rows, int n, int world);
 int mono_reduce_launch(const mono_reduce_args* a, void* stream);

@@ -134,3 +134,68 @@ class PeerBuffer:
         if self.local:
             self.backend.free(self.local)
             self.local = 0
+
+
+class MulticastPeerBuffer:
+    """The same buffer over NVLS: symmetric memory bound to an NVLink multicast object, so that a rank's push is one
+    ``multimem.st`` that the switch delivers to every rank's copy (the reads, the waits and the rank-ordered sum do
+    not change; ``north_star``: "P2P and NVLS-multicast stores").  The allocation, the handle exchange and the
+    multicast binding are torch's symmetric memory (``torch.distributed._symmetric_memory``): plumbing, as the
+    reference's is HIP IPC.  Collective: every rank of ``group`` builds it with the same sizes; all ranks refuse
+    together when the multicast address is missing on any of them (no NVSwitch, or NVLS off)."""
+
+    def __init__(self, n: int, rank: int, world: int, group, device, logits_local: int = 0):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.rank, self.world, self.n, self.device = rank, world, n, device
+        self.region = region_bytes(n, world)
+        self.logits_bytes = 2 * 16 * (world * logits_local // 2) * 8
+        self.nbytes = GUARD_BYTES + N_REGIONS * self.region + self.logits_bytes
+        name = group.group_name if hasattr(group, "group_name") else group
+        self.buf = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        torch.cuda.synchronize()
+        self.handle = symm_mem.rendezvous(self.buf, name)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        oks: list = [None] * world
+        dist.all_gather_object(oks, mc != 0, group=group)
+        if not all(oks):
+            raise RuntimeError(f"NVLS multicast is not available on ranks {[r for r, ok in enumerate(oks) if not ok]}: "
+                               "the all-reduce keeps its P2P stores (PeerBuffer)")
+        self.mc = mc
+        self.local = self.ptrs[rank]
+        self.guard = _Ptr(self.local)
+        self.guard_table = torch.tensor(self.ptrs, dtype=torch.int64, device=device)
+        self._regions = [torch.tensor([p + GUARD_BYTES + i * self.region for p in self.ptrs], dtype=torch.int64, device=device)
+                         for i in range(N_REGIONS)]
+        self.logits_table = None
+        if self.logits_bytes:
+            self.logits_table = torch.tensor([p + GUARD_BYTES + N_REGIONS * self.region for p in self.ptrs], dtype=torch.int64,
+                                             device=device)
+
+    def region_table(self, site: int):
+        return self._regions[site % N_REGIONS]
+
+    def mc_region(self, site: int) -> int:
+        """The multicast address of the region ``site`` pushes into."""
+        return self.mc + GUARD_BYTES + (site % N_REGIONS) * self.region
+
+    def release(self) -> None:
+        self.handle = None
+        self.buf = None
+
+
+def make_peer_buffer(n: int, rank: int, world: int, group, device, logits_local: int = 0, multicast=None):
+    """The all-reduce's peer buffer: P2P stores over CUDA IPC, or ``multimem.st`` over NVLS when ``multicast`` is true
+    (default: the environment's ``MONO_AR_MULTICAST=1``).  There is no silent fallback: asking for multicast where the
+    ranks have none raises on every rank."""
+    import os
+
+    if multicast is None:
+        multicast = os.environ.get("MONO_AR_MULTICAST") == "1"
+    if multicast:
+        return MulticastPeerBuffer(n, rank, world, group, device, logits_local=logits_local)
+    return PeerBuffer(n, rank, world, group, device, logits_local=logits_local)

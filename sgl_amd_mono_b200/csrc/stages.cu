@@ -419,6 +419,11 @@ __device__ __forceinline__ uint2 ld_sys_v2(uint64_t addr) {
     asm volatile("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(addr) : "memory");
     return v;
 }
+// One store that the switch delivers to every rank's copy of a multicast-bound buffer (NVLS).
+__device__ __forceinline__ void st_multimem_v2(uint64_t mc_addr, uint32_t a, uint32_t b) {
+    const uint64_t v = (uint64_t)a | ((uint64_t)b << 32);
+    asm volatile("multimem.st.relaxed.sys.global.b64 [%0], %1;" ::"l"(mc_addr), "l"(v) : "memory");
+}
 __device__ __forceinline__ void st_sys_u32(uint64_t addr, uint32_t a) {
     asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(a) : "memory");
 }
@@ -490,7 +495,9 @@ __global__ void __launch_bounds__(kReduceThreads) reduce_kernel(const mono_reduc
             const uint32_t word = *reinterpret_cast<uint32_t*>(&pb);
             const size_t slot_pairs = (size_t)kMaxRows * pairs;
             const size_t my_off = (((size_t)parity * a.world + a.rank) * slot_pairs + (size_t)row * pairs + pc) * 8;
-            for (int d = 0; d < a.world; ++d) st_sys_v2(a.peer_ptrs[d] + my_off, word, tag);
+            if (a.mc_ptr) st_multimem_v2(a.mc_ptr + my_off, word, tag);
+            else
+                for (int d = 0; d < a.world; ++d) st_sys_v2(a.peer_ptrs[d] + my_off, word, tag);
             acc0 = 0.f;
             acc1 = 0.f;
             const uint64_t mine = a.peer_ptrs[a.rank];
@@ -572,9 +579,14 @@ __global__ void __cluster_dims__(C, 1, 1) __launch_bounds__(kRnThreads) reduce_n
             const int pc = i >> 1;  // this thread's two pairs: pc, pc + 1
             const size_t my_off = (((size_t)parity * r.world + r.rank) * slot_pairs + (size_t)row * pairs + pc) * 8;
             const uint32_t w0 = *reinterpret_cast<const uint32_t*>(&pb0), w1 = *reinterpret_cast<const uint32_t*>(&pb1);
-            for (int d = 0; d < r.world; ++d) {
-                st_sys_v2(r.peer_ptrs[d] + my_off, w0, tag);
-                st_sys_v2(r.peer_ptrs[d] + my_off + 8, w1, tag);
+            if (r.mc_ptr) {
+                st_multimem_v2(r.mc_ptr + my_off, w0, tag);
+                st_multimem_v2(r.mc_ptr + my_off + 8, w1, tag);
+            } else {
+                for (int d = 0; d < r.world; ++d) {
+                    st_sys_v2(r.peer_ptrs[d] + my_off, w0, tag);
+                    st_sys_v2(r.peer_ptrs[d] + my_off + 8, w1, tag);
+                }
             }
             acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
             const uint64_t mine = r.peer_ptrs[r.rank];

@@ -104,7 +104,7 @@ def _build(model, hf_config, ctx):
                           layer=i, deadline_s=ctx.deadline_s, max_rows=max(ctx.widths), copies=ctx.copies)
 
     return build_layers(model, c, ctx, _covered_layers(hf_config), make,
-                        bind=lambda i: _bound(model, hf_config, ctx.tp_size, ctx.copies, i))
+                        bind=lambda i: _bound(model, hf_config, ctx.tp_size, ctx.copies, i), numerics=NUMERICS)
 
 
 SPEC = MonoSpec(

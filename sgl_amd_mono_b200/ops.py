@@ -315,6 +315,7 @@ def _reduce_args(rows, n, partial, nsum, out, residual, slots, peer, site, guard
         a.world, a.rank = peer.world, peer.rank
         a.peer_ptrs = peer.region_table(site).data_ptr()
         a.peer_guards = peer.guard_table.data_ptr()
+        a.mc_ptr = peer.mc_region(site) if getattr(peer, "mc_region", None) is not None else 0
         a.tag, a.parity = 0, 0
         a.deadline_ns = int(deadline_s * 1e9)
     if not 0 <= site <= 254:

@@ -14,6 +14,7 @@ from types import SimpleNamespace
 import torch
 
 from . import _lib as L
+from . import check
 from .config import KV_PAGE_BYTES, LayerConfig
 from .registry import BuildContext, Plan
 
@@ -71,8 +72,9 @@ def step_tables(plan: Plan, positions, forward_batch, rows: int, max_position: i
 class Built:
     """The routed forward of a model whose covered layers run on the monokernels."""
 
-    def __init__(self, model, cfg: LayerConfig, ops_by_layer: dict, max_rows: int, max_position: int):
+    def __init__(self, model, cfg: LayerConfig, ops_by_layer: dict, max_rows: int, max_position: int, numerics=None):
         self.model, self.cfg, self.ops, self.max_rows, self.max_position = model, cfg, ops_by_layer, max_rows, max_position
+        self.numerics = numerics  # the spec's bounds, read by check mode (MONO_CHECK=1)
 
     def forward(self, plan: Plan, input_ids, positions, forward_batch, input_embeds=None, *args, **kw):
         rows = plan.key.rows
@@ -94,7 +96,12 @@ class Built:
                                    f"needs contiguous uint8 [pages, {KV_PAGE_BYTES}]")
             tables = StepTables(st.positions, st.slots, st.page_table, caches.kv, getattr(caches, "idx", None),
                                 forward_batch.cos, forward_batch.sin)
-            h = op.launch(h, tables)
+            if self.numerics is not None and check.enabled():
+                # check mode (glm53/spec.py:402-417): the same rows through the model's own layer, compared as they run
+                ref = lambda x, t, layer=layer: {"out": layer.forward(x, positions, forward_batch)}  # noqa: E731
+                h, _ = check.check_layer_launch(i, self.numerics, op, h, tables, ref)
+            else:
+                h = op.launch(h, tables)
         return self.model.finish(h, forward_batch) if hasattr(self.model, "finish") else h
 
 
@@ -103,7 +110,7 @@ def model_layers(model):
     return getattr(model, "model", model).layers
 
 
-def build_layers(model, cfg: LayerConfig, ctx: BuildContext, covered: list[int], make_op, bind=None) -> Built:
+def build_layers(model, cfg: LayerConfig, ctx: BuildContext, covered: list[int], make_op, bind=None, numerics=None) -> Built:
     """Builds one op per covered layer in layer order (a collective when tp_size > 1:
     every rank builds the same runtimes in the same order, ``glm53/spec.py:499-581``).  ``bind(i)`` returns
     layer i's tensors bound to SGLang's storage and records every one-time copy in ``ctx.copies``; without
@@ -118,4 +125,4 @@ def build_layers(model, cfg: LayerConfig, ctx: BuildContext, covered: list[int],
     for key in list(ctx.copies)[before:]:
         t = ctx.copies[key]
         log.info("  copy %s: %s %s", key, getattr(t, "dtype", type(t).__name__), tuple(getattr(t, "shape", ())))
-    return Built(model, cfg, ops_by_layer, max(ctx.widths), ctx.max_context - 1)
+    return Built(model, cfg, ops_by_layer, max(ctx.widths), ctx.max_context - 1, numerics=numerics)

@@ -69,6 +69,39 @@ def main() -> None:
     bounds = [1, 4096, 4097, 32769, 65536, 65537, 131072, 262192, (1 << 20) - 1, 1 << 20]
     fx["slice_bounds"] = bounds
     fx["slices"] = [select_slices(b) for b in bounds]
+    # exact top-k of a row's own scores (glm53/check.py:100-117 `_exact_topk_outputs`): the reference's checker counts
+    # how many keys of ITS exact top-k (radix keys, stable descending sort = ties to the lowest position) a selection
+    # misses.  Stored: the inputs, the reference's own top-2048 slot sets, and the checker's verdict on the selection
+    # the oracle (oracle/stages.py exact_topk_positions) makes from the same scores.
+    import sys
+
+    sys.path.insert(0, str(Path(__file__).resolve().parents[2]))
+    from oracle import stages as S  # the restatement under test
+
+    from sgl_amd_mono.glm53.gfx950.runner import TOPK
+
+    rows, n_max, per = 4, 6000, -(-6000 // 64)
+    sc = torch.randn(rows, n_max, generator=g)
+    sc[1] = sc[1].round()             # long runs of exact ties around the threshold
+    sc[2, ::2] = -0.5                 # ties among negative scores
+    sc[3, :2100] = torch.linspace(4, -4, 2100)
+    positions = torch.tensor([5999, 4000, 2500, 2099])  # row 3 sees 2100 keys: 52 more than TOPK
+    page_table = (torch.randperm(rows * per, generator=g) + 1).to(torch.int32).reshape(rows, per)
+    picked, indptr, ref_sets = [], [0], []
+    for r in range(rows):
+        n = int(positions[r]) + 1
+        pos = S.exact_topk_positions(sc[r], n, TOPK)
+        picked += S.slots_of_positions(page_table[r], pos).tolist()
+        indptr.append(len(picked))
+        keys = glm_check._radix_keys(sc[r, :n].contiguous().view(torch.int32))
+        ref_pos = torch.sort(keys, descending=True, stable=True).indices[:TOPK]
+        ref_sets.append(sorted((page_table[r, ref_pos // 64].long() * 64 + ref_pos % 64).tolist()))
+    step = SimpleNamespace(indptr=torch.tensor(indptr), topk=torch.tensor(picked), positions=positions,
+                           page_table=page_table, req_ids=torch.arange(rows))
+    verdict = glm_check._exact_topk_outputs(step, sc.view(torch.int32), rows)
+    assert verdict == {"topk_exact": {"max_abs": 0.0}}, verdict
+    fx["topk_scores"], fx["topk_positions"], fx["topk_page_table"] = sc, positions, page_table
+    fx["topk_k"], fx["topk_ref_sets"], fx["topk_checker_verdict"] = TOPK, ref_sets, verdict
     torch.save(fx, OUT)
     print("wrote", OUT, OUT.stat().st_size, "bytes")
 

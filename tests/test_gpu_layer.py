@@ -208,3 +208,41 @@ def test_reductions_fused_into_the_norm_staging_launches(monkeypatch):
     assert torch.equal(op.ffn.ids[:rows], op2.ffn.ids[:rows])
     d = float((out.float() - out2.float()).abs().max())
     assert d <= 4e-2 * max(1.0, float(out2.float().abs().max())), f"fused and separate reductions differ by {d}"
+
+
+def test_check_mode_compares_a_launch_with_the_reference_layer_as_it_runs():
+    """``check.check_layer_launch`` (reference ``glm53/check.py:183-278``): the step's index rows are poisoned, the layer
+    is launched, and output, written cache rows, selection and routing are held to the spec's NUMERICS; a perturbed
+    reference output must be refused (negative control)."""
+    from layer_checks import cpu_weights
+    from oracle import layers as OL
+    from sgl_amd_mono_b200 import check
+    from sgl_amd_mono_b200.glm53.spec import NUMERICS
+    from sgl_amd_mono_b200.layer import MlaLayerOp
+    from sgl_amd_mono_b200.registry import Numerics, NumericsKind
+
+    cfg, rows, ctx = CFG_TINY, 5, 900
+    w = synth.layer_weights(cfg, 0, DEV, out_scale=0.1)
+    step = synth.decode_step(cfg, rows, ctx)
+    h = (torch.randn(rows, cfg.hidden, generator=torch.Generator().manual_seed(4)) * 0.25).bfloat16()
+    op = MlaLayerOp(cfg, w, DEV, max_ctx=-(-ctx // 64) * 64)
+    dstep = _step_to(step, DEV)
+    wc = cpu_weights(w)
+
+    def ref_layer(x, t, bump=0.0):
+        out, _ = OL.layer_all_ranks(cfg, [wc], x.cpu(), step.positions, step.slots, step.page_table, step.cos, step.sin,
+                                    step.kv_pages.clone(), step.idx_pages.clone())
+        return {"out": (out.float() + bump).to(DEV)}
+
+    # unit-scale streams: the literal 2e-2 / 0.999 bounds of NUMERICS apply as they stand
+    bounds = Numerics(NumericsKind.TOLERANCE, dict(NUMERICS.bounds))
+    out, m = check.check_layer_launch(0, bounds, op, h.to(DEV), dstep, ref_layer)
+    assert m["layer.topk_exact.max_abs"] == 0.0 and m["layer.router_ids.max_abs"] == 0.0
+    assert m["layer.streams.cosine"] >= 0.999 and m["layer.streams.max_abs"] <= 2e-2
+    # the poisoned scale codes of the step's own index rows were overwritten before anything read them
+    got_idx = dstep.idx_pages.cpu()
+    for i in range(rows):
+        p, o = divmod(int(step.slots[i]), 64)
+        assert 255 not in got_idx[p, 64 * 64 + o * 4 : 64 * 64 + (o + 1) * 4].tolist()
+    with pytest.raises(check.CheckError, match="layer.streams.max_abs"):
+        check.check_layer_launch(0, bounds, op, h.to(DEV), dstep, lambda x, t: ref_layer(x, t, bump=0.05))

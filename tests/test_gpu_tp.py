@@ -20,7 +20,40 @@ def _free_port():
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize("world,rows,ctx", [(2, 4, 400), (2, 13, 300)])
+def _run_ranks(world, rows, ctx, outdir, env=None):
+    import os
+
+    here = Path(__file__).resolve().parent
+    port = _free_port()
+    procs = [subprocess.Popen([sys.executable, str(here / "tp_worker.py"), str(r), str(world), str(port), str(rows),
+                               str(ctx), str(outdir)], env={**os.environ, **(env or {})}) for r in range(world)]
+    for p in procs:
+        assert p.wait(timeout=300) == 0
+    got = []
+    for r in range(world):
+        got.append(torch.load(outdir / f"rank{r}.pt", weights_only=False))
+        (outdir / f"rank{r}.pt").unlink()
+    return got
+
+
+@pytest.mark.parametrize("world,rows,ctx", [(2, 5, 350)])
+def test_tp_multicast_pushes_give_the_bits_of_the_peer_stores(world, rows, ctx):
+    """The NVLS variant (one multimem.st per word, delivered to every rank by the switch) against the P2P variant
+    (one st.relaxed.sys per peer): same waits, same local reads, same rank-ordered sum, so the same bits."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    outdir = Path(__file__).resolve().parent / "_tp_out"
+    outdir.mkdir(exist_ok=True)
+    p2p = _run_ranks(world, rows, ctx, outdir, {"MONO_AR_MULTICAST": "0"})
+    mc = _run_ranks(world, rows, ctx, outdir, {"MONO_AR_MULTICAST": "1"})
+    for r in range(world):
+        assert p2p[r]["rc"] == 0 and mc[r]["rc"] == 0, (p2p[r]["words"], mc[r]["words"])
+        for a, b in zip(p2p[r]["outs"], mc[r]["outs"]):
+            assert torch.equal(a, b), f"rank {r}: multicast pushes changed the result"
+        assert torch.equal(p2p[r]["h1"], mc[r]["h1"])
+
+
+@pytest.mark.parametrize("world,rows,ctx", [(2, 4, 400), (2, 13, 300), (4, 6, 320)])
 def test_tp_layer_ranks_agree_and_match_oracle(world, rows, ctx):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")

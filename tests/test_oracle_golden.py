@@ -97,3 +97,22 @@ def test_route_ties_to_lower_id():
     ids, w = S.route(logits, None, 3, 2.5)
     assert ids.tolist() == [[0, 1, 2]]
     assert torch.allclose(w, torch.full((1, 3), 2.5 / 3))
+
+
+def test_exact_topk_selection_matches_the_references_checker(golden):
+    """``exact_topk_positions`` against ``glm53/check.py:100-117``: on the stored scores (ties at the threshold, ties
+    among negatives, a row barely past 2048 keys) the oracle's selection is, as a set of KV slots, the reference's own
+    exact top-2048, and the reference's checker found nothing missing when the fixture was made."""
+    sc, positions, pt, k = golden["topk_scores"], golden["topk_positions"], golden["topk_page_table"], golden["topk_k"]
+    assert golden["topk_checker_verdict"] == {"topk_exact": {"max_abs": 0.0}}
+    for r in range(sc.shape[0]):
+        n = int(positions[r]) + 1
+        pos = S.exact_topk_positions(sc[r], n, k)
+        assert pos.numel() == k
+        slots = S.slots_of_positions(pt[r], pos).tolist()
+        assert sorted(slots) == golden["topk_ref_sets"][r], f"row {r}"
+        # the published order: keys above the threshold in position order, then the first ties in position order
+        keys = S.radix_key(sc[r, :n].contiguous().view(torch.int32))
+        thr = keys[pos].min()
+        above = pos[keys[pos] > thr]
+        assert above.tolist() == sorted(above.tolist()) and pos[above.numel():].tolist() == sorted(pos[above.numel():].tolist())

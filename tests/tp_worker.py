@@ -18,13 +18,14 @@ def main(rank, world, port, rows, ctx, outdir):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         from sgl_amd_mono_b200 import ops, synth
-        from sgl_amd_mono_b200.common.peer import PeerBuffer
+        from sgl_amd_mono_b200.common.peer import make_peer_buffer
         from sgl_amd_mono_b200.config import CFG_TINY
         from sgl_amd_mono_b200.layer import MlaLayerOp, StepTables
 
         dev = f"cuda:{rank}"
         cfg = CFG_TINY.with_tp(world)
-        peer = PeerBuffer(cfg.hidden, rank, world, dist.group.WORLD, dev)
+        # MONO_AR_MULTICAST=1: the pushes go out as multimem.st through the switch instead of one store per peer
+        peer = make_peer_buffer(cfg.hidden, rank, world, dist.group.WORLD, dev)
         w = synth.layer_weights(cfg, rank, dev)
         step = synth.decode_step(cfg, rows, ctx)
         t = lambda x: x.to(dev)  # noqa: E731
