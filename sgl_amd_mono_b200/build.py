@@ -31,7 +31,10 @@ def sources() -> list[Path]:
 
 def _flags() -> list[str]:
     # MONO_TIMELINE=1: kernels record global-timer stamps at numbered points (csrc/mono_common.cuh)
-    return NVCC_FLAGS + (["-DMONO_TIMELINE"] if os.environ.get("MONO_TIMELINE") == "1" else [])
+    # (MONO_TIMELINE_DEFS: further -D switches of a stamped build, space separated)
+    if os.environ.get("MONO_TIMELINE") != "1":
+        return NVCC_FLAGS
+    return NVCC_FLAGS + ["-DMONO_TIMELINE"] + [f"-D{d}" for d in os.environ.get("MONO_TIMELINE_DEFS", "").split()]
 
 
 def _digest() -> str:

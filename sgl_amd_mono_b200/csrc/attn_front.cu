@@ -12,6 +12,12 @@ extern void mono_set_error(const char* fmt, ...);
 namespace mono {
 
 constexpr int kMidThreads2 = 256;
+MONO_TL_DECLARE(tl_mid)
+#ifdef MONO_TIMELINE
+#define MID_TL(p) do { if (threadIdx.x == 0) tl_mid[blockIdx.y * 16 + blockIdx.x][p] = globaltimer_ns(); } while (0)
+#else
+#define MID_TL(p) do { } while (0)
+#endif
 
 // hi/lo E4M3 planes of 128 bf16-valued floats held 4 per lane (see MONO_ACT_HILO)
 __device__ __forceinline__ void hilo_chunk(const float v[4], int lane, uint8_t* hi, uint8_t* lo, float* scale) {
@@ -48,8 +54,9 @@ __device__ __forceinline__ void fwht128(float* x, int t /* 0..127 */) {
     __syncthreads();
 }
 
-__global__ void __launch_bounds__(kMidThreads2) mla_mid_kernel(const mono_mla_mid_args a) {
+__global__ void __launch_bounds__(kMidThreads2, 1) mla_mid_kernel(const mono_mla_mid_args a) {
     pdl_launch_dependents();
+    MID_TL(0);
     {
         // during the wait for the GEMV before this launch: the norm weights and this row's rotary entries
         // (the step's positions are inputs of the step, not results of that GEMV)
@@ -66,26 +73,35 @@ __global__ void __launch_bounds__(kMidThreads2) mla_mid_kernel(const mono_mla_mi
             prefetch_l2(reinterpret_cast<const __nv_bfloat16*>(a.sin) + pos_ * 32);
         }
     }
+    // grid = (rows, parts): part 0 = q_a, part 1 = latent | rope + cache write, part 2 = index key;
+    // the three are independent, so they run on three CTAs instead of one after the other
+    const int row = blockIdx.x, part = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // the row's position, slot and rotary entries are inputs of the step: read during the wait as well
+    const int64_t pos = a.positions[row];
+    const int64_t slot = a.slots ? a.slots[row] : 1;
+    float ikraw = 0.f, rc = 0.f, rs = 0.f;
+    if (tid < 32 && part != 0) {
+        rc = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.cos)[pos * 32 + tid]);
+        rs = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.sin)[pos * 32 + tid]);
+    }
+    MID_TL(1);
     pdl_wait();
+    MID_TL(2);
     __shared__ __align__(16) float xq[2048 + 64];
     __shared__ __align__(16) float kv[kKvDim];
     __shared__ float ikv[128];
     __shared__ float red[kMidThreads2 / 32];
-    // grid = (rows, parts): part 0 = q_a, part 1 = latent | rope + cache write, part 2 = index key;
-    // the three are independent, so they run on three CTAs instead of one after the other
-    const int row = blockIdx.x, part = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int64_t pos = a.positions[row];
-    const int64_t slot = a.slots ? a.slots[row] : 1;
     const float* src = a.qkv + (size_t)row * a.ld;
     // everything that does not depend on a reduction is fetched up front
-    float ikraw = 0.f, rc = 0.f, rs = 0.f;
     if (a.ik && part == 2 && tid < 128) {
-#pragma unroll 4
-        for (int s = 0; s < a.ik_nsum; ++s) ikraw += a.ik[(size_t)s * a.ik_sum_stride + (size_t)row * a.ik_ld + tid];
-    }
-    if (tid < 32) {
-        rc = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.cos)[pos * 32 + tid]);
-        rs = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.sin)[pos * 32 + tid]);
+        for (int s0 = 0; s0 < a.ik_nsum; s0 += 8) {
+            float t8[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                t8[j] = __ldcg(a.ik + (size_t)min(s0 + j, a.ik_nsum - 1) * a.ik_sum_stride + (size_t)row * a.ik_ld + tid);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ikraw += s0 + j < a.ik_nsum ? t8[j] : 0.f;
+        }
     }
     // ---- q_a: RMSNorm -> bf16 -> hi/lo planes
     // the whole row (q_a | latent | rope) is summed over the K splits with 16-byte loads
@@ -93,12 +109,7 @@ __global__ void __launch_bounds__(kMidThreads2) mla_mid_kernel(const mono_mla_mi
     float ssq = 0.f, ssq_kv = 0.f;
     const int i_lo = part == 0 ? 0 : a.q_lora, i_hi = part == 0 ? a.q_lora : (part == 1 ? a.q_lora + kKvDim : 0);
     for (int i = i_lo + tid * 4; i < i_hi; i += kMidThreads2 * 4) {
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-        for (int s = 0; s < a.nsum; ++s) {
-            const float4 p = *reinterpret_cast<const float4*>(src + (size_t)s * a.sum_stride + i);
-            v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
-        }
+        const float4 v = sum_partials4<16>(src + i, a.sum_stride, a.nsum);
         const float sq = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
         if (i < a.q_lora) {
             *reinterpret_cast<float4*>(xq + i) = v;
@@ -108,8 +119,10 @@ __global__ void __launch_bounds__(kMidThreads2) mla_mid_kernel(const mono_mla_mi
             if (i - a.q_lora < 512) ssq_kv += sq;
         }
     }
+    MID_TL(3);
     if (part == 0) {
         const float r = rsqrtf(block_sum<kMidThreads2 / 32>(ssq, red) / (float)a.q_lora + a.eps);
+        MID_TL(4);
         const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(a.q_a_norm);
         for (int i = tid; i < a.q_lora; i += kMidThreads2) xq[i] = bf16_round(xq[i] * r * __bfloat162float(g[i]));
         __syncthreads();
@@ -120,6 +133,7 @@ __global__ void __launch_bounds__(kMidThreads2) mla_mid_kernel(const mono_mla_mi
             uint8_t* hi = a.qa_planes + (size_t)row * a.qa_ld + c * 128;
             hilo_chunk(v, lane, hi, hi + a.qa_plane_stride, a.qa_scale + (size_t)row * a.qa_scale_ld + c);
         }
+        MID_TL(5);
         return;
     }
     // ---- latent: RMSNorm -> bf16; k_pe: interleaved RoPE -> bf16
@@ -161,6 +175,7 @@ __global__ void __launch_bounds__(kMidThreads2) mla_mid_kernel(const mono_mla_mi
         }
         if (tid == 0) reinterpret_cast<float*>(page + kPage * kKvDim)[off] = exp2_code(code);
     }
+    MID_TL(5);
     return;
     }
     // ---- index key: LayerNorm -> RoPE (dims 0..63) -> FWHT-128 -> E2M1 + E8M0 per 32
@@ -199,24 +214,18 @@ __global__ void __launch_bounds__(kMidThreads2) mla_mid_kernel(const mono_mla_mi
             }
         }
     }
+    MID_TL(5);
 }
 
 // ------------------------------------------------------------------ q_post
-// blocks [0, 8 * heads): one (head, 64 latent columns) each, all rows: q_nope -> bf16,
+// q_post_kernel, 8 * heads blocks: one (head, 64 latent columns) each, all rows: q_nope -> bf16,
 // W_UK absorb; the first block of a head also writes the rotated q_pe.
-// blocks [8 * heads, 8 * heads + rows * index_heads): one index query each.
+// q_post_index_kernel, rows * index_heads blocks: one index query each.
 constexpr int kQPostThreads = 128;
 
 __global__ void __launch_bounds__(kQPostThreads) q_post_kernel(const mono_q_post_args a) {
     pdl_launch_dependents();
-    if ((int)blockIdx.x < a.heads * 8) {
-        // during the wait for the GEMV before this launch: this block's 128 x 64-byte slab of W_UK
-        const int h_ = blockIdx.x >> 3, cq_ = blockIdx.x & 7;
-        prefetch_l2(a.kv_b + ((size_t)h_ * 256 + threadIdx.x) * 512 + cq_ * 64);
-    }
-    pdl_wait();
-    __shared__ float qn[kMaxRows][128];
-    __shared__ float iq[128];
+    __shared__ __align__(16) float qn[kMaxRows][128];
     const int tid = threadIdx.x;
     const __nv_bfloat16* cosb = reinterpret_cast<const __nv_bfloat16*>(a.cos);
     const __nv_bfloat16* sinb = reinterpret_cast<const __nv_bfloat16*>(a.sin);
@@ -224,75 +233,140 @@ __global__ void __launch_bounds__(kQPostThreads) q_post_kernel(const mono_q_post
         // one block per (head, 64-column slab of the latent): 8 x heads blocks keep every SM busy
         const int h = blockIdx.x >> 3, cq0 = blockIdx.x & 7;
         __nv_bfloat16* qf = reinterpret_cast<__nv_bfloat16*>(a.q_full);
-        for (int r = a.rows; r < kMaxRows; ++r) qn[r][tid] = 0.f;
-#pragma unroll 4
-        for (int r = 0; r < a.rows; ++r) {
-            const float* src = a.qb + (size_t)r * a.ld + h * 192;
-            float v = 0.f;
-#pragma unroll 4
-            for (int s = 0; s < a.nsum; ++s) v += src[(size_t)s * a.sum_stride + tid];
-            qn[r][tid] = bf16_round(v);
-            if (cq0 == 0 && tid < 32) {
-                float x0 = 0.f, x1 = 0.f;
-                for (int s = 0; s < a.nsum; ++s) {
-                    x0 += src[(size_t)s * a.sum_stride + 128 + 2 * tid];
-                    x1 += src[(size_t)s * a.sum_stride + 128 + 2 * tid + 1];
-                }
-                const int64_t pos = a.positions[r];
-                const float c = __bfloat162float(cosb[pos * 32 + tid]), sn = __bfloat162float(sinb[pos * 32 + tid]);
-                __nv_bfloat16* o = qf + ((size_t)r * a.heads + h) * kKvDim + 512;
-                o[2 * tid] = __float2bfloat16_rn(x0 * c - x1 * sn);
-                o[2 * tid + 1] = __float2bfloat16_rn(x0 * sn + x1 * c);
-            }
-        }
-        // q_lat[c] = sum_d W_UK[d][c] * q_nope[d].  All 512 sixteen-byte loads of a
-        // 128 x 64-column slab are issued before any is used (4 per thread), so the
-        // 64 KB of a head arrive in four latency periods instead of 128.
-        __shared__ __align__(16) uint8_t wt[128][64 + 16];
-        for (int cq = cq0; cq < cq0 + 1; ++cq) {
-            __syncthreads();
-            uint4 v[4];
+        // During the wait for the GEMV before this launch: this block's 128 x 64-byte slab of W_UK (all 512
+        // sixteen-byte loads issued before any is used, 4 per thread), stored transposed ([column][d], so that
+        // a thread reads four d of its column in one word), and, in the block that rotates q_pe, every row's
+        // rotary entries (positions and tables are inputs of the step).
+        __shared__ __align__(16) uint8_t wt[64][128 + 4];
+        __shared__ float rot[2][kMaxRows][32];
+        {
+            uint4 wv4[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int idx = tid + i * kQPostThreads;  // 0..511: row d = idx / 4, 16-byte piece idx % 4
-                v[i] = __ldg(reinterpret_cast<const uint4*>(a.kv_b + ((size_t)h * 256 + (idx >> 2)) * 512 + cq * 64) + (idx & 3));
+                wv4[i] = __ldg(reinterpret_cast<const uint4*>(a.kv_b + ((size_t)h * 256 + (idx >> 2)) * 512 + cq0 * 64) + (idx & 3));
+            }
+            if (cq0 == 0 && tid < 32) {
+                int64_t pos[kMaxRows];
+#pragma unroll
+                for (int r = 0; r < kMaxRows; ++r) pos[r] = a.positions[min(r, a.rows - 1)];
+#pragma unroll
+                for (int r = 0; r < kMaxRows; ++r) {
+                    rot[0][r][tid] = __bfloat162float(cosb[pos[r] * 32 + tid]);
+                    rot[1][r][tid] = __bfloat162float(sinb[pos[r] * 32 + tid]);
+                }
             }
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int idx = tid + i * kQPostThreads;
-                *reinterpret_cast<uint4*>(&wt[idx >> 2][(idx & 3) * 16]) = v[i];
-            }
-            __syncthreads();
-            // thread = (column c = tid % 64, row half = tid / 64): rows r = half, half + 2, ...
-            const int c = tid & 63, half = tid >> 6;
-            float acc[kMaxRows / 2];
+                const uint32_t w[4] = {wv4[i].x, wv4[i].y, wv4[i].z, wv4[i].w};
 #pragma unroll
-            for (int r = 0; r < kMaxRows / 2; ++r) acc[r] = 0.f;
-#pragma unroll 8
-            for (int d = 0; d < 128; ++d) {
-                const float w = e4m3_to_f32(wt[d][c]);
-#pragma unroll
-                for (int r = 0; r < kMaxRows / 2; ++r) acc[r] += qn[2 * r + half][d] * w;
-            }
-            const float sc = a.kv_b_scale[(size_t)(h * 2) * 4 + (cq * 64) / 128];
-#pragma unroll
-            for (int r = 0; r < kMaxRows / 2; ++r) {
-                const int row = 2 * r + half;
-                if (row < a.rows) qf[((size_t)row * a.heads + h) * kKvDim + cq * 64 + c] = __float2bfloat16_rn(acc[r] * sc);
+                for (int j = 0; j < 16; ++j) wt[(idx & 3) * 16 + j][idx >> 2] = (uint8_t)(w[j >> 2] >> (8 * (j & 3)));
             }
         }
-    } else {
-        const int idx = blockIdx.x - a.heads * 8;
+        const float wsc = a.kv_b_scale[(size_t)(h * 2) * 4 + (cq0 * 64) / 128];
+        pdl_wait();
+        // the rows' q_nope: one batch of loads per K split, all rows in flight together
+        {
+            float v[kMaxRows];
+#pragma unroll
+            for (int r = 0; r < kMaxRows; ++r) v[r] = 0.f;
+            for (int s = 0; s < a.nsum; ++s) {
+                float t[kMaxRows];
+#pragma unroll
+                for (int r = 0; r < kMaxRows; ++r)
+                    t[r] = __ldcg(a.qb + (size_t)s * a.sum_stride + (size_t)min(r, a.rows - 1) * a.ld + h * 192 + tid);
+#pragma unroll
+                for (int r = 0; r < kMaxRows; ++r) v[r] += t[r];  // rows past the last repeat the last row: not stored below
+            }
+#pragma unroll
+            for (int r = 0; r < kMaxRows; ++r) qn[r][tid] = r < a.rows ? bf16_round(v[r]) : 0.f;
+        }
+        if (cq0 == 0 && tid < 32) {  // q_pe: interleaved rotation of the head's last 64 values
+            float2 xp[kMaxRows];
+#pragma unroll
+            for (int r = 0; r < kMaxRows; ++r) xp[r] = make_float2(0.f, 0.f);
+            for (int s = 0; s < a.nsum; ++s) {
+                float2 t2[kMaxRows];
+#pragma unroll
+                for (int r = 0; r < kMaxRows; ++r)
+                    t2[r] = __ldcg(reinterpret_cast<const float2*>(a.qb + (size_t)s * a.sum_stride + (size_t)min(r, a.rows - 1) * a.ld + h * 192 + 128) + tid);
+#pragma unroll
+                for (int r = 0; r < kMaxRows; ++r) { xp[r].x += t2[r].x; xp[r].y += t2[r].y; }
+            }
+#pragma unroll
+            for (int r = 0; r < kMaxRows; ++r) {
+                if (r < a.rows) {
+                    const float c = rot[0][r][tid], sn = rot[1][r][tid];
+                    __nv_bfloat16* o = qf + ((size_t)r * a.heads + h) * kKvDim + 512;
+                    o[2 * tid] = __float2bfloat16_rn(xp[r].x * c - xp[r].y * sn);
+                    o[2 * tid + 1] = __float2bfloat16_rn(xp[r].x * sn + xp[r].y * c);
+                }
+            }
+        }
+        __syncthreads();
+        // q_lat[c] = sum_d W_UK[d][c] * q_nope[d], d ascending.  thread = (column c = tid % 64, row half = tid / 64):
+        // rows half, half + 2, ...; four d per step: one word of weights, one float4 of each row's q_nope
+        const int c = tid & 63, half = tid >> 6;
+        const int nr = (a.rows + 1 - half) >> 1;  // rows of this half that exist
+        float acc[kMaxRows / 2];
+#pragma unroll
+        for (int r = 0; r < kMaxRows / 2; ++r) acc[r] = 0.f;
+#pragma unroll 4
+        for (int d0 = 0; d0 < 128; d0 += 4) {
+            const uint32_t w4 = *reinterpret_cast<const uint32_t*>(&wt[c][d0]);
+            const float w0 = e4m3_to_f32((uint8_t)w4), w1 = e4m3_to_f32((uint8_t)(w4 >> 8)), w2 = e4m3_to_f32((uint8_t)(w4 >> 16)),
+                        w3 = e4m3_to_f32((uint8_t)(w4 >> 24));
+#pragma unroll
+            for (int r = 0; r < kMaxRows / 2; ++r) {
+                if (r < nr) {
+                    const float4 q4 = *reinterpret_cast<const float4*>(&qn[2 * r + half][d0]);
+                    acc[r] = fmaf(q4.x, w0, acc[r]);
+                    acc[r] = fmaf(q4.y, w1, acc[r]);
+                    acc[r] = fmaf(q4.z, w2, acc[r]);
+                    acc[r] = fmaf(q4.w, w3, acc[r]);
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < kMaxRows / 2; ++r) {
+            const int row = 2 * r + half;
+            if (row < a.rows) qf[((size_t)row * a.heads + h) * kKvDim + cq0 * 64 + c] = __float2bfloat16_rn(acc[r] * wsc);
+        }
+    }
+}
+
+// The index queries alone: a kernel of its own, so that its small blocks (few registers, 1 KB of shared memory) find
+// room on SMs that the head blocks of q_post_kernel already fill while they wait for the same projection.
+__global__ void __launch_bounds__(kQPostThreads) q_post_index_kernel(const mono_q_post_args a) {
+    pdl_launch_dependents();
+    __shared__ float iq[128];
+    const int tid = threadIdx.x;
+    const __nv_bfloat16* cosb = reinterpret_cast<const __nv_bfloat16*>(a.cos);
+    const __nv_bfloat16* sinb = reinterpret_cast<const __nv_bfloat16*>(a.sin);
+    {
+        const int idx = blockIdx.x;
         const int r = idx / a.index_heads, ih = idx - r * a.index_heads;
+        float c = 0.f, sn = 0.f;
+        if (tid < 32) {  // inputs of the step: read during the wait
+            const int64_t pos = a.positions[r];
+            c = __bfloat162float(cosb[pos * 32 + tid]);
+            sn = __bfloat162float(sinb[pos * 32 + tid]);
+        }
+        pdl_wait();
         const float* src = a.iq + (size_t)r * a.iq_ld + ih * 128;
         float v = 0.f;
-        for (int s = 0; s < a.iq_nsum; ++s) v += src[(size_t)s * a.iq_sum_stride + tid];
+        for (int s0 = 0; s0 < a.iq_nsum; s0 += 4) {
+            float t4[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) t4[j] = __ldcg(src + (size_t)min(s0 + j, a.iq_nsum - 1) * a.iq_sum_stride + tid);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v += s0 + j < a.iq_nsum ? t4[j] : 0.f;
+        }
         iq[tid] = v;
         __syncthreads();
         float r0 = 0.f, r1 = 0.f;
         if (tid < 32) {
-            const int64_t pos = a.positions[r];
-            const float c = __bfloat162float(cosb[pos * 32 + tid]), sn = __bfloat162float(sinb[pos * 32 + tid]);
             const float x0 = iq[2 * tid], x1 = iq[2 * tid + 1];
             r0 = x0 * c - x1 * sn;
             r1 = x0 * sn + x1 * c;
@@ -305,6 +379,14 @@ __global__ void __launch_bounds__(kQPostThreads) q_post_kernel(const mono_q_post
 }
 
 }  // namespace mono
+
+#ifdef MONO_TIMELINE
+extern "C" int mono_timeline_read_mla_mid(unsigned long long* out, int* ctas, int* points) {
+    *ctas = MONO_TL_CTAS;
+    *points = MONO_TL_POINTS;
+    return (int)cudaMemcpyFromSymbol(out, mono::tl_mid, sizeof(unsigned long long) * MONO_TL_CTAS * MONO_TL_POINTS);
+}
+#endif
 
 extern "C" int mono_mla_mid_launch(const mono_mla_mid_args* a, void* stream) {
     if (!a || a->rows < 1 || a->rows > MONO_MAX_ROWS || a->q_lora < 128 || a->q_lora > 2048 || (a->q_lora & 127) || !a->qkv ||
@@ -331,8 +413,9 @@ extern "C" int mono_q_post_launch(const mono_q_post_args* a, void* stream) {
         mono_set_error("mono_q_post_launch: rows 1..16, heads and / or index_heads > 0 with their pointers required");
         return MONO_E_ARG;
     }
-    const int blocks = a->heads * 8 + (a->index_heads > 0 ? a->rows * a->index_heads : 0);
-    mono::launch_k(mono::q_post_kernel, blocks, mono::kQPostThreads, 0, (cudaStream_t)stream, *a);
+    // the index queries first: the launch after them (the scores) is the longer path of the two
+    if (a->index_heads > 0) mono::launch_k(mono::q_post_index_kernel, a->rows * a->index_heads, mono::kQPostThreads, 0, (cudaStream_t)stream, *a);
+    if (a->heads > 0) mono::launch_k(mono::q_post_kernel, a->heads * 8, mono::kQPostThreads, 0, (cudaStream_t)stream, *a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_q_post_launch: %s", cudaGetErrorString(e));
     return (int)e;

@@ -39,6 +39,7 @@ constexpr int kTcScRows = 18;  // 16 activation-scale rows, the weight scales, t
 struct TcParams {
     mono_gemv_args a;
     int stages, stage_bytes;
+    int prefetch_tiles;  // weight tiles each CTA pulls towards L2 while the launch before it drains
 };
 
 struct TcSeg {
@@ -377,8 +378,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
         // Weights do not depend on the kernel before this one: while it drains, pull this CTA's tiles towards
         // L2, up to kPrefetchTiles of them (the leading dense jobs only: their task list needs no upstream data).
         // Short projections then run out of L2 instead of paying the DRAM ramp after the wait.
-        constexpr int kPrefetchTiles = 24;  // 384 KB per CTA, 57 MB over the grid
-        int budget = kPrefetchTiles, base = 0;
+        int budget = p.prefetch_tiles, base = 0;
         for (int j = 0; j < p.a.njobs && budget > 0; ++j) {
             const mono_gemv_job& jb = p.a.job[j];
             if (jb.mode != MONO_JOB_DENSE) break;
@@ -490,7 +490,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const __grid_con
                 // (the writer ordered its stores against the async proxy before it released the stamp)
             }
 #ifdef MONO_TIMELINE
-#define TLP(k) do { if (blockIdx.x == 0 && lane == 0 && tl_seg >= 4 && tl_seg < 7) tl_gemv[153][(tl_seg - 4) * 5 + (k)] = globaltimer_ns(); } while (0)
+#ifndef MONO_TLP_FIRST
+#define MONO_TLP_FIRST 4  // the first of the three segments whose producer steps are stamped
+#endif
+#define TLP(k) do { if (blockIdx.x == 0 && lane == 0 && tl_seg >= MONO_TLP_FIRST && tl_seg < MONO_TLP_FIRST + 3) tl_gemv[153][(tl_seg - MONO_TLP_FIRST) * 5 + (k)] = globaltimer_ns(); } while (0)
 #else
 #define TLP(k) do { } while (0)
 #endif
@@ -767,6 +770,9 @@ static int tc_plan(const mono_gemv_args* a, mono::TcParams* pp, int* unit_out, s
     int unit = forced_unit ? forced_unit : (expert && min_seg >= 8) ? 4 : (expert || dense_tiles >= tile_floor * mono_sm_count()) ? 2 : 1;
     if (unit == 4 && planes != 1) unit = 2;  // four-tile stages fit with one activation plane only
     const size_t fixed = 1024 + (size_t)tc_sc_slots(unit) * kTcScRows * kTcMaxSegTiles * sizeof(float) + 512;
+    // MONO_TC_PREFETCH_TILES: 24 tiles = 384 KB per CTA, 57 MB over the grid
+    static const int prefetch_tiles = [] { const char* e = getenv("MONO_TC_PREFETCH_TILES"); return e ? atoi(e) : 24; }();
+    p.prefetch_tiles = prefetch_tiles;
     p.stage_bytes = unit * (kTcABytes + planes * kTcBBytes);
     p.stages = (int)((kSmemMax - fixed) / p.stage_bytes);
     if (p.stages < tc_stages(unit)) return MONO_E_ARG;

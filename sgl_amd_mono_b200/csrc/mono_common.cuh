@@ -243,6 +243,51 @@ __device__ __forceinline__ float e2m1_to_f32(uint32_t c) {
 // issues its weight loads before it polls its inputs, glm53/gfx950/kernel.py:24-27,649-694).
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Sum of `nsum` partial results `stride` floats apart, in the order s = 0, 1, ...  The loads of a batch of B are
+// issued together, so a sum costs one memory round trip per batch rather than one per partial: every load of a
+// batch is unconditional (entries past the last repeat the last partial's address and add +0, which changes no
+// bit of a sum that starts at +0): a load whose only use sits under a condition is moved down into it, behind
+// the additions before it.
+// A 16-byte L2 load that keeps its place in program order among its kind (the compiler neither delays it to its
+// first use nor drops it into a branch): what lets a batch of loads be in flight together.
+__device__ __forceinline__ float4 ld_cg_f4_ordered(const float* p) {
+    float4 v;
+    asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+    return v;
+}
+template <int B>
+__device__ __forceinline__ float4 sum_partials4(const float* p, size_t stride, int nsum) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s0 = 0; s0 < nsum; s0 += B) {
+        float4 t[B];
+#pragma unroll
+        for (int j = 0; j < B; ++j)
+            t[j] = ld_cg_f4_ordered(p + (size_t)min(s0 + j, nsum - 1) * stride);
+#pragma unroll
+        for (int j = 0; j < B; ++j) {
+            const bool on = s0 + j < nsum;  // a select on the value: the load itself stays unconditional
+            v.x += on ? t[j].x : 0.f; v.y += on ? t[j].y : 0.f; v.z += on ? t[j].z : 0.f; v.w += on ? t[j].w : 0.f;
+        }
+    }
+    return v;
+}
+template <int B>
+__device__ __forceinline__ float2 sum_partials2(const float* p, size_t stride, int nsum) {
+    float2 v = make_float2(0.f, 0.f);
+    for (int s0 = 0; s0 < nsum; s0 += B) {
+        float2 t[B];
+#pragma unroll
+        for (int j = 0; j < B; ++j)
+            t[j] = __ldcg(reinterpret_cast<const float2*>(p + (size_t)min(s0 + j, nsum - 1) * stride));
+#pragma unroll
+        for (int j = 0; j < B; ++j) {
+            const bool on = s0 + j < nsum;
+            v.x += on ? t[j].x : 0.f; v.y += on ? t[j].y : 0.f;
+        }
+    }
+    return v;
+}
+
 __device__ __forceinline__ void pdl_prologue() {
     pdl_launch_dependents();
     pdl_wait();

@@ -17,6 +17,10 @@ namespace mono {
 // ------------------------------------------------------------------ act_prep
 // One CTA per row.  The row is staged in shared memory as f32, normalised, then
 // quantised one 128-chunk per warp.
+// Launch bounds of the small stage kernels name a minimum block count on purpose: with the thread count alone
+// the compiler settles on 32 registers per thread (full occupancy), spills, and waits for each load of a batch
+// before issuing the next.  These kernels run a handful of blocks and live on memory round trips: registers
+// for a whole batch of loads in flight are worth more than occupancy they never use.
 constexpr int kPrepThreads = 1024;
 
 // The part of the staging after a row is in shared memory as f32 (and `ssq` holds this thread's share of its
@@ -63,7 +67,7 @@ __device__ __forceinline__ void prep_tail(const mono_act_prep_args& a, int row, 
     }
 }
 
-__global__ void __launch_bounds__(kPrepThreads) act_prep_kernel(const mono_act_prep_args a) {
+__global__ void __launch_bounds__(kPrepThreads, 1) act_prep_kernel(const mono_act_prep_args a) {
     pdl_launch_dependents();
     prefetch_span(a.gamma_bf16, (size_t)a.k * 2, threadIdx.x, kPrepThreads);  // the norm weights, during the wait
     pdl_wait();
@@ -83,13 +87,7 @@ __global__ void __launch_bounds__(kPrepThreads) act_prep_kernel(const mono_act_p
             const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
             v = make_float4(lo.x, lo.y, hi.x, hi.y);
         } else {
-            v = make_float4(0.f, 0.f, 0.f, 0.f);
-            const float* src = a.src_f32 + (size_t)row * a.src_ld + (size_t)seg * a.k + i;
-#pragma unroll 4
-            for (int s = 0; s < a.nsum; ++s) {
-                const float4 p = *reinterpret_cast<const float4*>(src + (size_t)s * a.src_sum_stride);
-                v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
-            }
+            v = sum_partials4<8>(a.src_f32 + (size_t)row * a.src_ld + (size_t)seg * a.k + i, a.src_sum_stride, a.nsum);
         }
         *reinterpret_cast<float4*>(xrow + i) = v;
         ssq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
@@ -226,7 +224,7 @@ __device__ __forceinline__ void route_body(const mono_route_args& a, RouteSmem& 
     }
 }
 
-__global__ void __launch_bounds__(kRouteThreads) route_kernel(const mono_route_args a) {
+__global__ void __launch_bounds__(kRouteThreads, 1) route_kernel(const mono_route_args a) {
     __shared__ RouteSmem sm;
     pdl_launch_dependents();
     prefetch_span(a.bias, (size_t)a.n_experts * 4, threadIdx.x, kRouteThreads);  // during the wait for the logits
@@ -280,20 +278,47 @@ __device__ __forceinline__ void rowdot_col(const mono_rowdot_args& a, int n0, in
             }
         }
         if (k0 == 0) pdl_wait();  // the activations come from the launch before this one
+        // The activation loads of a batch (16 row x k-slice pairs) are all issued before the first is used:
+        // one L2 round trip per batch instead of one per row.  A column's sums keep their order (k slice,
+        // then row), so the bits do not depend on the batch shape.
+        if (a.rows <= 8) {
 #pragma unroll
-        for (int it = 0; it < 8; ++it) {
-            const int k = k0 + (it * kRowdotThreads + tid) * 4;
-            if (k < a.k) {
+            for (int it0 = 0; it0 < 8; it0 += 2) {
+                uint2 xv[2][8];
 #pragma unroll
-                for (int r = 0; r < kMaxRows; ++r) {
-                    if (r < a.rows) {
-                        const uint2 xv = __ldg(reinterpret_cast<const uint2*>(x + (size_t)r * a.k + k));
-                        const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.x));
-                        const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.y));
+                for (int h = 0; h < 2; ++h) {
+                    const int k = k0 + ((it0 + h) * kRowdotThreads + tid) * 4;
+#pragma unroll
+                    for (int r = 0; r < 8; ++r)
+                        xv[h][r] = __ldg(reinterpret_cast<const uint2*>(x + (size_t)min(r, a.rows - 1) * a.k + min(k, a.k - 4)));
+                }
+                asm volatile("" ::: "memory");  // the next batch's loads start after this batch's, not among them
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int r = 0; r < 8; ++r) {
+                        const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv[h][r].x));
+                        const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv[h][r].y));
 #pragma unroll
                         for (int c = 0; c < COLS; ++c)
-                            acc[c][r] += lo.x * wv[c][it].x + lo.y * wv[c][it].y + hi.x * wv[c][it].z + hi.y * wv[c][it].w;
+                            acc[c][r] += lo.x * wv[c][it0 + h].x + lo.y * wv[c][it0 + h].y + hi.x * wv[c][it0 + h].z + hi.y * wv[c][it0 + h].w;
                     }
+            }
+        } else {
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+                const int k = k0 + (it * kRowdotThreads + tid) * 4;
+                uint2 xv[kMaxRows];
+#pragma unroll
+                for (int r = 0; r < kMaxRows; ++r)
+                    xv[r] = __ldg(reinterpret_cast<const uint2*>(x + (size_t)min(r, a.rows - 1) * a.k + min(k, a.k - 4)));
+#pragma unroll
+                for (int r = 0; r < kMaxRows; ++r) {
+                    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv[r].x));
+                    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv[r].y));
+#pragma unroll
+                    for (int c = 0; c < COLS; ++c)
+                        acc[c][r] += lo.x * wv[c][it].x + lo.y * wv[c][it].y + hi.x * wv[c][it].z + hi.y * wv[c][it].w;
                 }
             }
         }
@@ -320,7 +345,7 @@ __device__ __forceinline__ void rowdot_col(const mono_rowdot_args& a, int n0, in
 }
 
 template <int COLS>
-__global__ void __launch_bounds__(kRowdotThreads) rowdot_kernel(const mono_rowdot_args a) {
+__global__ void __launch_bounds__(kRowdotThreads, 1) rowdot_kernel(const mono_rowdot_args a) {
     // one CTA per COLS output columns
     __shared__ float red[COLS][kRowdotThreads / 32][kMaxRows];
     pdl_launch_dependents();
@@ -369,15 +394,8 @@ __device__ __forceinline__ void mid_body(const mono_mid_args& a, int block, floa
     float* sf = a.scale_f32 ? a.scale_f32 + ((size_t)slot * kMaxRows + row) * a.scale_ld : nullptr;
     uint8_t* s8 = a.scale_e8 ? a.scale_e8 + ((size_t)slot * kMaxRows + row) * a.scale_ld : nullptr;
     for (int c = warp; c < a.inter / 128; c += kMidThreads / 32) {
-        float4 g4 = make_float4(0.f, 0.f, 0.f, 0.f), u4 = g4;
         const float* gp = up + c * 128 + 4 * lane;
-#pragma unroll 4
-        for (int s = 0; s < a.nsum; ++s) {
-            const float4 x = *reinterpret_cast<const float4*>(gp + s * sum_stride);
-            const float4 y = *reinterpret_cast<const float4*>(gp + s * sum_stride + a.inter);
-            g4.x += x.x; g4.y += x.y; g4.z += x.z; g4.w += x.w;
-            u4.x += y.x; u4.y += y.y; u4.z += y.z; u4.w += y.w;
-        }
+        const float4 g4 = sum_partials4<4>(gp, sum_stride, a.nsum), u4 = sum_partials4<4>(gp + a.inter, sum_stride, a.nsum);
         const float gs[4] = {g4.x, g4.y, g4.z, g4.w}, us[4] = {u4.x, u4.y, u4.z, u4.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -391,7 +409,7 @@ __device__ __forceinline__ void mid_body(const mono_mid_args& a, int block, floa
     }
 }
 
-__global__ void __launch_bounds__(kMidThreads) mid_kernel(const mono_mid_args a) {
+__global__ void __launch_bounds__(kMidThreads, 4) mid_kernel(const mono_mid_args a) {
     pdl_prologue();
     __shared__ float chunk[kMidThreads / 32][128];
     mid_body(a, blockIdx.x, chunk);
@@ -399,7 +417,7 @@ __global__ void __launch_bounds__(kMidThreads) mid_kernel(const mono_mid_args a)
 
 // Two activation stages in one launch (the shared expert's and the routed experts'): blocks
 // [0, a.max_slot * a.rows) serve `a`, the rest `b`.
-__global__ void __launch_bounds__(kMidThreads) mid_pair_kernel(const mono_mid_args a, const mono_mid_args b) {
+__global__ void __launch_bounds__(kMidThreads, 4) mid_pair_kernel(const mono_mid_args a, const mono_mid_args b) {
     pdl_prologue();
     __shared__ float chunk[kMidThreads / 32][128];
     const int na = a.max_slot * a.rows;
@@ -459,7 +477,7 @@ __device__ __forceinline__ uint2 poll_tagged(uint64_t addr, uint32_t tag, int32_
     return v;
 }
 
-__global__ void __launch_bounds__(kReduceThreads) reduce_kernel(const mono_reduce_args a) {
+__global__ void __launch_bounds__(kReduceThreads, 2) reduce_kernel(const mono_reduce_args a) {
     pdl_launch_dependents();
     const int pairs = a.n / 2;
     const int total = a.rows * pairs;
@@ -482,12 +500,9 @@ __global__ void __launch_bounds__(kReduceThreads) reduce_kernel(const mono_reduc
         const bool live = !a.slots || a.slots[row] >= 0;
         float p0 = 0.f, p1 = 0.f;
         if (live) {
-#pragma unroll 8
-            for (int s = 0; s < a.nsum; ++s) {
-                const float2 v = *reinterpret_cast<const float2*>(a.partial + (size_t)s * a.sum_stride + (size_t)row * a.ld + 2 * pc);
-                p0 += v.x;
-                p1 += v.y;
-            }
+            const float2 v = sum_partials2<8>(a.partial + (size_t)row * a.ld + 2 * pc, a.sum_stride, a.nsum);
+            p0 = v.x;
+            p1 = v.y;
         }
         __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
         float acc0, acc1;
@@ -534,7 +549,7 @@ __global__ void __launch_bounds__(kReduceThreads) reduce_kernel(const mono_reduc
 constexpr int kRnThreads = 256;
 
 template <int C>
-__global__ void __cluster_dims__(C, 1, 1) __launch_bounds__(kRnThreads) reduce_norm_kernel(const mono_reduce_args r, const mono_act_prep_args a) {
+__global__ void __cluster_dims__(C, 1, 1) __launch_bounds__(kRnThreads, 1) reduce_norm_kernel(const mono_reduce_args r, const mono_act_prep_args a) {
     namespace cg = cooperative_groups;
     pdl_launch_dependents();
     cg::cluster_group cluster = cg::this_cluster();
@@ -668,7 +683,7 @@ __global__ void epoch_advance_kernel(int32_t* guard) {
 // other rank in its own region and widens it to f32 (glm53_flash/gfx950/kernel.py:3700-3770; two slots by
 // launch parity, glm53_flash/gfx950/layout.py:193-215).  A thread waits for words of other GPUs only, never
 // for another CTA of this launch, so the grid need not be resident at once.
-__global__ void __launch_bounds__(kReduceThreads) logits_gather_kernel(const mono_logits_gather_args a) {
+__global__ void __launch_bounds__(kReduceThreads, 2) logits_gather_kernel(const mono_logits_gather_args a) {
     pdl_prologue();
     const int pairs = a.n_local / 2;
     const int total = a.rows * pairs;
@@ -767,10 +782,10 @@ extern "C" int mono_rowdot_launch(const mono_rowdot_args* a, void* stream) {
         mono_set_error("mono_rowdot_launch: rows 1..16, k a multiple of 128 and all pointers required");
         return MONO_E_ARG;
     }
-    // MONO_ROWDOT_COLS=2: two columns per CTA share the activation loads.  Measured slower (router logits of
-    // 256 experts: 9.3 us against 8.8 us), so one column per CTA is the default
+    // One wave of CTAs: a CTA holds a whole batch of loads in registers, so one CTA fits per SM; more columns
+    // than SMs go two to a CTA (sharing the activation loads).  MONO_ROWDOT_COLS=1 / 2 forces the choice.
     const char* cf = getenv("MONO_ROWDOT_COLS");
-    const int cols = cf && atoi(cf) == 2 ? 2 : 1;
+    const int cols = cf ? (atoi(cf) == 2 ? 2 : 1) : (a->n > mono_sm_count() ? 2 : 1);
     if (cols == 2)
         mono::launch_k(mono::rowdot_kernel<2>, (a->n + 1) / 2, mono::kRowdotThreads, 0, (cudaStream_t)stream, *a);
     else

@@ -49,8 +49,11 @@ class MlaLayerOp:
         # the index head weights depend on the normed input only: they run on a side stream, forked after the
         # input norm; the index queries, scores and top-k follow them there and join before the attention
         # (a fork / join that a CUDA graph capture records too)
-        self._side = torch.cuda.Stream(device=device) if os.environ.get("MONO_SIDE_STREAM", "1") == "1" else None
-        self._ev_fork, self._ev_join = torch.cuda.Event(), torch.cuda.Event()
+        # (a high-priority stream: the index path is the longer of the two branches, and its small launches should
+        # not queue behind the head blocks of the main branch)
+        self._side = torch.cuda.Stream(device=device, priority=-1) if os.environ.get("MONO_SIDE_STREAM", "1") == "1" else None
+        self._ev_fork, self._ev_join, self._ev_idxq = torch.cuda.Event(), torch.cuda.Event(), torch.cuda.Event()
+        self.head_after_idxq = os.environ.get("MONO_HEAD_AFTER_IDXQ", "1") != "0"
         h, hl, ql, ih = cfg.hidden, cfg.heads_local, cfg.q_lora, cfg.index_heads
         R = L.MAX_ROWS
         z = lambda *s, dt=torch.float32: torch.zeros(*s, dtype=dt, device=device)  # noqa: E731
@@ -198,9 +201,14 @@ class MlaLayerOp:
                 if not fused_q:
                     ops.q_post(rows, 0, self.qb_p, self.nsB, w["kv_b"], w["kv_b_s"], step.cos, step.sin, step.positions,
                                self.q_full, ih, self.iq_p, self.nsB, self.idx_q)
+                    self._ev_idxq.record(self._side)
                 ops.index_score(ia)
                 ops.index_topk(ia)
                 self._ev_join.record(self._side)
+            if not fused_q and self.head_after_idxq:
+                # the heads' blocks (8 per head, all resident at once) would fill every SM while they wait for
+                # q_b, and the index queries, which the longer branch starts with, would queue behind them
+                main.wait_event(self._ev_idxq)
             ops.q_post(rows, hl, self.qb_p, self.nsB, w["kv_b"], w["kv_b_s"], step.cos, step.sin, step.positions,
                        self.q_full, 0, None, 0, None)
             main.wait_event(self._ev_join)
