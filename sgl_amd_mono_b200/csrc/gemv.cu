@@ -437,6 +437,7 @@ extern void mono_set_error(const char* fmt, ...);
 int mono_gemv_tc_enabled();                                                      // gemv_tc.cu
 int mono_gemv_tc_launch(const mono_gemv_args* a, long tasks, cudaStream_t st);  // gemv_tc.cu
 int mono_gemv_tc4_launch(const mono_gemv_args* a, long tasks, cudaStream_t st); // gemv_tc4.cu
+int mono_gemv_tc4bs_launch(const mono_gemv_args* a, long tasks, cudaStream_t st); // gemv_tc4bs.cu
 
 namespace {
 template <int WK, int NT>
@@ -539,7 +540,11 @@ extern "C" int mono_gemv_launch(const mono_gemv_args* a, void* stream) {
         }
     }
     if (a->wkind == MONO_W_MXFP4 && mono_gemv_tc_enabled()) {
-        const int rc = mono_gemv_tc4_launch(a, tasks, (cudaStream_t)stream);  // -100: not eligible, use the warp-MMA consumer
+        // the block-scaled kind (scales read by the MMA from tensor memory) unless MONO_TC4_BLOCK_SCALE=0 asks for
+        // the kernel that issues one MMA per scale group and scales in its epilogue (read per launch: tests compare both)
+        const char* bs = getenv("MONO_TC4_BLOCK_SCALE");
+        int rc = (bs && bs[0] == '0') ? -100 : mono_gemv_tc4bs_launch(a, tasks, (cudaStream_t)stream);
+        if (rc == -100) rc = mono_gemv_tc4_launch(a, tasks, (cudaStream_t)stream);  // -100: not eligible, use the warp-MMA consumer
         if (rc != -100) {
             if (rc > 0) mono_set_error("mono_gemv_launch: CUDA error %d (%s)", rc, cudaGetErrorString((cudaError_t)rc));
             return rc;

@@ -95,6 +95,29 @@ def test_tcgen05_and_warp_mma_paths_agree(rows):
     assert float((d > 0).float().mean()) < 0.05, "only rare last-bit differences are expected"
 
 
+@pytest.mark.parametrize("cfg,rows", [(CFG_FFN_MXFP4, 4), (CFG_TINY_FFN_384, 5), (CFG_TINY_FFN_384, 16)])
+def test_block_scaled_mxfp4_agrees_with_the_group_kernel(cfg, rows, monkeypatch):
+    """MXFP4 experts on tcgen05 in two ways: kind::mxf8f6f4.block_scale (the MMA reads both operands' E8M0 codes from
+    tensor memory and adds a task's whole K run in one accumulator) and kind::f8f6f4 per 32-value group with the
+    codes applied in the epilogue in f32.  Same bytes, same exact products; the block-scaled sum is formed inside
+    the tensor core instead of group by group in f32, so the partial sums agree to f32 rounding of a K-long sum:
+    |difference| <= 2^-18 x (largest partial sum of the launch), and the block's bf16 output to one ulp."""
+    monkeypatch.setenv("MONO_TC4_BLOCK_SCALE", "1")
+    ffn, w, x, slots, out_bs = _run(cfg, rows)
+    n = int(ffn.n_expert.item())
+    up_bs, dn_bs = ffn.up_r[: n * ffn.ns_up].float().cpu().clone(), ffn.down_p.float().cpu().clone()
+    monkeypatch.setenv("MONO_TC4_BLOCK_SCALE", "0")
+    ffn2, _, _, _, out_g = _run(cfg, rows)
+    assert torch.equal(ffn.ids.cpu(), ffn2.ids.cpu())
+    up_g, dn_g = ffn2.up_r[: n * ffn2.ns_up].float().cpu(), ffn2.down_p.float().cpu()
+    for name, a, b in (("up/gate partial sums", up_bs, up_g), ("down partial sums", dn_bs, dn_g)):
+        assert torch.isfinite(a).all(), name
+        tol = 2.0 ** -18 * float(b.abs().max())
+        assert float((a - b).abs().max()) <= tol, f"{name}: {float((a - b).abs().max())} > {tol}"
+    d = (out_bs.float() - out_g.float()).abs()
+    assert bool((d <= 2.0 ** -7 * out_g.float().abs().clamp_min(1.0)).all()), f"max diff {float(d.max())}"
+
+
 @pytest.mark.parametrize("rows", [1, 8, 16])
 def test_chained_launch_equals_separate_launches(rows, monkeypatch):
     """up/gate -> SwiGLU -> down inside one launch does the arithmetic of the separate launches in the
