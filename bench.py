@@ -202,6 +202,10 @@ class SparseMlaWorkload:
 
     def __init__(self, rows=8, heads=16, ctx=32768, topk=2048):
         self.rows, self.heads, self.ctx, self.topk = rows, heads, ctx, topk
+        if heads != 16:
+            self.name = f"sparse_mla_{rows}rows_{heads}heads_ctx{ctx}_top{topk}"
+        if heads >= 64:
+            self.kernel = "mla_qsplit_kernel + sparse_mla_split_tc_kernel (tcgen05) + sparse_mla_merge_kernel"
 
     def make_inputs(self, dev, rank, tp):
         """Synthetic inputs only (torch): nothing of the kernel library is touched."""
@@ -909,7 +913,10 @@ def run_reference(args, wl_cls, rank: int) -> None:
         return
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    wl = wl_cls(rows=args.rows) if args.rows else wl_cls()
+    kw = dict(rows=args.rows) if args.rows else {}
+    if args.heads and args.workload == "sparse_mla":
+        kw["heads"] = args.heads
+    wl = wl_cls(**kw)
     if not hasattr(wl, "oracle_step"):
         print(json.dumps({"impl": "reference", "unavailable": f"the {args.workload} workload has no CPU counterpart"}))
         return
@@ -947,6 +954,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=os.environ.get("MONO_BENCH_WORKLOAD", DEFAULT_WORKLOAD), choices=sorted(WORKLOADS))
     ap.add_argument("--rows", type=int, default=0, help="rows of the step (default: 8; 16 for gqa_layer)")
+    ap.add_argument("--heads", type=int, default=0, help="sparse_mla: local heads (default 16, config 2; 128 = config 3 at TP 1)")
     ap.add_argument("--load-seconds", type=float, default=0.6, help="time under load before the timed steps")
     ap.add_argument("--shard-of", type=int, default=0, help="run one rank's share of TP = N on each GPU without peers")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -969,7 +977,10 @@ def main() -> None:
 
         dist = dist_mod
         dist.init_process_group("nccl", device_id=torch.device(dev))
-    wl = wl_cls(rows=args.rows) if args.rows else wl_cls()
+    kw = dict(rows=args.rows) if args.rows else {}
+    if args.heads and args.workload == "sparse_mla":
+        kw["heads"] = args.heads
+    wl = wl_cls(**kw)
     wl.shard_of = args.shard_of
     def trace(what):  # MONO_BENCH_TRACE=1: progress on stderr, to see where a multi-rank run stops
         if os.environ.get("MONO_BENCH_TRACE") == "1":

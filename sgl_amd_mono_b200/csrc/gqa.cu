@@ -20,7 +20,7 @@ constexpr int kGqaMaxGroup = 8;
 
 // ------------------------------------------------------------------ front
 // grid (rows, q_heads + 2 * kv_heads + 2), 128 threads: one head each
-__global__ void __launch_bounds__(kGqaDim) gqa_front_kernel(const mono_gqa_args a) {
+__global__ void __launch_bounds__(kGqaDim, 4) gqa_front_kernel(const mono_gqa_args a) {
     pdl_prologue();
     __shared__ float red[4];
     __shared__ float y[kGqaDim];
@@ -149,7 +149,7 @@ __device__ __forceinline__ int gqa_index_key(float sc, int b, int n_blk, int ini
     return key;
 }
 
-__global__ void __launch_bounds__(kSelThreads) gqa_select_kernel(const mono_gqa_args a) {
+__global__ void __launch_bounds__(kSelThreads, 1) gqa_select_kernel(const mono_gqa_args a) {
     pdl_prologue();
     extern __shared__ long long keys[];  // (key32 << 32) | block id
     __shared__ int s_tail_sel;
@@ -243,7 +243,7 @@ struct GqaSplitSmem {
     float p[kGqaMaxGroup][kGqaBlock];
 };
 
-__global__ void __launch_bounds__(kGqaDim) gqa_split_kernel(const mono_gqa_args a) {
+__global__ void __launch_bounds__(kGqaDim, 4) gqa_split_kernel(const mono_gqa_args a) {
     pdl_prologue();
     extern __shared__ uint8_t smem_raw[];
     GqaSplitSmem& sm = *reinterpret_cast<GqaSplitSmem*>(smem_raw);
@@ -325,7 +325,7 @@ __global__ void __launch_bounds__(kGqaDim) gqa_split_kernel(const mono_gqa_args 
 }
 
 // grid (rows * q_heads), 128 threads
-__global__ void __launch_bounds__(kGqaDim) gqa_merge_kernel(const mono_gqa_args a) {
+__global__ void __launch_bounds__(kGqaDim, 4) gqa_merge_kernel(const mono_gqa_args a) {
     pdl_prologue();
     const int row = blockIdx.x / a.q_heads, h = blockIdx.x - row * a.q_heads, tid = threadIdx.x;
     const int G = a.q_heads / a.kv_heads, kvh = h / G, g = h - kvh * G;

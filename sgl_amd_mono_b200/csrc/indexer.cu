@@ -148,7 +148,7 @@ __device__ __forceinline__ uint32_t score_key(float f) {
     return (b & 0x80000000u) ? ~b : (b ^ 0x80000000u);
 }
 
-__global__ void __launch_bounds__(kTopkThreads) index_topk_kernel(const mono_index_args a, int smem_keys) {
+__global__ void __launch_bounds__(kTopkThreads, 1) index_topk_kernel(const mono_index_args a, int smem_keys) {
     pdl_prologue();
     extern __shared__ uint32_t skeys[];  // the row's radix keys when they fit (smem_keys != 0)
     __shared__ int hist[256];
@@ -283,7 +283,7 @@ constexpr int kClSize = 8;
 constexpr int kClKeys = 2;
 constexpr int kClSpan = kTopkThreads * kClKeys;
 
-__global__ void __cluster_dims__(kClSize, 1, 1) __launch_bounds__(kTopkThreads)
+__global__ void __cluster_dims__(kClSize, 1, 1) __launch_bounds__(kTopkThreads, 1)
     index_topk_cluster_kernel(const mono_index_args a) {
     pdl_launch_dependents();
     if (threadIdx.x == 0) {  // during the wait for the scores: the step's tables of this row
