@@ -89,14 +89,29 @@ def _model_disable_reasons(model, hf_config, copies) -> list[str]:
 class _Built:
     """The routed forward: covered layers on the monokernels, the rest on the model's own code."""
 
-    def __init__(self, model, ops_by_layer: dict, max_rows: int, max_position: int):
+    def __init__(self, model, ops_by_layer: dict, max_rows: int, max_position: int, token_rows: dict | None = None):
         self.model, self.ops, self.max_rows, self.max_position = model, ops_by_layer, max_rows, max_position
+        self.token_rows = token_rows or {}  # width -> metadata.TokenRows (buffers allocated at build)
+
+    def _block_table(self, forward_batch, rows: int, fallback):
+        """The rows' block table: made on the device from SGLang's per-request tables when the batch carries them
+        (``minimax_m3/metadata.py:7-42``; inside the graph when captured), else the page table handed over."""
+        pool = getattr(getattr(forward_batch, "req_to_token_pool", None), "req_to_token", None)
+        tr = self.token_rows.get(rows)
+        if pool is None or tr is None:
+            return fallback
+        n_req = forward_batch.req_pool_indices.shape[0]
+        mode = getattr(forward_batch, "forward_mode", None)
+        verify = bool(mode is not None and mode.is_target_verify())
+        table, _ = tr(pool, forward_batch.req_pool_indices, forward_batch.seq_lens, forward_batch.out_cache_loc, rows // n_req, verify)
+        return table
 
     def forward(self, plan: Plan, input_ids, positions, forward_batch, input_embeds=None, *args, **kw):
         rows = plan.key.rows
         if rows > self.max_rows:
             return type(self.model).forward(self.model, input_ids, positions, forward_batch, input_embeds, *args, **kw)
         st = step_tables(plan, positions, forward_batch, rows, self.max_position)
+        st.page_table = self._block_table(forward_batch, rows, st.page_table)
         h = input_embeds if input_embeds is not None else self.model.embed(input_ids)
         h = h[:rows]
         for i, layer in enumerate(self.model.layers):
@@ -118,7 +133,10 @@ def _build(model, hf_config, ctx):
             ops_by_layer[i] = GqaLayerOp(g, m, layer.weights, ctx.device, ctx.max_context, peer=getattr(ctx, "peer", None),
                                          deadline_s=ctx.deadline_s)
     log.info("%s: %d layers on the monokernels, widths %s, TP %d", g.name, len(ops_by_layer), ctx.widths, ctx.tp_size)
-    return _Built(model, ops_by_layer, max(ctx.widths), ctx.max_context - 1)
+    from .metadata import TokenRows
+
+    token_rows = {w: TokenRows(w, ctx.max_context, ctx.device, block_tokens=64) for w in ctx.widths}
+    return _Built(model, ops_by_layer, max(ctx.widths), ctx.max_context - 1, token_rows)
 
 
 SPEC = MonoSpec(
