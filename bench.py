@@ -643,6 +643,24 @@ class AllReduceWorkload:
             dist.all_reduce(self.msg)
 
         self.g_ours, self.g_nccl = self._graph(ours), self._graph(nccl)
+        # the reduce-scatter + all-gather form of the same kernel (half the bytes per link, one more hop)
+        self.rsag_us, self.g_rsag = None, None
+        if (self.n // 2) % (2 * world) == 0:
+            self.out_rsag = torch.zeros_like(self.out)
+            old_env = os.environ.get("MONO_AR_RSAG")
+            os.environ["MONO_AR_RSAG"] = "always"
+            try:
+                def ours_rsag():
+                    ops.reduce_rows(self.rows, self.n, self.part, 1, self.out_rsag, residual=self.res, peer=self.peer, site=0,
+                                    guard=self.peer.guard, deadline_s=10.0)
+                    ops.epoch_advance(self.peer.guard)
+
+                self.g_rsag = self._graph(ours_rsag)
+            finally:
+                if old_env is None:
+                    del os.environ["MONO_AR_RSAG"]
+                else:
+                    os.environ["MONO_AR_RSAG"] = old_env
         # the NVLS variant: the same kernel, each word pushed by one multimem.st through the switch
         self.mc_us, self.mc_note = None, None
         try:
@@ -671,6 +689,13 @@ class AllReduceWorkload:
         if rc:
             raise RuntimeError(f"guard words {words}")
         self.nccl_us = self._time(self.g_nccl)
+        if self.g_rsag is not None:
+            self.g_rsag.replay()
+            torch.cuda.synchronize()
+            rc, words = ops.guard_read(self.peer.guard)
+            if rc or not torch.equal(self.out_rsag, self.out):
+                raise RuntimeError(f"the reduce-scatter form changed the all-reduce's bits (guard words {words})")
+            self.rsag_us = self._time(self.g_rsag)
         if self.g_mc is not None:
             self.g_mc.replay()
             torch.cuda.synchronize()
@@ -726,6 +751,7 @@ class AllReduceWorkload:
         return {"workload": self.name, "rows": self.rows, "n": self.n, "tp": self.world,
                 "nccl_allreduce_us": self.nccl_us, "in_kernel_allreduce_us_back_to_back": self._time(self.g_ours),
                 "in_kernel_allreduce_multicast_us": self.mc_us, "multicast_unavailable": self.mc_note,
+                "in_kernel_allreduce_rs_ag_us": self.rsag_us,
                 "nvlink_peak_gbs_per_direction": 900, "l2": "256 MiB buffer written between timed iterations"}
 
     def cpu_sample(self):

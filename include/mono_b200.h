@@ -371,6 +371,11 @@ typedef struct mono_reduce_args {
      * f32 sum are the same, so both variants give the same bits.  No reduction happens in the switch: an
      * order the hardware chooses would let routing decisions differ between ranks. */
     uint64_t mc_ptr;
+    /* Reduce-scatter + all-gather form (minimax_m3/gfx950/layout.py:33-34,97-114; the reference takes it from 12
+     * rows): the rank that owns a pair's column slice (n / world columns) receives the partials, sums them in rank
+     * order, adds the residual and pushes the finished bf16 word to the others.  Half the bytes per link, one more
+     * hop, the same bits.  Needs n / 2 divisible by 2 * world. */
+    int rsag;
 } mono_reduce_args;
 size_t mono_reduce_peer_bytes(int rows, int n, int world);
 int mono_reduce_launch(const mono_reduce_args* a, void* stream);

@@ -95,7 +95,7 @@ class ReduceArgs(C.Structure):
         ("rows", i32), ("n", i32), ("partial", vp), ("nsum", i32), ("ld", i32), ("sum_stride", i64),
         ("residual", vp), ("slots", vp), ("out", vp), ("world", i32), ("rank", i32), ("peer_ptrs", vp),
         ("tag", u32), ("parity", i32), ("deadline_ns", u64), ("site", i32), ("guard", vp),
-        ("peer_guards", vp), ("mc_ptr", u64),
+        ("peer_guards", vp), ("mc_ptr", u64), ("rsag", i32),
     ]
 
 

@@ -477,6 +477,54 @@ __device__ __forceinline__ uint2 poll_tagged(uint64_t addr, uint32_t tag, int32_
     return v;
 }
 
+// One pair of columns of one row through the ranks: `word` is this rank's bf16 partial, (res0, res1) the residual;
+// returns the finished bf16 pair (rank-ordered f32 sum + residual).  Two forms with the same arithmetic and bits:
+//   all-to-all   every rank pushes its word to every rank and sums the `world` words it received;
+//   rs + ag      (a.rsag; minimax_m3/gfx950/layout.py:33-34,97-114: "half the bytes a link, one more hop") the rank
+//                that owns the pair's column slice receives the words, sums them, adds the residual and pushes the
+//                FINISHED word to the others, which only wait for it.  The finished word travels in the slot the
+//                all-to-all form uses for the owner's partial: in a peer's buffer that slot's columns are free,
+//                because a rank sends a peer partials of the peer's own slice only.
+__device__ __forceinline__ uint32_t exchange_pair(const mono_reduce_args& a, int row, int pc, int pairs, uint32_t word, uint32_t tag,
+                                                  int parity, float res0, float res1, uint64_t t0, bool* failed) {
+    const size_t slot_pairs = (size_t)kMaxRows * pairs;
+    const size_t row_off = (size_t)row * pairs + pc;
+    const size_t my_off = (((size_t)parity * a.world + a.rank) * slot_pairs + row_off) * 8;
+    const uint64_t mine = a.peer_ptrs[a.rank];
+    const int owner = a.rsag ? pc / (pairs / a.world) : a.rank;
+    if (!a.rsag) {
+        if (a.mc_ptr) st_multimem_v2(a.mc_ptr + my_off, word, tag);
+        else
+            for (int d = 0; d < a.world; ++d) st_sys_v2(a.peer_ptrs[d] + my_off, word, tag);
+    } else {
+        st_sys_v2(a.peer_ptrs[owner] + my_off, word, tag);
+    }
+    *failed = *failed || guard_failed(a.guard);
+    if (owner != a.rank) {  // rs + ag, somebody else's slice: the finished word arrives in the owner's slot
+        const uint64_t addr = mine + (((size_t)parity * a.world + owner) * slot_pairs + row_off) * 8;
+        if (*failed) return 0u;
+        return poll_tagged(addr, tag, a.guard, a.peer_guards, a.world, a.rank, a.site, a.deadline_ns, t0, failed).x;
+    }
+    float acc0 = 0.f, acc1 = 0.f;
+    for (int src = 0; src < a.world && !*failed; ++src) {
+        const uint64_t addr = mine + (((size_t)parity * a.world + src) * slot_pairs + row_off) * 8;
+        const uint2 v = poll_tagged(addr, tag, a.guard, a.peer_guards, a.world, a.rank, a.site, a.deadline_ns, t0, failed);
+        if (*failed) break;
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&v.x);
+        acc0 += __low2float(b);
+        acc1 += __high2float(b);
+    }
+    const __nv_bfloat162 o = __floats2bfloat162_rn(acc0 + res0, acc1 + res1);
+    const uint32_t ow = *reinterpret_cast<const uint32_t*>(&o);
+    if (a.rsag && !*failed) {
+        if (a.mc_ptr) st_multimem_v2(a.mc_ptr + my_off, ow, tag);
+        else
+            for (int d = 0; d < a.world; ++d)
+                if (d != a.rank) st_sys_v2(a.peer_ptrs[d] + my_off, ow, tag);
+    }
+    return ow;
+}
+
 __global__ void __launch_bounds__(kReduceThreads, 2) reduce_kernel(const mono_reduce_args a) {
     pdl_launch_dependents();
     const int pairs = a.n / 2;
@@ -505,37 +553,21 @@ __global__ void __launch_bounds__(kReduceThreads, 2) reduce_kernel(const mono_re
             p1 = v.y;
         }
         __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-        float acc0, acc1;
-        if (a.world > 1) {
-            const uint32_t word = *reinterpret_cast<uint32_t*>(&pb);
-            const size_t slot_pairs = (size_t)kMaxRows * pairs;
-            const size_t my_off = (((size_t)parity * a.world + a.rank) * slot_pairs + (size_t)row * pairs + pc) * 8;
-            if (a.mc_ptr) st_multimem_v2(a.mc_ptr + my_off, word, tag);
-            else
-                for (int d = 0; d < a.world; ++d) st_sys_v2(a.peer_ptrs[d] + my_off, word, tag);
-            acc0 = 0.f;
-            acc1 = 0.f;
-            const uint64_t mine = a.peer_ptrs[a.rank];
-            const uint64_t t0 = globaltimer_ns();
-            bool failed = guard_failed(a.guard);
-            for (int src = 0; src < a.world && !failed; ++src) {
-                const uint64_t addr = mine + (((size_t)parity * a.world + src) * slot_pairs + (size_t)row * pairs + pc) * 8;
-                const uint2 v = poll_tagged(addr, tag, a.guard, a.peer_guards, a.world, a.rank, a.site, a.deadline_ns, t0, &failed);
-                if (failed) break;
-                const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&v.x);
-                acc0 += __low2float(b);
-                acc1 += __high2float(b);
-            }
-        } else {
-            acc0 = __low2float(pb);
-            acc1 = __high2float(pb);
-        }
+        float res0 = 0.f, res1 = 0.f;
         if (a.residual) {
             const __nv_bfloat162 r = reinterpret_cast<const __nv_bfloat162*>(a.residual)[(size_t)row * pairs + pc];
-            acc0 += __low2float(r);
-            acc1 += __high2float(r);
+            res0 = __low2float(r);
+            res1 = __high2float(r);
         }
-        reinterpret_cast<__nv_bfloat162*>(a.out)[(size_t)row * pairs + pc] = __floats2bfloat162_rn(acc0, acc1);
+        uint32_t ow;
+        if (a.world > 1) {
+            bool failed = false;
+            ow = exchange_pair(a, row, pc, pairs, *reinterpret_cast<uint32_t*>(&pb), tag, parity, res0, res1, globaltimer_ns(), &failed);
+        } else {
+            const __nv_bfloat162 o = __floats2bfloat162_rn(__low2float(pb) + res0, __high2float(pb) + res1);
+            ow = *reinterpret_cast<const uint32_t*>(&o);
+        }
+        reinterpret_cast<uint32_t*>(a.out)[(size_t)row * pairs + pc] = ow;
     }
 }
 
@@ -571,7 +603,6 @@ __global__ void __cluster_dims__(C, 1, 1) __launch_bounds__(kRnThreads, 1) reduc
     }
     const bool live = !r.slots || r.slots[row] >= 0;
     const uint64_t t0 = r.world > 1 ? globaltimer_ns() : 0;
-    const size_t slot_pairs = (size_t)kMaxRows * pairs;
     float ssq = 0.f;
     for (int li = tid * 4; li < kc; li += kRnThreads * 4) {
         const int i = col0 + li;
@@ -589,46 +620,26 @@ __global__ void __cluster_dims__(C, 1, 1) __launch_bounds__(kRnThreads, 1) reduc
             }
         }
         const __nv_bfloat162 pb0 = __floats2bfloat162_rn(v.x, v.y), pb1 = __floats2bfloat162_rn(v.z, v.w);
-        float acc[4];
-        if (r.world > 1) {
-            const int pc = i >> 1;  // this thread's two pairs: pc, pc + 1
-            const size_t my_off = (((size_t)parity * r.world + r.rank) * slot_pairs + (size_t)row * pairs + pc) * 8;
-            const uint32_t w0 = *reinterpret_cast<const uint32_t*>(&pb0), w1 = *reinterpret_cast<const uint32_t*>(&pb1);
-            if (r.mc_ptr) {
-                st_multimem_v2(r.mc_ptr + my_off, w0, tag);
-                st_multimem_v2(r.mc_ptr + my_off + 8, w1, tag);
-            } else {
-                for (int d = 0; d < r.world; ++d) {
-                    st_sys_v2(r.peer_ptrs[d] + my_off, w0, tag);
-                    st_sys_v2(r.peer_ptrs[d] + my_off + 8, w1, tag);
-                }
-            }
-            acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
-            const uint64_t mine = r.peer_ptrs[r.rank];
-            bool failed = guard_failed(r.guard);
-            for (int src = 0; src < r.world && !failed; ++src) {
-                const uint64_t addr = mine + (((size_t)parity * r.world + src) * slot_pairs + (size_t)row * pairs + pc) * 8;
-                const uint2 x0 = poll_tagged(addr, tag, r.guard, r.peer_guards, r.world, r.rank, r.site, r.deadline_ns, t0, &failed);
-                if (failed) break;
-                const uint2 x1 = poll_tagged(addr + 8, tag, r.guard, r.peer_guards, r.world, r.rank, r.site, r.deadline_ns, t0, &failed);
-                if (failed) break;
-                const __nv_bfloat162 b0 = *reinterpret_cast<const __nv_bfloat162*>(&x0.x), b1 = *reinterpret_cast<const __nv_bfloat162*>(&x1.x);
-                acc[0] += __low2float(b0); acc[1] += __high2float(b0);
-                acc[2] += __low2float(b1); acc[3] += __high2float(b1);
-            }
-        } else {
-            acc[0] = __low2float(pb0); acc[1] = __high2float(pb0);
-            acc[2] = __low2float(pb1); acc[3] = __high2float(pb1);
-        }
+        float2 rlo = make_float2(0.f, 0.f), rhi = rlo;
         if (r.residual) {
             const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(r.residual) + (size_t)row * r.n + i);
-            const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-            const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-            acc[0] += lo.x; acc[1] += lo.y; acc[2] += hi.x; acc[3] += hi.y;
+            rlo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+            rhi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
         }
-        const __nv_bfloat162 o0 = __floats2bfloat162_rn(acc[0], acc[1]), o1 = __floats2bfloat162_rn(acc[2], acc[3]);
-        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(r.out) + (size_t)row * r.n + i) =
-            make_uint2(*reinterpret_cast<const uint32_t*>(&o0), *reinterpret_cast<const uint32_t*>(&o1));
+        uint32_t ow0, ow1;
+        if (r.world > 1) {
+            const int pc = i >> 1;  // this thread's two pairs: pc, pc + 1
+            bool failed = false;
+            ow0 = exchange_pair(r, row, pc, pairs, *reinterpret_cast<const uint32_t*>(&pb0), tag, parity, rlo.x, rlo.y, t0, &failed);
+            ow1 = exchange_pair(r, row, pc + 1, pairs, *reinterpret_cast<const uint32_t*>(&pb1), tag, parity, rhi.x, rhi.y, t0, &failed);
+        } else {
+            const __nv_bfloat162 q0 = __floats2bfloat162_rn(__low2float(pb0) + rlo.x, __high2float(pb0) + rlo.y);
+            const __nv_bfloat162 q1 = __floats2bfloat162_rn(__low2float(pb1) + rhi.x, __high2float(pb1) + rhi.y);
+            ow0 = *reinterpret_cast<const uint32_t*>(&q0);
+            ow1 = *reinterpret_cast<const uint32_t*>(&q1);
+        }
+        const __nv_bfloat162 o0 = *reinterpret_cast<const __nv_bfloat162*>(&ow0), o1 = *reinterpret_cast<const __nv_bfloat162*>(&ow1);
+        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(r.out) + (size_t)row * r.n + i) = make_uint2(ow0, ow1);
         const float4 h = make_float4(__low2float(o0), __high2float(o0), __low2float(o1), __high2float(o1));
         *reinterpret_cast<float4*>(xrow + li) = h;
         ssq += h.x * h.x + h.y * h.y + h.z * h.z + h.w * h.w;
@@ -853,28 +864,6 @@ extern "C" size_t mono_reduce_peer_bytes(int rows, int n, int world) {
     return (size_t)2 * world * MONO_MAX_ROWS * (n / 2) * 8;
 }
 
-extern "C" int mono_reduce_launch(const mono_reduce_args* a, void* stream) {
-    if (!a || a->rows < 1 || a->rows > MONO_MAX_ROWS || a->n < 2 || (a->n & 1) || !a->partial || !a->out || a->nsum < 1 ||
-        (a->ld & 1)) {
-        mono_set_error("mono_reduce_launch: rows 1..16, even n and ld, partial and out required");
-        return MONO_E_ARG;
-    }
-    if (a->world > 1 && (!a->peer_ptrs || a->rank < 0 || a->rank >= a->world || a->world > 8 || a->deadline_ns == 0 ||
-                         (a->tag == 0 && !a->guard) || a->site < 0 || a->site > 254)) {
-        mono_set_error("mono_reduce_launch: world %d needs peer_ptrs, a rank, a deadline, a site in 0..254 (the tag is "
-                       "epoch * 256 + site + 1) and a tag or guard words", a->world);
-        return MONO_E_ARG;
-    }
-    const int total = a->rows * (a->n / 2);
-    int grid = (total + mono::kReduceThreads - 1) / mono::kReduceThreads;
-    const int sms = mono_sm_count();
-    if (grid > 2 * sms) grid = 2 * sms;
-    mono::launch_k(mono::reduce_kernel, grid, mono::kReduceThreads, 0, (cudaStream_t)stream, *a);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) mono_set_error("mono_reduce_launch: %s", cudaGetErrorString(e));
-    return (int)e;
-}
-
 static int reduce_args_check(const mono_reduce_args* a, const char* who) {
     if (!a || a->rows < 1 || a->rows > MONO_MAX_ROWS || a->n < 2 || (a->n & 1) || !a->partial || !a->out || a->nsum < 1 || (a->ld & 1)) {
         mono_set_error("%s: rows 1..16, even n and ld, partial and out required", who);
@@ -885,7 +874,23 @@ static int reduce_args_check(const mono_reduce_args* a, const char* who) {
         mono_set_error("%s: world %d needs peer_ptrs, a rank, a deadline, a site in 0..254 and a tag or guard words", who, a->world);
         return MONO_E_ARG;
     }
+    if (a->rsag && (a->world < 2 || (a->n / 2) % (2 * a->world) != 0)) {
+        mono_set_error("%s: the reduce-scatter form needs world > 1 and n / 2 = %d divisible by 2 x world = %d", who, a->n / 2, 2 * a->world);
+        return MONO_E_ARG;
+    }
     return 0;
+}
+
+extern "C" int mono_reduce_launch(const mono_reduce_args* a, void* stream) {
+    if (int rc = reduce_args_check(a, "mono_reduce_launch")) return rc;
+    const int total = a->rows * (a->n / 2);
+    int grid = (total + mono::kReduceThreads - 1) / mono::kReduceThreads;
+    const int sms = mono_sm_count();
+    if (grid > 2 * sms) grid = 2 * sms;
+    mono::launch_k(mono::reduce_kernel, grid, mono::kReduceThreads, 0, (cudaStream_t)stream, *a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) mono_set_error("mono_reduce_launch: %s", cudaGetErrorString(e));
+    return (int)e;
 }
 
 extern "C" int mono_reduce_norm_launch(const mono_reduce_args* r, const mono_act_prep_args* a, void* stream) {

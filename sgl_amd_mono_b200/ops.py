@@ -294,6 +294,22 @@ def rowdot(rows: int, w: torch.Tensor, x_bf16: torch.Tensor, out: torch.Tensor, 
     L.check(L.load().mono_rowdot_launch(C.byref(a), _stream()), "mono_rowdot_launch")
 
 
+RSAG_FROM_ROWS = 12  # the reference's switch point (minimax_m3/gfx950/layout.py:33-34)
+
+
+def rsag_wanted(rows: int, n: int, world: int) -> bool:
+    """Whether a step's all-reduces take the reduce-scatter + all-gather form: ``MONO_AR_RSAG=1`` asks for it from
+    ``RSAG_FROM_ROWS`` rows (where the column slices divide evenly), ``MONO_AR_RSAG=always`` for every step; the
+    default is the all-to-all form at every row count, which measured faster on NVSwitch (one hop; the messages of
+    a 16-row step are latency-bound, not bandwidth-bound).  Same bits either way."""
+    import os
+
+    mode = os.environ.get("MONO_AR_RSAG", "0")
+    if world < 2 or (n // 2) % (2 * world) or mode == "0":
+        return False
+    return mode == "always" or rows >= RSAG_FROM_ROWS
+
+
 _injectors: dict = {}
 
 
@@ -316,6 +332,7 @@ def _reduce_args(rows, n, partial, nsum, out, residual, slots, peer, site, guard
         a.peer_ptrs = peer.region_table(site).data_ptr()
         a.peer_guards = peer.guard_table.data_ptr()
         a.mc_ptr = peer.mc_region(site) if getattr(peer, "mc_region", None) is not None else 0
+        a.rsag = int(rsag_wanted(rows, n, peer.world))
         a.tag, a.parity = 0, 0
         a.deadline_ns = int(deadline_s * 1e9)
     if not 0 <= site <= 254:

@@ -55,8 +55,9 @@ class OneDeviceRanks:
         pair = partial_bf16.contiguous().view(torch.int32).to(torch.int64) & 0xFFFFFFFF
         self.slot(self.regions[self.rank], parity, src)[:rows] = (pair | (tag << 32)).to(DEV)
 
-    def launch(self, rows, partial_f32, out, residual, site, deadline_s=5.0, slots=None):
+    def launch(self, rows, partial_f32, out, residual, site, deadline_s=5.0, slots=None, rsag=0):
         a = L.ReduceArgs()
+        a.rsag = rsag
         a.rows, a.n, a.partial, a.nsum, a.ld = rows, self.n, partial_f32.data_ptr(), partial_f32.shape[0], self.n
         a.sum_stride = ROWS_MAX * self.n
         a.residual, a.out, a.slots = residual.data_ptr(), out.data_ptr(), None if slots is None else slots.data_ptr()
@@ -110,6 +111,59 @@ def test_all_reduce_sum_order_tags_and_parity_on_one_device(world, rank):
         ops.epoch_advance(R.guard)
     torch.cuda.synchronize()
     assert int(R.guard[0]) == 4
+
+
+@pytest.mark.parametrize("world,rank", [(2, 0), (2, 1), (4, 2), (8, 5)])
+def test_reduce_scatter_all_gather_form_on_one_device(world, rank):
+    """The rs + ag form (``minimax_m3/gfx950/layout.py:33-34,97-114``): this rank sums only its own column slice (from
+    the partials the others sent it), pushes the FINISHED words of that slice to everybody, and takes the other
+    slices' finished words from their owners.  The host plays the other ranks; the result must be the all-to-all
+    form's bits, and what this rank sends must be exactly: its partial of slice d to rank d, its finished slice to all."""
+    n, rows = 1024, 13
+    pairs, ps = n // 2, n // 2 // world
+    g = torch.Generator().manual_seed(7 * world + rank)
+    R = OneDeviceRanks(world, rank, n)
+    out = torch.zeros(ROWS_MAX, n, dtype=torch.bfloat16, device=DEV)
+    epoch, site = 0, 3
+    tag, parity = _tag(epoch, site), 0
+    parts = [(torch.randn(rows, n, generator=g) * (10.0 ** (r % 3))).float().bfloat16().float() for r in range(world)]
+    residual = torch.randn(rows, n, generator=g).bfloat16()
+    want = S.allreduce_rank_order(parts, residual)  # [rows, n] bf16: what every rank must end with
+    mine = torch.zeros(1, ROWS_MAX, n)
+    mine[0, :rows] = parts[rank]
+    for src in range(world):
+        if src == rank:
+            continue
+        # src's partial of MY slice, and src's finished words of ITS slice, both in slot [src] of my region
+        word = torch.zeros(rows, n, dtype=torch.bfloat16)
+        word[:, rank * 2 * ps : (rank + 1) * 2 * ps] = parts[src].bfloat16()[:, rank * 2 * ps : (rank + 1) * 2 * ps]
+        word[:, src * 2 * ps : (src + 1) * 2 * ps] = want[:, src * 2 * ps : (src + 1) * 2 * ps]
+        pair = word.contiguous().view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+        full = torch.zeros(rows, pairs, dtype=torch.int64)  # columns of other slices keep tag 0: never read
+        for sl in (rank, src):
+            full[:, sl * ps : (sl + 1) * ps] = pair[:, sl * ps : (sl + 1) * ps] | (tag << 32)
+        R.slot(R.regions[rank], parity, src)[:rows] = full.to(DEV)
+    R.launch(rows, mine.to(DEV), out, residual.to(DEV), site, rsag=1)
+    torch.cuda.synchronize()
+    rc, words = ops.guard_read(R.guard)
+    assert rc == 0, f"guard words {words}"
+    assert torch.equal(out[:rows].cpu(), want), "the rs + ag form must give the all-to-all form's bits"
+    my_pair = parts[rank].bfloat16().contiguous().view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    fin_pair = want.contiguous().view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    for dst in range(world):
+        if dst == rank:
+            continue
+        got = R.slot(R.regions[dst], parity, rank)[:rows].cpu()
+        assert torch.equal(got[:, dst * ps : (dst + 1) * ps], my_pair[:, dst * ps : (dst + 1) * ps] | (tag << 32)), "partial of dst's slice"
+        assert torch.equal(got[:, rank * ps : (rank + 1) * ps], fin_pair[:, rank * ps : (rank + 1) * ps] | (tag << 32)), "finished slice"
+        rest = [c for c in range(world) if c not in (dst, rank)]
+        for c in rest:
+            assert not bool(got[:, c * ps : (c + 1) * ps].any()), "nothing else is sent: half the bytes per link"
+    # refused where the slices do not divide
+    a = L.ReduceArgs()
+    a.rows, a.n, a.partial, a.nsum, a.ld, a.sum_stride = 1, 1000, mine.to(DEV).data_ptr(), 1, 1000, ROWS_MAX * 1000
+    a.out, a.world, a.rank, a.peer_ptrs, a.deadline_ns, a.guard, a.rsag = out.data_ptr(), 8, 0, R.ptrs.data_ptr(), 10**9, R.guard.data_ptr(), 1
+    assert L.load().mono_reduce_launch(C.byref(a), torch.cuda.current_stream().cuda_stream) == -1  # MONO_E_ARG
 
 
 def test_a_wait_that_runs_out_sets_the_words_flags_the_peers_and_later_launches_drain():

@@ -53,6 +53,22 @@ def test_tp_multicast_pushes_give_the_bits_of_the_peer_stores(world, rows, ctx):
         assert torch.equal(p2p[r]["h1"], mc[r]["h1"])
 
 
+@pytest.mark.parametrize("world,rows,ctx", [(2, 13, 300)])
+def test_tp_reduce_scatter_all_gather_gives_the_bits_of_the_all_to_all_form(world, rows, ctx):
+    """13 rows: from 12 rows ``MONO_AR_RSAG=1`` switches both all-reduces of the layer to reduce-scatter + all-gather."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    outdir = Path(__file__).resolve().parent / "_tp_out"
+    outdir.mkdir(exist_ok=True)
+    a2a = _run_ranks(world, rows, ctx, outdir, {"MONO_AR_RSAG": "0"})
+    rsag = _run_ranks(world, rows, ctx, outdir, {"MONO_AR_RSAG": "1"})
+    for r in range(world):
+        assert a2a[r]["rc"] == 0 and rsag[r]["rc"] == 0, (a2a[r]["words"], rsag[r]["words"])
+        for x, y in zip(a2a[r]["outs"], rsag[r]["outs"]):
+            assert torch.equal(x, y), f"rank {r}: the rs + ag form changed the result"
+        assert torch.equal(a2a[r]["h1"], rsag[r]["h1"])
+
+
 @pytest.mark.parametrize("world,rows,ctx", [(2, 4, 400), (2, 13, 300), (4, 6, 320)])
 def test_tp_layer_ranks_agree_and_match_oracle(world, rows, ctx):
     if torch.cuda.device_count() < world:
