@@ -390,6 +390,18 @@ int mono_reduce_norm_launch(const mono_reduce_args* r, const struct mono_act_pre
 /* Adds 1 to the epoch word on the device (glm53/gfx950/runner.py:209-210 advance_step). */
 int mono_epoch_advance_launch(int32_t* guard, void* stream);
 
+/* ---- weights towards L2 ahead of the stage that streams them ----
+ * Nothing in the reference (its one persistent kernel overlaps a stage's loads with the stage before it by
+ * construction); here consecutive stages are launches, and between two weight streams HBM is idle.  The launch only
+ * issues L2 prefetch requests for the byte ranges and returns; run it on a side branch of the step's graph. */
+#define MONO_PREFETCH_RANGES 8
+typedef struct mono_prefetch_args {
+    int n;                                /* ranges in use */
+    uint64_t ptr[MONO_PREFETCH_RANGES];   /* device addresses, 16-byte aligned */
+    uint64_t bytes[MONO_PREFETCH_RANGES]; /* at least 16 each; a tail shorter than 16 bytes is left out */
+} mono_prefetch_args;
+int mono_l2_prefetch_launch(const mono_prefetch_args* a, void* stream);
+
 /* ---- LM-head tail: K-split sum and logits all-gather (glm53_flash/gfx950/kernel.py:3700-3770 run_head's
  * push and gather; slots by launch parity, glm53_flash/gfx950/layout.py:193-215) ------------------------
  * logits = sum over nsum slices (in order) of f32 [16][ld], this rank's n_local columns.  world == 1: the

@@ -99,6 +99,13 @@ class ReduceArgs(C.Structure):
     ]
 
 
+PREFETCH_RANGES = 8
+
+
+class PrefetchArgs(C.Structure):
+    _fields_ = [("n", i32), ("ptr", u64 * PREFETCH_RANGES), ("bytes", u64 * PREFETCH_RANGES)]
+
+
 class RowdotArgs(C.Structure):
     _fields_ = [
         ("rows", i32), ("n", i32), ("k", i32), ("w", vp), ("w_is_f32", i32), ("x_bf16", vp),
@@ -156,7 +163,7 @@ class LogitsGatherArgs(C.Structure):
 
 
 _STRUCTS = [GemvJob, GemvArgs, ActPrepArgs, RouteArgs, MidArgs, SparseMlaArgs, ReduceArgs, RowdotArgs,
-            MlaMidArgs, QPostArgs, IndexArgs, GqaArgs, LogitsGatherArgs]
+            MlaMidArgs, QPostArgs, IndexArgs, GqaArgs, LogitsGatherArgs, PrefetchArgs]
 
 # every symbol include/mono_b200.h declares: name -> (restype, argtypes)
 SYMBOLS = {
@@ -185,6 +192,7 @@ SYMBOLS = {
     "mono_reduce_launch": (i32, [C.POINTER(ReduceArgs), vp]),
     "mono_reduce_norm_launch": (i32, [C.POINTER(ReduceArgs), C.POINTER(ActPrepArgs), vp]),
     "mono_epoch_advance_launch": (i32, [vp, vp]),
+    "mono_l2_prefetch_launch": (i32, [vp, vp]),
     "mono_logits_peer_bytes": (C.c_size_t, [i32, i32]),
     "mono_logits_gather_launch": (i32, [C.POINTER(LogitsGatherArgs), vp]),
     "mono_mla_mid_launch": (i32, [C.POINTER(MlaMidArgs), vp]),

@@ -218,6 +218,7 @@ extern "C" size_t mono_struct_size(int which) {
         case 10: return sizeof(mono_index_args);
         case 11: return sizeof(mono_gqa_args);
         case 12: return sizeof(mono_logits_gather_args);
+        case 13: return sizeof(mono_prefetch_args);
         default: return 0;
     }
 }

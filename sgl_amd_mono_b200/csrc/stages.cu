@@ -682,6 +682,25 @@ __global__ void __cluster_dims__(C, 1, 1) __launch_bounds__(kRnThreads, 1) reduc
     cluster.sync();  // no CTA leaves while another may still read its sum
 }
 
+// Pulls up to MONO_PREFETCH_RANGES byte ranges towards L2 (cp.async.bulk.prefetch.L2, 16 KB a request).  A launch of
+// its own on a side branch of the step's graph: weights that a later stage will stream do not depend on anything,
+// and the stages between two weight streams leave HBM idle (they live on memory round trips, not on bandwidth).
+// Nothing waits for these requests: the kernel only issues them.
+__global__ void __launch_bounds__(128, 1) l2_prefetch_kernel(const mono_prefetch_args a) {
+    pdl_launch_dependents();
+    constexpr uint32_t kChunk = 16384;
+    const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x, nthreads = (long)gridDim.x * blockDim.x;
+    for (int r = 0; r < a.n; ++r) {
+        const uint8_t* base = reinterpret_cast<const uint8_t*>(a.ptr[r]);
+        const long chunks = (long)((a.bytes[r] + kChunk - 1) / kChunk);
+        for (long c = tid; c < chunks; c += nthreads) {
+            const uint64_t left = a.bytes[r] - (uint64_t)c * kChunk;
+            const uint32_t sz = (uint32_t)(left < kChunk ? (left & ~15ull) : kChunk);
+            if (sz) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + (uint64_t)c * kChunk), "r"(sz) : "memory");
+        }
+    }
+}
+
 __global__ void epoch_advance_kernel(int32_t* guard) {
     pdl_prologue();
     guard[MONO_GUARD_EPOCH] += 1;
@@ -924,6 +943,22 @@ extern "C" int mono_reduce_norm_launch(const mono_reduce_args* r, const mono_act
     else mono::launch_k(mono::reduce_norm_kernel<1>, r->rows, mono::kRnThreads, smem, st, *r, *a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_reduce_norm_launch: %s", cudaGetErrorString(e));
+    return (int)e;
+}
+
+extern "C" int mono_l2_prefetch_launch(const mono_prefetch_args* a, void* stream) {
+    if (!a || a->n < 1 || a->n > MONO_PREFETCH_RANGES) {
+        mono_set_error("mono_l2_prefetch_launch: 1..%d ranges required", MONO_PREFETCH_RANGES);
+        return MONO_E_ARG;
+    }
+    for (int r = 0; r < a->n; ++r)
+        if (!a->ptr[r] || (a->ptr[r] & 15) || a->bytes[r] < 16) {
+            mono_set_error("mono_l2_prefetch_launch: range %d needs a 16-byte aligned address and at least 16 bytes", r);
+            return MONO_E_ARG;
+        }
+    mono::launch_k(mono::l2_prefetch_kernel, mono_sm_count(), 128, 0, (cudaStream_t)stream, *a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) mono_set_error("mono_l2_prefetch_launch: %s", cudaGetErrorString(e));
     return (int)e;
 }
 

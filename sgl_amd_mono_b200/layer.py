@@ -52,6 +52,19 @@ class MlaLayerOp:
         # (a high-priority stream: the index path is the longer of the two branches, and its small launches should
         # not queue behind the head blocks of the main branch)
         self._side = torch.cuda.Stream(device=device, priority=-1) if os.environ.get("MONO_SIDE_STREAM", "1") == "1" else None
+        # Weights towards L2 ahead of the stage that streams them (MONO_L2_PREFETCH=1; off by default): at the layer's
+        # start q_b + index q (and W_UK / W_UV) while q_a | kv_a runs; when the attention starts o_proj (as much as
+        # fits beside the attention's own working set) and the router.  Measured slower (config 3: 655 against 637 us
+        # at TP 1, 244 against 238 us for a TP 8 shard): the stages in between live on memory round trips, and their
+        # loads queue behind the prefetch traffic (q_a | kv_a 22 against 16 us, the attention merge 33 against 25 us).
+        self._pf_stream = self._pf_front = self._pf_back = None
+        if os.environ.get("MONO_L2_PREFETCH", "0") == "1":
+            lim = int(os.environ.get("MONO_L2_PREFETCH_MB", "72")) << 20
+            self._pf_front = ops.l2_prefetch_args([w["q_b"], w.get("idx_wq_b") if cfg.index_heads else None, w["kv_b"]], lim)
+            self._pf_back = ops.l2_prefetch_args([w["o_proj"], w.get("router")], lim)
+            self._pf_stream = torch.cuda.Stream(device=device)
+            self._ev_pf = torch.cuda.Event()
+            self._ev_pf_done = torch.cuda.Event()
         self._ev_fork, self._ev_join, self._ev_idxq = torch.cuda.Event(), torch.cuda.Event(), torch.cuda.Event()
         self.head_after_idxq = os.environ.get("MONO_HEAD_AFTER_IDXQ", "1") != "0"
         h, hl, ql, ih = cfg.hidden, cfg.heads_local, cfg.q_lora, cfg.index_heads
@@ -133,6 +146,23 @@ class MlaLayerOp:
         # the norm staging launch that consumes it (same bits either way)
         self.fuse_reduce = os.environ.get("MONO_FUSE_REDUCE", "1") != "0"
 
+    def _prefetch(self, args) -> None:
+        """Issues an L2 prefetch launch on its own branch, forked from here; the branch is joined at the layer's end."""
+        if args is None or self._pf_stream is None:
+            return
+        main = torch.cuda.current_stream()
+        self._ev_pf.record(main)
+        self._pf_stream.wait_event(self._ev_pf)
+        with torch.cuda.stream(self._pf_stream):
+            ops.l2_prefetch(args)
+            self._ev_pf_done.record(self._pf_stream)
+        self._pf_pending = True
+
+    def _join_prefetch(self) -> None:
+        if getattr(self, "_pf_pending", False):
+            torch.cuda.current_stream().wait_event(self._ev_pf_done)
+            self._pf_pending = False
+
     def _window_slots(self, rows: int, step: StepTables) -> None:
         """The step's selection for window-only attention: row r takes positions pos_r - window + 1 .. pos_r (those
         that exist), in order, as global KV slots; pad rows take none.  A handful of fixed-shape torch ops, captured
@@ -167,6 +197,7 @@ class MlaLayerOp:
                 raise ValueError(f"step.idx_pages: page of {step.idx_pages.shape[-1]} bytes, needs {IDX_PAGE_BYTES}")
         if step.page_table.shape[1] * 64 > self.max_ctx:
             raise ValueError(f"step.page_table: {step.page_table.shape[1]} pages exceed the built context {self.max_ctx}")
+        self._prefetch(self._pf_front)
         if pending is not None:
             ops.reduce_norm(pending, self.x, gamma=w["input_norm"], eps=cfg.eps, out_bf16=self.xbf)
         else:
@@ -221,6 +252,7 @@ class MlaLayerOp:
                 self._window_slots(rows, step)
             else:
                 ops.index_topk(ia)  # rows with at most topk keys keep every key in order
+        self._prefetch(self._pf_back)
         # the merge of the attention splits also stages every head's output for the W_UV GEMV
         # (MONO_MLA_STAGED=0: a staging launch of its own)
         if self.mla_staged:
@@ -232,6 +264,7 @@ class MlaLayerOp:
         if not self.uv_staged:
             ops.act_prep(rows, hl * 128, self.o, src_f32=self.uv_p, nsum=1)
         self.gO.launch(rows)
+        self._join_prefetch()
         # consecutive all-reduces of a step must alternate between the peer buffer's two regions (site % 2): a
         # rank may start pushing launch n + 1 while a peer still reads launch n's words.  A layer without an
         # FFN all-reduce therefore numbers its attention site by the layer alone

@@ -502,6 +502,28 @@ def index_topk(a) -> None:
     L.check(L.load().mono_index_topk_launch(C.byref(a), _stream()), "mono_index_topk_launch")
 
 
+def l2_prefetch_args(tensors, limit_bytes: int | None = None) -> "L.PrefetchArgs | None":
+    """Argument block that pulls ``tensors`` (contiguous device tensors) towards L2, in order, up to ``limit_bytes``."""
+    a = L.PrefetchArgs()
+    left = limit_bytes
+    for t in tensors:
+        if t is None or a.n >= L.PREFETCH_RANGES:
+            continue
+        nbytes = t.numel() * t.element_size()
+        if left is not None:
+            nbytes = min(nbytes, left)
+            left -= nbytes
+        if nbytes < 16 or t.data_ptr() % 16:
+            continue
+        a.ptr[a.n], a.bytes[a.n] = t.data_ptr(), nbytes
+        a.n += 1
+    return a if a.n else None
+
+
+def l2_prefetch(args: "L.PrefetchArgs") -> None:
+    L.check(L.load().mono_l2_prefetch_launch(C.byref(args), _stream()), "mono_l2_prefetch_launch")
+
+
 def epoch_advance(guard) -> None:
     """Adds 1 to the epoch word on the device (after the last layer of a step)."""
     L.check(L.load().mono_epoch_advance_launch(guard.data_ptr(), _stream()), "mono_epoch_advance_launch")
