@@ -539,6 +539,10 @@ int mono_peer_export(void* ptr, unsigned char handle[MONO_IPC_HANDLE_BYTES]);
 int mono_peer_open(const unsigned char handle[MONO_IPC_HANDLE_BYTES], void** out_ptr);
 int mono_peer_close(void* opened_ptr);
 int mono_peer_free(void* ptr);
+/* Blocking copy of device bytes (a peer buffer's words) to the host: for tests and post-mortems that read the
+ * (value, tag) words a step left behind (the reference's layer checks read its symmetric buffer the same way,
+ * test/kernels/glm53/check_layer.py:400-430). */
+int mono_peer_read(void* dst_host, const void* src_device, size_t bytes);
 
 /* ---- GQA block-sparse decode attention (minimax_m3/gfx950: pre_attn.py:8-19 head norms,
  * RoPE and cache insert; index_score.py:1-12 block scores; post_attn.py:466-592 and

@@ -210,6 +210,7 @@ SYMBOLS = {
     "mono_peer_open": (i32, [C.POINTER(C.c_ubyte * 64), C.POINTER(vp)]),
     "mono_peer_close": (i32, [vp]),
     "mono_peer_free": (i32, [vp]),
+    "mono_peer_read": (i32, [vp, vp, C.c_size_t]),
 }
 
 

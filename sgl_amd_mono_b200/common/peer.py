@@ -127,6 +127,10 @@ class PeerBuffer:
     def region_table(self, site: int):
         return self._regions[site % N_REGIONS]
 
+    def snapshot(self):
+        """This rank's buffer as int64 words on the host (blocking): ``[guard 32 words][region 0][region 1]...``."""
+        return _snapshot(self.local, self.nbytes)
+
     def release(self) -> None:
         for p in self.opened:
             self.backend.close(p)
@@ -134,6 +138,16 @@ class PeerBuffer:
         if self.local:
             self.backend.free(self.local)
             self.local = 0
+
+
+def _snapshot(ptr: int, nbytes: int):
+    import torch
+
+    from .. import _lib as L
+
+    out = torch.empty(nbytes // 8, dtype=torch.int64)
+    L.check(L.load().mono_peer_read(out.data_ptr(), ptr, out.numel() * 8), "mono_peer_read")
+    return out
 
 
 class MulticastPeerBuffer:
@@ -178,6 +192,9 @@ class MulticastPeerBuffer:
 
     def region_table(self, site: int):
         return self._regions[site % N_REGIONS]
+
+    def snapshot(self):
+        return _snapshot(self.local, self.nbytes)
 
     def mc_region(self, site: int) -> int:
         """The multicast address of the region ``site`` pushes into."""

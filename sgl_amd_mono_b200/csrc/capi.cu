@@ -203,6 +203,16 @@ extern "C" int mono_peer_free(void* ptr) {
     return (int)e;
 }
 
+// Copies `bytes` of a peer buffer (or any device memory of this process) to the host; blocks.  For tests and
+// post-mortems that look at the (value, tag) words a step left behind.
+extern "C" int mono_peer_read(void* dst_host, const void* src_device, size_t bytes) {
+    if (!dst_host || !src_device || bytes == 0) return MONO_E_ARG;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpy(dst_host, src_device, bytes, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) mono_set_error("mono_peer_read: %s", cudaGetErrorString(e));
+    return (int)e;
+}
+
 extern "C" size_t mono_struct_size(int which) {
     switch (which) {
         case 0: return sizeof(mono_gemv_job);

@@ -128,3 +128,50 @@ def test_tp_layer_ranks_agree_and_match_oracle(world, rows, ctx):
     ref = S.allreduce_rank_order(mparts, d0["h1"])
     assert_close_hidden(ref_out[0], ref, "layer output after the MoE all-reduce",
                         scale=float((ref.float() - d0["h1"].float()).abs().max()), max_abs=4e-2)
+
+
+@pytest.mark.parametrize("world,n_layers,rows,ctx", [(2, 6, 7, 130)])
+def test_tp_stack_under_one_graph_ranks_agree_and_every_word_carries_its_launchs_tag(world, n_layers, rows, ctx):
+    """Six layers + LM head at TP 2 from one CUDA graph, replayed: 13 reductions a step share two regions and one
+    parity.  Ranks agree bit for bit, replays repeat the eager step, the guard words stay clean, and afterwards every
+    (value, tag) word of the live rows in the slots of the step's parity carries the tag of the LAST launch that uses
+    its region (attention sites are even, FFN sites odd: ``tag = epoch * 256 + site + 1``), in every source slot: no
+    word of an earlier or later launch is left where a reader of the last one looked."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import os
+
+    here = Path(__file__).resolve().parent
+    outdir = here / "_tp_out"
+    outdir.mkdir(exist_ok=True)
+    port = _free_port()
+    procs = [subprocess.Popen([sys.executable, str(here / "tp_stack_worker.py"), str(r), str(world), str(port), str(n_layers),
+                               str(rows), str(ctx), str(outdir)], env=dict(os.environ)) for r in range(world)]
+    for p in procs:
+        assert p.wait(timeout=300) == 0
+    got = []
+    for r in range(world):
+        got.append(torch.load(outdir / f"stack_rank{r}.pt", weights_only=False))
+        (outdir / f"stack_rank{r}.pt").unlink()
+    for r in range(world):
+        assert got[r]["rc"] == 0, f"rank {r} guard words {got[r]['words']}"
+        assert got[r]["same"], f"rank {r}: a replay differs from the eager step"
+        assert torch.equal(got[r]["x"], got[0]["x"]) and torch.equal(got[r]["logits"], got[0]["logits"])
+    assert got[0]["logits"].shape[-1] == 5120 and torch.isfinite(got[0]["logits"]).all()
+    # the step ran 1 eager + 1 capture warm-up(s) + 3 replays; the epoch word says how many steps the device saw
+    d = got[0]
+    n, region_words, gw = d["n"], d["region"] // 8, d["guard_bytes"] // 8
+    pairs = n // 2
+    for r in range(world):
+        snap = got[r]["snap"]
+        epoch_now = int(snap[0] & 0xFFFFFFFF)   # guard word 0 (int32) sits in the low half of the first int64
+        last_epoch = epoch_now - 1              # the last step's launches read the epoch before its advance
+        parity = last_epoch & 1
+        for region, site in ((0, 2 * (n_layers - 1)), (1, 2 * (n_layers - 1) + 1)):
+            want = last_epoch * 256 + site + 1
+            base = gw + region * region_words
+            for src in range(world):
+                off = base + (parity * world + src) * 16 * pairs
+                tags = (snap[off : off + rows * pairs] >> 32) & 0xFFFFFFFF
+                assert bool((tags == want).all()), (f"rank {r} region {region} src {src}: tags {sorted(set(tags.tolist()))[:4]}, "
+                                                    f"want {want} (epoch {last_epoch}, site {site})")
