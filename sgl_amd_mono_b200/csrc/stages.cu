@@ -243,8 +243,22 @@ constexpr int kRowdotThreads = 256;
 // Column n by the 256 threads tid = 0..255 of one group (every thread of the CTA calls this:
 // it holds a CTA-wide barrier).  The weights do not depend on the launch before this one, so
 // the first batch of weight loads is issued before the wait on that launch.
-template <int COLS>
-__device__ __forceinline__ void rowdot_col(const mono_rowdot_args& a, int n0, int tid, float (*red)[kRowdotThreads / 32][kMaxRows]) {
+MONO_TL_DECLARE(tl_rowdot)
+template <bool SMEM>
+__device__ __forceinline__ uint2 ld_x(const __nv_bfloat16* p) {
+    if (SMEM) {
+        uint2 v;
+        asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(smem_u32(p)));
+        return v;
+    }
+    return __ldg(reinterpret_cast<const uint2*>(p));
+}
+#define COLS_GROUPS(c) 1  // rowdot_kernel: one 256-thread group per CTA calls rowdot_col
+// `xs`: the step's activation rows staged in shared memory by the caller's CTA (one round trip for all of them), or
+// NULL to read them from global memory as they are needed.
+template <int COLS, bool STAGED = false>
+__device__ __forceinline__ void rowdot_col(const mono_rowdot_args& a, int n0, int tid, float (*red)[kRowdotThreads / 32][kMaxRows],
+                                           const __nv_bfloat16* xs = nullptr) {
     // columns n0 .. n0 + COLS - 1 share every activation load.  The 256 threads split K (4 values per
     // thread per 1024), so every weight load of a column is in flight at once; the order of the sums of
     // one column does not depend on COLS
@@ -257,27 +271,58 @@ __device__ __forceinline__ void rowdot_col(const mono_rowdot_args& a, int n0, in
     const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(a.x_bf16);
     for (int k0 = 0; k0 < a.k; k0 += kRowdotThreads * 4 * 8) {
         // up to eight weight loads per thread and column are in flight before the first is used
+        // (every load is unconditional, from a clamped address: a load under a condition is not issued before the
+        // conversions of the one before it, and a column's weight loads would then cost a memory round trip each;
+        // values past the matrix are zeroed after the loads)
         float4 wv[COLS][8];
+        if (a.w_is_f32) {
 #pragma unroll
-        for (int c = 0; c < COLS; ++c) {
-            const int n = n0 + c;
+            for (int c = 0; c < COLS; ++c)
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                    const int k = k0 + (it * kRowdotThreads + tid) * 4;
+                    wv[c][it] = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.w) + (size_t)min(n0 + c, a.n - 1) * a.k + min(k, a.k - 4)));
+                }
+        } else {
+            uint2 raw[COLS][8];
+#pragma unroll
+            for (int c = 0; c < COLS; ++c)
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                    const int k = k0 + (it * kRowdotThreads + tid) * 4;
+                    raw[c][it] = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.w) + (size_t)min(n0 + c, a.n - 1) * a.k + min(k, a.k - 4)));
+                }
+#pragma unroll
+            for (int c = 0; c < COLS; ++c)
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[c][it].x));
+                    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[c][it].y));
+                    wv[c][it] = make_float4(lo.x, lo.y, hi.x, hi.y);
+                }
+        }
+#pragma unroll
+        for (int c = 0; c < COLS; ++c)
 #pragma unroll
             for (int it = 0; it < 8; ++it) {
                 const int k = k0 + (it * kRowdotThreads + tid) * 4;
-                wv[c][it] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (k < a.k && n < a.n) {
-                    if (a.w_is_f32) {
-                        wv[c][it] = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.w) + (size_t)n * a.k + k));
-                    } else {
-                        const uint2 v = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.w) + (size_t)n * a.k + k));
-                        const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
-                        const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
-                        wv[c][it] = make_float4(lo.x, lo.y, hi.x, hi.y);
-                    }
-                }
+                if (!(k < a.k && n0 + c < a.n)) wv[c][it] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
+        if (k0 == 0) {
+            MONO_TL(tl_rowdot, 1);
+            pdl_wait();  // the activations come from the launch before this one
+            MONO_TL(tl_rowdot, 2);
+            if (STAGED) {
+                // all rows into shared memory, every 16-byte piece requested at once
+                const int pieces = a.rows * a.k / 8;
+                for (int i = tid; i < pieces; i += kRowdotThreads * COLS_GROUPS(COLS))
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(xs + (size_t)i * 8)), "l"(x + (size_t)i * 8) : "memory");
+                asm volatile("cp.async.wait_all;" ::: "memory");
+                __syncthreads();
+                x = xs;
+            }
+            MONO_TL(tl_rowdot, 3);
         }
-        if (k0 == 0) pdl_wait();  // the activations come from the launch before this one
         // The activation loads of a batch (16 row x k-slice pairs) are all issued before the first is used:
         // one L2 round trip per batch instead of one per row.  A column's sums keep their order (k slice,
         // then row), so the bits do not depend on the batch shape.
@@ -290,7 +335,7 @@ __device__ __forceinline__ void rowdot_col(const mono_rowdot_args& a, int n0, in
                     const int k = k0 + ((it0 + h) * kRowdotThreads + tid) * 4;
 #pragma unroll
                     for (int r = 0; r < 8; ++r)
-                        xv[h][r] = __ldg(reinterpret_cast<const uint2*>(x + (size_t)min(r, a.rows - 1) * a.k + min(k, a.k - 4)));
+                        xv[h][r] = ld_x<STAGED>(x + (size_t)min(r, a.rows - 1) * a.k + min(k, a.k - 4));
                 }
                 asm volatile("" ::: "memory");  // the next batch's loads start after this batch's, not among them
 #pragma unroll
@@ -311,7 +356,7 @@ __device__ __forceinline__ void rowdot_col(const mono_rowdot_args& a, int n0, in
                 uint2 xv[kMaxRows];
 #pragma unroll
                 for (int r = 0; r < kMaxRows; ++r)
-                    xv[r] = __ldg(reinterpret_cast<const uint2*>(x + (size_t)min(r, a.rows - 1) * a.k + min(k, a.k - 4)));
+                    xv[r] = ld_x<STAGED>(x + (size_t)min(r, a.rows - 1) * a.k + min(k, a.k - 4));
 #pragma unroll
                 for (int r = 0; r < kMaxRows; ++r) {
                     const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv[r].x));
@@ -323,6 +368,7 @@ __device__ __forceinline__ void rowdot_col(const mono_rowdot_args& a, int n0, in
             }
         }
     }
+    MONO_TL(tl_rowdot, 4);
 #pragma unroll
     for (int c = 0; c < COLS; ++c)
 #pragma unroll
@@ -342,14 +388,17 @@ __device__ __forceinline__ void rowdot_col(const mono_rowdot_args& a, int n0, in
             a.out[(size_t)r * a.out_ld + n0 + c] = s * a.out_scale;
         }
     }
+    MONO_TL(tl_rowdot, 5);
 }
 
-template <int COLS>
+template <int COLS, bool STAGED>
 __global__ void __launch_bounds__(kRowdotThreads, 1) rowdot_kernel(const mono_rowdot_args a) {
-    // one CTA per COLS output columns
+    // one CTA per COLS output columns; STAGED: the launch has rows x k bf16 of dynamic shared memory for the rows
+    extern __shared__ __align__(16) uint8_t rowdot_xs[];
     __shared__ float red[COLS][kRowdotThreads / 32][kMaxRows];
     pdl_launch_dependents();
-    rowdot_col<COLS>(a, blockIdx.x * COLS, threadIdx.x, red);
+    MONO_TL(tl_rowdot, 0);
+    rowdot_col<COLS, STAGED>(a, blockIdx.x * COLS, threadIdx.x, red, reinterpret_cast<const __nv_bfloat16*>(rowdot_xs));
 }
 
 // Router logits and routing in one launch: every CTA computes two columns of the logits (one per
@@ -807,6 +856,14 @@ extern "C" int mono_route_launch(const mono_route_args* a, void* stream) {
     return (int)e;
 }
 
+#ifdef MONO_TIMELINE
+extern "C" int mono_timeline_read_rowdot(unsigned long long* out, int* ctas, int* points) {
+    *ctas = MONO_TL_CTAS;
+    *points = MONO_TL_POINTS;
+    return (int)cudaMemcpyFromSymbol(out, mono::tl_rowdot, sizeof(unsigned long long) * MONO_TL_CTAS * MONO_TL_POINTS);
+}
+#endif
+
 extern "C" int mono_rowdot_launch(const mono_rowdot_args* a, void* stream) {
     if (!a || a->rows < 1 || a->rows > MONO_MAX_ROWS || a->n < 1 || a->k < 128 || (a->k & 127) || !a->w || !a->x_bf16 || !a->out) {
         mono_set_error("mono_rowdot_launch: rows 1..16, k a multiple of 128 and all pointers required");
@@ -816,10 +873,25 @@ extern "C" int mono_rowdot_launch(const mono_rowdot_args* a, void* stream) {
     // than SMs go two to a CTA (sharing the activation loads).  MONO_ROWDOT_COLS=1 / 2 forces the choice.
     const char* cf = getenv("MONO_ROWDOT_COLS");
     const int cols = cf ? (atoi(cf) == 2 ? 2 : 1) : (a->n > mono_sm_count() ? 2 : 1);
-    if (cols == 2)
-        mono::launch_k(mono::rowdot_kernel<2>, (a->n + 1) / 2, mono::kRowdotThreads, 0, (cudaStream_t)stream, *a);
-    else
-        mono::launch_k(mono::rowdot_kernel<1>, a->n, mono::kRowdotThreads, 0, (cudaStream_t)stream, *a);
+    // the rows staged in shared memory when they fit beside a resident CTA (8 rows x 7168: 112 KB): one round trip
+    // for all activation loads instead of one per batch (MONO_ROWDOT_STAGED=0: read from global memory)
+    const char* sf = getenv("MONO_ROWDOT_STAGED");
+    const size_t xbytes = (size_t)a->rows * a->k * 2;
+    const int staged = (!sf || sf[0] != '0') && xbytes <= 160 * 1024 && (reinterpret_cast<uintptr_t>(a->x_bf16) & 15) == 0 && (a->k & 7) == 0;
+    static std::atomic<uint64_t> attr_once{0};  // bit d: set on device d
+    if (staged && mono::attr_needed(attr_once)) {
+        cudaError_t e1 = cudaFuncSetAttribute(mono::rowdot_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        if (e1 == cudaSuccess) e1 = cudaFuncSetAttribute(mono::rowdot_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        if (e1 != cudaSuccess) {
+            mono_set_error("mono_rowdot_launch: %s", cudaGetErrorString(e1));
+            return (int)e1;
+        }
+        mono::attr_done(attr_once);
+    }
+    if (cols == 2 && staged) mono::launch_k(mono::rowdot_kernel<2, true>, (a->n + 1) / 2, mono::kRowdotThreads, xbytes, (cudaStream_t)stream, *a);
+    else if (cols == 2) mono::launch_k(mono::rowdot_kernel<2, false>, (a->n + 1) / 2, mono::kRowdotThreads, 0, (cudaStream_t)stream, *a);
+    else if (staged) mono::launch_k(mono::rowdot_kernel<1, true>, a->n, mono::kRowdotThreads, xbytes, (cudaStream_t)stream, *a);
+    else mono::launch_k(mono::rowdot_kernel<1, false>, a->n, mono::kRowdotThreads, 0, (cudaStream_t)stream, *a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_rowdot_launch: %s", cudaGetErrorString(e));
     return (int)e;
