@@ -84,10 +84,20 @@ __global__ void __launch_bounds__(kMidThreads2, 1) mla_mid_kernel(const mono_mla
         rc = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.cos)[pos * 32 + tid]);
         rs = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.sin)[pos * 32 + tid]);
     }
+    // part 0: thread t owns columns 4 t .. 4 t + 3 of each 1024-column stretch of q_a: the four values lane t % 32 holds
+    // of chunk (stretch * 8 + warp) when the row is split into hi / lo planes, so the row never goes through shared
+    // memory.  Its norm weights are read here, during the wait.
+    uint2 qg[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)};
+    if (part == 0) {
+#pragma unroll
+        for (int it = 0; it < 2; ++it) {
+            const int i = it * kMidThreads2 * 4 + tid * 4;
+            qg[it] = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.q_a_norm) + min(i, a.q_lora - 4)));
+        }
+    }
     MID_TL(1);
     pdl_wait();
     MID_TL(2);
-    __shared__ __align__(16) float xq[2048 + 64];
     __shared__ __align__(16) float kv[kKvDim];
     __shared__ float ikv[128];
     __shared__ float red[kMidThreads2 / 32];
@@ -107,35 +117,41 @@ __global__ void __launch_bounds__(kMidThreads2, 1) mla_mid_kernel(const mono_mla
     // the whole row (q_a | latent | rope) is summed over the K splits with 16-byte loads
     // issued together, so it costs one memory latency rather than one per element
     float ssq = 0.f, ssq_kv = 0.f;
-    const int i_lo = part == 0 ? 0 : a.q_lora, i_hi = part == 0 ? a.q_lora : (part == 1 ? a.q_lora + kKvDim : 0);
-    for (int i = i_lo + tid * 4; i < i_hi; i += kMidThreads2 * 4) {
-        const float4 v = sum_partials4<16>(src + i, a.sum_stride, a.nsum);
-        const float sq = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-        if (i < a.q_lora) {
-            *reinterpret_cast<float4*>(xq + i) = v;
-            ssq += sq;
-        } else {
-            *reinterpret_cast<float4*>(kv + (i - a.q_lora)) = v;
-            if (i - a.q_lora < 512) ssq_kv += sq;
-        }
-    }
-    MID_TL(3);
     if (part == 0) {
+        float4 qv[2];
+#pragma unroll
+        for (int it = 0; it < 2; ++it) {
+            const int i = it * kMidThreads2 * 4 + tid * 4;
+            qv[it] = sum_partials4<16>(src + min(i, a.q_lora - 4), a.sum_stride, a.nsum);
+            if (i >= a.q_lora) qv[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+            ssq += qv[it].x * qv[it].x + qv[it].y * qv[it].y + qv[it].z * qv[it].z + qv[it].w * qv[it].w;
+        }
+        MID_TL(3);
         const float r = rsqrtf(block_sum<kMidThreads2 / 32>(ssq, red) / (float)a.q_lora + a.eps);
         MID_TL(4);
-        const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(a.q_a_norm);
-        for (int i = tid; i < a.q_lora; i += kMidThreads2) xq[i] = bf16_round(xq[i] * r * __bfloat162float(g[i]));
-        __syncthreads();
-        for (int c = warp; c < a.q_lora / 128; c += kMidThreads2 / 32) {
-            float v[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) v[i] = xq[c * 128 + 4 * lane + i];
-            uint8_t* hi = a.qa_planes + (size_t)row * a.qa_ld + c * 128;
-            hilo_chunk(v, lane, hi, hi + a.qa_plane_stride, a.qa_scale + (size_t)row * a.qa_scale_ld + c);
+        for (int it = 0; it < 2; ++it) {
+            const int c = it * (kMidThreads2 / 32) + warp;
+            if (c < a.q_lora / 128) {  // (the same for a whole warp)
+                const float2 glo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qg[it].x));
+                const float2 ghi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qg[it].y));
+                const float v[4] = {bf16_round(qv[it].x * r * glo.x), bf16_round(qv[it].y * r * glo.y), bf16_round(qv[it].z * r * ghi.x),
+                                    bf16_round(qv[it].w * r * ghi.y)};
+                uint8_t* hi = a.qa_planes + (size_t)row * a.qa_ld + c * 128;
+                hilo_chunk(v, lane, hi, hi + a.qa_plane_stride, a.qa_scale + (size_t)row * a.qa_scale_ld + c);
+            }
         }
         MID_TL(5);
         return;
     }
+    const int i_lo = a.q_lora, i_hi = part == 1 ? a.q_lora + kKvDim : 0;
+    for (int i = i_lo + tid * 4; i < i_hi; i += kMidThreads2 * 4) {
+        const float4 v = sum_partials4<16>(src + i, a.sum_stride, a.nsum);
+        const float sq = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        *reinterpret_cast<float4*>(kv + (i - a.q_lora)) = v;
+        if (i - a.q_lora < 512) ssq_kv += sq;
+    }
+    MID_TL(3);
     // ---- latent: RMSNorm -> bf16; k_pe: interleaved RoPE -> bf16
     if (part == 1) {
         const float r = rsqrtf(block_sum<kMidThreads2 / 32>(ssq_kv, red) / 512.f + a.eps);

@@ -657,16 +657,7 @@ __global__ void __cluster_dims__(C, 1, 1) __launch_bounds__(kRnThreads, 1) reduc
         const int i = col0 + li;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (live) {
-            const float* src = r.partial + (size_t)row * r.ld + i;
-            for (int s0 = 0; s0 < r.nsum; s0 += 8) {  // eight slices' loads in flight, added in slice order
-                float4 p[8];
-#pragma unroll
-                for (int s = 0; s < 8; ++s)
-                    p[s] = s0 + s < r.nsum ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)(s0 + s) * r.sum_stride)) : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                for (int s = 0; s < 8; ++s)
-                    if (s0 + s < r.nsum) { v.x += p[s].x; v.y += p[s].y; v.z += p[s].z; v.w += p[s].w; }
-            }
+            v = sum_partials4<8>(r.partial + (size_t)row * r.ld + i, r.sum_stride, r.nsum);  // slices added in order
         }
         const __nv_bfloat162 pb0 = __floats2bfloat162_rn(v.x, v.y), pb1 = __floats2bfloat162_rn(v.z, v.w);
         float2 rlo = make_float2(0.f, 0.f), rhi = rlo;

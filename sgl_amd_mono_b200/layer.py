@@ -67,6 +67,12 @@ class MlaLayerOp:
             self._ev_pf_done = torch.cuda.Event()
         self._ev_fork, self._ev_join, self._ev_idxq = torch.cuda.Event(), torch.cuda.Event(), torch.cuda.Event()
         self.head_after_idxq = os.environ.get("MONO_HEAD_AFTER_IDXQ", "1") != "0"
+        # The index head weights depend on the normed input only and used to run beside mla_mid on the index branch.
+        # Stamps showed what that costs: mla_mid's loads of the partial sums took 7 us with that launch running beside
+        # it and 1.8 us alone (every CTA's loads completing at the same instant: launches that end on one branch stall
+        # the loads in flight on the other).  They now run on the index branch after the index queries
+        # (MONO_IDXW_LATE=0: the old place): 8 us off the front, 5 us onto the index branch.
+        self.idxw_late = os.environ.get("MONO_IDXW_LATE", "1") != "0"
         h, hl, ql, ih = cfg.hidden, cfg.heads_local, cfg.q_lora, cfg.index_heads
         R = L.MAX_ROWS
         z = lambda *s, dt=torch.float32: torch.zeros(*s, dtype=dt, device=device)  # noqa: E731
@@ -203,7 +209,10 @@ class MlaLayerOp:
         else:
             ops.act_prep(rows, cfg.hidden, self.x, src_bf16=h, gamma=w["input_norm"], eps=cfg.eps, out_bf16=self.xbf)
         self.gA.launch(rows)
-        if ih and self._side is not None:
+        idxw_late = ih and self._side is not None and self.idxw_late
+        if idxw_late:
+            pass  # the index head weights run on the index branch, after the index queries (below)
+        elif ih and self._side is not None:
             main = torch.cuda.current_stream()
             self._ev_fork.record(main)
             self._side.wait_event(self._ev_fork)
@@ -233,6 +242,8 @@ class MlaLayerOp:
                     ops.q_post(rows, 0, self.qb_p, self.nsB, w["kv_b"], w["kv_b_s"], step.cos, step.sin, step.positions,
                                self.q_full, ih, self.iq_p, self.nsB, self.idx_q)
                     self._ev_idxq.record(self._side)
+                if idxw_late:
+                    ops.rowdot(rows, w["idx_wproj"], self.xbf, self.idx_w, out_scale=(ih**-0.5) * (128**-0.5))
                 ops.index_score(ia)
                 ops.index_topk(ia)
                 self._ev_join.record(self._side)
