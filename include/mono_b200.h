@@ -491,6 +491,11 @@ typedef struct mono_q_post_args {
     void* idx_q; /* bf16 [16][index_heads][128] */
 } mono_q_post_args;
 int mono_q_post_launch(const mono_q_post_args* a, void* stream);
+/* The index queries of mono_q_post_launch (heads ignored) and a row-dot (mono_rowdot_args: the index head weights,
+ * x @ weights_proj, glm53/gfx950/kernel.py:1781-1970) in one launch: the two inputs of the score launch that are still
+ * missing when the q_b projection ends (kernel.py:2262-2353).  mono_rowdot_args is declared further down. */
+struct mono_rowdot_args;
+int mono_index_prep_launch(const mono_q_post_args* q, const struct mono_rowdot_args* d, void* stream);
 
 /* ---- lightning indexer (glm53/gfx950/kernel.py:2684-3000 scores, :3002-3636 exact
  * top-k; FP4 keys as deepseek_v4/gfx950/kernels/stages/indexer.py:143-151) ----------

@@ -192,6 +192,7 @@ SYMBOLS = {
     "mono_reduce_launch": (i32, [C.POINTER(ReduceArgs), vp]),
     "mono_reduce_norm_launch": (i32, [C.POINTER(ReduceArgs), C.POINTER(ActPrepArgs), vp]),
     "mono_epoch_advance_launch": (i32, [vp, vp]),
+    "mono_index_prep_launch": (i32, [vp, vp, vp]),
     "mono_l2_prefetch_launch": (i32, [vp, vp]),
     "mono_logits_peer_bytes": (C.c_size_t, [i32, i32]),
     "mono_logits_gather_launch": (i32, [C.POINTER(LogitsGatherArgs), vp]),

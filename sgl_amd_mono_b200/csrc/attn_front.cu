@@ -6,6 +6,7 @@
 // Hadamard, scale + quantise), :2183-2353 (q_b epilogue: RoPE, index q), :2355-2443
 // (W_UK absorb); FP4 key format of deepseek_v4/gfx950/kernels/stages/indexer.py:143-151.
 #include "mono_common.cuh"
+#include "rowdot.cuh"
 
 extern void mono_set_error(const char* fmt, ...);
 
@@ -352,46 +353,60 @@ __global__ void __launch_bounds__(kQPostThreads) q_post_kernel(const mono_q_post
     }
 }
 
+// One index query (row r, index head ih) by the first 128 threads of a block; every thread of the block calls this
+// (the Hadamard butterflies hold block-wide barriers; threads past 127 mirror thread - 128).
+__device__ __forceinline__ void index_query_body(const mono_q_post_args& a, int idx, int tid, float* iq) {
+    const __nv_bfloat16* cosb = reinterpret_cast<const __nv_bfloat16*>(a.cos);
+    const __nv_bfloat16* sinb = reinterpret_cast<const __nv_bfloat16*>(a.sin);
+    const int r = idx / a.index_heads, ih = idx - r * a.index_heads, t = tid & 127;
+    float c = 0.f, sn = 0.f;
+    if (tid < 32) {  // inputs of the step: read during the wait
+        const int64_t pos = a.positions[r];
+        c = __bfloat162float(cosb[pos * 32 + tid]);
+        sn = __bfloat162float(sinb[pos * 32 + tid]);
+    }
+    pdl_wait();
+    const float* src = a.iq + (size_t)r * a.iq_ld + ih * 128;
+    float v = 0.f;
+    for (int s0 = 0; s0 < a.iq_nsum; s0 += 4) {
+        float t4[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) t4[j] = __ldcg(src + (size_t)min(s0 + j, a.iq_nsum - 1) * a.iq_sum_stride + t);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v += s0 + j < a.iq_nsum ? t4[j] : 0.f;
+    }
+    if (tid < 128) iq[t] = v;
+    __syncthreads();
+    float r0 = 0.f, r1 = 0.f;
+    if (tid < 32) {
+        const float x0 = iq[2 * tid], x1 = iq[2 * tid + 1];
+        r0 = x0 * c - x1 * sn;
+        r1 = x0 * sn + x1 * c;
+    }
+    __syncthreads();
+    if (tid < 32) { iq[2 * tid] = r0; iq[2 * tid + 1] = r1; }
+    fwht128(iq, t);
+    if (tid < 128) reinterpret_cast<__nv_bfloat16*>(a.idx_q)[((size_t)r * a.index_heads + ih) * 128 + t] = __float2bfloat16_rn(iq[t]);
+}
+
 // The index queries alone: a kernel of its own, so that its small blocks (few registers, 1 KB of shared memory) find
 // room on SMs that the head blocks of q_post_kernel already fill while they wait for the same projection.
 __global__ void __launch_bounds__(kQPostThreads) q_post_index_kernel(const mono_q_post_args a) {
     pdl_launch_dependents();
     __shared__ float iq[128];
-    const int tid = threadIdx.x;
-    const __nv_bfloat16* cosb = reinterpret_cast<const __nv_bfloat16*>(a.cos);
-    const __nv_bfloat16* sinb = reinterpret_cast<const __nv_bfloat16*>(a.sin);
-    {
-        const int idx = blockIdx.x;
-        const int r = idx / a.index_heads, ih = idx - r * a.index_heads;
-        float c = 0.f, sn = 0.f;
-        if (tid < 32) {  // inputs of the step: read during the wait
-            const int64_t pos = a.positions[r];
-            c = __bfloat162float(cosb[pos * 32 + tid]);
-            sn = __bfloat162float(sinb[pos * 32 + tid]);
-        }
-        pdl_wait();
-        const float* src = a.iq + (size_t)r * a.iq_ld + ih * 128;
-        float v = 0.f;
-        for (int s0 = 0; s0 < a.iq_nsum; s0 += 4) {
-            float t4[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) t4[j] = __ldcg(src + (size_t)min(s0 + j, a.iq_nsum - 1) * a.iq_sum_stride + tid);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) v += s0 + j < a.iq_nsum ? t4[j] : 0.f;
-        }
-        iq[tid] = v;
-        __syncthreads();
-        float r0 = 0.f, r1 = 0.f;
-        if (tid < 32) {
-            const float x0 = iq[2 * tid], x1 = iq[2 * tid + 1];
-            r0 = x0 * c - x1 * sn;
-            r1 = x0 * sn + x1 * c;
-        }
-        __syncthreads();
-        if (tid < 32) { iq[2 * tid] = r0; iq[2 * tid + 1] = r1; }
-        fwht128(iq, tid);
-        reinterpret_cast<__nv_bfloat16*>(a.idx_q)[((size_t)r * a.index_heads + ih) * 128 + tid] = __float2bfloat16_rn(iq[tid]);
-    }
+    index_query_body(a, blockIdx.x, threadIdx.x, iq);
+}
+
+// The index queries and the index head weights (x @ weights_proj) in one launch: the two inputs of the score launch
+// that are not there yet when the q_b projection ends.  Blocks [0, d.n): one head-weight column each (the body of
+// rowdot_kernel; they need the normed input only and are done before the projection is); the rest: one index query
+// each.  One launch on the step's longer branch instead of two.
+__global__ void __launch_bounds__(kRowdotThreads, 2) index_prep_kernel(const mono_q_post_args a, const mono_rowdot_args d) {
+    pdl_launch_dependents();
+    __shared__ float red[1][kRowdotThreads / 32][kMaxRows];
+    __shared__ float iq[128];
+    if ((int)blockIdx.x < d.n) rowdot_col<1, false>(d, blockIdx.x, threadIdx.x, red);
+    else index_query_body(a, blockIdx.x - d.n, threadIdx.x, iq);
 }
 
 }  // namespace mono
@@ -417,6 +432,19 @@ extern "C" int mono_mla_mid_launch(const mono_mla_mid_args* a, void* stream) {
     mono::launch_k(mono::mla_mid_kernel, dim3(a->rows, a->ik ? 3 : 2), mono::kMidThreads2, 0, (cudaStream_t)stream, *a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) mono_set_error("mono_mla_mid_launch: %s", cudaGetErrorString(e));
+    return (int)e;
+}
+
+extern "C" int mono_index_prep_launch(const mono_q_post_args* a, const mono_rowdot_args* d, void* stream) {
+    if (!a || !d || a->rows < 1 || a->rows > MONO_MAX_ROWS || a->index_heads < 1 || !a->cos || !a->sin || !a->positions || !a->iq ||
+        !a->idx_q || d->rows != a->rows || d->n < 1 || d->k < 128 || (d->k & 127) || !d->w || !d->x_bf16 || !d->out) {
+        mono_set_error("mono_index_prep_launch: rows 1..16, index heads with their partial sums and output, and a row-dot over "
+                       "the same rows (k a multiple of 128) required");
+        return MONO_E_ARG;
+    }
+    mono::launch_k(mono::index_prep_kernel, d->n + a->rows * a->index_heads, mono::kRowdotThreads, 0, (cudaStream_t)stream, *a, *d);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) mono_set_error("mono_index_prep_launch: %s", cudaGetErrorString(e));
     return (int)e;
 }
 

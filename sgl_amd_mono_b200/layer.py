@@ -238,11 +238,16 @@ class MlaLayerOp:
             self._ev_fork.record(main)
             self._side.wait_event(self._ev_fork)
             with torch.cuda.stream(self._side):
-                if not fused_q:
+                if not fused_q and idxw_late:
+                    # the index queries and the index head weights in one launch
+                    ops.index_prep(rows, ih, self.iq_p, self.nsB, step.cos, step.sin, step.positions, self.idx_q, w["idx_wproj"],
+                                   self.xbf, self.idx_w, (ih**-0.5) * (128**-0.5))
+                    self._ev_idxq.record(self._side)
+                elif not fused_q:
                     ops.q_post(rows, 0, self.qb_p, self.nsB, w["kv_b"], w["kv_b_s"], step.cos, step.sin, step.positions,
                                self.q_full, ih, self.iq_p, self.nsB, self.idx_q)
                     self._ev_idxq.record(self._side)
-                if idxw_late:
+                elif idxw_late:
                     ops.rowdot(rows, w["idx_wproj"], self.xbf, self.idx_w, out_scale=(ih**-0.5) * (128**-0.5))
                 ops.index_score(ia)
                 ops.index_topk(ia)

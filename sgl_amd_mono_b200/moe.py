@@ -114,11 +114,11 @@ class MoeFfn:
                       expert_list=self.expert_list, n_expert=self.n_expert, max_expert=self.max_expert,
                       coef=self.coef, nsplit=self.groups)
         self.out = z(L.MAX_ROWS, h, dt=torch.bfloat16)
-        # MONO_ROUTER_FUSED=1: router logits and routing in one launch (the last CTA routes).  Measured
-        # 2-3 us slower than two launches: the routing is a serial tail either way, and as a launch of
-        # its own its start-up overlaps the logits under programmatic dependent launch
+        # Router logits and routing in one launch (the CTA that finishes its logit columns last routes the step;
+        # MONO_ROUTER_FUSED=0: two launches).  Measured on config 3 once the logit weights' loads no longer cost a
+        # round trip each: 622.6 against 626.7 us at TP 1, equal for a TP 8 shard, one launch fewer
         self.route_counter = z(1, dt=torch.int32)
-        self.router_fused = os.environ.get("MONO_ROUTER_FUSED", "0") != "0"
+        self.router_fused = os.environ.get("MONO_ROUTER_FUSED", "1") != "0"
         # ---- one launch for up/gate -> SwiGLU -> down (FP8 on the tcgen05 path): the same jobs, chained
         self.chained = None
         # (the CTA that finishes an expert's last up/gate task computes the whole activation of that expert:

@@ -476,6 +476,18 @@ def q_post(rows: int, heads: int, qb, nsum: int, kv_b, kv_b_scale, cos, sin, pos
     L.check(L.load().mono_q_post_launch(C.byref(a), _stream()), "mono_q_post_launch")
 
 
+def index_prep(rows: int, index_heads: int, iq, iq_nsum: int, cos, sin, positions, idx_q, w_proj, x_bf16, idx_w,
+               out_scale: float) -> None:
+    """The index queries and the index head weights (``x_bf16 @ w_proj.T * out_scale``) in one launch."""
+    a = L.QPostArgs()
+    a.rows, a.heads, a.index_heads = rows, 0, index_heads
+    a.cos, a.sin, a.positions = cos.data_ptr(), sin.data_ptr(), positions.data_ptr()
+    a.iq, a.iq_nsum, a.iq_ld, a.iq_sum_stride = iq.data_ptr(), iq_nsum, iq.shape[-1], L.MAX_ROWS * iq.shape[-1]
+    a.idx_q = idx_q.data_ptr()
+    d = rowdot_args(rows, w_proj, x_bf16, idx_w, out_scale)
+    L.check(L.load().mono_index_prep_launch(C.byref(a), C.byref(d), _stream()), "mono_index_prep_launch")
+
+
 def index_args(rows: int, index_heads: int, topk: int, idx_q, idx_w, idx_pages, page_table, positions, slots,
                scores, topk_slots, topk_pos=None, iq=None, iq_nsum: int = 0, cos=None, sin=None) -> "L.IndexArgs":
     """``iq`` (with ``cos`` / ``sin``): the q_b GEMV's partial sums of the index queries; the score launch
