@@ -125,32 +125,15 @@ def time_steps(fn, steps: int, warmup: int, flush: torch.Tensor | None, sampler=
 
 
 def count_kernel_launches(fn) -> int:
-    """Kernels of this library that one call of ``fn`` launches, counted at the C ABI (the entry points
-    that launch two kernels count twice)."""
+    """Kernels of this library that one call of ``fn`` launches: the library counts every launch it makes
+    (``mono_launch_count``), so entry points that launch several kernels count as many."""
     from sgl_amd_mono_b200 import _lib as L
 
-    lib, n = L.load(), [0]
-    two = {"mono_sparse_mla_launch", "mono_sparse_mla_launch_noalloc", "mono_gqa_attn_launch"}
-
-    class Proxy:
-        def __getattr__(self, name):
-            f = getattr(lib, name)
-            if not (name.endswith("_launch") or name.endswith("_noalloc")):
-                return f
-
-            def counted(*a):
-                n[0] += 2 if name in two else 1
-                return f(*a)
-
-            return counted
-
-    L._lib = Proxy()
-    try:
-        fn()
-        torch.cuda.synchronize()
-    finally:
-        L._lib = lib
-    return n[0]
+    lib = L.load()
+    before = lib.mono_launch_count()
+    fn()
+    torch.cuda.synchronize()
+    return int(lib.mono_launch_count() - before)
 
 
 class _Null:
@@ -950,6 +933,7 @@ def measure_stack(args, dev, rank, flush) -> dict:
         torch.cuda.synchronize()
         e2e.append(a.elapsed_time(b))
     wl.check()
+    wl.launches_per_step = count_kernel_launches(wl._eager)
     h2d, d2h = wl.e2e_bytes()
     peak, _ = measured_peaks()
     return {"workload": wl.name, "steps": steps, "step_us": ms * 1000.0, "us_per_layer": ms * 1000.0 / wl.n_layers,

@@ -59,6 +59,8 @@ const char* mono_last_error(void);
 /* SM count of the current device (the grid every persistent launch is sized by;
  * reference: common/plan.py:23-25 BLOCKS = 256 CUs). */
 int mono_sm_count(void);
+/* Kernels this library has launched in this process so far (a graph replay launches none: count an eager step). */
+unsigned long long mono_launch_count(void);
 
 /* ---- guard (common/guard.py:100-241; reads replace the reference's process kill) */
 /* Copies the three error words to out[3] = {deadline, peer, arg} with a blocking

@@ -206,6 +206,7 @@ SYMBOLS = {
     "mono_gqa_select_launch": (i32, [C.POINTER(GqaArgs), vp]),
     "mono_gqa_attn_launch": (i32, [C.POINTER(GqaArgs), vp]),
     "mono_struct_size": (C.c_size_t, [i32]),
+    "mono_launch_count": (C.c_ulonglong, []),
     "mono_peer_alloc": (i32, [C.c_size_t, C.POINTER(vp)]),
     "mono_peer_export": (i32, [vp, C.POINTER(C.c_ubyte * 64)]),
     "mono_peer_open": (i32, [C.POINTER(C.c_ubyte * 64), C.POINTER(vp)]),

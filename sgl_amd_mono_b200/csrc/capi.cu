@@ -15,6 +15,11 @@ void mono_set_error(const char* fmt, ...) {
     va_end(ap);
 }
 
+std::atomic<unsigned long long> g_mono_launches{0};
+// Kernels this library has launched in this process (every launch goes through one helper): what a caller's
+// "launches per step" claim is counted from.
+extern "C" unsigned long long mono_launch_count(void) { return g_mono_launches.load(std::memory_order_relaxed); }
+
 int g_mono_pdl = 1;
 extern "C" int mono_set_pdl(int on) {
     const int old = g_mono_pdl;

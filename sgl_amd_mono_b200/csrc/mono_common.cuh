@@ -341,6 +341,7 @@ __device__ __forceinline__ float ld_cg_f32(const float* p) {
 // Host side: one launch helper, with or without the programmatic-serialization attribute.
 #include <atomic>
 extern int g_mono_pdl;
+extern std::atomic<unsigned long long> g_mono_launches;  // kernels launched through launch_k since the library was loaded
 namespace mono {
 // Function attributes (the > 48 KB dynamic shared memory opt-in) belong to a device's copy of a
 // kernel, so they are set once per device, whichever thread first launches there.  Usage:
@@ -373,6 +374,7 @@ inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = g_mono_pdl ? 1 : 0;
+    g_mono_launches.fetch_add(1, std::memory_order_relaxed);
     return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 }  // namespace mono
