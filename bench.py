@@ -821,7 +821,7 @@ class StackWorkload:
         self._eager()
         torch.cuda.synchronize()
         self.check()
-        self.launches_per_step = self.stack.launches_per_step
+        self.launches_per_step = 0  # counted from an eager step by the caller (count_kernel_launches)
         self.logits_host = torch.empty(self.total, self.logits.shape[-1], dtype=torch.float32).pin_memory()
         self.graph = None
         if os.environ.get("MONO_BENCH_GRAPH", "1") == "1":

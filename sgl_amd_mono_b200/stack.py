@@ -37,10 +37,12 @@ class DecoderStack:
                              peer=head_peer, site=254, deadline_s=deadline_s) if "lm_head" in last else None
         self.graph = None
 
-    @property
-    def launches_per_step(self) -> int:
-        per = 23 if self.cfg.index_heads else 20
-        return per * (len(self.layers) + (1 if self.draft else 0)) + (2 if self.head else 0) + 1
+    def count_launches(self, h: torch.Tensor, tables, draft_tables=None, draft_rows: int = 0) -> int:
+        """Kernels one eager step launches (the library counts its own launches; a graph replay launches none)."""
+        lib = L.load()
+        before = lib.mono_launch_count()
+        self.step(h, tables, draft_tables, draft_rows)
+        return int(lib.mono_launch_count() - before)
 
     def step(self, h: torch.Tensor, tables: list[StepTables], draft_tables: StepTables | None = None,
              draft_rows: int = 0):
