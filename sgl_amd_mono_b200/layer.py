@@ -46,11 +46,10 @@ class MlaLayerOp:
         self.cfg, self.w, self.dev, self.peer, self.layer = cfg, w, device, peer, layer
         self.deadline_s = deadline_s
         self.guard = guard if guard is not None else torch.zeros(L.GUARD_WORDS, dtype=torch.int32, device=device)
-        # the index head weights depend on the normed input only: they run on a side stream, forked after the
-        # input norm; the index queries, scores and top-k follow them there and join before the attention
-        # (a fork / join that a CUDA graph capture records too)
-        # (a high-priority stream: the index path is the longer of the two branches, and its small launches should
-        # not queue behind the head blocks of the main branch)
+        # the index path (index queries + head weights, scores, top-k) runs on a second stream, forked after the q_b
+        # projection and joined before the attention (a fork / join that a CUDA graph capture records too), beside
+        # the W_UK absorb of the heads on the main one.  A high-priority stream: the index path is the longer of the
+        # two branches, and its small launches should not queue behind the head blocks of the main branch
         self._side = torch.cuda.Stream(device=device, priority=-1) if os.environ.get("MONO_SIDE_STREAM", "1") == "1" else None
         # Weights towards L2 ahead of the stage that streams them (MONO_L2_PREFETCH=1; off by default): at the layer's
         # start q_b + index q (and W_UK / W_UV) while q_a | kv_a runs; when the attention starts o_proj (as much as

@@ -71,7 +71,7 @@ def main() -> None:
     fx["slices"] = [select_slices(b) for b in bounds]
     # exact top-k of a row's own scores (glm53/check.py:100-117 `_exact_topk_outputs`): the reference's checker counts
     # how many keys of ITS exact top-k (radix keys, stable descending sort = ties to the lowest position) a selection
-    # misses.  Stored: the inputs, the reference's own top-2048 slot sets, and the checker's verdict on the selection
+    # misses.  Stored: the inputs, the reference's own top-2048 slot sets, and the checker's answer on the selection
     # the oracle (oracle/stages.py exact_topk_positions) makes from the same scores.
     import sys
 
@@ -98,10 +98,10 @@ def main() -> None:
         ref_sets.append(sorted((page_table[r, ref_pos // 64].long() * 64 + ref_pos % 64).tolist()))
     step = SimpleNamespace(indptr=torch.tensor(indptr), topk=torch.tensor(picked), positions=positions,
                            page_table=page_table, req_ids=torch.arange(rows))
-    verdict = glm_check._exact_topk_outputs(step, sc.view(torch.int32), rows)
-    assert verdict == {"topk_exact": {"max_abs": 0.0}}, verdict
+    answer = glm_check._exact_topk_outputs(step, sc.view(torch.int32), rows)
+    assert answer == {"topk_exact": {"max_abs": 0.0}}, answer
     fx["topk_scores"], fx["topk_positions"], fx["topk_page_table"] = sc, positions, page_table
-    fx["topk_k"], fx["topk_ref_sets"], fx["topk_checker_verdict"] = TOPK, ref_sets, verdict
+    fx["topk_k"], fx["topk_ref_sets"], fx["topk_checker_verdict"] = TOPK, ref_sets, answer
     torch.save(fx, OUT)
     print("wrote", OUT, OUT.stat().st_size, "bytes")
 
