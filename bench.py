@@ -29,6 +29,7 @@ import torch
 
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
+sys.path.insert(1, str(ROOT / "tests"))  # the synthetic-input generator (tests/synth.py) lives beside the tests
 
 L2_FLUSH_BYTES = 256 << 20
 
@@ -192,7 +193,7 @@ class SparseMlaWorkload:
 
     def make_inputs(self, dev, rank, tp):
         """Synthetic inputs only (torch): nothing of the kernel library is touched."""
-        from sgl_amd_mono_b200 import synth
+        import synth
 
         self.dev = dev
         self.q, self.pages, self.sel, _ = synth.sparse_mla_inputs(self.rows, self.heads, self.ctx, self.topk, device=dev, seed=rank)
@@ -254,7 +255,7 @@ class MoeWorkload:
         self.rows = rows
 
     def make_inputs(self, dev, rank, tp, world=1):
-        from sgl_amd_mono_b200 import synth
+        import synth
         from sgl_amd_mono_b200.config import CFG_V3
         from dataclasses import replace
 
@@ -337,7 +338,7 @@ class LayerWorkload:
 
     def make_inputs(self, dev, rank, tp, world=1):
         """Synthetic weights, caches, tables and rows (torch only: nothing of the kernel library is touched)."""
-        from sgl_amd_mono_b200 import synth
+        import synth
         from sgl_amd_mono_b200.config import CFG_V3
 
         self.cfg = cfg = CFG_V3.with_tp(tp)
@@ -477,7 +478,7 @@ class GqaLayerWorkload(LayerWorkload):
         super().__init__(rows, ctx)
 
     def make_inputs(self, dev, rank, tp, world=1):
-        from sgl_amd_mono_b200 import synth
+        import synth
         from sgl_amd_mono_b200.config import LayerConfig
         from sgl_amd_mono_b200.gqa import CFG_GQA
 
@@ -760,7 +761,7 @@ class StackWorkload:
     def make_inputs(self, dev, rank, tp, world=1, layers=None):
         """Synthetic weights, caches and tables of ``layers`` (default: all of them).  StepTables is a plain
         dataclass of tensors: nothing of the kernel library is touched."""
-        from sgl_amd_mono_b200 import synth
+        import synth
         from sgl_amd_mono_b200.config import CFG_FLASH
         from sgl_amd_mono_b200.layer import StepTables
         from dataclasses import replace as dc_replace
@@ -795,7 +796,8 @@ class StackWorkload:
         self.h_host = torch.randn(self.total, cfg.hidden, generator=g).bfloat16()
 
     def setup(self, dev, rank, world):
-        from sgl_amd_mono_b200 import ops, synth
+        import synth
+        from sgl_amd_mono_b200 import ops
         from sgl_amd_mono_b200.layer import StepTables
         from sgl_amd_mono_b200.stack import DecoderStack
         from dataclasses import replace as dc_replace

@@ -15,8 +15,8 @@ from dataclasses import dataclass
 
 import torch
 
-from . import quant
-from .config import IDX_PAGE_BYTES, KV_DIM, KV_PAGE_BYTES, PAGE, LayerConfig
+from sgl_amd_mono_b200 import quant
+from sgl_amd_mono_b200.config import IDX_PAGE_BYTES, KV_DIM, KV_PAGE_BYTES, PAGE, LayerConfig
 
 
 def _gen(seed: int, device) -> torch.Generator:
@@ -217,7 +217,7 @@ def gqa_weights(cfg, rank: int = 0, device="cpu", layer: int = 0) -> dict:
 def gqa_step(cfg, rows: int, ctx: int, device="cpu", layer: int = 0, ragged: bool = True):
     """Caches of ``rows`` requests with up to ``ctx`` cached tokens each (random E4M3 bytes, no
     NaN codes), a shuffled page table, and one decode row per request at its last position."""
-    from .gqa import BLOCK, GqaTables
+    from sgl_amd_mono_b200.gqa import BLOCK, GqaTables
 
     g = _gen(1000 * layer + 11, device)
     blocks = -(-ctx // BLOCK)

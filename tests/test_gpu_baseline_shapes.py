@@ -24,7 +24,8 @@ from oracle import gqa as OG
 from oracle import layers as OL
 from oracle import quant as Q
 from oracle import stages as S
-from sgl_amd_mono_b200 import ops, synth
+import synth
+from sgl_amd_mono_b200 import ops
 from sgl_amd_mono_b200.config import CFG_FLASH, CFG_V3, LayerConfig
 from util import assert_close_hidden
 

@@ -10,7 +10,8 @@ from oracle import layers as OL
 from oracle import quant as Q
 from oracle import stages as S
 from sgl_amd_mono_b200 import _lib as L
-from sgl_amd_mono_b200 import ops, synth
+import synth
+from sgl_amd_mono_b200 import ops
 from sgl_amd_mono_b200.config import CFG_FFN_MXFP4, CFG_TINY, CFG_TINY_FFN
 from util import assert_close_hidden, assert_rel
 

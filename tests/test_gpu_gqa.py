@@ -7,7 +7,8 @@ import torch
 from oracle import gqa as OG
 from oracle import quant as Q
 from sgl_amd_mono_b200 import _lib as L
-from sgl_amd_mono_b200 import ops, synth
+import synth
+from sgl_amd_mono_b200 import ops
 from sgl_amd_mono_b200.gqa import BLOCK, CFG_GQA_TINY, TOPK_BLOCKS, GqaAttentionOp
 from util import assert_close_hidden
 

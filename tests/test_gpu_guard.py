@@ -216,7 +216,7 @@ def test_a_peer_flag_stops_this_rank():
 
 
 def _chained_ffn(deadline_s):
-    from sgl_amd_mono_b200 import synth
+    import synth
     from sgl_amd_mono_b200.config import CFG_TINY
     from sgl_amd_mono_b200.moe import MoeFfn
     from dataclasses import replace

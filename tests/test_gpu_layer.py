@@ -6,7 +6,8 @@ import pytest
 import torch
 
 from oracle import stages as S
-from sgl_amd_mono_b200 import ops, synth
+import synth
+from sgl_amd_mono_b200 import ops
 from sgl_amd_mono_b200.config import CFG_TINY
 from layer_checks import check_mla_layer
 

@@ -4,7 +4,7 @@ import pytest
 import torch
 
 from oracle import stages as S
-from sgl_amd_mono_b200 import synth
+import synth
 from util import assert_close_hidden
 
 pytestmark = pytest.mark.gpu

@@ -8,7 +8,8 @@ import torch
 
 from oracle import layers as OL
 from oracle import stages as S
-from sgl_amd_mono_b200 import ops, synth
+import synth
+from sgl_amd_mono_b200 import ops
 from sgl_amd_mono_b200.config import CFG_TINY
 
 pytestmark = pytest.mark.gpu

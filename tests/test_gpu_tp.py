@@ -74,7 +74,7 @@ def test_tp_layer_ranks_agree_and_match_oracle(world, rows, ctx):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     from oracle import layers as OL
-    from sgl_amd_mono_b200 import synth
+    import synth
     from sgl_amd_mono_b200.config import CFG_TINY
 
     here = Path(__file__).resolve().parent

@@ -83,7 +83,7 @@ def test_block_scores_are_causal_maxima():
 
 
 def test_attention_half_inserts_the_new_token_and_leaves_pad_rows_alone():
-    from sgl_amd_mono_b200 import synth
+    import synth
     from sgl_amd_mono_b200.gqa import CFG_GQA_TINY as cfg
 
     w = synth.gqa_weights(cfg, 0, "cpu")

@@ -7,7 +7,7 @@ from oracle import layers as OL
 from oracle import quant as Q
 from oracle import stages as S
 from sgl_amd_mono_b200 import quant as PQ
-from sgl_amd_mono_b200 import synth
+import synth
 from sgl_amd_mono_b200.config import CFG_FFN_MXFP4, CFG_TINY, CFG_TINY_FFN
 
 

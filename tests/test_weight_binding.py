@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from fake_sglang import layer_from_weights
-from sgl_amd_mono_b200 import synth
+import synth
 from sgl_amd_mono_b200.config import CFG_TINY
 from sgl_amd_mono_b200.glm53 import weights as W
 

@@ -20,7 +20,7 @@ import pytest
 import torch
 
 from sgl_amd_mono_b200 import _lib as L
-from sgl_amd_mono_b200 import synth
+import synth
 from util import assert_close_hidden
 
 pytestmark = pytest.mark.gpu

@@ -18,7 +18,8 @@ def main(rank, world, port, n_layers, rows, ctx, outdir):
     torch.cuda.set_device(rank)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        from sgl_amd_mono_b200 import ops, synth
+        import synth
+        from sgl_amd_mono_b200 import ops
         from sgl_amd_mono_b200.common.peer import GUARD_BYTES, make_peer_buffer
         from sgl_amd_mono_b200.config import CFG_TINY
         from sgl_amd_mono_b200.layer import StepTables
