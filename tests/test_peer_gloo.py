@@ -75,6 +75,16 @@ def _worker(rank, world, port, mode, out):
             ref = [torch.empty_like(got) for _ in range(world)]
             dist.all_gather(ref, got)
             assert all(torch.equal(ref[0], r) for r in ref), "ranks must agree bit for bit"
+            # the reduce-scatter + all-gather form: the owner of a column slice sums the partials it was sent in
+            # rank order, adds the residual, and everybody takes the finished slice from its owner
+            res = torch.randn(4, 1024, generator=torch.Generator().manual_seed(7)).bfloat16()
+            want = S.allreduce_rank_order([p.float() for p in parts], res)
+            sl = 1024 // world if 1024 % world == 0 else None
+            if sl is not None:
+                mine = S.allreduce_rank_order([p.float()[:, rank * sl : (rank + 1) * sl] for p in parts], res[:, rank * sl : (rank + 1) * sl])
+                slices = [torch.empty_like(mine) for _ in range(world)]
+                dist.all_gather(slices, mine.contiguous())  # stands in for the owners' pushes of finished words
+                assert torch.equal(torch.cat(slices, 1), want), "rs + ag must give the all-to-all form's bits"
             out.put((rank, "ok"))
         else:
             be = FakeBackend(rank, fail_alloc=(mode == "alloc" and rank == 1),
@@ -104,3 +114,18 @@ def test_peer_handshake(world, mode):
     got = dict(out.get(timeout=10) for _ in range(world))
     want = "ok" if mode == "ok" else "refused"
     assert got == {r: want for r in range(world)}
+
+
+def test_rs_ag_switch(monkeypatch):
+    """``ops.rsag_wanted``: off by default at every row count; ``MONO_AR_RSAG=1`` from 12 rows (the reference's switch
+    point, ``minimax_m3/gfx950/layout.py:33-34``) where the column slices divide evenly; ``always`` for every step."""
+    from sgl_amd_mono_b200 import ops
+
+    monkeypatch.delenv("MONO_AR_RSAG", raising=False)
+    assert not ops.rsag_wanted(16, 7168, 8)
+    monkeypatch.setenv("MONO_AR_RSAG", "1")
+    assert ops.rsag_wanted(12, 7168, 8) and ops.rsag_wanted(16, 6144, 4) and not ops.rsag_wanted(11, 7168, 8)
+    assert not ops.rsag_wanted(16, 7168, 1), "one rank has nothing to scatter"
+    assert not ops.rsag_wanted(16, 1000, 8), "1000 / 2 pairs do not split into 8 even slices of whole pairs"
+    monkeypatch.setenv("MONO_AR_RSAG", "always")
+    assert ops.rsag_wanted(1, 7168, 2)
