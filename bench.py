@@ -474,8 +474,13 @@ class GqaLayerWorkload(LayerWorkload):
     kernel = "gemv_tc4bs_kernel (tcgen05 kind::mxf8f6f4.block_scale MXFP4 expert up/gate, timed as its own launch)"
     traffic_key = "mxfp4_expert_up_gate"
 
-    def __init__(self, rows=16, ctx=65536):
+    def __init__(self, rows=16, ctx=65536, expert_fmt="mxfp4"):
+        """``expert_fmt`` "nvfp4": the same layer with NVFP4 experts (E4M3 scale per 16, 4-bit activations)."""
         super().__init__(rows, ctx)
+        self.expert_fmt = expert_fmt
+        if expert_fmt == "nvfp4":
+            self.kernel = "gemv_nvf4_kernel (tcgen05 kind::mxf4nvf4.block_scale NVFP4 expert up/gate, timed as its own launch)"
+            self.traffic_key = "nvfp4_expert_up_gate"
 
     def make_inputs(self, dev, rank, tp, world=1):
         import synth
@@ -483,9 +488,10 @@ class GqaLayerWorkload(LayerWorkload):
         from sgl_amd_mono_b200.gqa import CFG_GQA
 
         self.gcfg = g = CFG_GQA.with_tp(tp)
-        self.cfg = cfg = LayerConfig(name="cfg4_moe_mxfp4", hidden=g.hidden, n_experts=256, top_k=8, inter=1536, route_scale=1.0,
-                                     expert_fmt="mxfp4", shared_fmt="none", router_dtype="bf16", eps=g.eps, tp=tp)
-        self.name = f"cfg4_gqa_block_sparse_mxfp4_moe_layer_tp{tp}_{self.rows}rows_ctx{self.ctx}" + ("_one_shard" if tp != world else "")
+        fmt = self.expert_fmt
+        self.cfg = cfg = LayerConfig(name=f"cfg4_moe_{fmt}", hidden=g.hidden, n_experts=256, top_k=8, inter=1536, route_scale=1.0,
+                                     expert_fmt=fmt, shared_fmt="none", router_dtype="bf16", eps=g.eps, tp=tp)
+        self.name = f"cfg4_gqa_block_sparse_{fmt}_moe_layer_tp{tp}_{self.rows}rows_ctx{self.ctx}" + ("_one_shard" if tp != world else "")
         self.w = {**synth.layer_weights(cfg, rank, dev), **synth.gqa_weights(g, rank, dev)}
         self.tables = synth.gqa_step(g, self.rows, self.ctx, dev, ragged=False)
         gen = torch.Generator().manual_seed(0)
@@ -543,7 +549,7 @@ class GqaLayerWorkload(LayerWorkload):
         g, c, u = self.gcfg, self.cfg, self.distinct
         h, il = g.hidden, c.inter_local
         attn_w = g.qkv_rows * h + h * g.q_local * 128 + c.n_experts * h * 2
-        experts = u * (3 * il * h // 2 + 3 * il * h // 32)
+        experts = u * (3 * il * h // 2 + 3 * il * h // self.scale_group)
         kv = self.rows * 16 * 64 * g.kv_local * 128 * 2
         idx = self.rows * self.ctx * 128
         return attn_w + experts + kv + idx, u
@@ -551,7 +557,12 @@ class GqaLayerWorkload(LayerWorkload):
     def roofline_probe(self):
         u = self.distinct
         c = self.cfg
-        return u * (2 * c.inter_local * c.hidden // 2 + 2 * c.inter_local * c.hidden // 32), lambda: self.op.ffn.up.launch(self.rows)
+        return u * (2 * c.inter_local * c.hidden // 2 + 2 * c.inter_local * c.hidden // self.scale_group), lambda: self.op.ffn.up.launch(self.rows)
+
+    @property
+    def scale_group(self) -> int:
+        """Weight values per scale byte."""
+        return 16 if self.expert_fmt == "nvfp4" else 32
 
     def config(self):
         g, c = self.gcfg, self.cfg
@@ -559,7 +570,7 @@ class GqaLayerWorkload(LayerWorkload):
         return {"workload": self.name, "rows": self.rows, "context": self.ctx, "hidden": g.hidden, "q_heads": g.q_heads,
                 "kv_heads": g.kv_heads, "blocks_attended": 16, "block_tokens": 64, "experts": c.n_experts, "top_k": c.top_k,
                 "inter": c.inter, "tp": c.tp, "distinct_experts": u, "layer_algorithmic_bytes_per_rank": nbytes,
-                "cuda_graph": getattr(self, "graph", None) is not None, "weights": "fp8_e4m3 attention projections, mxfp4 experts",
+                "cuda_graph": getattr(self, "graph", None) is not None, "weights": f"fp8_e4m3 attention projections, {self.expert_fmt} experts",
                 "l2": "256 MiB buffer written between timed iterations"}
 
     def oracle_step(self):
@@ -957,6 +968,8 @@ def run_reference(args, wl_cls, rank: int) -> None:
     kw = dict(rows=args.rows) if args.rows else {}
     if args.heads and args.workload == "sparse_mla":
         kw["heads"] = args.heads
+    if args.workload == "gqa_layer" and args.expert_fmt != "mxfp4":
+        kw["expert_fmt"] = args.expert_fmt
     wl = wl_cls(**kw)
     if not hasattr(wl, "oracle_step"):
         print(json.dumps({"impl": "reference", "unavailable": f"the {args.workload} workload has no CPU counterpart"}))
@@ -996,6 +1009,7 @@ def main() -> None:
     ap.add_argument("--workload", default=os.environ.get("MONO_BENCH_WORKLOAD", DEFAULT_WORKLOAD), choices=sorted(WORKLOADS))
     ap.add_argument("--rows", type=int, default=0, help="rows of the step (default: 8; 16 for gqa_layer)")
     ap.add_argument("--heads", type=int, default=0, help="sparse_mla: local heads (default 16, config 2; 128 = config 3 at TP 1)")
+    ap.add_argument("--expert-fmt", default="mxfp4", choices=["mxfp4", "nvfp4"], help="gqa_layer: format of the routed experts")
     ap.add_argument("--load-seconds", type=float, default=0.6, help="time under load before the timed steps")
     ap.add_argument("--shard-of", type=int, default=0, help="run one rank's share of TP = N on each GPU without peers")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -1022,6 +1036,8 @@ def main() -> None:
     kw = dict(rows=args.rows) if args.rows else {}
     if args.heads and args.workload == "sparse_mla":
         kw["heads"] = args.heads
+    if args.workload == "gqa_layer" and args.expert_fmt != "mxfp4":
+        kw["expert_fmt"] = args.expert_fmt
     wl = wl_cls(**kw)
     wl.shard_of = args.shard_of
     def trace(what):  # MONO_BENCH_TRACE=1: progress on stderr, to see where a multi-rank run stops

@@ -99,8 +99,12 @@ int mono_tmap_encode_fp4(mono_tmap_t* out, const void* base, uint64_t inner_elem
  *                   each group of 8 stored as k0 k2 k4 k6 k1 k3 k5 k7 (the order the
  *                   MXFP4 weight nibbles unpack in on the warp-MMA consumer)
  *   MONO_ACT_MX8N   the same values in natural k order (the tcgen05 MXFP4 consumer)
+ *   MONO_ACT_NVF4   1 plane of packed E2M1 values (two per byte, even k in the low nibble, ld >= K/2
+ *                   bytes), one E4M3 scale byte per 16 values in scale_e8: scale =
+ *                   E4M3(max(amax, 6 * 2^-9) / 6), value = E2M1(v / scale), both round to nearest even
+ *                   (the NVFP4 consumer: both operands of the block-scaled FP4 MMA are 4-bit)
  * Rows >= `rows` of every plane stay zero. */
-enum { MONO_ACT_BF16 = 0, MONO_ACT_A8 = 1, MONO_ACT_HILO = 2, MONO_ACT_MX8 = 3, MONO_ACT_MX8N = 4 };
+enum { MONO_ACT_BF16 = 0, MONO_ACT_A8 = 1, MONO_ACT_HILO = 2, MONO_ACT_MX8 = 3, MONO_ACT_MX8N = 4, MONO_ACT_NVF4 = 5 };
 
 typedef struct mono_act_prep_args {
     int rows, k;
@@ -139,7 +143,11 @@ int mono_act_prep_launch(const mono_act_prep_args* a, void* stream);
  * MONO_JOB_EXPERT_DOWN, over a strided group of the step's experts); partial sums
  * go to f32 buffers that the next stage adds in a fixed order. */
 #define MONO_GEMV_MAX_JOBS 4
-enum { MONO_W_FP8 = 0, MONO_W_MXFP4 = 1, MONO_W_BF16 = 2 };
+/* MONO_W_NVFP4: packed E2M1 values with one E4M3 scale byte per 16 along K (wscale_e8, [mat][row][wscale_ld],
+ * wscale_ld a multiple of 16 = whole 256-value tiles, rows padded with 0x38 = 1.0) and one f32 scale per matrix
+ * (wglobal); activations MONO_ACT_NVF4.  tcgen05 only (kind::mxf4nvf4.block_scale, 16-value blocks); k_tiles
+ * counts 128-byte tiles = 256 values, as for MXFP4.  (M3.1-Flash's expert format: minimax_m31/spec.py:117-121.) */
+enum { MONO_W_FP8 = 0, MONO_W_MXFP4 = 1, MONO_W_BF16 = 2, MONO_W_NVFP4 = 3 };
 enum { MONO_JOB_DENSE = 0, MONO_JOB_EXPERT_UP = 1, MONO_JOB_EXPERT_DOWN = 2 };
 
 typedef struct mono_gemv_job {
@@ -208,6 +216,9 @@ typedef struct mono_gemv_job {
     uint8_t* stage_planes;
     float* stage_scale;
     int stage_ld, stage_scale_ld, stage_fmt, stage_plane_stride;
+    /* NVFP4: the f32 tensor scale of each matrix, [mat]; NULL = 1.  Applied to a task's f32 sum (before the
+     * route coefficient of a down job). */
+    const float* wglobal;
 } mono_gemv_job;
 
 typedef struct mono_gemv_args {

@@ -112,6 +112,8 @@ def attn_back(cfg, w, r, topk, kv_pages):
 def _expert(cfg, w, x, e: int):
     if cfg.expert_fmt == "fp8_block":
         return S.expert_fp8(x, w["w13"][e], w["w13_s"][e], w["w2"][e], w["w2_s"][e])
+    if cfg.expert_fmt == "nvfp4":
+        return S.expert_nvfp4(x, w["w13"][e], w["w13_s"][e], w["w13_g"][e], w["w2"][e], w["w2_s"][e], w["w2_g"][e])
     return S.expert_mxfp4(x, w["w13"][e], w["w13_s"][e], w["w2"][e], w["w2_s"][e])
 
 
@@ -122,6 +124,8 @@ def _shared(cfg, w, x):
         return S.expert_bf16(x, w["sh13"], w["sh2"])
     if cfg.shared_fmt == "fp8_block":
         return S.expert_fp8(x, w["sh13"], w["sh13_s"], w["sh2"], w["sh2_s"])
+    if cfg.shared_fmt == "nvfp4":
+        return S.expert_nvfp4(x, w["sh13"], w["sh13_s"], w["sh13_g"], w["sh2"], w["sh2_s"], w["sh2_g"])
     return S.expert_mxfp4(x, w["sh13"], w["sh13_s"], w["sh2"], w["sh2_s"])
 
 

@@ -147,6 +147,56 @@ def mxfp4_dequant(packed: torch.Tensor, code: torch.Tensor) -> torch.Tensor:
     return v * exp2_code(code.view(torch.uint8)).repeat_interleave(32, -1)
 
 
+# ---------------------------------------------------------------- NVFP4 (E2M1 values, one E4M3 scale per 16, one f32 scale per tensor)
+NVFP4_GROUP = 16
+
+
+def nvfp4_quant(w: torch.Tensor, global_scale: torch.Tensor | None = None):
+    """[.., K] f32 -> (packed uint8 [.., K/2], E4M3 scale bytes uint8 [.., K/16], f32 global scale [..leading dims of
+    a matrix] or scalar).
+
+    The published NVFP4 recipe (NVIDIA's block format for Blackwell: E2M1 elements, an unsigned E4M3 scale per 16
+    elements, a per-tensor f32 scale that brings the block scales into E4M3's range): global = amax(tensor) /
+    (6 * 448); block scale = E4M3(amax(block) / 6 / global), round to nearest even; element = E2M1(v / (scale *
+    global)), round to nearest even, saturating at +-6.  Packing as MXFP4: even index in the low nibble.  A matrix
+    is the last two dimensions; leading dimensions (experts) get a global scale each.
+    """
+    k = w.shape[-1]
+    wf = w.float()
+    if global_scale is None:
+        red = tuple(range(max(wf.dim() - 2, 0), wf.dim()))
+        global_scale = (wf.abs().amax(red) / (6.0 * 448.0)).clamp_min(2.0**-100)
+    g = global_scale.reshape(*global_scale.shape, *([1] * (wf.dim() - global_scale.dim())))
+    blk = wf.reshape(*wf.shape[:-1], k // NVFP4_GROUP, NVFP4_GROUP)
+    sb = e4m3_bytes(blk.abs().amax(-1) / 6.0 / g)                      # [.., K/16] bytes, all >= 0
+    sc = e4m3_from_bytes(sb) * g                                       # the scale a reader reconstructs
+    q = e2m1_encode((blk / sc.clamp_min(2.0**-120).unsqueeze(-1)).clamp(-6.0, 6.0)).reshape(*wf.shape[:-1], k)
+    q = torch.where((sc == 0).repeat_interleave(NVFP4_GROUP, -1), torch.zeros_like(q), q)
+    packed = q[..., 0::2] | (q[..., 1::2] << 4)
+    return packed.contiguous(), sb.contiguous(), global_scale.float().contiguous()
+
+
+def nvfp4_dequant(packed: torch.Tensor, scale_bytes: torch.Tensor, global_scale) -> torch.Tensor:
+    """element * E4M3 block scale * f32 global scale, all exact in f32."""
+    p = packed.view(torch.uint8)
+    v = torch.stack([e2m1_decode(p & 15), e2m1_decode(p >> 4)], -1).flatten(-2)
+    g = torch.as_tensor(global_scale, dtype=torch.float32)
+    g = g.reshape(*g.shape, *([1] * (v.dim() - g.dim())))
+    return v * e4m3_from_bytes(scale_bytes.view(torch.uint8)).repeat_interleave(NVFP4_GROUP, -1) * g
+
+
+def nvfp4_act_quant(x: torch.Tensor):
+    """Activation rows [.., K] -> (packed uint8 [.., K/2], E4M3 scale bytes [.., K/16]) with global scale 1:
+    block scale = E4M3(max(amax, 6 * 2^-9) / 6) rounded to nearest even (2^-9 is E4M3's smallest subnormal, so the
+    scale is never zero), element = E2M1(v / scale), round to nearest even, saturating."""
+    k = x.shape[-1]
+    blk = x.float().reshape(*x.shape[:-1], k // NVFP4_GROUP, NVFP4_GROUP)
+    sb = e4m3_bytes(blk.abs().amax(-1).clamp_min(6.0 * 2.0**-9) / 6.0)
+    sc = e4m3_from_bytes(sb)
+    q = e2m1_encode((blk / sc.unsqueeze(-1)).clamp(-6.0, 6.0)).reshape(*x.shape[:-1], k)
+    return (q[..., 0::2] | (q[..., 1::2] << 4)).contiguous(), sb.contiguous()
+
+
 # ---------------------------------------------------------------- block FP8 weights
 def fp8_block_dequant(w: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     """[N, K] E4M3 (uint8 or float8) with f32 [ceil(N/128), ceil(K/128)] scales -> f32.

@@ -302,6 +302,18 @@ def expert_mxfp4(x, w13, c13, w2, c2):
     return Q.mxfp8_dequant(q2, cc2) @ Q.mxfp4_dequant(w2, c2).T
 
 
+def expert_nvfp4(x, w13, s13, g13, w2, s2, g2):
+    """One NVFP4 expert on NVFP4 activations (W4A4: the only operand pairing Blackwell's block-scaled FP4 tensor-core
+    kind takes; both operands E2M1 with an E4M3 scale per 16, the weights' f32 tensor scale applied to the f32 sum),
+    bf16 mid, plain SwiGLU.  ``g13`` / ``g2``: this expert's f32 tensor scales."""
+    xq, xs = Q.nvfp4_act_quant(x)
+    h = Q.nvfp4_dequant(xq, xs, 1.0) @ Q.nvfp4_dequant(w13, s13, 1.0).T * float(g13)
+    inter = h.shape[-1] // 2
+    mid = Q.bf(swiglu(h[..., :inter], h[..., inter:]))
+    mq, ms = Q.nvfp4_act_quant(mid)
+    return Q.nvfp4_dequant(mq, ms, 1.0) @ Q.nvfp4_dequant(w2, s2, 1.0).T * float(g2)
+
+
 def expert_bf16(x, w13, w2):
     """bf16 shared expert: bf16 weights and activations, f32 accumulate, bf16 mid."""
     h = x.float() @ w13.float().T

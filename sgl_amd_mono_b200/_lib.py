@@ -17,8 +17,8 @@ LIB_PATH = Path(__file__).resolve().parent / "libmono_b200.so"
 MAX_ROWS = 16
 GUARD_WORDS = 16
 ERR_DEADLINE, ERR_PEER, ERR_ARG, GUARD_FLAGS = 3, 4, 5, 8
-ACT_BF16, ACT_A8, ACT_HILO, ACT_MX8, ACT_MX8N = 0, 1, 2, 3, 4
-W_FP8, W_MXFP4, W_BF16 = 0, 1, 2
+ACT_BF16, ACT_A8, ACT_HILO, ACT_MX8, ACT_MX8N, ACT_NVF4 = 0, 1, 2, 3, 4, 5
+W_FP8, W_MXFP4, W_BF16, W_NVFP4 = 0, 1, 2, 3
 JOB_DENSE, JOB_EXPERT_UP, JOB_EXPERT_DOWN = 0, 1, 2
 GEMV_MAX_JOBS = 4
 
@@ -44,7 +44,8 @@ class GemvJob(C.Structure):
         ("tmap4", Tmap), ("act_natural", i32), ("k_tiles4", i32),
         ("stage_planes", vp), ("stage_scale", vp), ("stage_ld", i32), ("stage_scale_ld", i32),
         ("stage_fmt", i32), ("stage_plane_stride", i32),
-        ("_tail", C.c_ubyte * 24),
+        ("wglobal", vp),
+        ("_tail", C.c_ubyte * 16),
     ]
 
 

@@ -39,8 +39,8 @@ class LayerConfig:
     top_k: int = 0
     inter: int = 0  # global expert intermediate size
     route_scale: float = 1.0
-    expert_fmt: str = "fp8_block"  # "fp8_block" | "mxfp4"
-    shared_fmt: str = "fp8_block"  # "fp8_block" | "mxfp4" | "bf16" | "none"
+    expert_fmt: str = "fp8_block"  # "fp8_block" | "mxfp4" | "nvfp4"
+    shared_fmt: str = "fp8_block"  # "fp8_block" | "mxfp4" | "nvfp4" | "bf16" | "none"
     router_dtype: str = "bf16"  # "bf16" | "f32"
     eps: float = 1e-6
     tp: int = 1
@@ -80,6 +80,11 @@ CFG_TINY = LayerConfig(
     name="tiny_mla_dsa_moe", hidden=1024, n_heads=8, q_lora=512, nope=128, rope=64, v_head=128,
     index_heads=8, index_topk=256, n_experts=16, top_k=4, inter=512, route_scale=2.5,
     expert_fmt="fp8_block", shared_fmt="fp8_block", eps=1e-6,
+)
+# The same block with NVFP4 experts (the expert format of MiniMax-M3.1-Flash's checkpoint), shared expert included.
+CFG_TINY_FFN_NVFP4 = LayerConfig(
+    name="tiny_ffn_nvfp4", hidden=512, n_experts=8, top_k=2, inter=256, route_scale=1.0,
+    expert_fmt="nvfp4", shared_fmt="nvfp4", router_dtype="f32", eps=1e-6,
 )
 CFG_TINY_FFN = LayerConfig(
     name="tiny_ffn_mxfp4", hidden=512, n_experts=8, top_k=2, inter=256, route_scale=1.0,

@@ -58,6 +58,18 @@ __device__ __forceinline__ void quant_chunk128(const float* x /* smem, 128 value
             dst[fmt == MONO_ACT_MX8 ? mx_perm8(k8) : k8] = f32_to_e4m3(v[i] * inv);
         }
         if ((lane & 7) == 0) scale_e8[chunk * 4 + (lane >> 3)] = (uint8_t)code;
+    } else if (fmt == MONO_ACT_NVF4) {
+        // eight blocks of 16: lanes 4q .. 4q+3 own block q; the scale is an E4M3 byte, never zero
+        float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+        for (int o = 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        const uint8_t sb = f32_to_e4m3(__fdiv_rn(fmaxf(amax, 0.01171875f /* 6 * 2^-9 */), 6.0f));
+        const float sc = e4m3_to_f32(sb);
+        uint32_t w = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) w |= f32_to_e2m1(__fdiv_rn(v[i], sc)) << (4 * i);
+        reinterpret_cast<uint16_t*>(plane0 + chunk * 64)[lane] = (uint16_t)w;
+        if ((lane & 3) == 0) scale_e8[chunk * 8 + (lane >> 2)] = sb;
     } else {  // MONO_ACT_BF16
         __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
         uint2 w = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));

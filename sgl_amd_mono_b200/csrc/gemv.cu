@@ -438,6 +438,7 @@ int mono_gemv_tc_enabled();                                                     
 int mono_gemv_tc_launch(const mono_gemv_args* a, long tasks, cudaStream_t st);  // gemv_tc.cu
 int mono_gemv_tc4_launch(const mono_gemv_args* a, long tasks, cudaStream_t st); // gemv_tc4.cu
 int mono_gemv_tc4bs_launch(const mono_gemv_args* a, long tasks, cudaStream_t st); // gemv_tc4bs.cu
+int mono_gemv_nvf4_launch(const mono_gemv_args* a, long tasks, cudaStream_t st);  // gemv_nvf4.cu
 
 namespace {
 template <int WK, int NT>
@@ -460,14 +461,14 @@ extern "C" int mono_gemv_launch(const mono_gemv_args* a, void* stream) {
         mono_set_error("mono_gemv_launch: njobs in 1..%d and rows in 1..%d required", MONO_GEMV_MAX_JOBS, MONO_MAX_ROWS);
         return MONO_E_ARG;
     }
-    if (a->wkind < MONO_W_FP8 || a->wkind > MONO_W_BF16) {
+    if (a->wkind < MONO_W_FP8 || a->wkind > MONO_W_NVFP4) {
         mono_set_error("mono_gemv_launch: unknown wkind %d", a->wkind);
         return MONO_E_ARG;
     }
     GemvParams p;
     p.a = *a;
     const int NT = a->rows > 8 ? 2 : 1, NPAD = NT * 8;
-    p.bb = a->wkind == MONO_W_MXFP4 ? 256 : 128;
+    p.bb = (a->wkind == MONO_W_MXFP4 || a->wkind == MONO_W_NVFP4) ? 256 : 128;
     int max_seg_tiles = 0, max_planes = 1;
     long tasks = 0;
     for (int j = 0; j < a->njobs; ++j) {
@@ -508,6 +509,10 @@ extern "C" int mono_gemv_launch(const mono_gemv_args* a, void* stream) {
             mono_set_error("mono_gemv_launch: job %d: MXFP4 jobs need E8M0 weight and activation scales", j);
             return MONO_E_ARG;
         }
+        if (a->wkind == MONO_W_NVFP4 && (!jb.wscale_e8 || !jb.ascale_e8)) {
+            mono_set_error("mono_gemv_launch: job %d: NVFP4 jobs need E4M3 weight and activation scale bytes", j);
+            return MONO_E_ARG;
+        }
         max_seg_tiles = seg_tiles > max_seg_tiles ? seg_tiles : max_seg_tiles;
         max_planes = jb.planes > max_planes ? jb.planes : max_planes;
         const int nrb = (jb.n_rows + 127) / 128;
@@ -538,6 +543,17 @@ extern "C" int mono_gemv_launch(const mono_gemv_args* a, void* stream) {
             mono_set_error("mono_gemv_launch: job %d: an output is staged by the FP8 tcgen05 path only (activation maps set)", j);
             return MONO_E_ARG;
         }
+    }
+    if (a->wkind == MONO_W_NVFP4) {
+        // one consumer only: the block-scaled FP4 tensor-core kind takes both operands in 4 bits
+        const int rc = mono_gemv_nvf4_launch(a, tasks, (cudaStream_t)stream);
+        if (rc == -100) {
+            mono_set_error("mono_gemv_launch: an NVFP4 job needs its weight and activation maps, one MONO_ACT_NVF4 plane, scale rows of "
+                           "whole 16-byte tiles at 16-byte aligned addresses, and segments of at most 2048 values");
+            return MONO_E_ARG;
+        }
+        if (rc > 0) mono_set_error("mono_gemv_launch: CUDA error %d (%s)", rc, cudaGetErrorString((cudaError_t)rc));
+        return rc;
     }
     if (a->wkind == MONO_W_MXFP4 && mono_gemv_tc_enabled()) {
         // the block-scaled kind (scales read by the MMA from tensor memory) unless MONO_TC4_BLOCK_SCALE=0 asks for

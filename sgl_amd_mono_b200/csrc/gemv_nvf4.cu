@@ -1,0 +1,463 @@
+// NVFP4 weight-streaming GEMV: E2M1 weights x E2M1 activations, one unsigned E4M3 scale per 16 values on both
+// operands, through tcgen05.mma.kind::mxf4nvf4.block_scale (16-value blocks); the weights' f32 tensor scale is
+// applied to a task's f32 sum in the epilogue.  The format of MiniMax-M3.1-Flash's experts, which the reference
+// leaves to SGLang's MoE runner (minimax_m31/spec.py:117-121); task list, outputs and job modes are those of the
+// MXFP4 kernel (gemv_tc4bs.cu; expert stages of glm53_flash/gfx950/kernel.py:4025-4392).
+//
+// Operands.  Both operands of this MMA kind are packed 4-bit values, K-major, 64 values (32 bytes) per MMA.  A
+// 128-byte-wide box of packed bytes is therefore an operand tile as TMA delivers it (128-byte swizzle): 128 weight
+// rows x 256 k, four MMAs.  Nothing is unpacked or spread: the staging ring holds nothing but HBM bytes
+// (9 slots x 16 KB of weights in flight per SM), and a slot is free again when the MMAs that read it are done.
+//
+// Scale factors.  An MMA reads 4 scale bytes per row (its four 16-value blocks) from 4 TMEM columns per operand:
+// row r's bytes are column r / 32 of lane r % 32.  tcgen05.cp (32 lanes x 128 bits, repeated for the four lane
+// quarters) brings them from a 512-byte block of shared memory laid out as bytes [(r % 32) * 16 + (r / 32) * 4 +
+// block].  A scale warp gathers the bytes from their row-major home in global memory into such blocks, one segment
+// ahead of the MMA threads: a block per MMA for the weights (128 rows); the activations have 16 rows (the first
+// 16 lanes of column 0), so their blocks overlap, 256 bytes apart.  Every scale byte the MMA can see is a valid
+// E4M3 number from the start (0x38 = 1.0).
+//
+// Issue rate.  Per 16 KB of weights: four MMAs and eight scale copies, about 90 cycles each for the issuing thread.
+// Two threads of two warps issue in turn, unit by unit, each into an accumulator of its own; the epilogue adds
+// the two.
+//
+// 256 threads: warp 0 TMA, one thread each of warps 1 and 7 issues tcgen05.cp + MMA, warps 2..5 own the 128 TMEM
+// lanes (epilogue), warp 6 stages scale bytes.  Every wait is bounded; TMEM is freed on every exit path.
+#include "mono_common.cuh"
+
+extern void mono_set_error(const char* fmt, ...);
+
+namespace mono {
+namespace nvf4 {
+
+constexpr int kThreads = 256;
+constexpr int kStages = 9;
+constexpr int kPackBytes = 128 * 128;   // a unit of weights: 128 rows x 128 bytes = 256 k values per row
+constexpr int kBBytes = 16 * 128;       // the unit's activations: 16 rows x 128 bytes
+constexpr int kStageBytes = kPackBytes + kBBytes;
+constexpr int kMaxSegUnits = 8;         // units (256 k values) per segment
+constexpr int kMmas = 4;                // MMAs per unit (64 k values each)
+constexpr int kScSlots = 2;
+constexpr int kSfBlock = 512;           // scale bytes of one MMA in the order tcgen05.cp wants
+constexpr int kSfaBytes = kMaxSegUnits * kMmas * kSfBlock;
+constexpr int kSfbStep = 256;           // activations: blocks half a block apart
+constexpr int kSfbBytes = kMaxSegUnits * kMmas * kSfbStep + kSfBlock / 2;
+constexpr int kSlotBytes = kSfaBytes + kSfbBytes + 128;  // + 16 route coefficients and the tensor scale
+constexpr int kAccCols = 16;            // one accumulator: 16 columns (the step's rows); [2 segments in turn][2 issuers]
+constexpr int kSfCol = 4 * kAccCols;    // per issuer 64 columns: [2 units in turn][4 MMAs][weights 4 | activations 4 ... ]
+constexpr int kTmemCols = 256;
+constexpr uint32_t kOne4 = 0x38383838u; // four E4M3 bytes of 1.0
+
+struct Params {
+    mono_gemv_args a;
+};
+
+struct Seg {
+    int c2, row0, t0, nt, aset;  // t0, nt in units of 256 k values
+    const uint8_t* asc;
+    const uint8_t* wsc;
+    const float* coef;
+    float g;
+};
+
+__device__ __forceinline__ int nrb_of(const mono_gemv_job& j) { return (j.n_rows + 127) >> 7; }
+
+__device__ __forceinline__ Seg make_seg(const mono_gemv_job& j, int rb, int ks, int u, const int* elist) {
+    Seg s;
+    int mat = 0;
+    if (j.mode == MONO_JOB_DENSE) {
+        s.t0 = ks * j.split_tiles;
+        s.nt = min(j.split_tiles, j.k_tiles - s.t0);
+        s.aset = 0;
+        s.coef = nullptr;
+    } else if (j.mode == MONO_JOB_EXPERT_UP) {
+        mat = (u < 128) ? elist[u] : j.expert_list[u];
+        s.t0 = ks * j.split_tiles;
+        s.nt = min(j.split_tiles, j.k_tiles - s.t0);
+        s.aset = 0;
+        s.coef = nullptr;
+    } else {
+        mat = (u < 128) ? elist[u] : j.expert_list[u];
+        s.t0 = 0;
+        s.nt = j.k_tiles;
+        s.aset = u;
+        s.coef = j.coef ? j.coef + (size_t)u * kMaxRows : nullptr;
+    }
+    s.c2 = mat;
+    s.row0 = j.row_off + rb * 128;
+    s.asc = j.ascale_e8 + (size_t)s.aset * j.ascale_seg_stride + (size_t)s.t0 * 16;
+    s.wsc = j.wscale_e8 + (size_t)mat * j.wscale_mat_stride + (size_t)s.row0 * j.wscale_ld + (size_t)s.t0 * 16;
+    s.g = j.wglobal ? __ldg(j.wglobal + mat) : 1.f;
+    return s;
+}
+
+// ---- tcgen05 wrappers (local to this file)
+__device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// 32 lanes x 128 bits of shared memory to 4 TMEM columns, the same 32 rows in each of the four lane quarters
+__device__ __forceinline__ void cp_sf(uint32_t tmem_col, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_col), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void mma_nvf4(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+}
+// 32 TMEM columns (both issuers' accumulators of a segment) of this thread's lane
+__device__ __forceinline__ void ld32(uint32_t taddr, uint32_t r[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
+          "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// K-major tile with 128-byte rows and the 128-byte swizzle: groups of 8 rows 1024 bytes apart
+__device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// A scale block: 32 rows of 16 bytes, no swizzle; groups of 8 rows 128 bytes apart (one 16-byte piece along K)
+__device__ __forceinline__ uint64_t desc_sf(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)(16 >> 4) << 16) | ((uint64_t)(128 >> 4) << 32) | (1ull << 46);
+}
+// Block-scaled descriptor: A and B E2M1 (format 1 of this kind), both K-major, N = 16, unsigned E4M3 scales
+// (scale-format bit 23 clear), M = 128; all four scale bytes of a column are used (scale ids 0)
+constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | (0u << 23) | ((128u >> 4) << 24);
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_constant__ Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* ring = smem;                                    // kStages slots: weights, then activations
+    uint8_t* sc_ring = ring + (size_t)kStages * kStageBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sc_ring + (size_t)kScSlots * kSlotBytes);
+    uint64_t* full = bars;                      // TMA -> MMA: a slot's boxes have landed
+    uint64_t* stage_free = full + kStages;      // MMA -> TMA: the MMAs that read the slot are done
+    uint64_t* sc_full = stage_free + kStages;   // scale warp -> MMA / epilogue: a segment's scale bytes are staged
+    uint64_t* sc_empty = sc_full + kScSlots;    // 2 issuers (their copies are done) + 4 epilogue warps (coefficients read)
+    uint64_t* acc_full = sc_empty + kScSlots;   // 2 issuers -> epilogue: a segment's accumulators are complete
+    uint64_t* acc_empty = acc_full + 2;         // 4 epilogue warps -> MMA
+    __shared__ int abort_flag;
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int s_elist[MONO_GEMV_MAX_JOBS][128];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int rows = p.a.rows;
+    if (tid == 0) {
+        abort_flag = guard_failed(p.a.guard) ? 1 : 0;
+        for (int i = 0; i < kStages; ++i) { mbar_init(&full[i], 1); mbar_init(&stage_free[i], 1); }
+        for (int i = 0; i < kScSlots; ++i) { mbar_init(&sc_full[i], 32); mbar_init(&sc_empty[i], 6); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 2); mbar_init(&acc_empty[i], 4); }
+        mbar_fence_init();
+    }
+    for (int i = tid; i < kScSlots * kSlotBytes / 4; i += kThreads) reinterpret_cast<uint32_t*>(sc_ring)[i] = kOne4;
+    fence_proxy_async_smem();
+    if (warp == 1) tmem_alloc(&tmem_base_s, kTmemCols);
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem_base = tmem_base_s;
+    pdl_launch_dependents();
+    pdl_wait();
+
+    int cnt[MONO_GEMV_MAX_JOBS], nexp[MONO_GEMV_MAX_JOBS], total = 0;
+#pragma unroll
+    for (int j = 0; j < MONO_GEMV_MAX_JOBS; ++j) {
+        cnt[j] = 0;
+        nexp[j] = 0;
+        if (j < p.a.njobs) {
+            const mono_gemv_job& jb = p.a.job[j];
+            const int nrb = nrb_of(jb);
+            if (jb.mode == MONO_JOB_DENSE) {
+                cnt[j] = nrb * jb.nsplit;
+            } else {
+                nexp[j] = min(*jb.n_expert, jb.max_expert);
+                cnt[j] = (jb.mode == MONO_JOB_EXPERT_UP) ? nexp[j] * nrb * jb.nsplit : nrb * jb.nsplit;
+            }
+        }
+        total += cnt[j];
+    }
+    for (int j = 0; j < p.a.njobs; ++j)
+        if (p.a.job[j].mode != MONO_JOB_DENSE)
+            for (int i = tid; i < min(nexp[j], 128); i += kThreads) s_elist[j][i] = p.a.job[j].expert_list[i];
+    __syncthreads();
+    volatile int* abortp = &abort_flag;
+    const uint64_t wait_ns = p.a.wait_ns ? p.a.wait_ns : kWaitLimitNs;
+
+// every role walks the same (task, segment) sequence
+#define NV_FOR_EACH_SEGMENT(...)                                                                                \
+    for (int task = blockIdx.x; task < total && !*abortp; task += gridDim.x) {                                  \
+        int j = 0, local = task;                                                                                \
+        while (local >= cnt[j]) { local -= cnt[j]; ++j; }                                                       \
+        const mono_gemv_job& jb = p.a.job[j];                                                                   \
+        const int nrb = nrb_of(jb);                                                                             \
+        int u = 0, nseg = 1;                                                                                    \
+        if (jb.mode == MONO_JOB_EXPERT_UP) { u = local / (nrb * jb.nsplit); local -= u * nrb * jb.nsplit; }     \
+        const int u_up = u, rb = local % nrb, ks = local / nrb;                                                 \
+        if (jb.mode == MONO_JOB_EXPERT_DOWN) nseg = (nexp[j] > ks) ? (nexp[j] - ks + jb.nsplit - 1) / jb.nsplit : 0; \
+        (void)u_up; (void)rb;                                                                                   \
+        TASK_BEGIN                                                                                              \
+        for (int sgi = 0; sgi < nseg && !*abortp; ++sgi) {                                                      \
+            if (jb.mode == MONO_JOB_EXPERT_DOWN) u = ks + sgi * jb.nsplit;                                      \
+            const Seg s = make_seg(jb, rb, ks, u, s_elist[j]);                                                  \
+            __VA_ARGS__                                                                                         \
+        }                                                                                                       \
+        TASK_END                                                                                                \
+    }
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer: weight boxes and activation tiles by TMA
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+#define TASK_BEGIN
+#define TASK_END
+            NV_FOR_EACH_SEGMENT({
+                const CUtensorMap* wmap = reinterpret_cast<const CUtensorMap*>(&jb.tmap);  // bytes: 128 per box row = 256 values
+                const CUtensorMap* amap = reinterpret_cast<const CUtensorMap*>(&jb.act_tmap);
+                for (int t = 0; t < s.nt; ++t) {
+                    if (!mbar_wait(&stage_free[stage], phase ^ 1, abortp, wait_ns)) break;
+                    uint8_t* st = ring + (size_t)stage * kStageBytes;
+                    // (a box that reaches past K reads zeros there and still counts its full size)
+                    mbar_expect_tx(&full[stage], kPackBytes + kBBytes);
+                    tma_load_3d(st, wmap, (s.t0 + t) * 128, s.row0, s.c2, &full[stage]);
+                    tma_load_3d(st + kPackBytes, amap, (s.t0 + t) * 128, 0, s.aset, &full[stage]);
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+            })
+#undef TASK_BEGIN
+#undef TASK_END
+        }
+    } else if (warp == 1 || warp == 7) {
+        // ------------------------------------------------------------ scale copies + MMA: issuer `me` takes the launch's
+        // units n = me, me + 2, ... and adds them into its own accumulator of the segment
+        if (lane == 0) {
+            const int me = warp == 1 ? 0 : 1;
+            int slot = 0, buf = 0, n = 0, stage = 0;
+            uint32_t phase = 0, sphase = 0, aphase = 0, mine = 0;
+#define TASK_BEGIN
+#define TASK_END
+            NV_FOR_EACH_SEGMENT({
+                if (!mbar_wait(&sc_full[slot], sphase, abortp, wait_ns)) break;
+                if (!mbar_wait(&acc_empty[buf], aphase ^ 1, abortp, wait_ns)) break;
+                fence_after();
+                const uint32_t sl = smem_u32(sc_ring + (size_t)slot * kSlotBytes);
+                const uint32_t acc = tmem_base + (buf * 2 + me) * kAccCols;
+                uint32_t accumulate = 0;
+                bool ok = true;
+                for (int t = 0; t < s.nt; ++t, ++n) {
+                    const int st_now = stage;
+                    const uint32_t ph_now = phase;
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                    if ((n & 1) != me) continue;
+                    if (!mbar_wait(&full[st_now], ph_now, abortp, wait_ns)) { ok = false; break; }
+                    fence_after();
+                    const uint32_t sa = smem_u32(ring + (size_t)st_now * kStageBytes);
+                    const uint64_t adesc = desc_sw128(sa), bdesc = desc_sw128(sa + kPackBytes);
+                    // (the tensor pipe runs a thread's copies and MMAs in the order it issued them; the column sets
+                    // alternate from unit to unit all the same)
+                    const uint32_t set = tmem_base + kSfCol + me * 64 + (mine & 1) * 32;
+                    ++mine;
+#pragma unroll
+                    for (int m = 0; m < kMmas; ++m) {  // 64 values per MMA, 32 bytes further along K
+                        const int blk = t * kMmas + m;
+                        const uint32_t sfa = set + m * 8, sfb = sfa + 4;
+                        cp_sf(sfa, desc_sf(sl + blk * kSfBlock));
+                        cp_sf(sfb, desc_sf(sl + kSfaBytes + blk * kSfbStep));
+                        mma_nvf4(acc, adesc + 2 * m, bdesc + 2 * m, kIdesc, sfa, sfb, accumulate);
+                        accumulate = 1;
+                    }
+                    commit(&stage_free[st_now]);
+                }
+                if (!ok) break;
+                commit(&acc_full[buf]);
+                commit(&sc_empty[slot]);
+                if (++slot == kScSlots) { slot = 0; sphase ^= 1; }
+                if (++buf == 2) { buf = 0; aphase ^= 1; }
+            })
+#undef TASK_BEGIN
+#undef TASK_END
+        }
+    } else if (warp < 6) {
+        // ------------------------------------------------------------ epilogue (TMEM lanes 32 * (warp % 4) ..)
+        const int q = warp & 3;
+        const int row_in_tile = q * 32 + lane;
+        const uint32_t tmem_lane = tmem_base + ((uint32_t)(q * 32) << 16);
+        int slot = 0, buf = 0, n = 0;
+        uint32_t sphase = 0, aphase = 0;
+        float total_acc[kMaxRows];
+#define TASK_BEGIN \
+        _Pragma("unroll") for (int c = 0; c < kMaxRows; ++c) total_acc[c] = 0.f;
+#define TASK_END                                                                                              \
+        if (!*abortp) {                                                                                       \
+            const int out_row = rb * 128 + row_in_tile;                                                       \
+            float* out = jb.out + (size_t)((jb.mode == MONO_JOB_EXPERT_UP ? u_up * jb.nsplit : 0) + ks) * jb.out_split_stride; \
+            if (out_row < jb.n_rows) {                                                                        \
+                _Pragma("unroll") for (int c = 0; c < kMaxRows; ++c)                                          \
+                    if (c < rows) out[(size_t)c * jb.out_ld + out_row] = total_acc[c];                        \
+            }                                                                                                 \
+        }
+        NV_FOR_EACH_SEGMENT({
+            if (!mbar_wait(&sc_full[slot], sphase, abortp, wait_ns)) break;
+            if (!mbar_wait(&acc_full[buf], aphase, abortp, wait_ns)) break;
+            fence_after();
+            uint32_t d[32];
+            ld32(tmem_lane + buf * 2 * kAccCols, d);
+            fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            // which issuers had a unit of this segment (an accumulator nobody wrote holds an older segment's sum)
+            const bool w0 = s.nt >= 2 || (n & 1) == 0, w1 = s.nt >= 2 || (n & 1) == 1;
+            n += s.nt;
+            const float* coef = reinterpret_cast<const float*>(sc_ring + (size_t)slot * kSlotBytes + kSfaBytes + kSfbBytes);
+            const float g = coef[kMaxRows];
+#pragma unroll
+            for (int c = 0; c < kMaxRows; ++c)
+                if (c < rows)
+                    total_acc[c] += ((w0 ? __uint_as_float(d[c]) : 0.f) + (w1 ? __uint_as_float(d[kAccCols + c]) : 0.f)) * g * coef[c];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sc_empty[slot]);
+            if (++slot == kScSlots) { slot = 0; sphase ^= 1; }
+            if (++buf == 2) { buf = 0; aphase ^= 1; }
+        })
+#undef TASK_BEGIN
+#undef TASK_END
+    } else if (warp == 6) {
+        // ------------------------------------------------------------ scale warp: a segment's scale bytes, one segment ahead
+        int slot = 0;
+        uint32_t sphase = 0;
+#define TASK_BEGIN
+#define TASK_END
+        NV_FOR_EACH_SEGMENT({
+            int ok = 1;
+            if (lane == 0) ok = mbar_wait(&sc_empty[slot], sphase ^ 1, abortp, wait_ns) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            uint8_t* sl = sc_ring + (size_t)slot * kSlotBytes;
+            // weights: lane l holds rows l, l + 32, l + 64, l + 96 of the block (rows past the matrix repeat the last
+            // one).  A row's 16 bytes of a unit are its four words of the unit's four MMAs; word m of the four rows
+            // is the lane's 16 bytes of MMA m's block.
+            const int last_row = jb.n_rows - 1 - rb * 128;
+            const uint8_t* wrow[4];
+#pragma unroll
+            for (int rr = 0; rr < 4; ++rr) wrow[rr] = s.wsc + (size_t)min(rr * 32 + lane, last_row) * jb.wscale_ld;
+#pragma unroll
+            for (int k0 = 0; k0 < kMaxSegUnits; k0 += 4) {
+                if (k0 >= s.nt) break;
+                // the loads of four units are issued before the first is stored
+                uint4 w[4][4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int t = min(k0 + k, s.nt - 1);
+#pragma unroll
+                    for (int rr = 0; rr < 4; ++rr) w[k][rr] = __ldg(reinterpret_cast<const uint4*>(wrow[rr] + t * 16));
+                }
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    if (k0 + k < s.nt) {
+                        uint8_t* blk = sl + (size_t)(k0 + k) * kMmas * kSfBlock + lane * 16;
+                        *reinterpret_cast<uint4*>(blk + 0 * kSfBlock) = make_uint4(w[k][0].x, w[k][1].x, w[k][2].x, w[k][3].x);
+                        *reinterpret_cast<uint4*>(blk + 1 * kSfBlock) = make_uint4(w[k][0].y, w[k][1].y, w[k][2].y, w[k][3].y);
+                        *reinterpret_cast<uint4*>(blk + 2 * kSfBlock) = make_uint4(w[k][0].z, w[k][1].z, w[k][2].z, w[k][3].z);
+                        *reinterpret_cast<uint4*>(blk + 3 * kSfBlock) = make_uint4(w[k][0].w, w[k][1].w, w[k][2].w, w[k][3].w);
+                    }
+            }
+            // activations: row c's four bytes of MMA m are the first four bytes of row c of the MMA's block (rows past
+            // the step: 1.0); lanes 0..15 take the even units, 16..31 the odd ones
+            {
+                const int c = lane & 15;
+                const uint8_t* arow = s.asc + (size_t)min(c, rows - 1) * jb.ascale_ld;
+                uint4 a4[kMaxSegUnits / 2];
+#pragma unroll
+                for (int k = 0; k < kMaxSegUnits / 2; ++k)
+                    a4[k] = __ldg(reinterpret_cast<const uint4*>(arow + min((lane >> 4) + 2 * k, s.nt - 1) * 16));
+#pragma unroll
+                for (int k = 0; k < kMaxSegUnits / 2; ++k) {
+                    const int t = (lane >> 4) + 2 * k;
+                    if (t < s.nt) {
+                        uint8_t* blk = sl + kSfaBytes + (size_t)t * kMmas * kSfbStep + c * 16;
+                        const bool live = c < rows;
+                        *reinterpret_cast<uint32_t*>(blk + 0 * kSfbStep) = live ? a4[k].x : kOne4;
+                        *reinterpret_cast<uint32_t*>(blk + 1 * kSfbStep) = live ? a4[k].y : kOne4;
+                        *reinterpret_cast<uint32_t*>(blk + 2 * kSfbStep) = live ? a4[k].z : kOne4;
+                        *reinterpret_cast<uint32_t*>(blk + 3 * kSfbStep) = live ? a4[k].w : kOne4;
+                    }
+                }
+            }
+            {
+                float* cf = reinterpret_cast<float*>(sl + kSfaBytes + kSfbBytes);
+                if (lane < kMaxRows) cf[lane] = (s.coef && lane < rows) ? __ldg(s.coef + lane) : 1.f;
+                if (lane == kMaxRows) cf[lane] = s.g;
+            }
+            fence_proxy_async_smem();  // the copies to TMEM read these bytes through the async proxy
+            mbar_arrive(&sc_full[slot]);
+            if (++slot == kScSlots) { slot = 0; sphase ^= 1; }
+        })
+#undef TASK_BEGIN
+#undef TASK_END
+    }
+#undef NV_FOR_EACH_SEGMENT
+    fence_before();
+    __syncthreads();
+    if (abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);  // let copies in flight land before the CTA's memory goes
+        if (tid == 0 && !guard_failed(p.a.guard)) guard_fail(p.a.guard, MONO_ERR_DEADLINE, 104);
+    }
+    if (warp == 1) {
+        fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+}  // namespace nvf4
+}  // namespace mono
+
+// Launches the NVFP4 kernel for an argument block that mono_gemv_launch has validated.  Returns -100 when the
+// block does not have what this kernel needs (there is no other consumer of the format).
+int mono_gemv_nvf4_launch(const mono_gemv_args* a, long tasks, cudaStream_t st) {
+    using namespace mono;
+    for (int j = 0; j < a->njobs; ++j) {
+        const mono_gemv_job& jb = a->job[j];
+        const unsigned long long* wa = reinterpret_cast<const unsigned long long*>(&jb.act_tmap);
+        const unsigned long long* wb = reinterpret_cast<const unsigned long long*>(&jb.tmap);
+        unsigned long long anya = 0, anyb = 0;
+        for (int i = 0; i < 16; ++i) { anya |= wa[i]; anyb |= wb[i]; }
+        const int seg = jb.mode == MONO_JOB_EXPERT_DOWN ? jb.k_tiles : (jb.split_tiles < jb.k_tiles ? jb.split_tiles : jb.k_tiles);
+        if (!anya || !anyb || jb.planes != 1 || jb.rb_per_mat != 0 || seg > nvf4::kMaxSegUnits || jb.feeds_job ||
+            (jb.wscale_ld & 15) || (jb.ascale_ld & 15) || (reinterpret_cast<uintptr_t>(jb.wscale_e8) & 15) ||
+            (reinterpret_cast<uintptr_t>(jb.ascale_e8) & 15) || (jb.wscale_mat_stride & 15) || (jb.ascale_seg_stride & 15) ||
+            (long)jb.wscale_ld < (long)jb.k_tiles * 16 || (long)jb.ascale_ld < (long)jb.k_tiles * 16)
+            return -100;
+    }
+    nvf4::Params p;
+    p.a = *a;
+    const size_t smem = 1024 + (size_t)nvf4::kStages * nvf4::kStageBytes + (size_t)nvf4::kScSlots * nvf4::kSlotBytes + 512;
+    static std::atomic<uint64_t> attr_once{0};  // bit d: set on device d
+    if (mono::attr_needed(attr_once)) {
+        cudaError_t e = cudaFuncSetAttribute(nvf4::gemv_nvf4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        mono::attr_done(attr_once);
+    }
+    int grid = a->max_ctas > 0 ? a->max_ctas : mono_sm_count();
+    if (grid > tasks) grid = (int)tasks;
+    if (grid < 1) grid = 1;
+    cudaError_t e = launch_k(nvf4::gemv_nvf4_kernel, grid, nvf4::kThreads, smem, st, p);
+    return (int)(e != cudaSuccess ? e : cudaGetLastError());
+}

@@ -657,7 +657,7 @@ extern "C" int mono_act_prep_launch(const mono_act_prep_args* a, void* stream) {
     }
     if (a->planes) {
         const bool need_f32 = a->fmt == MONO_ACT_A8 || a->fmt == MONO_ACT_HILO;
-        if ((need_f32 && !a->scale_f32) || ((a->fmt == MONO_ACT_MX8 || a->fmt == MONO_ACT_MX8N) && !a->scale_e8) || a->fmt < 0 || a->fmt > 4) {
+        if ((need_f32 && !a->scale_f32) || ((a->fmt == MONO_ACT_MX8 || a->fmt == MONO_ACT_MX8N || a->fmt == MONO_ACT_NVF4) && !a->scale_e8) || a->fmt < 0 || a->fmt > MONO_ACT_NVF4) {
             mono_set_error("mono_act_prep_launch: format %d needs its scale buffer", a->fmt);
             return MONO_E_ARG;
         }
@@ -757,7 +757,7 @@ extern "C" int mono_mid_launch(const mono_mid_args* a, void* stream) {
         mono_set_error("mono_mid_launch: rows 1..16 and inter a multiple of 128 required");
         return MONO_E_ARG;
     }
-    if ((a->fmt == MONO_ACT_A8 && !a->scale_f32) || ((a->fmt == MONO_ACT_MX8 || a->fmt == MONO_ACT_MX8N) && !a->scale_e8) || a->fmt == MONO_ACT_HILO) {
+    if ((a->fmt == MONO_ACT_A8 && !a->scale_f32) || ((a->fmt == MONO_ACT_MX8 || a->fmt == MONO_ACT_MX8N || a->fmt == MONO_ACT_NVF4) && !a->scale_e8) || a->fmt == MONO_ACT_HILO) {
         mono_set_error("mono_mid_launch: format %d not supported or missing scales", a->fmt);
         return MONO_E_ARG;
     }
@@ -769,7 +769,7 @@ extern "C" int mono_mid_launch(const mono_mid_args* a, void* stream) {
 
 static int mid_check(const mono_mid_args* a) {
     if (!a || a->rows < 1 || a->rows > MONO_MAX_ROWS || a->inter < 128 || (a->inter & 127) || !a->up || !a->planes || a->max_slot < 1) return 1;
-    if ((a->fmt == MONO_ACT_A8 && !a->scale_f32) || ((a->fmt == MONO_ACT_MX8 || a->fmt == MONO_ACT_MX8N) && !a->scale_e8) || a->fmt == MONO_ACT_HILO) return 1;
+    if ((a->fmt == MONO_ACT_A8 && !a->scale_f32) || ((a->fmt == MONO_ACT_MX8 || a->fmt == MONO_ACT_MX8N || a->fmt == MONO_ACT_NVF4) && !a->scale_e8) || a->fmt == MONO_ACT_HILO) return 1;
     return 0;
 }
 
@@ -829,7 +829,7 @@ extern "C" int mono_reduce_norm_launch(const mono_reduce_args* r, const mono_act
     }
     if (a->planes) {
         const bool need_f32 = a->fmt == MONO_ACT_A8 || a->fmt == MONO_ACT_HILO;
-        if ((need_f32 && !a->scale_f32) || ((a->fmt == MONO_ACT_MX8 || a->fmt == MONO_ACT_MX8N) && !a->scale_e8) || a->fmt < 0 || a->fmt > 4) {
+        if ((need_f32 && !a->scale_f32) || ((a->fmt == MONO_ACT_MX8 || a->fmt == MONO_ACT_MX8N || a->fmt == MONO_ACT_NVF4) && !a->scale_e8) || a->fmt < 0 || a->fmt > MONO_ACT_NVF4) {
             mono_set_error("mono_reduce_norm_launch: format %d needs its scale buffer", a->fmt);
             return MONO_E_ARG;
         }

@@ -18,8 +18,8 @@ from . import _lib as L
 from . import ops
 from .config import LayerConfig
 
-_WK = {"fp8_block": L.W_FP8, "mxfp4": L.W_MXFP4, "bf16": L.W_BF16}
-_ACT = {"fp8_block": L.ACT_A8, "mxfp4": L.ACT_MX8, "bf16": L.ACT_BF16}
+_WK = {"fp8_block": L.W_FP8, "mxfp4": L.W_MXFP4, "bf16": L.W_BF16, "nvfp4": L.W_NVFP4}
+_ACT = {"fp8_block": L.ACT_A8, "mxfp4": L.ACT_MX8, "bf16": L.ACT_BF16, "nvfp4": L.ACT_NVF4}
 
 
 def _ktiles(t: torch.Tensor) -> int:
@@ -75,7 +75,8 @@ class MoeFfn:
             self.ns_up_s = ns
             self.up_s = z(ns, L.MAX_ROWS, 2 * il)
             g = self.up if same else ops.Gemv(_WK[sfmt], self.guard, deadline_s)
-            g.add("sh13", w["sh13"], self.xs, self.up_s, wscale=w.get("sh13_s"), split_tiles=st, nsplit=ns)
+            g.add("sh13", w["sh13"], self.xs, self.up_s, wscale=w.get("sh13_s"), split_tiles=st, nsplit=ns,
+                  wglobal=w.get("sh13_g"))
             self.up_sh = None if same else g
         # the tcgen05 consumer takes K segments of up to 32 tiles (no activation slot to fit): fewer K splits
         probe = ops.plan_split(_ktiles(w["w13"]), -(-2 * il // 128) * self.max_expert, _WK[efmt],
@@ -85,7 +86,7 @@ class MoeFfn:
         self.up_r = z(self.max_expert * self.ns_up, L.MAX_ROWS, 2 * il)
         got = self.up.add("w13", w["w13"], self.xq, self.up_r, mode=L.JOB_EXPERT_UP, wscale=w["w13_s"],
                           expert_list=self.expert_list, n_expert=self.n_expert, max_expert=self.max_expert,
-                          split_tiles=probe[0], nsplit=probe[1])
+                          split_tiles=probe[0], nsplit=probe[1], wglobal=w.get("w13_g"))
         assert got == self.ns_up
         # ---- down launch: routed expert groups, then the shared expert's K splits
         nrb = -(-h // 128)
@@ -108,11 +109,11 @@ class MoeFfn:
         if self.has_shared:
             g = self.down if same else ops.Gemv(_WK[sfmt], self.guard, deadline_s)
             g.add("sh2", w["sh2"], self.mid_s, self.down_p, wscale=w.get("sh2_s"), out_slice=self.groups,
-                  split_tiles=self.st_dn_s, nsplit=ns_dn_s)
+                  split_tiles=self.st_dn_s, nsplit=ns_dn_s, wglobal=w.get("sh2_g"))
             self.down_sh = None if same else g
         self.down.add("w2", w["w2"], self.mid_r, self.down_p, mode=L.JOB_EXPERT_DOWN, wscale=w["w2_s"],
                       expert_list=self.expert_list, n_expert=self.n_expert, max_expert=self.max_expert,
-                      coef=self.coef, nsplit=self.groups)
+                      coef=self.coef, nsplit=self.groups, wglobal=w.get("w2_g"))
         self.out = z(L.MAX_ROWS, h, dt=torch.bfloat16)
         # Router logits and routing in one launch (the CTA that finishes its logit columns last routes the step;
         # MONO_ROUTER_FUSED=0: two launches).  Measured on config 3 once the logit weights' loads no longer cost a

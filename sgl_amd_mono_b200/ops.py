@@ -60,7 +60,7 @@ class ActBuf:
         self.fmt, self.k, self.segs = fmt, k, segs
         self.nplanes = 2 if fmt == L.ACT_HILO else 1
         kpad = _up(k, 256)  # room for the zero tail an MXFP4 tile may read
-        self.ld = 2 * kpad if fmt == L.ACT_BF16 else kpad
+        self.ld = 2 * kpad if fmt == L.ACT_BF16 else (kpad // 2 if fmt == L.ACT_NVF4 else kpad)
         self.planes = torch.zeros(segs, self.nplanes, L.MAX_ROWS, self.ld, dtype=torch.uint8, device=device)
         self.scale_f32 = self.scale_e8 = None
         self.scale_ld = 0
@@ -70,6 +70,10 @@ class ActBuf:
         elif fmt in (L.ACT_MX8, L.ACT_MX8N):
             self.scale_ld = _up(kpad // 32, 16) + 16
             self.scale_e8 = torch.full((segs, L.MAX_ROWS, self.scale_ld), 127, dtype=torch.uint8, device=device)
+        elif fmt == L.ACT_NVF4:
+            # an E4M3 byte per 16 values; bytes past K stay 1.0 (0x38)
+            self.scale_ld = _up(kpad // 16, 16) + 16
+            self.scale_e8 = torch.full((segs, L.MAX_ROWS, self.scale_ld), 0x38, dtype=torch.uint8, device=device)
 
     @property
     def plane_stride(self) -> int:
@@ -100,8 +104,8 @@ def act_prep(rows: int, k: int, dst: ActBuf | None, *, src_bf16=None, src_f32=No
     L.check(L.load().mono_act_prep_launch(C.byref(a), _stream()), "mono_act_prep_launch")
 
 
-_TILE_K = {L.W_FP8: 128, L.W_BF16: 64, L.W_MXFP4: 256}
-_MAX_SEG_TILES = {L.W_FP8: 16, L.W_BF16: 16, L.W_MXFP4: 8}
+_TILE_K = {L.W_FP8: 128, L.W_BF16: 64, L.W_MXFP4: 256, L.W_NVFP4: 256}
+_MAX_SEG_TILES = {L.W_FP8: 16, L.W_BF16: 16, L.W_MXFP4: 8, L.W_NVFP4: 8}
 
 
 def plan_split(k_tiles: int, row_blocks: int, wkind: int, sms: int | None = None, cap: int | None = None):
@@ -158,7 +162,7 @@ class Gemv:
             wscale: torch.Tensor | None = None, n_rows: int | None = None, row_off: int = 0,
             rb_per_mat: int = 0, n_mats: int = 0, nsplit: int | None = None, split_tiles: int | None = None,
             out_slice: int = 0, expert_list=None, n_expert=None, max_expert: int = 0, coef=None,
-            act_per_mat: bool = False, stage: ActBuf | None = None) -> int:
+            act_per_mat: bool = False, stage: ActBuf | None = None, wglobal: torch.Tensor | None = None) -> int:
         """Adds a job; returns the number of output slices (partial sums) it writes.  ``stage``: the
         activation buffer of the next GEMV (A8 or HILO); the job then also writes its output there,
         quantised, so that no staging launch is needed in between."""
@@ -207,6 +211,31 @@ class Gemv:
                 if self.copies is not None:
                     self.copies["MXFP4 scale rows padded to whole tiles", self.copy_tag, name] = padded
             job.wscale_e8, job.wscale_mat_stride, job.wscale_ld = ws.data_ptr(), ws3.shape[1] * ws3.shape[2], ws3.shape[2]
+        elif self.wkind == L.W_NVFP4:
+            ws = require(wscale, name + ".scale", torch.uint8)
+            ws3 = ws if ws.dim() == 3 else ws.unsqueeze(0)
+            if act.fmt != L.ACT_NVF4:
+                raise ValueError(f"{name}: NVFP4 weights take NVFP4 activations (both operands of the MMA are 4-bit)")
+            if ws3.shape[1] != rows_total or ws3.shape[2] * 8 < kb:
+                raise ValueError(f"{name}.scale: shape {tuple(ws.shape)} does not cover the weight (one byte per 16 values)")
+            if ws3.shape[2] % 16 or ws3.data_ptr() % 16:
+                # the kernel reads a row's 16 scale bytes of a 256-value tile at once: rows are padded once to whole
+                # tiles with the byte of 1.0 (the weight bytes past K read as zeros)
+                padded = torch.full((*ws3.shape[:2], _up(ws3.shape[2], 16)), 0x38, dtype=torch.uint8, device=ws.device)
+                padded[..., : ws3.shape[2]] = ws3
+                log.info("%s.scale: padded %s -> %s (one-time repack, %d bytes)", name, tuple(ws3.shape),
+                         tuple(padded.shape), padded.numel())
+                ws = ws3 = padded
+                self._keep.append(padded)
+                if self.copies is not None:
+                    self.copies["NVFP4 scale rows padded to whole tiles", self.copy_tag, name] = padded
+            job.wscale_e8, job.wscale_mat_stride, job.wscale_ld = ws.data_ptr(), ws3.shape[1] * ws3.shape[2], ws3.shape[2]
+            if wglobal is not None:
+                require(wglobal, name + ".global_scale", torch.float32)
+                if wglobal.numel() != mats:
+                    raise ValueError(f"{name}.global_scale: {wglobal.numel()} values for {mats} matrices")
+                job.wglobal = wglobal.data_ptr()
+            self._keep.append(wglobal)
         job.act, job.planes, job.act_plane_stride, job.act_ld = _p(act.planes), act.nplanes, act.plane_stride, act.ld
         L.check(L.load().mono_tmap_encode_box(C.byref(job.act_tmap), act.planes.data_ptr(), act.ld, L.MAX_ROWS,
                                               act.segs * act.nplanes, act.ld, act.plane_stride, 16),

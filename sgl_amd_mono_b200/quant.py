@@ -13,6 +13,8 @@ Rules follow the reference's device code:
     nibble (``test/kernels/deepseek_v41/check_ffn.py:107-115``).
   * block-FP8 weights: E4M3 bytes with f32 128 x 128 scales
     (``glm53/gfx950/kernel.py:35-42``).
+  * NVFP4 weights (the expert format of ``minimax_m31/spec.py:117-121``): E2M1 values, an E4M3 scale per 16
+    along K, an f32 scale per matrix.
 """
 
 from __future__ import annotations
@@ -47,6 +49,25 @@ def mxfp4_quant(w: torch.Tensor):
     q = e2m1_encode((g / sc).clamp(-6.0, 6.0)).reshape(*w.shape[:-1], k)
     packed = q[..., 0::2] | (q[..., 1::2] << 4)
     return packed.contiguous(), code.squeeze(-1).to(torch.uint8).contiguous()
+
+
+def nvfp4_quant(w: torch.Tensor):
+    """[E, N, K] float -> (packed uint8 [E, N, K/2], E4M3 scale bytes uint8 [E, N, K/16], f32 tensor scales [E]).
+
+    NVIDIA's published NVFP4 recipe: tensor scale = amax / (6 * 448) per matrix, block scale =
+    E4M3(amax(block of 16) / 6 / tensor scale), value = E2M1(v / (block scale * tensor scale)), round to nearest
+    even; even index in the low nibble.
+    """
+    k = w.shape[-1]
+    wf = w.float()
+    g = (wf.abs().amax((-2, -1)) / (6.0 * 448.0)).clamp_min(2.0**-100)
+    blk = wf.reshape(*wf.shape[:-1], k // 16, 16)
+    sb = (blk.abs().amax(-1) / 6.0 / g[:, None, None]).clamp(0.0, 448.0).to(F8)
+    sc = sb.float() * g[:, None, None]
+    q = e2m1_encode((blk / sc.clamp_min(2.0**-120).unsqueeze(-1)).clamp(-6.0, 6.0)).reshape(*wf.shape[:-1], k)
+    q = torch.where((sc == 0).repeat_interleave(16, -1), torch.zeros_like(q), q)
+    packed = q[..., 0::2] | (q[..., 1::2] << 4)
+    return packed.contiguous(), sb.view(torch.uint8).contiguous(), g.float().contiguous()
 
 
 def random_fp8_block(n: int, k: int, gen: torch.Generator, device, lead: tuple = ()):

@@ -3,7 +3,7 @@
 There are no checkpoints or datasets in the build environment, so parity tests and
 the benchmark run on random-init weights and caches with the reference's shapes and
 value recipes: block-FP8 values ``randn -> E4M3`` with scales ``(0.5 + U) * K^-0.5``
-(``test/kernels/glm53/check_layer.py:56-64,84-103``), MXFP4 experts drawn
+(``test/kernels/glm53/check_layer.py:56-64,84-103``), MXFP4 and NVFP4 experts drawn
 ``N(0, 0.02)``, a shuffled page table (``test/kernels/glm53_flash/check_layer.py:276-279``)
 and per-layer seeds ``1000 * layer + 7`` (weights) / ``+ 11`` (caches)
 (``test/kernels/glm53/check_layer.py:84,171``).
@@ -44,6 +44,19 @@ def _experts(cfg: LayerConfig, n: int, g, device, fmt: str, chunk: int = 8):
             w13[e0 : e0 + m], s13[e0 : e0 + m] = quant.random_fp8_block(2 * il, h, g, device, (m,))
             w2[e0 : e0 + m], s2[e0 : e0 + m] = quant.random_fp8_block(h, il, g, device, (m,))
         return w13, s13, w2, s2
+    if fmt == "nvfp4":
+        w13 = torch.empty(n, 2 * il, h // 2, dtype=torch.uint8, device=device)
+        w2 = torch.empty(n, h, il // 2, dtype=torch.uint8, device=device)
+        s13 = torch.empty(n, 2 * il, h // 16, dtype=torch.uint8, device=device)
+        s2 = torch.empty(n, h, il // 16, dtype=torch.uint8, device=device)
+        g13, g2 = torch.empty(n, device=device), torch.empty(n, device=device)
+        for e0 in range(0, n, chunk):
+            m = min(chunk, n - e0)
+            w13[e0 : e0 + m], s13[e0 : e0 + m], g13[e0 : e0 + m] = quant.nvfp4_quant(
+                torch.randn(m, 2 * il, h, generator=g, device=device) * 0.02)
+            w2[e0 : e0 + m], s2[e0 : e0 + m], g2[e0 : e0 + m] = quant.nvfp4_quant(
+                torch.randn(m, h, il, generator=g, device=device) * 0.02)
+        return w13, (s13, g13), w2, (s2, g2)
     assert fmt == "mxfp4"
     w13 = torch.empty(n, 2 * il, h // 2, dtype=torch.uint8, device=device)
     w2 = torch.empty(n, h, il // 2, dtype=torch.uint8, device=device)
@@ -89,10 +102,14 @@ def layer_weights(cfg: LayerConfig, rank: int = 0, device="cpu", layer: int = 0,
         w["router"] = r if cfg.router_dtype == "f32" else r.bfloat16()
         w["router_bias"] = 0.01 * torch.randn(cfg.n_experts, generator=g, device=device)
         w["w13"], w["w13_s"], w["w2"], w["w2_s"] = _experts(cfg, cfg.n_experts, gs, device, cfg.expert_fmt)
+        if cfg.expert_fmt == "nvfp4":  # scale bytes per 16 values and one f32 scale per expert
+            (w["w13_s"], w["w13_g"]), (w["w2_s"], w["w2_g"]) = w["w13_s"], w["w2_s"]
         if cfg.shared_fmt != "none":
             a, b, c, d = _experts(cfg, 1, gs, device, cfg.shared_fmt)
             w["sh13"], w["sh2"] = a[0], c[0]
-            if b is not None:
+            if cfg.shared_fmt == "nvfp4":
+                w["sh13_s"], w["sh13_g"], w["sh2_s"], w["sh2_g"] = b[0][0], b[1], d[0][0], d[1]
+            elif b is not None:
                 w["sh13_s"], w["sh2_s"] = b[0], d[0]
     if out_scale != 1.0:
         for k in ("o_proj_s", "w2_s", "sh2_s"):

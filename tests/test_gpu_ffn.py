@@ -12,7 +12,7 @@ from oracle import stages as S
 from sgl_amd_mono_b200 import _lib as L
 import synth
 from sgl_amd_mono_b200 import ops
-from sgl_amd_mono_b200.config import CFG_FFN_MXFP4, CFG_TINY, CFG_TINY_FFN
+from sgl_amd_mono_b200.config import CFG_FFN_MXFP4, CFG_TINY, CFG_TINY_FFN, CFG_TINY_FFN_NVFP4
 from util import assert_close_hidden, assert_rel
 
 pytestmark = pytest.mark.gpu
@@ -22,6 +22,11 @@ CFG_TINY_MOE8 = replace(CFG_TINY, name="tiny_moe_fp8", n_heads=0, index_heads=0)
 CFG_TINY_FFN_384 = replace(CFG_TINY_FFN, name="tiny_ffn_mxfp4_k384", inter=384, shared_fmt="none")
 # narrow experts: up/gate, activation and down run chained inside one launch by default
 CFG_TINY_MOE8_256 = replace(CFG_TINY_MOE8, name="tiny_moe_fp8_chained", inter=256)
+
+
+# NVFP4 experts: K that ends inside a 256-value tile and no shared expert; the 2048-wide block with 64 experts
+CFG_TINY_NVFP4_384 = replace(CFG_TINY_FFN_NVFP4, name="tiny_ffn_nvfp4_k384", inter=384, shared_fmt="none")
+CFG_FFN_NVFP4 = replace(CFG_FFN_MXFP4, name="ffn_nvfp4_2048", expert_fmt="nvfp4")
 
 
 def _cpu(w):
@@ -47,7 +52,9 @@ def _run(cfg, rows, seed=0, pad=()):
 @pytest.mark.parametrize("cfg,rows", [(CFG_TINY_FFN, 1), (CFG_TINY_FFN, 4), (CFG_TINY_FFN, 11),
                                       (CFG_TINY_MOE8, 1), (CFG_TINY_MOE8, 8), (CFG_TINY_MOE8, 16),
                                       (CFG_FFN_MXFP4, 4), (CFG_TINY_FFN_384, 5), (CFG_TINY_FFN_384, 16),
-                                      (CFG_TINY_MOE8_256, 8), (CFG_TINY_MOE8_256, 16)])
+                                      (CFG_TINY_MOE8_256, 8), (CFG_TINY_MOE8_256, 16),
+                                      (CFG_TINY_FFN_NVFP4, 1), (CFG_TINY_FFN_NVFP4, 7), (CFG_TINY_FFN_NVFP4, 16),
+                                      (CFG_TINY_NVFP4_384, 5), (CFG_FFN_NVFP4, 4)])
 def test_ffn_block_matches_oracle(cfg, rows):
     ffn, w, x, slots, out = _run(cfg, rows)
     wc = _cpu(w)
@@ -204,6 +211,48 @@ def test_replays_are_bit_equal():
     assert not torch.equal(ffn(x2, sd), out)
 
 
+def test_nvfp4_activation_bytes_are_bit_exact():
+    """Packed E2M1 values and E4M3 scale bytes of the NVFP4 activation format against the CPU restatement."""
+    rows, k = 5, 512
+    x = (torch.randn(rows, k, generator=torch.Generator().manual_seed(7)) * 2).bfloat16()
+    x[2, 128:256] = 0   # all-zero blocks: the smallest scale, zero values
+    x[3, 16:32] *= 4096  # a block whose scale saturates at 448: its values clamp at 6
+    buf = ops.ActBuf(L.ACT_NVF4, k, DEV)
+    ops.act_prep(rows, k, buf, src_bf16=x.to(DEV), round_bf16=False)
+    torch.cuda.synchronize()
+    q, sb = Q.nvfp4_act_quant(x)
+    assert torch.equal(buf.planes[0, 0, :rows, : k // 2].cpu(), q)
+    assert torch.equal(buf.scale_e8[0, :rows, : k // 16].cpu(), sb)
+    assert int(buf.planes[0, :, rows:].abs().sum()) == 0
+    assert int(sb[3, 1]) == 0x7E and int(sb[2, 8]) == 1
+
+
+@pytest.mark.parametrize("n,k,rows", [(128, 256, 16), (200, 640, 5), (384, 2048, 1)])
+def test_nvfp4_gemv_matches_dequantised_matmul(n, k, rows):
+    """One dense NVFP4 job (kind::mxf4nvf4.block_scale) against the f32 matmul of both operands' dequantised values:
+    every product and every scale is exact in f32, so only the summation inside the tensor core differs (5e-5 of the
+    largest sum; a misplaced scale byte or nibble would show as percents)."""
+    g = torch.Generator().manual_seed(n + k)
+    wf = torch.randn(1, n, k, generator=g) * 0.05
+    wf[0, :, 32:48] *= 40  # blocks with very different scales inside one MMA's 64 values
+    wq, ws, wg = Q.nvfp4_quant(wf)
+    x = (torch.randn(rows, k, generator=g) * torch.logspace(-2, 1, k // 16).repeat_interleave(16)).bfloat16()
+    buf = ops.ActBuf(L.ACT_NVF4, k, DEV)
+    ops.act_prep(rows, k, buf, src_bf16=x.to(DEV), round_bf16=False)
+    gemv = ops.Gemv(L.W_NVFP4)
+    st, ns = ops.plan_split(-(-k // 256), -(-n // 128), L.W_NVFP4)
+    out = torch.full((ns, 16, n), float("nan"), device=DEV)
+    assert gemv.add("w", wq.to(DEV), buf, out, wscale=ws.to(DEV), wglobal=wg.to(DEV), split_tiles=st, nsplit=ns) == ns
+    gemv.launch(rows)
+    torch.cuda.synchronize()
+    xq, xs = Q.nvfp4_act_quant(x)
+    ref = Q.nvfp4_dequant(xq, xs, 1.0) @ Q.nvfp4_dequant(wq[0], ws[0], 1.0).T * float(wg[0])
+    got = out[:, :rows].cpu()
+    assert torch.isfinite(got).all()
+    assert_rel(got.sum(0), ref, f"NVFP4 GEMV {n}x{k}, {rows} rows", 5e-5)
+    assert bool(torch.isnan(out[:, rows:]).all()), "rows past the step are not written"
+
+
 @pytest.mark.parametrize("fmt", [L.ACT_A8, L.ACT_HILO, L.ACT_MX8, L.ACT_MX8N, L.ACT_BF16])
 def test_activation_formats_are_bit_exact(fmt):
     rows, k = 5, 512
@@ -244,18 +293,25 @@ def _act_values(buf, seg, rows, k, fmt):
         inv = torch.tensor([0, 4, 1, 5, 2, 6, 3, 7] if fmt == L.ACT_MX8 else list(range(8)))
         v = Q.e4m3_from_bytes(pl[:, :k]).reshape(rows, k // 8, 8)[:, :, inv].reshape(rows, k)
         return Q.mxfp8_dequant(v, buf.scale_e8[seg, :rows, : k // 32].cpu())
+    if fmt == L.ACT_NVF4:
+        return Q.nvfp4_dequant(pl[:, : k // 2], buf.scale_e8[seg, :rows, : k // 16].cpu(), 1.0)
     return pl[:, : 2 * k].contiguous().view(torch.bfloat16).float()
 
 
-@pytest.mark.parametrize("cfg,rows", [(CFG_TINY_MOE8, 16), (CFG_TINY_MOE8, 3), (CFG_TINY_FFN, 11)])
+@pytest.mark.parametrize("cfg,rows", [(CFG_TINY_MOE8, 16), (CFG_TINY_MOE8, 3), (CFG_TINY_FFN, 11), (CFG_TINY_FFN_NVFP4, 9)])
 def test_gemv_stages_in_isolation(cfg, rows):
     """Each GEMV against the oracle's dequantised matmul fed the kernel's own quantised
     operands: the only difference left is the f32 summation order."""
     ffn, w, x, slots, out = _run(cfg, rows)
     wc = _cpu(w)
-    fp8 = cfg.expert_fmt == "fp8_block"
-    deq = Q.fp8_block_dequant if fp8 else Q.mxfp4_dequant
-    afmt = ffn.xq.fmt  # A8 for FP8 experts; MX8N (tcgen05 consumer) or MX8 (warp-MMA consumer) for MXFP4
+    fp8, nv4 = cfg.expert_fmt == "fp8_block", cfg.expert_fmt == "nvfp4"
+
+    def deq(name, e):
+        if nv4:
+            return Q.nvfp4_dequant(wc[name][e], wc[name + "_s"][e], wc[name + "_g"][e])
+        return (Q.fp8_block_dequant if fp8 else Q.mxfp4_dequant)(wc[name][e], wc[name + "_s"][e])
+
+    afmt = ffn.xq.fmt  # A8 for FP8 experts; MX8N (tcgen05 consumer) or MX8 (warp-MMA consumer) for MXFP4; NVF4
     assert ffn.mid_r.fmt == afmt
     h, il = cfg.hidden, cfg.inter_local
     n = int(ffn.n_expert.item())
@@ -265,21 +321,25 @@ def test_gemv_stages_in_isolation(cfg, rows):
     coef = ffn.coef[:n, :rows].cpu()
     down_ref = torch.zeros(rows, h)
     for u, e in enumerate(experts):
-        assert_rel(up[u, :rows], xq @ deq(wc["w13"][e], wc["w13_s"][e]).T, f"up/gate of expert {e}")
+        assert_rel(up[u, :rows], xq @ deq("w13", e).T, f"up/gate of expert {e}")
         mid_k = _act_values(ffn.mid_r, u, rows, il, afmt)
         mid_o = S.swiglu(up[u, :rows, :il], up[u, :rows, il:])
         if fp8:
             q, sc = Q.act_quant_128(mid_o)
             mid_ref = (q.reshape(rows, -1, 128) * sc[..., None]).reshape(rows, il)
+        elif nv4:
+            mq, ms = Q.nvfp4_act_quant(Q.bf(mid_o))
+            mid_ref = Q.nvfp4_dequant(mq, ms, 1.0)
+            step = 2.0 * Q.e4m3_from_bytes(ms).repeat_interleave(16, -1)  # the widest E2M1 step (4 -> 6) of each block
         else:
             q, c = Q.mxfp8_quant(Q.bf(mid_o))
             mid_ref = Q.mxfp8_dequant(q, c)
         # the same values up to a rounding step of the few elements that sit on a boundary
         # (a chunk whose amax moved by an ulp rescales all its values by an ulp: not a flip)
-        close = (mid_k - mid_ref).abs() <= 0.13 * mid_ref.abs() + 1e-6
+        close = (mid_k - mid_ref).abs() <= ((1.2 * step) if nv4 else (0.13 * mid_ref.abs() + 1e-6))
         flipped = (mid_k - mid_ref).abs() > 1e-4 * mid_ref.abs() + 1e-7
         assert bool(close.all()) and float(flipped.float().mean()) < 0.02
-        down_ref += coef[u, :, None] * (mid_k @ deq(wc["w2"][e], wc["w2_s"][e]).T)
+        down_ref += coef[u, :, None] * (mid_k @ deq("w2", e).T)
     routed = ffn.down_p[: ffn.groups, :rows].cpu().sum(0)
     assert_rel(routed, down_ref, "routed down projection")
 
