@@ -548,8 +548,9 @@ extern "C" int mono_gemv_launch(const mono_gemv_args* a, void* stream) {
         // one consumer only: the block-scaled FP4 tensor-core kind takes both operands in 4 bits
         const int rc = mono_gemv_nvf4_launch(a, tasks, (cudaStream_t)stream);
         if (rc == -100) {
-            mono_set_error("mono_gemv_launch: an NVFP4 job needs its weight and activation maps, one MONO_ACT_NVF4 plane, scale rows of "
-                           "whole 16-byte tiles at 16-byte aligned addresses, and segments of at most 2048 values");
+            mono_set_error("mono_gemv_launch: an NVFP4 job needs its weight and activation maps, one MONO_ACT_NVF4 plane, tiled weight "
+                           "scales (wscale_tiled, whole row blocks and tiles, 16-byte aligned), row_off a multiple of 128 and segments of "
+                           "at most 2048 values");
             return MONO_E_ARG;
         }
         if (rc > 0) mono_set_error("mono_gemv_launch: CUDA error %d (%s)", rc, cudaGetErrorString((cudaError_t)rc));

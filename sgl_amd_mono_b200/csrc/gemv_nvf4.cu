@@ -7,22 +7,28 @@
 // Operands.  Both operands of this MMA kind are packed 4-bit values, K-major, 64 values (32 bytes) per MMA.  A
 // 128-byte-wide box of packed bytes is therefore an operand tile as TMA delivers it (128-byte swizzle): 128 weight
 // rows x 256 k, four MMAs.  Nothing is unpacked or spread: the staging ring holds nothing but HBM bytes
-// (9 slots x 16 KB of weights in flight per SM), and a slot is free again when the MMAs that read it are done.
+// (9 slots x 18 KB of weights and their scales in flight per SM), and a slot is free again when the MMAs that read
+// it are done.
 //
 // Scale factors.  An MMA reads 4 scale bytes per row (its four 16-value blocks) from 4 TMEM columns per operand:
 // row r's bytes are column r / 32 of lane r % 32.  tcgen05.cp (32 lanes x 128 bits, repeated for the four lane
 // quarters) brings them from a 512-byte block of shared memory laid out as bytes [(r % 32) * 16 + (r / 32) * 4 +
-// block].  A scale warp gathers the bytes from their row-major home in global memory into such blocks, one segment
-// ahead of the MMA threads: a block per MMA for the weights (128 rows); the activations have 16 rows (the first
-// 16 lanes of column 0), so their blocks overlap, 256 bytes apart.  Every scale byte the MMA can see is a valid
+// block].  The weights' scale bytes are stored in that order (mono_gemv_job.wscale_tiled, a one-time repack when
+// the weight is bound): the 2 KB of a (row block, 256-k unit) arrive by one bulk copy beside the unit's weights.
+// (Gathered from row-major rows by warps of the kernel, a segment's bytes took 2.2 - 2.8 us under load, as long
+// as its MMAs, and the slots they needed left room for 7 ring stages only: 3.9 TB/s.)  The activations' bytes
+// (16 rows: the first 16 lanes of column 0, so their blocks overlap, 256 bytes apart) are gathered by a scale warp
+// into one of three slots, two segments ahead of the MMA threads.  Every scale byte the MMA can see is a valid
 // E4M3 number from the start (0x38 = 1.0).
 //
-// Issue rate.  Per 16 KB of weights: four MMAs and eight scale copies, about 90 cycles each for the issuing thread.
+// Issue rate.  Per 16 KB of weights: four MMAs and eight scale copies, about 70 cycles each for the issuing thread.
 // Two threads of two warps issue in turn, unit by unit, each into an accumulator of its own; the epilogue adds
-// the two.
+// the two.  The issuing threads do not walk the task list (a single thread needs about 1 us for the divisions and
+// address arithmetic of a segment): the scale warp leaves each segment's unit count in its slot.
 //
 // 256 threads: warp 0 TMA, one thread each of warps 1 and 7 issues tcgen05.cp + MMA, warps 2..5 own the 128 TMEM
-// lanes (epilogue), warp 6 stages scale bytes.  Every wait is bounded; TMEM is freed on every exit path.
+// lanes (epilogue), warp 6 stages the activations' scale bytes.  Every wait is bounded; TMEM is freed on every
+// exit path.
 #include "mono_common.cuh"
 
 extern void mono_set_error(const char* fmt, ...);
@@ -34,15 +40,15 @@ constexpr int kThreads = 256;
 constexpr int kStages = 9;
 constexpr int kPackBytes = 128 * 128;   // a unit of weights: 128 rows x 128 bytes = 256 k values per row
 constexpr int kBBytes = 16 * 128;       // the unit's activations: 16 rows x 128 bytes
-constexpr int kStageBytes = kPackBytes + kBBytes;
-constexpr int kMaxSegUnits = 8;         // units (256 k values) per segment
 constexpr int kMmas = 4;                // MMAs per unit (64 k values each)
-constexpr int kScSlots = 2;
 constexpr int kSfBlock = 512;           // scale bytes of one MMA in the order tcgen05.cp wants
-constexpr int kSfaBytes = kMaxSegUnits * kMmas * kSfBlock;
+constexpr int kSfaUnit = kMmas * kSfBlock;  // the unit's weight scales
+constexpr int kStageBytes = kPackBytes + kBBytes + kSfaUnit;
+constexpr int kMaxSegUnits = 8;         // units (256 k values) per segment
+constexpr int kScSlots = 3;             // activation scales of a segment: staged two segments ahead
 constexpr int kSfbStep = 256;           // activations: blocks half a block apart
 constexpr int kSfbBytes = kMaxSegUnits * kMmas * kSfbStep + kSfBlock / 2;
-constexpr int kSlotBytes = kSfaBytes + kSfbBytes + 128;  // + 16 route coefficients and the tensor scale
+constexpr int kSlotBytes = kSfbBytes + 128;  // + 16 route coefficients, the tensor scale and the unit count
 constexpr int kAccCols = 16;            // one accumulator: 16 columns (the step's rows); [2 segments in turn][2 issuers]
 constexpr int kSfCol = 4 * kAccCols;    // per issuer 64 columns: [2 units in turn][4 MMAs][weights 4 | activations 4 ... ]
 constexpr int kTmemCols = 256;
@@ -51,6 +57,14 @@ constexpr uint32_t kOne4 = 0x38383838u; // four E4M3 bytes of 1.0
 struct Params {
     mono_gemv_args a;
 };
+
+MONO_TL_DECLARE(tl_nv)
+#ifdef MONO_TIMELINE
+// stamps of CTA 0's roles, units 32.. of the launch (steady state): row 140 + k, one column per unit
+#define NV_TL(k, n) do { if (blockIdx.x == 0 && (n) >= 32 && (n) < 32 + MONO_TL_POINTS) tl_nv[140 + (k)][(n) - 32] = globaltimer_ns(); } while (0)
+#else
+#define NV_TL(k, n) do { } while (0)
+#endif
 
 struct Seg {
     int c2, row0, t0, nt, aset;  // t0, nt in units of 256 k values
@@ -86,7 +100,7 @@ __device__ __forceinline__ Seg make_seg(const mono_gemv_job& j, int rb, int ks, 
     s.c2 = mat;
     s.row0 = j.row_off + rb * 128;
     s.asc = j.ascale_e8 + (size_t)s.aset * j.ascale_seg_stride + (size_t)s.t0 * 16;
-    s.wsc = j.wscale_e8 + (size_t)mat * j.wscale_mat_stride + (size_t)s.row0 * j.wscale_ld + (size_t)s.t0 * 16;
+    s.wsc = j.wscale_e8 + (size_t)mat * j.wscale_mat_stride + (size_t)(s.row0 >> 7) * j.wscale_ld + (size_t)s.t0 * kSfaUnit;
     s.g = j.wglobal ? __ldg(j.wglobal + mat) : 1.f;
     return s;
 }
@@ -160,6 +174,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_con
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int rows = p.a.rows;
+    if (blockIdx.x < 140) MONO_TL(tl_nv, 0);
     if (tid == 0) {
         abort_flag = guard_failed(p.a.guard) ? 1 : 0;
         for (int i = 0; i < kStages; ++i) { mbar_init(&full[i], 1); mbar_init(&stage_free[i], 1); }
@@ -175,7 +190,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_con
     fence_after();
     const uint32_t tmem_base = tmem_base_s;
     pdl_launch_dependents();
+    if (blockIdx.x < 140) MONO_TL(tl_nv, 1);
     pdl_wait();
+    if (blockIdx.x < 140) MONO_TL(tl_nv, 2);
 
     int cnt[MONO_GEMV_MAX_JOBS], nexp[MONO_GEMV_MAX_JOBS], total = 0;
 #pragma unroll
@@ -225,7 +242,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_con
     if (warp == 0) {
         // ------------------------------------------------------------ producer: weight boxes and activation tiles by TMA
         if (lane == 0) {
-            int stage = 0;
+            int stage = 0, tl_n = 0;
+            (void)tl_n;
             uint32_t phase = 0;
 #define TASK_BEGIN
 #define TASK_END
@@ -233,12 +251,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_con
                 const CUtensorMap* wmap = reinterpret_cast<const CUtensorMap*>(&jb.tmap);  // bytes: 128 per box row = 256 values
                 const CUtensorMap* amap = reinterpret_cast<const CUtensorMap*>(&jb.act_tmap);
                 for (int t = 0; t < s.nt; ++t) {
+                    NV_TL(0, tl_n);
                     if (!mbar_wait(&stage_free[stage], phase ^ 1, abortp, wait_ns)) break;
+                    NV_TL(1, tl_n);
                     uint8_t* st = ring + (size_t)stage * kStageBytes;
                     // (a box that reaches past K reads zeros there and still counts its full size)
-                    mbar_expect_tx(&full[stage], kPackBytes + kBBytes);
+                    mbar_expect_tx(&full[stage], kStageBytes);
                     tma_load_3d(st, wmap, (s.t0 + t) * 128, s.row0, s.c2, &full[stage]);
                     tma_load_3d(st + kPackBytes, amap, (s.t0 + t) * 128, 0, s.aset, &full[stage]);
+                    bulk_load(st + kPackBytes + kBBytes, s.wsc + (size_t)t * kSfaUnit, kSfaUnit, &full[stage]);
+                    NV_TL(2, tl_n);
+                    ++tl_n;
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
             })
@@ -248,26 +271,32 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_con
     } else if (warp == 1 || warp == 7) {
         // ------------------------------------------------------------ scale copies + MMA: issuer `me` takes the launch's
         // units n = me, me + 2, ... and adds them into its own accumulator of the segment
+        // The issuing threads do not walk the task list (a single thread needs about 1 us for the divisions and
+        // address arithmetic of a segment, time in which no MMA is issued): the scale warps leave each segment's
+        // unit count in its slot, and a count of zero ends the launch.
         if (lane == 0) {
             const int me = warp == 1 ? 0 : 1;
-            int slot = 0, buf = 0, n = 0, stage = 0;
-            uint32_t phase = 0, sphase = 0, aphase = 0, mine = 0;
-#define TASK_BEGIN
-#define TASK_END
-            NV_FOR_EACH_SEGMENT({
+            int slot = 0, buf = 0, n0 = 0;
+            uint32_t sphase = 0, aphase = 0, mine = 0;
+            for (;;) {
                 if (!mbar_wait(&sc_full[slot], sphase, abortp, wait_ns)) break;
+                const int nt = reinterpret_cast<const volatile int*>(sc_ring + (size_t)slot * kSlotBytes + kSfbBytes)[kMaxRows + 1];
+                if (nt <= 0) break;
+                if (me == 0) NV_TL(13, n0);
                 if (!mbar_wait(&acc_empty[buf], aphase ^ 1, abortp, wait_ns)) break;
+                if (me == 0) NV_TL(7, n0);
+                if (me == 0 && n0 == 0 && blockIdx.x < 140) MONO_TL_AT(tl_nv, 5);
                 fence_after();
                 const uint32_t sl = smem_u32(sc_ring + (size_t)slot * kSlotBytes);
                 const uint32_t acc = tmem_base + (buf * 2 + me) * kAccCols;
                 uint32_t accumulate = 0;
                 bool ok = true;
-                for (int t = 0; t < s.nt; ++t, ++n) {
-                    const int st_now = stage;
-                    const uint32_t ph_now = phase;
-                    if (++stage == kStages) { stage = 0; phase ^= 1; }
-                    if ((n & 1) != me) continue;
+                for (int t = (n0 + me) & 1; t < nt; t += 2) {  // this issuer's units: launch-wide numbers of its parity
+                    const int n = n0 + t, st_now = n % kStages;
+                    const uint32_t ph_now = (uint32_t)(n / kStages) & 1u;
+                    NV_TL(3, n);
                     if (!mbar_wait(&full[st_now], ph_now, abortp, wait_ns)) { ok = false; break; }
+                    NV_TL(4, n);
                     fence_after();
                     const uint32_t sa = smem_u32(ring + (size_t)st_now * kStageBytes);
                     const uint64_t adesc = desc_sw128(sa), bdesc = desc_sw128(sa + kPackBytes);
@@ -279,21 +308,23 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_con
                     for (int m = 0; m < kMmas; ++m) {  // 64 values per MMA, 32 bytes further along K
                         const int blk = t * kMmas + m;
                         const uint32_t sfa = set + m * 8, sfb = sfa + 4;
-                        cp_sf(sfa, desc_sf(sl + blk * kSfBlock));
-                        cp_sf(sfb, desc_sf(sl + kSfaBytes + blk * kSfbStep));
+                        cp_sf(sfa, desc_sf(sa + kPackBytes + kBBytes + m * kSfBlock));
+                        cp_sf(sfb, desc_sf(sl + blk * kSfbStep));
                         mma_nvf4(acc, adesc + 2 * m, bdesc + 2 * m, kIdesc, sfa, sfb, accumulate);
                         accumulate = 1;
                     }
                     commit(&stage_free[st_now]);
+                    NV_TL(5, n);
                 }
                 if (!ok) break;
+                n0 += nt;
+                NV_TL(6, n0 - 1);
                 commit(&acc_full[buf]);
                 commit(&sc_empty[slot]);
+                if (me == 0) NV_TL(18, n0 - 1);
                 if (++slot == kScSlots) { slot = 0; sphase ^= 1; }
                 if (++buf == 2) { buf = 0; aphase ^= 1; }
-            })
-#undef TASK_BEGIN
-#undef TASK_END
+            }
         }
     } else if (warp < 6) {
         // ------------------------------------------------------------ epilogue (TMEM lanes 32 * (warp % 4) ..)
@@ -316,7 +347,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_con
         }
         NV_FOR_EACH_SEGMENT({
             if (!mbar_wait(&sc_full[slot], sphase, abortp, wait_ns)) break;
+            if (tid == 64) NV_TL(11, n);
             if (!mbar_wait(&acc_full[buf], aphase, abortp, wait_ns)) break;
+            if (tid == 64) NV_TL(12, n);
             fence_after();
             uint32_t d[32];
             ld32(tmem_lane + buf * 2 * kAccCols, d);
@@ -326,7 +359,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_con
             // which issuers had a unit of this segment (an accumulator nobody wrote holds an older segment's sum)
             const bool w0 = s.nt >= 2 || (n & 1) == 0, w1 = s.nt >= 2 || (n & 1) == 1;
             n += s.nt;
-            const float* coef = reinterpret_cast<const float*>(sc_ring + (size_t)slot * kSlotBytes + kSfaBytes + kSfbBytes);
+            if (tid == 64) NV_TL(15, n - s.nt);
+            const float* coef = reinterpret_cast<const float*>(sc_ring + (size_t)slot * kSlotBytes + kSfbBytes);
             const float g = coef[kMaxRows];
 #pragma unroll
             for (int c = 0; c < kMaxRows; ++c)
@@ -340,82 +374,73 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_con
 #undef TASK_BEGIN
 #undef TASK_END
     } else if (warp == 6) {
-        // ------------------------------------------------------------ scale warp: a segment's scale bytes, one segment ahead
-        int slot = 0;
+        // ------------------------------------------------------------ scale warp: a segment's activation scale bytes,
+        // route coefficients, tensor scale and unit count, two segments ahead
+        int slot = 0, tl_n = 0;
+        (void)tl_n;
         uint32_t sphase = 0;
 #define TASK_BEGIN
 #define TASK_END
         NV_FOR_EACH_SEGMENT({
             int ok = 1;
+            if (lane == 0) NV_TL(8, tl_n);
             if (lane == 0) ok = mbar_wait(&sc_empty[slot], sphase ^ 1, abortp, wait_ns) ? 1 : 0;
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
+            if (lane == 0) NV_TL(9, tl_n);
             uint8_t* sl = sc_ring + (size_t)slot * kSlotBytes;
-            // weights: lane l holds rows l, l + 32, l + 64, l + 96 of the block (rows past the matrix repeat the last
-            // one).  A row's 16 bytes of a unit are its four words of the unit's four MMAs; word m of the four rows
-            // is the lane's 16 bytes of MMA m's block.
-            const int last_row = jb.n_rows - 1 - rb * 128;
-            const uint8_t* wrow[4];
+            // row c's four bytes of MMA m are the first four bytes of row c of the MMA's block (rows past the step:
+            // 1.0); lanes 0..15 take the even units, 16..31 the odd ones; every load is issued before the first store
+            const int c = lane & 15;
+            const uint8_t* arow = s.asc + (size_t)min(c, rows - 1) * jb.ascale_ld;
+            uint4 a4[kMaxSegUnits / 2];
 #pragma unroll
-            for (int rr = 0; rr < 4; ++rr) wrow[rr] = s.wsc + (size_t)min(rr * 32 + lane, last_row) * jb.wscale_ld;
+            for (int k = 0; k < kMaxSegUnits / 2; ++k)
+                a4[k] = __ldg(reinterpret_cast<const uint4*>(arow + min((lane >> 4) + 2 * k, s.nt - 1) * 16));
+            float cf_v = 1.f;
+            if (s.coef && lane < rows) cf_v = __ldg(s.coef + lane);
 #pragma unroll
-            for (int k0 = 0; k0 < kMaxSegUnits; k0 += 4) {
-                if (k0 >= s.nt) break;
-                // the loads of four units are issued before the first is stored
-                uint4 w[4][4];
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const int t = min(k0 + k, s.nt - 1);
-#pragma unroll
-                    for (int rr = 0; rr < 4; ++rr) w[k][rr] = __ldg(reinterpret_cast<const uint4*>(wrow[rr] + t * 16));
-                }
-#pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    if (k0 + k < s.nt) {
-                        uint8_t* blk = sl + (size_t)(k0 + k) * kMmas * kSfBlock + lane * 16;
-                        *reinterpret_cast<uint4*>(blk + 0 * kSfBlock) = make_uint4(w[k][0].x, w[k][1].x, w[k][2].x, w[k][3].x);
-                        *reinterpret_cast<uint4*>(blk + 1 * kSfBlock) = make_uint4(w[k][0].y, w[k][1].y, w[k][2].y, w[k][3].y);
-                        *reinterpret_cast<uint4*>(blk + 2 * kSfBlock) = make_uint4(w[k][0].z, w[k][1].z, w[k][2].z, w[k][3].z);
-                        *reinterpret_cast<uint4*>(blk + 3 * kSfBlock) = make_uint4(w[k][0].w, w[k][1].w, w[k][2].w, w[k][3].w);
-                    }
-            }
-            // activations: row c's four bytes of MMA m are the first four bytes of row c of the MMA's block (rows past
-            // the step: 1.0); lanes 0..15 take the even units, 16..31 the odd ones
-            {
-                const int c = lane & 15;
-                const uint8_t* arow = s.asc + (size_t)min(c, rows - 1) * jb.ascale_ld;
-                uint4 a4[kMaxSegUnits / 2];
-#pragma unroll
-                for (int k = 0; k < kMaxSegUnits / 2; ++k)
-                    a4[k] = __ldg(reinterpret_cast<const uint4*>(arow + min((lane >> 4) + 2 * k, s.nt - 1) * 16));
-#pragma unroll
-                for (int k = 0; k < kMaxSegUnits / 2; ++k) {
-                    const int t = (lane >> 4) + 2 * k;
-                    if (t < s.nt) {
-                        uint8_t* blk = sl + kSfaBytes + (size_t)t * kMmas * kSfbStep + c * 16;
-                        const bool live = c < rows;
-                        *reinterpret_cast<uint32_t*>(blk + 0 * kSfbStep) = live ? a4[k].x : kOne4;
-                        *reinterpret_cast<uint32_t*>(blk + 1 * kSfbStep) = live ? a4[k].y : kOne4;
-                        *reinterpret_cast<uint32_t*>(blk + 2 * kSfbStep) = live ? a4[k].z : kOne4;
-                        *reinterpret_cast<uint32_t*>(blk + 3 * kSfbStep) = live ? a4[k].w : kOne4;
-                    }
+            for (int k = 0; k < kMaxSegUnits / 2; ++k) {
+                const int t = (lane >> 4) + 2 * k;
+                if (t < s.nt) {
+                    uint8_t* blk = sl + (size_t)t * kMmas * kSfbStep + c * 16;
+                    const bool live = c < rows;
+                    *reinterpret_cast<uint32_t*>(blk + 0 * kSfbStep) = live ? a4[k].x : kOne4;
+                    *reinterpret_cast<uint32_t*>(blk + 1 * kSfbStep) = live ? a4[k].y : kOne4;
+                    *reinterpret_cast<uint32_t*>(blk + 2 * kSfbStep) = live ? a4[k].z : kOne4;
+                    *reinterpret_cast<uint32_t*>(blk + 3 * kSfbStep) = live ? a4[k].w : kOne4;
                 }
             }
             {
-                float* cf = reinterpret_cast<float*>(sl + kSfaBytes + kSfbBytes);
-                if (lane < kMaxRows) cf[lane] = (s.coef && lane < rows) ? __ldg(s.coef + lane) : 1.f;
+                float* cf = reinterpret_cast<float*>(sl + kSfbBytes);
+                if (lane < kMaxRows) cf[lane] = cf_v;
                 if (lane == kMaxRows) cf[lane] = s.g;
+                if (lane == kMaxRows + 1) reinterpret_cast<int*>(cf)[lane] = s.nt;  // for the issuing threads
             }
             fence_proxy_async_smem();  // the copies to TMEM read these bytes through the async proxy
             mbar_arrive(&sc_full[slot]);
+            if (lane == 0) NV_TL(10, tl_n);
+            tl_n += s.nt;
             if (++slot == kScSlots) { slot = 0; sphase ^= 1; }
         })
 #undef TASK_BEGIN
 #undef TASK_END
+        // the end marker: a slot with a unit count of zero
+        if (!*abortp) {
+            int ok = 1;
+            if (lane == 0) ok = mbar_wait(&sc_empty[slot], sphase ^ 1, abortp, wait_ns) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (ok) {
+                if (lane == kMaxRows + 1) reinterpret_cast<int*>(sc_ring + (size_t)slot * kSlotBytes + kSfbBytes)[lane] = 0;
+                mbar_arrive(&sc_full[slot]);
+            }
+        }
     }
 #undef NV_FOR_EACH_SEGMENT
+    if (blockIdx.x < 140) MONO_TL(tl_nv, 3);  // the producer has issued its last unit
     fence_before();
     __syncthreads();
+    if (blockIdx.x < 140) MONO_TL(tl_nv, 4);
     if (abort_flag) {
         for (int i = 0; i < 64; ++i) __nanosleep(1000);  // let copies in flight land before the CTA's memory goes
         if (tid == 0 && !guard_failed(p.a.guard)) guard_fail(p.a.guard, MONO_ERR_DEADLINE, 104);
@@ -431,6 +456,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_con
 
 // Launches the NVFP4 kernel for an argument block that mono_gemv_launch has validated.  Returns -100 when the
 // block does not have what this kernel needs (there is no other consumer of the format).
+#ifdef MONO_TIMELINE
+extern "C" int mono_timeline_read_nvf4(unsigned long long* out, int* ctas, int* points) {
+    *ctas = MONO_TL_CTAS;
+    *points = MONO_TL_POINTS;
+    return (int)cudaMemcpyFromSymbol(out, mono::nvf4::tl_nv, sizeof(unsigned long long) * MONO_TL_CTAS * MONO_TL_POINTS);
+}
+#endif
+
 int mono_gemv_nvf4_launch(const mono_gemv_args* a, long tasks, cudaStream_t st) {
     using namespace mono;
     for (int j = 0; j < a->njobs; ++j) {
@@ -441,9 +474,11 @@ int mono_gemv_nvf4_launch(const mono_gemv_args* a, long tasks, cudaStream_t st) 
         for (int i = 0; i < 16; ++i) { anya |= wa[i]; anyb |= wb[i]; }
         const int seg = jb.mode == MONO_JOB_EXPERT_DOWN ? jb.k_tiles : (jb.split_tiles < jb.k_tiles ? jb.split_tiles : jb.k_tiles);
         if (!anya || !anyb || jb.planes != 1 || jb.rb_per_mat != 0 || seg > nvf4::kMaxSegUnits || jb.feeds_job ||
-            (jb.wscale_ld & 15) || (jb.ascale_ld & 15) || (reinterpret_cast<uintptr_t>(jb.wscale_e8) & 15) ||
-            (reinterpret_cast<uintptr_t>(jb.ascale_e8) & 15) || (jb.wscale_mat_stride & 15) || (jb.ascale_seg_stride & 15) ||
-            (long)jb.wscale_ld < (long)jb.k_tiles * 16 || (long)jb.ascale_ld < (long)jb.k_tiles * 16)
+            !jb.wscale_tiled || (jb.row_off & 127) || (jb.wscale_ld & 15) || (jb.ascale_ld & 15) ||
+            (reinterpret_cast<uintptr_t>(jb.wscale_e8) & 15) || (reinterpret_cast<uintptr_t>(jb.ascale_e8) & 15) ||
+            (jb.wscale_mat_stride & 15) || (jb.ascale_seg_stride & 15) ||
+            (long)jb.wscale_ld < (long)jb.k_tiles * nvf4::kSfaUnit || (long)jb.ascale_ld < (long)jb.k_tiles * 16 ||
+            jb.wscale_mat_stride < (long)((jb.row_off + jb.n_rows + 127) / 128) * jb.wscale_ld)
             return -100;
     }
     nvf4::Params p;

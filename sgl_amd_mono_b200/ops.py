@@ -126,6 +126,20 @@ def plan_split(k_tiles: int, row_blocks: int, wkind: int, sms: int | None = None
     return split, -(-k_tiles // split)
 
 
+def tile_nvfp4_scales(ws: torch.Tensor) -> torch.Tensor:
+    """NVFP4 scale bytes [mats, rows, K/16] -> [mats, row blocks, tiles * 2048] in the order ``mono_gemv_job.wscale_tiled``
+    describes: per (128-row block, 256-value tile) four 512-byte pieces (one per 64-value MMA), byte
+    ``(r % 32) * 16 + (r // 32) * 4 + b`` of a piece = row ``r`` of the block, 16-value block ``b`` of the MMA.
+    Rows and tiles are padded with 0x38 (1.0)."""
+    mats, rows, kb = ws.shape
+    rp, kp = _up(rows, 128), _up(kb, 16)
+    pad = torch.full((mats, rp, kp), 0x38, dtype=torch.uint8, device=ws.device)
+    pad[:, :rows, :kb] = ws
+    # [mat, row block, r // 32, r % 32, tile, MMA, block] -> [mat, row block, tile, MMA, r % 32, r // 32, block]
+    t = pad.view(mats, rp // 128, 4, 32, kp // 16, 4, 4).permute(0, 1, 4, 5, 3, 2, 6).contiguous()
+    return t.view(mats, rp // 128, (kp // 16) * 2048)
+
+
 def fp4_tma_ok(w: torch.Tensor) -> bool:
     """Whether a packed-nibble weight [..., N, K/2] can be read as a 4-bit tensor by TMA: K a multiple of
     128, rows a multiple of 32 bytes apart, base 32-byte aligned."""
@@ -218,18 +232,19 @@ class Gemv:
                 raise ValueError(f"{name}: NVFP4 weights take NVFP4 activations (both operands of the MMA are 4-bit)")
             if ws3.shape[1] != rows_total or ws3.shape[2] * 8 < kb:
                 raise ValueError(f"{name}.scale: shape {tuple(ws.shape)} does not cover the weight (one byte per 16 values)")
-            if ws3.shape[2] % 16 or ws3.data_ptr() % 16:
-                # the kernel reads a row's 16 scale bytes of a 256-value tile at once: rows are padded once to whole
-                # tiles with the byte of 1.0 (the weight bytes past K read as zeros)
-                padded = torch.full((*ws3.shape[:2], _up(ws3.shape[2], 16)), 0x38, dtype=torch.uint8, device=ws.device)
-                padded[..., : ws3.shape[2]] = ws3
-                log.info("%s.scale: padded %s -> %s (one-time repack, %d bytes)", name, tuple(ws3.shape),
-                         tuple(padded.shape), padded.numel())
-                ws = ws3 = padded
-                self._keep.append(padded)
-                if self.copies is not None:
-                    self.copies["NVFP4 scale rows padded to whole tiles", self.copy_tag, name] = padded
-            job.wscale_e8, job.wscale_mat_stride, job.wscale_ld = ws.data_ptr(), ws3.shape[1] * ws3.shape[2], ws3.shape[2]
+            # the kernel fetches the scale bytes of a (128-row block, 256-value tile) with one bulk copy, in the order
+            # the tensor core copies them to its memory: repacked once (the reference logs its few repacks the same
+            # way: glm53/gfx950/weights.py:207-310)
+            tiled = tile_nvfp4_scales(ws3)
+            log.info("%s.scale: %s -> tiled %s (one-time repack, %d bytes)", name, tuple(ws3.shape), tuple(tiled.shape),
+                     tiled.numel())
+            self._keep.append(tiled)
+            if self.copies is not None:
+                self.copies["NVFP4 scale bytes in tensor-core order", self.copy_tag, name] = tiled
+            job.wscale_e8, job.wscale_mat_stride, job.wscale_ld = tiled.data_ptr(), tiled.shape[1] * tiled.shape[2], tiled.shape[2]
+            job.wscale_tiled = 1
+            if row_off % 128:
+                raise ValueError(f"{name}: an NVFP4 job starts at a multiple of 128 rows")
             if wglobal is not None:
                 require(wglobal, name + ".global_scale", torch.float32)
                 if wglobal.numel() != mats:

@@ -118,3 +118,27 @@ def test_quantisation_error_of_the_block_against_float_weights():
     got = S.expert_nvfp4(Q.bf(xn), w["w13"][e], w["w13_s"][e], w["w13_g"][e], w["w2"][e], w["w2_s"][e], w["w2_g"][e])
     cos = torch.nn.functional.cosine_similarity(got.flatten(), want.flatten(), dim=0)
     assert float(cos) > 0.98
+
+
+def test_scale_bytes_in_tensor_core_order():
+    """The one-time repack of the weights' scale bytes: byte (r % 32) * 16 + (r // 32) * 4 + b of the 512-byte piece of
+    (row block, 256-value tile, MMA) is the scale of row r, 16-value block b; padding rows and tiles hold 1.0."""
+    from sgl_amd_mono_b200 import ops
+
+    g = torch.Generator().manual_seed(11)
+    mats, rows, kb = 2, 200, 40  # K = 640: two and a half tiles; one and a half row blocks
+    ws = torch.randint(0, 127, (mats, rows, kb), generator=g, dtype=torch.uint8)
+    t = ops.tile_nvfp4_scales(ws)
+    assert t.shape == (mats, 2, 3 * 2048)
+    for mat, r, k16 in [(0, 0, 0), (1, 37, 5), (0, 129, 17), (1, 199, 39), (0, 64, 16), (1, 127, 31)]:
+        rb, rr = divmod(r, 128)
+        tile, rem = divmod(k16, 16)
+        mma, b = divmod(rem, 4)
+        off = tile * 2048 + mma * 512 + (rr % 32) * 16 + (rr // 32) * 4 + b
+        assert int(t[mat, rb, off]) == int(ws[mat, r, k16]), (mat, r, k16)
+    # padding: rows 200..255 of block 1, tiles past K
+    assert int(t[0, 1, (199 - 128 + 1) % 32 * 16 + ((199 - 128 + 1) // 32) * 4]) == 0x38
+    assert set(t[0, 0, 2 * 2048 + 2 * 512 :].tolist()) == {0x38}
+    # every source byte appears exactly once
+    assert int((t != 0x38).sum()) <= mats * rows * kb
+    assert sorted(t[t != 0x38].tolist()) == sorted(ws[ws != 0x38].tolist())
