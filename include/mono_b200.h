@@ -207,7 +207,8 @@ typedef struct mono_gemv_job {
      * runs on the warp-MMA consumer, which needs MONO_ACT_MX8. */
     mono_tmap_t tmap4;
     int act_natural; /* 1 = the activation planes are MONO_ACT_MX8N */
-    int k_tiles4;    /* K in 128-element tiles (0 = 2 * k_tiles): exact when K ends inside a 128-byte tile */
+    int k_tiles4;    /* K in 128-element tiles (0 = 2 * k_tiles): exact when K ends inside a 128-byte tile.
+                        NVFP4: K in 64-value MMAs (0 = 4 * k_tiles); the MMAs past K in the last tile are skipped */
     /* Optional staging of the output as the next GEMV's activations (dense jobs on the tcgen05 consumer
      * with nsplit == 1): output (row c, column n) is rounded to bf16 and written as E4M3 to
      * stage_planes[c * stage_ld + n] (MONO_ACT_HILO: high byte there, low byte stage_plane_stride

@@ -17,8 +17,8 @@
 // the weight is bound): the 2 KB of a (row block, 256-k unit) arrive by one bulk copy beside the unit's weights.
 // (Gathered from row-major rows by warps of the kernel, a segment's bytes took 2.2 - 2.8 us under load, as long
 // as its MMAs, and the slots they needed left room for 7 ring stages only: 3.9 TB/s.)  The activations' bytes
-// (16 rows: the first 16 lanes of column 0, so their blocks overlap, 256 bytes apart) are gathered by a scale warp
-// into one of three slots, two segments ahead of the MMA threads.  Every scale byte the MMA can see is a valid
+// (16 rows: the first 16 lanes of column 0, so their blocks overlap, 256 bytes apart) are gathered by four scale
+// warps, segment by segment in turn, each into a slot of its own, up to four segments ahead of the MMA threads.  Every scale byte the MMA can see is a valid
 // E4M3 number from the start (0x38 = 1.0).
 //
 // Issue rate.  Per 16 KB of weights: four MMAs and eight scale copies, about 70 cycles each for the issuing thread.
@@ -26,8 +26,8 @@
 // the two.  The issuing threads do not walk the task list (a single thread needs about 1 us for the divisions and
 // address arithmetic of a segment): the scale warp leaves each segment's unit count in its slot.
 //
-// 256 threads: warp 0 TMA, one thread each of warps 1 and 7 issues tcgen05.cp + MMA, warps 2..5 own the 128 TMEM
-// lanes (epilogue), warp 6 stages the activations' scale bytes.  Every wait is bounded; TMEM is freed on every
+// 352 threads: warp 0 TMA, one thread each of warps 1 and 7 issues tcgen05.cp + MMA, warps 2..5 own the 128 TMEM
+// lanes (epilogue), warps 6, 8, 9, 10 stage the activations' scale bytes.  Every wait is bounded; TMEM is freed on every
 // exit path.
 #include "mono_common.cuh"
 
@@ -36,7 +36,7 @@ extern void mono_set_error(const char* fmt, ...);
 namespace mono {
 namespace nvf4 {
 
-constexpr int kThreads = 256;
+constexpr int kThreads = 352;
 constexpr int kStages = 9;
 constexpr int kPackBytes = 128 * 128;   // a unit of weights: 128 rows x 128 bytes = 256 k values per row
 constexpr int kBBytes = 16 * 128;       // the unit's activations: 16 rows x 128 bytes
@@ -45,7 +45,8 @@ constexpr int kSfBlock = 512;           // scale bytes of one MMA in the order t
 constexpr int kSfaUnit = kMmas * kSfBlock;  // the unit's weight scales
 constexpr int kStageBytes = kPackBytes + kBBytes + kSfaUnit;
 constexpr int kMaxSegUnits = 8;         // units (256 k values) per segment
-constexpr int kScSlots = 3;             // activation scales of a segment: staged two segments ahead
+constexpr int kScWarps = 4;             // scale warps: warp i takes segments i, i + 4, ...
+constexpr int kScSlots = kScWarps;      // ... into a slot of its own (one writer per slot: its uses follow one another)
 constexpr int kSfbStep = 256;           // activations: blocks half a block apart
 constexpr int kSfbBytes = kMaxSegUnits * kMmas * kSfbStep + kSfBlock / 2;
 constexpr int kSlotBytes = kSfbBytes + 128;  // + 16 route coefficients, the tensor scale and the unit count
@@ -71,37 +72,57 @@ struct Seg {
     const uint8_t* asc;
     const uint8_t* wsc;
     const float* coef;
-    float g;
+    const float* gp;  // the matrix's tensor scale (or null)
 };
 
 __device__ __forceinline__ int nrb_of(const mono_gemv_job& j) { return (j.n_rows + 127) >> 7; }
 
-__device__ __forceinline__ Seg make_seg(const mono_gemv_job& j, int rb, int ks, int u, const int* elist) {
-    Seg s;
-    int mat = 0;
-    if (j.mode == MONO_JOB_DENSE) {
-        s.t0 = ks * j.split_tiles;
-        s.nt = min(j.split_tiles, j.k_tiles - s.t0);
-        s.aset = 0;
-        s.coef = nullptr;
-    } else if (j.mode == MONO_JOB_EXPERT_UP) {
-        mat = (u < 128) ? elist[u] : j.expert_list[u];
-        s.t0 = ks * j.split_tiles;
-        s.nt = min(j.split_tiles, j.k_tiles - s.t0);
-        s.aset = 0;
-        s.coef = nullptr;
+// What a task's segments share: computed once per task, so that a segment of a down projection (an expert of a few
+// hundred values) costs a role a table lookup and a handful of multiply-adds.
+struct TaskC {
+    int mode, row0, t0, nt;
+    const uint8_t* asc0;  // + aset * ascale_seg_stride
+    const uint8_t* wsc0;  // + mat * wscale_mat_stride
+    long a_stride, w_stride;
+    const float* coef;
+    const float* wglobal;
+    const int32_t* expert_list;
+};
+
+__device__ __forceinline__ TaskC make_task(const mono_gemv_job& j, int rb, int ks) {
+    TaskC t;
+    t.mode = j.mode;
+    t.row0 = j.row_off + rb * 128;
+    if (j.mode == MONO_JOB_EXPERT_DOWN) {
+        t.t0 = 0;
+        t.nt = j.k_tiles;
     } else {
-        mat = (u < 128) ? elist[u] : j.expert_list[u];
-        s.t0 = 0;
-        s.nt = j.k_tiles;
-        s.aset = u;
-        s.coef = j.coef ? j.coef + (size_t)u * kMaxRows : nullptr;
+        t.t0 = ks * j.split_tiles;
+        t.nt = min(j.split_tiles, j.k_tiles - t.t0);
     }
+    t.asc0 = j.ascale_e8 + (size_t)t.t0 * 16;
+    t.wsc0 = j.wscale_e8 + (size_t)(t.row0 >> 7) * j.wscale_ld + (size_t)t.t0 * kSfaUnit;
+    t.a_stride = j.ascale_seg_stride;
+    t.w_stride = j.wscale_mat_stride;
+    t.coef = j.coef;
+    t.wglobal = j.wglobal;
+    t.expert_list = j.expert_list;
+    return t;
+}
+
+__device__ __forceinline__ Seg make_seg(const TaskC& t, int u, const int* elist) {
+    Seg s;
+    const int mat = t.mode == MONO_JOB_DENSE ? 0 : ((u < 128) ? elist[u] : t.expert_list[u]);
+    const bool down = t.mode == MONO_JOB_EXPERT_DOWN;
     s.c2 = mat;
-    s.row0 = j.row_off + rb * 128;
-    s.asc = j.ascale_e8 + (size_t)s.aset * j.ascale_seg_stride + (size_t)s.t0 * 16;
-    s.wsc = j.wscale_e8 + (size_t)mat * j.wscale_mat_stride + (size_t)(s.row0 >> 7) * j.wscale_ld + (size_t)s.t0 * kSfaUnit;
-    s.g = j.wglobal ? __ldg(j.wglobal + mat) : 1.f;
+    s.row0 = t.row0;
+    s.t0 = t.t0;
+    s.nt = t.nt;
+    s.aset = down ? u : 0;
+    s.coef = (down && t.coef) ? t.coef + (size_t)u * kMaxRows : nullptr;
+    s.asc = t.asc0 + (size_t)s.aset * t.a_stride;
+    s.wsc = t.wsc0 + (size_t)mat * t.w_stride;
+    s.gp = t.wglobal ? t.wglobal + mat : nullptr;
     return s;
 }
 
@@ -165,9 +186,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_con
     uint64_t* full = bars;                      // TMA -> MMA: a slot's boxes have landed
     uint64_t* stage_free = full + kStages;      // MMA -> TMA: the MMAs that read the slot are done
     uint64_t* sc_full = stage_free + kStages;   // scale warp -> MMA / epilogue: a segment's scale bytes are staged
-    uint64_t* sc_empty = sc_full + kScSlots;    // 2 issuers (their copies are done) + 4 epilogue warps (coefficients read)
-    uint64_t* acc_full = sc_empty + kScSlots;   // 2 issuers -> epilogue: a segment's accumulators are complete
-    uint64_t* acc_empty = acc_full + 2;         // 4 epilogue warps -> MMA
+    uint64_t* sc_empty = sc_full + kScSlots;    // 2 issuers (unit count read) + 4 epilogue warps (coefficients read; the
+                                                // accumulators they waited for were complete, so the issuers' copies from
+                                                // the slot are done too)
+    uint64_t* acc_full = sc_empty + kScSlots;   // [buffer][issuer] -> epilogue: that issuer's accumulator of the segment is complete
+    uint64_t* acc_empty = acc_full + 4;         // 4 epilogue warps -> MMA
     __shared__ int abort_flag;
     __shared__ uint32_t tmem_base_s;
     __shared__ int s_elist[MONO_GEMV_MAX_JOBS][128];
@@ -179,7 +202,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_con
         abort_flag = guard_failed(p.a.guard) ? 1 : 0;
         for (int i = 0; i < kStages; ++i) { mbar_init(&full[i], 1); mbar_init(&stage_free[i], 1); }
         for (int i = 0; i < kScSlots; ++i) { mbar_init(&sc_full[i], 32); mbar_init(&sc_empty[i], 6); }
-        for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 2); mbar_init(&acc_empty[i], 4); }
+        for (int i = 0; i < 4; ++i) mbar_init(&acc_full[i], 1);
+        for (int i = 0; i < 2; ++i) mbar_init(&acc_empty[i], 4);
         mbar_fence_init();
     }
     for (int i = tid; i < kScSlots * kSlotBytes / 4; i += kThreads) reinterpret_cast<uint32_t*>(sc_ring)[i] = kOne4;
@@ -230,10 +254,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_con
         const int u_up = u, rb = local % nrb, ks = local / nrb;                                                 \
         if (jb.mode == MONO_JOB_EXPERT_DOWN) nseg = (nexp[j] > ks) ? (nexp[j] - ks + jb.nsplit - 1) / jb.nsplit : 0; \
         (void)u_up; (void)rb;                                                                                   \
+        const TaskC tc = make_task(jb, rb, ks);                                                                 \
+        const int u_step = jb.nsplit;                                                                           \
         TASK_BEGIN                                                                                              \
         for (int sgi = 0; sgi < nseg && !*abortp; ++sgi) {                                                      \
-            if (jb.mode == MONO_JOB_EXPERT_DOWN) u = ks + sgi * jb.nsplit;                                      \
-            const Seg s = make_seg(jb, rb, ks, u, s_elist[j]);                                                  \
+            if (tc.mode == MONO_JOB_EXPERT_DOWN) u = ks + sgi * u_step;                                         \
+            const Seg s = make_seg(tc, u, s_elist[j]);                                                          \
             __VA_ARGS__                                                                                         \
         }                                                                                                       \
         TASK_END                                                                                                \
@@ -274,56 +300,71 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_con
         // The issuing threads do not walk the task list (a single thread needs about 1 us for the divisions and
         // address arithmetic of a segment, time in which no MMA is issued): the scale warps leave each segment's
         // unit count in its slot, and a count of zero ends the launch.
+        // A segment of one or two units (a down projection of a narrow expert) belongs to ONE issuer, the segments
+        // alternating between the two: the handshakes of a segment cost an issuing thread about as much as the twelve
+        // instructions of a unit, so two threads sharing such a segment spent 1.3 us on it, while each taking every
+        // other segment as a whole they overlap their handshakes.
         if (lane == 0) {
             const int me = warp == 1 ? 0 : 1;
-            int slot = 0, buf = 0, n0 = 0;
-            uint32_t sphase = 0, aphase = 0, mine = 0;
+            int slot = 0, n0 = 0, seg_no = 0;
+            uint32_t sphase = 0, mine = 0;
             for (;;) {
                 if (!mbar_wait(&sc_full[slot], sphase, abortp, wait_ns)) break;
-                const int nt = reinterpret_cast<const volatile int*>(sc_ring + (size_t)slot * kSlotBytes + kSfbBytes)[kMaxRows + 1];
+                const int word = reinterpret_cast<const volatile int*>(sc_ring + (size_t)slot * kSlotBytes + kSfbBytes)[kMaxRows + 1];
+                const int nt = word & 0xFF, nm_last = word >> 8;  // units; MMAs of the last unit
                 if (nt <= 0) break;
+                mbar_arrive(&sc_empty[slot]);  // this thread has read the slot's words (its copies: see sc_empty)
+                const int buf = seg_no & 1;
+                const uint32_t aphase = (uint32_t)(seg_no >> 1) & 1u;
+                const bool alone = nt <= 2;  // the segment has one owner: issuer `buf`
                 if (me == 0) NV_TL(13, n0);
+                // (every issuer waits for every buffer turn, owner or not: the parities of a barrier it skipped
+                // for two turns would no longer tell it anything)
                 if (!mbar_wait(&acc_empty[buf], aphase ^ 1, abortp, wait_ns)) break;
                 if (me == 0) NV_TL(7, n0);
                 if (me == 0 && n0 == 0 && blockIdx.x < 140) MONO_TL_AT(tl_nv, 5);
-                fence_after();
-                const uint32_t sl = smem_u32(sc_ring + (size_t)slot * kSlotBytes);
-                const uint32_t acc = tmem_base + (buf * 2 + me) * kAccCols;
-                uint32_t accumulate = 0;
                 bool ok = true;
-                for (int t = (n0 + me) & 1; t < nt; t += 2) {  // this issuer's units: launch-wide numbers of its parity
-                    const int n = n0 + t, st_now = n % kStages;
-                    const uint32_t ph_now = (uint32_t)(n / kStages) & 1u;
-                    NV_TL(3, n);
-                    if (!mbar_wait(&full[st_now], ph_now, abortp, wait_ns)) { ok = false; break; }
-                    NV_TL(4, n);
+                if (!alone || buf == me) {
                     fence_after();
-                    const uint32_t sa = smem_u32(ring + (size_t)st_now * kStageBytes);
-                    const uint64_t adesc = desc_sw128(sa), bdesc = desc_sw128(sa + kPackBytes);
-                    // (the tensor pipe runs a thread's copies and MMAs in the order it issued them; the column sets
-                    // alternate from unit to unit all the same)
-                    const uint32_t set = tmem_base + kSfCol + me * 64 + (mine & 1) * 32;
-                    ++mine;
+                    const uint32_t sl = smem_u32(sc_ring + (size_t)slot * kSlotBytes);
+                    const uint32_t acc = tmem_base + (buf * 2 + me) * kAccCols;
+                    uint32_t accumulate = 0;
+                    // shared segment: the units of this issuer's parity (launch-wide numbers); own segment: all
+                    for (int t = alone ? 0 : ((n0 + me) & 1); t < nt; t += alone ? 1 : 2) {
+                        const int n = n0 + t, st_now = n % kStages;
+                        const uint32_t ph_now = (uint32_t)(n / kStages) & 1u;
+                        NV_TL(3, n);
+                        if (!mbar_wait(&full[st_now], ph_now, abortp, wait_ns)) { ok = false; break; }
+                        NV_TL(4, n);
+                        fence_after();
+                        const uint32_t sa = smem_u32(ring + (size_t)st_now * kStageBytes);
+                        const uint64_t adesc = desc_sw128(sa), bdesc = desc_sw128(sa + kPackBytes);
+                        // (the tensor pipe runs a thread's copies and MMAs in the order it issued them; the column sets
+                        // alternate from unit to unit all the same)
+                        const uint32_t set = tmem_base + kSfCol + me * 64 + (mine & 1) * 32;
+                        ++mine;
+                        const int nm = t == nt - 1 ? nm_last : kMmas;  // K may end inside the segment's last unit
 #pragma unroll
-                    for (int m = 0; m < kMmas; ++m) {  // 64 values per MMA, 32 bytes further along K
-                        const int blk = t * kMmas + m;
-                        const uint32_t sfa = set + m * 8, sfb = sfa + 4;
-                        cp_sf(sfa, desc_sf(sa + kPackBytes + kBBytes + m * kSfBlock));
-                        cp_sf(sfb, desc_sf(sl + blk * kSfbStep));
-                        mma_nvf4(acc, adesc + 2 * m, bdesc + 2 * m, kIdesc, sfa, sfb, accumulate);
-                        accumulate = 1;
+                        for (int m = 0; m < kMmas; ++m) {  // 64 values per MMA, 32 bytes further along K
+                            if (m >= nm) break;
+                            const int blk = t * kMmas + m;
+                            const uint32_t sfa = set + m * 8, sfb = sfa + 4;
+                            cp_sf(sfa, desc_sf(sa + kPackBytes + kBBytes + m * kSfBlock));
+                            cp_sf(sfb, desc_sf(sl + blk * kSfbStep));
+                            mma_nvf4(acc, adesc + 2 * m, bdesc + 2 * m, kIdesc, sfa, sfb, accumulate);
+                            accumulate = 1;
+                        }
+                        commit(&stage_free[st_now]);
+                        NV_TL(5, n);
                     }
-                    commit(&stage_free[st_now]);
-                    NV_TL(5, n);
+                    if (!ok) break;
+                    NV_TL(6, n0 + nt - 1);
+                    commit(&acc_full[buf * 2 + me]);
+                    if (me == 0) NV_TL(18, n0 + nt - 1);
                 }
-                if (!ok) break;
                 n0 += nt;
-                NV_TL(6, n0 - 1);
-                commit(&acc_full[buf]);
-                commit(&sc_empty[slot]);
-                if (me == 0) NV_TL(18, n0 - 1);
+                ++seg_no;
                 if (++slot == kScSlots) { slot = 0; sphase ^= 1; }
-                if (++buf == 2) { buf = 0; aphase ^= 1; }
             }
         }
     } else if (warp < 6) {
@@ -331,8 +372,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_con
         const int q = warp & 3;
         const int row_in_tile = q * 32 + lane;
         const uint32_t tmem_lane = tmem_base + ((uint32_t)(q * 32) << 16);
-        int slot = 0, buf = 0, n = 0;
-        uint32_t sphase = 0, aphase = 0;
+        int slot = 0, n = 0, seg_no = 0;
+        uint32_t sphase = 0, fphase = 0;  // fphase: bit (buffer * 2 + issuer) = parity of that accumulator's next turn
         float total_acc[kMaxRows];
 #define TASK_BEGIN \
         _Pragma("unroll") for (int c = 0; c < kMaxRows; ++c) total_acc[c] = 0.f;
@@ -348,7 +389,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_con
         NV_FOR_EACH_SEGMENT({
             if (!mbar_wait(&sc_full[slot], sphase, abortp, wait_ns)) break;
             if (tid == 64) NV_TL(11, n);
-            if (!mbar_wait(&acc_full[buf], aphase, abortp, wait_ns)) break;
+            // whose accumulators hold this segment: its owner's (one or two units), else both issuers'
+            const int buf = seg_no & 1;
+            const bool alone = s.nt <= 2, w0 = !alone || buf == 0, w1 = !alone || buf == 1;
+            ++seg_no;
+            bool got = true;
+            if (w0) { got = mbar_wait(&acc_full[buf * 2], (fphase >> (buf * 2)) & 1u, abortp, wait_ns); fphase ^= 1u << (buf * 2); }
+            if (got && w1) { got = mbar_wait(&acc_full[buf * 2 + 1], (fphase >> (buf * 2 + 1)) & 1u, abortp, wait_ns); fphase ^= 1u << (buf * 2 + 1); }
+            if (!got) break;
             if (tid == 64) NV_TL(12, n);
             fence_after();
             uint32_t d[32];
@@ -356,8 +404,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_con
             fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
-            // which issuers had a unit of this segment (an accumulator nobody wrote holds an older segment's sum)
-            const bool w0 = s.nt >= 2 || (n & 1) == 0, w1 = s.nt >= 2 || (n & 1) == 1;
             n += s.nt;
             if (tid == 64) NV_TL(15, n - s.nt);
             const float* coef = reinterpret_cast<const float*>(sc_ring + (size_t)slot * kSlotBytes + kSfbBytes);
@@ -369,25 +415,31 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_con
             __syncwarp();
             if (lane == 0) mbar_arrive(&sc_empty[slot]);
             if (++slot == kScSlots) { slot = 0; sphase ^= 1; }
-            if (++buf == 2) { buf = 0; aphase ^= 1; }
         })
 #undef TASK_BEGIN
 #undef TASK_END
-    } else if (warp == 6) {
-        // ------------------------------------------------------------ scale warp: a segment's activation scale bytes,
-        // route coefficients, tensor scale and unit count, two segments ahead
-        int slot = 0, tl_n = 0;
+    } else if (warp == 6 || warp >= 8) {
+        // ------------------------------------------------------------ scale warps: a segment's activation scale bytes,
+        // route coefficients, tensor scale and unit count, up to four segments ahead.  A segment costs its warp a
+        // memory round trip (1 - 2 us under load), more than the MMAs of a short segment (a down projection of 384
+        // values: two units, 0.8 us): four warps take the segments in turn, so four round trips overlap.
+        const int sw = warp == 6 ? 0 : warp - 7;
+        int seg_no = 0, tl_n = 0;
         (void)tl_n;
-        uint32_t sphase = 0;
 #define TASK_BEGIN
 #define TASK_END
         NV_FOR_EACH_SEGMENT({
+            const int slot = seg_no % kScSlots;
+            const uint32_t sphase = (uint32_t)(seg_no / kScSlots) & 1u;
+            const bool mine = (seg_no % kScWarps) == sw;
+            ++seg_no;
+            if (!mine) { tl_n += s.nt; continue; }
             int ok = 1;
-            if (lane == 0) NV_TL(8, tl_n);
+            if (lane == 0 && sw == 0) NV_TL(8, tl_n);
             if (lane == 0) ok = mbar_wait(&sc_empty[slot], sphase ^ 1, abortp, wait_ns) ? 1 : 0;
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
-            if (lane == 0) NV_TL(9, tl_n);
+            if (lane == 0 && sw == 0) NV_TL(9, tl_n);
             uint8_t* sl = sc_ring + (size_t)slot * kSlotBytes;
             // row c's four bytes of MMA m are the first four bytes of row c of the MMA's block (rows past the step:
             // 1.0); lanes 0..15 take the even units, 16..31 the odd ones; every load is issued before the first store
@@ -414,19 +466,23 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_con
             {
                 float* cf = reinterpret_cast<float*>(sl + kSfbBytes);
                 if (lane < kMaxRows) cf[lane] = cf_v;
-                if (lane == kMaxRows) cf[lane] = s.g;
-                if (lane == kMaxRows + 1) reinterpret_cast<int*>(cf)[lane] = s.nt;  // for the issuing threads
+                if (lane == kMaxRows) cf[lane] = s.gp ? __ldg(s.gp) : 1.f;
+                if (lane == kMaxRows + 1) {  // for the issuing threads: units, and the MMAs of the last unit (K may end inside it)
+                    const int k_mmas = jb.k_tiles4 > 0 ? jb.k_tiles4 : jb.k_tiles * kMmas;
+                    reinterpret_cast<int*>(cf)[lane] = s.nt | (max(1, min(kMmas, k_mmas - (s.t0 + s.nt - 1) * kMmas)) << 8);
+                }
             }
             fence_proxy_async_smem();  // the copies to TMEM read these bytes through the async proxy
             mbar_arrive(&sc_full[slot]);
-            if (lane == 0) NV_TL(10, tl_n);
+            if (lane == 0 && sw == 0) NV_TL(10, tl_n);
             tl_n += s.nt;
-            if (++slot == kScSlots) { slot = 0; sphase ^= 1; }
         })
 #undef TASK_BEGIN
 #undef TASK_END
-        // the end marker: a slot with a unit count of zero
-        if (!*abortp) {
+        // the end marker: a slot with a unit count of zero, from the warp whose turn it is
+        if (!*abortp && (seg_no % kScWarps) == sw) {
+            const int slot = seg_no % kScSlots;
+            const uint32_t sphase = (uint32_t)(seg_no / kScSlots) & 1u;
             int ok = 1;
             if (lane == 0) ok = mbar_wait(&sc_empty[slot], sphase ^ 1, abortp, wait_ns) ? 1 : 0;
             ok = __shfl_sync(0xffffffffu, ok, 0);

@@ -243,6 +243,7 @@ class Gemv:
                 self.copies["NVFP4 scale bytes in tensor-core order", self.copy_tag, name] = tiled
             job.wscale_e8, job.wscale_mat_stride, job.wscale_ld = tiled.data_ptr(), tiled.shape[1] * tiled.shape[2], tiled.shape[2]
             job.wscale_tiled = 1
+            job.k_tiles4 = -(-kb // 32)  # K in 64-value MMAs: the kernel skips the MMAs past K in the last tile
             if row_off % 128:
                 raise ValueError(f"{name}: an NVFP4 job starts at a multiple of 128 rows")
             if wglobal is not None:
