@@ -196,3 +196,36 @@ def test_ffn_runner_takes_the_attention_output_through_the_seam():
         run(attn.to(DEV), residual.to(DEV), dict(w), slots.to(DEV))
     out_b, res_b = run(None, residual.to(DEV), None, slots.to(DEV))
     assert res_b.data_ptr() == residual.to(DEV).data_ptr() or torch.equal(res_b.cpu(), residual)
+
+
+def test_m31_spec_builds_nvfp4_experts_from_the_checkpoint_config():
+    """MiniMax-M3.1-Flash's checkpoint config (``moe_quant_algo: NVFP4``, reference ``minimax_m31/spec.py:116-121`` and
+    ``test/unit/test_minimax_m31_spec.py:16``) builds FFN launches over NVFP4 experts; the one-time repack of their
+    scale bytes lands among the build context's copies; the block matches the CPU restatement."""
+    from types import SimpleNamespace
+
+    from sgl_amd_mono_b200.minimax_m31 import spec as m31
+    from util import assert_close_hidden
+
+    hf = SimpleNamespace(hidden_size=512, n_routed_experts=8, num_experts_per_tok=2, moe_intermediate_size=256,
+                         routed_scaling_factor=1.0, scoring_func="sigmoid", rms_norm_eps=1e-6, shared_expert_format="none",
+                         quantization_config=dict(quant_method="mxfp8", moe_quant_algo="NVFP4"))
+    assert m31.SPEC.config_disable_reasons(SimpleNamespace(tp_size=1, page_size=64, speculative_algorithm=None), hf) == []
+    cfg = m31.layer_config(hf, 1)
+    assert cfg.expert_fmt == "nvfp4"
+    w = synth.layer_weights(cfg, 0, DEV)
+    model = SimpleNamespace(layers=[SimpleNamespace(weights=w)])
+    ctx = SimpleNamespace(tp_size=1, device=DEV, deadline_s=5.0, copies={}, widths=(16,), max_context=4096)
+    built = m31.SPEC.build(model, hf, ctx)
+    kinds = {k[0] for k in ctx.copies}
+    assert kinds == {"NVFP4 scale bytes in tensor-core order"} and len(ctx.copies) == 2, ctx.copies.keys()
+    rows = 6
+    x = torch.randn(rows, cfg.hidden, generator=torch.Generator().manual_seed(21)).bfloat16()
+    slots = torch.arange(1, rows + 1, dtype=torch.int64)
+    run = built.ops[0]
+    out, res = run(None, x.to(DEV), None, slots.to(DEV))
+    torch.cuda.synchronize()
+    assert ops.guard_read(run.guard)[0] == 0
+    ref, det = OL.ffn_block(cfg, [_cpu(w)], x)
+    assert torch.equal(run.ffn.ids[:rows].cpu(), det["ids"])
+    assert_close_hidden(out, ref, "M3.1 FFN launch over NVFP4 experts", scale=float((ref.float() - x.float()).abs().max()))

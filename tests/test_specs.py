@@ -72,6 +72,13 @@ def test_the_minimax_dispatcher_picks_by_checkpoint_quantisation():
     assert any("block-sparse" in r for r in minimax.SPEC.config_disable_reasons(CFG, m3))
     odd = SimpleNamespace(**{**vars(m31), "moe_intermediate_size": 384})
     assert any("multiples of 256" in r for r in minimax.SPEC.config_disable_reasons(CFG, odd))
+    # M3.1-Flash's checkpoint: NVFP4 experts next to MXFP8 dense layers (the reference's own test config:
+    # test/unit/test_minimax_m31_spec.py:16)
+    from sgl_amd_mono_b200.minimax_m31 import spec as m31_spec
+
+    nv = SimpleNamespace(**{**vars(m31), "quantization_config": dict(quant_method="mxfp8", moe_quant_algo="NVFP4")})
+    assert m31_spec.is_m31(nv) and minimax.SPEC.config_disable_reasons(CFG, nv) == []
+    assert m31_spec.layer_config(nv, 4).expert_fmt == "nvfp4" and m31_spec.layer_config(m31, 4).expert_fmt == "mxfp4"
 
 
 def test_the_m3_spec_lists_every_reason_and_accepts_the_block_sparse_layout():
