@@ -144,8 +144,7 @@ int mono_act_prep_launch(const mono_act_prep_args* a, void* stream);
  * go to f32 buffers that the next stage adds in a fixed order. */
 #define MONO_GEMV_MAX_JOBS 4
 /* MONO_W_NVFP4: packed E2M1 values with one E4M3 scale byte per 16 along K (wscale_e8, [mat][row][wscale_ld],
- * wscale_ld a multiple of 16 = whole 256-value tiles, rows padded with 0x38 = 1.0; or in the tensor core's order,
- * see wscale_tiled) and one f32 scale per matrix (wglobal); activations MONO_ACT_NVF4.  tcgen05 only (kind::mxf4nvf4.block_scale, 16-value blocks); k_tiles
+ * repacked into the tensor core's order: wscale_t) and one f32 scale per matrix (wglobal); activations MONO_ACT_NVF4.  tcgen05 only (kind::mxf4nvf4.block_scale, 16-value blocks); k_tiles
  * counts 128-byte tiles = 256 values, as for MXFP4.  (M3.1-Flash's expert format: minimax_m31/spec.py:117-121.) */
 enum { MONO_W_FP8 = 0, MONO_W_MXFP4 = 1, MONO_W_BF16 = 2, MONO_W_NVFP4 = 3 };
 enum { MONO_JOB_DENSE = 0, MONO_JOB_EXPERT_UP = 1, MONO_JOB_EXPERT_DOWN = 2 };
@@ -220,13 +219,16 @@ typedef struct mono_gemv_job {
     /* NVFP4: the f32 tensor scale of each matrix, [mat]; NULL = 1.  Applied to a task's f32 sum (before the
      * route coefficient of a down job). */
     const float* wglobal;
-    /* NVFP4: 1 = wscale_e8 holds the scale bytes in the order the tensor core copies them, one 2048-byte piece
-     * per (128-row block, 256-value tile): [mat][row block][tile][MMA 0..3][lane 0..31][row / 32][16-value block],
-     * i.e. byte ((r % 32) * 16 + (r / 32) * 4 + b) of the MMA's 512 bytes for row r of the block; rows and tiles
-     * padded with 0x38.  wscale_ld = bytes per row block, wscale_mat_stride = bytes per matrix, row_off a multiple
-     * of 128.  The kernel then fetches a tile's scales with one bulk copy next to its weights.  0 = row-major
-     * [mat][row][wscale_ld], gathered by a warp of the kernel. */
-    int wscale_tiled;
+    /* The weight's scale bytes in the order the tensor core copies them, one piece per (128-row block, unit of
+     * K): [mat][row block][unit][piece], where byte ((r % 32) * 16 + (r / 32) * 4 + b) of a 512-byte block is row r
+     * of the block and scale b.  NVFP4: unit = 256 values, piece = four blocks (one per 64-value MMA, b = its
+     * 16-value blocks), padding 0x38.  MXFP4: unit = 128 values, piece = one block (b = its 32-value groups),
+     * padding 127.  wscale_t_ld = bytes per row block, wscale_t_mat_stride = bytes per matrix; row_off a multiple
+     * of 128.  The kernel fetches a unit's scales with one bulk copy next to its weights.  Required for NVFP4;
+     * for MXFP4 it selects the kernel that lets TMA pad the nibbles (else warps of the kernel gather wscale_e8). */
+    const uint8_t* wscale_t;
+    long wscale_t_mat_stride;
+    int wscale_t_ld;
 } mono_gemv_job;
 
 typedef struct mono_gemv_args {

@@ -44,8 +44,8 @@ class GemvJob(C.Structure):
         ("tmap4", Tmap), ("act_natural", i32), ("k_tiles4", i32),
         ("stage_planes", vp), ("stage_scale", vp), ("stage_ld", i32), ("stage_scale_ld", i32),
         ("stage_fmt", i32), ("stage_plane_stride", i32),
-        ("wglobal", vp), ("wscale_tiled", i32),
-        ("_tail", C.c_ubyte * 12),
+        ("wglobal", vp), ("wscale_t", vp), ("wscale_t_mat_stride", i64), ("wscale_t_ld", i32),
+        ("_tail", C.c_ubyte * 60),
     ]
 
 

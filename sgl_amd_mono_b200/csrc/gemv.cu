@@ -439,6 +439,7 @@ int mono_gemv_tc_launch(const mono_gemv_args* a, long tasks, cudaStream_t st);  
 int mono_gemv_tc4_launch(const mono_gemv_args* a, long tasks, cudaStream_t st); // gemv_tc4.cu
 int mono_gemv_tc4bs_launch(const mono_gemv_args* a, long tasks, cudaStream_t st); // gemv_tc4bs.cu
 int mono_gemv_nvf4_launch(const mono_gemv_args* a, long tasks, cudaStream_t st);  // gemv_nvf4.cu
+int mono_gemv_mxf4_launch(const mono_gemv_args* a, long tasks, cudaStream_t st);  // gemv_nvf4.cu (its MXFP4 instance)
 
 namespace {
 template <int WK, int NT>
@@ -509,7 +510,7 @@ extern "C" int mono_gemv_launch(const mono_gemv_args* a, void* stream) {
             mono_set_error("mono_gemv_launch: job %d: MXFP4 jobs need E8M0 weight and activation scales", j);
             return MONO_E_ARG;
         }
-        if (a->wkind == MONO_W_NVFP4 && (!jb.wscale_e8 || !jb.ascale_e8)) {
+        if (a->wkind == MONO_W_NVFP4 && (!jb.wscale_t || !jb.ascale_e8)) {
             mono_set_error("mono_gemv_launch: job %d: NVFP4 jobs need E4M3 weight and activation scale bytes", j);
             return MONO_E_ARG;
         }
@@ -548,8 +549,8 @@ extern "C" int mono_gemv_launch(const mono_gemv_args* a, void* stream) {
         // one consumer only: the block-scaled FP4 tensor-core kind takes both operands in 4 bits
         const int rc = mono_gemv_nvf4_launch(a, tasks, (cudaStream_t)stream);
         if (rc == -100) {
-            mono_set_error("mono_gemv_launch: an NVFP4 job needs its weight and activation maps, one MONO_ACT_NVF4 plane, tiled weight "
-                           "scales (wscale_tiled, whole row blocks and tiles, 16-byte aligned), row_off a multiple of 128 and segments of "
+            mono_set_error("mono_gemv_launch: an NVFP4 job needs its weight and activation maps, one MONO_ACT_NVF4 plane, repacked weight "
+                           "scales (wscale_t: whole row blocks and tiles, 16-byte aligned), row_off a multiple of 128 and segments of "
                            "at most 2048 values");
             return MONO_E_ARG;
         }
@@ -557,10 +558,14 @@ extern "C" int mono_gemv_launch(const mono_gemv_args* a, void* stream) {
         return rc;
     }
     if (a->wkind == MONO_W_MXFP4 && mono_gemv_tc_enabled()) {
-        // the block-scaled kind (scales read by the MMA from tensor memory) unless MONO_TC4_BLOCK_SCALE=0 asks for
-        // the kernel that issues one MMA per scale group and scales in its epilogue (read per launch: tests compare both)
+        // the block-scaled kind (scales read by the MMA from tensor memory): with repacked scale codes (wscale_t) the
+        // kernel whose nibbles TMA pads, else (or MONO_TC4_BLOCK_SCALE=1) the one whose warps spread them;
+        // MONO_TC4_BLOCK_SCALE=0 asks for the kernel that issues one MMA per scale group and scales in its epilogue
+        // (read per launch: tests compare the three)
         const char* bs = getenv("MONO_TC4_BLOCK_SCALE");
-        int rc = (bs && bs[0] == '0') ? -100 : mono_gemv_tc4bs_launch(a, tasks, (cudaStream_t)stream);
+        const char mode = bs ? bs[0] : '2';
+        int rc = mode == '2' ? mono_gemv_mxf4_launch(a, tasks, (cudaStream_t)stream) : -100;
+        if (rc == -100 && mode != '0') rc = mono_gemv_tc4bs_launch(a, tasks, (cudaStream_t)stream);
         if (rc == -100) rc = mono_gemv_tc4_launch(a, tasks, (cudaStream_t)stream);  // -100: not eligible, use the warp-MMA consumer
         if (rc != -100) {
             if (rc > 0) mono_set_error("mono_gemv_launch: CUDA error %d (%s)", rc, cudaGetErrorString((cudaError_t)rc));

@@ -1,30 +1,39 @@
-// NVFP4 weight-streaming GEMV: E2M1 weights x E2M1 activations, one unsigned E4M3 scale per 16 values on both
-// operands, through tcgen05.mma.kind::mxf4nvf4.block_scale (16-value blocks); the weights' f32 tensor scale is
-// applied to a task's f32 sum in the epilogue.  The format of MiniMax-M3.1-Flash's experts, which the reference
-// leaves to SGLang's MoE runner (minimax_m31/spec.py:117-121); task list, outputs and job modes are those of the
-// MXFP4 kernel (gemv_tc4bs.cu; expert stages of glm53_flash/gfx950/kernel.py:4025-4392).
+// 4-bit weight-streaming GEMV on the block-scaled tensor-core kinds, one kernel body for two formats:
 //
-// Operands.  Both operands of this MMA kind are packed 4-bit values, K-major, 64 values (32 bytes) per MMA.  A
-// 128-byte-wide box of packed bytes is therefore an operand tile as TMA delivers it (128-byte swizzle): 128 weight
-// rows x 256 k, four MMAs.  Nothing is unpacked or spread: the staging ring holds nothing but HBM bytes
-// (9 slots x 18 KB of weights and their scales in flight per SM), and a slot is free again when the MMAs that read
-// it are done.
+//   NVFP4  E2M1 weights x E2M1 activations, one unsigned E4M3 scale per 16 values on both operands, through
+//          tcgen05.mma.kind::mxf4nvf4.block_scale (16-value blocks, K = 64 per MMA); the weights' f32 tensor scale is
+//          applied to a task's f32 sum in the epilogue.  The format of MiniMax-M3.1-Flash's experts, which the
+//          reference leaves to SGLang's MoE runner (minimax_m31/spec.py:117-121).
+//   MXFP4  E2M1 weights x E4M3 activations, one E8M0 code per 32 values on both operands, through
+//          tcgen05.mma.kind::mxf8f6f4.block_scale (K = 32 per MMA): the reference's W4A8 expert arithmetic
+//          (minimax_m3/gfx950/post_attn.py:1304-1314, glm53_flash/gfx950/kernel.py:4025-4392; E8M0 rule
+//          common/mx.py:27-39).  Same sums as gemv_tc4bs.cu, which this kernel replaces where the weight's scale
+//          codes have been repacked (mono_gemv_job.wscale_t).
 //
-// Scale factors.  An MMA reads 4 scale bytes per row (its four 16-value blocks) from 4 TMEM columns per operand:
-// row r's bytes are column r / 32 of lane r % 32.  tcgen05.cp (32 lanes x 128 bits, repeated for the four lane
-// quarters) brings them from a 512-byte block of shared memory laid out as bytes [(r % 32) * 16 + (r / 32) * 4 +
-// block].  The weights' scale bytes are stored in that order (mono_gemv_job.wscale_tiled, a one-time repack when
-// the weight is bound): the 2 KB of a (row block, 256-k unit) arrive by one bulk copy beside the unit's weights.
-// (Gathered from row-major rows by warps of the kernel, a segment's bytes took 2.2 - 2.8 us under load, as long
-// as its MMAs, and the slots they needed left room for 7 ring stages only: 3.9 TB/s.)  The activations' bytes
-// (16 rows: the first 16 lanes of column 0, so their blocks overlap, 256 bytes apart) are gathered by four scale
-// warps, segment by segment in turn, each into a slot of its own, up to four segments ahead of the MMA threads.  Every scale byte the MMA can see is a valid
-// E4M3 number from the start (0x38 = 1.0).
+// Task list, outputs and job modes are those of the other GEMV kernels.
 //
-// Issue rate.  Per 16 KB of weights: four MMAs and eight scale copies, about 70 cycles each for the issuing thread.
-// Two threads of two warps issue in turn, unit by unit, each into an accumulator of its own; the epilogue adds
-// the two.  The issuing threads do not walk the task list (a single thread needs about 1 us for the divisions and
-// address arithmetic of a segment): the scale warp leaves each segment's unit count in its slot.
+// Operands.  A unit is one TMA box of weights: 128 rows x 16 KB of shared memory.  NVFP4: both operands of the MMA
+// are packed 4-bit values, 64 per MMA, so a 128-byte-wide box of packed bytes (256 k values) is the operand as TMA
+// delivers it (128-byte swizzle) and the ring holds nothing but HBM bytes.  MXFP4 next to 8-bit activations: the MMA
+// reads 4-bit values padded to 16 per 16 bytes, and TMA writes that form itself from a tensor map of 4-bit elements
+// (128 k values per box, 8 KB fetched for 16 KB written): no warp touches the nibbles, but a ring slot holds half as
+// many HBM bytes.  The ring's slots (9 or 10) are free again when the MMAs that read them are done.
+//
+// Scale factors.  An MMA reads 4 scale bytes per row from 4 TMEM columns per operand: row r's bytes are column r / 32
+// of lane r % 32 (NVFP4: the four 16-value blocks of the MMA; MXFP4: the four 32-value groups of the unit, one per
+// MMA, picked by the instruction descriptor).  tcgen05.cp (32 lanes x 128 bits, repeated for the four lane quarters)
+// brings them from a 512-byte block of shared memory laid out as bytes [(r % 32) * 16 + (r / 32) * 4 + block].  The
+// weights' scale bytes are stored in that order (mono_gemv_job.wscale_t, a one-time repack when the weight is
+// bound): those of a (row block, unit) arrive by one bulk copy beside the unit's weights.  (Gathered from row-major
+// rows by warps of the kernel, a segment's bytes took 2.2 - 2.8 us under load, as long as its MMAs.)  The
+// activations' bytes (16 rows: the first 16 lanes of column 0, so their blocks overlap, 256 bytes apart) are gathered
+// by four scale warps, segment by segment in turn, each into a slot of its own, up to four segments ahead of the MMA
+// threads.  Every scale byte the MMA can see is a valid number from the start (1.0).
+//
+// Issue rate.  Per unit: four MMAs and two (MXFP4) or eight (NVFP4) scale copies, about 70 cycles each for the
+// issuing thread.  Two threads of two warps issue in turn, unit by unit, each into an accumulator of its own; the
+// epilogue adds the two.  The issuing threads do not walk the task list (a single thread needs about 1 us for the
+// divisions and address arithmetic of a segment): the scale warps leave each segment's unit count in its slot.
 //
 // 352 threads: warp 0 TMA, one thread each of warps 1 and 7 issues tcgen05.cp + MMA, warps 2..5 own the 128 TMEM
 // lanes (epilogue), warps 6, 8, 9, 10 stage the activations' scale bytes.  Every wait is bounded; TMEM is freed on every
@@ -37,23 +46,34 @@ namespace mono {
 namespace nvf4 {
 
 constexpr int kThreads = 352;
-constexpr int kStages = 9;
-constexpr int kPackBytes = 128 * 128;   // a unit of weights: 128 rows x 128 bytes = 256 k values per row
+constexpr int kPackBytes = 128 * 128;   // a unit of weights in shared memory: 128 rows x 128 bytes
 constexpr int kBBytes = 16 * 128;       // the unit's activations: 16 rows x 128 bytes
-constexpr int kMmas = 4;                // MMAs per unit (64 k values each)
-constexpr int kSfBlock = 512;           // scale bytes of one MMA in the order tcgen05.cp wants
-constexpr int kSfaUnit = kMmas * kSfBlock;  // the unit's weight scales
-constexpr int kStageBytes = kPackBytes + kBBytes + kSfaUnit;
-constexpr int kMaxSegUnits = 8;         // units (256 k values) per segment
+constexpr int kMmas = 4;                // MMAs per unit
+constexpr int kSfBlock = 512;           // scale bytes in the order tcgen05.cp wants: 128 rows x 4
 constexpr int kScWarps = 4;             // scale warps: warp i takes segments i, i + 4, ...
 constexpr int kScSlots = kScWarps;      // ... into a slot of its own (one writer per slot: its uses follow one another)
 constexpr int kSfbStep = 256;           // activations: blocks half a block apart
-constexpr int kSfbBytes = kMaxSegUnits * kMmas * kSfbStep + kSfBlock / 2;
-constexpr int kSlotBytes = kSfbBytes + 128;  // + 16 route coefficients, the tensor scale and the unit count
 constexpr int kAccCols = 16;            // one accumulator: 16 columns (the step's rows); [2 segments in turn][2 issuers]
 constexpr int kSfCol = 4 * kAccCols;    // per issuer 64 columns: [2 units in turn][4 MMAs][weights 4 | activations 4 ... ]
 constexpr int kTmemCols = 256;
-constexpr uint32_t kOne4 = 0x38383838u; // four E4M3 bytes of 1.0
+
+// What differs between the two formats
+template <bool NV>
+struct Fmt {
+    static constexpr int kUnitK = NV ? 256 : 128;             // k values per unit
+    static constexpr int kSfaUnit = NV ? kMmas * kSfBlock : kSfBlock;  // weight scale bytes per (row block, unit)
+    static constexpr int kSfbPerUnit = NV ? kMmas : 1;        // activation scale blocks per unit
+    static constexpr int kAscBytes = NV ? 16 : 4;             // activation scale bytes per row and unit
+    static constexpr int kTxBytes = (NV ? kPackBytes : kPackBytes / 2) + kBBytes + kSfaUnit;  // bytes TMA fetches per unit
+    static constexpr int kStageBytes = (kPackBytes + kBBytes + kSfaUnit + 1023) & ~1023;
+    static constexpr int kStages = NV ? 9 : 10;
+    static constexpr int kMaxSegUnits = NV ? 8 : 16;          // 2048 k values per segment
+    static constexpr int kSfbBytes = kMaxSegUnits * kSfbPerUnit * kSfbStep + kSfBlock / 2;
+    static constexpr int kSlotBytes = kSfbBytes + 128;        // + 16 route coefficients, the tensor scale and the unit count
+    static constexpr int kAloneUnits = NV ? 2 : 4;            // a segment of so few units has one issuing thread
+    static constexpr uint32_t kOne4 = NV ? 0x38383838u : 0x7F7F7F7Fu;  // four scale bytes of 1.0 (E4M3 / E8M0)
+    static constexpr size_t kSmem = 1024 + (size_t)kStages * kStageBytes + (size_t)kScSlots * kSlotBytes + 512;
+};
 
 struct Params {
     mono_gemv_args a;
@@ -68,7 +88,7 @@ MONO_TL_DECLARE(tl_nv)
 #endif
 
 struct Seg {
-    int c2, row0, t0, nt, aset;  // t0, nt in units of 256 k values
+    int c2, row0, t0, nt, aset;  // t0, nt in units
     const uint8_t* asc;
     const uint8_t* wsc;
     const float* coef;
@@ -89,21 +109,27 @@ struct TaskC {
     const int32_t* expert_list;
 };
 
+// units of the job's K: NVFP4 counts k_tiles in units; MXFP4 in 128-byte tiles of nibbles = two units
+template <bool NV>
+__device__ __forceinline__ int units_of(const mono_gemv_job& j) { return NV ? j.k_tiles : (j.k_tiles4 > 0 ? j.k_tiles4 : 2 * j.k_tiles); }
+
+template <bool NV>
 __device__ __forceinline__ TaskC make_task(const mono_gemv_job& j, int rb, int ks) {
     TaskC t;
     t.mode = j.mode;
     t.row0 = j.row_off + rb * 128;
+    const int total = units_of<NV>(j), per_split = (NV ? 1 : 2) * j.split_tiles;
     if (j.mode == MONO_JOB_EXPERT_DOWN) {
         t.t0 = 0;
-        t.nt = j.k_tiles;
+        t.nt = total;
     } else {
-        t.t0 = ks * j.split_tiles;
-        t.nt = min(j.split_tiles, j.k_tiles - t.t0);
+        t.t0 = ks * per_split;
+        t.nt = min(per_split, total - t.t0);
     }
-    t.asc0 = j.ascale_e8 + (size_t)t.t0 * 16;
-    t.wsc0 = j.wscale_e8 + (size_t)(t.row0 >> 7) * j.wscale_ld + (size_t)t.t0 * kSfaUnit;
+    t.asc0 = j.ascale_e8 + (size_t)t.t0 * Fmt<NV>::kAscBytes;
+    t.wsc0 = j.wscale_t + (size_t)(t.row0 >> 7) * j.wscale_t_ld + (size_t)t.t0 * Fmt<NV>::kSfaUnit;
     t.a_stride = j.ascale_seg_stride;
-    t.w_stride = j.wscale_mat_stride;
+    t.w_stride = j.wscale_t_mat_stride;
     t.coef = j.coef;
     t.wglobal = j.wglobal;
     t.expert_list = j.expert_list;
@@ -151,6 +177,14 @@ __device__ __forceinline__ void mma_nvf4(uint32_t tmem_d, uint64_t adesc, uint64
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
         : "memory");
 }
+__device__ __forceinline__ void mma_mxf4(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+}
 // 32 TMEM columns (both issuers' accumulators of a segment) of this thread's lane
 __device__ __forceinline__ void ld32(uint32_t taddr, uint32_t r[32]) {
     asm volatile(
@@ -175,9 +209,19 @@ __device__ __forceinline__ uint64_t desc_sf(uint32_t saddr) {
 // Block-scaled descriptor: A and B E2M1 (format 1 of this kind), both K-major, N = 16, unsigned E4M3 scales
 // (scale-format bit 23 clear), M = 128; all four scale bytes of a column are used (scale ids 0)
 constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | (0u << 23) | ((128u >> 4) << 24);
+// MXFP4 x MXFP8: A E2M1 (format 5 of this kind), B E4M3 (format 0), E8M0 scales, N = 16, M = 128; group g of the
+// unit: byte g of the scale columns for both operands
+__device__ __forceinline__ uint32_t idesc_group(uint32_t g) {
+    return (g << 4) | (5u << 7) | (0u << 10) | ((16u >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24) | (g << 29);
+}
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-__global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_constant__ Params p) {
+template <bool NV>
+__device__ __forceinline__ void gemv_fp4_body(const Params& p) {
+    using F = Fmt<NV>;
+    constexpr int kStages = F::kStages, kStageBytes = F::kStageBytes, kSlotBytes = F::kSlotBytes, kSfbBytes = F::kSfbBytes;
+    constexpr int kSfaUnit = F::kSfaUnit, kMaxSegUnits = F::kMaxSegUnits, kSfbPerUnit = F::kSfbPerUnit;
+    constexpr uint32_t kOne4 = F::kOne4;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* ring = smem;                                    // kStages slots: weights, then activations
@@ -254,7 +298,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_con
         const int u_up = u, rb = local % nrb, ks = local / nrb;                                                 \
         if (jb.mode == MONO_JOB_EXPERT_DOWN) nseg = (nexp[j] > ks) ? (nexp[j] - ks + jb.nsplit - 1) / jb.nsplit : 0; \
         (void)u_up; (void)rb;                                                                                   \
-        const TaskC tc = make_task(jb, rb, ks);                                                                 \
+        const TaskC tc = make_task<NV>(jb, rb, ks);                                                             \
         const int u_step = jb.nsplit;                                                                           \
         TASK_BEGIN                                                                                              \
         for (int sgi = 0; sgi < nseg && !*abortp; ++sgi) {                                                      \
@@ -274,15 +318,20 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_con
 #define TASK_BEGIN
 #define TASK_END
             NV_FOR_EACH_SEGMENT({
-                const CUtensorMap* wmap = reinterpret_cast<const CUtensorMap*>(&jb.tmap);  // bytes: 128 per box row = 256 values
+                // NVFP4: the weight as bytes, 128 per box row = 256 values; MXFP4: as 4-bit elements, 128 per box row,
+                // which TMA pads to 128 bytes.  The box's first coordinate is unit * 128 in both (bytes / elements).
+                const CUtensorMap* wmap = reinterpret_cast<const CUtensorMap*>(NV ? &jb.tmap : &jb.tmap4);
                 const CUtensorMap* amap = reinterpret_cast<const CUtensorMap*>(&jb.act_tmap);
+                // (L2 prefetch requests for a segment's later boxes, issued here before its first copy, made both
+                // formats slower: 77.6 -> 87.3 us and 51.4 -> 56.7 us for the config-4 up/gate launch; the copies
+                // themselves start later by the time this thread spends on the requests.)
                 for (int t = 0; t < s.nt; ++t) {
                     NV_TL(0, tl_n);
                     if (!mbar_wait(&stage_free[stage], phase ^ 1, abortp, wait_ns)) break;
                     NV_TL(1, tl_n);
                     uint8_t* st = ring + (size_t)stage * kStageBytes;
                     // (a box that reaches past K reads zeros there and still counts its full size)
-                    mbar_expect_tx(&full[stage], kStageBytes);
+                    mbar_expect_tx(&full[stage], F::kTxBytes);
                     tma_load_3d(st, wmap, (s.t0 + t) * 128, s.row0, s.c2, &full[stage]);
                     tma_load_3d(st + kPackBytes, amap, (s.t0 + t) * 128, 0, s.aset, &full[stage]);
                     bulk_load(st + kPackBytes + kBBytes, s.wsc + (size_t)t * kSfaUnit, kSfaUnit, &full[stage]);
@@ -316,7 +365,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_con
                 mbar_arrive(&sc_empty[slot]);  // this thread has read the slot's words (its copies: see sc_empty)
                 const int buf = seg_no & 1;
                 const uint32_t aphase = (uint32_t)(seg_no >> 1) & 1u;
-                const bool alone = nt <= 2;  // the segment has one owner: issuer `buf`
+                const bool alone = nt <= F::kAloneUnits;  // the segment has one owner: issuer `buf`
                 if (me == 0) NV_TL(13, n0);
                 // (every issuer waits for every buffer turn, owner or not: the parities of a barrier it skipped
                 // for two turns would no longer tell it anything)
@@ -344,15 +393,26 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_con
                         const uint32_t set = tmem_base + kSfCol + me * 64 + (mine & 1) * 32;
                         ++mine;
                         const int nm = t == nt - 1 ? nm_last : kMmas;  // K may end inside the segment's last unit
+                        if (NV) {
 #pragma unroll
-                        for (int m = 0; m < kMmas; ++m) {  // 64 values per MMA, 32 bytes further along K
-                            if (m >= nm) break;
-                            const int blk = t * kMmas + m;
-                            const uint32_t sfa = set + m * 8, sfb = sfa + 4;
-                            cp_sf(sfa, desc_sf(sa + kPackBytes + kBBytes + m * kSfBlock));
-                            cp_sf(sfb, desc_sf(sl + blk * kSfbStep));
-                            mma_nvf4(acc, adesc + 2 * m, bdesc + 2 * m, kIdesc, sfa, sfb, accumulate);
-                            accumulate = 1;
+                            for (int m = 0; m < kMmas; ++m) {  // 64 values per MMA, 32 bytes further along K
+                                if (m >= nm) break;
+                                const int blk = t * kMmas + m;
+                                const uint32_t sfa = set + m * 8, sfb = sfa + 4;
+                                cp_sf(sfa, desc_sf(sa + kPackBytes + kBBytes + m * kSfBlock));
+                                cp_sf(sfb, desc_sf(sl + blk * kSfbStep));
+                                mma_nvf4(acc, adesc + 2 * m, bdesc + 2 * m, kIdesc, sfa, sfb, accumulate);
+                                accumulate = 1;
+                            }
+                        } else {
+                            const uint32_t sfa = set, sfb = set + 4;
+                            cp_sf(sfa, desc_sf(sa + kPackBytes + kBBytes));
+                            cp_sf(sfb, desc_sf(sl + t * kSfbStep));
+#pragma unroll
+                            for (uint32_t g = 0; g < (uint32_t)kMmas; ++g) {  // one 32-value group per MMA, 32 bytes further along K
+                                mma_mxf4(acc, adesc + 2 * g, bdesc + 2 * g, idesc_group(g), sfa, sfb, accumulate);
+                                accumulate = 1;
+                            }
                         }
                         commit(&stage_free[st_now]);
                         NV_TL(5, n);
@@ -391,7 +451,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_con
             if (tid == 64) NV_TL(11, n);
             // whose accumulators hold this segment: its owner's (one or two units), else both issuers'
             const int buf = seg_no & 1;
-            const bool alone = s.nt <= 2, w0 = !alone || buf == 0, w1 = !alone || buf == 1;
+            const bool alone = s.nt <= F::kAloneUnits, w0 = !alone || buf == 0, w1 = !alone || buf == 1;
             ++seg_no;
             bool got = true;
             if (w0) { got = mbar_wait(&acc_full[buf * 2], (fphase >> (buf * 2)) & 1u, abortp, wait_ns); fphase ^= 1u << (buf * 2); }
@@ -445,22 +505,27 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_con
             // 1.0); lanes 0..15 take the even units, 16..31 the odd ones; every load is issued before the first store
             const int c = lane & 15;
             const uint8_t* arow = s.asc + (size_t)min(c, rows - 1) * jb.ascale_ld;
-            uint4 a4[kMaxSegUnits / 2];
+            uint32_t a4[kMaxSegUnits / 2][kSfbPerUnit];  // NVFP4: a row's 16 bytes of a unit; MXFP4: its 4
 #pragma unroll
-            for (int k = 0; k < kMaxSegUnits / 2; ++k)
-                a4[k] = __ldg(reinterpret_cast<const uint4*>(arow + min((lane >> 4) + 2 * k, s.nt - 1) * 16));
+            for (int k = 0; k < kMaxSegUnits / 2; ++k) {
+                const uint8_t* src = arow + min((lane >> 4) + 2 * k, s.nt - 1) * F::kAscBytes;
+                if (NV) {
+                    const uint4 v = __ldg(reinterpret_cast<const uint4*>(src));
+                    a4[k][0] = v.x; a4[k][kSfbPerUnit > 1 ? 1 : 0] = v.y; a4[k][kSfbPerUnit > 2 ? 2 : 0] = v.z; a4[k][kSfbPerUnit > 3 ? 3 : 0] = v.w;
+                } else {
+                    a4[k][0] = __ldg(reinterpret_cast<const uint32_t*>(src));
+                }
+            }
             float cf_v = 1.f;
             if (s.coef && lane < rows) cf_v = __ldg(s.coef + lane);
 #pragma unroll
             for (int k = 0; k < kMaxSegUnits / 2; ++k) {
                 const int t = (lane >> 4) + 2 * k;
                 if (t < s.nt) {
-                    uint8_t* blk = sl + (size_t)t * kMmas * kSfbStep + c * 16;
+                    uint8_t* blk = sl + (size_t)t * kSfbPerUnit * kSfbStep + c * 16;
                     const bool live = c < rows;
-                    *reinterpret_cast<uint32_t*>(blk + 0 * kSfbStep) = live ? a4[k].x : kOne4;
-                    *reinterpret_cast<uint32_t*>(blk + 1 * kSfbStep) = live ? a4[k].y : kOne4;
-                    *reinterpret_cast<uint32_t*>(blk + 2 * kSfbStep) = live ? a4[k].z : kOne4;
-                    *reinterpret_cast<uint32_t*>(blk + 3 * kSfbStep) = live ? a4[k].w : kOne4;
+#pragma unroll
+                    for (int m = 0; m < kSfbPerUnit; ++m) *reinterpret_cast<uint32_t*>(blk + m * kSfbStep) = live ? a4[k][m] : kOne4;
                 }
             }
             {
@@ -468,8 +533,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_con
                 if (lane < kMaxRows) cf[lane] = cf_v;
                 if (lane == kMaxRows) cf[lane] = s.gp ? __ldg(s.gp) : 1.f;
                 if (lane == kMaxRows + 1) {  // for the issuing threads: units, and the MMAs of the last unit (K may end inside it)
-                    const int k_mmas = jb.k_tiles4 > 0 ? jb.k_tiles4 : jb.k_tiles * kMmas;
-                    reinterpret_cast<int*>(cf)[lane] = s.nt | (max(1, min(kMmas, k_mmas - (s.t0 + s.nt - 1) * kMmas)) << 8);
+                    int nm_last = kMmas;
+                    if (NV) {
+                        const int k_mmas = jb.k_tiles4 > 0 ? jb.k_tiles4 : jb.k_tiles * kMmas;
+                        nm_last = max(1, min(kMmas, k_mmas - (s.t0 + s.nt - 1) * kMmas));
+                    }
+                    reinterpret_cast<int*>(cf)[lane] = s.nt | (nm_last << 8);
                 }
             }
             fence_proxy_async_smem();  // the copies to TMEM read these bytes through the async proxy
@@ -507,11 +576,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_con
     }
 }
 
+__global__ void __launch_bounds__(kThreads, 1) gemv_nvf4_kernel(const __grid_constant__ Params p) { gemv_fp4_body<true>(p); }
+__global__ void __launch_bounds__(kThreads, 1) gemv_mxf4_kernel(const __grid_constant__ Params p) { gemv_fp4_body<false>(p); }
+
 }  // namespace nvf4
 }  // namespace mono
 
-// Launches the NVFP4 kernel for an argument block that mono_gemv_launch has validated.  Returns -100 when the
-// block does not have what this kernel needs (there is no other consumer of the format).
 #ifdef MONO_TIMELINE
 extern "C" int mono_timeline_read_nvf4(unsigned long long* out, int* ctas, int* points) {
     *ctas = MONO_TL_CTAS;
@@ -520,35 +590,44 @@ extern "C" int mono_timeline_read_nvf4(unsigned long long* out, int* ctas, int* 
 }
 #endif
 
-int mono_gemv_nvf4_launch(const mono_gemv_args* a, long tasks, cudaStream_t st) {
+// Launches the kernel for an argument block that mono_gemv_launch has validated (wkind MONO_W_NVFP4 or MONO_W_MXFP4).
+// Returns -100 when the block does not have what this kernel needs.
+template <bool NV>
+static int fp4_launch(const mono_gemv_args* a, long tasks, cudaStream_t st) {
     using namespace mono;
+    using F = nvf4::Fmt<NV>;
     for (int j = 0; j < a->njobs; ++j) {
         const mono_gemv_job& jb = a->job[j];
         const unsigned long long* wa = reinterpret_cast<const unsigned long long*>(&jb.act_tmap);
-        const unsigned long long* wb = reinterpret_cast<const unsigned long long*>(&jb.tmap);
+        const unsigned long long* wb = reinterpret_cast<const unsigned long long*>(NV ? &jb.tmap : &jb.tmap4);
         unsigned long long anya = 0, anyb = 0;
         for (int i = 0; i < 16; ++i) { anya |= wa[i]; anyb |= wb[i]; }
-        const int seg = jb.mode == MONO_JOB_EXPERT_DOWN ? jb.k_tiles : (jb.split_tiles < jb.k_tiles ? jb.split_tiles : jb.k_tiles);
-        if (!anya || !anyb || jb.planes != 1 || jb.rb_per_mat != 0 || seg > nvf4::kMaxSegUnits || jb.feeds_job ||
-            !jb.wscale_tiled || (jb.row_off & 127) || (jb.wscale_ld & 15) || (jb.ascale_ld & 15) ||
-            (reinterpret_cast<uintptr_t>(jb.wscale_e8) & 15) || (reinterpret_cast<uintptr_t>(jb.ascale_e8) & 15) ||
-            (jb.wscale_mat_stride & 15) || (jb.ascale_seg_stride & 15) ||
-            (long)jb.wscale_ld < (long)jb.k_tiles * nvf4::kSfaUnit || (long)jb.ascale_ld < (long)jb.k_tiles * 16 ||
-            jb.wscale_mat_stride < (long)((jb.row_off + jb.n_rows + 127) / 128) * jb.wscale_ld)
+        const int units = NV ? jb.k_tiles : (jb.k_tiles4 > 0 ? jb.k_tiles4 : 2 * jb.k_tiles);
+        const int per_split = (NV ? 1 : 2) * jb.split_tiles;
+        const int seg = jb.mode == MONO_JOB_EXPERT_DOWN ? units : (per_split < units ? per_split : units);
+        if (!anya || !anyb || jb.planes != 1 || jb.rb_per_mat != 0 || seg > F::kMaxSegUnits || jb.feeds_job || (!NV && !jb.act_natural) ||
+            !jb.wscale_t || (jb.row_off & 127) || (jb.wscale_t_ld & 15) || (jb.ascale_ld & 3) ||
+            (reinterpret_cast<uintptr_t>(jb.wscale_t) & 15) || (reinterpret_cast<uintptr_t>(jb.ascale_e8) & 15) ||
+            (jb.wscale_t_mat_stride & 15) || (jb.ascale_seg_stride & 15) || (NV && (jb.ascale_ld & 15)) ||
+            (long)jb.wscale_t_ld < (long)units * F::kSfaUnit || (long)jb.ascale_ld < (long)units * F::kAscBytes ||
+            jb.wscale_t_mat_stride < (long)((jb.row_off + jb.n_rows + 127) / 128) * jb.wscale_t_ld)
             return -100;
     }
     nvf4::Params p;
     p.a = *a;
-    const size_t smem = 1024 + (size_t)nvf4::kStages * nvf4::kStageBytes + (size_t)nvf4::kScSlots * nvf4::kSlotBytes + 512;
-    static std::atomic<uint64_t> attr_once{0};  // bit d: set on device d
+    auto kernel = NV ? nvf4::gemv_nvf4_kernel : nvf4::gemv_mxf4_kernel;
+    static std::atomic<uint64_t> attr_once{0};  // bit d: set on device d (one instance of this function per format)
     if (mono::attr_needed(attr_once)) {
-        cudaError_t e = cudaFuncSetAttribute(nvf4::gemv_nvf4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)F::kSmem);
         if (e != cudaSuccess) return (int)e;
         mono::attr_done(attr_once);
     }
     int grid = a->max_ctas > 0 ? a->max_ctas : mono_sm_count();
     if (grid > tasks) grid = (int)tasks;
     if (grid < 1) grid = 1;
-    cudaError_t e = launch_k(nvf4::gemv_nvf4_kernel, grid, nvf4::kThreads, smem, st, p);
+    cudaError_t e = launch_k(kernel, grid, nvf4::kThreads, F::kSmem, st, p);
     return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
+
+int mono_gemv_nvf4_launch(const mono_gemv_args* a, long tasks, cudaStream_t st) { return fp4_launch<true>(a, tasks, st); }
+int mono_gemv_mxf4_launch(const mono_gemv_args* a, long tasks, cudaStream_t st) { return fp4_launch<false>(a, tasks, st); }

@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import ctypes as C
 import logging
+import os
 
 import torch
 
@@ -140,6 +141,19 @@ def tile_nvfp4_scales(ws: torch.Tensor) -> torch.Tensor:
     return t.view(mats, rp // 128, (kp // 16) * 2048)
 
 
+def tile_mxfp4_scales(ws: torch.Tensor) -> torch.Tensor:
+    """MXFP4 scale codes [mats, rows, K/32] -> [mats, row blocks, tiles * 512] (``mono_gemv_job.wscale_t``): per
+    (128-row block, 128-value tile) one 512-byte block, byte ``(r % 32) * 16 + (r // 32) * 4 + g`` = row ``r`` of the
+    block, 32-value group ``g`` of the tile.  Rows and tiles are padded with 127 (2^0)."""
+    mats, rows, kb = ws.shape
+    rp, kp = _up(rows, 128), _up(kb, 4)
+    pad = torch.full((mats, rp, kp), 127, dtype=torch.uint8, device=ws.device)
+    pad[:, :rows, :kb] = ws
+    # [mat, row block, r // 32, r % 32, tile, group] -> [mat, row block, tile, r % 32, r // 32, group]
+    t = pad.view(mats, rp // 128, 4, 32, kp // 4, 4).permute(0, 1, 4, 3, 2, 5).contiguous()
+    return t.view(mats, rp // 128, (kp // 4) * 512)
+
+
 def fp4_tma_ok(w: torch.Tensor) -> bool:
     """Whether a packed-nibble weight [..., N, K/2] can be read as a 4-bit tensor by TMA: K a multiple of
     128, rows a multiple of 32 bytes apart, base 32-byte aligned."""
@@ -241,8 +255,8 @@ class Gemv:
             self._keep.append(tiled)
             if self.copies is not None:
                 self.copies["NVFP4 scale bytes in tensor-core order", self.copy_tag, name] = tiled
-            job.wscale_e8, job.wscale_mat_stride, job.wscale_ld = tiled.data_ptr(), tiled.shape[1] * tiled.shape[2], tiled.shape[2]
-            job.wscale_tiled = 1
+            job.wscale_e8, job.wscale_mat_stride, job.wscale_ld = ws.data_ptr(), ws3.shape[1] * ws3.shape[2], ws3.shape[2]
+            job.wscale_t, job.wscale_t_mat_stride, job.wscale_t_ld = tiled.data_ptr(), tiled.shape[1] * tiled.shape[2], tiled.shape[2]
             job.k_tiles4 = -(-kb // 32)  # K in 64-value MMAs: the kernel skips the MMAs past K in the last tile
             if row_off % 128:
                 raise ValueError(f"{name}: an NVFP4 job starts at a multiple of 128 rows")
@@ -283,6 +297,18 @@ class Gemv:
             L.check(L.load().mono_tmap_encode_fp4(C.byref(job.tmap4), w.data_ptr(), 2 * kb, rows_total, mats, kb, rows_total * kb),
                     f"mono_tmap_encode_fp4({name})")
             job.k_tiles4 = (2 * kb) // 128
+            if row_off % 128 == 0 and os.environ.get("MONO_MXFP4_TILED_SCALES", "1") != "0":
+                # the scale codes once more in the order the tensor core copies them: a tile's 512 bytes then arrive by
+                # one bulk copy beside its weights (one-time repack, recorded like the reference's:
+                # glm53/gfx950/weights.py:207-310)
+                ws3 = ws if ws.dim() == 3 else ws.unsqueeze(0)
+                tiled = tile_mxfp4_scales(ws3[..., : -(-(2 * kb) // 32)])
+                log.info("%s.scale: %s -> tiled %s (one-time repack, %d bytes)", name, tuple(ws3.shape), tuple(tiled.shape),
+                         tiled.numel())
+                self._keep.append(tiled)
+                if self.copies is not None:
+                    self.copies["MXFP4 scale codes in tensor-core order", self.copy_tag, name] = tiled
+                job.wscale_t, job.wscale_t_mat_stride, job.wscale_t_ld = tiled.data_ptr(), tiled.shape[1] * tiled.shape[2], tiled.shape[2]
         self._keep += [w, wscale, act, out, expert_list, n_expert, coef]
         self.args.njobs = j + 1
         return job.nsplit

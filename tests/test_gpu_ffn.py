@@ -103,14 +103,17 @@ def test_tcgen05_and_warp_mma_paths_agree(rows):
     assert float((d > 0).float().mean()) < 0.05, "only rare last-bit differences are expected"
 
 
+@pytest.mark.parametrize("mode", ["2", "1"])
 @pytest.mark.parametrize("cfg,rows", [(CFG_FFN_MXFP4, 4), (CFG_TINY_FFN_384, 5), (CFG_TINY_FFN_384, 16)])
-def test_block_scaled_mxfp4_agrees_with_the_group_kernel(cfg, rows, monkeypatch):
-    """MXFP4 experts on tcgen05 in two ways: kind::mxf8f6f4.block_scale (the MMA reads both operands' E8M0 codes from
-    tensor memory and adds a task's whole K run in one accumulator) and kind::f8f6f4 per 32-value group with the
-    codes applied in the epilogue in f32.  Same bytes, same exact products; the block-scaled sum is formed inside
-    the tensor core instead of group by group in f32, so the partial sums agree to f32 rounding of a K-long sum:
-    |difference| <= 2^-18 x (largest partial sum of the launch), and the block's bf16 output to one ulp."""
-    monkeypatch.setenv("MONO_TC4_BLOCK_SCALE", "1")
+def test_block_scaled_mxfp4_agrees_with_the_group_kernel(cfg, rows, mode, monkeypatch):
+    """MXFP4 experts on tcgen05 in three ways: kind::mxf8f6f4.block_scale (the MMA reads both operands' E8M0 codes from
+    tensor memory and adds a task's whole K run in one accumulator) with the nibbles padded by TMA and the weights'
+    codes fetched in tensor-core order (mode 2, the default) or spread and gathered by warps of the kernel (mode 1),
+    and kind::f8f6f4 per 32-value group with the codes applied in the epilogue in f32 (mode 0).  Same bytes, same
+    exact products; the block-scaled sum is formed inside the tensor core instead of group by group in f32, so the
+    partial sums agree to f32 rounding of a K-long sum: |difference| <= 2^-18 x (largest partial sum of the launch),
+    and the block's bf16 output to one ulp."""
+    monkeypatch.setenv("MONO_TC4_BLOCK_SCALE", mode)
     ffn, w, x, slots, out_bs = _run(cfg, rows)
     n = int(ffn.n_expert.item())
     up_bs, dn_bs = ffn.up_r[: n * ffn.ns_up].float().cpu().clone(), ffn.down_p.float().cpu().clone()

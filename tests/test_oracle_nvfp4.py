@@ -142,3 +142,21 @@ def test_scale_bytes_in_tensor_core_order():
     # every source byte appears exactly once
     assert int((t != 0x38).sum()) <= mats * rows * kb
     assert sorted(t[t != 0x38].tolist()) == sorted(ws[ws != 0x38].tolist())
+
+
+def test_mxfp4_scale_codes_in_tensor_core_order():
+    """The same repack for MXFP4 codes: one 512-byte block per (128-row block, 128-value tile), byte
+    (r % 32) * 16 + (r // 32) * 4 + g = row r, 32-value group g; padding holds the code of 2^0."""
+    from sgl_amd_mono_b200 import ops
+
+    g = torch.Generator().manual_seed(12)
+    mats, rows, kb = 3, 130, 14  # K = 448: three and a half tiles
+    ws = torch.randint(100, 126, (mats, rows, kb), generator=g, dtype=torch.uint8)
+    t = ops.tile_mxfp4_scales(ws)
+    assert t.shape == (mats, 2, 4 * 512)
+    for mat, r, k32 in [(0, 0, 0), (2, 37, 5), (1, 129, 13), (0, 127, 12), (2, 64, 3)]:
+        rb, rr = divmod(r, 128)
+        tile, grp = divmod(k32, 4)
+        assert int(t[mat, rb, tile * 512 + (rr % 32) * 16 + (rr // 32) * 4 + grp]) == int(ws[mat, r, k32]), (mat, r, k32)
+    assert int(t[0, 1, 2 * 16]) == 127 and int(t[0, 0, 3 * 512 + 2]) == 127  # a row past the matrix; a group past K
+    assert sorted(t[t != 127].tolist()) == sorted(ws.flatten().tolist())
