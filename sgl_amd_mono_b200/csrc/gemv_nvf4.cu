@@ -17,7 +17,7 @@
 // delivers it (128-byte swizzle) and the ring holds nothing but HBM bytes.  MXFP4 next to 8-bit activations: the MMA
 // reads 4-bit values padded to 16 per 16 bytes, and TMA writes that form itself from a tensor map of 4-bit elements
 // (128 k values per box, 8 KB fetched for 16 KB written): no warp touches the nibbles, but a ring slot holds half as
-// many HBM bytes.  The ring's slots (9 or 10) are free again when the MMAs that read them are done.
+// many HBM bytes.  The ring's slots (8 or 10) are free again when the MMAs that read them are done.
 //
 // Scale factors.  An MMA reads 4 scale bytes per row from 4 TMEM columns per operand: row r's bytes are column r / 32
 // of lane r % 32 (NVFP4: the four 16-value blocks of the MMA; MXFP4: the four 32-value groups of the unit, one per
@@ -35,8 +35,8 @@
 // epilogue adds the two.  The issuing threads do not walk the task list (a single thread needs about 1 us for the
 // divisions and address arithmetic of a segment): the scale warps leave each segment's unit count in its slot.
 //
-// 352 threads: warp 0 TMA, one thread each of warps 1 and 7 issues tcgen05.cp + MMA, warps 2..5 own the 128 TMEM
-// lanes (epilogue), warps 6, 8, 9, 10 stage the activations' scale bytes.  Every wait is bounded; TMEM is freed on every
+// 384 threads: one thread each of warps 0 and 11 issues the TMA copies, one thread each of warps 1 and 7 issues
+// tcgen05.cp + MMA, warps 2..5 own the 128 TMEM lanes (epilogue), warps 6, 8, 9, 10 stage the activations' scale bytes.  Every wait is bounded; TMEM is freed on every
 // exit path.
 #include "mono_common.cuh"
 
@@ -45,7 +45,7 @@ extern void mono_set_error(const char* fmt, ...);
 namespace mono {
 namespace nvf4 {
 
-constexpr int kThreads = 352;
+constexpr int kThreads = 384;
 constexpr int kPackBytes = 128 * 128;   // a unit of weights in shared memory: 128 rows x 128 bytes
 constexpr int kBBytes = 16 * 128;       // the unit's activations: 16 rows x 128 bytes
 constexpr int kMmas = 4;                // MMAs per unit
@@ -66,7 +66,13 @@ struct Fmt {
     static constexpr int kAscBytes = NV ? 16 : 4;             // activation scale bytes per row and unit
     static constexpr int kTxBytes = (NV ? kPackBytes : kPackBytes / 2) + kBBytes + kSfaUnit;  // bytes TMA fetches per unit
     static constexpr int kStageBytes = (kPackBytes + kBBytes + kSfaUnit + 1023) & ~1023;
-    static constexpr int kStages = NV ? 9 : 10;
+    // Two rings of kStages / 2 slots: ring i is filled by producing thread i and read by issuing thread i only, so a
+    // slot's uses follow one another in one thread on either side.  (A waiter only knows a barrier's parity: were a
+    // slot's previous use pending in ANOTHER thread's queue, a barrier two uses behind would look like one that is
+    // ready.)
+    static constexpr int kStages = NV ? 8 : 10;
+    static constexpr int kRing = kStages / 2;
+    static_assert(kStages % 2 == 0, "one ring per issuing thread");
     static constexpr int kMaxSegUnits = NV ? 8 : 16;          // 2048 k values per segment
     static constexpr int kSfbBytes = kMaxSegUnits * kSfbPerUnit * kSfbStep + kSfBlock / 2;
     static constexpr int kSlotBytes = kSfbBytes + 128;        // + 16 route coefficients, the tensor scale and the unit count
@@ -309,12 +315,15 @@ __device__ __forceinline__ void gemv_fp4_body(const Params& p) {
         TASK_END                                                                                                \
     }
 
-    if (warp == 0) {
-        // ------------------------------------------------------------ producer: weight boxes and activation tiles by TMA
+    if (warp == 0 || warp == 11) {
+        // ------------------------------------------------------------ producers: weight boxes, activation tiles and weight
+        // scales by TMA.  One thread needs about 0.3 us for a unit's wait and four instructions, which bounded the
+        // MXFP4 launch (8 KB of HBM bytes per unit) at 3.1 TB/s.  Thread i feeds issuing thread i through ring i: the
+        // units of its parity (launch-wide numbers) of a long segment, every unit of a short segment that is its
+        // issuer's (see the issuers).
         if (lane == 0) {
-            int stage = 0, tl_n = 0;
-            (void)tl_n;
-            uint32_t phase = 0;
+            const int pid = warp == 0 ? 0 : 1;
+            int n = 0, seg_no = 0, mine = 0;  // launch-wide unit and segment numbers; units this thread has copied
 #define TASK_BEGIN
 #define TASK_END
             NV_FOR_EACH_SEGMENT({
@@ -325,20 +334,26 @@ __device__ __forceinline__ void gemv_fp4_body(const Params& p) {
                 // (L2 prefetch requests for a segment's later boxes, issued here before its first copy, made both
                 // formats slower: 77.6 -> 87.3 us and 51.4 -> 56.7 us for the config-4 up/gate launch; the copies
                 // themselves start later by the time this thread spends on the requests.)
-                for (int t = 0; t < s.nt; ++t) {
-                    NV_TL(0, tl_n);
+                const bool alone = s.nt <= F::kAloneUnits;
+                const bool skip = alone && (seg_no & 1) != pid;
+                ++seg_no;
+                for (int t = alone ? 0 : ((n + pid) & 1); t < s.nt && !skip; t += alone ? 1 : 2) {
+                    const int un = n + t, stage = pid * F::kRing + mine % F::kRing;
+                    const uint32_t phase = (uint32_t)(mine / F::kRing) & 1u;
+                    ++mine;
+                    (void)un;
+                    NV_TL(0, un);
                     if (!mbar_wait(&stage_free[stage], phase ^ 1, abortp, wait_ns)) break;
-                    NV_TL(1, tl_n);
+                    NV_TL(1, un);
                     uint8_t* st = ring + (size_t)stage * kStageBytes;
                     // (a box that reaches past K reads zeros there and still counts its full size)
                     mbar_expect_tx(&full[stage], F::kTxBytes);
                     tma_load_3d(st, wmap, (s.t0 + t) * 128, s.row0, s.c2, &full[stage]);
                     tma_load_3d(st + kPackBytes, amap, (s.t0 + t) * 128, 0, s.aset, &full[stage]);
                     bulk_load(st + kPackBytes + kBBytes, s.wsc + (size_t)t * kSfaUnit, kSfaUnit, &full[stage]);
-                    NV_TL(2, tl_n);
-                    ++tl_n;
-                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                    NV_TL(2, un);
                 }
+                n += s.nt;
             })
 #undef TASK_BEGIN
 #undef TASK_END
@@ -380,8 +395,9 @@ __device__ __forceinline__ void gemv_fp4_body(const Params& p) {
                     uint32_t accumulate = 0;
                     // shared segment: the units of this issuer's parity (launch-wide numbers); own segment: all
                     for (int t = alone ? 0 : ((n0 + me) & 1); t < nt; t += alone ? 1 : 2) {
-                        const int n = n0 + t, st_now = n % kStages;
-                        const uint32_t ph_now = (uint32_t)(n / kStages) & 1u;
+                        const int n = n0 + t, st_now = me * F::kRing + (int)(mine % F::kRing);  // ring `me`, its units in order
+                        const uint32_t ph_now = (mine / F::kRing) & 1u;
+                        (void)n;
                         NV_TL(3, n);
                         if (!mbar_wait(&full[st_now], ph_now, abortp, wait_ns)) { ok = false; break; }
                         NV_TL(4, n);
@@ -478,7 +494,7 @@ __device__ __forceinline__ void gemv_fp4_body(const Params& p) {
         })
 #undef TASK_BEGIN
 #undef TASK_END
-    } else if (warp == 6 || warp >= 8) {
+    } else if (warp == 6 || (warp >= 8 && warp <= 10)) {
         // ------------------------------------------------------------ scale warps: a segment's activation scale bytes,
         // route coefficients, tensor scale and unit count, up to four segments ahead.  A segment costs its warp a
         // memory round trip (1 - 2 us under load), more than the MMAs of a short segment (a down projection of 384
