@@ -492,7 +492,7 @@ class GqaLayerWorkload(LayerWorkload):
     experts top-8 of intermediate 1536 in MXFP4, sigmoid router), 16 verify rows, one rank's share of
     TP 4 (or TP = number of GPUs)."""
 
-    kernel = "gemv_tc4bs_kernel (tcgen05 kind::mxf8f6f4.block_scale MXFP4 expert up/gate, timed as its own launch)"
+    kernel = "gemv_mxf4_kernel (tcgen05 kind::mxf8f6f4.block_scale MXFP4 expert up/gate, nibbles padded by TMA, timed as its own launch)"
     traffic_key = "mxfp4_expert_up_gate"
 
     def __init__(self, rows=16, ctx=65536, expert_fmt="mxfp4"):
