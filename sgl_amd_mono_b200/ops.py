@@ -128,7 +128,7 @@ def plan_split(k_tiles: int, row_blocks: int, wkind: int, sms: int | None = None
 
 
 def tile_nvfp4_scales(ws: torch.Tensor) -> torch.Tensor:
-    """NVFP4 scale bytes [mats, rows, K/16] -> [mats, row blocks, tiles * 2048] in the order ``mono_gemv_job.wscale_tiled``
+    """NVFP4 scale bytes [mats, rows, K/16] -> [mats, row blocks, tiles * 2048] in the order ``mono_gemv_job.wscale_t``
     describes: per (128-row block, 256-value tile) four 512-byte pieces (one per 64-value MMA), byte
     ``(r % 32) * 16 + (r // 32) * 4 + b`` of a piece = row ``r`` of the block, 16-value block ``b`` of the MMA.
     Rows and tiles are padded with 0x38 (1.0)."""
