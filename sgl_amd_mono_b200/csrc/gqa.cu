@@ -85,26 +85,33 @@ __global__ void __launch_bounds__(kGqaBlock * kScoreBlocksPerCta) gqa_score_kern
     const int row = blockIdx.x / groups, tid = threadIdx.x;
     const int sub = tid >> 6, key = tid & 63;
     const int b = (blockIdx.x - row * groups) * kScoreBlocksPerCta + sub;
-    if (a.slots && a.slots[row] < 0) return;
+    // The slot, the position and the page number are asked for together, and the block's keys as soon as the page
+    // number is known: two memory round trips before the arithmetic instead of four (the query is staged while the
+    // keys are in flight).  Every load is unconditional, from a clamped address.
+    const int slot_v = a.slots ? (int)a.slots[row] : 0;
     const int seq = (int)a.positions[row] + 1;
+    const int b_ld = min(b, a.score_ld - 1);
+    const int page_raw = a.page_table[(size_t)row * a.pt_ld + b_ld];
+    const __nv_bfloat16* iq = reinterpret_cast<const __nv_bfloat16*>(a.iq_out) + (size_t)row * kGqaDim;
+    const float qv_stage = tid < kGqaDim ? __bfloat162float(iq[tid]) : 0.f;
+    const int lane = tid & 31, chunk = lane & 7, half = (tid >> 5) & 1;
+    const bool page_ok = page_raw >= 0 && page_raw < a.n_pages;
+    const uint8_t* base = a.index_cache + (size_t)(page_ok ? page_raw : 0) * kGqaBlock * kGqaDim;
+    uint4 w[8];
+#pragma unroll
+    for (int it = 0; it < 8; ++it)
+        w[it] = *reinterpret_cast<const uint4*>(base + (size_t)(half * 32 + it * 4 + (lane >> 3)) * kGqaDim + chunk * 16);
+    if (slot_v < 0) return;
     const int n_blk = (seq + kGqaBlock - 1) / kGqaBlock;
     if ((b - sub) >= n_blk) return;  // the whole CTA is past the row's context
-    const __nv_bfloat16* iq = reinterpret_cast<const __nv_bfloat16*>(a.iq_out) + (size_t)row * kGqaDim;
-    if (tid < kGqaDim) q[tid] = __bfloat162float(iq[tid]);
+    if (tid < kGqaDim) q[tid] = qv_stage;
     __syncthreads();
     // eight lanes share a key row (16 bytes each: one coalesced 512-byte request covers four rows), so a warp
     // walks its 32 keys four at a time; the eight partial dots of a row meet in a 3-step butterfly
     float dot = -INFINITY;
     if (b < n_blk && b < a.score_ld) {
-        const int page = a.page_table[(size_t)row * a.pt_ld + b];
-        if (page >= 0 && page < a.n_pages) {
-            const int lane = tid & 31, chunk = lane & 7, half = (tid >> 5) & 1;
-            const uint8_t* base = a.index_cache + (size_t)page * kGqaBlock * kGqaDim;
+        if (page_ok) {
             const float4* q4 = reinterpret_cast<const float4*>(q) + chunk * 4;
-            uint4 w[8];
-#pragma unroll
-            for (int it = 0; it < 8; ++it)
-                w[it] = *reinterpret_cast<const uint4*>(base + (size_t)(half * 32 + it * 4 + (lane >> 3)) * kGqaDim + chunk * 16);
 #pragma unroll
             for (int it = 0; it < 8; ++it) {
                 const uint32_t ws[4] = {w[it].x, w[it].y, w[it].z, w[it].w};
@@ -261,25 +268,38 @@ __global__ void __launch_bounds__(kGqaDim, 4) gqa_split_kernel(const mono_gqa_ar
     }
     // q of the group
     const __nv_bfloat16* qg = reinterpret_cast<const __nv_bfloat16*>(a.q_out) + ((size_t)row * a.q_heads + kvh * G) * kGqaDim;
-    for (int g = 0; g < G; ++g) sm.q[g][tid] = __bfloat162float(qg[g * kGqaDim + tid]);
-    // K block: 64 keys x 128 bytes, rows kv_heads * 128 apart
+    // K and V blocks: 64 keys x 128 bytes each, rows kv_heads * 128 apart.  All of a thread's loads (four pieces of
+    // K, four of V, its q values) are issued before the first is used: one memory round trip after the page number's.
     {
+        constexpr int kPieces = kGqaBlock * 8 / kGqaDim;  // 16-byte pieces per thread and block
         const uint8_t* kb = a.k_cache + ((size_t)page * kGqaBlock * a.kv_heads + kvh) * kGqaDim;
-        for (int c = tid; c < kGqaBlock * 8; c += kGqaDim) {
-            const int key = c >> 3, piece = c & 7;
-            const uint4 w = *reinterpret_cast<const uint4*>(kb + (size_t)key * a.kv_heads * kGqaDim + piece * 16);
-            const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+        const uint8_t* vbase = a.v_cache + ((size_t)page * kGqaBlock * a.kv_heads + kvh) * kGqaDim;
+        uint4 kw[kPieces], vw[kPieces];
+        float qv[kGqaMaxGroup];
+#pragma unroll
+        for (int i = 0; i < kPieces; ++i) {
+            const int c = tid + i * kGqaDim, key = c >> 3, piece = c & 7;
+            kw[i] = *reinterpret_cast<const uint4*>(kb + (size_t)key * a.kv_heads * kGqaDim + piece * 16);
+        }
+#pragma unroll
+        for (int i = 0; i < kPieces; ++i) {
+            const int c = tid + i * kGqaDim, key = c >> 3, piece = c & 7;
+            vw[i] = *reinterpret_cast<const uint4*>(vbase + (size_t)key * a.kv_heads * kGqaDim + piece * 16);
+        }
+#pragma unroll
+        for (int g = 0; g < kGqaMaxGroup; ++g) qv[g] = __bfloat162float(qg[min(g, G - 1) * kGqaDim + tid]);
+#pragma unroll
+        for (int g = 0; g < kGqaMaxGroup; ++g)
+            if (g < G) sm.q[g][tid] = qv[g];
+#pragma unroll
+        for (int i = 0; i < kPieces; ++i) {
+            const int c = tid + i * kGqaDim, key = c >> 3, piece = c & 7;
+            const uint32_t ws[4] = {kw[i].x, kw[i].y, kw[i].z, kw[i].w};
 #pragma unroll
             for (int j = 0; j < 4; ++j)
 #pragma unroll
                 for (int k = 0; k < 4; ++k) sm.k[key][piece * 16 + j * 4 + k] = e4m3_to_f32((ws[j] >> (8 * k)) & 0xFF);
-        }
-        // V block: the same rows of the V cache, kept as bytes (every 16-byte load is in flight before the scores)
-        const uint8_t* vbase = a.v_cache + ((size_t)page * kGqaBlock * a.kv_heads + kvh) * kGqaDim;
-        for (int c = tid; c < kGqaBlock * 8; c += kGqaDim) {
-            const int key = c >> 3, piece = c & 7;
-            *reinterpret_cast<uint4*>(&sm.v[key][piece * 16]) =
-                *reinterpret_cast<const uint4*>(vbase + (size_t)key * a.kv_heads * kGqaDim + piece * 16);
+            *reinterpret_cast<uint4*>(&sm.v[key][piece * 16]) = vw[i];  // V stays bytes
         }
     }
     __syncthreads();
@@ -381,8 +401,8 @@ extern "C" int mono_gqa_front_launch(const mono_gqa_args* a, void* stream) {
 
 extern "C" int mono_gqa_score_launch(const mono_gqa_args* a, void* stream) {
     if (int rc = gqa_check(a, "mono_gqa_score_launch")) return rc;
-    if (!a->iq_out || !a->index_cache || !a->page_table || !a->scores || a->score_ld < 1 || a->score_ld > a->pt_ld) {
-        mono_set_error("mono_gqa_score_launch: index q, index cache, page table and a score buffer of at most pt_ld blocks required");
+    if (!a->iq_out || !a->index_cache || !a->page_table || !a->scores || a->score_ld < 1 || a->score_ld > a->pt_ld || a->n_pages < 1) {
+        mono_set_error("mono_gqa_score_launch: index q, an index cache of at least one page, page table and a score buffer of at most pt_ld blocks required");
         return MONO_E_ARG;
     }
     // fp32(fp32(sm_scale) * fp32(log2 e)) as index_score.py:59-62
