@@ -351,17 +351,24 @@ __global__ void __launch_bounds__(kGqaDim, 4) gqa_merge_kernel(const mono_gqa_ar
     const int G = a.q_heads / a.kv_heads, kvh = h / G, g = h - kvh * G;
     const float* part = a.scratch + (size_t)(row * a.kv_heads + kvh) * kGqaTopk * G * (kGqaDim + 2) + g * (kGqaDim + 2);
     const size_t stride = (size_t)G * (kGqaDim + 2);
-    float m[kGqaTopk], M = -INFINITY;
+    // every load of the merge is issued before the first is used (a load under a condition waits for the condition:
+    // sixteen round trips); a dead split's sum and values are replaced by zeros, which add nothing
+    float m[kGqaTopk], l[kGqaTopk], v[kGqaTopk], M = -INFINITY;
 #pragma unroll
-    for (int j = 0; j < kGqaTopk; ++j) { m[j] = part[j * stride]; M = fmaxf(M, m[j]); }
+    for (int j = 0; j < kGqaTopk; ++j) {
+        m[j] = part[j * stride];
+        l[j] = part[j * stride + 1];
+        v[j] = part[j * stride + 2 + tid];
+    }
+#pragma unroll
+    for (int j = 0; j < kGqaTopk; ++j) M = fmaxf(M, m[j]);
     float num = 0.f, den = 0.f;
 #pragma unroll
     for (int j = 0; j < kGqaTopk; ++j) {
-        if (m[j] > -INFINITY) {
-            const float w = expf(m[j] - M);
-            num += part[j * stride + 2 + tid] * w;
-            den += part[j * stride + 1] * w;
-        }
+        const bool live = m[j] > -INFINITY;
+        const float w = live ? expf(m[j] - M) : 0.f;
+        num += (live ? v[j] : 0.f) * w;
+        den += (live ? l[j] : 0.f) * w;
     }
     const float o = den > 0.f ? num / den * a.v_scale : 0.f;
     reinterpret_cast<__nv_bfloat16*>(a.out)[((size_t)row * a.q_heads + h) * kGqaDim + tid] = __float2bfloat16_rn(o);
