@@ -2,6 +2,11 @@
 
 Each helper cites the reference lines whose rule it follows (paths are relative to
 the reference project).  All functions take and return torch CPU tensors.
+
+The NVFP4 helpers (``nvfp4_*``) have no reference lines to follow: the reference leaves
+that format's arithmetic to SGLang's MoE runner (minimax_m31/spec.py:117-121).  They
+restate the published format and are checked against its value tables only: parity
+unpinned against any reference output.
 """
 
 from __future__ import annotations
